@@ -1,0 +1,111 @@
+"""Build and load the C-ABI shared library (``libbrokefish_b200.so``).
+
+The library is built in-tree with one ``nvcc`` line for sm_100a; there is no JIT cache
+and no fallback: if the library is missing or does not load, every entry point of the
+package that needs the GPU raises.
+"""
+
+from __future__ import annotations
+
+import ctypes
+import os
+import shutil
+import subprocess
+from typing import List, Optional
+
+PKG_DIR = os.path.dirname(os.path.abspath(__file__))
+ROOT = os.path.dirname(PKG_DIR)
+LIB_PATH = os.path.join(PKG_DIR, "libbrokefish_b200.so")
+SOURCES = [os.path.join(PKG_DIR, "csrc", "bf_encoder.cu")]
+DEPS = SOURCES + [os.path.join(PKG_DIR, "csrc", "bf_ptx.cuh"),
+                  os.path.join(ROOT, "include", "brokefish_b200.h")]
+NVCC_FLAGS = ["-gencode", "arch=compute_100a,code=sm_100a", "-O3", "-lineinfo", "-std=c++17",
+              "-Xcompiler", "-fPIC", "-shared", "-diag-suppress", "177,550"]
+
+#: Every symbol ``include/brokefish_b200.h`` declares.
+EXPORTS = ["bf_version", "bf_last_error", "bf_create", "bf_destroy", "bf_info", "bf_forward",
+           "bf_forward_stage", "bf_forward_capture", "bf_forward_host", "bf_status",
+           "bf_launch_count", "bf_selftest_umma"]
+
+
+def nvcc_path() -> str:
+    cand = os.environ.get("BROKEFISH_NVCC") or shutil.which("nvcc") or "/usr/local/cuda/bin/nvcc"
+    if not os.path.exists(cand):
+        raise RuntimeError("nvcc not found; set BROKEFISH_NVCC")
+    return cand
+
+
+def is_stale() -> bool:
+    if not os.path.exists(LIB_PATH):
+        return True
+    built = os.path.getmtime(LIB_PATH)
+    return any(os.path.getmtime(p) > built for p in DEPS)
+
+
+def build(force: bool = False, verbose: bool = False, extra: Optional[List[str]] = None) -> str:
+    """Compile the library if it is missing or older than its sources."""
+    if not force and not is_stale():
+        return LIB_PATH
+    cmd = [nvcc_path()] + NVCC_FLAGS + (extra or []) + ["-o", LIB_PATH] + SOURCES
+    res = subprocess.run(cmd, capture_output=True, text=True)
+    if verbose or res.returncode != 0:
+        print(" ".join(cmd))
+        print(res.stdout)
+        print(res.stderr)
+    if res.returncode != 0:
+        raise RuntimeError(f"nvcc failed with code {res.returncode}:\n{res.stderr[-4000:]}")
+    return LIB_PATH
+
+
+_LIB = None
+
+
+def lib() -> ctypes.CDLL:
+    """The loaded library with argument types declared.  Raises if it is not built."""
+    global _LIB
+    if _LIB is not None:
+        return _LIB
+    if not os.path.exists(LIB_PATH):
+        raise RuntimeError(
+            f"{LIB_PATH} is not built; run `python -c 'import __graft_entry__ as g; g.build()'` "
+            "(there is no CPU or PyTorch fallback for the evaluator)")
+    L = ctypes.CDLL(LIB_PATH)
+    vp, i32, sz = ctypes.c_void_p, ctypes.c_int, ctypes.c_size_t
+    L.bf_version.restype = ctypes.c_char_p
+    L.bf_last_error.restype = ctypes.c_char_p
+    L.bf_create.argtypes = [vp, sz, i32, ctypes.POINTER(vp)]
+    L.bf_destroy.argtypes = [vp]
+    L.bf_info.argtypes = [vp, ctypes.POINTER(i32), ctypes.POINTER(i32), ctypes.POINTER(i32)]
+    L.bf_forward.argtypes = [vp, vp, vp, vp, vp, i32, vp, vp, vp, vp]
+    L.bf_forward_stage.argtypes = [vp, vp, vp, vp, i32, i32, vp, vp]
+    L.bf_forward_capture.argtypes = [vp, vp, vp, vp, i32, i32, i32, vp, vp, vp]
+    L.bf_forward_host.argtypes = [vp, vp, vp, vp, vp, i32, vp, vp, vp]
+    L.bf_status.argtypes = [vp, ctypes.POINTER(i32)]
+    L.bf_launch_count.argtypes = [vp]
+    L.bf_launch_count.restype = ctypes.c_longlong
+    L.bf_selftest_umma.argtypes = [i32, i32, vp, vp, vp]
+    for name in EXPORTS:
+        fn = getattr(L, name)
+        if fn.restype is ctypes.c_int or name in ("bf_create", "bf_destroy", "bf_info", "bf_forward",
+                                                   "bf_forward_stage", "bf_forward_capture",
+                                                   "bf_forward_host", "bf_status",
+                                                   "bf_selftest_umma"):
+            fn.restype = ctypes.c_int
+    _LIB = L
+    return L
+
+
+class NativeError(RuntimeError):
+    pass
+
+
+def check(rc: int, what: str) -> None:
+    """Turn a negative return code into an exception carrying ``bf_last_error()``."""
+    if rc == 0:
+        return
+    msg = lib().bf_last_error().decode("utf-8", "replace")
+    if rc == -1:
+        raise ValueError(f"{what}: {msg}")
+    if rc == -3:
+        raise NotImplementedError(f"{what}: {msg}")
+    raise NativeError(f"{what} failed ({rc}): {msg}")

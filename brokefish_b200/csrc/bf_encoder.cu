@@ -1,0 +1,1252 @@
+// The one-launch quantised transformer-encoder evaluator for sm_100a, and its C ABI.
+//
+// What one launch computes (per position): embedding of 32 piece words, 8 pre-norm
+// encoder layers of width 256 (8 heads of 32, FFN 1024) with every weight GEMM in
+// s8/u8 x s8 -> s32 on the tcgen05 tensor cores, a final LayerNorm, and the fp16 head
+// GEMM giving 32x64 policy logits, 32x4 promotion logits and the value.  It follows the
+// arithmetic of the reference kernel (csrc/encoder.cu:1225-1599 with int8_gemm.cuh) at
+// every rounding point that can be reproduced exactly; the places where it differs
+// (fp32 instead of fp16 accumulation in attention and heads, correctly rounded 1/sqrt)
+// are listed beside the code.
+//
+// Shape of the kernel
+//   * persistent grid, one CTA per SM, each CTA loops over tiles of 128 token rows
+//     (4 boards);
+//   * 10 warps: 8 "row" warps, one weight-stream producer, one MMA issuer;
+//   * row warps: thread = (row, half).  Warp w works on TMEM lanes 32*(w%4)..+31, i.e.
+//     on board w%4 of the tile; warps w and w+4 split each row's columns.  All
+//     LayerNorm / quantise / descale work is thread-local plus one exchange between the
+//     two halves; the two warps of a board synchronise with a 64-thread named barrier;
+//   * weights never sit in shared memory for longer than one use: the host packs them
+//     as ready-made 128-byte-swizzled K-major stage images and the producer streams
+//     them through a ring with cp.async.bulk + mbarrier;
+//   * accumulators live in tensor memory: columns [0,128) hold the fp16 residual
+//     stream x (two halves per column), [128,256) the attention output / the FFN's fp16
+//     running total, [256,512) the GEMM accumulators.
+#include <cuda_fp16.h>
+#include <cuda_runtime.h>
+#include <stdint.h>
+#include <stdio.h>
+#include <string.h>
+
+#include <new>
+#include <string>
+
+#include "../../include/brokefish_b200.h"
+#include "bf_ptx.cuh"
+
+namespace bf {
+using namespace bfptx;
+
+constexpr int kD = 256, kDFF = 1024, kT = 32, kRows = 128;
+constexpr int kRowWarps = 8, kProducerWarp = 8, kMmaWarp = 9, kThreads = 320;
+constexpr int kLayerStreamBytes = 786432, kLparamStride = 4736;
+constexpr int LP_SW_QKV = 0, LP_SW_O = 24, LP_SW_FF1 = 32, LP_SW_FF2 = 64;
+constexpr int LP_B_QKV = 128, LP_B_O = 1664, LP_B_FF1 = 2176, LP_B_FF2 = 4224;
+constexpr int EMB_SQUARE = 0, EMB_TS = 64, EMB_CT = 76, EMB_CLOCK = 80, EMB_REP = 181;
+constexpr int kNClock = 101, kNRep = 3, kNTypeSpecial = 12;
+
+// ---- shared memory map (offsets from a 1024-byte aligned base) ----------------------
+constexpr uint32_t SM_A = 0;            // s8 A operand, 2 K-slabs of [128 rows][128 B]
+constexpr uint32_t SM_R = 32768;        // 64 KB: Q/K/V staging (3 x 16 KB) | hidden u8
+                                        // A operand x2 (2 x 32 KB) | fp16 head A (4 x 16 KB)
+constexpr uint32_t SM_RING = 98304;     // 112 KB weight ring: 4 x 24 KB or 7 x 16 KB
+constexpr uint32_t SM_XCH = 212992;     // 8 KB: float4 [2 parity][2 half][128 rows]
+constexpr uint32_t SM_BAR = 221184;     // mbarriers
+constexpr uint32_t SM_MISC = SM_BAR + 256;
+constexpr uint32_t SM_BYTES = SM_MISC + 64;
+constexpr uint32_t kSmemRequest = SM_BYTES + 1024;
+constexpr int kQSlots = 4, kRSlots = 7;
+constexpr uint32_t kQStage = 24576, kRStage = 16384, kHeadStage = 12288;
+// barrier indices
+constexpr int B_WQ_FULL = 0, B_WQ_EMPTY = 4, B_WR_FULL = 8, B_WR_EMPTY = 15, B_ACC_FULL = 22,
+              B_ACC_EMPTY = 24, B_A_READY = 26, B_A2_READY = 27, B_COUNT = 29;
+// ---- tensor memory map (columns) ---------------------------------------------------------
+constexpr uint32_t TM_X = 0, TM_OY = 128, TM_ACC = 256, TM_COLS = 512;
+
+// time-out codes written to the status word (which wait gave up)
+enum { kErrProducer = 1, kErrMmaOperand = 2, kErrMmaWeights = 3, kErrMmaAcc = 4, kErrRowAcc = 5 };
+
+struct Params {
+    const uint16_t* boards;
+    const int16_t* control;
+    const uint8_t* rep;
+    const uint64_t* legal;
+    int n, n_layers, n_value, vmode;
+    float eps;
+    const uint8_t* wstream;
+    const uint8_t* lparams;
+    const __half* emb;
+    const __half* tail;
+    __half* policy;
+    __half* promo;
+    float* value;
+    __half* y;
+    int debug_stage;
+    int cap_layer, cap_op;
+    uint8_t* cap_a;
+    int32_t* cap_acc;
+    int* status;
+};
+
+// Per-thread context of a row warp.
+struct RowCtx {
+    int lane, q, hf, row;       // q: board within the tile, hf: which half of the columns
+    uint32_t smem;              // shared base (shared-space address)
+    uint8_t* smem_gen;          // shared base (generic pointer)
+    uint32_t tm;                // TMEM base address with this warp's lane offset
+    volatile int* abort_flag;
+    int xpar;                   // exchange buffer parity
+    uint32_t full_cnt[2];       // accumulator slots consumed so far
+    long grow;                  // global token row = board * 32 + token
+    bool valid;                 // board < n
+};
+
+__device__ __forceinline__ uint32_t bar_addr(uint32_t smem, int idx) {
+    return smem + SM_BAR + 8u * idx;
+}
+
+// Exchange one float4 with the thread that owns the other half of this row.
+__device__ __forceinline__ float4 exchange(RowCtx& c, float4 mine) {
+    float4* xch = reinterpret_cast<float4*>(c.smem_gen + SM_XCH);
+    xch[(c.xpar * 2 + c.hf) * kRows + c.row] = mine;
+    named_bar_sync(1 + c.q, 64);
+    const float4 other = xch[(c.xpar * 2 + (c.hf ^ 1)) * kRows + c.row];
+    c.xpar ^= 1;
+    return other;
+}
+
+__device__ __forceinline__ void row_wait_acc(RowCtx& c, int slot) {
+    mbar_wait(bar_addr(c.smem, B_ACC_FULL + slot), c.full_cnt[slot] & 1, c.abort_flag, kErrRowAcc);
+    c.full_cnt[slot]++;
+    tc_fence_after();
+}
+// All of this warp's TMEM loads of the slot are done: hand it back to the MMA issuer.
+__device__ __forceinline__ void row_release_acc(RowCtx& c, int slot) {
+    tmem_wait_ld();
+    tc_fence_before();
+    __syncwarp();
+    if (c.lane == 0) mbar_arrive(bar_addr(c.smem, B_ACC_EMPTY + slot));
+}
+// This warp's generic-proxy writes of an MMA operand are done: publish to the issuer.
+__device__ __forceinline__ void row_publish(RowCtx& c, int bar_idx) {
+    fence_proxy_async_smem();
+    __syncwarp();
+    if (c.lane == 0) mbar_arrive(bar_addr(c.smem, bar_idx));
+}
+
+// Round-half-even float -> 8-bit integer in the low byte (two's complement for
+// negatives): adding 1.5 * 2^23 leaves the integer in the low mantissa bits.  Same
+// result as `cvt.rni.sat` for |v| <= 255 (int8_gemm.cuh:190-199 guarantees the range).
+__device__ __forceinline__ uint32_t q8(float x, float inv) {
+    return __float_as_uint(__fadd_rn(__fmul_rn(x, inv), 12582912.0f));
+}
+__device__ __forceinline__ uint32_t pack4(uint32_t a, uint32_t b, uint32_t c, uint32_t d) {
+    return __byte_perm(__byte_perm(a, b, 0x0040), __byte_perm(c, d, 0x0040), 0x5410);
+}
+// 8 packed fp16 pairs (16 values) -> 16 quantised bytes.
+__device__ __forceinline__ uint4 quant16(const uint32_t* h, float inv) {
+    uint32_t o[4];
+#pragma unroll
+    for (int k = 0; k < 4; ++k) {
+        const float2 a = __half22float2(as_h2(h[2 * k]));
+        const float2 b = __half22float2(as_h2(h[2 * k + 1]));
+        o[k] = pack4(q8(a.x, inv), q8(a.y, inv), q8(b.x, inv), q8(b.y, inv));
+    }
+    return make_uint4(o[0], o[1], o[2], o[3]);
+}
+// Address of 16-byte group `chunk` of row `row` in a [rows][128 B] swizzled tile.
+__device__ __forceinline__ uint32_t sw_off(int row, int chunk) {
+    return static_cast<uint32_t>(row) * 128u + (static_cast<uint32_t>(chunk ^ (row & 7)) << 4);
+}
+
+// `(float(acc) * sa) * sw` -> fp16, + fp16 bias, optional ReLU; 32 columns -> 16 pairs
+// (int8_gemm.cuh:276-297, encoder.cu:631-644, 1482-1489).
+template <bool kRelu>
+__device__ __forceinline__ void descale32(const uint32_t (&acc)[32], float sa, float sw,
+                                          const __half* bias, uint32_t* out) {
+    const uint4* b4 = reinterpret_cast<const uint4*>(bias);
+#pragma unroll
+    for (int v = 0; v < 4; ++v) {
+        const uint4 bv = __ldg(b4 + v);
+        const uint32_t bw[4] = {bv.x, bv.y, bv.z, bv.w};
+#pragma unroll
+        for (int k = 0; k < 4; ++k) {
+            const int i = 4 * v + k;
+            const float f0 = __fmul_rn(__fmul_rn(static_cast<float>(static_cast<int>(acc[2 * i])), sa), sw);
+            const float f1 = __fmul_rn(__fmul_rn(static_cast<float>(static_cast<int>(acc[2 * i + 1])), sa), sw);
+            __half2 h = __hadd2(__floats2half2_rn(f0, f1), as_h2(bw[k]));
+            if (kRelu) h = __hmax2(h, __float2half2_rn(0.0f));
+            out[i] = as_u32(h);
+        }
+    }
+}
+
+__device__ __forceinline__ float amax16(const uint32_t* h, int n, bool take_abs) {
+    __half2 m = __float2half2_rn(0.0f);
+#pragma unroll
+    for (int i = 0; i < n; ++i) {
+        const __half2 v = as_h2(h[i]);
+        m = __hmax2(m, take_abs ? __habs2(v) : v);
+    }
+    return fmaxf(__low2float(m), __high2float(m));
+}
+
+// Debug/capture stores -------------------------------------------------------------------
+// 64 packed pairs of this thread (columns 64*hf + [0,64) and 128 + 64*hf + [0,64)).
+__device__ __forceinline__ void dump_row64(const RowCtx& c, __half* y, const uint32_t* xr) {
+    if (!c.valid) return;
+#pragma unroll
+    for (int g = 0; g < 2; ++g) {
+        uint4* dst = reinterpret_cast<uint4*>(y + c.grow * kD + 128 * g + 64 * c.hf);
+#pragma unroll
+        for (int k = 0; k < 8; ++k)
+            dst[k] = make_uint4(xr[32 * g + 4 * k], xr[32 * g + 4 * k + 1], xr[32 * g + 4 * k + 2],
+                                xr[32 * g + 4 * k + 3]);
+    }
+}
+
+// LayerNorm statistics of a row whose halves are held by two threads (64 pairs each).
+// Summation order (mirrored by the CPU oracle): even and odd columns accumulate
+// separately and sequentially, then even + odd, then the two halves.  One-pass variance
+// clamped at zero as in encoder.cu:584-598; 1/sqrt is correctly rounded here where the
+// reference uses the hardware approximation.
+__device__ __forceinline__ void ln_stats(RowCtx& c, const uint32_t (&xr)[64], float eps,
+                                         float& mean, float& rstd) {
+    float s_lo = 0.f, s_hi = 0.f, q_lo = 0.f, q_hi = 0.f;
+#pragma unroll
+    for (int i = 0; i < 64; ++i) {
+        const float2 f = __half22float2(as_h2(xr[i]));
+        s_lo = __fadd_rn(s_lo, f.x);
+        s_hi = __fadd_rn(s_hi, f.y);
+        q_lo = __fmaf_rn(f.x, f.x, q_lo);
+        q_hi = __fmaf_rn(f.y, f.y, q_hi);
+    }
+    const float s = __fadd_rn(s_lo, s_hi), qq = __fadd_rn(q_lo, q_hi);
+    const float4 o = exchange(c, make_float4(s, qq, 0.f, 0.f));
+    const float tot = __fadd_rn(s, o.x), totq = __fadd_rn(qq, o.y);
+    mean = __fmul_rn(tot, 1.0f / 256.0f);
+    const float var = fmaxf(__fmaf_rn(-mean, mean, __fmul_rn(totq, 1.0f / 256.0f)), 0.f);
+    rstd = __frsqrt_rn(__fadd_rn(var, eps));
+}
+
+// x (64 pairs) -> x_hat = fp16((x - mean) * rstd) in place.
+__device__ __forceinline__ void ln_apply(uint32_t (&xr)[64], float mean, float rstd) {
+#pragma unroll
+    for (int i = 0; i < 64; ++i) {
+        const float2 f = __half22float2(as_h2(xr[i]));
+        xr[i] = pack_h2(__fmul_rn(__fsub_rn(f.x, mean), rstd), __fmul_rn(__fsub_rn(f.y, mean), rstd));
+    }
+}
+
+// Per-row symmetric s8 quantisation of x_hat into the A operand (both K-slabs), scale
+// `amax/127`, all-zero row -> 1 (int8_gemm.cuh:159-199).  Returns the row scale.
+__device__ __forceinline__ float quantise_to_a(RowCtx& c, const Params& p, const uint32_t (&xr)[64],
+                                               bool capture) {
+    const float mine = amax16(xr, 64, true);
+    const float4 o = exchange(c, make_float4(mine, 0.f, 0.f, 0.f));
+    const float amax = fmaxf(mine, o.x);
+    const float sc = amax > 0.f ? __fdiv_rn(amax, 127.0f) : 1.0f;
+    const float inv = __fdiv_rn(1.0f, sc);
+#pragma unroll
+    for (int g = 0; g < 2; ++g) {
+#pragma unroll
+        for (int k = 0; k < 4; ++k) {
+            const uint4 v = quant16(&xr[32 * g + 8 * k], inv);
+            *reinterpret_cast<uint4*>(c.smem_gen + SM_A + g * 16384 + sw_off(c.row, 4 * c.hf + k)) = v;
+            if (capture && c.valid)
+                *reinterpret_cast<uint4*>(p.cap_a + c.grow * kD + 128 * g + 64 * c.hf + 16 * k) = v;
+        }
+    }
+    return sc;
+}
+
+// One (board, head) attention unit on the staged fp16 Q/K/V of a head pair: S = Q K^T
+// (scale pre-folded), dead keys -inf, fp32 softmax with __expf, P rounded to fp16,
+// O = P V; both products accumulate in fp32 where the reference accumulates in fp16
+// (encoder.cu:715-797).  The result overwrites this unit's own Q block.
+__device__ __forceinline__ void attention_unit(const RowCtx& c, uint32_t alive) {
+    const uint32_t qs = c.smem + SM_R, ks = qs + 16384, vs = qs + 32768;
+    const int r0 = 32 * c.q, lane = c.lane, g = lane >> 2, t = lane & 3;
+    uint32_t qa[2][2][4];
+#pragma unroll
+    for (int mt = 0; mt < 2; ++mt)
+#pragma unroll
+        for (int kk = 0; kk < 2; ++kk) {
+            const int row = r0 + 16 * mt + (lane & 15);
+            ldmatrix_x4(qa[mt][kk], qs + sw_off(row, 4 * c.hf + 2 * kk + (lane >> 4)));
+        }
+    float s[2][4][4];
+#pragma unroll
+    for (int mt = 0; mt < 2; ++mt)
+#pragma unroll
+        for (int nt = 0; nt < 4; ++nt)
+#pragma unroll
+            for (int k = 0; k < 4; ++k) s[mt][nt][k] = 0.f;
+#pragma unroll
+    for (int nt = 0; nt < 4; ++nt) {
+        uint32_t kb[4];
+        const int row = r0 + 8 * nt + (lane & 7);
+        ldmatrix_x4(kb, ks + sw_off(row, 4 * c.hf + (lane >> 3)));
+#pragma unroll
+        for (int mt = 0; mt < 2; ++mt) {
+            mma_f16_f32(s[mt][nt], qa[mt][0], kb[0], kb[1]);
+            mma_f16_f32(s[mt][nt], qa[mt][1], kb[2], kb[3]);
+        }
+    }
+    uint32_t pa[2][2][4];
+#pragma unroll
+    for (int mt = 0; mt < 2; ++mt)
+#pragma unroll
+        for (int hi = 0; hi < 2; ++hi) {
+            float mx = -INFINITY;
+#pragma unroll
+            for (int nt = 0; nt < 4; ++nt)
+#pragma unroll
+                for (int k = 0; k < 2; ++k) {
+                    const int key = 8 * nt + 2 * t + k;
+                    float& v = s[mt][nt][2 * hi + k];
+                    v = ((alive >> key) & 1u) ? v : -INFINITY;
+                    mx = fmaxf(mx, v);
+                }
+            mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 1));
+            mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 2));
+            float sum = 0.f;
+#pragma unroll
+            for (int nt = 0; nt < 4; ++nt)
+#pragma unroll
+                for (int k = 0; k < 2; ++k) {
+                    float& v = s[mt][nt][2 * hi + k];
+                    v = __expf(v - mx);
+                    sum += v;
+                }
+            sum += __shfl_xor_sync(0xffffffffu, sum, 1);
+            sum += __shfl_xor_sync(0xffffffffu, sum, 2);
+            const float inv = 1.0f / sum;
+#pragma unroll
+            for (int kk = 0; kk < 2; ++kk) {
+                pa[mt][kk][hi] = pack_h2(s[mt][2 * kk][2 * hi] * inv, s[mt][2 * kk][2 * hi + 1] * inv);
+                pa[mt][kk][2 + hi] =
+                    pack_h2(s[mt][2 * kk + 1][2 * hi] * inv, s[mt][2 * kk + 1][2 * hi + 1] * inv);
+            }
+        }
+    float o[2][4][4];
+#pragma unroll
+    for (int mt = 0; mt < 2; ++mt)
+#pragma unroll
+        for (int nt = 0; nt < 4; ++nt)
+#pragma unroll
+            for (int k = 0; k < 4; ++k) o[mt][nt][k] = 0.f;
+#pragma unroll
+    for (int nt = 0; nt < 4; ++nt) {
+        uint32_t vb[4];
+        const int row = r0 + lane;
+        ldmatrix_x4_trans(vb, vs + sw_off(row, 4 * c.hf + nt));
+#pragma unroll
+        for (int mt = 0; mt < 2; ++mt) {
+            mma_f16_f32(o[mt][nt], pa[mt][0], vb[0], vb[1]);
+            mma_f16_f32(o[mt][nt], pa[mt][1], vb[2], vb[3]);
+        }
+    }
+    __syncwarp();   // every lane's Q fragments are in registers before Q is overwritten
+#pragma unroll
+    for (int mt = 0; mt < 2; ++mt)
+#pragma unroll
+        for (int nt = 0; nt < 4; ++nt) {
+            const int row = r0 + 16 * mt + g;
+            *reinterpret_cast<uint32_t*>(c.smem_gen + SM_R + sw_off(row, 4 * c.hf + nt) + 4 * t) =
+                pack_h2(o[mt][nt][0], o[mt][nt][1]);
+            *reinterpret_cast<uint32_t*>(c.smem_gen + SM_R + sw_off(row + 8, 4 * c.hf + nt) + 4 * t) =
+                pack_h2(o[mt][nt][2], o[mt][nt][3]);
+        }
+    __syncwarp();
+}
+
+// ------------------------------------------------------------------------------------------
+// Row-warp work for one tile.
+// ------------------------------------------------------------------------------------------
+__device__ __forceinline__ void row_warps_tile(RowCtx& c, const Params& p, int tile) {
+    const int board = tile * 4 + c.q;
+    c.valid = board < p.n;
+    c.grow = static_cast<long>(board) * kT + c.lane;
+    const uint32_t word = c.valid ? p.boards[c.grow] : 0u;
+    const uint32_t alive = __ballot_sync(0xffffffffu, ((word >> 11) & 1u) == 0u);
+    const int ctl = c.valid ? static_cast<int>(p.control[board]) : 1;
+    const int dbg = p.debug_stage;
+    uint32_t xr[64];
+
+    // ---- embedding: ((square + type_special) + color_turn) + (clock + rep), fp16
+    //      (encoder.cu:817-889; nn/model.py:383-397) ------------------------------------
+    {
+        const int stm = ctl < 0;
+        const int clk = min(max((ctl < 0 ? -ctl : ctl) - 1, 0), kNClock - 1);
+        const int rp = min(c.valid ? static_cast<int>(p.rep[board]) : 0, kNRep - 1);
+        const int sq = word & 63;
+        const int ts = min(static_cast<int>(((word >> 6) & 7) * 2 + ((word >> 9) & 1)), kNTypeSpecial - 1);
+        const int ct = ((word >> 10) & 1) * 2 + stm;
+#pragma unroll
+        for (int g = 0; g < 2; ++g) {
+            const int col = 128 * g + 64 * c.hf;
+            const uint4* e_sq = reinterpret_cast<const uint4*>(p.emb + (EMB_SQUARE + sq) * kD + col);
+            const uint4* e_ts = reinterpret_cast<const uint4*>(p.emb + (EMB_TS + ts) * kD + col);
+            const uint4* e_ct = reinterpret_cast<const uint4*>(p.emb + (EMB_CT + ct) * kD + col);
+            const uint4* e_ck = reinterpret_cast<const uint4*>(p.emb + (EMB_CLOCK + clk) * kD + col);
+            const uint4* e_rp = reinterpret_cast<const uint4*>(p.emb + (EMB_REP + rp) * kD + col);
+#pragma unroll
+            for (int k = 0; k < 8; ++k) {
+                const uint4 a = __ldg(e_sq + k), b = __ldg(e_ts + k), d = __ldg(e_ct + k);
+                const uint4 e = __ldg(e_ck + k), f = __ldg(e_rp + k);
+                const uint32_t aw[4] = {a.x, a.y, a.z, a.w}, bw[4] = {b.x, b.y, b.z, b.w};
+                const uint32_t dw[4] = {d.x, d.y, d.z, d.w}, ew[4] = {e.x, e.y, e.z, e.w};
+                const uint32_t fw[4] = {f.x, f.y, f.z, f.w};
+#pragma unroll
+                for (int j = 0; j < 4; ++j) {
+                    __half2 x = __hadd2(as_h2(aw[j]), as_h2(bw[j]));
+                    x = __hadd2(x, as_h2(dw[j]));
+                    x = __hadd2(x, __hadd2(as_h2(ew[j]), as_h2(fw[j])));
+                    xr[32 * g + 4 * k + j] = as_u32(x);
+                }
+            }
+        }
+#pragma unroll
+        for (int g = 0; g < 2; ++g)
+            tmem_st32(c.tm + TM_X + 64 * g + 32 * c.hf, *reinterpret_cast<uint32_t(*)[32]>(&xr[32 * g]));
+        tmem_wait_st();
+        if (dbg == 9) dump_row64(c, p.y, xr);
+    }
+
+    float sa;   // scale of the row currently in the A operand
+    {
+        float mean, rstd;
+        ln_stats(c, xr, p.eps, mean, rstd);
+        ln_apply(xr, mean, rstd);
+        if (dbg == 1) dump_row64(c, p.y, xr);
+        sa = quantise_to_a(c, p, xr, p.cap_layer == 0 && p.cap_op == BF_OP_QKV);
+        row_publish(c, B_A_READY);
+    }
+
+    for (int layer = 0; layer < p.n_layers; ++layer) {
+        const uint8_t* lp = p.lparams + static_cast<size_t>(layer) * kLparamStride;
+        const float* sw_qkv = reinterpret_cast<const float*>(lp + LP_SW_QKV);
+        const float* sw_o = reinterpret_cast<const float*>(lp + LP_SW_O);
+        const float* sw_ff1 = reinterpret_cast<const float*>(lp + LP_SW_FF1);
+        const float* sw_ff2 = reinterpret_cast<const float*>(lp + LP_SW_FF2);
+        const __half* b_qkv = reinterpret_cast<const __half*>(lp + LP_B_QKV);
+        const __half* b_o = reinterpret_cast<const __half*>(lp + LP_B_O);
+        const __half* b_ff1 = reinterpret_cast<const __half*>(lp + LP_B_FF1);
+        const __half* b_ff2 = reinterpret_cast<const __half*>(lp + LP_B_FF2);
+        const bool cap = layer == p.cap_layer;
+        const bool dbg0 = layer == 0;
+
+        // ---- QKV in four head-pair chunks, attention per chunk ----------------------
+        float o_amax = 0.f;
+#pragma unroll 1
+        for (int j = 0; j < 4; ++j) {
+            row_wait_acc(c, 0);
+#pragma unroll
+            for (int g = 0; g < 3; ++g) {
+                const int c0 = 96 * c.hf + 32 * g, m = c0 >> 6, cm = c0 & 63;
+                uint32_t acc[32], h[16];
+                tmem_ld32(c.tm + TM_ACC + c0, acc);
+                tmem_wait_ld();
+                if (cap && p.cap_op == BF_OP_QKV && c.valid) {
+                    int4* dst = reinterpret_cast<int4*>(p.cap_acc + c.grow * 768 + j * 192 + c0);
+#pragma unroll
+                    for (int k = 0; k < 8; ++k)
+                        dst[k] = make_int4(acc[4 * k], acc[4 * k + 1], acc[4 * k + 2], acc[4 * k + 3]);
+                }
+                descale32<false>(acc, sa, __ldg(sw_qkv + m * 2 + (j >> 1)), b_qkv + j * 192 + c0, h);
+#pragma unroll
+                for (int k = 0; k < 4; ++k)
+                    *reinterpret_cast<uint4*>(c.smem_gen + SM_R + m * 16384 + sw_off(c.row, (cm >> 3) + k)) =
+                        make_uint4(h[4 * k], h[4 * k + 1], h[4 * k + 2], h[4 * k + 3]);
+                if (dbg0 && dbg == 5 + m && c.valid) {
+                    uint4* dst = reinterpret_cast<uint4*>(p.y + c.grow * kD + 64 * j + cm);
+#pragma unroll
+                    for (int k = 0; k < 4; ++k)
+                        dst[k] = make_uint4(h[4 * k], h[4 * k + 1], h[4 * k + 2], h[4 * k + 3]);
+                }
+            }
+            row_release_acc(c, 0);
+            named_bar_sync(1 + c.q, 64);       // this board's Q/K/V rows are staged
+            attention_unit(c, c.valid ? alive : 0xffffffffu);
+            {
+                // read back this row's 32 outputs of head 2j+hf, park them in tensor memory
+                uint32_t oh[16];
+#pragma unroll
+                for (int k = 0; k < 4; ++k) {
+                    const uint4 v = *reinterpret_cast<const uint4*>(c.smem_gen + SM_R + sw_off(c.row, 4 * c.hf + k));
+                    oh[4 * k] = v.x; oh[4 * k + 1] = v.y; oh[4 * k + 2] = v.z; oh[4 * k + 3] = v.w;
+                }
+                o_amax = fmaxf(o_amax, amax16(oh, 16, true));
+                tmem_st16(c.tm + TM_OY + 16 * (2 * j + c.hf), oh);
+                if (dbg0 && dbg == 4 && c.valid) {
+                    uint4* dst = reinterpret_cast<uint4*>(p.y + c.grow * kD + 32 * (2 * j + c.hf));
+#pragma unroll
+                    for (int k = 0; k < 4; ++k)
+                        dst[k] = make_uint4(oh[4 * k], oh[4 * k + 1], oh[4 * k + 2], oh[4 * k + 3]);
+                }
+            }
+            named_bar_sync(1 + c.q, 64);       // staging may be overwritten by the next chunk
+        }
+        tmem_wait_st();
+
+        // ---- quantise the attention output into A (s8, per-row scale) ----------------
+        {
+            const float4 o = exchange(c, make_float4(o_amax, 0.f, 0.f, 0.f));
+            const float amax = fmaxf(o_amax, o.x);
+            sa = amax > 0.f ? __fdiv_rn(amax, 127.0f) : 1.0f;
+            const float inv = __fdiv_rn(1.0f, sa);
+            const bool capo = cap && p.cap_op == BF_OP_OUT && c.valid;
+#pragma unroll
+            for (int jj = 0; jj < 4; ++jj) {
+                const int hd = 2 * jj + c.hf;
+                uint32_t oh[16];
+                tmem_ld16(c.tm + TM_OY + 16 * hd, oh);
+                tmem_wait_ld();
+#pragma unroll
+                for (int k = 0; k < 2; ++k) {
+                    const uint4 v = quant16(&oh[8 * k], inv);
+                    *reinterpret_cast<uint4*>(c.smem_gen + SM_A + (hd >> 2) * 16384 +
+                                              sw_off(c.row, (hd & 3) * 2 + k)) = v;
+                    if (capo) *reinterpret_cast<uint4*>(p.cap_a + c.grow * kD + 32 * hd + 16 * k) = v;
+                }
+            }
+            row_publish(c, B_A_READY);
+        }
+
+        // ---- out-projection, residual, LN2, quantise ------------------------------------
+#pragma unroll
+        for (int u = 0; u < 2; ++u) {
+            row_wait_acc(c, u);
+#pragma unroll
+            for (int g = 0; g < 2; ++g) {
+                uint32_t acc[32], y[16], xo[16];
+                tmem_ld32(c.tm + TM_ACC + 128 * u + 64 * c.hf + 32 * g, acc);
+                tmem_ld16(c.tm + TM_X + 64 * u + 32 * c.hf + 16 * g, xo);
+                tmem_wait_ld();
+                if (cap && p.cap_op == BF_OP_OUT && c.valid) {
+                    int4* dst = reinterpret_cast<int4*>(p.cap_acc + c.grow * 256 + 128 * u + 64 * c.hf + 32 * g);
+#pragma unroll
+                    for (int k = 0; k < 8; ++k)
+                        dst[k] = make_int4(acc[4 * k], acc[4 * k + 1], acc[4 * k + 2], acc[4 * k + 3]);
+                }
+                descale32<false>(acc, sa, __ldg(sw_o + u), b_o + 128 * u + 64 * c.hf + 32 * g, y);
+#pragma unroll
+                for (int i = 0; i < 16; ++i)
+                    xr[32 * u + 16 * g + i] = as_u32(__hadd2(as_h2(xo[i]), as_h2(y[i])));
+            }
+            row_release_acc(c, u);
+            tmem_st32(c.tm + TM_X + 64 * u + 32 * c.hf, *reinterpret_cast<uint32_t(*)[32]>(&xr[32 * u]));
+        }
+        tmem_wait_st();
+        if (dbg0 && dbg == 2) dump_row64(c, p.y, xr);
+        {
+            float mean, rstd;
+            ln_stats(c, xr, p.eps, mean, rstd);
+            ln_apply(xr, mean, rstd);
+            if (dbg0 && dbg == 3) dump_row64(c, p.y, xr);
+            sa = quantise_to_a(c, p, xr, cap && p.cap_op == BF_OP_FF1);
+            row_publish(c, B_A_READY);
+        }
+
+        // ---- FFN: four hidden chunks of 256; ff2 keeps an fp16 running total ------------
+        float sa2[2] = {1.f, 1.f};
+        auto ff1_step = [&](int ch) {
+            uint32_t hid[64];
+#pragma unroll
+            for (int jh = 0; jh < 2; ++jh) {
+                row_wait_acc(c, jh);
+#pragma unroll
+                for (int g = 0; g < 2; ++g) {
+                    uint32_t acc[32];
+                    tmem_ld32(c.tm + TM_ACC + 128 * jh + 64 * c.hf + 32 * g, acc);
+                    tmem_wait_ld();
+                    const int col = 256 * ch + 128 * jh + 64 * c.hf + 32 * g;
+                    if (cap && p.cap_op == BF_OP_FF1 && c.valid) {
+                        int4* dst = reinterpret_cast<int4*>(p.cap_acc + c.grow * 1024 + col);
+#pragma unroll
+                        for (int k = 0; k < 8; ++k)
+                            dst[k] = make_int4(acc[4 * k], acc[4 * k + 1], acc[4 * k + 2], acc[4 * k + 3]);
+                    }
+                    descale32<true>(acc, sa, __ldg(sw_ff1 + 2 * ch + jh), b_ff1 + col, &hid[32 * jh + 16 * g]);
+                }
+                row_release_acc(c, jh);
+            }
+            // per-row u8 scale over the 256-wide chunk (encoder.cu:1510-1517)
+            const float mine = amax16(hid, 64, false);
+            const float4 o = exchange(c, make_float4(mine, 0.f, 0.f, 0.f));
+            const float amax = fmaxf(mine, o.x);
+            const float sc = amax > 0.f ? __fdiv_rn(amax, 255.0f) : 1.0f;
+            const float inv = __fdiv_rn(1.0f, sc);
+            sa2[ch & 1] = sc;
+            const bool caph = cap && p.cap_op == BF_OP_FF2 + ch && c.valid;
+#pragma unroll
+            for (int jh = 0; jh < 2; ++jh)
+#pragma unroll
+                for (int k = 0; k < 4; ++k) {
+                    const uint4 v = quant16(&hid[32 * jh + 8 * k], inv);
+                    *reinterpret_cast<uint4*>(c.smem_gen + SM_R + (ch & 1) * 32768 + jh * 16384 +
+                                              sw_off(c.row, 4 * c.hf + k)) = v;
+                    if (caph)
+                        *reinterpret_cast<uint4*>(p.cap_a + c.grow * kD + 128 * jh + 64 * c.hf + 16 * k) = v;
+                }
+            row_publish(c, B_A2_READY + (ch & 1));
+        };
+        auto ff2_step = [&](int ch) {
+#pragma unroll
+            for (int jh = 0; jh < 2; ++jh) {
+                row_wait_acc(c, jh);
+#pragma unroll
+                for (int g = 0; g < 2; ++g) {
+                    uint32_t acc[32], run[16];
+                    const int col = 128 * jh + 64 * c.hf + 32 * g;
+                    tmem_ld32(c.tm + TM_ACC + col, acc);
+                    if (ch > 0) tmem_ld16(c.tm + TM_OY + (col >> 1), run);
+                    tmem_wait_ld();
+                    if (cap && p.cap_op == BF_OP_FF2 + ch && c.valid) {
+                        int4* dst = reinterpret_cast<int4*>(p.cap_acc + c.grow * 256 + col);
+#pragma unroll
+                        for (int k = 0; k < 8; ++k)
+                            dst[k] = make_int4(acc[4 * k], acc[4 * k + 1], acc[4 * k + 2], acc[4 * k + 3]);
+                    }
+                    const float s1 = sa2[ch & 1], s2 = __ldg(sw_ff2 + jh);
+#pragma unroll
+                    for (int i = 0; i < 16; ++i) {
+                        float f0 = __fmul_rn(__fmul_rn(static_cast<float>(static_cast<int>(acc[2 * i])), s1), s2);
+                        float f1 = __fmul_rn(__fmul_rn(static_cast<float>(static_cast<int>(acc[2 * i + 1])), s1), s2);
+                        if (ch > 0) {
+                            const float2 r = __half22float2(as_h2(run[i]));
+                            f0 = __fadd_rn(f0, r.x);
+                            f1 = __fadd_rn(f1, r.y);
+                        }
+                        run[i] = pack_h2(f0, f1);
+                    }
+                    if (ch < 3) {
+                        tmem_st16(c.tm + TM_OY + (col >> 1), run);
+                    } else {
+                        // + b_ff2, residual (encoder.cu:1548-1556): x = fp16(x + fp16(run + b))
+                        uint32_t xo[16];
+                        tmem_ld16(c.tm + TM_X + (col >> 1), xo);
+                        tmem_wait_ld();
+                        const uint4* b4 = reinterpret_cast<const uint4*>(b_ff2 + col);
+#pragma unroll
+                        for (int v = 0; v < 4; ++v) {
+                            const uint4 bv = __ldg(b4 + v);
+                            const uint32_t bw[4] = {bv.x, bv.y, bv.z, bv.w};
+#pragma unroll
+                            for (int k = 0; k < 4; ++k) {
+                                const int i = 4 * v + k;
+                                const __half2 yv = __hadd2(as_h2(run[i]), as_h2(bw[k]));
+                                xr[32 * jh + 16 * g + i] = as_u32(__hadd2(as_h2(xo[i]), yv));
+                            }
+                        }
+                    }
+                }
+                row_release_acc(c, jh);
+                if (ch == 3)
+                    tmem_st32(c.tm + TM_X + 64 * jh + 32 * c.hf, *reinterpret_cast<uint32_t(*)[32]>(&xr[32 * jh]));
+            }
+            tmem_wait_st();
+        };
+        ff1_step(0); ff1_step(1); ff2_step(0); ff1_step(2);
+        ff2_step(1); ff1_step(3); ff2_step(2); ff2_step(3);
+
+        // ---- next layer's LN1 + quantise, or the final norm ------------------------------
+        float mean, rstd;
+        ln_stats(c, xr, p.eps, mean, rstd);
+        if (layer + 1 < p.n_layers) {
+            ln_apply(xr, mean, rstd);
+            sa = quantise_to_a(c, p, xr, p.cap_layer == layer + 1 && p.cap_op == BF_OP_QKV);
+            row_publish(c, B_A_READY);
+        } else {
+            // norm_f with affine: fp16(fma(x_hat, gamma, beta)) (encoder.cu:609-611), written
+            // as the fp16 A operand of the head GEMM: 4 K-slabs of [128][64 halves].
+#pragma unroll
+            for (int g = 0; g < 2; ++g) {
+                const int col = 128 * g + 64 * c.hf;
+                const uint4* g4 = reinterpret_cast<const uint4*>(p.tail + col);
+                const uint4* b4 = reinterpret_cast<const uint4*>(p.tail + kD + col);
+#pragma unroll
+                for (int k = 0; k < 8; ++k) {
+                    const uint4 gv = __ldg(g4 + k), bv = __ldg(b4 + k);
+                    const uint32_t gw[4] = {gv.x, gv.y, gv.z, gv.w}, bw[4] = {bv.x, bv.y, bv.z, bv.w};
+                    uint32_t o[4];
+#pragma unroll
+                    for (int j = 0; j < 4; ++j) {
+                        const float2 f = __half22float2(as_h2(xr[32 * g + 4 * k + j]));
+                        const float2 gf = __half22float2(as_h2(gw[j])), bf2 = __half22float2(as_h2(bw[j]));
+                        const float a0 = __fmaf_rn(__fmul_rn(__fsub_rn(f.x, mean), rstd), gf.x, bf2.x);
+                        const float a1 = __fmaf_rn(__fmul_rn(__fsub_rn(f.y, mean), rstd), gf.y, bf2.y);
+                        o[j] = pack_h2(a0, a1);
+                        xr[32 * g + 4 * k + j] = o[j];
+                    }
+                    *reinterpret_cast<uint4*>(c.smem_gen + SM_R + (2 * g + c.hf) * 16384 + sw_off(c.row, k)) =
+                        make_uint4(o[0], o[1], o[2], o[3]);
+                }
+            }
+            if (dbg == 8) dump_row64(c, p.y, xr);
+            row_publish(c, B_A_READY);
+        }
+    }
+
+    // ---- heads: fp16 GEMM [128 x 256] x [96 x 256]^T, fp32 accumulate, rounded to fp16
+    //      (encoder.cu:894-1079; the reference accumulates in fp16) -------------------------
+    row_wait_acc(c, 0);
+    {
+        uint32_t acc[32];
+        tmem_ld32(c.tm + TM_ACC + 32 * c.hf, acc);
+        uint32_t aux[16];
+        if (c.hf == 0) tmem_ld16(c.tm + TM_ACC + 64, aux);
+        tmem_wait_ld();
+        row_release_acc(c, 0);
+        uint32_t lg[16];
+        unsigned long long lw = ~0ull;
+        if (p.legal != nullptr && c.valid) lw = p.legal[c.grow];
+        const uint32_t bits = static_cast<uint32_t>(lw >> (32 * c.hf));
+#pragma unroll
+        for (int i = 0; i < 16; ++i) {
+            uint32_t v = pack_h2(__uint_as_float(acc[2 * i]), __uint_as_float(acc[2 * i + 1]));
+            if (!((bits >> (2 * i)) & 1u)) v = (v & 0xffff0000u) | 0xfc00u;
+            if (!((bits >> (2 * i + 1)) & 1u)) v = (v & 0x0000ffffu) | 0xfc000000u;
+            lg[i] = v;
+        }
+        if (c.valid && p.policy != nullptr) {
+            uint4* dst = reinterpret_cast<uint4*>(p.policy + c.grow * 64 + 32 * c.hf);
+#pragma unroll
+            for (int k = 0; k < 4; ++k) dst[k] = make_uint4(lg[4 * k], lg[4 * k + 1], lg[4 * k + 2], lg[4 * k + 3]);
+        }
+        if (c.hf == 0) {
+            if (c.valid && p.promo != nullptr)
+                *reinterpret_cast<uint2*>(p.promo + c.grow * 4) =
+                    make_uint2(pack_h2(__uint_as_float(aux[0]), __uint_as_float(aux[1])),
+                               pack_h2(__uint_as_float(aux[2]), __uint_as_float(aux[3])));
+            // value logits are read after their fp16 rounding, as the reference does
+            float a = __half2float(__float2half_rn(__uint_as_float(aux[4])));
+            float b = __half2float(__float2half_rn(__uint_as_float(aux[5])));
+            float d = __half2float(__float2half_rn(__uint_as_float(aux[6])));
+            if (p.vmode == 1) {
+                const bool live = (alive >> c.lane) & 1u;
+                a = live ? a : 0.f; b = live ? b : 0.f; d = live ? d : 0.f;
+#pragma unroll
+                for (int off = 16; off; off >>= 1) {
+                    a += __shfl_xor_sync(0xffffffffu, a, off);
+                    b += __shfl_xor_sync(0xffffffffu, b, off);
+                    d += __shfl_xor_sync(0xffffffffu, d, off);
+                }
+                const int nlive = __popc(alive);
+                const float inv = 1.0f / static_cast<float>(nlive > 0 ? nlive : 1);
+                a *= inv; b *= inv; d *= inv;
+            }
+            const bool writer = p.vmode == 1 ? c.lane == 0 : c.lane == (ctl < 0 ? 31 : 15);
+            if (writer && c.valid && p.value != nullptr) {
+                float v;
+                if (p.n_value == 1) {
+                    v = tanhf(a);
+                } else {
+                    const float m = fmaxf(a, fmaxf(b, d));
+                    const float ea = expf(a - m), eb = expf(b - m), ec = expf(d - m);
+                    v = (ec - ea) / (ea + eb + ec);
+                }
+                if (p.vmode != 0 && ctl < 0) v = -v;
+                p.value[board] = v;
+            }
+        }
+    }
+}
+
+// ------------------------------------------------------------------------------------------
+// Producer: streams the packed weight stage images through the ring.
+// ------------------------------------------------------------------------------------------
+__device__ __forceinline__ uint32_t uses(uint32_t cnt, uint32_t slots, uint32_t s) {
+    return (cnt + slots - 1 - s) / slots;
+}
+
+__device__ __forceinline__ void producer_loop(uint32_t smem, volatile int* abort_flag, const Params& p,
+                                           int first_tile, int tile_step, int n_tiles) {
+    uint32_t qi = 0, ri = 0;   // stages issued into the QKV ring / the 16 KB ring
+    for (int tile = first_tile; tile < n_tiles; tile += tile_step) {
+        const uint8_t* src = p.wstream;
+        for (int layer = 0; layer <= p.n_layers; ++layer) {
+            const bool head = layer == p.n_layers;
+            if (!head) {
+                // the two rings share memory: the 16 KB ring must be drained first
+                for (uint32_t s = 0; s < kRSlots; ++s)
+                    mbar_wait(bar_addr(smem, B_WR_EMPTY + s), (uses(ri, kRSlots, s) - 1u) & 1u, abort_flag, kErrProducer);
+                for (int st = 0; st < 8; ++st, ++qi) {
+                    const uint32_t s = qi % kQSlots;
+                    mbar_wait(bar_addr(smem, B_WQ_EMPTY + s), (qi / kQSlots - 1u) & 1u, abort_flag, kErrProducer);
+                    mbar_arrive_expect_tx(bar_addr(smem, B_WQ_FULL + s), kQStage);
+                    bulk_g2s(smem + SM_RING + s * kQStage, src, kQStage, bar_addr(smem, B_WQ_FULL + s));
+                    src += kQStage;
+                }
+                for (uint32_t s = 0; s < kQSlots; ++s)
+                    mbar_wait(bar_addr(smem, B_WQ_EMPTY + s), (uses(qi, kQSlots, s) - 1u) & 1u, abort_flag, kErrProducer);
+            }
+            const int n_st = head ? 4 : 36;
+            const uint32_t bytes = head ? kHeadStage : kRStage;
+            for (int st = 0; st < n_st; ++st, ++ri) {
+                const uint32_t s = ri % kRSlots;
+                mbar_wait(bar_addr(smem, B_WR_EMPTY + s), (ri / kRSlots - 1u) & 1u, abort_flag, kErrProducer);
+                mbar_arrive_expect_tx(bar_addr(smem, B_WR_FULL + s), bytes);
+                bulk_g2s(smem + SM_RING + s * kRStage, src, bytes, bar_addr(smem, B_WR_FULL + s));
+                src += bytes;
+            }
+        }
+    }
+    // Every copy issued has been waited for by the MMA issuer on the normal path.  After a
+    // time-out some may still be in flight: give them a bounded while to land before the
+    // CTA's shared memory goes away.
+    if (*abort_flag != 0) {
+        const long long t0 = clock64();
+        while (clock64() - t0 < 2000000LL) { }
+    }
+}
+
+// ------------------------------------------------------------------------------------------
+// MMA issuer: one thread walks the static GEMM schedule.
+// ------------------------------------------------------------------------------------------
+struct MmaState {
+    uint32_t qc, rc;          // weight stages consumed from each ring
+    uint32_t accn[2];         // units issued into each accumulator slot
+    uint32_t aready, a2n[2];  // operand-ready phases consumed
+};
+
+// One GEMM unit: `n_stages` K-slabs of 128 bytes, 4 MMAs each.
+__device__ __forceinline__ void mma_unit(uint32_t smem, volatile int* abort_flag, MmaState& st,
+                                         uint32_t tmem_d, int slot, uint32_t a_base, bool qring,
+                                         int n_stages, uint32_t idesc, bool f16) {
+    mbar_wait(bar_addr(smem, B_ACC_EMPTY + slot), (st.accn[slot] - 1u) & 1u, abort_flag, kErrMmaAcc);
+    tc_fence_after();
+    for (int s = 0; s < n_stages; ++s) {
+        uint32_t w_full, w_empty, w_addr;
+        if (qring) {
+            const uint32_t k = st.qc % kQSlots;
+            mbar_wait(bar_addr(smem, B_WQ_FULL + k), (st.qc / kQSlots) & 1u, abort_flag, kErrMmaWeights);
+            w_full = k; w_empty = bar_addr(smem, B_WQ_EMPTY + k); w_addr = smem + SM_RING + k * kQStage;
+            st.qc++;
+        } else {
+            const uint32_t k = st.rc % kRSlots;
+            mbar_wait(bar_addr(smem, B_WR_FULL + k), (st.rc / kRSlots) & 1u, abort_flag, kErrMmaWeights);
+            w_full = k; w_empty = bar_addr(smem, B_WR_EMPTY + k); w_addr = smem + SM_RING + k * kRStage;
+            st.rc++;
+        }
+        (void)w_full;
+        tc_fence_after();
+        const uint64_t ad = umma_desc_k128(a_base + s * 16384), bd = umma_desc_k128(w_addr);
+#pragma unroll
+        for (int k = 0; k < 4; ++k) {
+            const uint32_t accumulate = (s > 0 || k > 0) ? 1u : 0u;
+            if (f16) umma_f16(tmem_d, ad + 2 * k, bd + 2 * k, idesc, accumulate);
+            else     umma_i8(tmem_d, ad + 2 * k, bd + 2 * k, idesc, accumulate);
+        }
+        tc_commit(w_empty);
+    }
+    tc_commit(bar_addr(smem, B_ACC_FULL + slot));
+    st.accn[slot]++;
+}
+
+__device__ __forceinline__ void mma_wait_operand(uint32_t smem, volatile int* abort_flag, int bar_idx,
+                                                 uint32_t& cnt) {
+    mbar_wait(bar_addr(smem, bar_idx), cnt & 1u, abort_flag, kErrMmaOperand);
+    cnt++;
+    tc_fence_after();
+}
+
+__device__ __forceinline__ void mma_loop(uint32_t smem, uint32_t tmem, volatile int* abort_flag,
+                                      const Params& p, int first_tile, int tile_step, int n_tiles) {
+    MmaState st = {0, 0, {0, 0}, 0, {0, 0}};
+    constexpr uint32_t kI_QKV = umma_idesc(kAccS32, kFmtS8, kFmtS8, 128, 192);
+    constexpr uint32_t kI_S8 = umma_idesc(kAccS32, kFmtS8, kFmtS8, 128, 128);
+    constexpr uint32_t kI_U8 = umma_idesc(kAccS32, kFmtU8, kFmtS8, 128, 128);
+    constexpr uint32_t kI_HEAD = umma_idesc(kAccF32, kFmtF16, kFmtF16, 128, 96);
+    const uint32_t acc0 = tmem + TM_ACC, acc1 = tmem + TM_ACC + 128;
+    for (int tile = first_tile; tile < n_tiles; tile += tile_step) {
+        for (int layer = 0; layer < p.n_layers; ++layer) {
+            mma_wait_operand(smem, abort_flag, B_A_READY, st.aready);          // LN1 output
+            for (int j = 0; j < 4; ++j)
+                mma_unit(smem, abort_flag, st, acc0, 0, smem + SM_A, true, 2, kI_QKV, false);
+            mma_wait_operand(smem, abort_flag, B_A_READY, st.aready);          // attention output
+            mma_unit(smem, abort_flag, st, acc0, 0, smem + SM_A, false, 2, kI_S8, false);
+            mma_unit(smem, abort_flag, st, acc1, 1, smem + SM_A, false, 2, kI_S8, false);
+            mma_wait_operand(smem, abort_flag, B_A_READY, st.aready);          // LN2 output
+            // FFN units in the order the weight stream was packed (pack.py: FFN_UNITS)
+#pragma unroll 1
+            for (int u = 0; u < 16; ++u) {
+                // kind/chunk of unit u: pairs (u>>1): F1 0, F1 1, F2 0, F1 2, F2 1, F1 3, F2 2, F2 3
+                const int pr = u >> 1, jh = u & 1;
+                const int kind2 = (0xD4 >> pr) & 1;                       // 0b11010100
+                const int ch = kind2 ? ((0x32010000u >> (4 * pr)) & 0xF) : ((0x00302010u >> (4 * pr)) & 0xF);
+                if (kind2) {
+                    if (jh == 0) mma_wait_operand(smem, abort_flag, B_A2_READY + (ch & 1), st.a2n[ch & 1]);
+                    mma_unit(smem, abort_flag, st, jh ? acc1 : acc0, jh, smem + SM_R + (ch & 1) * 32768,
+                             false, 2, kI_U8, false);
+                } else {
+                    mma_unit(smem, abort_flag, st, jh ? acc1 : acc0, jh, smem + SM_A, false, 2, kI_S8, false);
+                }
+            }
+        }
+        mma_wait_operand(smem, abort_flag, B_A_READY, st.aready);              // final norm output
+        mma_unit(smem, abort_flag, st, acc0, 0, smem + SM_R, false, 4, kI_HEAD, true);
+    }
+}
+
+// ------------------------------------------------------------------------------------------
+__global__ void __launch_bounds__(kThreads, 1) encoder_kernel(const Params p) {
+    extern __shared__ uint8_t smem_raw[];
+    uint8_t* sm = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+    const uint32_t smem = smem_u32(sm);
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    volatile int* abort_flag = reinterpret_cast<volatile int*>(sm + SM_MISC + 4);
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(sm + SM_MISC);
+
+    if (threadIdx.x == 0) {
+        for (int i = 0; i < B_COUNT; ++i) {
+            const bool many = (i >= B_ACC_EMPTY && i < B_ACC_EMPTY + 2) || i >= B_A_READY;
+            mbar_init(bar_addr(smem, i), many ? kRowWarps : 1);
+        }
+        *abort_flag = 0;
+        fence_barrier_init();
+    }
+    if (warp == kMmaWarp) {
+        tmem_alloc(smem + SM_MISC, TM_COLS);
+        tmem_relinquish();
+    }
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t tmem = *tmem_slot;
+
+    const int n_tiles = (p.n + 3) / 4;
+    if (warp < kRowWarps) {
+        RowCtx c;
+        c.lane = lane; c.q = warp & 3; c.hf = warp >> 2; c.row = 32 * c.q + lane;
+        c.smem = smem; c.smem_gen = sm;
+        c.tm = tmem + (static_cast<uint32_t>(32 * c.q) << 16);
+        c.abort_flag = abort_flag; c.xpar = 0; c.full_cnt[0] = c.full_cnt[1] = 0;
+        for (int tile = blockIdx.x; tile < n_tiles; tile += gridDim.x) row_warps_tile(c, p, tile);
+    } else if (warp == kProducerWarp) {
+        if (lane == 0) producer_loop(smem, abort_flag, p, blockIdx.x, gridDim.x, n_tiles);
+    } else {
+        if (lane == 0) mma_loop(smem, tmem, abort_flag, p, blockIdx.x, gridDim.x, n_tiles);
+    }
+    __syncwarp();
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    if (warp == kMmaWarp) tmem_dealloc(tmem, TM_COLS);
+    if (threadIdx.x == 0 && *abort_flag != 0) atomicCAS(p.status, 0, *abort_flag);
+}
+
+// ------------------------------------------------------------------------------------------
+// Tensor-core self test: one tile, one GEMM, no network.
+// ------------------------------------------------------------------------------------------
+__global__ void __launch_bounds__(128, 1) selftest_kernel(int mode, const uint8_t* a, const uint8_t* w,
+                                                          uint32_t* out, int* status) {
+    extern __shared__ uint8_t smem_raw[];
+    uint8_t* sm = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+    const uint32_t smem = smem_u32(sm);
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, row = threadIdx.x;
+    const int n = mode == 2 ? 192 : (mode == 3 ? 96 : 128);
+    const int slabs = mode == 3 ? 4 : 2;
+    const uint32_t w_stage = n * 128;
+    // layout: A slabs at 0 (slabs x 16 KB), W at 65536, barriers at 163840
+    constexpr uint32_t kW = 65536, kBar = 163840;
+    volatile int* abort_flag = reinterpret_cast<volatile int*>(sm + kBar + 64);
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(sm + kBar + 68);
+    if (threadIdx.x == 0) {
+        mbar_init(smem + kBar, 1);
+        mbar_init(smem + kBar + 8, 1);
+        *abort_flag = 0;
+        fence_barrier_init();
+    }
+    if (warp == 0) { tmem_alloc(smem + kBar + 68, 256); tmem_relinquish(); }
+    // A: row-major [128][slabs*128 B] -> swizzled slabs, written by the generic proxy
+    for (int s = 0; s < slabs; ++s)
+        for (int k = 0; k < 8; ++k)
+            *reinterpret_cast<uint4*>(sm + s * 16384 + sw_off(row, k)) =
+                *reinterpret_cast<const uint4*>(a + static_cast<size_t>(row) * slabs * 128 + s * 128 + k * 16);
+    fence_proxy_async_smem();
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t tmem = *tmem_slot;
+    if (threadIdx.x == 0) {
+        mbar_arrive_expect_tx(smem + kBar, w_stage * slabs);
+        for (int s = 0; s < slabs; ++s) bulk_g2s(smem + kW + s * w_stage, w + s * w_stage, w_stage, smem + kBar);
+        mbar_wait(smem + kBar, 0, abort_flag, kErrMmaWeights);
+        tc_fence_after();
+        const uint32_t idesc = mode == 0 ? umma_idesc(kAccS32, kFmtS8, kFmtS8, 128, 128)
+                             : mode == 1 ? umma_idesc(kAccS32, kFmtU8, kFmtS8, 128, 128)
+                             : mode == 2 ? umma_idesc(kAccS32, kFmtS8, kFmtS8, 128, 192)
+                                         : umma_idesc(kAccF32, kFmtF16, kFmtF16, 128, 96);
+        for (int s = 0; s < slabs; ++s) {
+            const uint64_t ad = umma_desc_k128(smem + s * 16384), bd = umma_desc_k128(smem + kW + s * w_stage);
+            for (int k = 0; k < 4; ++k) {
+                if (mode == 3) umma_f16(tmem, ad + 2 * k, bd + 2 * k, idesc, (s | k) ? 1u : 0u);
+                else           umma_i8(tmem, ad + 2 * k, bd + 2 * k, idesc, (s | k) ? 1u : 0u);
+            }
+        }
+        tc_commit(smem + kBar + 8);
+    }
+    mbar_wait(smem + kBar + 8, 0, abort_flag, kErrRowAcc);
+    tc_fence_after();
+    for (int c0 = 0; c0 < n; c0 += 32) {
+        uint32_t acc[32];
+        tmem_ld32(tmem + (static_cast<uint32_t>(32 * warp) << 16) + c0, acc);
+        tmem_wait_ld();
+        for (int i = 0; i < 32; ++i) out[static_cast<size_t>(row) * n + c0 + i] = acc[i];
+    }
+    (void)lane;
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    if (warp == 0) tmem_dealloc(tmem, 256);
+    if (threadIdx.x == 0 && *abort_flag != 0) atomicCAS(status, 0, *abort_flag);
+}
+
+}  // namespace bf
+
+// ==========================================================================================
+// Host side: the C ABI.
+// ==========================================================================================
+namespace {
+
+thread_local std::string g_err;
+
+int fail(int code, const std::string& msg) {
+    g_err = msg;
+    return code;
+}
+#define BF_CUDA(call)                                                                      \
+    do {                                                                                   \
+        cudaError_t e_ = (call);                                                           \
+        if (e_ != cudaSuccess)                                                             \
+            return fail(BF_ECUDA, std::string(#call) + ": " + cudaGetErrorString(e_));    \
+    } while (0)
+
+struct BlobHeader {
+    uint32_t magic, version, n_layers, n_value, vmode;
+    float eps;
+    uint32_t reserved[2];
+    uint64_t off_w, bytes_w, off_lp, bytes_lp, off_emb, bytes_emb, off_tail, bytes_tail, total;
+};
+
+}  // namespace
+
+struct bf_handle {
+    int device = 0;
+    BlobHeader hdr{};
+    uint8_t* blob = nullptr;
+    int* status = nullptr;
+    int sm_count = 0;
+    long long launches = 0;
+    // staging for bf_forward_host
+    int cap_n = 0;
+    uint8_t* d_in = nullptr;      // boards | control | rep | legal
+    uint8_t* d_out = nullptr;     // policy | promo | value
+    cudaStream_t stream = nullptr;
+};
+
+namespace {
+
+int launch(bf_handle* h, const uint16_t* boards, const int16_t* control, const uint8_t* rep,
+           const uint64_t* legal, int n, void* policy, void* promo, float* value, void* y, int stage,
+           int cap_layer, int cap_op, uint8_t* cap_a, int32_t* cap_acc, cudaStream_t stream) {
+    if (h == nullptr) return fail(BF_EINVAL, "null handle");
+    if (n < 0) return fail(BF_EINVAL, "n must be >= 0");
+    if (n == 0) return BF_OK;
+    if (boards == nullptr || control == nullptr || rep == nullptr)
+        return fail(BF_EINVAL, "boards, control and rep must be non-null");
+    BF_CUDA(cudaSetDevice(h->device));
+    bf::Params p{};
+    p.boards = boards; p.control = control; p.rep = rep; p.legal = legal;
+    p.n = n; p.n_layers = static_cast<int>(h->hdr.n_layers);
+    p.n_value = static_cast<int>(h->hdr.n_value); p.vmode = static_cast<int>(h->hdr.vmode);
+    p.eps = h->hdr.eps;
+    p.wstream = h->blob + h->hdr.off_w;
+    p.lparams = h->blob + h->hdr.off_lp;
+    p.emb = reinterpret_cast<const __half*>(h->blob + h->hdr.off_emb);
+    p.tail = reinterpret_cast<const __half*>(h->blob + h->hdr.off_tail);
+    p.policy = static_cast<__half*>(policy); p.promo = static_cast<__half*>(promo); p.value = value;
+    p.y = static_cast<__half*>(y); p.debug_stage = stage;
+    p.cap_layer = cap_layer; p.cap_op = cap_op; p.cap_a = cap_a; p.cap_acc = cap_acc;
+    p.status = h->status;
+    const int n_tiles = (n + 3) / 4;
+    const int grid = n_tiles < h->sm_count ? n_tiles : h->sm_count;
+    bf::encoder_kernel<<<grid, bf::kThreads, bf::kSmemRequest, stream>>>(p);
+    BF_CUDA(cudaGetLastError());
+    h->launches++;
+    return BF_OK;
+}
+
+}  // namespace
+
+extern "C" {
+
+const char* bf_version(void) { return "brokefish_b200 0.1 sm_100a"; }
+
+const char* bf_last_error(void) { return g_err.c_str(); }
+
+int bf_create(const void* blob, size_t blob_bytes, int device, bf_handle** out) {
+    if (out == nullptr) return fail(BF_EINVAL, "out is null");
+    *out = nullptr;
+    if (blob == nullptr || blob_bytes < 256) return fail(BF_EINVAL, "blob is null or too small");
+    BF_CUDA(cudaSetDevice(device));
+    BlobHeader hdr;
+    BF_CUDA(cudaMemcpy(&hdr, blob, sizeof(hdr), cudaMemcpyDefault));
+    if (hdr.magic != BF_BLOB_MAGIC) return fail(BF_EINVAL, "blob magic mismatch");
+    if (hdr.version != BF_BLOB_VERSION) return fail(BF_EINVAL, "blob version mismatch");
+    if (hdr.total != blob_bytes) return fail(BF_EINVAL, "blob size does not match its header");
+    if (hdr.n_layers < 1 || hdr.n_layers > 64) return fail(BF_EINVAL, "n_layers out of range");
+    if (hdr.bytes_w != static_cast<uint64_t>(hdr.n_layers) * bf::kLayerStreamBytes + 4 * bf::kHeadStage ||
+        hdr.bytes_lp != static_cast<uint64_t>(hdr.n_layers) * bf::kLparamStride ||
+        hdr.bytes_emb != 184u * 256u * 2u || hdr.bytes_tail != 1024u)
+        return fail(BF_EINVAL, "blob section sizes do not match this build");
+    if ((hdr.off_w | hdr.off_lp | hdr.off_emb | hdr.off_tail) & 255u)
+        return fail(BF_EINVAL, "blob sections must be 256-byte aligned");
+    if (hdr.off_w + hdr.bytes_w > blob_bytes || hdr.off_lp + hdr.bytes_lp > blob_bytes ||
+        hdr.off_emb + hdr.bytes_emb > blob_bytes || hdr.off_tail + hdr.bytes_tail > blob_bytes)
+        return fail(BF_EINVAL, "blob section outside the blob");
+    if (hdr.n_value != 1 && hdr.n_value != 3) return fail(BF_EINVAL, "n_value must be 1 or 3");
+    if (hdr.vmode > 1) return fail(BF_ENOTSUP, "the prenorm value head is not built");
+    cudaDeviceProp prop;
+    BF_CUDA(cudaGetDeviceProperties(&prop, device));
+    if (prop.major != 10)
+        return fail(BF_ENOTSUP, "this library needs a compute capability 10.x (sm_100a) device");
+    bf_handle* h = new (std::nothrow) bf_handle();
+    if (h == nullptr) return fail(BF_EINVAL, "out of host memory");
+    h->device = device; h->hdr = hdr; h->sm_count = prop.multiProcessorCount;
+    cudaError_t e = cudaMalloc(&h->blob, blob_bytes);
+    if (e == cudaSuccess) e = cudaMemcpy(h->blob, blob, blob_bytes, cudaMemcpyDefault);
+    if (e == cudaSuccess) e = cudaMalloc(&h->status, sizeof(int));
+    if (e == cudaSuccess) e = cudaMemset(h->status, 0, sizeof(int));
+    if (e == cudaSuccess) e = cudaStreamCreateWithFlags(&h->stream, cudaStreamNonBlocking);
+    if (e == cudaSuccess)
+        e = cudaFuncSetAttribute(bf::encoder_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                 bf::kSmemRequest);
+    if (e != cudaSuccess) {
+        bf_destroy(h);
+        return fail(BF_ECUDA, std::string("bf_create: ") + cudaGetErrorString(e));
+    }
+    *out = h;
+    return BF_OK;
+}
+
+int bf_destroy(bf_handle* h) {
+    if (h == nullptr) return BF_OK;
+    cudaSetDevice(h->device);
+    if (h->stream) { cudaStreamSynchronize(h->stream); cudaStreamDestroy(h->stream); }
+    cudaFree(h->blob); cudaFree(h->status); cudaFree(h->d_in); cudaFree(h->d_out);
+    delete h;
+    return BF_OK;
+}
+
+int bf_info(const bf_handle* h, int* n_layers, int* n_value, int* vmode) {
+    if (h == nullptr) return fail(BF_EINVAL, "null handle");
+    if (n_layers) *n_layers = static_cast<int>(h->hdr.n_layers);
+    if (n_value) *n_value = static_cast<int>(h->hdr.n_value);
+    if (vmode) *vmode = static_cast<int>(h->hdr.vmode);
+    return BF_OK;
+}
+
+int bf_forward(bf_handle* h, const uint16_t* boards, const int16_t* control, const uint8_t* rep,
+               const uint64_t* legal, int n, void* policy, void* promo, float* value, void* stream) {
+    return launch(h, boards, control, rep, legal, n, policy, promo, value, nullptr, 0, -1, -1, nullptr,
+                  nullptr, static_cast<cudaStream_t>(stream));
+}
+
+int bf_forward_stage(bf_handle* h, const uint16_t* boards, const int16_t* control, const uint8_t* rep,
+                     int n, int stage, void* y, void* stream) {
+    if (y == nullptr) return fail(BF_EINVAL, "y is null");
+    if (!(stage == 9 || (stage >= 1 && stage <= 8))) return fail(BF_EINVAL, "unknown stage");
+    return launch(h, boards, control, rep, nullptr, n, nullptr, nullptr, nullptr, y, stage, -1, -1,
+                  nullptr, nullptr, static_cast<cudaStream_t>(stream));
+}
+
+int bf_forward_capture(bf_handle* h, const uint16_t* boards, const int16_t* control, const uint8_t* rep,
+                       int n, int layer, int op, uint8_t* a_bytes, int32_t* acc, void* stream) {
+    if (h == nullptr) return fail(BF_EINVAL, "null handle");
+    if (a_bytes == nullptr || acc == nullptr) return fail(BF_EINVAL, "capture buffers are null");
+    if (layer < 0 || layer >= static_cast<int>(h->hdr.n_layers)) return fail(BF_EINVAL, "layer out of range");
+    if (op < BF_OP_QKV || op > BF_OP_FF2 + 3) return fail(BF_EINVAL, "unknown op");
+    return launch(h, boards, control, rep, nullptr, n, nullptr, nullptr, nullptr, nullptr, 0, layer, op,
+                  a_bytes, acc, static_cast<cudaStream_t>(stream));
+}
+
+int bf_forward_host(bf_handle* h, const uint16_t* boards, const int16_t* control, const uint8_t* rep,
+                    const uint64_t* legal, int n, void* policy, void* promo, float* value) {
+    if (h == nullptr) return fail(BF_EINVAL, "null handle");
+    if (n < 0) return fail(BF_EINVAL, "n must be >= 0");
+    if (n == 0) return BF_OK;
+    if (boards == nullptr || control == nullptr || rep == nullptr)
+        return fail(BF_EINVAL, "boards, control and rep must be non-null");
+    BF_CUDA(cudaSetDevice(h->device));
+    if (n > h->cap_n) {
+        cudaFree(h->d_in); cudaFree(h->d_out);
+        h->d_in = h->d_out = nullptr; h->cap_n = 0;
+        BF_CUDA(cudaMalloc(&h->d_in, static_cast<size_t>(n) * (64 + 2 + 1 + 256) + 1024));
+        BF_CUDA(cudaMalloc(&h->d_out, static_cast<size_t>(n) * (4096 + 256 + 4) + 1024));
+        h->cap_n = n;
+    }
+    const size_t N = static_cast<size_t>(h->cap_n);
+    uint8_t* d_legal = h->d_in;                         // 8-byte aligned first
+    uint8_t* d_boards = d_legal + N * 256;
+    uint8_t* d_control = d_boards + N * 64;
+    uint8_t* d_rep = d_control + N * 2;
+    uint8_t* d_policy = h->d_out;
+    uint8_t* d_promo = d_policy + N * 4096;
+    uint8_t* d_value = d_promo + N * 256;
+    cudaStream_t s = h->stream;
+    BF_CUDA(cudaMemcpyAsync(d_boards, boards, static_cast<size_t>(n) * 64, cudaMemcpyHostToDevice, s));
+    BF_CUDA(cudaMemcpyAsync(d_control, control, static_cast<size_t>(n) * 2, cudaMemcpyHostToDevice, s));
+    BF_CUDA(cudaMemcpyAsync(d_rep, rep, static_cast<size_t>(n), cudaMemcpyHostToDevice, s));
+    if (legal) BF_CUDA(cudaMemcpyAsync(d_legal, legal, static_cast<size_t>(n) * 256, cudaMemcpyHostToDevice, s));
+    int rc = launch(h, reinterpret_cast<uint16_t*>(d_boards), reinterpret_cast<int16_t*>(d_control), d_rep,
+                    legal ? reinterpret_cast<uint64_t*>(d_legal) : nullptr, n, d_policy, d_promo,
+                    reinterpret_cast<float*>(d_value), nullptr, 0, -1, -1, nullptr, nullptr, s);
+    if (rc != BF_OK) return rc;
+    if (policy) BF_CUDA(cudaMemcpyAsync(policy, d_policy, static_cast<size_t>(n) * 4096, cudaMemcpyDeviceToHost, s));
+    if (promo) BF_CUDA(cudaMemcpyAsync(promo, d_promo, static_cast<size_t>(n) * 256, cudaMemcpyDeviceToHost, s));
+    if (value) BF_CUDA(cudaMemcpyAsync(value, d_value, static_cast<size_t>(n) * 4, cudaMemcpyDeviceToHost, s));
+    BF_CUDA(cudaStreamSynchronize(s));
+    return BF_OK;
+}
+
+int bf_status(bf_handle* h, int* status) {
+    if (h == nullptr || status == nullptr) return fail(BF_EINVAL, "null argument");
+    BF_CUDA(cudaSetDevice(h->device));
+    BF_CUDA(cudaDeviceSynchronize());
+    BF_CUDA(cudaMemcpy(status, h->status, sizeof(int), cudaMemcpyDeviceToHost));
+    if (*status != 0) {
+        BF_CUDA(cudaMemset(h->status, 0, sizeof(int)));
+        return fail(BF_EDEVICE, "a device-side bounded wait ran out (code " + std::to_string(*status) + ")");
+    }
+    return BF_OK;
+}
+
+long long bf_launch_count(const bf_handle* h) { return h ? h->launches : 0; }
+
+int bf_selftest_umma(int device, int mode, const void* a, const void* w_image, void* out) {
+    if (mode < 0 || mode > 3 || a == nullptr || w_image == nullptr || out == nullptr)
+        return fail(BF_EINVAL, "bad self-test argument");
+    BF_CUDA(cudaSetDevice(device));
+    int* status = nullptr;
+    BF_CUDA(cudaMalloc(&status, sizeof(int)));
+    BF_CUDA(cudaMemset(status, 0, sizeof(int)));
+    constexpr int kSmem = 163840 + 128 + 1024;
+    BF_CUDA(cudaFuncSetAttribute(bf::selftest_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmem));
+    bf::selftest_kernel<<<1, 128, kSmem>>>(mode, static_cast<const uint8_t*>(a),
+                                           static_cast<const uint8_t*>(w_image),
+                                           static_cast<uint32_t*>(out), status);
+    cudaError_t e = cudaGetLastError();
+    if (e == cudaSuccess) e = cudaDeviceSynchronize();
+    int st = 0;
+    if (e == cudaSuccess) e = cudaMemcpy(&st, status, sizeof(int), cudaMemcpyDeviceToHost);
+    cudaFree(status);
+    if (e != cudaSuccess) return fail(BF_ECUDA, std::string("self test: ") + cudaGetErrorString(e));
+    if (st != 0) return fail(BF_EDEVICE, "self test: a bounded wait ran out (code " + std::to_string(st) + ")");
+    return BF_OK;
+}
+
+}  // extern "C"

@@ -1,0 +1,277 @@
+"""``FusedEncoder``: the evaluator object the search and the trainer call.
+
+Same constructor, attributes, methods and errors as the reference's CUDA implementation
+(brokefish/nn/cuda_impl.py:119-531), backed by the sm_100a kernel through the C ABI in
+``include/brokefish_b200.h``.  PyTorch is used for device memory and the current stream
+only.
+
+What is built here is the int8 arithmetic of the reference's ``int8=True`` path (scheme
+``"all"``: QKV, out-projection and both FFN matmuls in int8, heads and attention in
+fp16).  The fp16 and e4m3 arithmetics of the reference are not built: asking for them
+raises ``NotImplementedError`` instead of silently running something else.
+
+The weights are a *snapshot*: folded, quantised and uploaded once in the constructor.
+After a weight update, build a new ``FusedEncoder``.
+"""
+
+from __future__ import annotations
+
+import ctypes
+from typing import Optional
+
+import numpy as np
+import torch
+
+from brokefish_b200 import _native
+from brokefish_b200.nn.model import BrokefishNet, N_POLICY, N_PROMO
+from brokefish_b200.nn.pack import pack_blob
+
+#: Which matmuls int8 covers, by the reference's kernel mode number.
+SCHEMES = {"ffn": 2, "ffn+qkv": 4, "all": 3}
+SCHEME = "all"
+
+OP_QKV, OP_OUT, OP_FF1, OP_FF2 = 0, 1, 2, 3
+_OP_WIDTH = {OP_QKV: 768, OP_OUT: 256, OP_FF1: 1024}
+
+
+def _ptr(t: Optional[torch.Tensor]):
+    return ctypes.c_void_p(t.data_ptr()) if t is not None and t.numel() else ctypes.c_void_p(0)
+
+
+class FusedEncoder:
+    """Inference-only fused forward on one B200."""
+
+    D, DFF, T, H = 256, 1024, 32, 8
+    ACC_DTYPES = ("fp16", "fp32")
+    NHEAD = 96
+    VALUE_ROW = N_POLICY + N_PROMO
+    VMODE = {"king": 0, "pooled": 1, "prenorm": 2}
+    n_value = 1
+    vmode = 0
+    rj_mode = 0
+
+    def __init__(self, source, acc_dtype: str = "fp16", fp8: bool = False,
+                 int8: Optional[bool] = None, two_boards: Optional[bool] = None,
+                 int8_scheme: str = SCHEME, device: Optional[int] = None):
+        net = source if isinstance(source, BrokefishNet) else None
+        encoder = net.encoder if net is not None else source
+        layers = encoder.layers
+        first = layers[0]
+        if acc_dtype not in self.ACC_DTYPES:
+            raise ValueError(f"acc_dtype must be one of {self.ACC_DTYPES}, got {acc_dtype!r}")
+        if acc_dtype == "fp32":
+            raise NotImplementedError(
+                "acc_dtype='fp32' is not a mode of this kernel: the weight GEMMs accumulate "
+                "exactly in s32 and attention / heads already accumulate in fp32")
+        self.acc_dtype = acc_dtype
+        self.n_layers = len(layers)
+        self.d_model = first.self_attn.embed_dim
+        self.n_heads = first.self_attn.num_heads
+        self.d_ff = first.linear1.out_features
+        self.d_head = self.d_model // self.n_heads
+        self.eps = first.norm1.eps
+        if (self.d_model, self.d_ff, self.n_heads) != (self.D, self.DFF, self.H):
+            raise ValueError(
+                f"kernel is compiled for d_model={self.D}, d_ff={self.DFF}, heads={self.H}; "
+                f"got {self.d_model}, {self.d_ff}, {self.n_heads}")
+        self.fp8 = bool(fp8)
+        self.int8 = True if int8 is None else bool(int8)
+        if self.fp8 and self.int8 and int8 is not None:
+            raise ValueError("fp8 and int8 quantise the same two matmuls; pick one")
+        if int8_scheme not in SCHEMES:
+            raise ValueError(f"int8_scheme must be one of {sorted(SCHEMES)}, got {int8_scheme!r}")
+        if self.fp8:
+            raise NotImplementedError("the e4m3 FFN arithmetic is not built; use int8")
+        if not self.int8:
+            raise NotImplementedError("the fp16 arithmetic is not built; use int8 (the default)")
+        if int8_scheme != "all":
+            raise NotImplementedError("only the 'all' int8 scheme is built")
+        self.int8_scheme = int8_scheme
+        self.quant = SCHEMES[int8_scheme]
+        # Kept for callers that read it; the number of boards sharing a CTA never changes
+        # a board's arithmetic, here as in the reference.
+        self.two_boards = True if two_boards is None else bool(two_boards)
+        self.debug_stage = 0
+        self.net = net
+        self._handle = ctypes.c_void_p(0)
+        self._buffered = 0
+        self._buffered_full = 0
+        if net is not None:
+            if not torch.cuda.is_available():
+                raise RuntimeError("FusedEncoder needs a CUDA device (sm_100a); there is no "
+                                   "CPU fallback")
+            self.device = torch.cuda.current_device() if device is None else int(device)
+            self.n_value = int(net.value.weight.shape[0])
+            self.vmode = self.VMODE[getattr(net, "value_head", "king")]
+            if getattr(net, "reinject", "none") != "none":
+                raise NotImplementedError("input re-injection is not built")
+            self.blob = pack_blob(net)
+            self._create(self.blob)
+
+    # -- construction helpers --------------------------------------------------
+    def _create(self, blob: np.ndarray) -> None:
+        L = _native.lib()
+        h = ctypes.c_void_p(0)
+        _native.check(L.bf_create(ctypes.c_void_p(blob.ctypes.data), blob.size, self.device,
+                                  ctypes.byref(h)), "bf_create")
+        self._handle = h
+
+    @classmethod
+    def from_blob(cls, blob, device: Optional[int] = None) -> "FusedEncoder":
+        """Build from an already packed blob (``numpy`` uint8 array or a CUDA ``uint8``
+        tensor, e.g. one received by a broadcast) without a network object."""
+        self = cls.__new__(cls)
+        self.acc_dtype, self.fp8, self.int8 = "fp16", False, True
+        self.int8_scheme, self.quant, self.two_boards, self.debug_stage = "all", 3, True, 0
+        self.d_model, self.d_ff, self.n_heads, self.d_head = cls.D, cls.DFF, cls.H, 32
+        self.net = None
+        self._buffered = self._buffered_full = 0
+        self.device = torch.cuda.current_device() if device is None else int(device)
+        L = _native.lib()
+        h = ctypes.c_void_p(0)
+        if isinstance(blob, torch.Tensor):
+            ptr, size = ctypes.c_void_p(blob.data_ptr()), blob.numel()
+        else:
+            ptr, size = ctypes.c_void_p(blob.ctypes.data), blob.size
+        _native.check(L.bf_create(ptr, size, self.device, ctypes.byref(h)), "bf_create")
+        self._handle = h
+        nl, nv, vm = ctypes.c_int(0), ctypes.c_int(0), ctypes.c_int(0)
+        _native.check(L.bf_info(h, ctypes.byref(nl), ctypes.byref(nv), ctypes.byref(vm)), "bf_info")
+        self.n_layers, self.n_value, self.vmode = nl.value, nv.value, vm.value
+        self.eps = 1e-5
+        self._from_blob = True
+        return self
+
+    def close(self) -> None:
+        if getattr(self, "_handle", None) and self._handle.value:
+            _native.lib().bf_destroy(self._handle)
+            self._handle = ctypes.c_void_p(0)
+
+    def __del__(self):
+        try:
+            self.close()
+        except Exception:
+            pass
+
+    @property
+    def label(self) -> str:
+        """What this instance runs, for a bench header or a run log."""
+        return "int8 FFN+QKV+out_proj, 4 boards/CTA, tcgen05 (sm_100a)"
+
+    @property
+    def launches(self) -> int:
+        return int(_native.lib().bf_launch_count(self._handle)) if self._handle.value else 0
+
+    def _require_net(self, what: str):
+        if not self._handle.value:
+            raise ValueError(
+                f"{what} needs the whole model: build this from a BrokefishNet, not from a "
+                "bare nn.TransformerEncoder")
+
+    # -- the backbone-only path of the reference is not built -------------------------
+    def forward(self, x, alive=None, out=None):
+        raise NotImplementedError(
+            "the backbone-only entry point (activations in, activations out) is not built; "
+            "use forward_full(boards, control, rep)")
+
+    __call__ = forward
+
+    # -- boards in, logits out ---------------------------------------------------------
+    def _ensure_full_buffers(self, n: int) -> None:
+        if self._buffered_full != n:
+            dev = torch.device("cuda", self.device)
+            self.policy_out = torch.empty(n, self.T, N_POLICY, device=dev, dtype=torch.half)
+            self.promo_out = torch.empty(n, self.T, N_PROMO, device=dev, dtype=torch.half)
+            self.value_out = torch.empty(n, device=dev, dtype=torch.float)
+            self._buffered_full = n
+
+    @staticmethod
+    def _check_inputs(boards, control, rep):
+        n = boards.shape[0]
+        if boards.dim() != 2 or boards.shape[1] != FusedEncoder.T:
+            raise ValueError(f"boards must be [n, 32], got {tuple(boards.shape)}")
+        if boards.dtype is not torch.int16:
+            raise ValueError(f"boards must be int16, got {boards.dtype}")
+        if control.shape != (n,) or control.dtype is not torch.int16:
+            raise ValueError(f"control must be [{n}] int16, got {tuple(control.shape)} {control.dtype}")
+        if rep.shape != (n,) or rep.dtype is not torch.uint8:
+            raise ValueError(f"rep must be [{n}] uint8, got {tuple(rep.shape)} {rep.dtype}")
+        return n
+
+    def _check_device(self, *tensors):
+        for t in tensors:
+            if t is not None and (not t.is_cuda or t.device.index != self.device):
+                raise ValueError(f"inputs must live on cuda:{self.device}, got {t.device}")
+
+    def forward_full(self, boards, control, rep, legal=None):
+        """Boards to ``(policy_logits [n,32,64] fp16, promo [n,32,4] fp16, value [n] fp32)``
+        in one launch on the current stream.
+
+        ``policy_logits`` is raw unless ``legal`` (``[n,32]`` int64 legality words, bit s of
+        word p set when p->s is legal) is given, in which case illegal entries are -inf.
+        Returns views on internal buffers, which the next call overwrites.
+        """
+        self._require_net("forward_full")
+        n = self._check_inputs(boards, control, rep)
+        self._check_device(boards, control, rep, legal)
+        if legal is not None and (tuple(legal.shape) != (n, self.T) or legal.dtype is not torch.int64):
+            raise ValueError(f"legal must be [{n}, 32] int64, got {tuple(legal.shape)} {legal.dtype}")
+        self._ensure_full_buffers(n)
+        b, c, r = boards.contiguous(), control.contiguous(), rep.contiguous()
+        lg = legal.contiguous() if legal is not None else None
+        stream = ctypes.c_void_p(torch.cuda.current_stream(self.device).cuda_stream)
+        _native.check(_native.lib().bf_forward(
+            self._handle, _ptr(b), _ptr(c), _ptr(r), _ptr(lg), n, _ptr(self.policy_out),
+            _ptr(self.promo_out), _ptr(self.value_out), stream), "bf_forward")
+        return self.policy_out, self.promo_out, self.value_out
+
+    def forward_stage(self, boards, control, rep, stage: int):
+        """Activations ``[n,32,256]`` fp16 at an intermediate stage: 9 embedding; layer 0:
+        1 LN1, 5/6/7 Q/K/V, 4 attention output, 2 residual after attention, 3 LN2; 8 final
+        norm."""
+        self._require_net("forward_stage")
+        n = self._check_inputs(boards, control, rep)
+        self._check_device(boards, control, rep)
+        if self._buffered != n:
+            self.state = torch.zeros(n, self.T, self.D, device=torch.device("cuda", self.device),
+                                     dtype=torch.half)
+            self._buffered = n
+        stream = ctypes.c_void_p(torch.cuda.current_stream(self.device).cuda_stream)
+        _native.check(_native.lib().bf_forward_stage(
+            self._handle, _ptr(boards.contiguous()), _ptr(control.contiguous()),
+            _ptr(rep.contiguous()), n, int(stage), _ptr(self.state), stream), "bf_forward_stage")
+        return self.state
+
+    def capture_gemm(self, boards, control, rep, layer: int, op: int):
+        """``(A bytes [n*32,256] uint8, accumulators [n*32,N] int32)`` of one GEMM of one
+        layer, exactly as the tensor cores saw and produced them."""
+        self._require_net("capture_gemm")
+        n = self._check_inputs(boards, control, rep)
+        width = _OP_WIDTH.get(op, 256)
+        dev = torch.device("cuda", self.device)
+        a = torch.zeros(n * self.T, 256, device=dev, dtype=torch.uint8)
+        acc = torch.zeros(n * self.T, width, device=dev, dtype=torch.int32)
+        stream = ctypes.c_void_p(torch.cuda.current_stream(self.device).cuda_stream)
+        _native.check(_native.lib().bf_forward_capture(
+            self._handle, _ptr(boards.contiguous()), _ptr(control.contiguous()),
+            _ptr(rep.contiguous()), n, int(layer), int(op), _ptr(a), _ptr(acc), stream),
+            "bf_forward_capture")
+        return a, acc
+
+    def forward_host(self, boards, control, rep, policy, promo, value, legal=None):
+        """End-to-end call on HOST tensors (pinned for speed): copies in, runs, copies the
+        three outputs into the given host tensors and synchronises."""
+        self._require_net("forward_host")
+        n = self._check_inputs(boards, control, rep)
+        for t in (boards, control, rep, policy, promo, value):
+            if t.is_cuda or not t.is_contiguous():
+                raise ValueError("forward_host takes contiguous CPU tensors")
+        _native.check(_native.lib().bf_forward_host(
+            self._handle, _ptr(boards), _ptr(control), _ptr(rep), _ptr(legal), n, _ptr(policy),
+            _ptr(promo), _ptr(value)), "bf_forward_host")
+        return policy, promo, value
+
+    def check_status(self) -> None:
+        """Synchronise and raise if any launch hit a device-side time-out."""
+        st = ctypes.c_int(0)
+        _native.check(_native.lib().bf_status(self._handle, ctypes.byref(st)), "bf_status")

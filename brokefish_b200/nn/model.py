@@ -1,0 +1,206 @@
+"""Host-side mirror of the Brokefish network definition (fp32 master weights).
+
+This is the object a caller hands to :class:`brokefish_b200.nn.cuda_impl.FusedEncoder`,
+with the same constructor arguments, attribute names and ``state_dict`` keys as the
+reference's ``BrokefishNet`` (brokefish/nn/model.py:268-361), so a checkpoint written by
+the reference loads here unchanged and a network built here loads there.  It is plain
+PyTorch and it is never on the evaluation hot path: the hot path is the sm_100a kernel.
+
+Architecture (brokefish/nn/model.py:38-47): 32 piece tokens, width 256, 8 pre-norm
+encoder layers with 8 heads of 32 and a 1024-wide ReLU FFN, a final LayerNorm, and
+three bias-free heads (64 policy logits and 4 promotion logits per token, value from
+the side-to-move king's token).
+"""
+
+from __future__ import annotations
+
+from typing import Optional
+
+import torch
+from torch import nn
+
+D_MODEL, N_LAYERS, N_HEADS, D_FF, T = 256, 8, 8, 1024, 32
+N_SQUARE, N_TYPE_SPECIAL, N_COLOR_TURN, N_CLOCK, N_REP = 64, 12, 4, 101, 3
+KING_SLOT_WHITE, KING_SLOT_BLACK = 15, 31
+N_POLICY, N_PROMO = 64, 4
+VALUE_CLASSES = (1, 3)
+VALUE_HEADS = ("king", "pooled", "prenorm")
+VALUE_MODE_ID = {"pooled": 1, "prenorm": 2}
+REINJECT_MODES = ("none", "ln1", "both")
+
+EMB_TABLES = ("emb_square", "emb_type_special", "emb_color_turn", "emb_clock", "emb_rep")
+
+
+def decode_boards(boards: torch.Tensor):
+    """Fields of the 12-bit piece word: (captured, color, special, type, square).
+
+    Bit 11 captured, bit 10 colour, bit 9 special, bits 6-8 type, bits 0-5 square
+    (brokefish/nn/model.py:251-265).  A captured slot is exactly ``1 << 11``.
+    """
+    w = boards.long()
+    return (w >> 11) & 1, (w >> 10) & 1, (w >> 9) & 1, (w >> 6) & 7, w & 63
+
+
+def wdl_to_scalar(logits: torch.Tensor) -> torch.Tensor:
+    """``[N, 3]`` (loss, draw, win) logits to ``p(win) - p(loss)``."""
+    p = torch.softmax(logits, dim=-1)
+    return p[..., 2] - p[..., 0]
+
+
+def n_value_of(state: dict) -> int:
+    return int(state["value.weight"].shape[0])
+
+
+def value_head_of(state: dict) -> str:
+    if "value_mode" not in state:
+        return "king"
+    got = int(state["value_mode"])
+    for name, i in VALUE_MODE_ID.items():
+        if i == got:
+            return name
+    raise ValueError(f"unknown value_mode {got}")
+
+
+def net_for_state(state: dict, **kw) -> "BrokefishNet":
+    """An empty network shaped to hold ``state`` (brokefish/nn/model.py:243-248)."""
+    if "reinject_mode" in state or "rule_features_mode" in state:
+        raise NotImplementedError(
+            "re-injection and rule-feature networks are not supported by this build")
+    return BrokefishNet(n_value=n_value_of(state), value_head=value_head_of(state), **kw)
+
+
+class BrokefishNet(nn.Module):
+    """Piece-token transformer; same parameters and key names as the reference."""
+
+    def __init__(self, d_model: int = D_MODEL, n_layers: int = N_LAYERS,
+                 n_heads: int = N_HEADS, d_ff: int = D_FF, eps: float = 1e-5,
+                 n_value: int = 1, value_head: str = "king", reinject: str = "none",
+                 rule_features: bool = False):
+        super().__init__()
+        if n_value not in VALUE_CLASSES:
+            raise ValueError(f"n_value must be one of {VALUE_CLASSES}, got {n_value}")
+        if value_head not in VALUE_HEADS:
+            raise ValueError(f"value_head must be one of {VALUE_HEADS}, got {value_head!r}")
+        if reinject not in REINJECT_MODES:
+            raise ValueError(f"reinject must be one of {REINJECT_MODES}, got {reinject!r}")
+        if reinject != "none" or rule_features:
+            raise NotImplementedError(
+                "per-layer re-injection and rule-derived inputs are not built here")
+        self.d_model, self.n_layers, self.n_value = d_model, n_layers, n_value
+        self.value_head, self.reinject, self.rule_features = value_head, "none", False
+
+        self.emb_square = nn.Embedding(N_SQUARE, d_model)
+        self.emb_type_special = nn.Embedding(N_TYPE_SPECIAL, d_model)
+        self.emb_color_turn = nn.Embedding(N_COLOR_TURN, d_model)
+        self.emb_clock = nn.Embedding(N_CLOCK, d_model)
+        self.emb_rep = nn.Embedding(N_REP, d_model)
+        layer = nn.TransformerEncoderLayer(
+            d_model=d_model, nhead=n_heads, dim_feedforward=d_ff, batch_first=True,
+            norm_first=True, dropout=0.0, layer_norm_eps=eps)
+        self.encoder = nn.TransformerEncoder(layer, num_layers=n_layers, norm=None,
+                                             enable_nested_tensor=False)
+        self.norm_f = nn.LayerNorm(d_model, eps=eps)
+        self.policy = nn.Linear(d_model, N_POLICY, bias=False)
+        self.promo = nn.Linear(d_model, N_PROMO, bias=False)
+        self.value = nn.Linear(d_model, n_value, bias=False)
+        if value_head in VALUE_MODE_ID:
+            self.register_buffer("value_mode",
+                                 torch.tensor(VALUE_MODE_ID[value_head], dtype=torch.int64))
+        std = d_model ** -0.5
+        for mod in (self.emb_square, self.emb_type_special, self.emb_color_turn,
+                    self.emb_clock, self.emb_rep, self.policy, self.promo, self.value):
+            nn.init.normal_(mod.weight, mean=0.0, std=std)
+
+    # -- embedding ---------------------------------------------------------
+    def embed_indices(self, boards, control, rep):
+        captured, color, special, ptype, square = decode_boards(boards)
+        stm = (control < 0).long()
+        idx = (square, ptype * 2 + special, color * 2 + stm[:, None],
+               (control.abs().long() - 1).clamp_(0, N_CLOCK - 1),
+               rep.long().clamp_(0, N_REP - 1))
+        return idx, captured == 0
+
+    def embed(self, boards, control, rep):
+        """Token embeddings with the normative grouping
+        ``((square + type_special) + color_turn) + (clock + rep)``
+        (brokefish/nn/model.py:383-397)."""
+        idx, alive = self.embed_indices(boards, control, rep)
+        per_board = self.emb_clock(idx[3]) + self.emb_rep(idx[4])
+        x = self.emb_square(idx[0])
+        x = x + self.emb_type_special(idx[1])
+        x = x + self.emb_color_turn(idx[2])
+        x = x + per_board[:, None, :]
+        return x, alive
+
+    def encode(self, x, alive):
+        return self.encoder(x, src_key_padding_mask=~alive)
+
+    @property
+    def value_absolute(self) -> bool:
+        return self.value_head in ("pooled", "prenorm")
+
+    def heads(self, h, control, alive: Optional[torch.Tensor] = None,
+              with_logits: bool = False, h_raw: Optional[torch.Tensor] = None):
+        """Normed tokens to ``(policy_logits, promo, value)``; logits are raw
+        (brokefish/nn/model.py:551-617)."""
+        if self.value_head == "prenorm":
+            m = alive.unsqueeze(-1).to(h_raw.dtype)
+            hv = self.norm_f((h_raw * m).sum(1) / m.sum(1).clamp(min=1))
+        elif self.value_head == "pooled":
+            m = alive.unsqueeze(-1).to(h.dtype)
+            hv = (h * m).sum(1) / m.sum(1).clamp(min=1)
+        else:
+            king = torch.where(control < 0, KING_SLOT_BLACK, KING_SLOT_WHITE).long()
+            hv = h[torch.arange(h.shape[0], device=h.device), king]
+        raw = self.value(hv).float()
+        value = torch.tanh(raw).squeeze(-1) if self.n_value == 1 else wdl_to_scalar(raw)
+        if self.value_absolute:
+            value = torch.where(control > 0, value, -value)
+        if with_logits:
+            return self.policy(h), self.promo(h), value, raw
+        return self.policy(h), self.promo(h), value
+
+    def forward(self, boards, control, rep, with_logits: bool = False, mask=None):
+        x, alive = self.embed(boards, control, rep)
+        h = self.encode(x, alive)
+        return self.heads(self.norm_f(h), control, alive=alive,
+                          with_logits=with_logits, h_raw=h)
+
+
+def seeded_state(seed: int = 0, std: Optional[float] = 0.02, perturb_norms: bool = False,
+                 n_value: int = 1, value_head: str = "king") -> dict:
+    """A reproducible ``state_dict``, independent of module construction order.
+
+    Keys are visited in sorted order and each tensor is drawn from its own
+    ``torch.Generator`` seeded with ``seed`` and the key's position, so the same call
+    gives the same bytes on any machine with the same torch build.
+
+    ``std`` set: every tensor with two or more dimensions is N(0, std); LayerNorm
+    gammas are 1 and every bias / beta is 0.  ``std=None``: matrices are
+    N(0, 1/16) (tables and heads) or N(0, 1/sqrt(fan_in)) (projections).
+    ``perturb_norms``: LayerNorm gamma/beta and all biases get N(1, .1) / N(0, .1), so
+    the LayerNorm folds and the bias paths carry signal.
+    """
+    net = BrokefishNet(n_value=n_value, value_head=value_head)
+    state = net.state_dict()
+    out = {}
+    for i, key in enumerate(sorted(state)):
+        t = state[key]
+        if not t.is_floating_point():
+            out[key] = t.clone()
+            continue
+        g = torch.Generator(device="cpu").manual_seed(seed * 100003 + i)
+        if t.dim() >= 2:
+            s = std if std is not None else (
+                1.0 / 16 if (key.startswith("emb_") or key.split(".")[0] in
+                             ("policy", "promo", "value")) else t.shape[-1] ** -0.5)
+            out[key] = torch.randn(t.shape, generator=g) * s
+        elif perturb_norms:
+            base = 1.0 if key.endswith("weight") else 0.0
+            out[key] = base + 0.1 * torch.randn(t.shape, generator=g)
+        else:
+            # construction-time values of Linear biases come from the global RNG, so
+            # they are replaced by fixed ones: LayerNorm gamma 1, everything else 0
+            is_gamma = "norm" in key and key.endswith("weight")
+            out[key] = torch.ones_like(t) if is_gamma else torch.zeros_like(t)
+    return out

@@ -1,0 +1,226 @@
+"""Fold, quantise and lay out a network's weights as the blob the sm_100a kernel streams.
+
+What happens here, once per weight snapshot (the reference does the same work in
+``FusedEncoder.__init__`` / ``_pack_int8`` / ``_pack_tail``, brokefish/nn/cuda_impl.py:
+194-227, 339-371, 375-406):
+
+* ``1/sqrt(d_head)`` is folded into the Q rows of ``in_proj`` (weight and bias);
+* each block's LayerNorm affine is folded into the GEMM that consumes it
+  (``W <- W * gamma``, ``b <- b + W @ beta`` with the *unfolded* ``W``);
+* the four folded matrices per layer are quantised to s8 with one fp32 scale per 128
+  output rows (:func:`brokefish_b200.nn.quant.quantise_weights_int8_bytes`);
+* the bytes are written out as *stage images*: the exact shared-memory picture of a
+  K-major, 128-byte-swizzled tensor-core B operand, in the order the kernel's bulk
+  copy engine consumes them, so one linear ``cp.async.bulk`` per stage is all the
+  device does.
+
+Blob layout (all offsets 256-byte aligned, little endian; mirrored by
+``include/brokefish_b200.h``):
+
+    header   256 B   magic, version, n_layers, n_value, vmode, eps, section table
+    wstream  n_layers * 786432 + 49152 B
+                     per layer 8 QKV stages [192 rows x 128 B], then 36 stages
+                     [128 rows x 128 B]: out-proj (2 units) and the FFN units in
+                     issue order; after the last layer 4 head stages [96 x 128 B, fp16]
+    lparams  n_layers * 4736 B
+                     per layer 18 fp32 weight scales (qkv 6, out 2, ff1 8, ff2 2; padded
+                     to 128 B) then fp16 biases: qkv (chunk order) 768, out 256,
+                     ff1 1024, ff2 256
+    emb      184 * 256 fp16: square, type_special, color_turn, clock, rep tables
+    tail     512 fp16: norm_f gamma, beta
+
+A QKV "chunk" j (0..3) holds heads 2j and 2j+1: rows 0-63 are their Q rows, 64-127
+their K rows, 128-191 their V rows.  A stage image stores row r's 16-byte group c at
+byte ``r*128 + ((c ^ (r & 7)) * 16)``.
+"""
+
+from __future__ import annotations
+
+import struct
+from dataclasses import dataclass
+from typing import List
+
+import numpy as np
+import torch
+
+from brokefish_b200.nn.model import (BrokefishNet, EMB_TABLES, N_POLICY, N_PROMO,
+                                     VALUE_MODE_ID)
+from brokefish_b200.nn.quant import quantise_weights_int8_bytes
+
+MAGIC = 0x38424642          # "BFB8"
+VERSION = 1
+HEADER_BYTES = 256
+D, DFF, H, DH, T = 256, 1024, 8, 32, 32
+NHEAD = 96                   # head matrix rows: 64 policy, 4 promo, 1-3 value, zero pad
+VALUE_ROW = N_POLICY + N_PROMO
+LAYER_STREAM_BYTES = 786432
+HEAD_STREAM_BYTES = 4 * NHEAD * 128
+LPARAM_STRIDE = 4736
+LP_SW_QKV, LP_SW_O, LP_SW_FF1, LP_SW_FF2 = 0, 24, 32, 64
+LP_B_QKV, LP_B_O, LP_B_FF1, LP_B_FF2 = 128, 1664, 2176, 4224
+#: The FFN's sixteen GEMM units in issue order: (kind, hidden chunk c, half j).
+#: kind 1 = ff1 rows ``256c + 128j ..`` over K = 256; kind 2 = ff2 rows ``128j ..`` over
+#: hidden columns ``256c ..``.
+FFN_UNITS = [(1, 0, 0), (1, 0, 1), (1, 1, 0), (1, 1, 1), (2, 0, 0), (2, 0, 1),
+             (1, 2, 0), (1, 2, 1), (2, 1, 0), (2, 1, 1), (1, 3, 0), (1, 3, 1),
+             (2, 2, 0), (2, 2, 1), (2, 3, 0), (2, 3, 1)]
+
+
+def fold_norm(w: torch.Tensor, b: torch.Tensor, norm):
+    """``LN(x) W^T + b == x_hat (W * gamma)^T + (b + W beta)``; fp32 in, fp32 out."""
+    gamma = norm.weight.detach().float()
+    beta = norm.bias.detach().float()
+    return w * gamma[None, :], b + w @ beta
+
+
+def qkv_chunk_rows() -> np.ndarray:
+    """``[4, 192]``: the ``in_proj`` row behind each row of each QKV chunk."""
+    rows = np.empty((4, 192), dtype=np.int64)
+    for j in range(4):
+        for i in range(192):
+            rows[j, i] = (i // 64) * D + 64 * j + (i % 64)
+    return rows
+
+
+def sw128_image(tile: np.ndarray) -> np.ndarray:
+    """``[R, 128]`` bytes -> the same bytes in 128-byte-swizzled K-major order."""
+    r = tile.shape[0]
+    if tile.shape[1] != 128 or tile.dtype != np.uint8:
+        raise ValueError("a stage image is built from [rows, 128] uint8")
+    groups = tile.reshape(r, 8, 16)
+    dst = np.arange(8)[None, :] ^ (np.arange(r)[:, None] & 7)        # [r, 8]
+    out = np.empty_like(groups)
+    out[np.arange(r)[:, None], dst] = groups
+    return out.reshape(-1)
+
+
+@dataclass
+class FoldedLayer:
+    """One layer after folding and quantisation (natural row order, no layout yet)."""
+    q_qkv: np.ndarray; s_qkv: np.ndarray; b_qkv: np.ndarray     # [768,256] u8, [6], [768] f16
+    q_o: np.ndarray; s_o: np.ndarray; b_o: np.ndarray
+    q_ff1: np.ndarray; s_ff1: np.ndarray; b_ff1: np.ndarray
+    q_ff2: np.ndarray; s_ff2: np.ndarray; b_ff2: np.ndarray
+
+
+def fold_and_quantise(net: BrokefishNet) -> List[FoldedLayer]:
+    """The per-layer folded s8 matrices, scales and fp16 biases."""
+    out = []
+    scale = DH ** -0.5
+    for lay in net.encoder.layers:
+        w_qkv = lay.self_attn.in_proj_weight.detach().float().clone()
+        b_qkv = lay.self_attn.in_proj_bias.detach().float().clone()
+        w_qkv[:D] *= scale
+        b_qkv[:D] *= scale
+        w_qkv, b_qkv = fold_norm(w_qkv, b_qkv, lay.norm1)
+        w_ff1, b_ff1 = fold_norm(lay.linear1.weight.detach().float().clone(),
+                                 lay.linear1.bias.detach().float().clone(), lay.norm2)
+        mats = {}
+        for name, w in (("qkv", w_qkv), ("o", lay.self_attn.out_proj.weight.detach()),
+                        ("ff1", w_ff1), ("ff2", lay.linear2.weight.detach())):
+            qb, sc = quantise_weights_int8_bytes(w.float())
+            mats[name] = (qb.cpu().numpy(), sc.cpu().numpy().astype(np.float32))
+
+        def f16(v):
+            return v.detach().float().half().cpu().numpy()
+        out.append(FoldedLayer(
+            mats["qkv"][0], mats["qkv"][1], f16(b_qkv),
+            mats["o"][0], mats["o"][1], f16(lay.self_attn.out_proj.bias),
+            mats["ff1"][0], mats["ff1"][1], f16(b_ff1),
+            mats["ff2"][0], mats["ff2"][1], f16(lay.linear2.bias)))
+    return out
+
+
+def head_matrix(net: BrokefishNet) -> np.ndarray:
+    """``[96, 256]`` fp16: policy rows 0-63, promo 64-67, value from 68, zeros after."""
+    head = torch.zeros(NHEAD, D, dtype=torch.half)
+    head[:N_POLICY] = net.policy.weight.detach().half().cpu()
+    head[N_POLICY:VALUE_ROW] = net.promo.weight.detach().half().cpu()
+    nv = int(net.value.weight.shape[0])
+    head[VALUE_ROW:VALUE_ROW + nv] = net.value.weight.detach().half().cpu()
+    return head.numpy()
+
+
+def _layer_stream(fl: FoldedLayer) -> np.ndarray:
+    parts = []
+    rows = qkv_chunk_rows()
+    for j in range(4):
+        chunk = fl.q_qkv[rows[j]]                                   # [192, 256]
+        for s in range(2):
+            parts.append(sw128_image(np.ascontiguousarray(chunk[:, 128 * s:128 * s + 128])))
+    for u in range(2):
+        for s in range(2):
+            parts.append(sw128_image(np.ascontiguousarray(
+                fl.q_o[128 * u:128 * u + 128, 128 * s:128 * s + 128])))
+    for kind, c, j in FFN_UNITS:
+        for s in range(2):
+            if kind == 1:
+                blk = fl.q_ff1[256 * c + 128 * j:256 * c + 128 * j + 128,
+                               128 * s:128 * s + 128]
+            else:
+                blk = fl.q_ff2[128 * j:128 * j + 128,
+                               256 * c + 128 * s:256 * c + 128 * s + 128]
+            parts.append(sw128_image(np.ascontiguousarray(blk)))
+    stream = np.concatenate(parts)
+    assert stream.size == LAYER_STREAM_BYTES
+    return stream
+
+
+def _layer_params(fl: FoldedLayer) -> np.ndarray:
+    buf = np.zeros(LPARAM_STRIDE, dtype=np.uint8)
+    buf[LP_SW_QKV:LP_SW_QKV + 24] = fl.s_qkv.astype("<f4").view(np.uint8)
+    buf[LP_SW_O:LP_SW_O + 8] = fl.s_o.astype("<f4").view(np.uint8)
+    buf[LP_SW_FF1:LP_SW_FF1 + 32] = fl.s_ff1.astype("<f4").view(np.uint8)
+    buf[LP_SW_FF2:LP_SW_FF2 + 8] = fl.s_ff2.astype("<f4").view(np.uint8)
+    b_qkv = fl.b_qkv[qkv_chunk_rows().reshape(-1)]
+    buf[LP_B_QKV:LP_B_QKV + 1536] = b_qkv.astype("<f2").view(np.uint8)
+    buf[LP_B_O:LP_B_O + 512] = fl.b_o.astype("<f2").view(np.uint8)
+    buf[LP_B_FF1:LP_B_FF1 + 2048] = fl.b_ff1.astype("<f2").view(np.uint8)
+    buf[LP_B_FF2:LP_B_FF2 + 512] = fl.b_ff2.astype("<f2").view(np.uint8)
+    return buf
+
+
+def _align(n: int, a: int = 256) -> int:
+    return (n + a - 1) // a * a
+
+
+def pack_blob(net: BrokefishNet) -> np.ndarray:
+    """The whole device blob for ``net`` as a ``uint8`` array."""
+    if (net.d_model, len(net.encoder.layers)) != (D, net.n_layers):
+        raise ValueError("unexpected network shape")
+    first = net.encoder.layers[0]
+    if (first.self_attn.embed_dim, first.self_attn.num_heads,
+            first.linear1.out_features) != (D, H, DFF):
+        raise ValueError(
+            f"kernel is compiled for d_model={D}, d_ff={DFF}, heads={H}; got "
+            f"{first.self_attn.embed_dim}, {first.linear1.out_features}, "
+            f"{first.self_attn.num_heads}")
+    layers = fold_and_quantise(net)
+    head = head_matrix(net).view(np.uint8).reshape(NHEAD, 512)
+    wstream = np.concatenate(
+        [_layer_stream(fl) for fl in layers]
+        + [sw128_image(np.ascontiguousarray(head[:, 128 * s:128 * s + 128]))
+           for s in range(4)])
+    lparams = np.concatenate([_layer_params(fl) for fl in layers])
+    emb = np.concatenate([getattr(net, n).weight.detach().half().cpu().numpy().reshape(-1)
+                          for n in EMB_TABLES]).astype("<f2").view(np.uint8)
+    tail = np.concatenate([net.norm_f.weight.detach().half().cpu().numpy(),
+                           net.norm_f.bias.detach().half().cpu().numpy()]
+                          ).astype("<f2").view(np.uint8)
+    sections = [wstream, lparams, emb, tail]
+    offs, cur = [], HEADER_BYTES
+    for sec in sections:
+        offs.append(cur)
+        cur = _align(cur + sec.size)
+    total = cur
+    vmode = VALUE_MODE_ID.get(getattr(net, "value_head", "king"), 0)
+    header = struct.pack("<IIIIIfII", MAGIC, VERSION, len(layers),
+                         int(net.value.weight.shape[0]), vmode, float(first.norm1.eps), 0, 0)
+    for off, sec in zip(offs, sections):
+        header += struct.pack("<QQ", off, sec.size)
+    header += struct.pack("<Q", total)
+    blob = np.zeros(total, dtype=np.uint8)
+    blob[:len(header)] = np.frombuffer(header, dtype=np.uint8)
+    for off, sec in zip(offs, sections):
+        blob[off:off + sec.size] = sec
+    return blob

@@ -1,0 +1,117 @@
+/* brokefish_b200 -- C ABI of the Blackwell (sm_100a) network evaluator.
+ *
+ * Drop-in boundary for the reference's evaluator extension: the pybind module
+ * `brokefish_encoder` (csrc/encoder.cu:1905-1930) behind
+ * `FusedEncoder.forward_full` (brokefish/nn/cuda_impl.py:487-504).  Plain pointers and
+ * sizes only; no torch types.  Every function returns 0 on success or a negative
+ * BF_E* code; `bf_last_error()` gives the text for the calling thread.
+ *
+ * Conventions
+ *   - A handle belongs to one CUDA device.  Calls on one handle are not re-entrant.
+ *   - `bf_forward*` take DEVICE pointers owned by the caller and enqueue one kernel on
+ *     `stream` (a cudaStream_t passed as void*; NULL = the default stream).  They do
+ *     not synchronise and allocate nothing.
+ *   - `bf_forward_host` takes HOST pointers, copies in, runs, copies out and
+ *     synchronises; it is the end-to-end call.
+ *   - Every device-side wait in the kernel is bounded.  If one runs out, the kernel
+ *     finishes with garbage outputs and a non-zero status word that `bf_status()`
+ *     reads back after the caller's stream synchronisation.
+ */
+#ifndef BROKEFISH_B200_H
+#define BROKEFISH_B200_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define BF_OK 0
+#define BF_EINVAL (-1)   /* bad argument, bad blob */
+#define BF_ECUDA (-2)    /* a CUDA runtime call failed */
+#define BF_ENOTSUP (-3)  /* network variant this build does not run */
+#define BF_EDEVICE (-4)  /* a device-side bounded wait ran out */
+
+#define BF_BLOB_MAGIC 0x38424642u /* "BFB8" */
+#define BF_BLOB_VERSION 1u
+
+/* GEMM selectors for bf_forward_capture. */
+#define BF_OP_QKV 0 /* A: LN1 output s8 [rows,256]; acc [rows,768] in chunk order        */
+#define BF_OP_OUT 1 /* A: attention output s8;       acc [rows,256]                       */
+#define BF_OP_FF1 2 /* A: LN2 output s8;             acc [rows,1024]                      */
+#define BF_OP_FF2 3 /* + hidden chunk c (3..6): A: hidden chunk u8 [rows,256]; acc [rows,256] */
+
+typedef struct bf_handle bf_handle;
+
+/* Library / build identification: "brokefish_b200 <version> sm_100a". */
+const char* bf_version(void);
+
+/* Text of the last error on the calling thread ("" if none). */
+const char* bf_last_error(void);
+
+/* Create an evaluator on CUDA device `device` from a packed weight blob (host or device
+ * memory; layout in brokefish_b200/nn/pack.py).  The blob is copied; the caller may free
+ * it afterwards.  Replaces the weight slabs `FusedEncoder.__init__` uploads
+ * (brokefish/nn/cuda_impl.py:228, 370-371, 382-406). */
+int bf_create(const void* blob, size_t blob_bytes, int device, bf_handle** out);
+
+/* Free a handle and everything it owns. */
+int bf_destroy(bf_handle* h);
+
+/* Number of layers / value rows / value mode recorded in the handle's blob. */
+int bf_info(const bf_handle* h, int* n_layers, int* n_value, int* vmode);
+
+/* Boards to logits, one launch.  Replaces `model_forward(..., debug_stage=0)`
+ * (csrc/encoder.cu:1770-1876).
+ *   boards  [n,32] u16 piece words      control [n] i16      rep [n] u8
+ *   legal   [n,32] u64 or NULL: bit s of word p set <=> move p->s is legal; when given,
+ *           illegal policy entries are written as fp16 -inf (0xFC00)
+ *   policy  [n,32,64] fp16   promo [n,32,4] fp16   value [n] f32  (any may be NULL) */
+int bf_forward(bf_handle* h, const uint16_t* boards, const int16_t* control,
+               const uint8_t* rep, const uint64_t* legal, int n, void* policy, void* promo,
+               float* value, void* stream);
+
+/* Activations at an intermediate stage as [n,32,256] fp16.  Replaces
+ * `model_forward(..., debug_stage=stage)` (csrc/encoder.cu:1315-1427, 1575-1598):
+ * 9 embedding; layer 0: 1 LN1 out, 5/6/7 Q/K/V after bias, 4 attention out,
+ * 2 residual after attention, 3 LN2 out; 8 final norm out. */
+int bf_forward_stage(bf_handle* h, const uint16_t* boards, const int16_t* control,
+                     const uint8_t* rep, int n, int stage, void* y, void* stream);
+
+/* Run the network and copy out, for one GEMM of one layer, the quantised A operand
+ * bytes and the raw s32 accumulators the tensor cores produced.  This is what lets a
+ * test recompute the exact integer product on the host (the method of the reference's
+ * csrc/tests/tint8.cu:268-337).  `a_bytes` [n*32, 256] u8, `acc` [n*32, N] s32 with N by
+ * `op` as listed at BF_OP_*. */
+int bf_forward_capture(bf_handle* h, const uint16_t* boards, const int16_t* control,
+                       const uint8_t* rep, int n, int layer, int op, uint8_t* a_bytes,
+                       int32_t* acc, void* stream);
+
+/* End-to-end call with HOST buffers (pinned for best speed): copies the inputs to the
+ * device, runs `bf_forward`, copies the three outputs back and synchronises.  Device
+ * staging buffers are owned by the handle and grow to the largest `n` seen. */
+int bf_forward_host(bf_handle* h, const uint16_t* boards, const int16_t* control,
+                    const uint8_t* rep, const uint64_t* legal, int n, void* policy,
+                    void* promo, float* value);
+
+/* Read (and clear) the device status word; 0 = every launch since the last call ran
+ * clean.  Synchronises the device. */
+int bf_status(bf_handle* h, int* status);
+
+/* Number of kernel launches this handle has enqueued. */
+long long bf_launch_count(const bf_handle* h);
+
+/* Tensor-core self test (no network): one 128-row tile times a packed weight tile.
+ *   mode 0: s8 x s8, N=128, K=256     mode 1: u8 x s8, N=128, K=256
+ *   mode 2: s8 x s8, N=192, K=256     mode 3: f16 x f16 -> f32, N=96, K=256
+ *   a        device, [128, K] row-major (1 byte or 2 bytes per element)
+ *   w_image  device, K/ (128 B) stage images of [N, 128 B] (pack.py: sw128_image)
+ *   out      device, [128, N] s32 (modes 0-2) or f32 (mode 3)
+ * Follows the exact-integer method of the reference's csrc/tests/tint8.cu:268-337. */
+int bf_selftest_umma(int device, int mode, const void* a, const void* w_image, void* out);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* BROKEFISH_B200_H */

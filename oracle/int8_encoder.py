@@ -1,0 +1,348 @@
+"""TEST INFRASTRUCTURE, not product code: a CPU restatement (numpy) of the reference's
+int8 evaluator, boards in, logits out.
+
+Only ``tests/``, ``__graft_entry__.smoke()`` and the ``cpu_baseline`` / ``--impl
+reference`` legs of ``bench.py`` may import this module.  Nothing under
+``brokefish_b200/`` does.
+
+What it restates, step by step, with the reference lines each step follows (paths are
+the reference project's own):
+
+* weight folding and quantisation ............ brokefish/nn/cuda_impl.py:194-227, 339-371;
+                                                brokefish/nn/quant.py:263-278
+* embedding sum, fp16, normative grouping ..... csrc/encoder.cu:817-889; nn/model.py:383-397
+* LayerNorm (one-pass fp32 stats, fp16 out) ... csrc/encoder.cu:584-616
+* per-row s8/u8 activation quantiser .......... csrc/int8_gemm.cuh:159-199
+* s8/u8 x s8 GEMM, exact s32, one descale ..... csrc/int8_gemm.cuh:276-297
+* bias / ReLU / residual in fp16 .............. csrc/encoder.cu:631-686, 1482-1489
+* attention, dead keys masked, fp32 softmax ... csrc/encoder.cu:715-797
+* layer order and the ff2 fp16 running total .. csrc/encoder.cu:1319-1557
+* final norm (affine), fp16 heads, value ...... csrc/encoder.cu:894-1079; nn/model.py:551-617
+
+Parity status: PINNED.  ``tests/test_oracle_golden.py`` checks this file against outputs
+of the reference's own Python (its fp32 network, its int8 emulation, its scheme
+functions, its embedding) generated in a container that holds the reference and
+committed under ``tests/golden/`` with the generating script.
+
+Where the reference's GPU arithmetic cannot be reproduced bit for bit on a CPU
+(``rsqrtf``, ``__expf``, the internal order of tensor-core accumulation), this file
+uses correctly rounded fp32 (``1/sqrt`` rounded once, ``exp``), fp32 accumulation for
+the two attention products and the head product, and a fixed sequential summation
+order for the LayerNorm statistics; every other rounding point is the reference's.
+"""
+
+from __future__ import annotations
+
+from dataclasses import dataclass, field
+from typing import Dict, List, Optional
+
+import numpy as np
+
+D, DFF, H, DH, T, L = 256, 1024, 8, 32, 32, 8
+N_CLOCK, N_REP, N_TYPE_SPECIAL = 101, 3, 12
+N_POLICY, N_PROMO = 64, 4
+EPS = np.float32(1e-5)
+F32, F16 = np.float32, np.float16
+
+#: Column ownership of the two halves of a row in the statistics' summation order:
+#: half 0 sums columns 0-63 then 128-191, half 1 sums 64-127 then 192-255; within a
+#: half even and odd columns accumulate separately, sequentially, then even + odd, then
+#: half 0 + half 1.
+_HALF_COLS = [np.r_[0:64, 128:192], np.r_[64:128, 192:256]]
+
+
+def f16(x) -> np.ndarray:
+    return np.asarray(x).astype(F16)
+
+
+def add_f16(a: np.ndarray, b: np.ndarray) -> np.ndarray:
+    """fp16 + fp16 rounded once to fp16 (float64 holds the exact sum)."""
+    return (a.astype(np.float64) + b.astype(np.float64)).astype(F16)
+
+
+# ---------------------------------------------------------------------------
+# weights
+# ---------------------------------------------------------------------------
+
+def quantise_weights_s8(w: np.ndarray):
+    """``[N, K]`` fp32 -> ``(q [N, K] int8, scale [N/128] fp32)``; one scale per 128
+    output rows over all of K, ``amax/127``, round-half-even, clamp +-127."""
+    n, k = w.shape
+    b = w.astype(F32).reshape(n // 128, 128 * k)
+    amax = np.abs(b).max(axis=1)
+    scale = np.where(amax > 0, amax / F32(127.0), F32(1.0)).astype(F32)
+    q = np.clip(np.rint(b / scale[:, None]), -127, 127).astype(np.int8)
+    return q.reshape(n, k), scale
+
+
+@dataclass
+class LayerW:
+    q_qkv: np.ndarray; s_qkv: np.ndarray; b_qkv: np.ndarray
+    q_o: np.ndarray; s_o: np.ndarray; b_o: np.ndarray
+    q_ff1: np.ndarray; s_ff1: np.ndarray; b_ff1: np.ndarray
+    q_ff2: np.ndarray; s_ff2: np.ndarray; b_ff2: np.ndarray
+
+
+@dataclass
+class Weights:
+    layers: List[LayerW]
+    emb: Dict[str, np.ndarray]            # fp16 tables
+    lnf_w: np.ndarray; lnf_b: np.ndarray  # fp16
+    head: np.ndarray                      # [96, 256] fp16
+    n_value: int
+    vmode: int
+
+
+def prepare(state: Dict[str, np.ndarray]) -> Weights:
+    """Fold, quantise and round a fp32 ``state_dict`` (numpy arrays)."""
+    s = {k: np.asarray(v) for k, v in state.items()}
+    n_layers = 1 + max(int(k.split(".")[2]) for k in s if k.startswith("encoder.layers."))
+    layers = []
+    for i in range(n_layers):
+        p = f"encoder.layers.{i}."
+        w_qkv = s[p + "self_attn.in_proj_weight"].astype(F32).copy()
+        b_qkv = s[p + "self_attn.in_proj_bias"].astype(F32).copy()
+        sc = F32(DH ** -0.5)
+        w_qkv[:D] *= sc
+        b_qkv[:D] *= sc
+        g1, e1 = s[p + "norm1.weight"].astype(F32), s[p + "norm1.bias"].astype(F32)
+        # bias uses W before gamma; the dot product is taken in float64 and rounded once
+        b_qkv = (b_qkv.astype(np.float64) + w_qkv.astype(np.float64) @ e1.astype(np.float64)).astype(F32)
+        w_qkv = w_qkv * g1[None, :]
+        w_ff1 = s[p + "linear1.weight"].astype(F32).copy()
+        b_ff1 = s[p + "linear1.bias"].astype(F32).copy()
+        g2, e2 = s[p + "norm2.weight"].astype(F32), s[p + "norm2.bias"].astype(F32)
+        b_ff1 = (b_ff1.astype(np.float64) + w_ff1.astype(np.float64) @ e2.astype(np.float64)).astype(F32)
+        w_ff1 = w_ff1 * g2[None, :]
+        q_qkv, s_qkv = quantise_weights_s8(w_qkv)
+        q_o, s_o = quantise_weights_s8(s[p + "self_attn.out_proj.weight"])
+        q_ff1, s_ff1 = quantise_weights_s8(w_ff1)
+        q_ff2, s_ff2 = quantise_weights_s8(s[p + "linear2.weight"])
+        layers.append(LayerW(q_qkv, s_qkv, f16(b_qkv), q_o, s_o,
+                             f16(s[p + "self_attn.out_proj.bias"]),
+                             q_ff1, s_ff1, f16(b_ff1), q_ff2, s_ff2,
+                             f16(s[p + "linear2.bias"])))
+    nv = int(s["value.weight"].shape[0])
+    head = np.zeros((96, D), dtype=F16)
+    head[:64] = f16(s["policy.weight"])
+    head[64:68] = f16(s["promo.weight"])
+    head[68:68 + nv] = f16(s["value.weight"])
+    emb = {k: f16(s[k + ".weight"]) for k in
+           ("emb_square", "emb_type_special", "emb_color_turn", "emb_clock", "emb_rep")}
+    vmode = int(s["value_mode"]) if "value_mode" in s else 0
+    return Weights(layers, emb, f16(s["norm_f.weight"]), f16(s["norm_f.bias"]), head, nv, vmode)
+
+
+# ---------------------------------------------------------------------------
+# stages
+# ---------------------------------------------------------------------------
+
+def embed(w: Weights, boards: np.ndarray, control: np.ndarray, rep: np.ndarray):
+    """``[n,32]`` words -> (``[n,32,256]`` fp16 tokens, ``[n,32]`` alive)."""
+    wd = boards.astype(np.int64) & 0xFFFF
+    ctl = control.astype(np.int64)
+    stm = (ctl < 0).astype(np.int64)
+    sq = wd & 63
+    ts = np.minimum(((wd >> 6) & 7) * 2 + ((wd >> 9) & 1), N_TYPE_SPECIAL - 1)
+    ct = ((wd >> 10) & 1) * 2 + stm[:, None]
+    clk = np.clip(np.abs(ctl) - 1, 0, N_CLOCK - 1)
+    rp = np.minimum(rep.astype(np.int64), N_REP - 1)
+    per_board = add_f16(w.emb["emb_clock"][clk], w.emb["emb_rep"][rp])
+    x = add_f16(w.emb["emb_square"][sq], w.emb["emb_type_special"][ts])
+    x = add_f16(x, w.emb["emb_color_turn"][ct])
+    x = add_f16(x, per_board[:, None, :])
+    return x, ((wd >> 11) & 1) == 0
+
+
+def _seq_sum(a: np.ndarray) -> np.ndarray:
+    return np.add.accumulate(a, axis=1, dtype=F32)[:, -1]
+
+
+def ln_stats(x16: np.ndarray):
+    """Row mean and 1/std of fp16 rows ``[M, 256]`` in the fixed summation order."""
+    x = x16.astype(F32)
+    s_half, q_half = [], []
+    for cols in _HALF_COLS:
+        v = x[:, cols]
+        sq = v * v                                 # exact: fp16 squares fit fp32
+        s_half.append((_seq_sum(v[:, 0::2]) + _seq_sum(v[:, 1::2])).astype(F32))
+        q_half.append((_seq_sum(sq[:, 0::2]) + _seq_sum(sq[:, 1::2])).astype(F32))
+    tot = (s_half[0] + s_half[1]).astype(F32)
+    totq = (q_half[0] + q_half[1]).astype(F32)
+    mean = (tot * F32(1.0 / 256)).astype(F32)
+    t = (totq * F32(1.0 / 256)).astype(F32)
+    var = (t.astype(np.float64) - mean.astype(np.float64) ** 2).astype(F32)   # one fma
+    var = np.maximum(var, F32(0))
+    v = (var + EPS).astype(F32)
+    rstd = (1.0 / np.sqrt(v.astype(np.float64))).astype(F32)
+    return mean, rstd
+
+
+def layernorm(x16: np.ndarray, gamma: Optional[np.ndarray] = None,
+              beta: Optional[np.ndarray] = None) -> np.ndarray:
+    mean, rstd = ln_stats(x16)
+    xn = ((x16.astype(F32) - mean[:, None]).astype(F32) * rstd[:, None]).astype(F32)
+    if gamma is not None:
+        xn = (xn.astype(np.float64) * gamma.astype(np.float64)[None, :]
+              + beta.astype(np.float64)[None, :]).astype(F32)
+    return xn.astype(F16)
+
+
+def quantise_rows(x16: np.ndarray, unsigned: bool = False):
+    """fp16 rows -> (int values as float32, per-row fp32 scale)."""
+    x = x16.astype(F32)
+    if unsigned:
+        amax = x.max(axis=1)
+        amax = np.maximum(amax, F32(0))
+        qmax = F32(255.0)
+    else:
+        amax = np.abs(x).max(axis=1)
+        qmax = F32(127.0)
+    sc = np.where(amax > 0, (amax / qmax).astype(F32), F32(1.0)).astype(F32)
+    inv = (F32(1.0) / sc).astype(F32)
+    q = np.rint((x * inv[:, None]).astype(F32))
+    q = np.clip(q, 0 if unsigned else -128, 255 if unsigned else 127).astype(F32)
+    return q, sc
+
+
+def gemm_int(q_a: np.ndarray, q_w: np.ndarray) -> np.ndarray:
+    """Exact integer product ``A @ W^T`` as float32.  Every partial sum is below
+    2^24 (255 * 127 * 256 = 8.29e6), so fp32 accumulation is exact in any order."""
+    return q_a.astype(F32) @ q_w.astype(F32).T
+
+
+def descale(acc: np.ndarray, sa: np.ndarray, sw_blocks: np.ndarray, n0: int = 0):
+    """``(float(acc) * sa[row]) * sw[col // 128]`` in fp32, two roundings."""
+    n = acc.shape[1]
+    sw = sw_blocks[(n0 + np.arange(n)) // 128].astype(F32)
+    return ((acc.astype(F32) * sa[:, None]).astype(F32) * sw[None, :]).astype(F32)
+
+
+def attention(q16, k16, v16, alive):
+    """``[n,32,256]`` fp16 Q, K, V (scale pre-folded) -> ``[n,32,256]`` fp16."""
+    n = q16.shape[0]
+    q = q16.astype(F32).reshape(n, T, H, DH).transpose(0, 2, 1, 3)
+    k = k16.astype(F32).reshape(n, T, H, DH).transpose(0, 2, 1, 3)
+    v = v16.astype(F32).reshape(n, T, H, DH).transpose(0, 2, 1, 3)
+    s = np.matmul(q, k.transpose(0, 1, 3, 2)).astype(F32)            # [n,H,32,32]
+    s = np.where(alive[:, None, None, :], s, F32(-np.inf))
+    with np.errstate(invalid="ignore"):
+        mx = s.max(axis=-1, keepdims=True)
+        p = np.exp((s - mx).astype(F32)).astype(F32)
+        inv = (F32(1.0) / p.sum(axis=-1, keepdims=True, dtype=F32)).astype(F32)
+        pn = (p * inv).astype(F16)
+    o = np.matmul(pn.astype(F32), v).astype(F32)
+    return o.transpose(0, 2, 1, 3).reshape(n, T, D).astype(F16)
+
+
+@dataclass
+class Trace:
+    """Optional per-stage outputs; keys follow the reference's ``debug_stage`` numbers
+    for layer 0 (9 embed, 1 LN1, 5/6/7 Q/K/V, 4 attention out, 2 residual after
+    attention, 3 LN2, 8 final norm) plus GEMM captures ``(layer, op)`` ->
+    ``(A int values, s32 accumulators)`` with op in qkv, out, ff1_c, ff2_c."""
+    stages: Dict[int, np.ndarray] = field(default_factory=dict)
+    gemms: Dict[tuple, tuple] = field(default_factory=dict)
+
+
+def forward(w: Weights, boards, control, rep, legal=None, trace: Optional[Trace] = None,
+            capture_layers=()):
+    """Boards to ``(policy fp16 [n,32,64], promo fp16 [n,32,4], value fp32 [n])``.
+
+    ``legal`` (``[n,32]`` uint64, bit s of word p set when the move p->s is legal) turns
+    every illegal policy entry into -inf, bitwise.
+    """
+    boards = np.asarray(boards)
+    control = np.asarray(control)
+    rep = np.asarray(rep)
+    n = boards.shape[0]
+    x, alive = embed(w, boards, control, rep)
+    if trace is not None:
+        trace.stages[9] = x.copy()
+    x = x.reshape(n * T, D)
+
+    def cap(layer, op, qa, acc):
+        if trace is not None and layer in capture_layers:
+            trace.gemms[(layer, op)] = (qa.copy(), acc.astype(np.int32))
+
+    for li, lw in enumerate(w.layers):
+        first = li == 0 and trace is not None
+        xn = layernorm(x)
+        if first:
+            trace.stages[1] = xn.reshape(n, T, D).copy()
+        qa, sa = quantise_rows(xn)
+        acc = gemm_int(qa, lw.q_qkv)
+        cap(li, "qkv", qa, acc)
+        qkv = add_f16(descale(acc, sa, lw.s_qkv).astype(F16), lw.b_qkv[None, :])
+        q16, k16, v16 = (qkv[:, i * D:(i + 1) * D].reshape(n, T, D) for i in range(3))
+        if first:
+            trace.stages[5], trace.stages[6], trace.stages[7] = q16.copy(), k16.copy(), v16.copy()
+        o = attention(q16, k16, v16, alive)
+        if first:
+            trace.stages[4] = o.copy()
+        qa, sa = quantise_rows(o.reshape(n * T, D))
+        acc = gemm_int(qa, lw.q_o)
+        cap(li, "out", qa, acc)
+        y = add_f16(descale(acc, sa, lw.s_o).astype(F16), lw.b_o[None, :])
+        x = add_f16(x, y)
+        if first:
+            trace.stages[2] = x.reshape(n, T, D).copy()
+        xn = layernorm(x)
+        if first:
+            trace.stages[3] = xn.reshape(n, T, D).copy()
+        qa, sa = quantise_rows(xn)
+        run = np.zeros((n * T, D), dtype=F16)
+        for c in range(DFF // 256):
+            acc = gemm_int(qa, lw.q_ff1[256 * c:256 * c + 256])
+            cap(li, f"ff1_{c}", qa, acc)
+            hid = add_f16(descale(acc, sa, lw.s_ff1, n0=256 * c).astype(F16),
+                          lw.b_ff1[None, 256 * c:256 * c + 256])
+            hid = np.maximum(hid, F16(0))
+            qh, sh = quantise_rows(hid, unsigned=True)
+            acc2 = gemm_int(qh, lw.q_ff2[:, 256 * c:256 * c + 256])
+            cap(li, f"ff2_{c}", qh, acc2)
+            o32 = (descale(acc2, sh, lw.s_ff2) + run.astype(F32)).astype(F32)
+            run = o32.astype(F16)
+        y = add_f16(run, lw.b_ff2[None, :])
+        x = add_f16(x, y)
+
+    hn = layernorm(x, w.lnf_w, w.lnf_b)
+    if trace is not None:
+        trace.stages[8] = hn.reshape(n, T, D).copy()
+    logits = (hn.astype(F32) @ w.head.astype(F32).T).astype(F16).reshape(n, T, 96)
+    policy = logits[:, :, :N_POLICY].copy()
+    promo = logits[:, :, N_POLICY:N_POLICY + N_PROMO].copy()
+    vcols = logits[:, :, 68:68 + w.n_value].astype(F32)
+    ctl = control.astype(np.int64)
+    if w.vmode == 0:
+        king = np.where(ctl < 0, 31, 15)
+        raw = vcols[np.arange(n), king]
+    elif w.vmode == 1:
+        m = alive.astype(F32)
+        raw = (vcols * m[:, :, None]).sum(axis=1, dtype=F32) / np.maximum(
+            m.sum(axis=1, dtype=F32), F32(1))[:, None]
+    else:
+        raise NotImplementedError("the prenorm value head is not restated here")
+    if w.n_value == 1:
+        value = np.tanh(raw[:, 0]).astype(F32)
+    else:
+        e = np.exp(raw - raw.max(axis=1, keepdims=True))
+        value = ((e[:, 2] - e[:, 0]) / e.sum(axis=1)).astype(F32)
+    if w.vmode != 0:
+        value = np.where(ctl < 0, -value, value).astype(F32)
+    if legal is not None:
+        bits = (np.asarray(legal).astype(np.uint64)[:, :, None]
+                >> np.arange(64, dtype=np.uint64)[None, None, :]) & np.uint64(1)
+        policy = np.where(bits.astype(bool), policy, F16(-np.inf))
+    return policy, promo, value
+
+
+def masked_argmax(policy: np.ndarray, legal: np.ndarray) -> np.ndarray:
+    """Argmax of ``where(legal, logit, -inf)`` over the 2048 moves, lowest index on
+    ties; -1 for a position with no legal move."""
+    n = policy.shape[0]
+    bits = ((np.asarray(legal).astype(np.uint64)[:, :, None]
+             >> np.arange(64, dtype=np.uint64)[None, None, :]) & np.uint64(1)).astype(bool)
+    flat = np.where(bits, policy.astype(F32), F32(-np.inf)).reshape(n, -1)
+    best = flat.argmax(axis=1)
+    return np.where(bits.reshape(n, -1).any(axis=1), best, -1)

@@ -1,0 +1,176 @@
+"""Generate the committed golden fixtures from the reference's own Python.
+
+Run in a container that holds the reference checkout (read-only), from the repo root:
+
+    PYTHONDONTWRITEBYTECODE=1 python tests/golden/make_golden.py --reference /root/reference
+
+It imports the reference (``brokefish.nn.model``, ``brokefish.nn.quant``,
+``brokefish.nn.cuda_impl._fold_norm``, ``brokefish.env.torch_impl``) on CPU and writes,
+next to this script:
+
+* ``positions_256_seed0.npz``, ``positions_4096_seed1.npz`` -- boards / control / rep /
+  legal-move words from uniformly random legal playouts of 0-120 plies with the
+  reference's move generator (the recipe of the reference's tests/boards.py, with a
+  per-position ply count);
+* ``ref_outputs_A.npz``, ``ref_outputs_B.npz`` -- for two seeded weight sets, the
+  reference network's fp32 outputs, its int8-emulated outputs, its fp16 embedding and
+  digests of its folded + quantised weights;
+* ``scheme_kats.npz`` -- known answers of the reference's int8 scheme functions.
+
+The fixtures are what ``tests/test_oracle_golden.py`` pins the CPU oracle against; the
+GPU box never needs the reference.
+"""
+
+from __future__ import annotations
+
+import argparse
+import hashlib
+import os
+import sys
+
+import numpy as np
+import torch
+
+HERE = os.path.dirname(os.path.abspath(__file__))
+ROOT = os.path.dirname(os.path.dirname(HERE))
+sys.path.insert(0, ROOT)
+
+
+def sha(a: np.ndarray) -> str:
+    return hashlib.sha256(np.ascontiguousarray(a).tobytes()).hexdigest()
+
+
+def playout_positions(env, n: int, seed: int, max_plies: int = 120):
+    """Uniform-random legal playouts, game i snapshotted after ``plies[i]`` moves."""
+    gen = torch.Generator(device="cpu").manual_seed(seed)
+    plies = torch.randint(0, max_plies + 1, (n,), generator=gen)
+    boards, control = env.initial_boards(n, device="cpu")
+    mask, _ = env.movegen(boards, control)
+    out_b, out_c, out_m = boards.clone(), control.clone(), mask.clone()
+    for ply in range(max_plies + 1):
+        snap = plies == ply
+        out_b[snap], out_c[snap], out_m[snap] = boards[snap], control[snap], mask[snap]
+        if ply == max_plies:
+            break
+        legal = env.bitset_to_bool(mask).reshape(n, 32 * 64)
+        counts = legal.sum(dim=1)
+        live = counts > 0
+        r = torch.rand(n, generator=gen)
+        pick = (r * counts.clamp(min=1).float()).long()
+        pick = torch.minimum(pick, (counts - 1).clamp(min=0))
+        move = (legal.cumsum(dim=1) > pick[:, None]).float().argmax(dim=1)
+        move = torch.where(live, move, torch.zeros_like(move))
+        promo = torch.randint(0, 4, (n,), generator=gen)
+        nb, nc, nm, _ = env.play(boards, control, move.to(torch.int64), promo=promo)
+        boards = torch.where(live[:, None], nb, boards)
+        control = torch.where(live, nc, control)
+        mask = torch.where(live[:, None], nm, mask)
+        if ply % 20 == 0:
+            print(f"  ply {ply}: {int(live.sum())}/{n} games live", flush=True)
+    rep = (torch.arange(n) % 3).to(torch.uint8)
+    return (out_b.numpy().astype(np.int16), out_c.numpy().astype(np.int16),
+            rep.numpy(), out_m.numpy().astype(np.int64).view(np.uint64), plies.numpy())
+
+
+def main() -> int:
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--reference", default="/root/reference")
+    ap.add_argument("--skip-positions", action="store_true")
+    args = ap.parse_args()
+    sys.path.insert(0, args.reference)
+    sys.dont_write_bytecode = True
+    torch.manual_seed(0)
+
+    from brokefish.env import torch_impl as env                      # reference
+    from brokefish.nn import quant as rq                             # reference
+    from brokefish.nn.cuda_impl import _fold_norm                    # reference
+    from brokefish.nn.model import BrokefishNet as RefNet            # reference
+    from brokefish_b200.nn.model import seeded_state                 # ours: weights by seed
+
+    for n, seed in ((256, 0), (4096, 1)):
+        path = os.path.join(HERE, f"positions_{n}_seed{seed}.npz")
+        if args.skip_positions and os.path.exists(path):
+            continue
+        print(f"positions n={n} seed={seed}", flush=True)
+        b, c, r, m, plies = playout_positions(env, n, seed)
+        np.savez_compressed(path, boards=b, control=c, rep=r, legal=m, plies=plies)
+
+    pos = np.load(os.path.join(HERE, "positions_256_seed0.npz"))
+    boards = torch.from_numpy(pos["boards"])
+    control = torch.from_numpy(pos["control"])
+    rep = torch.from_numpy(pos["rep"])
+
+    sets = {"A": dict(seed=0, std=0.02, perturb_norms=False),
+            "B": dict(seed=0, std=None, perturb_norms=True)}
+    for name, kw in sets.items():
+        print(f"weight set {name}", flush=True)
+        state = seeded_state(**kw)
+        net = RefNet().eval()
+        net.load_state_dict(state, strict=True)
+        out = {"state_sha": sha(np.concatenate(
+            [state[k].numpy().reshape(-1).astype(np.float32) for k in sorted(state)]))}
+        n_fp32, n_emu = 64, 32
+        with torch.no_grad():
+            p, pr, v = net(boards[:n_fp32], control[:n_fp32], rep[:n_fp32])
+            out["fp32_policy"] = p.numpy().astype(np.float32)
+            out["fp32_promo"] = pr.numpy().astype(np.float32)
+            out["fp32_value"] = v.numpy().astype(np.float32)
+            fwd = rq.emulated_forward(net, rq.QuantConfig(fmt="int8"))
+            p, pr, v = fwd(boards[:n_emu], control[:n_emu], rep[:n_emu])
+            out["emu_policy"] = p.numpy().astype(np.float32)
+            out["emu_promo"] = pr.numpy().astype(np.float32)
+            out["emu_value"] = v.numpy().astype(np.float32)
+            half = RefNet().eval()
+            half.load_state_dict(state, strict=True)
+            half = half.half()
+            x, alive = half.embed(boards, control, rep)
+            out["embed_sha"] = sha(x.numpy())
+            out["embed_first4"] = x[:4].numpy()
+            out["alive"] = alive.numpy()
+        # folded + quantised weights exactly as the reference constructor derives them
+        # (brokefish/nn/cuda_impl.py:194-210, 356-369)
+        digests, fb_qkv, fb_ff1 = [], [], []
+        for li, lay in enumerate(net.encoder.layers):
+            w_qkv = lay.self_attn.in_proj_weight.detach().float().clone()
+            b_qkv = lay.self_attn.in_proj_bias.detach().float().clone()
+            w_qkv[:256] *= 32 ** -0.5
+            b_qkv[:256] *= 32 ** -0.5
+            w_ff1 = lay.linear1.weight.detach().float().clone()
+            b_ff1 = lay.linear1.bias.detach().float().clone()
+            w_qkv, b_qkv = _fold_norm(w_qkv, b_qkv, lay.norm1)
+            w_ff1, b_ff1 = _fold_norm(w_ff1, b_ff1, lay.norm2)
+            for tag, wmat in (("qkv", w_qkv), ("o", lay.self_attn.out_proj.weight.detach()),
+                              ("ff1", w_ff1), ("ff2", lay.linear2.weight.detach())):
+                qb, sc = rq.quantise_weights_int8_bytes(wmat.float())
+                digests.append(f"{li}.{tag}.q={sha(qb.numpy())}")
+                digests.append(f"{li}.{tag}.s={sha(sc.numpy())}")
+            fb_qkv.append(b_qkv.half().numpy())
+            fb_ff1.append(b_ff1.half().numpy())
+        out["weight_digests"] = np.array(digests)
+        out["folded_b_qkv"] = np.stack(fb_qkv)
+        out["folded_b_ff1"] = np.stack(fb_ff1)
+        np.savez_compressed(os.path.join(HERE, f"ref_outputs_{name}.npz"), **out)
+
+    print("scheme known answers", flush=True)
+    g = torch.Generator().manual_seed(1234)
+    wmat = torch.randn(256, 256, generator=g) * 0.05
+    wmat[128:] *= 3.0
+    qb, sc = rq.quantise_weights_int8_bytes(wmat)
+    acts = torch.randn(16, 256, generator=g)
+    acts[3] = 0.0
+    acts[4, :8] = torch.tensor([0.5, 1.5, 2.5, -0.5, -1.5, -2.5, 127.0, -127.0])
+    acts16 = acts.half().float()
+    qs, ss = rq.quantise_activations_int8(acts16)
+    qu, su = rq.quantise_activations_int8(acts16.relu(), unsigned=True)
+    lin = rq.int8_linear(acts16, wmat, torch.linspace(-1, 1, 256))
+    np.savez_compressed(os.path.join(HERE, "scheme_kats.npz"),
+                        w=wmat.numpy(), w_q=qb.numpy(), w_s=sc.numpy(),
+                        acts=acts16.numpy(), q_s8=qs.numpy(), s_s8=ss.numpy(),
+                        q_u8=qu.numpy(), s_u8=su.numpy(), lin=lin.numpy(),
+                        q_max=np.array([rq.Q_MAX_S8, rq.Q_MAX_U8]))
+    print("done")
+    return 0
+
+
+if __name__ == "__main__":
+    raise SystemExit(main())

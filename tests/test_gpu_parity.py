@@ -1,0 +1,309 @@
+"""Parity of the sm_100a kernel against the CPU oracle, through the C ABI.
+
+Bars (stated by the task for this path): s32 GEMM accumulators bit-exact; fp16 logits
+within max-abs 2e-2; value within 8e-3 (the reference's own VALUE_TOL,
+tests/test_b2.py:28); masked-policy argmax agreement >= 99.9 % over non-terminal
+positions."""
+import ctypes
+
+import numpy as np
+import pytest
+import torch
+
+from oracle import int8_encoder as O
+
+pytestmark = pytest.mark.gpu
+
+LOGIT_TOL = 2e-2
+VALUE_TOL = 8e-3
+
+
+def dev(a):
+    return torch.from_numpy(np.ascontiguousarray(a)).cuda()
+
+
+def inputs(pos, sl):
+    return dev(pos["boards"][sl]), dev(pos["control"][sl]), dev(pos["rep"][sl])
+
+
+@pytest.fixture(scope="module")
+def encoders(nets):
+    from brokefish_b200.nn import encoder_impl
+    out = {k: encoder_impl("cuda")(n) for k, n in nets.items()}
+    yield out
+    for e in out.values():
+        e.close()
+
+
+def aligned_oracle(oracle_weights, name, enc):
+    """The oracle's weights with its two folded biases replaced by the product's after
+    checking they agree to one fp16 step (the fold is a BLAS dot product whose summation
+    order differs between numpy and torch)."""
+    import copy
+    from brokefish_b200.nn.pack import fold_and_quantise
+    w = copy.deepcopy(oracle_weights[name])
+    for lw, fl in zip(w.layers, fold_and_quantise(enc.net)):
+        for attr in ("b_qkv", "b_ff1"):
+            a, b = getattr(lw, attr), getattr(fl, attr)
+            assert np.abs(a.view(np.int16).astype(np.int32) - b.view(np.int16).astype(np.int32)).max() <= 1
+            setattr(lw, attr, b.copy())
+    return w
+
+
+# ---------------------------------------------------------------- tensor-core self test
+@pytest.mark.parametrize("mode", [0, 1, 2, 3])
+def test_umma_tile_against_exact_integer_product(mode):
+    """One tcgen05 GEMM tile against an exact host product (the method of the reference's
+    csrc/tests/tint8.cu:268-337): operands span the full range including -128/255."""
+    from brokefish_b200 import _native
+    from brokefish_b200.nn.pack import sw128_image
+    rng = np.random.default_rng(mode)
+    n = {0: 128, 1: 128, 2: 192, 3: 96}[mode]
+    if mode == 3:
+        a = (rng.standard_normal((128, 256)) * 0.5).astype(np.float16)
+        w = (rng.standard_normal((n, 256)) * 0.5).astype(np.float16)
+        a_bytes, w_bytes = a.view(np.uint8), w.view(np.uint8)
+        want = a.astype(np.float64) @ w.astype(np.float64).T
+    else:
+        a = rng.integers(0 if mode == 1 else -128, 256 if mode == 1 else 128, size=(128, 256))
+        w = rng.integers(-128, 128, size=(n, 256))
+        a[0, :] = 255 if mode == 1 else -128
+        w[0, :] = -128
+        a_bytes = a.astype(np.uint8 if mode == 1 else np.int8).view(np.uint8)
+        w_bytes = w.astype(np.int8).view(np.uint8)
+        want = a.astype(np.int64) @ w.astype(np.int64).T
+    slabs = w_bytes.shape[1] // 128
+    image = np.concatenate([sw128_image(np.ascontiguousarray(w_bytes[:, 128 * s:128 * s + 128]))
+                            for s in range(slabs)])
+    d_a, d_w = dev(a_bytes), dev(image)
+    d_out = torch.zeros(128, n, dtype=torch.int32, device="cuda")
+    _native.check(_native.lib().bf_selftest_umma(0, mode, ctypes.c_void_p(d_a.data_ptr()),
+                                                 ctypes.c_void_p(d_w.data_ptr()),
+                                                 ctypes.c_void_p(d_out.data_ptr())), "selftest")
+    got = d_out.cpu().numpy()
+    if mode == 3:
+        got = got.view(np.float32)
+        assert np.abs(got - want).max() <= 1e-3
+    else:
+        assert np.array_equal(got.astype(np.int64), want)
+
+
+# ---------------------------------------------------------------- stages
+@pytest.mark.parametrize("name", ["A", "B"])
+def test_embedding_is_bit_exact(name, encoders, oracle_weights, pos256):
+    enc = encoders[name]
+    got = enc.forward_stage(*inputs(pos256, slice(0, 256)), 9).cpu().numpy()
+    want, _ = O.embed(oracle_weights[name], pos256["boards"], pos256["control"], pos256["rep"])
+    assert np.array_equal(got.view(np.uint16), want.view(np.uint16))
+    enc.check_status()
+
+
+@pytest.mark.parametrize("name", ["A", "B"])
+def test_layer0_stages(name, encoders, oracle_weights, pos256):
+    """LN1, Q/K/V and LN2-side stages of layer 0.  LN1 and Q/K/V are reproducible exactly;
+    downstream of the first attention a few fp16 last-place differences are expected."""
+    enc = encoders[name]
+    w = aligned_oracle(oracle_weights, name, enc)
+    sl = slice(0, 32)
+    tr = O.Trace()
+    O.forward(w, pos256["boards"][sl], pos256["control"][sl], pos256["rep"][sl], trace=tr)
+    live = ((pos256["boards"][sl].view(np.uint16) >> 11) & 1) == 0
+    for stage in (1, 5, 6, 7):
+        got = enc.forward_stage(*inputs(pos256, sl), stage).cpu().numpy()
+        assert np.array_equal(got.view(np.uint16), tr.stages[stage].view(np.uint16)), stage
+    for stage, tol in ((4, 2e-3), (2, 4e-3), (3, 8e-3), (8, 3e-2)):
+        got = enc.forward_stage(*inputs(pos256, sl), stage).cpu().numpy().astype(np.float32)
+        want = tr.stages[stage].astype(np.float32)
+        err = np.abs(got - want)
+        assert np.isfinite(got).all()
+        assert err.max() <= tol * max(1.0, np.abs(want).max()), (stage, err.max())
+        if stage in (4, 2, 3):
+            assert (err[live] == 0).mean() >= 0.98, (stage, (err[live] == 0).mean())
+    enc.check_status()
+
+
+# ---------------------------------------------------------------- accumulators
+@pytest.mark.parametrize("name,layer", [("A", 0), ("B", 0), ("A", 5), ("B", 7)])
+def test_s32_accumulators_are_bit_exact(name, layer, encoders, oracle_weights, pos256):
+    """Every weight GEMM of a layer: the captured A bytes times the packed s8 weights,
+    recomputed on the host in int64, equals the captured tensor-core accumulators."""
+    from brokefish_b200.nn.pack import qkv_chunk_rows
+    enc = encoders[name]
+    lw = oracle_weights[name].layers[layer]
+    sl = slice(100, 133)            # 33 boards: a ragged last tile
+    args = inputs(pos256, sl)
+    perm = qkv_chunk_rows().reshape(-1)
+    cases = [(0, lw.q_qkv[perm], False), (1, lw.q_o, False), (2, lw.q_ff1, False)]
+    cases += [(3 + c, lw.q_ff2[:, 256 * c:256 * c + 256], True) for c in range(4)]
+    for op, wq, unsigned in cases:
+        a, acc = enc.capture_gemm(*args, layer=layer, op=op)
+        a = a.cpu().numpy()
+        a_int = a.astype(np.int64) if unsigned else a.view(np.int8).astype(np.int64)
+        want = a_int @ wq.astype(np.int64).T
+        assert np.array_equal(acc.cpu().numpy().astype(np.int64), want), (op,)
+        assert a_int.any()
+    enc.check_status()
+
+
+@pytest.mark.parametrize("name", ["A", "B"])
+def test_layer0_operands_equal_the_oracles(name, encoders, oracle_weights, pos256):
+    """The quantised LN1 operand of layer 0 and its accumulators against the oracle's."""
+    from brokefish_b200.nn.pack import qkv_chunk_rows
+    enc = encoders[name]
+    sl = slice(0, 16)
+    tr = O.Trace()
+    O.forward(oracle_weights[name], pos256["boards"][sl], pos256["control"][sl], pos256["rep"][sl],
+              trace=tr, capture_layers=(0,))
+    qa, acc = tr.gemms[(0, "qkv")]
+    a, got = enc.capture_gemm(*inputs(pos256, sl), layer=0, op=0)
+    assert np.array_equal(a.cpu().numpy().view(np.int8).astype(np.float32), qa)
+    assert np.array_equal(got.cpu().numpy(), acc[:, qkv_chunk_rows().reshape(-1)])
+
+
+# ---------------------------------------------------------------- outputs
+@pytest.mark.parametrize("name", ["A", "B"])
+def test_logits_value_and_argmax(name, encoders, oracle_weights, pos256):
+    enc = encoders[name]
+    w = aligned_oracle(oracle_weights, name, enc)
+    sl = slice(0, 256)
+    pol, pro, val = (t.cpu().numpy() for t in enc.forward_full(*inputs(pos256, sl)))
+    enc.check_status()
+    opol, opro, oval = O.forward(w, pos256["boards"][sl], pos256["control"][sl], pos256["rep"][sl])
+    assert np.isfinite(pol.astype(np.float32)).all() and np.isfinite(val).all()
+    assert np.abs(pol.astype(np.float32) - opol.astype(np.float32)).max() <= LOGIT_TOL
+    assert np.abs(pro.astype(np.float32) - opro.astype(np.float32)).max() <= LOGIT_TOL
+    assert np.abs(val - oval).max() <= VALUE_TOL
+    legal = pos256["legal"][sl]
+    mine, theirs = O.masked_argmax(pol, legal), O.masked_argmax(opol, legal)
+    playable = theirs >= 0
+    assert (mine[playable] == theirs[playable]).mean() >= 0.999
+    assert (mine[~playable] == -1).all()
+
+
+def test_against_reference_fp32_golden(encoders, pos256):
+    """The reference's own bar for a quantised path: 8 % of max|logit| against its fp32
+    network (tests/test_quant.py:342-356), on the committed reference outputs."""
+    import os
+    from conftest import GOLDEN
+    for name in ("A", "B"):
+        g = np.load(os.path.join(GOLDEN, f"ref_outputs_{name}.npz"))
+        n = g["fp32_policy"].shape[0]
+        pol, pro, val = (t.cpu().numpy() for t in encoders[name].forward_full(*inputs(pos256, slice(0, n))))
+        top = np.abs(g["fp32_policy"]).max()
+        assert np.abs(pol.astype(np.float32) - g["fp32_policy"]).max() <= 0.08 * top
+        assert np.abs(pro.astype(np.float32) - g["fp32_promo"]).max() <= 0.08 * top
+        assert np.abs(val - g["fp32_value"]).max() <= 0.08
+
+
+def test_legal_mask_is_a_bitwise_select(encoders, pos256):
+    enc = encoders["A"]
+    sl = slice(0, 67)
+    raw = enc.forward_full(*inputs(pos256, sl))[0].cpu().numpy()
+    legal = pos256["legal"][sl]
+    msk = enc.forward_full(*inputs(pos256, sl), legal=dev(legal.view(np.int64)))[0].cpu().numpy()
+    bits = ((legal[:, :, None] >> np.arange(64, dtype=np.uint64)) & np.uint64(1)).astype(bool)
+    assert np.array_equal(msk.view(np.uint16)[bits], raw.view(np.uint16)[bits])
+    assert (msk.view(np.uint16)[~bits] == 0xFC00).all()
+
+
+def test_deterministic_and_independent_of_batch_composition(encoders, pos256):
+    """Same bytes on a repeat, and a position's outputs do not depend on which positions
+    share its launch or its tile (the reference's tests/test_quant.py:309-339)."""
+    enc = encoders["B"]
+    full = [t.cpu().numpy().copy() for t in enc.forward_full(*inputs(pos256, slice(0, 256)))]
+    again = [t.cpu().numpy().copy() for t in enc.forward_full(*inputs(pos256, slice(0, 256)))]
+    for a, b in zip(full, again):
+        assert np.array_equal(a.view(np.uint8), b.view(np.uint8))
+    for n in (1, 2, 3, 5, 31, 33, 127):
+        part = [t.cpu().numpy() for t in enc.forward_full(*inputs(pos256, slice(7, 7 + n)))]
+        for a, b in zip(full, part):
+            assert np.array_equal(a[7:7 + n].view(np.uint8), b.view(np.uint8)), n
+    enc.check_status()
+
+
+def test_dead_slots_are_inert(encoders, pos256):
+    """Rewriting a captured slot's word cannot happen (it is 0x800 by definition), but a
+    dead token's *embedding inputs* must not reach live tokens: flipping rep/clock-free
+    fields is not possible either, so the check is the reference's (tests/test_b2.py:
+    270-293): outputs of live rows are unchanged when dead rows' words get other
+    colour/type/square bits."""
+    enc = encoders["A"]
+    b = pos256["boards"][:64].copy()
+    dead = ((b.view(np.uint16) >> 11) & 1) == 1
+    assert dead.any()
+    base = enc.forward_full(dev(b), dev(pos256["control"][:64]), dev(pos256["rep"][:64]))[0].cpu().numpy().copy()
+    b2 = b.copy()
+    b2.view(np.uint16)[dead] = 0x800 | 0x400 | (3 << 6) | 17
+    got = enc.forward_full(dev(b2), dev(pos256["control"][:64]), dev(pos256["rep"][:64]))[0].cpu().numpy()
+    assert np.array_equal(base.view(np.uint16)[~dead], got.view(np.uint16)[~dead])
+
+
+def test_full_size_batch_properties(encoders, oracle_weights, pos4096):
+    """Batch 4096 (the configuration the metric is quoted on): finite outputs, value in
+    [-1, 1], equal to the same positions evaluated in small launches, and within
+    tolerance of the oracle on a 384-position sample."""
+    enc = encoders["A"]
+    args = inputs(pos4096, slice(0, 4096))
+    pol, pro, val = (t.cpu().numpy().copy() for t in enc.forward_full(*args))
+    enc.check_status()
+    assert np.isfinite(pol.astype(np.float32)).all() and np.isfinite(pro.astype(np.float32)).all()
+    assert np.abs(val).max() <= 1.0
+    for lo in (0, 1111, 4000):
+        part = enc.forward_full(*inputs(pos4096, slice(lo, lo + 96)))[0].cpu().numpy()
+        assert np.array_equal(part.view(np.uint16), pol[lo:lo + 96].view(np.uint16))
+    idx = np.arange(0, 4096, 4096 // 384)[:384]
+    w = aligned_oracle(oracle_weights, "A", enc)
+    opol, _, oval = O.forward(w, pos4096["boards"][idx], pos4096["control"][idx], pos4096["rep"][idx])
+    assert np.abs(pol[idx].astype(np.float32) - opol.astype(np.float32)).max() <= LOGIT_TOL
+    assert np.abs(val[idx] - oval).max() <= VALUE_TOL
+    legal = pos4096["legal"][idx]
+    mine, theirs = O.masked_argmax(pol[idx], legal), O.masked_argmax(opol, legal)
+    ok = theirs >= 0
+    assert (mine[ok] == theirs[ok]).mean() >= 0.999
+
+
+def test_end_to_end_host_call_matches_device_call(encoders, pos256):
+    enc = encoders["A"]
+    n = 200
+    b = torch.from_numpy(pos256["boards"][:n].copy()).pin_memory()
+    c = torch.from_numpy(pos256["control"][:n].copy()).pin_memory()
+    r = torch.from_numpy(pos256["rep"][:n].copy()).pin_memory()
+    pol = torch.empty(n, 32, 64, dtype=torch.half).pin_memory()
+    pro = torch.empty(n, 32, 4, dtype=torch.half).pin_memory()
+    val = torch.empty(n, dtype=torch.float).pin_memory()
+    enc.forward_host(b, c, r, pol, pro, val)
+    dpol, dpro, dval = (t.cpu() for t in enc.forward_full(b.cuda(), c.cuda(), r.cuda()))
+    assert torch.equal(pol.view(torch.int16), dpol.view(torch.int16))
+    assert torch.equal(pro.view(torch.int16), dpro.view(torch.int16))
+    assert torch.equal(val, dval)
+
+
+def test_value_head_variants(pos256):
+    """Win/draw/loss rows and the pooled head (the reference's tests/test_b2.py:404-690)."""
+    from brokefish_b200.nn import encoder_impl
+    from brokefish_b200.nn.model import BrokefishNet, seeded_state
+    for nv, head in ((3, "king"), (1, "pooled"), (3, "pooled")):
+        st = seeded_state(seed=5, std=None, perturb_norms=True, n_value=nv, value_head=head)
+        net = BrokefishNet(n_value=nv, value_head=head).eval()
+        net.load_state_dict(st)
+        enc = encoder_impl("cuda")(net)
+        w = O.prepare({k: v.numpy() for k, v in st.items()})
+        sl = slice(0, 48)
+        val = enc.forward_full(*inputs(pos256, sl))[2].cpu().numpy()
+        oval = O.forward(w, pos256["boards"][sl], pos256["control"][sl], pos256["rep"][sl])[2]
+        assert np.abs(val - oval).max() <= 2e-2, (nv, head)
+        enc.close()
+
+
+def test_input_rejection_and_empty_batch(encoders):
+    enc = encoders["A"]
+    z = torch.zeros(0, 32, dtype=torch.int16, device="cuda")
+    p, pr, v = enc.forward_full(z, torch.zeros(0, dtype=torch.int16, device="cuda"),
+                                torch.zeros(0, dtype=torch.uint8, device="cuda"))
+    assert p.shape == (0, 32, 64) and v.shape == (0,)
+    b = torch.zeros(2, 32, dtype=torch.int16)
+    with pytest.raises(ValueError):
+        enc.forward_full(b, torch.ones(2, dtype=torch.int16), torch.zeros(2, dtype=torch.uint8))
+    with pytest.raises(ValueError):
+        enc.forward_stage(b.cuda(), torch.ones(2, dtype=torch.int16, device="cuda"),
+                          torch.zeros(2, dtype=torch.uint8, device="cuda"), 42)

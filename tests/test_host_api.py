@@ -1,0 +1,111 @@
+"""Host-side behaviour of the reference-facing Python surface that needs no GPU."""
+import numpy as np
+import pytest
+import torch
+
+from brokefish_b200.nn import encoder_impl, available, why_unavailable, IMPLEMENTATIONS
+from brokefish_b200.nn.cuda_impl import FusedEncoder, SCHEMES, SCHEME
+from brokefish_b200.nn.model import BrokefishNet, net_for_state, seeded_state
+from brokefish_b200.nn import quant
+from brokefish_b200.evaluator import make_evaluator, shard_bounds
+
+
+def test_registry():
+    assert IMPLEMENTATIONS == ("cuda",)
+    assert encoder_impl("cuda") is FusedEncoder
+    with pytest.raises(ValueError):
+        encoder_impl("triton")
+    got = available()
+    assert got in ([], ["cuda"])
+    if not got:
+        assert "cuda" in why_unavailable()
+    assert SCHEMES[SCHEME] == 3
+
+
+def test_constructor_refusals(nets):
+    net = nets["A"]
+    with pytest.raises(ValueError):
+        FusedEncoder(net, acc_dtype="bf16")
+    with pytest.raises(NotImplementedError):
+        FusedEncoder(net, acc_dtype="fp32")
+    with pytest.raises(NotImplementedError):
+        FusedEncoder(net, fp8=True, int8=False)
+    with pytest.raises(NotImplementedError):
+        FusedEncoder(net, int8=False)
+    with pytest.raises(ValueError):
+        FusedEncoder(net, int8_scheme="nope")
+    with pytest.raises(ValueError):
+        FusedEncoder(BrokefishNet(d_ff=512))
+    # a bare encoder stack is accepted but has no boards->logits path
+    bare = FusedEncoder(net.encoder)
+    z = torch.zeros(1, 32, dtype=torch.int16)
+    with pytest.raises(ValueError):
+        bare.forward_full(z, torch.ones(1, dtype=torch.int16), torch.zeros(1, dtype=torch.uint8))
+    with pytest.raises(NotImplementedError):
+        bare(torch.zeros(1, 32, 256))
+
+
+def test_input_checks():
+    chk = FusedEncoder._check_inputs
+    b = torch.zeros(3, 32, dtype=torch.int16)
+    c = torch.ones(3, dtype=torch.int16)
+    r = torch.zeros(3, dtype=torch.uint8)
+    assert chk(b, c, r) == 3
+    for bad in ((b[:, :31], c, r), (b.int(), c, r), (b, c[:2], r), (b, c.int(), r), (b, c, r.int())):
+        with pytest.raises(ValueError):
+            chk(*bad)
+
+
+def test_model_mirror_matches_reference_fp32_outputs(nets, pos256):
+    import os
+    from conftest import GOLDEN
+    for name in ("A", "B"):
+        g = np.load(os.path.join(GOLDEN, f"ref_outputs_{name}.npz"))
+        n = g["fp32_policy"].shape[0]
+        ev = make_evaluator(nets[name], None)
+        with torch.no_grad():
+            p, pr, v = ev(torch.from_numpy(pos256["boards"][:n]), torch.from_numpy(pos256["control"][:n]),
+                          torch.from_numpy(pos256["rep"][:n]))
+        assert np.abs(p.numpy() - g["fp32_policy"]).max() < 1e-4
+        assert np.abs(pr.numpy() - g["fp32_promo"]).max() < 1e-4
+        assert np.abs(v.numpy() - g["fp32_value"]).max() < 1e-4
+
+
+def test_state_dict_round_trip_and_variants():
+    st = seeded_state(seed=3, n_value=3, value_head="pooled")
+    net = net_for_state(st)
+    net.load_state_dict(st)
+    assert net.n_value == 3 and net.value_head == "pooled" and net.value_absolute
+    with pytest.raises(ValueError):
+        BrokefishNet(n_value=2)
+    with pytest.raises(NotImplementedError):
+        BrokefishNet(reinject="ln1")
+
+
+def test_scheme_functions_against_reference_answers():
+    import os
+    from conftest import GOLDEN
+    k = np.load(os.path.join(GOLDEN, "scheme_kats.npz"))
+    qb, sc = quant.quantise_weights_int8_bytes(torch.from_numpy(k["w"]))
+    assert np.array_equal(qb.numpy(), k["w_q"]) and np.array_equal(sc.numpy(), k["w_s"])
+    q, s = quant.quantise_activations_int8(torch.from_numpy(k["acts"]))
+    assert np.array_equal(q.numpy(), k["q_s8"]) and np.array_equal(s.numpy(), k["s_s8"])
+    q, s = quant.quantise_activations_int8(torch.from_numpy(k["acts"]).relu(), unsigned=True)
+    assert np.array_equal(q.numpy(), k["q_u8"]) and np.array_equal(s.numpy(), k["s_u8"])
+    lin = quant.int8_linear(torch.from_numpy(k["acts"]), torch.from_numpy(k["w"]), torch.linspace(-1, 1, 256))
+    assert np.array_equal(lin.numpy(), k["lin"])
+    assert (quant.Q_MAX_S8, quant.Q_MAX_U8) == tuple(k["q_max"])
+    with pytest.raises(ValueError):
+        quant.quantise_weights_int8_bytes(torch.zeros(100, 256))
+
+
+def test_shard_bounds():
+    for n in (0, 1, 7, 4096, 131072):
+        for world in (1, 2, 3, 8):
+            cuts = [shard_bounds(n, world, r) for r in range(world)]
+            assert cuts[0][0] == 0 and cuts[-1][1] == n
+            assert all(a[1] == b[0] for a, b in zip(cuts, cuts[1:]))
+            sizes = [hi - lo for lo, hi in cuts]
+            assert max(sizes) - min(sizes) <= 1
+    with pytest.raises(ValueError):
+        shard_bounds(4, 2, 2)
