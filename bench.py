@@ -1,0 +1,264 @@
+"""Benchmark of the network-evaluation hot path: positions evaluated per second.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference] [--batch B]
+
+One step = one pass of the evaluator over one batch of positions per GPU (batch 4096,
+the reference's self-play leaf-evaluation batch).  For N > 1 launch under
+``python -m torch.distributed.run --nproc-per-node N``; every rank holds a full copy of
+the weights (one broadcast from rank 0 before the timed loop), evaluates its own 4096
+positions and nothing is exchanged on the evaluation path ("weak" scaling: N x 4096
+positions per step).  ``--total 131072`` instead splits a fixed 131072-position step
+evenly across the ranks.
+
+Rank 0 prints one JSON line.  ``value`` is device-timed with inputs resident in HBM;
+``e2e`` is the same metric through the host-buffer C-ABI call with both copies inside
+the timed region; ``roofline`` is the int8 tensor throughput of the one kernel against
+twice the measured dense bf16 peak; ``cpu_baseline`` is the reference's fp32 PyTorch
+evaluator (restated in ``oracle/fp32_model.py``) on the host cores.
+"""
+
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import subprocess
+import sys
+import threading
+import time
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+if ROOT not in sys.path:
+    sys.path.insert(0, ROOT)
+
+import numpy as np
+import torch
+
+OPS_PER_POSITION = 402653184          # int8 ops of the 32 weight GEMMs of one position
+BYTES_IN, BYTES_OUT = 67, 4356        # boards+control+rep ; policy+promo+value
+METRIC = "positions evaluated/sec at batch 4096 int8"
+WORKLOAD = ("8-layer d256 h8 ff1024 int8 evaluator, N(0,0.02) seed-0 weights, seeded "
+            "random-playout positions, batch 4096 per GPU")
+
+
+def load_positions(n: int):
+    """``n`` positions: the committed 4096 random-playout positions, tiled when more are
+    asked for (a tile keeps the distribution of piece counts, clocks and side to move)."""
+    z = np.load(os.path.join(ROOT, "tests", "golden", "positions_4096_seed1.npz"))
+    reps = (n + 4095) // 4096
+    take = lambda a: np.ascontiguousarray(np.concatenate([a] * reps)[:n])
+    return take(z["boards"]), take(z["control"]), take(z["rep"]), take(z["legal"])
+
+
+def peaks():
+    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(path):
+        m = json.load(open(path))
+        return 2.0 * float(m["bf16_tflops"]), "2 x measured dense bf16 burst (MEASURED_PEAKS.json)"
+    return 2.0 * 1590.0, "2 x fallback dense bf16 (1.59 PFLOP/s)"
+
+
+class ClockSampler:
+    """Samples SM clock and throttle reasons with nvidia-smi while the timed region runs."""
+
+    def __init__(self, index: int):
+        self.rows, self.proc, self.index = [], None, index
+
+    def start(self):
+        q = ("clocks.sm,clocks.max.sm,clocks_event_reasons.hw_slowdown,"
+             "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,"
+             "clocks_event_reasons.sw_power_cap")
+        try:
+            self.proc = subprocess.Popen(
+                ["nvidia-smi", f"--id={self.index}", f"--query-gpu={q}", "--format=csv,noheader,nounits",
+                 "-lms", "100"], stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+            threading.Thread(target=self._read, daemon=True).start()
+        except OSError:
+            self.proc = None
+
+    def _read(self):
+        for line in self.proc.stdout:
+            self.rows.append([c.strip() for c in line.split(",")])
+
+    def stop(self):
+        if self.proc is None:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
+        self.proc.terminate()
+        try:
+            self.proc.wait(timeout=5)
+        except Exception:
+            pass
+        sm = [float(r[0]) for r in self.rows if len(r) >= 6 and r[0].replace(".", "").isdigit()]
+        mx = [float(r[1]) for r in self.rows if len(r) >= 6 and r[1].replace(".", "").isdigit()]
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        reasons = [nm for i, nm in enumerate(names)
+                   if any(len(r) >= 6 and r[2 + i].lower().startswith("active") for r in self.rows)]
+        return {"sm_mhz": float(np.median(sm)) if sm else None,
+                "sm_max_mhz": max(mx) if mx else None, "reasons": reasons, "samples": len(sm)}
+
+
+def cpu_reference(steps: int, warmup: int, batch: int = 256):
+    """The reference's CPU evaluator (fp32 PyTorch network, all host threads) on ``batch``
+    positions per step; returns positions/s and a description of the sample."""
+    from brokefish_b200.nn.model import seeded_state
+    from oracle import fp32_model
+    threads = os.cpu_count() or 1
+    torch.set_num_threads(threads)
+    state = seeded_state(seed=0, std=0.02)
+    b, c, r, _ = load_positions(batch)
+    b, c, r = torch.from_numpy(b), torch.from_numpy(c), torch.from_numpy(r)
+    for _ in range(max(1, warmup)):
+        fp32_model.forward(state, b, c, r)
+    t0 = time.perf_counter()
+    for _ in range(steps):
+        fp32_model.forward(state, b, c, r)
+    dt = time.perf_counter() - t0
+    return batch * steps / dt, dt / steps * 1e3, {
+        "cores": torch.get_num_threads(), "kind": "port",
+        "sample": f"{steps} steps x {batch} positions, fp32 PyTorch evaluator on host threads"}
+
+
+def main() -> int:
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=50)
+    ap.add_argument("--warmup", type=int, default=5)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--batch", type=int, default=4096, help="positions per GPU per step")
+    ap.add_argument("--total", type=int, default=0,
+                    help="fixed number of positions per step split across the GPUs")
+    ap.add_argument("--no-cpu-baseline", action="store_true")
+    args = ap.parse_args()
+    rank = int(os.environ.get("RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    warmup = max(3, args.warmup)
+
+    if args.impl == "reference":
+        if rank != 0:
+            return 0
+        steps = min(args.steps, 40)
+        value, ms, info = cpu_reference(steps, min(warmup, 3))
+        line = {"impl": "reference", "metric": METRIC, "value": value, "unit": "positions/s",
+                "n_gpus": args.gpus, "steps": steps, "warmup": min(warmup, 3), "ms_per_step": ms,
+                "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f32",
+                "data": "synthetic", "config": {"workload": WORKLOAD, "l2": "n/a (CPU)"},
+                "cpu_baseline": dict(info, value=value, unit="positions/s"),
+                "e2e": {"value": value, "unit": "positions/s", "h2d_bytes_per_step": 0,
+                        "d2h_bytes_per_step": 0}, "gpu_launches": 0}
+        print(json.dumps(line))
+        return 0
+
+    if not torch.cuda.is_available():
+        raise SystemExit("bench.py needs a CUDA device; there is no CPU fallback for the evaluator")
+    import torch.distributed as dist
+    from brokefish_b200.evaluator import ShardedEvaluator, shard_bounds
+    from brokefish_b200.nn.model import BrokefishNet, seeded_state
+
+    torch.cuda.set_device(local)
+    dev = torch.device("cuda", local)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=dev)
+    net = None
+    if rank == 0 or world == 1:
+        net = BrokefishNet().eval()
+        net.load_state_dict(seeded_state(seed=0, std=0.02))
+    ev = ShardedEvaluator(net, rank, world, local)        # one broadcast of the packed blob
+    enc = ev.encoder
+
+    if args.total:
+        lo, hi = shard_bounds(args.total, world, rank)
+        n_local, n_global, scaling = hi - lo, args.total, "strong"
+        b, c, r, lg = (a[lo:hi] for a in load_positions(args.total))
+    else:
+        n_local, n_global, scaling = args.batch, args.batch * world, "weak"
+        b, c, r, lg = load_positions(args.batch)
+    d_b, d_c, d_r = (torch.from_numpy(np.ascontiguousarray(a)).to(dev) for a in (b, c, r))
+    flush = torch.empty(256 << 20, dtype=torch.uint8, device=dev)     # > 126 MB L2
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize(dev)
+
+    for _ in range(warmup):
+        enc.forward_full(d_b, d_c, d_r)
+    barrier()
+    sampler = ClockSampler(local)
+    if rank == 0:
+        sampler.start()
+    starts = [torch.cuda.Event(enable_timing=True) for _ in range(args.steps)]
+    stops = [torch.cuda.Event(enable_timing=True) for _ in range(args.steps)]
+    launches0 = enc.launches
+    barrier()
+    t_wall = time.perf_counter()
+    for i in range(args.steps):
+        flush.fill_(i & 0xFF)                      # L2 flush between timed iterations
+        starts[i].record()
+        enc.forward_full(d_b, d_c, d_r)
+        stops[i].record()
+    barrier()
+    t_wall = time.perf_counter() - t_wall
+    enc.check_status()
+    kernel_ms = [s.elapsed_time(e) for s, e in zip(starts, stops)]
+    dev_ms = float(sum(kernel_ms))
+    launches = enc.launches - launches0
+
+    # end to end: pinned host buffers in, pinned host buffers out, every step
+    h_b, h_c, h_r = (torch.from_numpy(np.ascontiguousarray(a)).pin_memory() for a in (b, c, r))
+    h_pol = torch.empty(n_local, 32, 64, dtype=torch.half).pin_memory()
+    h_pro = torch.empty(n_local, 32, 4, dtype=torch.half).pin_memory()
+    h_val = torch.empty(n_local, dtype=torch.float).pin_memory()
+    for _ in range(3):
+        enc.forward_host(h_b, h_c, h_r, h_pol, h_pro, h_val)
+    barrier()
+    e2e_steps = args.steps
+    t0 = time.perf_counter()
+    for _ in range(e2e_steps):
+        enc.forward_host(h_b, h_c, h_r, h_pol, h_pro, h_val)
+    torch.cuda.synchronize(dev)
+    e2e_ms = (time.perf_counter() - t0) * 1e3
+    clocks = sampler.stop() if rank == 0 else None
+
+    times = torch.tensor([dev_ms, e2e_ms], dtype=torch.float64, device=dev)
+    if world > 1:
+        dist.all_reduce(times, op=dist.ReduceOp.MAX)
+    dev_ms, e2e_ms = float(times[0]), float(times[1])
+    if rank != 0:
+        if world > 1:
+            dist.destroy_process_group()
+        return 0
+
+    value = n_global * args.steps / (dev_ms * 1e-3)
+    e2e = n_global * e2e_steps / (e2e_ms * 1e-3)
+    peak, peak_src = peaks()
+    kern_avg_ms = float(np.mean(kernel_ms))
+    achieved = n_local * OPS_PER_POSITION / (kern_avg_ms * 1e-3) / 1e12
+    line = {
+        "metric": METRIC, "value": value, "unit": "positions/s", "n_gpus": world,
+        "steps": args.steps, "warmup": warmup, "ms_per_step": dev_ms / args.steps,
+        "higher_is_better": True, "scaling": scaling, "vs_baseline": None, "dtype": "s8",
+        "data": "synthetic",
+        "config": {"workload": WORKLOAD, "positions_per_step": n_global, "parallelism": f"dp{world}",
+                   "l2": "flushed between timed iterations (256 MiB fill)",
+                   "timing": "CUDA events per launch on the launching stream, summed; max over ranks",
+                   "wall_ms_incl_flush": t_wall * 1e3},
+        "roofline": {"bound": "tensor", "achieved": achieved, "peak": peak, "unit": "TFLOP/s",
+                     "frac": achieved / peak, "peak_source": peak_src + "; int8 dense nominal 4500",
+                     "traffic": None,
+                     "hbm_algorithmic_GBps": n_local * (BYTES_IN + BYTES_OUT) / (kern_avg_ms * 1e-3) / 1e9},
+        "e2e": {"value": e2e, "unit": "positions/s", "h2d_bytes_per_step": n_local * BYTES_IN,
+                "d2h_bytes_per_step": n_local * BYTES_OUT},
+        "gpu_launches": launches, "clocks": clocks,
+    }
+    if world == 1 and not args.no_cpu_baseline:
+        cv, cms, info = cpu_reference(25, 3)
+        line["cpu_baseline"] = dict(info, value=cv, unit="positions/s")
+    print(json.dumps(line))
+    if world > 1:
+        dist.destroy_process_group()
+    return 0
+
+
+if __name__ == "__main__":
+    raise SystemExit(main())

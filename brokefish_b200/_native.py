@@ -24,7 +24,7 @@ NVCC_FLAGS = ["-gencode", "arch=compute_100a,code=sm_100a", "-O3", "-lineinfo", 
 
 #: Every symbol ``include/brokefish_b200.h`` declares.
 EXPORTS = ["bf_version", "bf_last_error", "bf_create", "bf_destroy", "bf_info", "bf_forward",
-           "bf_forward_stage", "bf_forward_capture", "bf_forward_host", "bf_status",
+           "bf_forward_stage", "bf_forward_stage_at", "bf_forward_capture", "bf_forward_host", "bf_status",
            "bf_launch_count", "bf_selftest_umma"]
 
 
@@ -78,6 +78,7 @@ def lib() -> ctypes.CDLL:
     L.bf_info.argtypes = [vp, ctypes.POINTER(i32), ctypes.POINTER(i32), ctypes.POINTER(i32)]
     L.bf_forward.argtypes = [vp, vp, vp, vp, vp, i32, vp, vp, vp, vp]
     L.bf_forward_stage.argtypes = [vp, vp, vp, vp, i32, i32, vp, vp]
+    L.bf_forward_stage_at.argtypes = [vp, vp, vp, vp, i32, i32, i32, vp, vp]
     L.bf_forward_capture.argtypes = [vp, vp, vp, vp, i32, i32, i32, vp, vp, vp]
     L.bf_forward_host.argtypes = [vp, vp, vp, vp, vp, i32, vp, vp, vp]
     L.bf_status.argtypes = [vp, ctypes.POINTER(i32)]
@@ -86,10 +87,7 @@ def lib() -> ctypes.CDLL:
     L.bf_selftest_umma.argtypes = [i32, i32, vp, vp, vp]
     for name in EXPORTS:
         fn = getattr(L, name)
-        if fn.restype is ctypes.c_int or name in ("bf_create", "bf_destroy", "bf_info", "bf_forward",
-                                                   "bf_forward_stage", "bf_forward_capture",
-                                                   "bf_forward_host", "bf_status",
-                                                   "bf_selftest_umma"):
+        if name not in ("bf_version", "bf_last_error", "bf_launch_count"):
             fn.restype = ctypes.c_int
     _LIB = L
     return L

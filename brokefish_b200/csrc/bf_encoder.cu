@@ -82,7 +82,7 @@ struct Params {
     __half* promo;
     float* value;
     __half* y;
-    int debug_stage;
+    int debug_stage, debug_layer;
     int cap_layer, cap_op;
     uint8_t* cap_a;
     int32_t* cap_acc;
@@ -97,7 +97,7 @@ struct RowCtx {
     uint32_t tm;                // TMEM base address with this warp's lane offset
     volatile int* abort_flag;
     int xpar;                   // exchange buffer parity
-    uint32_t full_cnt[2];       // accumulator slots consumed so far
+    uint32_t full0, full1;      // accumulator slots consumed so far
     long grow;                  // global token row = board * 32 + token
     bool valid;                 // board < n
 };
@@ -117,8 +117,9 @@ __device__ __forceinline__ float4 exchange(RowCtx& c, float4 mine) {
 }
 
 __device__ __forceinline__ void row_wait_acc(RowCtx& c, int slot) {
-    mbar_wait(bar_addr(c.smem, B_ACC_FULL + slot), c.full_cnt[slot] & 1, c.abort_flag, kErrRowAcc);
-    c.full_cnt[slot]++;
+    const uint32_t n = slot ? c.full1 : c.full0;
+    mbar_wait(bar_addr(c.smem, B_ACC_FULL + slot), n & 1, c.abort_flag, kErrRowAcc);
+    if (slot) c.full1 = n + 1; else c.full0 = n + 1;
     tc_fence_after();
 }
 // All of this warp's TMEM loads of the slot are done: hand it back to the MMA issuer.
@@ -138,20 +139,20 @@ __device__ __forceinline__ void row_publish(RowCtx& c, int bar_idx) {
 // Round-half-even float -> 8-bit integer in the low byte (two's complement for
 // negatives): adding 1.5 * 2^23 leaves the integer in the low mantissa bits.  Same
 // result as `cvt.rni.sat` for |v| <= 255 (int8_gemm.cuh:190-199 guarantees the range).
-__device__ __forceinline__ uint32_t q8(float x, float inv) {
-    return __float_as_uint(__fadd_rn(__fmul_rn(x, inv), 12582912.0f));
-}
 __device__ __forceinline__ uint32_t pack4(uint32_t a, uint32_t b, uint32_t c, uint32_t d) {
     return __byte_perm(__byte_perm(a, b, 0x0040), __byte_perm(c, d, 0x0040), 0x5410);
 }
-// 8 packed fp16 pairs (16 values) -> 16 quantised bytes.
+// 8 packed fp16 pairs (16 values) -> 16 quantised bytes: fp32 multiply by 1/scale, then the
+// rounding add, two lanes at a time.
 __device__ __forceinline__ uint4 quant16(const uint32_t* h, float inv) {
+    const uint64_t inv2 = pk2(inv, inv), magic2 = pk2(12582912.0f, 12582912.0f);
     uint32_t o[4];
 #pragma unroll
     for (int k = 0; k < 4; ++k) {
-        const float2 a = __half22float2(as_h2(h[2 * k]));
-        const float2 b = __half22float2(as_h2(h[2 * k + 1]));
-        o[k] = pack4(q8(a.x, inv), q8(a.y, inv), q8(b.x, inv), q8(b.y, inv));
+        float a0, a1, b0, b1;
+        upk2(add2_after_mul(mul2(h2_to_f2(h[2 * k]), inv2), magic2), a0, a1);
+        upk2(add2_after_mul(mul2(h2_to_f2(h[2 * k + 1]), inv2), magic2), b0, b1);
+        o[k] = pack4(__float_as_uint(a0), __float_as_uint(a1), __float_as_uint(b0), __float_as_uint(b1));
     }
     return make_uint4(o[0], o[1], o[2], o[3]);
 }
@@ -160,12 +161,28 @@ __device__ __forceinline__ uint32_t sw_off(int row, int chunk) {
     return static_cast<uint32_t>(row) * 128u + (static_cast<uint32_t>(chunk ^ (row & 7)) << 4);
 }
 
+// Exact s32 -> f32 without the conversion unit (which issues at a quarter of the FMA
+// rate).  |v| < 2^22: add v to the bit pattern of 1.5 * 2^23 and subtract that constant.
+// s8 x s8 over K = 256 is bounded by 127 * 127 * 256 = 4,129,024 < 2^22.
+__device__ __forceinline__ float i2f_22(uint32_t v) {
+    return __fadd_rn(__uint_as_float(v + 0x4B400000u), -12582912.0f);
+}
+// |v| < 2^23 (u8 x s8 over K = 256 reaches 255 * 127 * 256 = 8,290,560): the magnitude
+// goes into the mantissa of 2^23, the sign bit is put back afterwards.
+__device__ __forceinline__ float i2f_23(uint32_t v) {
+    const int s = static_cast<int>(v);
+    const uint32_t a = static_cast<uint32_t>(s < 0 ? -s : s);
+    const float f = __fadd_rn(__uint_as_float(a | 0x4B000000u), -8388608.0f);
+    return __uint_as_float(__float_as_uint(f) | (v & 0x80000000u));
+}
+
 // `(float(acc) * sa) * sw` -> fp16, + fp16 bias, optional ReLU; 32 columns -> 16 pairs
 // (int8_gemm.cuh:276-297, encoder.cu:631-644, 1482-1489).
 template <bool kRelu>
 __device__ __forceinline__ void descale32(const uint32_t (&acc)[32], float sa, float sw,
                                           const __half* bias, uint32_t* out) {
     const uint4* b4 = reinterpret_cast<const uint4*>(bias);
+    const uint64_t sa2 = pk2(sa, sa), sw2 = pk2(sw, sw), nm2 = pk2(-12582912.0f, -12582912.0f);
 #pragma unroll
     for (int v = 0; v < 4; ++v) {
         const uint4 bv = __ldg(b4 + v);
@@ -173,9 +190,10 @@ __device__ __forceinline__ void descale32(const uint32_t (&acc)[32], float sa, f
 #pragma unroll
         for (int k = 0; k < 4; ++k) {
             const int i = 4 * v + k;
-            const float f0 = __fmul_rn(__fmul_rn(static_cast<float>(static_cast<int>(acc[2 * i])), sa), sw);
-            const float f1 = __fmul_rn(__fmul_rn(static_cast<float>(static_cast<int>(acc[2 * i + 1])), sa), sw);
-            __half2 h = __hadd2(__floats2half2_rn(f0, f1), as_h2(bw[k]));
+            // exact s32 -> f32 (see i2f_22), then the two fp32 multiplies, both lanes at once
+            const uint64_t f = add2(pk2(__uint_as_float(acc[2 * i] + 0x4B400000u),
+                                        __uint_as_float(acc[2 * i + 1] + 0x4B400000u)), nm2);
+            __half2 h = __hadd2(as_h2(f2_to_h2(mul2(mul2(f, sa2), sw2))), as_h2(bw[k]));
             if (kRelu) h = __hmax2(h, __float2half2_rn(0.0f));
             out[i] = as_u32(h);
         }
@@ -192,70 +210,119 @@ __device__ __forceinline__ float amax16(const uint32_t* h, int n, bool take_abs)
     return fmaxf(__low2float(m), __high2float(m));
 }
 
-// Debug/capture stores -------------------------------------------------------------------
-// 64 packed pairs of this thread (columns 64*hf + [0,64) and 128 + 64*hf + [0,64)).
+__device__ __forceinline__ void store_acc32(int32_t* dst, const uint32_t (&acc)[32]) {
+    int4* d4 = reinterpret_cast<int4*>(dst);
+#pragma unroll
+    for (int k = 0; k < 8; ++k) d4[k] = make_int4(acc[4 * k], acc[4 * k + 1], acc[4 * k + 2], acc[4 * k + 3]);
+}
+__device__ __forceinline__ void store_h16(__half* dst, const uint32_t* h) {
+    uint4* d4 = reinterpret_cast<uint4*>(dst);
+#pragma unroll
+    for (int k = 0; k < 4; ++k) d4[k] = make_uint4(h[4 * k], h[4 * k + 1], h[4 * k + 2], h[4 * k + 3]);
+}
+
+// Debug store of this thread's 64 packed pairs (columns 64*hf + [0,64) and
+// 128 + 64*hf + [0,64)) of its row.
 __device__ __forceinline__ void dump_row64(const RowCtx& c, __half* y, const uint32_t* xr) {
     if (!c.valid) return;
 #pragma unroll
-    for (int g = 0; g < 2; ++g) {
-        uint4* dst = reinterpret_cast<uint4*>(y + c.grow * kD + 128 * g + 64 * c.hf);
+    for (int g = 0; g < 2; ++g)
 #pragma unroll
-        for (int k = 0; k < 8; ++k)
-            dst[k] = make_uint4(xr[32 * g + 4 * k], xr[32 * g + 4 * k + 1], xr[32 * g + 4 * k + 2],
-                                xr[32 * g + 4 * k + 3]);
-    }
+        for (int k = 0; k < 2; ++k)
+            store_h16(y + c.grow * kD + 128 * g + 64 * c.hf + 32 * k, xr + 32 * g + 16 * k);
 }
 
-// LayerNorm statistics of a row whose halves are held by two threads (64 pairs each).
-// Summation order (mirrored by the CPU oracle): even and odd columns accumulate
-// separately and sequentially, then even + odd, then the two halves.  One-pass variance
-// clamped at zero as in encoder.cu:584-598; 1/sqrt is correctly rounded here where the
-// reference uses the hardware approximation.
-__device__ __forceinline__ void ln_stats(RowCtx& c, const uint32_t (&xr)[64], float eps,
-                                         float& mean, float& rstd) {
-    float s_lo = 0.f, s_hi = 0.f, q_lo = 0.f, q_hi = 0.f;
+// One LayerNorm of the residual stream (TMEM) for this thread's half row, in two passes over
+// four 32-column groups, followed either by the s8 quantisation into the A operand
+// (returns the row scale) or, for the final norm, by the affine and the fp16 store into the
+// head GEMM's A operand.
+//
+// Statistics: fp32, one pass, variance clamped at zero (encoder.cu:584-598); summation order
+// (mirrored by the CPU oracle): even and odd columns accumulate separately and sequentially,
+// then even + odd, then the two halves.  1/sqrt is correctly rounded where the reference uses
+// the hardware approximation.  x_hat = fp16((x - mean) * rstd).
+//
+// Quantisation (int8_gemm.cuh:159-199): scale = amax(x_hat)/127, all-zero row -> 1.  The map
+// x -> x_hat is monotone (every rounding in it is), so amax(x_hat) is reached at the row's
+// largest or smallest x and needs no second pass: the row minimum and maximum travel in the
+// same exchange as the sums.
+__device__ __forceinline__ float ln_stage(RowCtx& c, const Params& p, bool final_norm, bool dump_x,
+                                          bool dump_xn, bool capture) {
+    uint64_t sum2 = pk2(0.f, 0.f), sq2 = pk2(0.f, 0.f);      // (even, odd) column lanes
+    __half2 mn = __float2half2_rn(65504.0f), mx = __float2half2_rn(-65504.0f);
+#pragma unroll 1
+    for (int k = 0; k < 4; ++k) {
+        uint32_t x[16];
+        tmem_ld16(c.tm + TM_X + 64 * (k >> 1) + 32 * c.hf + 16 * (k & 1), x);
+        tmem_wait_ld();
+        if (dump_x && c.valid) {
+            __half* dst = p.y + c.grow * kD + 128 * (k >> 1) + 64 * c.hf + 32 * (k & 1);
+            store_h16(dst, x);
+            store_h16(dst + 16, x + 8);
+        }
 #pragma unroll
-    for (int i = 0; i < 64; ++i) {
-        const float2 f = __half22float2(as_h2(xr[i]));
-        s_lo = __fadd_rn(s_lo, f.x);
-        s_hi = __fadd_rn(s_hi, f.y);
-        q_lo = __fmaf_rn(f.x, f.x, q_lo);
-        q_hi = __fmaf_rn(f.y, f.y, q_hi);
+        for (int i = 0; i < 16; ++i) {
+            const __half2 h = as_h2(x[i]);
+            const uint64_t f = h2_to_f2(x[i]);
+            sum2 = add2(sum2, f);
+            sq2 = fma2(f, f, sq2);
+            mn = __hmin2(mn, h);
+            mx = __hmax2(mx, h);
+        }
     }
+    float s_lo, s_hi, q_lo, q_hi;
+    upk2(sum2, s_lo, s_hi);
+    upk2(sq2, q_lo, q_hi);
     const float s = __fadd_rn(s_lo, s_hi), qq = __fadd_rn(q_lo, q_hi);
-    const float4 o = exchange(c, make_float4(s, qq, 0.f, 0.f));
+    const float my_min = fminf(__low2float(mn), __high2float(mn));
+    const float my_max = fmaxf(__low2float(mx), __high2float(mx));
+    const float4 o = exchange(c, make_float4(s, qq, my_min, my_max));
     const float tot = __fadd_rn(s, o.x), totq = __fadd_rn(qq, o.y);
-    mean = __fmul_rn(tot, 1.0f / 256.0f);
+    const float mean = __fmul_rn(tot, 1.0f / 256.0f);
     const float var = fmaxf(__fmaf_rn(-mean, mean, __fmul_rn(totq, 1.0f / 256.0f)), 0.f);
-    rstd = __frsqrt_rn(__fadd_rn(var, eps));
-}
-
-// x (64 pairs) -> x_hat = fp16((x - mean) * rstd) in place.
-__device__ __forceinline__ void ln_apply(uint32_t (&xr)[64], float mean, float rstd) {
-#pragma unroll
-    for (int i = 0; i < 64; ++i) {
-        const float2 f = __half22float2(as_h2(xr[i]));
-        xr[i] = pack_h2(__fmul_rn(__fsub_rn(f.x, mean), rstd), __fmul_rn(__fsub_rn(f.y, mean), rstd));
-    }
-}
-
-// Per-row symmetric s8 quantisation of x_hat into the A operand (both K-slabs), scale
-// `amax/127`, all-zero row -> 1 (int8_gemm.cuh:159-199).  Returns the row scale.
-__device__ __forceinline__ float quantise_to_a(RowCtx& c, const Params& p, const uint32_t (&xr)[64],
-                                               bool capture) {
-    const float mine = amax16(xr, 64, true);
-    const float4 o = exchange(c, make_float4(mine, 0.f, 0.f, 0.f));
-    const float amax = fmaxf(mine, o.x);
+    const float rstd = __frsqrt_rn(__fadd_rn(var, p.eps));
+    const float e_lo = __half2float(__float2half_rn(__fmul_rn(__fsub_rn(fminf(my_min, o.z), mean), rstd)));
+    const float e_hi = __half2float(__float2half_rn(__fmul_rn(__fsub_rn(fmaxf(my_max, o.w), mean), rstd)));
+    const float amax = fmaxf(fabsf(e_lo), fabsf(e_hi));
     const float sc = amax > 0.f ? __fdiv_rn(amax, 127.0f) : 1.0f;
     const float inv = __fdiv_rn(1.0f, sc);
+#pragma unroll 1
+    for (int k = 0; k < 4; ++k) {
+        const int g = k >> 1, sub = k & 1;
+        uint32_t x[16];
+        tmem_ld16(c.tm + TM_X + 64 * g + 32 * c.hf + 16 * sub, x);
+        tmem_wait_ld();
+        const int col = 128 * g + 64 * c.hf + 32 * sub;
+        const uint64_t nmean2 = pk2(-mean, -mean), rstd2 = pk2(rstd, rstd);
+        if (!final_norm) {
 #pragma unroll
-    for (int g = 0; g < 2; ++g) {
+            for (int i = 0; i < 16; ++i) x[i] = f2_to_h2(mul2(add2(h2_to_f2(x[i]), nmean2), rstd2));
 #pragma unroll
-        for (int k = 0; k < 4; ++k) {
-            const uint4 v = quant16(&xr[32 * g + 8 * k], inv);
-            *reinterpret_cast<uint4*>(c.smem_gen + SM_A + g * 16384 + sw_off(c.row, 4 * c.hf + k)) = v;
-            if (capture && c.valid)
-                *reinterpret_cast<uint4*>(p.cap_a + c.grow * kD + 128 * g + 64 * c.hf + 16 * k) = v;
+            for (int v = 0; v < 2; ++v) {
+                const uint4 qv = quant16(&x[8 * v], inv);
+                *reinterpret_cast<uint4*>(c.smem_gen + SM_A + g * 16384 + sw_off(c.row, 4 * c.hf + 2 * sub + v)) = qv;
+                if (capture && c.valid) *reinterpret_cast<uint4*>(p.cap_a + c.grow * kD + col + 16 * v) = qv;
+            }
+        } else {
+            // norm_f with affine: fp16(fma(x_hat, gamma, beta)) (encoder.cu:609-611), written as
+            // the fp16 A operand of the head GEMM: 4 K-slabs of [128 rows][64 halves]
+            const uint4* g4 = reinterpret_cast<const uint4*>(p.tail + col);
+            const uint4* b4 = reinterpret_cast<const uint4*>(p.tail + kD + col);
+#pragma unroll
+            for (int v = 0; v < 4; ++v) {
+                const uint4 gv = __ldg(g4 + v), bv = __ldg(b4 + v);
+                const uint32_t gw[4] = {gv.x, gv.y, gv.z, gv.w}, bw[4] = {bv.x, bv.y, bv.z, bv.w};
+#pragma unroll
+                for (int j = 0; j < 4; ++j)
+                    x[4 * v + j] = f2_to_h2(fma2(mul2(add2(h2_to_f2(x[4 * v + j]), nmean2), rstd2),
+                                                 h2_to_f2(gw[j]), h2_to_f2(bw[j])));
+                *reinterpret_cast<uint4*>(c.smem_gen + SM_R + (2 * g + c.hf) * 16384 + sw_off(c.row, 4 * sub + v)) =
+                    make_uint4(x[4 * v], x[4 * v + 1], x[4 * v + 2], x[4 * v + 3]);
+            }
+        }
+        if (dump_xn && c.valid) {
+            store_h16(p.y + c.grow * kD + col, x);
+            store_h16(p.y + c.grow * kD + col + 16, x + 8);
         }
     }
     return sc;
@@ -294,6 +361,12 @@ __device__ __forceinline__ void attention_unit(const RowCtx& c, uint32_t alive) 
             mma_f16_f32(s[mt][nt], qa[mt][1], kb[2], kb[3]);
         }
     }
+    // dead keys get -inf added; this lane's eight key columns are 8*nt + 2*t + {0,1}
+    float kb_mask[4][2];
+#pragma unroll
+    for (int nt = 0; nt < 4; ++nt)
+#pragma unroll
+        for (int k = 0; k < 2; ++k) kb_mask[nt][k] = ((alive >> (8 * nt + 2 * t + k)) & 1u) ? 0.f : -INFINITY;
     uint32_t pa[2][2][4];
 #pragma unroll
     for (int mt = 0; mt < 2; ++mt)
@@ -304,20 +377,21 @@ __device__ __forceinline__ void attention_unit(const RowCtx& c, uint32_t alive) 
             for (int nt = 0; nt < 4; ++nt)
 #pragma unroll
                 for (int k = 0; k < 2; ++k) {
-                    const int key = 8 * nt + 2 * t + k;
                     float& v = s[mt][nt][2 * hi + k];
-                    v = ((alive >> key) & 1u) ? v : -INFINITY;
+                    v += kb_mask[nt][k];
                     mx = fmaxf(mx, v);
                 }
             mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 1));
             mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 2));
+            // exp(v - mx) = 2^(v*log2e - mx*log2e); an all-dead row keeps the reference's NaN
+            const float nmx = -mx * 1.4426950408889634f;
             float sum = 0.f;
 #pragma unroll
             for (int nt = 0; nt < 4; ++nt)
 #pragma unroll
                 for (int k = 0; k < 2; ++k) {
                     float& v = s[mt][nt][2 * hi + k];
-                    v = __expf(v - mx);
+                    v = ex2_approx(__fmaf_rn(v, 1.4426950408889634f, nmx));
                     sum += v;
                 }
             sum += __shfl_xor_sync(0xffffffffu, sum, 1);
@@ -363,8 +437,201 @@ __device__ __forceinline__ void attention_unit(const RowCtx& c, uint32_t alive) 
 }
 
 // ------------------------------------------------------------------------------------------
-// Row-warp work for one tile.
+// Row-warp work, written as run-time loops over 32-column groups so that the whole layer
+// body stays small enough for the instruction cache.
 // ------------------------------------------------------------------------------------------
+struct LayerParams {
+    const float *sw_qkv, *sw_o, *sw_ff1, *sw_ff2;
+    const __half *b_qkv, *b_o, *b_ff1, *b_ff2;
+};
+
+// QKV in four head-pair chunks with attention per chunk, then the attention output is
+// quantised into A, then out-projection + residual into the residual stream (TMEM).
+// Returns nothing; `sa` is the scale of the row in A on entry.
+__device__ __forceinline__ void attention_block(RowCtx& c, const Params& p, const LayerParams& lp,
+                                                float sa, uint32_t alive, bool cap, bool dbgl) {
+    const int dbg = p.debug_stage;
+    float o_amax = 0.f;
+#pragma unroll 1
+    for (int j = 0; j < 4; ++j) {
+        row_wait_acc(c, 0);
+#pragma unroll 1
+        for (int g = 0; g < 3; ++g) {
+            const int c0 = 96 * c.hf + 32 * g, m = c0 >> 6, cm = c0 & 63;
+            uint32_t acc[32], h[16];
+            tmem_ld32(c.tm + TM_ACC + c0, acc);
+            tmem_wait_ld();
+            if (cap && p.cap_op == BF_OP_QKV && c.valid) store_acc32(p.cap_acc + c.grow * 768 + j * 192 + c0, acc);
+            descale32<false>(acc, sa, __ldg(lp.sw_qkv + m * 2 + (j >> 1)), lp.b_qkv + j * 192 + c0, h);
+#pragma unroll
+            for (int k = 0; k < 4; ++k)
+                *reinterpret_cast<uint4*>(c.smem_gen + SM_R + m * 16384 + sw_off(c.row, (cm >> 3) + k)) =
+                    make_uint4(h[4 * k], h[4 * k + 1], h[4 * k + 2], h[4 * k + 3]);
+            if (dbgl && dbg == 5 + m && c.valid) {
+                store_h16(p.y + c.grow * kD + 64 * j + cm, h);
+                store_h16(p.y + c.grow * kD + 64 * j + cm + 16, h + 8);
+            }
+        }
+        row_release_acc(c, 0);
+        named_bar_sync(1 + c.q, 64);       // this board's Q/K/V rows are staged
+        attention_unit(c, alive);
+        {
+            // read back this row's 32 outputs of head 2j+hf, park them in tensor memory
+            uint32_t oh[16];
+#pragma unroll
+            for (int k = 0; k < 4; ++k) {
+                const uint4 v = *reinterpret_cast<const uint4*>(c.smem_gen + SM_R + sw_off(c.row, 4 * c.hf + k));
+                oh[4 * k] = v.x; oh[4 * k + 1] = v.y; oh[4 * k + 2] = v.z; oh[4 * k + 3] = v.w;
+            }
+            o_amax = fmaxf(o_amax, amax16(oh, 16, true));
+            tmem_st16(c.tm + TM_OY + 16 * (2 * j + c.hf), oh);
+            if (dbgl && dbg == 4 && c.valid) {
+                store_h16(p.y + c.grow * kD + 32 * (2 * j + c.hf), oh);
+                store_h16(p.y + c.grow * kD + 32 * (2 * j + c.hf) + 16, oh + 8);
+            }
+        }
+        named_bar_sync(1 + c.q, 64);       // staging may be overwritten by the next chunk
+    }
+    tmem_wait_st();
+
+    // quantise the attention output into A (s8, per-row scale)
+    {
+        const float4 o = exchange(c, make_float4(o_amax, 0.f, 0.f, 0.f));
+        const float amax = fmaxf(o_amax, o.x);
+        sa = amax > 0.f ? __fdiv_rn(amax, 127.0f) : 1.0f;
+        const float inv = __fdiv_rn(1.0f, sa);
+        const bool capo = cap && p.cap_op == BF_OP_OUT && c.valid;
+#pragma unroll 1
+        for (int jj = 0; jj < 4; ++jj) {
+            const int hd = 2 * jj + c.hf;
+            uint32_t oh[16];
+            tmem_ld16(c.tm + TM_OY + 16 * hd, oh);
+            tmem_wait_ld();
+#pragma unroll
+            for (int k = 0; k < 2; ++k) {
+                const uint4 v = quant16(&oh[8 * k], inv);
+                *reinterpret_cast<uint4*>(c.smem_gen + SM_A + (hd >> 2) * 16384 + sw_off(c.row, (hd & 3) * 2 + k)) = v;
+                if (capo) *reinterpret_cast<uint4*>(p.cap_a + c.grow * kD + 32 * hd + 16 * k) = v;
+            }
+        }
+        row_publish(c, B_A_READY);
+    }
+
+    // out-projection: x = fp16(x + fp16(fp16(descale) + b_o)) (encoder.cu:631-686)
+#pragma unroll 1
+    for (int u = 0; u < 2; ++u) {
+        row_wait_acc(c, u);
+#pragma unroll 1
+        for (int g = 0; g < 2; ++g) {
+            const int col = 128 * u + 64 * c.hf + 32 * g;
+            uint32_t acc[32], y[16], xo[16];
+            tmem_ld32(c.tm + TM_ACC + col, acc);
+            tmem_ld16(c.tm + TM_X + (col >> 1), xo);
+            tmem_wait_ld();
+            if (cap && p.cap_op == BF_OP_OUT && c.valid) store_acc32(p.cap_acc + c.grow * 256 + col, acc);
+            descale32<false>(acc, sa, __ldg(lp.sw_o + u), lp.b_o + col, y);
+#pragma unroll
+            for (int i = 0; i < 16; ++i) xo[i] = as_u32(__hadd2(as_h2(xo[i]), as_h2(y[i])));
+            tmem_st16(c.tm + TM_X + (col >> 1), xo);
+        }
+        row_release_acc(c, u);
+    }
+    tmem_wait_st();
+}
+
+// FFN: four hidden chunks of 256; ff1 -> ReLU -> per-row u8 -> ff2 with an fp16 running
+// total (encoder.cu:1431-1556).  The eight steps follow the MMA issue order.
+__device__ __forceinline__ void ffn_block(RowCtx& c, const Params& p, const LayerParams& lp,
+                                          float sa, bool cap) {
+    float sa2_0 = 1.f, sa2_1 = 1.f;
+#pragma unroll 1
+    for (int st = 0; st < 8; ++st) {
+        const int kind2 = (0xD4 >> st) & 1;
+        const int ch = kind2 ? ((0x32010000u >> (4 * st)) & 0xF) : ((0x00302010u >> (4 * st)) & 0xF);
+        if (!kind2) {
+            uint32_t hid[64];
+#pragma unroll
+            for (int jh = 0; jh < 2; ++jh) {
+                row_wait_acc(c, jh);
+#pragma unroll
+                for (int g = 0; g < 2; ++g) {
+                    uint32_t acc[32];
+                    tmem_ld32(c.tm + TM_ACC + 128 * jh + 64 * c.hf + 32 * g, acc);
+                    tmem_wait_ld();
+                    const int col = 256 * ch + 128 * jh + 64 * c.hf + 32 * g;
+                    if (cap && p.cap_op == BF_OP_FF1 && c.valid) store_acc32(p.cap_acc + c.grow * 1024 + col, acc);
+                    descale32<true>(acc, sa, __ldg(lp.sw_ff1 + 2 * ch + jh), lp.b_ff1 + col, &hid[32 * jh + 16 * g]);
+                }
+                row_release_acc(c, jh);
+            }
+            // per-row u8 scale over the 256-wide chunk (encoder.cu:1510-1517)
+            const float mine = amax16(hid, 64, false);
+            const float4 o = exchange(c, make_float4(mine, 0.f, 0.f, 0.f));
+            const float amax = fmaxf(mine, o.x);
+            const float sc = amax > 0.f ? __fdiv_rn(amax, 255.0f) : 1.0f;
+            const float inv = __fdiv_rn(1.0f, sc);
+            if (ch & 1) sa2_1 = sc; else sa2_0 = sc;
+            const bool caph = cap && p.cap_op == BF_OP_FF2 + ch && c.valid;
+#pragma unroll
+            for (int jh = 0; jh < 2; ++jh)
+#pragma unroll
+                for (int k = 0; k < 4; ++k) {
+                    const uint4 v = quant16(&hid[32 * jh + 8 * k], inv);
+                    *reinterpret_cast<uint4*>(c.smem_gen + SM_R + (ch & 1) * 32768 + jh * 16384 +
+                                              sw_off(c.row, 4 * c.hf + k)) = v;
+                    if (caph) *reinterpret_cast<uint4*>(p.cap_a + c.grow * kD + 128 * jh + 64 * c.hf + 16 * k) = v;
+                }
+            row_publish(c, B_A2_READY + (ch & 1));
+        } else {
+            const float s1 = (ch & 1) ? sa2_1 : sa2_0;
+#pragma unroll 1
+            for (int jh = 0; jh < 2; ++jh) {
+                row_wait_acc(c, jh);
+                const float s2 = __ldg(lp.sw_ff2 + jh);
+#pragma unroll 1
+                for (int g = 0; g < 2; ++g) {
+                    uint32_t acc[32], run[16];
+                    const int col = 128 * jh + 64 * c.hf + 32 * g;
+                    tmem_ld32(c.tm + TM_ACC + col, acc);
+                    if (ch > 0) tmem_ld16(c.tm + TM_OY + (col >> 1), run);
+                    tmem_wait_ld();
+                    if (cap && p.cap_op == BF_OP_FF2 + ch && c.valid) store_acc32(p.cap_acc + c.grow * 256 + col, acc);
+                    const uint64_t s1_2 = pk2(s1, s1), s2_2 = pk2(s2, s2);
+#pragma unroll
+                    for (int i = 0; i < 16; ++i) {
+                        uint64_t f = mul2(mul2(pk2(i2f_23(acc[2 * i]), i2f_23(acc[2 * i + 1])), s1_2), s2_2);
+                        if (ch > 0) f = add2_after_mul(f, h2_to_f2(run[i]));
+                        run[i] = f2_to_h2(f);
+                    }
+                    if (ch < 3) {
+                        tmem_st16(c.tm + TM_OY + (col >> 1), run);
+                    } else {
+                        // + b_ff2, residual (encoder.cu:1548-1556): x = fp16(x + fp16(run + b))
+                        uint32_t xo[16];
+                        tmem_ld16(c.tm + TM_X + (col >> 1), xo);
+                        tmem_wait_ld();
+                        const uint4* b4 = reinterpret_cast<const uint4*>(lp.b_ff2 + col);
+#pragma unroll
+                        for (int v = 0; v < 4; ++v) {
+                            const uint4 bv = __ldg(b4 + v);
+                            const uint32_t bw[4] = {bv.x, bv.y, bv.z, bv.w};
+#pragma unroll
+                            for (int k = 0; k < 4; ++k) {
+                                const int i = 4 * v + k;
+                                const __half2 yv = __hadd2(as_h2(run[i]), as_h2(bw[k]));
+                                xo[i] = as_u32(__hadd2(as_h2(xo[i]), yv));
+                            }
+                        }
+                        tmem_st16(c.tm + TM_X + (col >> 1), xo);
+                    }
+                }
+                row_release_acc(c, jh);
+            }
+            tmem_wait_st();
+        }
+    }
+}
+
 __device__ __forceinline__ void row_warps_tile(RowCtx& c, const Params& p, int tile) {
     const int board = tile * 4 + c.q;
     c.valid = board < p.n;
@@ -373,10 +640,9 @@ __device__ __forceinline__ void row_warps_tile(RowCtx& c, const Params& p, int t
     const uint32_t alive = __ballot_sync(0xffffffffu, ((word >> 11) & 1u) == 0u);
     const int ctl = c.valid ? static_cast<int>(p.control[board]) : 1;
     const int dbg = p.debug_stage;
-    uint32_t xr[64];
 
     // ---- embedding: ((square + type_special) + color_turn) + (clock + rep), fp16
-    //      (encoder.cu:817-889; nn/model.py:383-397) ------------------------------------
+    //      (encoder.cu:817-889; nn/model.py:383-397), written to the residual stream ----
     {
         const int stm = ctl < 0;
         const int clk = min(max((ctl < 0 ? -ctl : ctl) - 1, 0), kNClock - 1);
@@ -384,7 +650,7 @@ __device__ __forceinline__ void row_warps_tile(RowCtx& c, const Params& p, int t
         const int sq = word & 63;
         const int ts = min(static_cast<int>(((word >> 6) & 7) * 2 + ((word >> 9) & 1)), kNTypeSpecial - 1);
         const int ct = ((word >> 10) & 1) * 2 + stm;
-#pragma unroll
+#pragma unroll 1
         for (int g = 0; g < 2; ++g) {
             const int col = 128 * g + 64 * c.hf;
             const uint4* e_sq = reinterpret_cast<const uint4*>(p.emb + (EMB_SQUARE + sq) * kD + col);
@@ -392,6 +658,7 @@ __device__ __forceinline__ void row_warps_tile(RowCtx& c, const Params& p, int t
             const uint4* e_ct = reinterpret_cast<const uint4*>(p.emb + (EMB_CT + ct) * kD + col);
             const uint4* e_ck = reinterpret_cast<const uint4*>(p.emb + (EMB_CLOCK + clk) * kD + col);
             const uint4* e_rp = reinterpret_cast<const uint4*>(p.emb + (EMB_REP + rp) * kD + col);
+            uint32_t e32[32];
 #pragma unroll
             for (int k = 0; k < 8; ++k) {
                 const uint4 a = __ldg(e_sq + k), b = __ldg(e_ts + k), d = __ldg(e_ct + k);
@@ -404,290 +671,44 @@ __device__ __forceinline__ void row_warps_tile(RowCtx& c, const Params& p, int t
                     __half2 x = __hadd2(as_h2(aw[j]), as_h2(bw[j]));
                     x = __hadd2(x, as_h2(dw[j]));
                     x = __hadd2(x, __hadd2(as_h2(ew[j]), as_h2(fw[j])));
-                    xr[32 * g + 4 * k + j] = as_u32(x);
+                    e32[4 * k + j] = as_u32(x);
                 }
             }
+            tmem_st32(c.tm + TM_X + 64 * g + 32 * c.hf, e32);
         }
-#pragma unroll
-        for (int g = 0; g < 2; ++g)
-            tmem_st32(c.tm + TM_X + 64 * g + 32 * c.hf, *reinterpret_cast<uint32_t(*)[32]>(&xr[32 * g]));
         tmem_wait_st();
-        if (dbg == 9) dump_row64(c, p.y, xr);
     }
 
-    float sa;   // scale of the row currently in the A operand
-    {
-        float mean, rstd;
-        ln_stats(c, xr, p.eps, mean, rstd);
-        ln_apply(xr, mean, rstd);
-        if (dbg == 1) dump_row64(c, p.y, xr);
-        sa = quantise_to_a(c, p, xr, p.cap_layer == 0 && p.cap_op == BF_OP_QKV);
-        row_publish(c, B_A_READY);
-    }
-
-    for (int layer = 0; layer < p.n_layers; ++layer) {
-        const uint8_t* lp = p.lparams + static_cast<size_t>(layer) * kLparamStride;
-        const float* sw_qkv = reinterpret_cast<const float*>(lp + LP_SW_QKV);
-        const float* sw_o = reinterpret_cast<const float*>(lp + LP_SW_O);
-        const float* sw_ff1 = reinterpret_cast<const float*>(lp + LP_SW_FF1);
-        const float* sw_ff2 = reinterpret_cast<const float*>(lp + LP_SW_FF2);
-        const __half* b_qkv = reinterpret_cast<const __half*>(lp + LP_B_QKV);
-        const __half* b_o = reinterpret_cast<const __half*>(lp + LP_B_O);
-        const __half* b_ff1 = reinterpret_cast<const __half*>(lp + LP_B_FF1);
-        const __half* b_ff2 = reinterpret_cast<const __half*>(lp + LP_B_FF2);
-        const bool cap = layer == p.cap_layer;
-        const bool dbg0 = layer == 0;
-
-        // ---- QKV in four head-pair chunks, attention per chunk ----------------------
-        float o_amax = 0.f;
+    const int n_ph = 2 * p.n_layers;
 #pragma unroll 1
-        for (int j = 0; j < 4; ++j) {
-            row_wait_acc(c, 0);
-#pragma unroll
-            for (int g = 0; g < 3; ++g) {
-                const int c0 = 96 * c.hf + 32 * g, m = c0 >> 6, cm = c0 & 63;
-                uint32_t acc[32], h[16];
-                tmem_ld32(c.tm + TM_ACC + c0, acc);
-                tmem_wait_ld();
-                if (cap && p.cap_op == BF_OP_QKV && c.valid) {
-                    int4* dst = reinterpret_cast<int4*>(p.cap_acc + c.grow * 768 + j * 192 + c0);
-#pragma unroll
-                    for (int k = 0; k < 8; ++k)
-                        dst[k] = make_int4(acc[4 * k], acc[4 * k + 1], acc[4 * k + 2], acc[4 * k + 3]);
-                }
-                descale32<false>(acc, sa, __ldg(sw_qkv + m * 2 + (j >> 1)), b_qkv + j * 192 + c0, h);
-#pragma unroll
-                for (int k = 0; k < 4; ++k)
-                    *reinterpret_cast<uint4*>(c.smem_gen + SM_R + m * 16384 + sw_off(c.row, (cm >> 3) + k)) =
-                        make_uint4(h[4 * k], h[4 * k + 1], h[4 * k + 2], h[4 * k + 3]);
-                if (dbg0 && dbg == 5 + m && c.valid) {
-                    uint4* dst = reinterpret_cast<uint4*>(p.y + c.grow * kD + 64 * j + cm);
-#pragma unroll
-                    for (int k = 0; k < 4; ++k)
-                        dst[k] = make_uint4(h[4 * k], h[4 * k + 1], h[4 * k + 2], h[4 * k + 3]);
-                }
-            }
-            row_release_acc(c, 0);
-            named_bar_sync(1 + c.q, 64);       // this board's Q/K/V rows are staged
-            attention_unit(c, c.valid ? alive : 0xffffffffu);
-            {
-                // read back this row's 32 outputs of head 2j+hf, park them in tensor memory
-                uint32_t oh[16];
-#pragma unroll
-                for (int k = 0; k < 4; ++k) {
-                    const uint4 v = *reinterpret_cast<const uint4*>(c.smem_gen + SM_R + sw_off(c.row, 4 * c.hf + k));
-                    oh[4 * k] = v.x; oh[4 * k + 1] = v.y; oh[4 * k + 2] = v.z; oh[4 * k + 3] = v.w;
-                }
-                o_amax = fmaxf(o_amax, amax16(oh, 16, true));
-                tmem_st16(c.tm + TM_OY + 16 * (2 * j + c.hf), oh);
-                if (dbg0 && dbg == 4 && c.valid) {
-                    uint4* dst = reinterpret_cast<uint4*>(p.y + c.grow * kD + 32 * (2 * j + c.hf));
-#pragma unroll
-                    for (int k = 0; k < 4; ++k)
-                        dst[k] = make_uint4(oh[4 * k], oh[4 * k + 1], oh[4 * k + 2], oh[4 * k + 3]);
-                }
-            }
-            named_bar_sync(1 + c.q, 64);       // staging may be overwritten by the next chunk
-        }
-        tmem_wait_st();
-
-        // ---- quantise the attention output into A (s8, per-row scale) ----------------
-        {
-            const float4 o = exchange(c, make_float4(o_amax, 0.f, 0.f, 0.f));
-            const float amax = fmaxf(o_amax, o.x);
-            sa = amax > 0.f ? __fdiv_rn(amax, 127.0f) : 1.0f;
-            const float inv = __fdiv_rn(1.0f, sa);
-            const bool capo = cap && p.cap_op == BF_OP_OUT && c.valid;
-#pragma unroll
-            for (int jj = 0; jj < 4; ++jj) {
-                const int hd = 2 * jj + c.hf;
-                uint32_t oh[16];
-                tmem_ld16(c.tm + TM_OY + 16 * hd, oh);
-                tmem_wait_ld();
-#pragma unroll
-                for (int k = 0; k < 2; ++k) {
-                    const uint4 v = quant16(&oh[8 * k], inv);
-                    *reinterpret_cast<uint4*>(c.smem_gen + SM_A + (hd >> 2) * 16384 +
-                                              sw_off(c.row, (hd & 3) * 2 + k)) = v;
-                    if (capo) *reinterpret_cast<uint4*>(p.cap_a + c.grow * kD + 32 * hd + 16 * k) = v;
-                }
-            }
+    for (int ph = 0; ph <= n_ph; ++ph) {
+        const int layer = ph >> 1;
+        const bool odd = ph & 1;
+        const bool dbgl = layer == p.debug_layer;
+        const bool dump_x = (dbg == 9 && ph == 0) || (dbg == 2 && odd && dbgl) ||
+                            (dbg == 10 && !odd && ph > 0 && layer - 1 == p.debug_layer);
+        if (ph == n_ph) {
+            ln_stage(c, p, true, dump_x, dbg == 8, false);
             row_publish(c, B_A_READY);
+            break;
         }
+        const bool cap = layer == p.cap_layer;
+        const float sa = ln_stage(c, p, false, dump_x, dbgl && dbg == (odd ? 3 : 1),
+                                  cap && p.cap_op == (odd ? BF_OP_FF1 : BF_OP_QKV));
+        row_publish(c, B_A_READY);
 
-        // ---- out-projection, residual, LN2, quantise ------------------------------------
-#pragma unroll
-        for (int u = 0; u < 2; ++u) {
-            row_wait_acc(c, u);
-#pragma unroll
-            for (int g = 0; g < 2; ++g) {
-                uint32_t acc[32], y[16], xo[16];
-                tmem_ld32(c.tm + TM_ACC + 128 * u + 64 * c.hf + 32 * g, acc);
-                tmem_ld16(c.tm + TM_X + 64 * u + 32 * c.hf + 16 * g, xo);
-                tmem_wait_ld();
-                if (cap && p.cap_op == BF_OP_OUT && c.valid) {
-                    int4* dst = reinterpret_cast<int4*>(p.cap_acc + c.grow * 256 + 128 * u + 64 * c.hf + 32 * g);
-#pragma unroll
-                    for (int k = 0; k < 8; ++k)
-                        dst[k] = make_int4(acc[4 * k], acc[4 * k + 1], acc[4 * k + 2], acc[4 * k + 3]);
-                }
-                descale32<false>(acc, sa, __ldg(sw_o + u), b_o + 128 * u + 64 * c.hf + 32 * g, y);
-#pragma unroll
-                for (int i = 0; i < 16; ++i)
-                    xr[32 * u + 16 * g + i] = as_u32(__hadd2(as_h2(xo[i]), as_h2(y[i])));
-            }
-            row_release_acc(c, u);
-            tmem_st32(c.tm + TM_X + 64 * u + 32 * c.hf, *reinterpret_cast<uint32_t(*)[32]>(&xr[32 * u]));
-        }
-        tmem_wait_st();
-        if (dbg0 && dbg == 2) dump_row64(c, p.y, xr);
-        {
-            float mean, rstd;
-            ln_stats(c, xr, p.eps, mean, rstd);
-            ln_apply(xr, mean, rstd);
-            if (dbg0 && dbg == 3) dump_row64(c, p.y, xr);
-            sa = quantise_to_a(c, p, xr, cap && p.cap_op == BF_OP_FF1);
-            row_publish(c, B_A_READY);
-        }
-
-        // ---- FFN: four hidden chunks of 256; ff2 keeps an fp16 running total ------------
-        float sa2[2] = {1.f, 1.f};
-        auto ff1_step = [&](int ch) {
-            uint32_t hid[64];
-#pragma unroll
-            for (int jh = 0; jh < 2; ++jh) {
-                row_wait_acc(c, jh);
-#pragma unroll
-                for (int g = 0; g < 2; ++g) {
-                    uint32_t acc[32];
-                    tmem_ld32(c.tm + TM_ACC + 128 * jh + 64 * c.hf + 32 * g, acc);
-                    tmem_wait_ld();
-                    const int col = 256 * ch + 128 * jh + 64 * c.hf + 32 * g;
-                    if (cap && p.cap_op == BF_OP_FF1 && c.valid) {
-                        int4* dst = reinterpret_cast<int4*>(p.cap_acc + c.grow * 1024 + col);
-#pragma unroll
-                        for (int k = 0; k < 8; ++k)
-                            dst[k] = make_int4(acc[4 * k], acc[4 * k + 1], acc[4 * k + 2], acc[4 * k + 3]);
-                    }
-                    descale32<true>(acc, sa, __ldg(sw_ff1 + 2 * ch + jh), b_ff1 + col, &hid[32 * jh + 16 * g]);
-                }
-                row_release_acc(c, jh);
-            }
-            // per-row u8 scale over the 256-wide chunk (encoder.cu:1510-1517)
-            const float mine = amax16(hid, 64, false);
-            const float4 o = exchange(c, make_float4(mine, 0.f, 0.f, 0.f));
-            const float amax = fmaxf(mine, o.x);
-            const float sc = amax > 0.f ? __fdiv_rn(amax, 255.0f) : 1.0f;
-            const float inv = __fdiv_rn(1.0f, sc);
-            sa2[ch & 1] = sc;
-            const bool caph = cap && p.cap_op == BF_OP_FF2 + ch && c.valid;
-#pragma unroll
-            for (int jh = 0; jh < 2; ++jh)
-#pragma unroll
-                for (int k = 0; k < 4; ++k) {
-                    const uint4 v = quant16(&hid[32 * jh + 8 * k], inv);
-                    *reinterpret_cast<uint4*>(c.smem_gen + SM_R + (ch & 1) * 32768 + jh * 16384 +
-                                              sw_off(c.row, 4 * c.hf + k)) = v;
-                    if (caph)
-                        *reinterpret_cast<uint4*>(p.cap_a + c.grow * kD + 128 * jh + 64 * c.hf + 16 * k) = v;
-                }
-            row_publish(c, B_A2_READY + (ch & 1));
-        };
-        auto ff2_step = [&](int ch) {
-#pragma unroll
-            for (int jh = 0; jh < 2; ++jh) {
-                row_wait_acc(c, jh);
-#pragma unroll
-                for (int g = 0; g < 2; ++g) {
-                    uint32_t acc[32], run[16];
-                    const int col = 128 * jh + 64 * c.hf + 32 * g;
-                    tmem_ld32(c.tm + TM_ACC + col, acc);
-                    if (ch > 0) tmem_ld16(c.tm + TM_OY + (col >> 1), run);
-                    tmem_wait_ld();
-                    if (cap && p.cap_op == BF_OP_FF2 + ch && c.valid) {
-                        int4* dst = reinterpret_cast<int4*>(p.cap_acc + c.grow * 256 + col);
-#pragma unroll
-                        for (int k = 0; k < 8; ++k)
-                            dst[k] = make_int4(acc[4 * k], acc[4 * k + 1], acc[4 * k + 2], acc[4 * k + 3]);
-                    }
-                    const float s1 = sa2[ch & 1], s2 = __ldg(sw_ff2 + jh);
-#pragma unroll
-                    for (int i = 0; i < 16; ++i) {
-                        float f0 = __fmul_rn(__fmul_rn(static_cast<float>(static_cast<int>(acc[2 * i])), s1), s2);
-                        float f1 = __fmul_rn(__fmul_rn(static_cast<float>(static_cast<int>(acc[2 * i + 1])), s1), s2);
-                        if (ch > 0) {
-                            const float2 r = __half22float2(as_h2(run[i]));
-                            f0 = __fadd_rn(f0, r.x);
-                            f1 = __fadd_rn(f1, r.y);
-                        }
-                        run[i] = pack_h2(f0, f1);
-                    }
-                    if (ch < 3) {
-                        tmem_st16(c.tm + TM_OY + (col >> 1), run);
-                    } else {
-                        // + b_ff2, residual (encoder.cu:1548-1556): x = fp16(x + fp16(run + b))
-                        uint32_t xo[16];
-                        tmem_ld16(c.tm + TM_X + (col >> 1), xo);
-                        tmem_wait_ld();
-                        const uint4* b4 = reinterpret_cast<const uint4*>(b_ff2 + col);
-#pragma unroll
-                        for (int v = 0; v < 4; ++v) {
-                            const uint4 bv = __ldg(b4 + v);
-                            const uint32_t bw[4] = {bv.x, bv.y, bv.z, bv.w};
-#pragma unroll
-                            for (int k = 0; k < 4; ++k) {
-                                const int i = 4 * v + k;
-                                const __half2 yv = __hadd2(as_h2(run[i]), as_h2(bw[k]));
-                                xr[32 * jh + 16 * g + i] = as_u32(__hadd2(as_h2(xo[i]), yv));
-                            }
-                        }
-                    }
-                }
-                row_release_acc(c, jh);
-                if (ch == 3)
-                    tmem_st32(c.tm + TM_X + 64 * jh + 32 * c.hf, *reinterpret_cast<uint32_t(*)[32]>(&xr[32 * jh]));
-            }
-            tmem_wait_st();
-        };
-        ff1_step(0); ff1_step(1); ff2_step(0); ff1_step(2);
-        ff2_step(1); ff1_step(3); ff2_step(2); ff2_step(3);
-
-        // ---- next layer's LN1 + quantise, or the final norm ------------------------------
-        float mean, rstd;
-        ln_stats(c, xr, p.eps, mean, rstd);
-        if (layer + 1 < p.n_layers) {
-            ln_apply(xr, mean, rstd);
-            sa = quantise_to_a(c, p, xr, p.cap_layer == layer + 1 && p.cap_op == BF_OP_QKV);
-            row_publish(c, B_A_READY);
-        } else {
-            // norm_f with affine: fp16(fma(x_hat, gamma, beta)) (encoder.cu:609-611), written
-            // as the fp16 A operand of the head GEMM: 4 K-slabs of [128][64 halves].
-#pragma unroll
-            for (int g = 0; g < 2; ++g) {
-                const int col = 128 * g + 64 * c.hf;
-                const uint4* g4 = reinterpret_cast<const uint4*>(p.tail + col);
-                const uint4* b4 = reinterpret_cast<const uint4*>(p.tail + kD + col);
-#pragma unroll
-                for (int k = 0; k < 8; ++k) {
-                    const uint4 gv = __ldg(g4 + k), bv = __ldg(b4 + k);
-                    const uint32_t gw[4] = {gv.x, gv.y, gv.z, gv.w}, bw[4] = {bv.x, bv.y, bv.z, bv.w};
-                    uint32_t o[4];
-#pragma unroll
-                    for (int j = 0; j < 4; ++j) {
-                        const float2 f = __half22float2(as_h2(xr[32 * g + 4 * k + j]));
-                        const float2 gf = __half22float2(as_h2(gw[j])), bf2 = __half22float2(as_h2(bw[j]));
-                        const float a0 = __fmaf_rn(__fmul_rn(__fsub_rn(f.x, mean), rstd), gf.x, bf2.x);
-                        const float a1 = __fmaf_rn(__fmul_rn(__fsub_rn(f.y, mean), rstd), gf.y, bf2.y);
-                        o[j] = pack_h2(a0, a1);
-                        xr[32 * g + 4 * k + j] = o[j];
-                    }
-                    *reinterpret_cast<uint4*>(c.smem_gen + SM_R + (2 * g + c.hf) * 16384 + sw_off(c.row, k)) =
-                        make_uint4(o[0], o[1], o[2], o[3]);
-                }
-            }
-            if (dbg == 8) dump_row64(c, p.y, xr);
-            row_publish(c, B_A_READY);
-        }
+        const uint8_t* lpb = p.lparams + static_cast<size_t>(layer) * kLparamStride;
+        LayerParams lp;
+        lp.sw_qkv = reinterpret_cast<const float*>(lpb + LP_SW_QKV);
+        lp.sw_o = reinterpret_cast<const float*>(lpb + LP_SW_O);
+        lp.sw_ff1 = reinterpret_cast<const float*>(lpb + LP_SW_FF1);
+        lp.sw_ff2 = reinterpret_cast<const float*>(lpb + LP_SW_FF2);
+        lp.b_qkv = reinterpret_cast<const __half*>(lpb + LP_B_QKV);
+        lp.b_o = reinterpret_cast<const __half*>(lpb + LP_B_O);
+        lp.b_ff1 = reinterpret_cast<const __half*>(lpb + LP_B_FF1);
+        lp.b_ff2 = reinterpret_cast<const __half*>(lpb + LP_B_FF2);
+        if (!odd) attention_block(c, p, lp, sa, c.valid ? alive : 0xffffffffu, cap, dbgl);
+        else      ffn_block(c, p, lp, sa, cap);
     }
 
     // ---- heads: fp16 GEMM [128 x 256] x [96 x 256]^T, fp32 accumulate, rounded to fp16
@@ -712,9 +733,8 @@ __device__ __forceinline__ void row_warps_tile(RowCtx& c, const Params& p, int t
             lg[i] = v;
         }
         if (c.valid && p.policy != nullptr) {
-            uint4* dst = reinterpret_cast<uint4*>(p.policy + c.grow * 64 + 32 * c.hf);
-#pragma unroll
-            for (int k = 0; k < 4; ++k) dst[k] = make_uint4(lg[4 * k], lg[4 * k + 1], lg[4 * k + 2], lg[4 * k + 3]);
+            store_h16(p.policy + c.grow * 64 + 32 * c.hf, lg);
+            store_h16(p.policy + c.grow * 64 + 32 * c.hf + 16, lg + 8);
         }
         if (c.hf == 0) {
             if (c.valid && p.promo != nullptr)
@@ -923,7 +943,7 @@ __global__ void __launch_bounds__(kThreads, 1) encoder_kernel(const Params p) {
         c.lane = lane; c.q = warp & 3; c.hf = warp >> 2; c.row = 32 * c.q + lane;
         c.smem = smem; c.smem_gen = sm;
         c.tm = tmem + (static_cast<uint32_t>(32 * c.q) << 16);
-        c.abort_flag = abort_flag; c.xpar = 0; c.full_cnt[0] = c.full_cnt[1] = 0;
+        c.abort_flag = abort_flag; c.xpar = 0; c.full0 = c.full1 = 0;
         for (int tile = blockIdx.x; tile < n_tiles; tile += gridDim.x) row_warps_tile(c, p, tile);
     } else if (warp == kProducerWarp) {
         if (lane == 0) producer_loop(smem, abort_flag, p, blockIdx.x, gridDim.x, n_tiles);
@@ -1052,7 +1072,7 @@ namespace {
 
 int launch(bf_handle* h, const uint16_t* boards, const int16_t* control, const uint8_t* rep,
            const uint64_t* legal, int n, void* policy, void* promo, float* value, void* y, int stage,
-           int cap_layer, int cap_op, uint8_t* cap_a, int32_t* cap_acc, cudaStream_t stream) {
+           int stage_layer, int cap_layer, int cap_op, uint8_t* cap_a, int32_t* cap_acc, cudaStream_t stream) {
     if (h == nullptr) return fail(BF_EINVAL, "null handle");
     if (n < 0) return fail(BF_EINVAL, "n must be >= 0");
     if (n == 0) return BF_OK;
@@ -1069,7 +1089,7 @@ int launch(bf_handle* h, const uint16_t* boards, const int16_t* control, const u
     p.emb = reinterpret_cast<const __half*>(h->blob + h->hdr.off_emb);
     p.tail = reinterpret_cast<const __half*>(h->blob + h->hdr.off_tail);
     p.policy = static_cast<__half*>(policy); p.promo = static_cast<__half*>(promo); p.value = value;
-    p.y = static_cast<__half*>(y); p.debug_stage = stage;
+    p.y = static_cast<__half*>(y); p.debug_stage = stage; p.debug_layer = stage_layer;
     p.cap_layer = cap_layer; p.cap_op = cap_op; p.cap_a = cap_a; p.cap_acc = cap_acc;
     p.status = h->status;
     const int n_tiles = (n + 3) / 4;
@@ -1152,16 +1172,24 @@ int bf_info(const bf_handle* h, int* n_layers, int* n_value, int* vmode) {
 
 int bf_forward(bf_handle* h, const uint16_t* boards, const int16_t* control, const uint8_t* rep,
                const uint64_t* legal, int n, void* policy, void* promo, float* value, void* stream) {
-    return launch(h, boards, control, rep, legal, n, policy, promo, value, nullptr, 0, -1, -1, nullptr,
+    return launch(h, boards, control, rep, legal, n, policy, promo, value, nullptr, 0, 0, -1, -1, nullptr,
                   nullptr, static_cast<cudaStream_t>(stream));
+}
+
+int bf_forward_stage_at(bf_handle* h, const uint16_t* boards, const int16_t* control,
+                        const uint8_t* rep, int n, int layer, int stage, void* y, void* stream) {
+    if (h == nullptr) return fail(BF_EINVAL, "null handle");
+    if (y == nullptr) return fail(BF_EINVAL, "y is null");
+    if (!((stage >= 1 && stage <= 10))) return fail(BF_EINVAL, "unknown stage");
+    if (layer < 0 || layer >= static_cast<int>(h->hdr.n_layers)) return fail(BF_EINVAL, "layer out of range");
+    return launch(h, boards, control, rep, nullptr, n, nullptr, nullptr, nullptr, y, stage, layer, -1, -1,
+                  nullptr, nullptr, static_cast<cudaStream_t>(stream));
 }
 
 int bf_forward_stage(bf_handle* h, const uint16_t* boards, const int16_t* control, const uint8_t* rep,
                      int n, int stage, void* y, void* stream) {
-    if (y == nullptr) return fail(BF_EINVAL, "y is null");
     if (!(stage == 9 || (stage >= 1 && stage <= 8))) return fail(BF_EINVAL, "unknown stage");
-    return launch(h, boards, control, rep, nullptr, n, nullptr, nullptr, nullptr, y, stage, -1, -1,
-                  nullptr, nullptr, static_cast<cudaStream_t>(stream));
+    return bf_forward_stage_at(h, boards, control, rep, n, 0, stage, y, stream);
 }
 
 int bf_forward_capture(bf_handle* h, const uint16_t* boards, const int16_t* control, const uint8_t* rep,
@@ -1170,7 +1198,7 @@ int bf_forward_capture(bf_handle* h, const uint16_t* boards, const int16_t* cont
     if (a_bytes == nullptr || acc == nullptr) return fail(BF_EINVAL, "capture buffers are null");
     if (layer < 0 || layer >= static_cast<int>(h->hdr.n_layers)) return fail(BF_EINVAL, "layer out of range");
     if (op < BF_OP_QKV || op > BF_OP_FF2 + 3) return fail(BF_EINVAL, "unknown op");
-    return launch(h, boards, control, rep, nullptr, n, nullptr, nullptr, nullptr, nullptr, 0, layer, op,
+    return launch(h, boards, control, rep, nullptr, n, nullptr, nullptr, nullptr, nullptr, 0, 0, layer, op,
                   a_bytes, acc, static_cast<cudaStream_t>(stream));
 }
 
@@ -1204,7 +1232,7 @@ int bf_forward_host(bf_handle* h, const uint16_t* boards, const int16_t* control
     if (legal) BF_CUDA(cudaMemcpyAsync(d_legal, legal, static_cast<size_t>(n) * 256, cudaMemcpyHostToDevice, s));
     int rc = launch(h, reinterpret_cast<uint16_t*>(d_boards), reinterpret_cast<int16_t*>(d_control), d_rep,
                     legal ? reinterpret_cast<uint64_t*>(d_legal) : nullptr, n, d_policy, d_promo,
-                    reinterpret_cast<float*>(d_value), nullptr, 0, -1, -1, nullptr, nullptr, s);
+                    reinterpret_cast<float*>(d_value), nullptr, 0, 0, -1, -1, nullptr, nullptr, s);
     if (rc != BF_OK) return rc;
     if (policy) BF_CUDA(cudaMemcpyAsync(policy, d_policy, static_cast<size_t>(n) * 4096, cudaMemcpyDeviceToHost, s));
     if (promo) BF_CUDA(cudaMemcpyAsync(promo, d_promo, static_cast<size_t>(n) * 256, cudaMemcpyDeviceToHost, s));

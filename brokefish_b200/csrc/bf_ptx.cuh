@@ -42,9 +42,8 @@ __device__ __forceinline__ uint32_t mbar_try_wait(uint32_t bar, uint32_t parity)
 // out of time it is set, and every later wait returns at once, so a lost arrival ends
 // the kernel with an error status instead of a hang.  Returns false on time-out.
 constexpr long long kWaitCycles = 400000000LL;   // ~0.2 s at 2 GHz
-__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity,
-                                          volatile int* abort_flag, int code) {
-    if (mbar_try_wait(bar, parity)) return true;
+__device__ __noinline__ bool mbar_wait_slow(uint32_t bar, uint32_t parity, volatile int* abort_flag,
+                                            int code) {
     const long long t0 = clock64();
     while (true) {
         if (mbar_try_wait(bar, parity)) return true;
@@ -54,6 +53,11 @@ __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity,
             return false;
         }
     }
+}
+__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity,
+                                          volatile int* abort_flag, int code) {
+    if (mbar_try_wait(bar, parity)) return true;
+    return mbar_wait_slow(bar, parity, abort_flag, code);
 }
 
 // ---------------------------------------------------------------- proxies / fences
@@ -213,6 +217,54 @@ __device__ __forceinline__ void mma_f16_f32(float (&d)[4], const uint32_t (&a)[4
         "{%0, %1, %2, %3}, {%4, %5, %6, %7}, {%8, %9}, {%0, %1, %2, %3};"
         : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3])
         : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
+}
+
+// ---------------------------------------------------------------- packed fp32 (sm_100 f32x2)
+// Two fp32 lanes in one 64-bit register; each lane rounds exactly as the scalar op does.
+__device__ __forceinline__ uint64_t pk2(float lo, float hi) {
+    uint64_t r;
+    asm("mov.b64 %0, {%1, %2};" : "=l"(r) : "f"(lo), "f"(hi));
+    return r;
+}
+__device__ __forceinline__ void upk2(uint64_t v, float& lo, float& hi) {
+    asm("mov.b64 {%0, %1}, %2;" : "=f"(lo), "=f"(hi) : "l"(v));
+}
+__device__ __forceinline__ uint64_t add2(uint64_t a, uint64_t b) {
+    uint64_t d;
+    asm("add.rn.f32x2 %0, %1, %2;" : "=l"(d) : "l"(a), "l"(b));
+    return d;
+}
+__device__ __forceinline__ uint64_t mul2(uint64_t a, uint64_t b) {
+    uint64_t d;
+    asm("mul.rn.f32x2 %0, %1, %2;" : "=l"(d) : "l"(a), "l"(b));
+    return d;
+}
+__device__ __forceinline__ uint64_t fma2(uint64_t a, uint64_t b, uint64_t c) {
+    uint64_t d;
+    asm("fma.rn.f32x2 %0, %1, %2, %3;" : "=l"(d) : "l"(a), "l"(b), "l"(c));
+    return d;
+}
+// a + b rounded once, written as fma(a, 1, b) so that the assembler cannot contract a
+// preceding packed multiply into it (the two-step rounding is part of the arithmetic).
+__device__ __forceinline__ uint64_t add2_after_mul(uint64_t a, uint64_t b) {
+    return fma2(a, pk2(1.0f, 1.0f), b);
+}
+__device__ __forceinline__ uint64_t h2_to_f2(uint32_t h) {
+    const float2 f = __half22float2(*reinterpret_cast<__half2*>(&h));
+    return pk2(f.x, f.y);
+}
+__device__ __forceinline__ uint32_t f2_to_h2(uint64_t v) {
+    float lo, hi;
+    upk2(v, lo, hi);
+    __half2 h = __floats2half2_rn(lo, hi);
+    return *reinterpret_cast<uint32_t*>(&h);
+}
+
+// 2^x, hardware approximation (what `__expf` uses after its multiply by log2 e)
+__device__ __forceinline__ float ex2_approx(float x) {
+    float y;
+    asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+    return y;
 }
 
 // ---------------------------------------------------------------- small helpers

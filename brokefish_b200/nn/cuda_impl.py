@@ -225,10 +225,11 @@ class FusedEncoder:
             _ptr(self.promo_out), _ptr(self.value_out), stream), "bf_forward")
         return self.policy_out, self.promo_out, self.value_out
 
-    def forward_stage(self, boards, control, rep, stage: int):
+    def forward_stage(self, boards, control, rep, stage: int, layer: int = 0):
         """Activations ``[n,32,256]`` fp16 at an intermediate stage: 9 embedding; layer 0:
         1 LN1, 5/6/7 Q/K/V, 4 attention output, 2 residual after attention, 3 LN2; 8 final
-        norm."""
+        norm.  ``layer`` (an extension) selects another layer for stages 1-7 and allows
+        stage 10, the residual stream at the end of that layer."""
         self._require_net("forward_stage")
         n = self._check_inputs(boards, control, rep)
         self._check_device(boards, control, rep)
@@ -237,9 +238,15 @@ class FusedEncoder:
                                      dtype=torch.half)
             self._buffered = n
         stream = ctypes.c_void_p(torch.cuda.current_stream(self.device).cuda_stream)
-        _native.check(_native.lib().bf_forward_stage(
-            self._handle, _ptr(boards.contiguous()), _ptr(control.contiguous()),
-            _ptr(rep.contiguous()), n, int(stage), _ptr(self.state), stream), "bf_forward_stage")
+        if layer == 0 and stage != 10:
+            rc = _native.lib().bf_forward_stage(
+                self._handle, _ptr(boards.contiguous()), _ptr(control.contiguous()),
+                _ptr(rep.contiguous()), n, int(stage), _ptr(self.state), stream)
+        else:
+            rc = _native.lib().bf_forward_stage_at(
+                self._handle, _ptr(boards.contiguous()), _ptr(control.contiguous()),
+                _ptr(rep.contiguous()), n, int(layer), int(stage), _ptr(self.state), stream)
+        _native.check(rc, "bf_forward_stage")
         return self.state
 
     def capture_gemm(self, boards, control, rep, layer: int, op: int):

@@ -79,6 +79,12 @@ int bf_forward(bf_handle* h, const uint16_t* boards, const int16_t* control,
 int bf_forward_stage(bf_handle* h, const uint16_t* boards, const int16_t* control,
                      const uint8_t* rep, int n, int stage, void* y, void* stream);
 
+/* The same for any layer: stages 1-7 as above for layer `layer`, plus 10 = the residual
+ * stream at the end of that layer; 8 and 9 ignore `layer`.  No counterpart in the
+ * reference (its stage dumps stop at layer 0); used to locate a divergence by layer. */
+int bf_forward_stage_at(bf_handle* h, const uint16_t* boards, const int16_t* control,
+                        const uint8_t* rep, int n, int layer, int stage, void* y, void* stream);
+
 /* Run the network and copy out, for one GEMM of one layer, the quantised A operand
  * bytes and the raw s32 accumulators the tensor cores produced.  This is what lets a
  * test recompute the exact integer product on the host (the method of the reference's

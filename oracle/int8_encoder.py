@@ -243,6 +243,8 @@ class Trace:
     ``(A int values, s32 accumulators)`` with op in qkv, out, ff1_c, ff2_c."""
     stages: Dict[int, np.ndarray] = field(default_factory=dict)
     gemms: Dict[tuple, tuple] = field(default_factory=dict)
+    #: (layer, stage) -> activations for every layer; stage 10 = residual at layer end
+    by_layer: Dict[tuple, np.ndarray] = field(default_factory=dict)
 
 
 def forward(w: Weights, boards, control, rep, legal=None, trace: Optional[Trace] = None,
@@ -285,6 +287,9 @@ def forward(w: Weights, boards, control, rep, legal=None, trace: Optional[Trace]
         cap(li, "out", qa, acc)
         y = add_f16(descale(acc, sa, lw.s_o).astype(F16), lw.b_o[None, :])
         x = add_f16(x, y)
+        if trace is not None:
+            trace.by_layer[(li, 4)] = o.copy()
+            trace.by_layer[(li, 2)] = x.reshape(n, T, D).copy()
         if first:
             trace.stages[2] = x.reshape(n, T, D).copy()
         xn = layernorm(x)
@@ -305,6 +310,8 @@ def forward(w: Weights, boards, control, rep, legal=None, trace: Optional[Trace]
             run = o32.astype(F16)
         y = add_f16(run, lw.b_ff2[None, :])
         x = add_f16(x, y)
+        if trace is not None:
+            trace.by_layer[(li, 10)] = x.reshape(n, T, D).copy()
 
     hn = layernorm(x, w.lnf_w, w.lnf_b)
     if trace is not None:

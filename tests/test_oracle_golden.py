@@ -121,3 +121,19 @@ def test_legal_mask_and_argmax(oracle_weights, pos256):
     assert np.all(np.isneginf(msk[~bits].astype(np.float32)))
     am = O.masked_argmax(raw, pos256["legal"][sl])
     assert all(bits.reshape(8, -1)[i, a] for i, a in enumerate(am) if a >= 0)
+
+
+@pytest.mark.parametrize("name", ["A", "B"])
+def test_fp32_port_matches_reference_fp32(name, states, pos256):
+    """The functional fp32 restatement timed as the CPU baseline equals the reference's own
+    fp32 network on the committed outputs."""
+    import torch
+    from oracle import fp32_model
+    g = np.load(os.path.join(GOLDEN, f"ref_outputs_{name}.npz"))
+    n = g["fp32_policy"].shape[0]
+    p, pr, v = fp32_model.forward(states[name], torch.from_numpy(pos256["boards"][:n]),
+                                  torch.from_numpy(pos256["control"][:n]),
+                                  torch.from_numpy(pos256["rep"][:n]))
+    assert np.abs(p.numpy() - g["fp32_policy"]).max() < 1e-4
+    assert np.abs(pr.numpy() - g["fp32_promo"]).max() < 1e-4
+    assert np.abs(v.numpy() - g["fp32_value"]).max() < 1e-4
