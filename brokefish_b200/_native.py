@@ -25,7 +25,8 @@ NVCC_FLAGS = ["-gencode", "arch=compute_100a,code=sm_100a", "-O3", "-lineinfo", 
 #: Every symbol ``include/brokefish_b200.h`` declares.
 EXPORTS = ["bf_version", "bf_last_error", "bf_create", "bf_destroy", "bf_info", "bf_forward",
            "bf_forward_stage", "bf_forward_stage_at", "bf_forward_capture", "bf_forward_host", "bf_status",
-           "bf_launch_count", "bf_selftest_umma"]
+           "bf_launch_count", "bf_profile", "bf_profile_read", "bf_profile_phases",
+           "bf_selftest_umma"]
 
 
 def nvcc_path() -> str:
@@ -84,10 +85,13 @@ def lib() -> ctypes.CDLL:
     L.bf_status.argtypes = [vp, ctypes.POINTER(i32)]
     L.bf_launch_count.argtypes = [vp]
     L.bf_launch_count.restype = ctypes.c_longlong
+    L.bf_profile.argtypes = [vp, i32]
+    L.bf_profile_read.argtypes = [vp, ctypes.POINTER(ctypes.c_longlong), i32]
+    L.bf_profile_phases.restype = ctypes.c_char_p
     L.bf_selftest_umma.argtypes = [i32, i32, vp, vp, vp]
     for name in EXPORTS:
         fn = getattr(L, name)
-        if name not in ("bf_version", "bf_last_error", "bf_launch_count"):
+        if name not in ("bf_version", "bf_last_error", "bf_launch_count", "bf_profile_phases"):
             fn.restype = ctypes.c_int
     _LIB = L
     return L

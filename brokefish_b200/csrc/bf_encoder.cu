@@ -54,7 +54,8 @@ constexpr uint32_t SM_RING = 98304;     // 112 KB weight ring: 4 x 24 KB or 7 x 
 constexpr uint32_t SM_XCH = 212992;     // 8 KB: float4 [2 parity][2 half][128 rows]
 constexpr uint32_t SM_BAR = 221184;     // mbarriers
 constexpr uint32_t SM_MISC = SM_BAR + 256;
-constexpr uint32_t SM_BYTES = SM_MISC + 64;
+constexpr uint32_t SM_PROF = SM_MISC + 64;     // 16 x int64 phase cycle counters
+constexpr uint32_t SM_BYTES = SM_PROF + 128;
 constexpr uint32_t kSmemRequest = SM_BYTES + 1024;
 constexpr int kQSlots = 4, kRSlots = 7;
 constexpr uint32_t kQStage = 24576, kRStage = 16384, kHeadStage = 12288;
@@ -87,6 +88,7 @@ struct Params {
     uint8_t* cap_a;
     int32_t* cap_acc;
     int* status;
+    unsigned long long* prof;   // 16 phase counters (cycles of warp 0, lane 0 of every CTA) or null
 };
 
 // Per-thread context of a row warp.
@@ -100,7 +102,23 @@ struct RowCtx {
     uint32_t full0, full1;      // accumulator slots consumed so far
     long grow;                  // global token row = board * 32 + token
     bool valid;                 // board < n
+    bool prof_on;               // this thread keeps the CTA's phase clock
+    long long t_last;
 };
+
+// In-kernel phase accounting (the counterpart of the reference's prof::Timer,
+// csrc/encoder.cu:1110-1177): one thread per CTA charges the cycles since its previous mark to
+// a phase.  Off (one predictable branch per mark) unless the launch carries a counter buffer.
+enum { PH_EMBED = 0, PH_LN, PH_WAIT_MMA, PH_QKV_EPI, PH_PAIR_BAR, PH_ATTENTION, PH_O_READBACK, PH_O_QUANT,
+       PH_OUT_EPI, PH_FF1_EPI, PH_FF2_EPI, PH_HEAD, PH_COUNT };
+__device__ __forceinline__ void prof_mark(RowCtx& c, int phase) {
+    if (c.prof_on) {
+        const long long t = clock64();
+        long long* a = reinterpret_cast<long long*>(c.smem_gen + SM_PROF);
+        a[phase] += t - c.t_last;
+        c.t_last = t;
+    }
+}
 
 __device__ __forceinline__ uint32_t bar_addr(uint32_t smem, int idx) {
     return smem + SM_BAR + 8u * idx;
@@ -116,11 +134,13 @@ __device__ __forceinline__ float4 exchange(RowCtx& c, float4 mine) {
     return other;
 }
 
-__device__ __forceinline__ void row_wait_acc(RowCtx& c, int slot) {
+__device__ __forceinline__ void row_wait_acc(RowCtx& c, int slot, int phase_before) {
+    prof_mark(c, phase_before);
     const uint32_t n = slot ? c.full1 : c.full0;
     mbar_wait(bar_addr(c.smem, B_ACC_FULL + slot), n & 1, c.abort_flag, kErrRowAcc);
     if (slot) c.full1 = n + 1; else c.full0 = n + 1;
     tc_fence_after();
+    prof_mark(c, PH_WAIT_MMA);
 }
 // All of this warp's TMEM loads of the slot are done: hand it back to the MMA issuer.
 __device__ __forceinline__ void row_release_acc(RowCtx& c, int slot) {
@@ -454,7 +474,7 @@ __device__ __forceinline__ void attention_block(RowCtx& c, const Params& p, cons
     float o_amax = 0.f;
 #pragma unroll 1
     for (int j = 0; j < 4; ++j) {
-        row_wait_acc(c, 0);
+        row_wait_acc(c, 0, j == 0 ? PH_LN : PH_PAIR_BAR);
 #pragma unroll 1
         for (int g = 0; g < 3; ++g) {
             const int c0 = 96 * c.hf + 32 * g, m = c0 >> 6, cm = c0 & 63;
@@ -473,8 +493,11 @@ __device__ __forceinline__ void attention_block(RowCtx& c, const Params& p, cons
             }
         }
         row_release_acc(c, 0);
+        prof_mark(c, PH_QKV_EPI);
         named_bar_sync(1 + c.q, 64);       // this board's Q/K/V rows are staged
+        prof_mark(c, PH_PAIR_BAR);
         attention_unit(c, alive);
+        prof_mark(c, PH_ATTENTION);
         {
             // read back this row's 32 outputs of head 2j+hf, park them in tensor memory
             uint32_t oh[16];
@@ -490,9 +513,11 @@ __device__ __forceinline__ void attention_block(RowCtx& c, const Params& p, cons
                 store_h16(p.y + c.grow * kD + 32 * (2 * j + c.hf) + 16, oh + 8);
             }
         }
+        prof_mark(c, PH_O_READBACK);
         named_bar_sync(1 + c.q, 64);       // staging may be overwritten by the next chunk
     }
     tmem_wait_st();
+    prof_mark(c, PH_PAIR_BAR);
 
     // quantise the attention output into A (s8, per-row scale)
     {
@@ -520,7 +545,7 @@ __device__ __forceinline__ void attention_block(RowCtx& c, const Params& p, cons
     // out-projection: x = fp16(x + fp16(fp16(descale) + b_o)) (encoder.cu:631-686)
 #pragma unroll 1
     for (int u = 0; u < 2; ++u) {
-        row_wait_acc(c, u);
+        row_wait_acc(c, u, u == 0 ? PH_O_QUANT : PH_OUT_EPI);
 #pragma unroll 1
         for (int g = 0; g < 2; ++g) {
             const int col = 128 * u + 64 * c.hf + 32 * g;
@@ -537,6 +562,7 @@ __device__ __forceinline__ void attention_block(RowCtx& c, const Params& p, cons
         row_release_acc(c, u);
     }
     tmem_wait_st();
+    prof_mark(c, PH_OUT_EPI);
 }
 
 // FFN: four hidden chunks of 256; ff1 -> ReLU -> per-row u8 -> ff2 with an fp16 running
@@ -544,6 +570,7 @@ __device__ __forceinline__ void attention_block(RowCtx& c, const Params& p, cons
 __device__ __forceinline__ void ffn_block(RowCtx& c, const Params& p, const LayerParams& lp,
                                           float sa, bool cap) {
     float sa2_0 = 1.f, sa2_1 = 1.f;
+    prof_mark(c, PH_LN);
 #pragma unroll 1
     for (int st = 0; st < 8; ++st) {
         const int kind2 = (0xD4 >> st) & 1;
@@ -552,7 +579,7 @@ __device__ __forceinline__ void ffn_block(RowCtx& c, const Params& p, const Laye
             uint32_t hid[64];
 #pragma unroll
             for (int jh = 0; jh < 2; ++jh) {
-                row_wait_acc(c, jh);
+                row_wait_acc(c, jh, PH_FF1_EPI);
 #pragma unroll
                 for (int g = 0; g < 2; ++g) {
                     uint32_t acc[32];
@@ -582,11 +609,12 @@ __device__ __forceinline__ void ffn_block(RowCtx& c, const Params& p, const Laye
                     if (caph) *reinterpret_cast<uint4*>(p.cap_a + c.grow * kD + 128 * jh + 64 * c.hf + 16 * k) = v;
                 }
             row_publish(c, B_A2_READY + (ch & 1));
+            prof_mark(c, PH_FF1_EPI);
         } else {
             const float s1 = (ch & 1) ? sa2_1 : sa2_0;
 #pragma unroll 1
             for (int jh = 0; jh < 2; ++jh) {
-                row_wait_acc(c, jh);
+                row_wait_acc(c, jh, PH_FF2_EPI);
                 const float s2 = __ldg(lp.sw_ff2 + jh);
 #pragma unroll 1
                 for (int g = 0; g < 2; ++g) {
@@ -628,6 +656,7 @@ __device__ __forceinline__ void ffn_block(RowCtx& c, const Params& p, const Laye
                 row_release_acc(c, jh);
             }
             tmem_wait_st();
+            prof_mark(c, PH_FF2_EPI);
         }
     }
 }
@@ -678,6 +707,7 @@ __device__ __forceinline__ void row_warps_tile(RowCtx& c, const Params& p, int t
         }
         tmem_wait_st();
     }
+    prof_mark(c, PH_EMBED);
 
     const int n_ph = 2 * p.n_layers;
 #pragma unroll 1
@@ -713,7 +743,7 @@ __device__ __forceinline__ void row_warps_tile(RowCtx& c, const Params& p, int t
 
     // ---- heads: fp16 GEMM [128 x 256] x [96 x 256]^T, fp32 accumulate, rounded to fp16
     //      (encoder.cu:894-1079; the reference accumulates in fp16) -------------------------
-    row_wait_acc(c, 0);
+    row_wait_acc(c, 0, PH_LN);
     {
         uint32_t acc[32];
         tmem_ld32(c.tm + TM_ACC + 32 * c.hf, acc);
@@ -773,6 +803,7 @@ __device__ __forceinline__ void row_warps_tile(RowCtx& c, const Params& p, int t
             }
         }
     }
+    prof_mark(c, PH_HEAD);
 }
 
 // ------------------------------------------------------------------------------------------
@@ -926,6 +957,7 @@ __global__ void __launch_bounds__(kThreads, 1) encoder_kernel(const Params p) {
             mbar_init(bar_addr(smem, i), many ? kRowWarps : 1);
         }
         *abort_flag = 0;
+        for (int i = 0; i < 16; ++i) reinterpret_cast<long long*>(sm + SM_PROF)[i] = 0;
         fence_barrier_init();
     }
     if (warp == kMmaWarp) {
@@ -944,6 +976,8 @@ __global__ void __launch_bounds__(kThreads, 1) encoder_kernel(const Params p) {
         c.smem = smem; c.smem_gen = sm;
         c.tm = tmem + (static_cast<uint32_t>(32 * c.q) << 16);
         c.abort_flag = abort_flag; c.xpar = 0; c.full0 = c.full1 = 0;
+        c.prof_on = p.prof != nullptr && threadIdx.x == 0;
+        c.t_last = c.prof_on ? clock64() : 0;
         for (int tile = blockIdx.x; tile < n_tiles; tile += gridDim.x) row_warps_tile(c, p, tile);
     } else if (warp == kProducerWarp) {
         if (lane == 0) producer_loop(smem, abort_flag, p, blockIdx.x, gridDim.x, n_tiles);
@@ -956,6 +990,9 @@ __global__ void __launch_bounds__(kThreads, 1) encoder_kernel(const Params p) {
     tc_fence_after();
     if (warp == kMmaWarp) tmem_dealloc(tmem, TM_COLS);
     if (threadIdx.x == 0 && *abort_flag != 0) atomicCAS(p.status, 0, *abort_flag);
+    if (threadIdx.x == 0 && p.prof != nullptr)
+        for (int i = 0; i < PH_COUNT; ++i)
+            atomicAdd(p.prof + i, static_cast<unsigned long long>(reinterpret_cast<long long*>(sm + SM_PROF)[i]));
 }
 
 // ------------------------------------------------------------------------------------------
@@ -1059,6 +1096,8 @@ struct bf_handle {
     BlobHeader hdr{};
     uint8_t* blob = nullptr;
     int* status = nullptr;
+    unsigned long long* prof = nullptr;
+    bool prof_on = false;
     int sm_count = 0;
     long long launches = 0;
     // staging for bf_forward_host
@@ -1092,6 +1131,7 @@ int launch(bf_handle* h, const uint16_t* boards, const int16_t* control, const u
     p.y = static_cast<__half*>(y); p.debug_stage = stage; p.debug_layer = stage_layer;
     p.cap_layer = cap_layer; p.cap_op = cap_op; p.cap_a = cap_a; p.cap_acc = cap_acc;
     p.status = h->status;
+    p.prof = h->prof_on ? h->prof : nullptr;
     const int n_tiles = (n + 3) / 4;
     const int grid = n_tiles < h->sm_count ? n_tiles : h->sm_count;
     bf::encoder_kernel<<<grid, bf::kThreads, bf::kSmemRequest, stream>>>(p);
@@ -1157,7 +1197,7 @@ int bf_destroy(bf_handle* h) {
     if (h == nullptr) return BF_OK;
     cudaSetDevice(h->device);
     if (h->stream) { cudaStreamSynchronize(h->stream); cudaStreamDestroy(h->stream); }
-    cudaFree(h->blob); cudaFree(h->status); cudaFree(h->d_in); cudaFree(h->d_out);
+    cudaFree(h->blob); cudaFree(h->status); cudaFree(h->prof); cudaFree(h->d_in); cudaFree(h->d_out);
     delete h;
     return BF_OK;
 }
@@ -1254,6 +1294,32 @@ int bf_status(bf_handle* h, int* status) {
 }
 
 long long bf_launch_count(const bf_handle* h) { return h ? h->launches : 0; }
+
+int bf_profile(bf_handle* h, int enable) {
+    if (h == nullptr) return fail(BF_EINVAL, "null handle");
+    BF_CUDA(cudaSetDevice(h->device));
+    if (enable && h->prof == nullptr) BF_CUDA(cudaMalloc(&h->prof, 16 * sizeof(unsigned long long)));
+    if (h->prof != nullptr) BF_CUDA(cudaMemset(h->prof, 0, 16 * sizeof(unsigned long long)));
+    h->prof_on = enable != 0;
+    return BF_OK;
+}
+
+int bf_profile_read(bf_handle* h, long long* cycles, int n) {
+    if (h == nullptr || cycles == nullptr || n < 0) return fail(BF_EINVAL, "bad argument");
+    if (h->prof == nullptr) return fail(BF_EINVAL, "profiling was never enabled on this handle");
+    BF_CUDA(cudaSetDevice(h->device));
+    BF_CUDA(cudaDeviceSynchronize());
+    unsigned long long tmp[16];
+    BF_CUDA(cudaMemcpy(tmp, h->prof, sizeof(tmp), cudaMemcpyDeviceToHost));
+    BF_CUDA(cudaMemset(h->prof, 0, sizeof(tmp)));
+    for (int i = 0; i < n && i < 16; ++i) cycles[i] = static_cast<long long>(tmp[i]);
+    return BF_OK;
+}
+
+const char* bf_profile_phases(void) {
+    return "embed,layernorm_quantise,wait_mma,qkv_epilogue,pair_barrier,attention,attn_readback,"
+           "attn_quantise,out_proj_epilogue,ff1_epilogue,ff2_epilogue,heads";
+}
 
 int bf_selftest_umma(int device, int mode, const void* a, const void* w_image, void* out) {
     if (mode < 0 || mode > 3 || a == nullptr || w_image == nullptr || out == nullptr)

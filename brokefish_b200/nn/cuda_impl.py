@@ -278,6 +278,17 @@ class FusedEncoder:
             _ptr(promo), _ptr(value)), "bf_forward_host")
         return policy, promo, value
 
+    # -- in-kernel phase accounting (the reference's set_profile / read_profile hooks) ----
+    def set_profile(self, on: bool) -> None:
+        _native.check(_native.lib().bf_profile(self._handle, int(bool(on))), "bf_profile")
+
+    def read_profile(self) -> dict:
+        """``{phase: cycles}`` summed over CTAs since the last read; synchronises."""
+        buf = (ctypes.c_longlong * 16)()
+        _native.check(_native.lib().bf_profile_read(self._handle, buf, 16), "bf_profile_read")
+        names = _native.lib().bf_profile_phases().decode().split(",")
+        return {n: int(buf[i]) for i, n in enumerate(names)}
+
     def check_status(self) -> None:
         """Synchronise and raise if any launch hit a device-side time-out."""
         st = ctypes.c_int(0)

@@ -108,6 +108,16 @@ int bf_status(bf_handle* h, int* status);
 /* Number of kernel launches this handle has enqueued. */
 long long bf_launch_count(const bf_handle* h);
 
+/* In-kernel phase accounting, the counterpart of the reference's `set_profile /
+ * reset_profile / read_profile / profile_phases` hooks (csrc/encoder.cu:1110-1177,
+ * 1886-1916).  While enabled, one thread of every CTA charges its clock cycles to the phase
+ * it is in; `bf_profile_read` synchronises, returns the cycle sums since the last read (up
+ * to 16 values, in the order `bf_profile_phases()` names them, comma separated) and clears
+ * them.  Enabling or disabling also clears. */
+int bf_profile(bf_handle* h, int enable);
+int bf_profile_read(bf_handle* h, long long* cycles, int n);
+const char* bf_profile_phases(void);
+
 /* Tensor-core self test (no network): one 128-row tile times a packed weight tile.
  *   mode 0: s8 x s8, N=128, K=256     mode 1: u8 x s8, N=128, K=256
  *   mode 2: s8 x s8, N=192, K=256     mode 3: f16 x f16 -> f32, N=96, K=256
