@@ -12,11 +12,12 @@
 // Shape of the kernel
 //   * persistent grid, one CTA per SM, each CTA loops over tiles of 128 token rows
 //     (4 boards);
-//   * 10 warps: 8 "row" warps, one weight-stream producer, one MMA issuer;
-//   * row warps: thread = (row, half).  Warp w works on TMEM lanes 32*(w%4)..+31, i.e.
-//     on board w%4 of the tile; warps w and w+4 split each row's columns.  All
-//     LayerNorm / quantise / descale work is thread-local plus one exchange between the
-//     two halves; the two warps of a board synchronise with a 64-thread named barrier;
+//   * 18 warps: 16 "row" warps, one weight-stream producer, one MMA issuer;
+//   * row warps: thread = (row, quarter).  Warp w works on TMEM lanes 32*(w%4)..+31, i.e.
+//     on board w%4 of the tile, and on quarter w/4 of each row's columns.  All LayerNorm /
+//     quantise / descale work is thread-local plus one exchange among the four quarters;
+//     the four warps of a board synchronise with a 128-thread named barrier, and the four
+//     boards of a tile never wait for one another except through the shared MMA;
 //   * weights never sit in shared memory for longer than one use: the host packs them
 //     as ready-made 128-byte-swizzled K-major stage images and the producer streams
 //     them through a ring with cp.async.bulk + mbarrier;
@@ -39,7 +40,7 @@ namespace bf {
 using namespace bfptx;
 
 constexpr int kD = 256, kDFF = 1024, kT = 32, kRows = 128;
-constexpr int kRowWarps = 8, kProducerWarp = 8, kMmaWarp = 9, kThreads = 320;
+constexpr int kRowWarps = 16, kProducerWarp = 16, kMmaWarp = 17, kThreads = 576;
 constexpr int kLayerStreamBytes = 786432, kLparamStride = 4736;
 constexpr int LP_SW_QKV = 0, LP_SW_O = 24, LP_SW_FF1 = 32, LP_SW_FF2 = 64;
 constexpr int LP_B_QKV = 128, LP_B_O = 1664, LP_B_FF1 = 2176, LP_B_FF2 = 4224;
@@ -51,8 +52,8 @@ constexpr uint32_t SM_A = 0;            // s8 A operand, 2 K-slabs of [128 rows]
 constexpr uint32_t SM_R = 32768;        // 64 KB: Q/K/V staging (3 x 16 KB) | hidden u8
                                         // A operand x2 (2 x 32 KB) | fp16 head A (4 x 16 KB)
 constexpr uint32_t SM_RING = 98304;     // 112 KB weight ring: 4 x 24 KB or 7 x 16 KB
-constexpr uint32_t SM_XCH = 212992;     // 8 KB: float4 [2 parity][2 half][128 rows]
-constexpr uint32_t SM_BAR = 221184;     // mbarriers
+constexpr uint32_t SM_XCH = 212992;     // 16 KB: float4 [2 parity][4 quarter][128 rows]
+constexpr uint32_t SM_BAR = 229376;     // mbarriers
 constexpr uint32_t SM_MISC = SM_BAR + 256;
 constexpr uint32_t SM_PROF = SM_MISC + 64;     // 16 x int64 phase cycle counters
 constexpr uint32_t SM_BYTES = SM_PROF + 128;
@@ -91,9 +92,10 @@ struct Params {
     unsigned long long* prof;   // 16 phase counters (cycles of warp 0, lane 0 of every CTA) or null
 };
 
-// Per-thread context of a row warp.
+// Per-thread context of a row warp.  Sixteen row warps: warp w works on TMEM lanes
+// 32*(w%4)..+31 (board w%4 of the tile) and on quarter w/4 of each row's columns.
 struct RowCtx {
-    int lane, q, hf, row;       // q: board within the tile, hf: which half of the columns
+    int lane, q, qt, row;       // q: board within the tile, qt: which quarter of the columns
     uint32_t smem;              // shared base (shared-space address)
     uint8_t* smem_gen;          // shared base (generic pointer)
     uint32_t tm;                // TMEM base address with this warp's lane offset
@@ -124,14 +126,22 @@ __device__ __forceinline__ uint32_t bar_addr(uint32_t smem, int idx) {
     return smem + SM_BAR + 8u * idx;
 }
 
-// Exchange one float4 with the thread that owns the other half of this row.
-__device__ __forceinline__ float4 exchange(RowCtx& c, float4 mine) {
+// The four warps of a board meet here (named barrier 1 + board, 128 threads).
+__device__ __forceinline__ void board_sync(const RowCtx& c) { named_bar_sync(1 + c.q, 128); }
+
+// Exchange one float4 among the four threads that share a row; `all[k]` is quarter k's.
+__device__ __forceinline__ void exchange4(RowCtx& c, float4 mine, float4 (&all)[4]) {
     float4* xch = reinterpret_cast<float4*>(c.smem_gen + SM_XCH);
-    xch[(c.xpar * 2 + c.hf) * kRows + c.row] = mine;
-    named_bar_sync(1 + c.q, 64);
-    const float4 other = xch[(c.xpar * 2 + (c.hf ^ 1)) * kRows + c.row];
+    xch[(c.xpar * 4 + c.qt) * kRows + c.row] = mine;
+    board_sync(c);
+#pragma unroll
+    for (int k = 0; k < 4; ++k) all[k] = xch[(c.xpar * 4 + k) * kRows + c.row];
     c.xpar ^= 1;
-    return other;
+}
+__device__ __forceinline__ float exchange_max(RowCtx& c, float mine) {
+    float4 all[4];
+    exchange4(c, make_float4(mine, 0.f, 0.f, 0.f), all);
+    return fmaxf(fmaxf(all[0].x, all[1].x), fmaxf(all[2].x, all[3].x));
 }
 
 __device__ __forceinline__ void row_wait_acc(RowCtx& c, int slot, int phase_before) {
@@ -184,9 +194,6 @@ __device__ __forceinline__ uint32_t sw_off(int row, int chunk) {
 // Exact s32 -> f32 without the conversion unit (which issues at a quarter of the FMA
 // rate).  |v| < 2^22: add v to the bit pattern of 1.5 * 2^23 and subtract that constant.
 // s8 x s8 over K = 256 is bounded by 127 * 127 * 256 = 4,129,024 < 2^22.
-__device__ __forceinline__ float i2f_22(uint32_t v) {
-    return __fadd_rn(__uint_as_float(v + 0x4B400000u), -12582912.0f);
-}
 // |v| < 2^23 (u8 x s8 over K = 256 reaches 255 * 127 * 256 = 8,290,560): the magnitude
 // goes into the mantissa of 2^23, the sign bit is put back afterwards.
 __device__ __forceinline__ float i2f_23(uint32_t v) {
@@ -196,21 +203,21 @@ __device__ __forceinline__ float i2f_23(uint32_t v) {
     return __uint_as_float(__float_as_uint(f) | (v & 0x80000000u));
 }
 
-// `(float(acc) * sa) * sw` -> fp16, + fp16 bias, optional ReLU; 32 columns -> 16 pairs
+// `(float(acc) * sa) * sw` -> fp16, + fp16 bias, optional ReLU; kN columns -> kN/2 pairs
 // (int8_gemm.cuh:276-297, encoder.cu:631-644, 1482-1489).
-template <bool kRelu>
-__device__ __forceinline__ void descale32(const uint32_t (&acc)[32], float sa, float sw,
-                                          const __half* bias, uint32_t* out) {
+template <int kN, bool kRelu>
+__device__ __forceinline__ void descale(const uint32_t* acc, float sa, float sw, const __half* bias,
+                                        uint32_t* out) {
     const uint4* b4 = reinterpret_cast<const uint4*>(bias);
     const uint64_t sa2 = pk2(sa, sa), sw2 = pk2(sw, sw), nm2 = pk2(-12582912.0f, -12582912.0f);
 #pragma unroll
-    for (int v = 0; v < 4; ++v) {
+    for (int v = 0; v < kN / 8; ++v) {
         const uint4 bv = __ldg(b4 + v);
         const uint32_t bw[4] = {bv.x, bv.y, bv.z, bv.w};
 #pragma unroll
         for (int k = 0; k < 4; ++k) {
             const int i = 4 * v + k;
-            // exact s32 -> f32 (see i2f_22), then the two fp32 multiplies, both lanes at once
+            // exact s32 -> f32, then the two fp32 multiplies, both lanes at once
             const uint64_t f = add2(pk2(__uint_as_float(acc[2 * i] + 0x4B400000u),
                                         __uint_as_float(acc[2 * i + 1] + 0x4B400000u)), nm2);
             __half2 h = __hadd2(as_h2(f2_to_h2(mul2(mul2(f, sa2), sw2))), as_h2(bw[k]));
@@ -220,47 +227,34 @@ __device__ __forceinline__ void descale32(const uint32_t (&acc)[32], float sa, f
     }
 }
 
-__device__ __forceinline__ float amax16(const uint32_t* h, int n, bool take_abs) {
+template <int kN>
+__device__ __forceinline__ float amax_h2(const uint32_t* h, bool take_abs) {
     __half2 m = __float2half2_rn(0.0f);
 #pragma unroll
-    for (int i = 0; i < n; ++i) {
+    for (int i = 0; i < kN; ++i) {
         const __half2 v = as_h2(h[i]);
         m = __hmax2(m, take_abs ? __habs2(v) : v);
     }
     return fmaxf(__low2float(m), __high2float(m));
 }
 
-__device__ __forceinline__ void store_acc32(int32_t* dst, const uint32_t (&acc)[32]) {
-    int4* d4 = reinterpret_cast<int4*>(dst);
-#pragma unroll
-    for (int k = 0; k < 8; ++k) d4[k] = make_int4(acc[4 * k], acc[4 * k + 1], acc[4 * k + 2], acc[4 * k + 3]);
-}
-__device__ __forceinline__ void store_h16(__half* dst, const uint32_t* h) {
+template <int kN>
+__device__ __forceinline__ void store_words(void* dst, const uint32_t* w) {
     uint4* d4 = reinterpret_cast<uint4*>(dst);
 #pragma unroll
-    for (int k = 0; k < 4; ++k) d4[k] = make_uint4(h[4 * k], h[4 * k + 1], h[4 * k + 2], h[4 * k + 3]);
+    for (int k = 0; k < kN / 4; ++k) d4[k] = make_uint4(w[4 * k], w[4 * k + 1], w[4 * k + 2], w[4 * k + 3]);
 }
 
-// Debug store of this thread's 64 packed pairs (columns 64*hf + [0,64) and
-// 128 + 64*hf + [0,64)) of its row.
-__device__ __forceinline__ void dump_row64(const RowCtx& c, __half* y, const uint32_t* xr) {
-    if (!c.valid) return;
-#pragma unroll
-    for (int g = 0; g < 2; ++g)
-#pragma unroll
-        for (int k = 0; k < 2; ++k)
-            store_h16(y + c.grow * kD + 128 * g + 64 * c.hf + 32 * k, xr + 32 * g + 16 * k);
-}
-
-// One LayerNorm of the residual stream (TMEM) for this thread's half row, in two passes over
-// four 32-column groups, followed either by the s8 quantisation into the A operand
-// (returns the row scale) or, for the final norm, by the affine and the fp16 store into the
-// head GEMM's A operand.
+// One LayerNorm of the residual stream (TMEM) for this thread's quarter row (columns
+// 32*qt + [0,32) and 128 + 32*qt + [0,32)), in two passes, followed either by the s8
+// quantisation into the A operand (returns the row scale) or, for the final norm, by the
+// affine and the fp16 store into the head GEMM's A operand.
 //
 // Statistics: fp32, one pass, variance clamped at zero (encoder.cu:584-598); summation order
-// (mirrored by the CPU oracle): even and odd columns accumulate separately and sequentially,
-// then even + odd, then the two halves.  1/sqrt is correctly rounded where the reference uses
-// the hardware approximation.  x_hat = fp16((x - mean) * rstd).
+// (mirrored by the CPU oracle): within a quarter even and odd columns accumulate separately
+// and sequentially, then even + odd; the quarters combine as (q0 + q1) + (q2 + q3).  1/sqrt
+// is correctly rounded where the reference uses the hardware approximation.
+// x_hat = fp16((x - mean) * rstd).
 //
 // Quantisation (int8_gemm.cuh:159-199): scale = amax(x_hat)/127, all-zero row -> 1.  The map
 // x -> x_hat is monotone (every rounding in it is), so amax(x_hat) is reached at the row's
@@ -271,15 +265,11 @@ __device__ __forceinline__ float ln_stage(RowCtx& c, const Params& p, bool final
     uint64_t sum2 = pk2(0.f, 0.f), sq2 = pk2(0.f, 0.f);      // (even, odd) column lanes
     __half2 mn = __float2half2_rn(65504.0f), mx = __float2half2_rn(-65504.0f);
 #pragma unroll 1
-    for (int k = 0; k < 4; ++k) {
+    for (int u = 0; u < 2; ++u) {
         uint32_t x[16];
-        tmem_ld16(c.tm + TM_X + 64 * (k >> 1) + 32 * c.hf + 16 * (k & 1), x);
+        tmem_ld16(c.tm + TM_X + 64 * u + 16 * c.qt, x);
         tmem_wait_ld();
-        if (dump_x && c.valid) {
-            __half* dst = p.y + c.grow * kD + 128 * (k >> 1) + 64 * c.hf + 32 * (k & 1);
-            store_h16(dst, x);
-            store_h16(dst + 16, x + 8);
-        }
+        if (dump_x && c.valid) store_words<16>(p.y + c.grow * kD + 128 * u + 32 * c.qt, x);
 #pragma unroll
         for (int i = 0; i < 16; ++i) {
             const __half2 h = as_h2(x[i]);
@@ -293,34 +283,36 @@ __device__ __forceinline__ float ln_stage(RowCtx& c, const Params& p, bool final
     float s_lo, s_hi, q_lo, q_hi;
     upk2(sum2, s_lo, s_hi);
     upk2(sq2, q_lo, q_hi);
-    const float s = __fadd_rn(s_lo, s_hi), qq = __fadd_rn(q_lo, q_hi);
-    const float my_min = fminf(__low2float(mn), __high2float(mn));
-    const float my_max = fmaxf(__low2float(mx), __high2float(mx));
-    const float4 o = exchange(c, make_float4(s, qq, my_min, my_max));
-    const float tot = __fadd_rn(s, o.x), totq = __fadd_rn(qq, o.y);
+    float4 all[4];
+    exchange4(c, make_float4(__fadd_rn(s_lo, s_hi), __fadd_rn(q_lo, q_hi),
+                             fminf(__low2float(mn), __high2float(mn)),
+                             fmaxf(__low2float(mx), __high2float(mx))), all);
+    const float tot = __fadd_rn(__fadd_rn(all[0].x, all[1].x), __fadd_rn(all[2].x, all[3].x));
+    const float totq = __fadd_rn(__fadd_rn(all[0].y, all[1].y), __fadd_rn(all[2].y, all[3].y));
+    const float xmin = fminf(fminf(all[0].z, all[1].z), fminf(all[2].z, all[3].z));
+    const float xmax = fmaxf(fmaxf(all[0].w, all[1].w), fmaxf(all[2].w, all[3].w));
     const float mean = __fmul_rn(tot, 1.0f / 256.0f);
     const float var = fmaxf(__fmaf_rn(-mean, mean, __fmul_rn(totq, 1.0f / 256.0f)), 0.f);
     const float rstd = __frsqrt_rn(__fadd_rn(var, p.eps));
-    const float e_lo = __half2float(__float2half_rn(__fmul_rn(__fsub_rn(fminf(my_min, o.z), mean), rstd)));
-    const float e_hi = __half2float(__float2half_rn(__fmul_rn(__fsub_rn(fmaxf(my_max, o.w), mean), rstd)));
+    const float e_lo = __half2float(__float2half_rn(__fmul_rn(__fsub_rn(xmin, mean), rstd)));
+    const float e_hi = __half2float(__float2half_rn(__fmul_rn(__fsub_rn(xmax, mean), rstd)));
     const float amax = fmaxf(fabsf(e_lo), fabsf(e_hi));
     const float sc = amax > 0.f ? __fdiv_rn(amax, 127.0f) : 1.0f;
     const float inv = __fdiv_rn(1.0f, sc);
+    const uint64_t nmean2 = pk2(-mean, -mean), rstd2 = pk2(rstd, rstd);
 #pragma unroll 1
-    for (int k = 0; k < 4; ++k) {
-        const int g = k >> 1, sub = k & 1;
+    for (int u = 0; u < 2; ++u) {
         uint32_t x[16];
-        tmem_ld16(c.tm + TM_X + 64 * g + 32 * c.hf + 16 * sub, x);
+        tmem_ld16(c.tm + TM_X + 64 * u + 16 * c.qt, x);
         tmem_wait_ld();
-        const int col = 128 * g + 64 * c.hf + 32 * sub;
-        const uint64_t nmean2 = pk2(-mean, -mean), rstd2 = pk2(rstd, rstd);
+        const int col = 128 * u + 32 * c.qt;
         if (!final_norm) {
 #pragma unroll
             for (int i = 0; i < 16; ++i) x[i] = f2_to_h2(mul2(add2(h2_to_f2(x[i]), nmean2), rstd2));
 #pragma unroll
             for (int v = 0; v < 2; ++v) {
                 const uint4 qv = quant16(&x[8 * v], inv);
-                *reinterpret_cast<uint4*>(c.smem_gen + SM_A + g * 16384 + sw_off(c.row, 4 * c.hf + 2 * sub + v)) = qv;
+                *reinterpret_cast<uint4*>(c.smem_gen + SM_A + u * 16384 + sw_off(c.row, 2 * c.qt + v)) = qv;
                 if (capture && c.valid) *reinterpret_cast<uint4*>(p.cap_a + c.grow * kD + col + 16 * v) = qv;
             }
         } else {
@@ -336,50 +328,45 @@ __device__ __forceinline__ float ln_stage(RowCtx& c, const Params& p, bool final
                 for (int j = 0; j < 4; ++j)
                     x[4 * v + j] = f2_to_h2(fma2(mul2(add2(h2_to_f2(x[4 * v + j]), nmean2), rstd2),
                                                  h2_to_f2(gw[j]), h2_to_f2(bw[j])));
-                *reinterpret_cast<uint4*>(c.smem_gen + SM_R + (2 * g + c.hf) * 16384 + sw_off(c.row, 4 * sub + v)) =
+                // head A slab = col / 64 = 2u + qt/2; 16-byte group within the 64-column slab
+                *reinterpret_cast<uint4*>(c.smem_gen + SM_R + (2 * u + (c.qt >> 1)) * 16384 +
+                                          sw_off(c.row, 4 * (c.qt & 1) + v)) =
                     make_uint4(x[4 * v], x[4 * v + 1], x[4 * v + 2], x[4 * v + 3]);
             }
         }
-        if (dump_xn && c.valid) {
-            store_h16(p.y + c.grow * kD + col, x);
-            store_h16(p.y + c.grow * kD + col + 16, x + 8);
-        }
+        if (dump_xn && c.valid) store_words<16>(p.y + c.grow * kD + col, x);
     }
     return sc;
 }
 
-// One (board, head) attention unit on the staged fp16 Q/K/V of a head pair: S = Q K^T
-// (scale pre-folded), dead keys -inf, fp32 softmax with __expf, P rounded to fp16,
-// O = P V; both products accumulate in fp32 where the reference accumulates in fp16
-// (encoder.cu:715-797).  The result overwrites this unit's own Q block.
+// Half of one (board, head) attention unit: 16 query rows against the board's 32 keys, on the
+// staged fp16 Q/K/V of a head pair.  S = Q K^T (scale pre-folded), dead keys -inf, fp32
+// softmax with the hardware 2^x, P rounded to fp16, O = P V; both products accumulate in fp32
+// where the reference accumulates in fp16 (encoder.cu:715-797).  Warp (q, qt) takes head
+// qt & 1 of the pair and query rows 16 * (qt >> 1) .. +15; the result overwrites its own
+// block of Q.
 __device__ __forceinline__ void attention_unit(const RowCtx& c, uint32_t alive) {
     const uint32_t qs = c.smem + SM_R, ks = qs + 16384, vs = qs + 32768;
-    const int r0 = 32 * c.q, lane = c.lane, g = lane >> 2, t = lane & 3;
-    uint32_t qa[2][2][4];
+    const int hh = c.qt & 1, r0 = 32 * c.q, rq = r0 + 16 * (c.qt >> 1);
+    const int lane = c.lane, g = lane >> 2, t = lane & 3;
+    uint32_t qa[2][4];
 #pragma unroll
-    for (int mt = 0; mt < 2; ++mt)
+    for (int kk = 0; kk < 2; ++kk) {
+        const int row = rq + (lane & 15);
+        ldmatrix_x4(qa[kk], qs + sw_off(row, 4 * hh + 2 * kk + (lane >> 4)));
+    }
+    float s[4][4];
 #pragma unroll
-        for (int kk = 0; kk < 2; ++kk) {
-            const int row = r0 + 16 * mt + (lane & 15);
-            ldmatrix_x4(qa[mt][kk], qs + sw_off(row, 4 * c.hf + 2 * kk + (lane >> 4)));
-        }
-    float s[2][4][4];
+    for (int nt = 0; nt < 4; ++nt)
 #pragma unroll
-    for (int mt = 0; mt < 2; ++mt)
-#pragma unroll
-        for (int nt = 0; nt < 4; ++nt)
-#pragma unroll
-            for (int k = 0; k < 4; ++k) s[mt][nt][k] = 0.f;
+        for (int k = 0; k < 4; ++k) s[nt][k] = 0.f;
 #pragma unroll
     for (int nt = 0; nt < 4; ++nt) {
         uint32_t kb[4];
         const int row = r0 + 8 * nt + (lane & 7);
-        ldmatrix_x4(kb, ks + sw_off(row, 4 * c.hf + (lane >> 3)));
-#pragma unroll
-        for (int mt = 0; mt < 2; ++mt) {
-            mma_f16_f32(s[mt][nt], qa[mt][0], kb[0], kb[1]);
-            mma_f16_f32(s[mt][nt], qa[mt][1], kb[2], kb[3]);
-        }
+        ldmatrix_x4(kb, ks + sw_off(row, 4 * hh + (lane >> 3)));
+        mma_f16_f32(s[nt], qa[0], kb[0], kb[1]);
+        mma_f16_f32(s[nt], qa[1], kb[2], kb[3]);
     }
     // dead keys get -inf added; this lane's eight key columns are 8*nt + 2*t + {0,1}
     float kb_mask[4][2];
@@ -387,78 +374,66 @@ __device__ __forceinline__ void attention_unit(const RowCtx& c, uint32_t alive) 
     for (int nt = 0; nt < 4; ++nt)
 #pragma unroll
         for (int k = 0; k < 2; ++k) kb_mask[nt][k] = ((alive >> (8 * nt + 2 * t + k)) & 1u) ? 0.f : -INFINITY;
-    uint32_t pa[2][2][4];
+    uint32_t pa[2][4];
 #pragma unroll
-    for (int mt = 0; mt < 2; ++mt)
-#pragma unroll
-        for (int hi = 0; hi < 2; ++hi) {
-            float mx = -INFINITY;
-#pragma unroll
-            for (int nt = 0; nt < 4; ++nt)
-#pragma unroll
-                for (int k = 0; k < 2; ++k) {
-                    float& v = s[mt][nt][2 * hi + k];
-                    v += kb_mask[nt][k];
-                    mx = fmaxf(mx, v);
-                }
-            mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 1));
-            mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 2));
-            // exp(v - mx) = 2^(v*log2e - mx*log2e); an all-dead row keeps the reference's NaN
-            const float nmx = -mx * 1.4426950408889634f;
-            float sum = 0.f;
-#pragma unroll
-            for (int nt = 0; nt < 4; ++nt)
-#pragma unroll
-                for (int k = 0; k < 2; ++k) {
-                    float& v = s[mt][nt][2 * hi + k];
-                    v = ex2_approx(__fmaf_rn(v, 1.4426950408889634f, nmx));
-                    sum += v;
-                }
-            sum += __shfl_xor_sync(0xffffffffu, sum, 1);
-            sum += __shfl_xor_sync(0xffffffffu, sum, 2);
-            const float inv = 1.0f / sum;
-#pragma unroll
-            for (int kk = 0; kk < 2; ++kk) {
-                pa[mt][kk][hi] = pack_h2(s[mt][2 * kk][2 * hi] * inv, s[mt][2 * kk][2 * hi + 1] * inv);
-                pa[mt][kk][2 + hi] =
-                    pack_h2(s[mt][2 * kk + 1][2 * hi] * inv, s[mt][2 * kk + 1][2 * hi + 1] * inv);
-            }
-        }
-    float o[2][4][4];
-#pragma unroll
-    for (int mt = 0; mt < 2; ++mt)
+    for (int hi = 0; hi < 2; ++hi) {
+        float mx = -INFINITY;
 #pragma unroll
         for (int nt = 0; nt < 4; ++nt)
 #pragma unroll
-            for (int k = 0; k < 4; ++k) o[mt][nt][k] = 0.f;
+            for (int k = 0; k < 2; ++k) {
+                float& v = s[nt][2 * hi + k];
+                v += kb_mask[nt][k];
+                mx = fmaxf(mx, v);
+            }
+        mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 1));
+        mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 2));
+        // exp(v - mx) = 2^(v*log2e - mx*log2e); an all-dead row keeps the reference's NaN
+        const float nmx = -mx * 1.4426950408889634f;
+        float sum = 0.f;
+#pragma unroll
+        for (int nt = 0; nt < 4; ++nt)
+#pragma unroll
+            for (int k = 0; k < 2; ++k) {
+                float& v = s[nt][2 * hi + k];
+                v = ex2_approx(__fmaf_rn(v, 1.4426950408889634f, nmx));
+                sum += v;
+            }
+        sum += __shfl_xor_sync(0xffffffffu, sum, 1);
+        sum += __shfl_xor_sync(0xffffffffu, sum, 2);
+        const float inv = 1.0f / sum;
+#pragma unroll
+        for (int kk = 0; kk < 2; ++kk) {
+            pa[kk][hi] = pack_h2(s[2 * kk][2 * hi] * inv, s[2 * kk][2 * hi + 1] * inv);
+            pa[kk][2 + hi] = pack_h2(s[2 * kk + 1][2 * hi] * inv, s[2 * kk + 1][2 * hi + 1] * inv);
+        }
+    }
+    float o[4][4];
+#pragma unroll
+    for (int nt = 0; nt < 4; ++nt)
+#pragma unroll
+        for (int k = 0; k < 4; ++k) o[nt][k] = 0.f;
 #pragma unroll
     for (int nt = 0; nt < 4; ++nt) {
         uint32_t vb[4];
-        const int row = r0 + lane;
-        ldmatrix_x4_trans(vb, vs + sw_off(row, 4 * c.hf + nt));
-#pragma unroll
-        for (int mt = 0; mt < 2; ++mt) {
-            mma_f16_f32(o[mt][nt], pa[mt][0], vb[0], vb[1]);
-            mma_f16_f32(o[mt][nt], pa[mt][1], vb[2], vb[3]);
-        }
+        ldmatrix_x4_trans(vb, vs + sw_off(r0 + lane, 4 * hh + nt));
+        mma_f16_f32(o[nt], pa[0], vb[0], vb[1]);
+        mma_f16_f32(o[nt], pa[1], vb[2], vb[3]);
     }
     __syncwarp();   // every lane's Q fragments are in registers before Q is overwritten
 #pragma unroll
-    for (int mt = 0; mt < 2; ++mt)
-#pragma unroll
-        for (int nt = 0; nt < 4; ++nt) {
-            const int row = r0 + 16 * mt + g;
-            *reinterpret_cast<uint32_t*>(c.smem_gen + SM_R + sw_off(row, 4 * c.hf + nt) + 4 * t) =
-                pack_h2(o[mt][nt][0], o[mt][nt][1]);
-            *reinterpret_cast<uint32_t*>(c.smem_gen + SM_R + sw_off(row + 8, 4 * c.hf + nt) + 4 * t) =
-                pack_h2(o[mt][nt][2], o[mt][nt][3]);
-        }
-    __syncwarp();
+    for (int nt = 0; nt < 4; ++nt) {
+        const int row = rq + g;
+        *reinterpret_cast<uint32_t*>(c.smem_gen + SM_R + sw_off(row, 4 * hh + nt) + 4 * t) =
+            pack_h2(o[nt][0], o[nt][1]);
+        *reinterpret_cast<uint32_t*>(c.smem_gen + SM_R + sw_off(row + 8, 4 * hh + nt) + 4 * t) =
+            pack_h2(o[nt][2], o[nt][3]);
+    }
 }
 
 // ------------------------------------------------------------------------------------------
-// Row-warp work, written as run-time loops over 32-column groups so that the whole layer
-// body stays small enough for the instruction cache.
+// Row-warp work, written as run-time loops over column groups so that the whole layer body
+// stays small enough for the instruction cache.
 // ------------------------------------------------------------------------------------------
 struct LayerParams {
     const float *sw_qkv, *sw_o, *sw_ff1, *sw_ff2;
@@ -467,7 +442,7 @@ struct LayerParams {
 
 // QKV in four head-pair chunks with attention per chunk, then the attention output is
 // quantised into A, then out-projection + residual into the residual stream (TMEM).
-// Returns nothing; `sa` is the scale of the row in A on entry.
+// `sa` is the scale of the row in A on entry.
 __device__ __forceinline__ void attention_block(RowCtx& c, const Params& p, const LayerParams& lp,
                                                 float sa, uint32_t alive, bool cap, bool dbgl) {
     const int dbg = p.debug_stage;
@@ -475,69 +450,60 @@ __device__ __forceinline__ void attention_block(RowCtx& c, const Params& p, cons
 #pragma unroll 1
     for (int j = 0; j < 4; ++j) {
         row_wait_acc(c, 0, j == 0 ? PH_LN : PH_PAIR_BAR);
+        // this thread's 48 of the chunk's 192 columns, 16 at a time
 #pragma unroll 1
         for (int g = 0; g < 3; ++g) {
-            const int c0 = 96 * c.hf + 32 * g, m = c0 >> 6, cm = c0 & 63;
-            uint32_t acc[32], h[16];
-            tmem_ld32(c.tm + TM_ACC + c0, acc);
+            const int c0 = 48 * c.qt + 16 * g, m = c0 >> 6, cm = c0 & 63;
+            uint32_t acc[16], h[8];
+            tmem_ld16(c.tm + TM_ACC + c0, acc);
             tmem_wait_ld();
-            if (cap && p.cap_op == BF_OP_QKV && c.valid) store_acc32(p.cap_acc + c.grow * 768 + j * 192 + c0, acc);
-            descale32<false>(acc, sa, __ldg(lp.sw_qkv + m * 2 + (j >> 1)), lp.b_qkv + j * 192 + c0, h);
+            if (cap && p.cap_op == BF_OP_QKV && c.valid) store_words<16>(p.cap_acc + c.grow * 768 + j * 192 + c0, acc);
+            descale<16, false>(acc, sa, __ldg(lp.sw_qkv + m * 2 + (j >> 1)), lp.b_qkv + j * 192 + c0, h);
 #pragma unroll
-            for (int k = 0; k < 4; ++k)
+            for (int k = 0; k < 2; ++k)
                 *reinterpret_cast<uint4*>(c.smem_gen + SM_R + m * 16384 + sw_off(c.row, (cm >> 3) + k)) =
                     make_uint4(h[4 * k], h[4 * k + 1], h[4 * k + 2], h[4 * k + 3]);
-            if (dbgl && dbg == 5 + m && c.valid) {
-                store_h16(p.y + c.grow * kD + 64 * j + cm, h);
-                store_h16(p.y + c.grow * kD + 64 * j + cm + 16, h + 8);
-            }
+            if (dbgl && dbg == 5 + m && c.valid) store_words<8>(p.y + c.grow * kD + 64 * j + cm, h);
         }
         row_release_acc(c, 0);
         prof_mark(c, PH_QKV_EPI);
-        named_bar_sync(1 + c.q, 64);       // this board's Q/K/V rows are staged
+        board_sync(c);                     // this board's Q/K/V rows are staged
         prof_mark(c, PH_PAIR_BAR);
         attention_unit(c, alive);
         prof_mark(c, PH_ATTENTION);
+        board_sync(c);                     // all four warps' outputs are in the Q block
         {
-            // read back this row's 32 outputs of head 2j+hf, park them in tensor memory
-            uint32_t oh[16];
+            // read back 16 of this row's 64 outputs of the head pair, park them in tensor memory
+            uint32_t oh[8];
 #pragma unroll
-            for (int k = 0; k < 4; ++k) {
-                const uint4 v = *reinterpret_cast<const uint4*>(c.smem_gen + SM_R + sw_off(c.row, 4 * c.hf + k));
+            for (int k = 0; k < 2; ++k) {
+                const uint4 v = *reinterpret_cast<const uint4*>(c.smem_gen + SM_R + sw_off(c.row, 2 * c.qt + k));
                 oh[4 * k] = v.x; oh[4 * k + 1] = v.y; oh[4 * k + 2] = v.z; oh[4 * k + 3] = v.w;
             }
-            o_amax = fmaxf(o_amax, amax16(oh, 16, true));
-            tmem_st16(c.tm + TM_OY + 16 * (2 * j + c.hf), oh);
-            if (dbgl && dbg == 4 && c.valid) {
-                store_h16(p.y + c.grow * kD + 32 * (2 * j + c.hf), oh);
-                store_h16(p.y + c.grow * kD + 32 * (2 * j + c.hf) + 16, oh + 8);
-            }
+            o_amax = fmaxf(o_amax, amax_h2<8>(oh, true));
+            tmem_st8(c.tm + TM_OY + 32 * j + 8 * c.qt, oh);
+            if (dbgl && dbg == 4 && c.valid) store_words<8>(p.y + c.grow * kD + 64 * j + 16 * c.qt, oh);
         }
         prof_mark(c, PH_O_READBACK);
-        named_bar_sync(1 + c.q, 64);       // staging may be overwritten by the next chunk
+        board_sync(c);                     // staging may be overwritten by the next chunk
     }
     tmem_wait_st();
     prof_mark(c, PH_PAIR_BAR);
 
     // quantise the attention output into A (s8, per-row scale)
     {
-        const float4 o = exchange(c, make_float4(o_amax, 0.f, 0.f, 0.f));
-        const float amax = fmaxf(o_amax, o.x);
+        const float amax = exchange_max(c, o_amax);
         sa = amax > 0.f ? __fdiv_rn(amax, 127.0f) : 1.0f;
         const float inv = __fdiv_rn(1.0f, sa);
         const bool capo = cap && p.cap_op == BF_OP_OUT && c.valid;
 #pragma unroll 1
-        for (int jj = 0; jj < 4; ++jj) {
-            const int hd = 2 * jj + c.hf;
-            uint32_t oh[16];
-            tmem_ld16(c.tm + TM_OY + 16 * hd, oh);
+        for (int j = 0; j < 4; ++j) {
+            uint32_t oh[8];
+            tmem_ld8(c.tm + TM_OY + 32 * j + 8 * c.qt, oh);
             tmem_wait_ld();
-#pragma unroll
-            for (int k = 0; k < 2; ++k) {
-                const uint4 v = quant16(&oh[8 * k], inv);
-                *reinterpret_cast<uint4*>(c.smem_gen + SM_A + (hd >> 2) * 16384 + sw_off(c.row, (hd & 3) * 2 + k)) = v;
-                if (capo) *reinterpret_cast<uint4*>(p.cap_a + c.grow * kD + 32 * hd + 16 * k) = v;
-            }
+            const uint4 v = quant16(oh, inv);
+            *reinterpret_cast<uint4*>(c.smem_gen + SM_A + (j >> 1) * 16384 + sw_off(c.row, 4 * (j & 1) + c.qt)) = v;
+            if (capo) *reinterpret_cast<uint4*>(p.cap_a + c.grow * kD + 64 * j + 16 * c.qt) = v;
         }
         row_publish(c, B_A_READY);
     }
@@ -546,20 +512,17 @@ __device__ __forceinline__ void attention_block(RowCtx& c, const Params& p, cons
 #pragma unroll 1
     for (int u = 0; u < 2; ++u) {
         row_wait_acc(c, u, u == 0 ? PH_O_QUANT : PH_OUT_EPI);
-#pragma unroll 1
-        for (int g = 0; g < 2; ++g) {
-            const int col = 128 * u + 64 * c.hf + 32 * g;
-            uint32_t acc[32], y[16], xo[16];
-            tmem_ld32(c.tm + TM_ACC + col, acc);
-            tmem_ld16(c.tm + TM_X + (col >> 1), xo);
-            tmem_wait_ld();
-            if (cap && p.cap_op == BF_OP_OUT && c.valid) store_acc32(p.cap_acc + c.grow * 256 + col, acc);
-            descale32<false>(acc, sa, __ldg(lp.sw_o + u), lp.b_o + col, y);
-#pragma unroll
-            for (int i = 0; i < 16; ++i) xo[i] = as_u32(__hadd2(as_h2(xo[i]), as_h2(y[i])));
-            tmem_st16(c.tm + TM_X + (col >> 1), xo);
-        }
+        const int col = 128 * u + 32 * c.qt;
+        uint32_t acc[32], y[16], xo[16];
+        tmem_ld32(c.tm + TM_ACC + col, acc);
+        tmem_ld16(c.tm + TM_X + (col >> 1), xo);
+        tmem_wait_ld();
         row_release_acc(c, u);
+        if (cap && p.cap_op == BF_OP_OUT && c.valid) store_words<32>(p.cap_acc + c.grow * 256 + col, acc);
+        descale<32, false>(acc, sa, __ldg(lp.sw_o + u), lp.b_o + col, y);
+#pragma unroll
+        for (int i = 0; i < 16; ++i) xo[i] = as_u32(__hadd2(as_h2(xo[i]), as_h2(y[i])));
+        tmem_st16(c.tm + TM_X + (col >> 1), xo);
     }
     tmem_wait_st();
     prof_mark(c, PH_OUT_EPI);
@@ -576,25 +539,20 @@ __device__ __forceinline__ void ffn_block(RowCtx& c, const Params& p, const Laye
         const int kind2 = (0xD4 >> st) & 1;
         const int ch = kind2 ? ((0x32010000u >> (4 * st)) & 0xF) : ((0x00302010u >> (4 * st)) & 0xF);
         if (!kind2) {
-            uint32_t hid[64];
+            uint32_t hid[32];
 #pragma unroll
             for (int jh = 0; jh < 2; ++jh) {
                 row_wait_acc(c, jh, PH_FF1_EPI);
-#pragma unroll
-                for (int g = 0; g < 2; ++g) {
-                    uint32_t acc[32];
-                    tmem_ld32(c.tm + TM_ACC + 128 * jh + 64 * c.hf + 32 * g, acc);
-                    tmem_wait_ld();
-                    const int col = 256 * ch + 128 * jh + 64 * c.hf + 32 * g;
-                    if (cap && p.cap_op == BF_OP_FF1 && c.valid) store_acc32(p.cap_acc + c.grow * 1024 + col, acc);
-                    descale32<true>(acc, sa, __ldg(lp.sw_ff1 + 2 * ch + jh), lp.b_ff1 + col, &hid[32 * jh + 16 * g]);
-                }
+                uint32_t acc[32];
+                tmem_ld32(c.tm + TM_ACC + 128 * jh + 32 * c.qt, acc);
+                tmem_wait_ld();
                 row_release_acc(c, jh);
+                const int col = 256 * ch + 128 * jh + 32 * c.qt;
+                if (cap && p.cap_op == BF_OP_FF1 && c.valid) store_words<32>(p.cap_acc + c.grow * 1024 + col, acc);
+                descale<32, true>(acc, sa, __ldg(lp.sw_ff1 + 2 * ch + jh), lp.b_ff1 + col, &hid[16 * jh]);
             }
             // per-row u8 scale over the 256-wide chunk (encoder.cu:1510-1517)
-            const float mine = amax16(hid, 64, false);
-            const float4 o = exchange(c, make_float4(mine, 0.f, 0.f, 0.f));
-            const float amax = fmaxf(mine, o.x);
+            const float amax = exchange_max(c, amax_h2<32>(hid, false));
             const float sc = amax > 0.f ? __fdiv_rn(amax, 255.0f) : 1.0f;
             const float inv = __fdiv_rn(1.0f, sc);
             if (ch & 1) sa2_1 = sc; else sa2_0 = sc;
@@ -602,11 +560,11 @@ __device__ __forceinline__ void ffn_block(RowCtx& c, const Params& p, const Laye
 #pragma unroll
             for (int jh = 0; jh < 2; ++jh)
 #pragma unroll
-                for (int k = 0; k < 4; ++k) {
-                    const uint4 v = quant16(&hid[32 * jh + 8 * k], inv);
+                for (int k = 0; k < 2; ++k) {
+                    const uint4 v = quant16(&hid[16 * jh + 8 * k], inv);
                     *reinterpret_cast<uint4*>(c.smem_gen + SM_R + (ch & 1) * 32768 + jh * 16384 +
-                                              sw_off(c.row, 4 * c.hf + k)) = v;
-                    if (caph) *reinterpret_cast<uint4*>(p.cap_a + c.grow * kD + 128 * jh + 64 * c.hf + 16 * k) = v;
+                                              sw_off(c.row, 2 * c.qt + k)) = v;
+                    if (caph) *reinterpret_cast<uint4*>(p.cap_a + c.grow * kD + 128 * jh + 32 * c.qt + 16 * k) = v;
                 }
             row_publish(c, B_A2_READY + (ch & 1));
             prof_mark(c, PH_FF1_EPI);
@@ -616,44 +574,41 @@ __device__ __forceinline__ void ffn_block(RowCtx& c, const Params& p, const Laye
             for (int jh = 0; jh < 2; ++jh) {
                 row_wait_acc(c, jh, PH_FF2_EPI);
                 const float s2 = __ldg(lp.sw_ff2 + jh);
-#pragma unroll 1
-                for (int g = 0; g < 2; ++g) {
-                    uint32_t acc[32], run[16];
-                    const int col = 128 * jh + 64 * c.hf + 32 * g;
-                    tmem_ld32(c.tm + TM_ACC + col, acc);
-                    if (ch > 0) tmem_ld16(c.tm + TM_OY + (col >> 1), run);
-                    tmem_wait_ld();
-                    if (cap && p.cap_op == BF_OP_FF2 + ch && c.valid) store_acc32(p.cap_acc + c.grow * 256 + col, acc);
-                    const uint64_t s1_2 = pk2(s1, s1), s2_2 = pk2(s2, s2);
-#pragma unroll
-                    for (int i = 0; i < 16; ++i) {
-                        uint64_t f = mul2(mul2(pk2(i2f_23(acc[2 * i]), i2f_23(acc[2 * i + 1])), s1_2), s2_2);
-                        if (ch > 0) f = add2_after_mul(f, h2_to_f2(run[i]));
-                        run[i] = f2_to_h2(f);
-                    }
-                    if (ch < 3) {
-                        tmem_st16(c.tm + TM_OY + (col >> 1), run);
-                    } else {
-                        // + b_ff2, residual (encoder.cu:1548-1556): x = fp16(x + fp16(run + b))
-                        uint32_t xo[16];
-                        tmem_ld16(c.tm + TM_X + (col >> 1), xo);
-                        tmem_wait_ld();
-                        const uint4* b4 = reinterpret_cast<const uint4*>(lp.b_ff2 + col);
-#pragma unroll
-                        for (int v = 0; v < 4; ++v) {
-                            const uint4 bv = __ldg(b4 + v);
-                            const uint32_t bw[4] = {bv.x, bv.y, bv.z, bv.w};
-#pragma unroll
-                            for (int k = 0; k < 4; ++k) {
-                                const int i = 4 * v + k;
-                                const __half2 yv = __hadd2(as_h2(run[i]), as_h2(bw[k]));
-                                xo[i] = as_u32(__hadd2(as_h2(xo[i]), yv));
-                            }
-                        }
-                        tmem_st16(c.tm + TM_X + (col >> 1), xo);
-                    }
-                }
+                uint32_t acc[32], run[16];
+                const int col = 128 * jh + 32 * c.qt;
+                tmem_ld32(c.tm + TM_ACC + col, acc);
+                if (ch > 0) tmem_ld16(c.tm + TM_OY + (col >> 1), run);
+                tmem_wait_ld();
                 row_release_acc(c, jh);
+                if (cap && p.cap_op == BF_OP_FF2 + ch && c.valid) store_words<32>(p.cap_acc + c.grow * 256 + col, acc);
+                const uint64_t s1_2 = pk2(s1, s1), s2_2 = pk2(s2, s2);
+#pragma unroll
+                for (int i = 0; i < 16; ++i) {
+                    uint64_t f = mul2(mul2(pk2(i2f_23(acc[2 * i]), i2f_23(acc[2 * i + 1])), s1_2), s2_2);
+                    if (ch > 0) f = add2_after_mul(f, h2_to_f2(run[i]));
+                    run[i] = f2_to_h2(f);
+                }
+                if (ch < 3) {
+                    tmem_st16(c.tm + TM_OY + (col >> 1), run);
+                } else {
+                    // + b_ff2, residual (encoder.cu:1548-1556): x = fp16(x + fp16(run + b))
+                    uint32_t xo[16];
+                    tmem_ld16(c.tm + TM_X + (col >> 1), xo);
+                    tmem_wait_ld();
+                    const uint4* b4 = reinterpret_cast<const uint4*>(lp.b_ff2 + col);
+#pragma unroll
+                    for (int v = 0; v < 4; ++v) {
+                        const uint4 bv = __ldg(b4 + v);
+                        const uint32_t bw[4] = {bv.x, bv.y, bv.z, bv.w};
+#pragma unroll
+                        for (int k = 0; k < 4; ++k) {
+                            const int i = 4 * v + k;
+                            const __half2 yv = __hadd2(as_h2(run[i]), as_h2(bw[k]));
+                            xo[i] = as_u32(__hadd2(as_h2(xo[i]), yv));
+                        }
+                    }
+                    tmem_st16(c.tm + TM_X + (col >> 1), xo);
+                }
             }
             tmem_wait_st();
             prof_mark(c, PH_FF2_EPI);
@@ -680,16 +635,16 @@ __device__ __forceinline__ void row_warps_tile(RowCtx& c, const Params& p, int t
         const int ts = min(static_cast<int>(((word >> 6) & 7) * 2 + ((word >> 9) & 1)), kNTypeSpecial - 1);
         const int ct = ((word >> 10) & 1) * 2 + stm;
 #pragma unroll 1
-        for (int g = 0; g < 2; ++g) {
-            const int col = 128 * g + 64 * c.hf;
+        for (int u = 0; u < 2; ++u) {
+            const int col = 128 * u + 32 * c.qt;
             const uint4* e_sq = reinterpret_cast<const uint4*>(p.emb + (EMB_SQUARE + sq) * kD + col);
             const uint4* e_ts = reinterpret_cast<const uint4*>(p.emb + (EMB_TS + ts) * kD + col);
             const uint4* e_ct = reinterpret_cast<const uint4*>(p.emb + (EMB_CT + ct) * kD + col);
             const uint4* e_ck = reinterpret_cast<const uint4*>(p.emb + (EMB_CLOCK + clk) * kD + col);
             const uint4* e_rp = reinterpret_cast<const uint4*>(p.emb + (EMB_REP + rp) * kD + col);
-            uint32_t e32[32];
+            uint32_t e16[16];
 #pragma unroll
-            for (int k = 0; k < 8; ++k) {
+            for (int k = 0; k < 4; ++k) {
                 const uint4 a = __ldg(e_sq + k), b = __ldg(e_ts + k), d = __ldg(e_ct + k);
                 const uint4 e = __ldg(e_ck + k), f = __ldg(e_rp + k);
                 const uint32_t aw[4] = {a.x, a.y, a.z, a.w}, bw[4] = {b.x, b.y, b.z, b.w};
@@ -700,10 +655,10 @@ __device__ __forceinline__ void row_warps_tile(RowCtx& c, const Params& p, int t
                     __half2 x = __hadd2(as_h2(aw[j]), as_h2(bw[j]));
                     x = __hadd2(x, as_h2(dw[j]));
                     x = __hadd2(x, __hadd2(as_h2(ew[j]), as_h2(fw[j])));
-                    e32[4 * k + j] = as_u32(x);
+                    e16[4 * k + j] = as_u32(x);
                 }
             }
-            tmem_st32(c.tm + TM_X + 64 * g + 32 * c.hf, e32);
+            tmem_st16(c.tm + TM_X + 64 * u + 16 * c.qt, e16);
         }
         tmem_wait_st();
     }
@@ -745,28 +700,24 @@ __device__ __forceinline__ void row_warps_tile(RowCtx& c, const Params& p, int t
     //      (encoder.cu:894-1079; the reference accumulates in fp16) -------------------------
     row_wait_acc(c, 0, PH_LN);
     {
-        uint32_t acc[32];
-        tmem_ld32(c.tm + TM_ACC + 32 * c.hf, acc);
-        uint32_t aux[16];
-        if (c.hf == 0) tmem_ld16(c.tm + TM_ACC + 64, aux);
+        uint32_t acc[16], aux[16];
+        tmem_ld16(c.tm + TM_ACC + 16 * c.qt, acc);
+        if (c.qt == 0) tmem_ld16(c.tm + TM_ACC + 64, aux);
         tmem_wait_ld();
         row_release_acc(c, 0);
-        uint32_t lg[16];
+        uint32_t lg[8];
         unsigned long long lw = ~0ull;
         if (p.legal != nullptr && c.valid) lw = p.legal[c.grow];
-        const uint32_t bits = static_cast<uint32_t>(lw >> (32 * c.hf));
+        const uint32_t bits = static_cast<uint32_t>(lw >> (16 * c.qt)) & 0xffffu;
 #pragma unroll
-        for (int i = 0; i < 16; ++i) {
+        for (int i = 0; i < 8; ++i) {
             uint32_t v = pack_h2(__uint_as_float(acc[2 * i]), __uint_as_float(acc[2 * i + 1]));
             if (!((bits >> (2 * i)) & 1u)) v = (v & 0xffff0000u) | 0xfc00u;
             if (!((bits >> (2 * i + 1)) & 1u)) v = (v & 0x0000ffffu) | 0xfc000000u;
             lg[i] = v;
         }
-        if (c.valid && p.policy != nullptr) {
-            store_h16(p.policy + c.grow * 64 + 32 * c.hf, lg);
-            store_h16(p.policy + c.grow * 64 + 32 * c.hf + 16, lg + 8);
-        }
-        if (c.hf == 0) {
+        if (c.valid && p.policy != nullptr) store_words<8>(p.policy + c.grow * 64 + 16 * c.qt, lg);
+        if (c.qt == 0) {
             if (c.valid && p.promo != nullptr)
                 *reinterpret_cast<uint2*>(p.promo + c.grow * 4) =
                     make_uint2(pack_h2(__uint_as_float(aux[0]), __uint_as_float(aux[1])),
@@ -972,7 +923,7 @@ __global__ void __launch_bounds__(kThreads, 1) encoder_kernel(const Params p) {
     const int n_tiles = (p.n + 3) / 4;
     if (warp < kRowWarps) {
         RowCtx c;
-        c.lane = lane; c.q = warp & 3; c.hf = warp >> 2; c.row = 32 * c.q + lane;
+        c.lane = lane; c.q = warp & 3; c.qt = warp >> 2; c.row = 32 * c.q + lane;
         c.smem = smem; c.smem_gen = sm;
         c.tm = tmem + (static_cast<uint32_t>(32 * c.q) << 16);
         c.abort_flag = abort_flag; c.xpar = 0; c.full0 = c.full1 = 0;

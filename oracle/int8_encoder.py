@@ -44,11 +44,11 @@ N_POLICY, N_PROMO = 64, 4
 EPS = np.float32(1e-5)
 F32, F16 = np.float32, np.float16
 
-#: Column ownership of the two halves of a row in the statistics' summation order:
-#: half 0 sums columns 0-63 then 128-191, half 1 sums 64-127 then 192-255; within a
-#: half even and odd columns accumulate separately, sequentially, then even + odd, then
-#: half 0 + half 1.
-_HALF_COLS = [np.r_[0:64, 128:192], np.r_[64:128, 192:256]]
+#: Column ownership of the four quarters of a row in the statistics' summation order:
+#: quarter q sums columns 32q..32q+31 then 128+32q..128+32q+31; within a quarter even and
+#: odd columns accumulate separately, sequentially, then even + odd; the quarters combine
+#: as (q0 + q1) + (q2 + q3).
+_QUARTER_COLS = [np.r_[32 * q:32 * q + 32, 128 + 32 * q:128 + 32 * q + 32] for q in range(4)]
 
 
 def f16(x) -> np.ndarray:
@@ -161,14 +161,14 @@ def _seq_sum(a: np.ndarray) -> np.ndarray:
 def ln_stats(x16: np.ndarray):
     """Row mean and 1/std of fp16 rows ``[M, 256]`` in the fixed summation order."""
     x = x16.astype(F32)
-    s_half, q_half = [], []
-    for cols in _HALF_COLS:
+    s_part, q_part = [], []
+    for cols in _QUARTER_COLS:
         v = x[:, cols]
         sq = v * v                                 # exact: fp16 squares fit fp32
-        s_half.append((_seq_sum(v[:, 0::2]) + _seq_sum(v[:, 1::2])).astype(F32))
-        q_half.append((_seq_sum(sq[:, 0::2]) + _seq_sum(sq[:, 1::2])).astype(F32))
-    tot = (s_half[0] + s_half[1]).astype(F32)
-    totq = (q_half[0] + q_half[1]).astype(F32)
+        s_part.append((_seq_sum(v[:, 0::2]) + _seq_sum(v[:, 1::2])).astype(F32))
+        q_part.append((_seq_sum(sq[:, 0::2]) + _seq_sum(sq[:, 1::2])).astype(F32))
+    tot = ((s_part[0] + s_part[1]).astype(F32) + (s_part[2] + s_part[3]).astype(F32)).astype(F32)
+    totq = ((q_part[0] + q_part[1]).astype(F32) + (q_part[2] + q_part[3]).astype(F32)).astype(F32)
     mean = (tot * F32(1.0 / 256)).astype(F32)
     t = (totq * F32(1.0 / 256)).astype(F32)
     var = (t.astype(np.float64) - mean.astype(np.float64) ** 2).astype(F32)   # one fma
