@@ -15,7 +15,8 @@ from typing import List, Optional
 
 PKG_DIR = os.path.dirname(os.path.abspath(__file__))
 ROOT = os.path.dirname(PKG_DIR)
-LIB_PATH = os.path.join(PKG_DIR, "libbrokefish_b200.so")
+#: The in-tree library; ``BROKEFISH_B200_LIB`` points the loader at another build of it.
+LIB_PATH = os.environ.get("BROKEFISH_B200_LIB") or os.path.join(PKG_DIR, "libbrokefish_b200.so")
 SOURCES = [os.path.join(PKG_DIR, "csrc", "bf_encoder.cu")]
 DEPS = SOURCES + [os.path.join(PKG_DIR, "csrc", "bf_ptx.cuh"),
                   os.path.join(ROOT, "include", "brokefish_b200.h")]
