@@ -27,7 +27,7 @@ NVCC_FLAGS = ["-gencode", "arch=compute_100a,code=sm_100a", "-O3", "-lineinfo", 
 EXPORTS = ["bf_version", "bf_last_error", "bf_create", "bf_destroy", "bf_info", "bf_forward",
            "bf_forward_stage", "bf_forward_stage_at", "bf_forward_capture", "bf_forward_host", "bf_status",
            "bf_launch_count", "bf_profile", "bf_profile_read", "bf_profile_phases",
-           "bf_selftest_umma"]
+           "bf_forward_noalloc", "bf_noalloc_status", "bf_selftest_umma"]
 
 
 def nvcc_path() -> str:
@@ -89,6 +89,8 @@ def lib() -> ctypes.CDLL:
     L.bf_profile.argtypes = [vp, i32]
     L.bf_profile_read.argtypes = [vp, ctypes.POINTER(ctypes.c_longlong), i32]
     L.bf_profile_phases.restype = ctypes.c_char_p
+    L.bf_forward_noalloc.argtypes = [i32, vp, sz, vp, vp, vp, vp, i32, vp, vp, vp, vp]
+    L.bf_noalloc_status.argtypes = [i32, ctypes.POINTER(i32)]
     L.bf_selftest_umma.argtypes = [i32, i32, vp, vp, vp]
     for name in EXPORTS:
         fn = getattr(L, name)

@@ -1287,3 +1287,132 @@ int bf_selftest_umma(int device, int mode, const void* a, const void* w_image, v
 
 }  // extern "C"
 
+// ==========================================================================================
+// An entry point that allocates nothing.
+//
+// Who this is for: code that may enqueue work on a GPU but must not grow its memory
+// footprint while doing so -- a search worker running inside a process whose device memory
+// was carved up in advance by somebody else, a plugin loaded into a host that forbids device
+// allocation after start-up, a caller that runs with the allocator locked down for
+// determinism.  Such a caller cannot create a `bf_handle` (bf_create calls cudaMalloc for the
+// weight copy and the status word).  Here the caller keeps the packed weight blob in device
+// memory it already owns and passes it on every call together with its inputs and outputs;
+// the only memory the kernel needs beyond those -- its status word -- lives in a fixed
+// 256-byte array that is part of the library image on every GPU that loads it.
+// ==========================================================================================
+namespace bf {
+constexpr int kNoAllocScratchBytes = 256;
+static __device__ __align__(256) unsigned char g_noalloc_scratch[kNoAllocScratchBytes];
+}  // namespace bf
+
+namespace {
+constexpr int kNoAllocMaxDevices = 64;
+struct NoAllocDevice {
+    bool ready = false;
+    void* scratch = nullptr;      // device address of bf::g_noalloc_scratch on this device
+    int sm_count = 0;
+    const void* blob = nullptr;   // blob whose header is cached below
+    size_t blob_bytes = 0;
+    BlobHeader hdr{};
+};
+NoAllocDevice g_noalloc[kNoAllocMaxDevices];
+
+// Once per device, with that device current: resolve the scratch array's device address (in
+// host code the array's name is only a handle, never an address a kernel may use), raise the
+// kernel's shared-memory limit, read the SM count, zero the scratch.
+int noalloc_setup(int device, NoAllocDevice** out) {
+    if (device < 0 || device >= kNoAllocMaxDevices) return fail(BF_EINVAL, "device index out of range");
+    NoAllocDevice& d = g_noalloc[device];
+    BF_CUDA(cudaSetDevice(device));
+    if (!d.ready) {
+        cudaDeviceProp prop;
+        BF_CUDA(cudaGetDeviceProperties(&prop, device));
+        if (prop.major != 10)
+            return fail(BF_ENOTSUP, "this library needs a compute capability 10.x (sm_100a) device");
+        void* ptr = nullptr;
+        BF_CUDA(cudaGetSymbolAddress(&ptr, bf::g_noalloc_scratch));
+        BF_CUDA(cudaMemset(ptr, 0, bf::kNoAllocScratchBytes));
+        BF_CUDA(cudaFuncSetAttribute(bf::encoder_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                     bf::kSmemRequest));
+        d.scratch = ptr;
+        d.sm_count = prop.multiProcessorCount;
+        d.ready = true;
+    }
+    *out = &d;
+    return BF_OK;
+}
+}  // namespace
+
+extern "C" {
+
+int bf_forward_noalloc(int device, const void* blob_dev, size_t blob_bytes, const uint16_t* boards,
+                       const int16_t* control, const uint8_t* rep, const uint64_t* legal, int n,
+                       void* policy, void* promo, float* value, void* stream) {
+    if (n < 0) return fail(BF_EINVAL, "n must be >= 0");
+    if (n > BF_NOALLOC_MAX_POSITIONS)
+        return fail(BF_EINVAL, "bf_forward_noalloc: n exceeds BF_NOALLOC_MAX_POSITIONS (" +
+                                   std::to_string(BF_NOALLOC_MAX_POSITIONS) + "); split the batch");
+    if (blob_dev == nullptr || blob_bytes < 256) return fail(BF_EINVAL, "blob is null or too small");
+    if (n > 0 && (boards == nullptr || control == nullptr || rep == nullptr))
+        return fail(BF_EINVAL, "boards, control and rep must be non-null");
+    NoAllocDevice* d = nullptr;
+    int rc = noalloc_setup(device, &d);
+    if (rc != BF_OK) return rc;
+    if (d->blob != blob_dev || d->blob_bytes != blob_bytes) {
+        // a blob this device has not seen: read and check its header once
+        BlobHeader hdr;
+        BF_CUDA(cudaMemcpy(&hdr, blob_dev, sizeof(hdr), cudaMemcpyDeviceToHost));
+        if (hdr.magic != BF_BLOB_MAGIC || hdr.version != BF_BLOB_VERSION || hdr.total != blob_bytes)
+            return fail(BF_EINVAL, "blob header does not match (magic, version or size)");
+        if (hdr.n_layers < 1 || hdr.n_layers > 64 ||
+            hdr.bytes_w != static_cast<uint64_t>(hdr.n_layers) * bf::kLayerStreamBytes + 4 * bf::kHeadStage ||
+            hdr.bytes_lp != static_cast<uint64_t>(hdr.n_layers) * bf::kLparamStride ||
+            hdr.bytes_emb != 184u * 256u * 2u || hdr.bytes_tail != 1024u ||
+            ((hdr.off_w | hdr.off_lp | hdr.off_emb | hdr.off_tail) & 255u) ||
+            hdr.off_w + hdr.bytes_w > blob_bytes || hdr.off_lp + hdr.bytes_lp > blob_bytes ||
+            hdr.off_emb + hdr.bytes_emb > blob_bytes || hdr.off_tail + hdr.bytes_tail > blob_bytes)
+            return fail(BF_EINVAL, "blob sections do not match this build");
+        if ((hdr.n_value != 1 && hdr.n_value != 3) || hdr.vmode > 1)
+            return fail(BF_ENOTSUP, "value head variant not built");
+        if (reinterpret_cast<uintptr_t>(blob_dev) & 255u)
+            return fail(BF_EINVAL, "the device blob must be 256-byte aligned");
+        d->hdr = hdr; d->blob = blob_dev; d->blob_bytes = blob_bytes;
+    }
+    if (n == 0) return BF_OK;
+    const uint8_t* base = static_cast<const uint8_t*>(blob_dev);
+    bf::Params p{};
+    p.boards = boards; p.control = control; p.rep = rep; p.legal = legal;
+    p.n = n; p.n_layers = static_cast<int>(d->hdr.n_layers);
+    p.n_value = static_cast<int>(d->hdr.n_value); p.vmode = static_cast<int>(d->hdr.vmode);
+    p.eps = d->hdr.eps;
+    p.wstream = base + d->hdr.off_w;
+    p.lparams = base + d->hdr.off_lp;
+    p.emb = reinterpret_cast<const __half*>(base + d->hdr.off_emb);
+    p.tail = reinterpret_cast<const __half*>(base + d->hdr.off_tail);
+    p.policy = static_cast<__half*>(policy); p.promo = static_cast<__half*>(promo); p.value = value;
+    p.y = nullptr; p.debug_stage = 0; p.debug_layer = 0;
+    p.cap_layer = -1; p.cap_op = -1; p.cap_a = nullptr; p.cap_acc = nullptr;
+    p.status = static_cast<int*>(d->scratch);      // the device address, not the symbol
+    p.prof = nullptr;
+    const int n_tiles = (n + 3) / 4;
+    const int grid = n_tiles < d->sm_count ? n_tiles : d->sm_count;
+    bf::encoder_kernel<<<grid, bf::kThreads, bf::kSmemRequest, static_cast<cudaStream_t>(stream)>>>(p);
+    BF_CUDA(cudaGetLastError());
+    return BF_OK;
+}
+
+int bf_noalloc_status(int device, int* status) {
+    if (status == nullptr) return fail(BF_EINVAL, "status is null");
+    NoAllocDevice* d = nullptr;
+    int rc = noalloc_setup(device, &d);
+    if (rc != BF_OK) return rc;
+    BF_CUDA(cudaDeviceSynchronize());
+    BF_CUDA(cudaMemcpy(status, d->scratch, sizeof(int), cudaMemcpyDeviceToHost));
+    if (*status != 0) {
+        BF_CUDA(cudaMemset(d->scratch, 0, sizeof(int)));
+        return fail(BF_EDEVICE, "a device-side bounded wait ran out (code " + std::to_string(*status) + ")");
+    }
+    return BF_OK;
+}
+
+}  // extern "C"

@@ -118,6 +118,37 @@ int bf_profile(bf_handle* h, int enable);
 int bf_profile_read(bf_handle* h, long long* cycles, int n);
 const char* bf_profile_phases(void);
 
+/* Evaluate without allocating anything.  No counterpart in the reference, which allocates
+ * its slabs with torch: this exists for callers that must not (or cannot) allocate device
+ * memory -- a worker inside a process whose GPU memory was partitioned up front, a plugin
+ * host that forbids allocation after start-up -- and therefore cannot hold a `bf_handle`.
+ *
+ * The caller owns everything it passes: `blob_dev` is the packed weight blob already in
+ * DEVICE memory (256-byte aligned, `blob_bytes` long), the rest is as for `bf_forward`.  The
+ * kernel's only other memory, its status word, is a 256-byte `static __device__` array
+ * inside the library: every GPU that loads the library holds those 256 bytes until the
+ * process exits, and nothing is ever cudaMalloc'ed or freed here.
+ *
+ * Limits and rules
+ *   - `n` above BF_NOALLOC_MAX_POSITIONS is refused (BF_EINVAL, text says so): split it.
+ *   - The first call on a device resolves the array's device address, sets the kernel's
+ *     shared-memory attribute and zeroes the status word; a call with a blob pointer the
+ *     device has not seen reads and checks its 256-byte header (a synchronous copy).  Make
+ *     that first call before any stream capture.
+ *   - All calls on a device share the one status word and it keeps what the last failing
+ *     launch wrote until `bf_noalloc_status` reads it (which clears it).  Two launches that
+ *     overlap on the GPU race on it: a time-out is still reported, but not whose it was.
+ *   - Not thread-safe per device for the first call; afterwards concurrent callers only
+ *     share the status word as described. */
+#define BF_NOALLOC_MAX_POSITIONS 1048576
+int bf_forward_noalloc(int device, const void* blob_dev, size_t blob_bytes, const uint16_t* boards,
+                       const int16_t* control, const uint8_t* rep, const uint64_t* legal, int n,
+                       void* policy, void* promo, float* value, void* stream);
+
+/* Synchronise `device` and read (and clear) the status word `bf_forward_noalloc` launches
+ * share; 0 = clean.  No counterpart in the reference. */
+int bf_noalloc_status(int device, int* status);
+
 /* Tensor-core self test (no network): one 128-row tile times a packed weight tile.
  *   mode 0: s8 x s8, N=128, K=256     mode 1: u8 x s8, N=128, K=256
  *   mode 2: s8 x s8, N=192, K=256     mode 3: f16 x f16 -> f32, N=96, K=256
