@@ -112,9 +112,10 @@ struct RowCtx {
 // csrc/encoder.cu:1110-1177): one thread per CTA charges the cycles since its previous mark to
 // a phase.  Off (one predictable branch per mark) unless the launch carries a counter buffer.
 enum { PH_EMBED = 0, PH_LN, PH_WAIT_MMA, PH_QKV_EPI, PH_PAIR_BAR, PH_ATTENTION, PH_O_READBACK, PH_O_QUANT,
-       PH_OUT_EPI, PH_FF1_EPI, PH_FF2_EPI, PH_HEAD, PH_COUNT };
+       PH_OUT_EPI, PH_FF1_EPI, PH_FF2_EPI, PH_HEAD, PH_WAIT_OUT, PH_WAIT_FF1, PH_WAIT_FF2, PH_COUNT };
+template <bool kDbg>
 __device__ __forceinline__ void prof_mark(RowCtx& c, int phase) {
-    if (c.prof_on) {
+    if (kDbg && c.prof_on) {
         const long long t = clock64();
         long long* a = reinterpret_cast<long long*>(c.smem_gen + SM_PROF);
         a[phase] += t - c.t_last;
@@ -131,11 +132,11 @@ __device__ __forceinline__ void board_sync(const RowCtx& c) { named_bar_sync(1 +
 
 // Exchange one float4 among the four threads that share a row; `all[k]` is quarter k's.
 __device__ __forceinline__ void exchange4(RowCtx& c, float4 mine, float4 (&all)[4]) {
-    float4* xch = reinterpret_cast<float4*>(c.smem_gen + SM_XCH);
-    xch[(c.xpar * 4 + c.qt) * kRows + c.row] = mine;
+    const uint32_t xch = c.smem + SM_XCH + 16u * (c.xpar * 4 * kRows + c.row);
+    sts_f4(xch + 16u * kRows * c.qt, mine);
     board_sync(c);
 #pragma unroll
-    for (int k = 0; k < 4; ++k) all[k] = xch[(c.xpar * 4 + k) * kRows + c.row];
+    for (int k = 0; k < 4; ++k) all[k] = lds_f4(xch + 16u * kRows * k);
     c.xpar ^= 1;
 }
 __device__ __forceinline__ float exchange_max(RowCtx& c, float mine) {
@@ -144,13 +145,14 @@ __device__ __forceinline__ float exchange_max(RowCtx& c, float mine) {
     return fmaxf(fmaxf(all[0].x, all[1].x), fmaxf(all[2].x, all[3].x));
 }
 
-__device__ __forceinline__ void row_wait_acc(RowCtx& c, int slot, int phase_before) {
-    prof_mark(c, phase_before);
+template <bool kDbg>
+__device__ __forceinline__ void row_wait_acc(RowCtx& c, int slot, int phase_before, int phase_wait = PH_WAIT_MMA) {
+    prof_mark<kDbg>(c, phase_before);
     const uint32_t n = slot ? c.full1 : c.full0;
     mbar_wait(bar_addr(c.smem, B_ACC_FULL + slot), n & 1, c.abort_flag, kErrRowAcc);
     if (slot) c.full1 = n + 1; else c.full0 = n + 1;
     tc_fence_after();
-    prof_mark(c, PH_WAIT_MMA);
+    prof_mark<kDbg>(c, phase_wait);
 }
 // All of this warp's TMEM loads of the slot are done: hand it back to the MMA issuer.
 __device__ __forceinline__ void row_release_acc(RowCtx& c, int slot) {
@@ -250,6 +252,7 @@ __device__ __forceinline__ void store_words(void* dst, const uint32_t* w) {
 // x -> x_hat is monotone (every rounding in it is), so amax(x_hat) is reached at the row's
 // largest or smallest x and needs no second pass: the row minimum and maximum travel in the
 // same exchange as the sums.
+template <bool kDbg>
 __device__ __forceinline__ float ln_stage(RowCtx& c, const Params& p, bool final_norm, bool dump_x,
                                           bool dump_xn, bool capture) {
     uint64_t sum2 = pk2(0.f, 0.f), sq2 = pk2(0.f, 0.f);      // (even, odd) column lanes
@@ -259,7 +262,7 @@ __device__ __forceinline__ float ln_stage(RowCtx& c, const Params& p, bool final
         uint32_t x[16];
         tmem_ld16(c.tm + TM_X + 64 * u + 16 * c.qt, x);
         tmem_wait_ld();
-        if (dump_x && c.valid) store_words<16>(p.y + c.grow * kD + 128 * u + 32 * c.qt, x);
+        if (kDbg && dump_x && c.valid) store_words<16>(p.y + c.grow * kD + 128 * u + 32 * c.qt, x);
 #pragma unroll
         for (int i = 0; i < 16; ++i) {
             const __half2 h = as_h2(x[i]);
@@ -302,8 +305,8 @@ __device__ __forceinline__ float ln_stage(RowCtx& c, const Params& p, bool final
 #pragma unroll
             for (int v = 0; v < 2; ++v) {
                 const uint4 qv = quant16(&x[8 * v], inv);
-                *reinterpret_cast<uint4*>(c.smem_gen + SM_A + u * 16384 + sw_off(c.row, 2 * c.qt + v)) = qv;
-                if (capture && c.valid) *reinterpret_cast<uint4*>(p.cap_a + c.grow * kD + col + 16 * v) = qv;
+                sts128(c.smem + SM_A + u * 16384 + sw_off(c.row, 2 * c.qt + v), qv);
+                if (kDbg && capture && c.valid) *reinterpret_cast<uint4*>(p.cap_a + c.grow * kD + col + 16 * v) = qv;
             }
         } else {
             // norm_f with affine: fp16(fma(x_hat, gamma, beta)) (encoder.cu:609-611), written as
@@ -319,12 +322,11 @@ __device__ __forceinline__ float ln_stage(RowCtx& c, const Params& p, bool final
                     x[4 * v + j] = f2_to_h2(fma2(mul2(add2(h2_to_f2(x[4 * v + j]), nmean2), rstd2),
                                                  h2_to_f2(gw[j]), h2_to_f2(bw[j])));
                 // head A slab = col / 64 = 2u + qt/2; 16-byte group within the 64-column slab
-                *reinterpret_cast<uint4*>(c.smem_gen + SM_R + (2 * u + (c.qt >> 1)) * 16384 +
-                                          sw_off(c.row, 4 * (c.qt & 1) + v)) =
-                    make_uint4(x[4 * v], x[4 * v + 1], x[4 * v + 2], x[4 * v + 3]);
+                sts128(c.smem + SM_R + (2 * u + (c.qt >> 1)) * 16384 + sw_off(c.row, 4 * (c.qt & 1) + v),
+                       make_uint4(x[4 * v], x[4 * v + 1], x[4 * v + 2], x[4 * v + 3]));
             }
         }
-        if (dump_xn && c.valid) store_words<16>(p.y + c.grow * kD + col, x);
+        if (kDbg && dump_xn && c.valid) store_words<16>(p.y + c.grow * kD + col, x);
     }
     return sc;
 }
@@ -414,10 +416,8 @@ __device__ __forceinline__ void attention_unit(const RowCtx& c, uint32_t alive) 
 #pragma unroll
     for (int nt = 0; nt < 4; ++nt) {
         const int row = rq + g;
-        *reinterpret_cast<uint32_t*>(c.smem_gen + SM_R + sw_off(row, 4 * hh + nt) + 4 * t) =
-            pack_h2(o[nt][0], o[nt][1]);
-        *reinterpret_cast<uint32_t*>(c.smem_gen + SM_R + sw_off(row + 8, 4 * hh + nt) + 4 * t) =
-            pack_h2(o[nt][2], o[nt][3]);
+        sts32(qs + sw_off(row, 4 * hh + nt) + 4 * t, pack_h2(o[nt][0], o[nt][1]));
+        sts32(qs + sw_off(row + 8, 4 * hh + nt) + 4 * t, pack_h2(o[nt][2], o[nt][3]));
     }
 }
 
@@ -433,13 +433,14 @@ struct LayerParams {
 // QKV in four head-pair chunks with attention per chunk, then the attention output is
 // quantised into A, then out-projection + residual into the residual stream (TMEM).
 // `sa` is the scale of the row in A on entry.
+template <bool kDbg>
 __device__ __forceinline__ void attention_block(RowCtx& c, const Params& p, const LayerParams& lp,
                                                 float sa, uint32_t alive, bool cap, bool dbgl) {
     const int dbg = p.debug_stage;
     float o_amax = 0.f;
 #pragma unroll 1
     for (int j = 0; j < 4; ++j) {
-        row_wait_acc(c, 0, j == 0 ? PH_LN : PH_PAIR_BAR);
+        row_wait_acc<kDbg>(c, 0, j == 0 ? PH_LN : PH_PAIR_BAR);
         // this thread's 48 of the chunk's 192 columns, 16 at a time
 #pragma unroll 1
         for (int g = 0; g < 3; ++g) {
@@ -447,52 +448,52 @@ __device__ __forceinline__ void attention_block(RowCtx& c, const Params& p, cons
             uint32_t acc[16], h[8];
             tmem_ld16(c.tm + TM_ACC + c0, acc);
             tmem_wait_ld();
-            if (cap && p.cap_op == BF_OP_QKV && c.valid) store_words<16>(p.cap_acc + c.grow * 768 + j * 192 + c0, acc);
+            if (kDbg && cap && p.cap_op == BF_OP_QKV && c.valid) store_words<16>(p.cap_acc + c.grow * 768 + j * 192 + c0, acc);
             descale<16, false>(acc, sa, __ldg(lp.sw_qkv + m * 2 + (j >> 1)), lp.b_qkv + j * 192 + c0, h);
 #pragma unroll
             for (int k = 0; k < 2; ++k)
-                *reinterpret_cast<uint4*>(c.smem_gen + SM_R + m * 16384 + sw_off(c.row, (cm >> 3) + k)) =
-                    make_uint4(h[4 * k], h[4 * k + 1], h[4 * k + 2], h[4 * k + 3]);
-            if (dbgl && dbg == 5 + m && c.valid) store_words<8>(p.y + c.grow * kD + 64 * j + cm, h);
+                sts128(c.smem + SM_R + m * 16384 + sw_off(c.row, (cm >> 3) + k),
+                       make_uint4(h[4 * k], h[4 * k + 1], h[4 * k + 2], h[4 * k + 3]));
+            if (kDbg && dbgl && dbg == 5 + m && c.valid) store_words<8>(p.y + c.grow * kD + 64 * j + cm, h);
         }
         row_release_acc(c, 0);
-        prof_mark(c, PH_QKV_EPI);
+        prof_mark<kDbg>(c, PH_QKV_EPI);
         board_sync(c);                     // this board's Q/K/V rows are staged
-        prof_mark(c, PH_PAIR_BAR);
+        prof_mark<kDbg>(c, PH_PAIR_BAR);
         attention_unit(c, alive);
-        prof_mark(c, PH_ATTENTION);
+        prof_mark<kDbg>(c, PH_ATTENTION);
         board_sync(c);                     // all four warps' outputs are in the Q block
         {
             // read back 16 of this row's 64 outputs of the head pair, park them in tensor memory
             uint32_t oh[8];
 #pragma unroll
             for (int k = 0; k < 2; ++k) {
-                const uint4 v = *reinterpret_cast<const uint4*>(c.smem_gen + SM_R + sw_off(c.row, 2 * c.qt + k));
+                const uint4 v = lds128(c.smem + SM_R + sw_off(c.row, 2 * c.qt + k));
                 oh[4 * k] = v.x; oh[4 * k + 1] = v.y; oh[4 * k + 2] = v.z; oh[4 * k + 3] = v.w;
             }
             o_amax = fmaxf(o_amax, amax_h2<8>(oh, true));
             tmem_st8(c.tm + TM_OY + 32 * j + 8 * c.qt, oh);
-            if (dbgl && dbg == 4 && c.valid) store_words<8>(p.y + c.grow * kD + 64 * j + 16 * c.qt, oh);
+            if (kDbg && dbgl && dbg == 4 && c.valid) store_words<8>(p.y + c.grow * kD + 64 * j + 16 * c.qt, oh);
         }
-        prof_mark(c, PH_O_READBACK);
+        prof_mark<kDbg>(c, PH_O_READBACK);
         board_sync(c);                     // staging may be overwritten by the next chunk
     }
     tmem_wait_st();
-    prof_mark(c, PH_PAIR_BAR);
+    prof_mark<kDbg>(c, PH_PAIR_BAR);
 
     // quantise the attention output into A (s8, per-row scale)
     {
         const float amax = exchange_max(c, o_amax);
         sa = amax > 0.f ? __fdiv_rn(amax, 127.0f) : 1.0f;
         const float inv = __fdiv_rn(1.0f, sa);
-        const bool capo = cap && p.cap_op == BF_OP_OUT && c.valid;
+        const bool capo = kDbg && cap && p.cap_op == BF_OP_OUT && c.valid;
 #pragma unroll 1
         for (int j = 0; j < 4; ++j) {
             uint32_t oh[8];
             tmem_ld8(c.tm + TM_OY + 32 * j + 8 * c.qt, oh);
             tmem_wait_ld();
             const uint4 v = quant16(oh, inv);
-            *reinterpret_cast<uint4*>(c.smem_gen + SM_A + (j >> 1) * 16384 + sw_off(c.row, 4 * (j & 1) + c.qt)) = v;
+            sts128(c.smem + SM_A + (j >> 1) * 16384 + sw_off(c.row, 4 * (j & 1) + c.qt), v);
             if (capo) *reinterpret_cast<uint4*>(p.cap_a + c.grow * kD + 64 * j + 16 * c.qt) = v;
         }
         row_publish(c, B_A_READY);
@@ -501,29 +502,30 @@ __device__ __forceinline__ void attention_block(RowCtx& c, const Params& p, cons
     // out-projection: x = fp16(x + fp16(fp16(descale) + b_o)) (encoder.cu:631-686)
 #pragma unroll 1
     for (int u = 0; u < 2; ++u) {
-        row_wait_acc(c, u, u == 0 ? PH_O_QUANT : PH_OUT_EPI);
+        row_wait_acc<kDbg>(c, u, u == 0 ? PH_O_QUANT : PH_OUT_EPI, PH_WAIT_OUT);
         const int col = 128 * u + 32 * c.qt;
         uint32_t acc[32], y[16], xo[16];
         tmem_ld32(c.tm + TM_ACC + col, acc);
         tmem_ld16(c.tm + TM_X + (col >> 1), xo);
         tmem_wait_ld();
         row_release_acc(c, u);
-        if (cap && p.cap_op == BF_OP_OUT && c.valid) store_words<32>(p.cap_acc + c.grow * 256 + col, acc);
+        if (kDbg && cap && p.cap_op == BF_OP_OUT && c.valid) store_words<32>(p.cap_acc + c.grow * 256 + col, acc);
         descale<32, false>(acc, sa, __ldg(lp.sw_o + u), lp.b_o + col, y);
 #pragma unroll
         for (int i = 0; i < 16; ++i) xo[i] = as_u32(__hadd2(as_h2(xo[i]), as_h2(y[i])));
         tmem_st16(c.tm + TM_X + (col >> 1), xo);
     }
     tmem_wait_st();
-    prof_mark(c, PH_OUT_EPI);
+    prof_mark<kDbg>(c, PH_OUT_EPI);
 }
 
 // FFN: four hidden chunks of 256; ff1 -> ReLU -> per-row u8 -> ff2 with an fp16 running
 // total (encoder.cu:1431-1556).  The eight steps follow the MMA issue order.
+template <bool kDbg>
 __device__ __forceinline__ void ffn_block(RowCtx& c, const Params& p, const LayerParams& lp,
                                           float sa, bool cap) {
     float sa2_0 = 1.f, sa2_1 = 1.f;
-    prof_mark(c, PH_LN);
+    prof_mark<kDbg>(c, PH_LN);
 #pragma unroll 1
     for (int st = 0; st < 8; ++st) {
         const int kind2 = (0xD4 >> st) & 1;
@@ -532,13 +534,13 @@ __device__ __forceinline__ void ffn_block(RowCtx& c, const Params& p, const Laye
             uint32_t hid[32];
 #pragma unroll
             for (int jh = 0; jh < 2; ++jh) {
-                row_wait_acc(c, jh, PH_FF1_EPI);
+                row_wait_acc<kDbg>(c, jh, PH_FF1_EPI, PH_WAIT_FF1);
                 uint32_t acc[32];
                 tmem_ld32(c.tm + TM_ACC + 128 * jh + 32 * c.qt, acc);
                 tmem_wait_ld();
                 row_release_acc(c, jh);
                 const int col = 256 * ch + 128 * jh + 32 * c.qt;
-                if (cap && p.cap_op == BF_OP_FF1 && c.valid) store_words<32>(p.cap_acc + c.grow * 1024 + col, acc);
+                if (kDbg && cap && p.cap_op == BF_OP_FF1 && c.valid) store_words<32>(p.cap_acc + c.grow * 1024 + col, acc);
                 descale<32, true>(acc, sa, __ldg(lp.sw_ff1 + 2 * ch + jh), lp.b_ff1 + col, &hid[16 * jh]);
             }
             // per-row u8 scale over the 256-wide chunk (encoder.cu:1510-1517)
@@ -546,23 +548,22 @@ __device__ __forceinline__ void ffn_block(RowCtx& c, const Params& p, const Laye
             const float sc = amax > 0.f ? __fdiv_rn(amax, 255.0f) : 1.0f;
             const float inv = __fdiv_rn(1.0f, sc);
             if (ch & 1) sa2_1 = sc; else sa2_0 = sc;
-            const bool caph = cap && p.cap_op == BF_OP_FF2 + ch && c.valid;
+            const bool caph = kDbg && cap && p.cap_op == BF_OP_FF2 + ch && c.valid;
 #pragma unroll
             for (int jh = 0; jh < 2; ++jh)
 #pragma unroll
                 for (int k = 0; k < 2; ++k) {
                     const uint4 v = quant16(&hid[16 * jh + 8 * k], inv);
-                    *reinterpret_cast<uint4*>(c.smem_gen + SM_R + (ch & 1) * 32768 + jh * 16384 +
-                                              sw_off(c.row, 2 * c.qt + k)) = v;
+                    sts128(c.smem + SM_R + (ch & 1) * 32768 + jh * 16384 + sw_off(c.row, 2 * c.qt + k), v);
                     if (caph) *reinterpret_cast<uint4*>(p.cap_a + c.grow * kD + 128 * jh + 32 * c.qt + 16 * k) = v;
                 }
             row_publish(c, B_A2_READY + (ch & 1));
-            prof_mark(c, PH_FF1_EPI);
+            prof_mark<kDbg>(c, PH_FF1_EPI);
         } else {
             const float s1 = (ch & 1) ? sa2_1 : sa2_0;
 #pragma unroll 1
             for (int jh = 0; jh < 2; ++jh) {
-                row_wait_acc(c, jh, PH_FF2_EPI);
+                row_wait_acc<kDbg>(c, jh, PH_FF2_EPI, PH_WAIT_FF2);
                 const float s2 = __ldg(lp.sw_ff2 + jh);
                 uint32_t acc[32], run[16];
                 const int col = 128 * jh + 32 * c.qt;
@@ -570,7 +571,7 @@ __device__ __forceinline__ void ffn_block(RowCtx& c, const Params& p, const Laye
                 if (ch > 0) tmem_ld16(c.tm + TM_OY + (col >> 1), run);
                 tmem_wait_ld();
                 row_release_acc(c, jh);
-                if (cap && p.cap_op == BF_OP_FF2 + ch && c.valid) store_words<32>(p.cap_acc + c.grow * 256 + col, acc);
+                if (kDbg && cap && p.cap_op == BF_OP_FF2 + ch && c.valid) store_words<32>(p.cap_acc + c.grow * 256 + col, acc);
                 const uint64_t s1_2 = pk2(s1, s1), s2_2 = pk2(s2, s2);
 #pragma unroll
                 for (int i = 0; i < 16; ++i) {
@@ -602,11 +603,12 @@ __device__ __forceinline__ void ffn_block(RowCtx& c, const Params& p, const Laye
                 }
             }
             tmem_wait_st();
-            prof_mark(c, PH_FF2_EPI);
+            prof_mark<kDbg>(c, PH_FF2_EPI);
         }
     }
 }
 
+template <bool kDbg>
 __device__ __forceinline__ void row_warps_tile(RowCtx& c, const Params& p, int tile) {
     const int board = tile * 4 + c.q;
     c.valid = board < p.n;
@@ -653,7 +655,7 @@ __device__ __forceinline__ void row_warps_tile(RowCtx& c, const Params& p, int t
         }
         tmem_wait_st();
     }
-    prof_mark(c, PH_EMBED);
+    prof_mark<kDbg>(c, PH_EMBED);
 
     const int n_ph = 2 * p.n_layers;
 #pragma unroll 1
@@ -664,12 +666,12 @@ __device__ __forceinline__ void row_warps_tile(RowCtx& c, const Params& p, int t
         const bool dump_x = (dbg == 9 && ph == 0) || (dbg == 2 && odd && dbgl) ||
                             (dbg == 10 && !odd && ph > 0 && layer - 1 == p.debug_layer);
         if (ph == n_ph) {
-            ln_stage(c, p, true, dump_x, dbg == 8, false);
+            ln_stage<kDbg>(c, p, true, dump_x, dbg == 8, false);
             row_publish(c, B_A_READY);
             break;
         }
         const bool cap = layer == p.cap_layer;
-        const float sa = ln_stage(c, p, false, dump_x, dbgl && dbg == (odd ? 3 : 1),
+        const float sa = ln_stage<kDbg>(c, p, false, dump_x, dbgl && dbg == (odd ? 3 : 1),
                                   cap && p.cap_op == (odd ? BF_OP_FF1 : BF_OP_QKV));
         row_publish(c, B_A_READY);
 
@@ -683,13 +685,13 @@ __device__ __forceinline__ void row_warps_tile(RowCtx& c, const Params& p, int t
         lp.b_o = reinterpret_cast<const __half*>(lpb + LP_B_O);
         lp.b_ff1 = reinterpret_cast<const __half*>(lpb + LP_B_FF1);
         lp.b_ff2 = reinterpret_cast<const __half*>(lpb + LP_B_FF2);
-        if (!odd) attention_block(c, p, lp, sa, c.valid ? alive : 0xffffffffu, cap, dbgl);
-        else      ffn_block(c, p, lp, sa, cap);
+        if (!odd) attention_block<kDbg>(c, p, lp, sa, c.valid ? alive : 0xffffffffu, cap, dbgl);
+        else      ffn_block<kDbg>(c, p, lp, sa, cap);
     }
 
     // ---- heads: fp16 GEMM [128 x 256] x [96 x 256]^T, fp32 accumulate, rounded to fp16
     //      (encoder.cu:894-1079; the reference accumulates in fp16) -------------------------
-    row_wait_acc(c, 0, PH_LN);
+    row_wait_acc<kDbg>(c, 0, PH_LN);
     {
         uint32_t acc[16], aux[16];
         tmem_ld16(c.tm + TM_ACC + 16 * c.qt, acc);
@@ -745,7 +747,7 @@ __device__ __forceinline__ void row_warps_tile(RowCtx& c, const Params& p, int t
             }
         }
     }
-    prof_mark(c, PH_HEAD);
+    prof_mark<kDbg>(c, PH_HEAD);
 }
 
 // ------------------------------------------------------------------------------------------
@@ -885,6 +887,7 @@ __device__ __forceinline__ void mma_loop(uint32_t smem, uint32_t tmem, volatile 
 }
 
 // ------------------------------------------------------------------------------------------
+template <bool kDbg>
 __global__ void __launch_bounds__(kThreads, 1) encoder_kernel(const Params p) {
     extern __shared__ uint8_t smem_raw[];
     uint8_t* sm = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
@@ -918,9 +921,9 @@ __global__ void __launch_bounds__(kThreads, 1) encoder_kernel(const Params p) {
         c.smem = smem; c.smem_gen = sm;
         c.tm = tmem + (static_cast<uint32_t>(32 * c.q) << 16);
         c.abort_flag = abort_flag; c.xpar = 0; c.full0 = c.full1 = 0;
-        c.prof_on = p.prof != nullptr && threadIdx.x == 0;
+        c.prof_on = kDbg && p.prof != nullptr && threadIdx.x == 0;
         c.t_last = c.prof_on ? clock64() : 0;
-        for (int tile = blockIdx.x; tile < n_tiles; tile += gridDim.x) row_warps_tile(c, p, tile);
+        for (int tile = blockIdx.x; tile < n_tiles; tile += gridDim.x) row_warps_tile<kDbg>(c, p, tile);
     } else if (warp == kProducerWarp) {
         if (lane == 0) producer_loop(smem, abort_flag, p, blockIdx.x, gridDim.x, n_tiles);
     } else {
@@ -932,7 +935,7 @@ __global__ void __launch_bounds__(kThreads, 1) encoder_kernel(const Params p) {
     tc_fence_after();
     if (warp == kMmaWarp) tmem_dealloc(tmem, TM_COLS);
     if (threadIdx.x == 0 && *abort_flag != 0) atomicCAS(p.status, 0, *abort_flag);
-    if (threadIdx.x == 0 && p.prof != nullptr)
+    if (kDbg && threadIdx.x == 0 && p.prof != nullptr)
         for (int i = 0; i < PH_COUNT; ++i)
             atomicAdd(p.prof + i, static_cast<unsigned long long>(reinterpret_cast<long long*>(sm + SM_PROF)[i]));
 }
@@ -1046,7 +1049,9 @@ struct bf_handle {
     int cap_n = 0;
     uint8_t* d_in = nullptr;      // boards | control | rep | legal
     uint8_t* d_out = nullptr;     // policy | promo | value
-    cudaStream_t stream = nullptr;
+    cudaStream_t stream = nullptr;       // inputs and kernels of bf_forward_host
+    cudaStream_t copy_stream = nullptr;  // its device-to-host copies
+    cudaEvent_t chunk_done = nullptr;
 };
 
 namespace {
@@ -1076,7 +1081,11 @@ int launch(bf_handle* h, const uint16_t* boards, const int16_t* control, const u
     p.prof = h->prof_on ? h->prof : nullptr;
     const int n_tiles = (n + 3) / 4;
     const int grid = n_tiles < h->sm_count ? n_tiles : h->sm_count;
-    bf::encoder_kernel<<<grid, bf::kThreads, bf::kSmemRequest, stream>>>(p);
+    // the instrumented instantiation only when a dump, a capture or the phase clock is asked for
+    if (stage != 0 || cap_layer >= 0 || p.prof != nullptr)
+        bf::encoder_kernel<true><<<grid, bf::kThreads, bf::kSmemRequest, stream>>>(p);
+    else
+        bf::encoder_kernel<false><<<grid, bf::kThreads, bf::kSmemRequest, stream>>>(p);
     BF_CUDA(cudaGetLastError());
     h->launches++;
     return BF_OK;
@@ -1124,8 +1133,13 @@ int bf_create(const void* blob, size_t blob_bytes, int device, bf_handle** out) 
     if (e == cudaSuccess) e = cudaMalloc(&h->status, sizeof(int));
     if (e == cudaSuccess) e = cudaMemset(h->status, 0, sizeof(int));
     if (e == cudaSuccess) e = cudaStreamCreateWithFlags(&h->stream, cudaStreamNonBlocking);
+    if (e == cudaSuccess) e = cudaStreamCreateWithFlags(&h->copy_stream, cudaStreamNonBlocking);
+    if (e == cudaSuccess) e = cudaEventCreateWithFlags(&h->chunk_done, cudaEventDisableTiming);
     if (e == cudaSuccess)
-        e = cudaFuncSetAttribute(bf::encoder_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+        e = cudaFuncSetAttribute(bf::encoder_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                 bf::kSmemRequest);
+    if (e == cudaSuccess)
+        e = cudaFuncSetAttribute(bf::encoder_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                  bf::kSmemRequest);
     if (e != cudaSuccess) {
         bf_destroy(h);
@@ -1139,6 +1153,8 @@ int bf_destroy(bf_handle* h) {
     if (h == nullptr) return BF_OK;
     cudaSetDevice(h->device);
     if (h->stream) { cudaStreamSynchronize(h->stream); cudaStreamDestroy(h->stream); }
+    if (h->copy_stream) { cudaStreamSynchronize(h->copy_stream); cudaStreamDestroy(h->copy_stream); }
+    if (h->chunk_done) cudaEventDestroy(h->chunk_done);
     cudaFree(h->blob); cudaFree(h->status); cudaFree(h->prof); cudaFree(h->d_in); cudaFree(h->d_out);
     delete h;
     return BF_OK;
@@ -1212,14 +1228,27 @@ int bf_forward_host(bf_handle* h, const uint16_t* boards, const int16_t* control
     BF_CUDA(cudaMemcpyAsync(d_control, control, static_cast<size_t>(n) * 2, cudaMemcpyHostToDevice, s));
     BF_CUDA(cudaMemcpyAsync(d_rep, rep, static_cast<size_t>(n), cudaMemcpyHostToDevice, s));
     if (legal) BF_CUDA(cudaMemcpyAsync(d_legal, legal, static_cast<size_t>(n) * 256, cudaMemcpyHostToDevice, s));
-    int rc = launch(h, reinterpret_cast<uint16_t*>(d_boards), reinterpret_cast<int16_t*>(d_control), d_rep,
-                    legal ? reinterpret_cast<uint64_t*>(d_legal) : nullptr, n, d_policy, d_promo,
-                    reinterpret_cast<float*>(d_value), nullptr, 0, 0, -1, -1, nullptr, nullptr, s);
-    if (rc != BF_OK) return rc;
-    if (policy) BF_CUDA(cudaMemcpyAsync(policy, d_policy, static_cast<size_t>(n) * 4096, cudaMemcpyDeviceToHost, s));
-    if (promo) BF_CUDA(cudaMemcpyAsync(promo, d_promo, static_cast<size_t>(n) * 256, cudaMemcpyDeviceToHost, s));
-    if (value) BF_CUDA(cudaMemcpyAsync(value, d_value, static_cast<size_t>(n) * 4, cudaMemcpyDeviceToHost, s));
+    // The batch goes out as launches of one full wave (one tile per SM) each, so that the
+    // copy-out of a finished wave overlaps the next wave's compute on a second stream.
+    const int wave = h->sm_count * 4;
+    cudaStream_t c = h->copy_stream;
+    for (int lo = 0; lo < n; lo += wave) {
+        const int m = n - lo < wave ? n - lo : wave;
+        const size_t o = static_cast<size_t>(lo);
+        int rc = launch(h, reinterpret_cast<uint16_t*>(d_boards) + o * 32, reinterpret_cast<int16_t*>(d_control) + o,
+                        d_rep + o, legal ? reinterpret_cast<uint64_t*>(d_legal) + o * 32 : nullptr, m,
+                        d_policy + o * 4096, d_promo + o * 256, reinterpret_cast<float*>(d_value) + o, nullptr,
+                        0, 0, -1, -1, nullptr, nullptr, s);
+        if (rc != BF_OK) return rc;
+        BF_CUDA(cudaEventRecord(h->chunk_done, s));
+        BF_CUDA(cudaStreamWaitEvent(c, h->chunk_done, 0));
+        const size_t M = static_cast<size_t>(m);
+        if (policy) BF_CUDA(cudaMemcpyAsync(static_cast<uint8_t*>(policy) + o * 4096, d_policy + o * 4096, M * 4096, cudaMemcpyDeviceToHost, c));
+        if (promo) BF_CUDA(cudaMemcpyAsync(static_cast<uint8_t*>(promo) + o * 256, d_promo + o * 256, M * 256, cudaMemcpyDeviceToHost, c));
+        if (value) BF_CUDA(cudaMemcpyAsync(value + o, d_value + o * 4, M * 4, cudaMemcpyDeviceToHost, c));
+    }
     BF_CUDA(cudaStreamSynchronize(s));
+    BF_CUDA(cudaStreamSynchronize(c));
     return BF_OK;
 }
 
@@ -1259,8 +1288,9 @@ int bf_profile_read(bf_handle* h, long long* cycles, int n) {
 }
 
 const char* bf_profile_phases(void) {
-    return "embed,layernorm_quantise,wait_mma,qkv_epilogue,pair_barrier,attention,attn_readback,"
-           "attn_quantise,out_proj_epilogue,ff1_epilogue,ff2_epilogue,heads";
+    return "embed,layernorm_quantise,wait_mma_qkv_heads,qkv_epilogue,pair_barrier,attention,attn_readback,"
+           "attn_quantise,out_proj_epilogue,ff1_epilogue,ff2_epilogue,heads,wait_mma_out,wait_mma_ff1,"
+           "wait_mma_ff2";
 }
 
 int bf_selftest_umma(int device, int mode, const void* a, const void* w_image, void* out) {
@@ -1332,7 +1362,7 @@ int noalloc_setup(int device, NoAllocDevice** out) {
         void* ptr = nullptr;
         BF_CUDA(cudaGetSymbolAddress(&ptr, bf::g_noalloc_scratch));
         BF_CUDA(cudaMemset(ptr, 0, bf::kNoAllocScratchBytes));
-        BF_CUDA(cudaFuncSetAttribute(bf::encoder_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+        BF_CUDA(cudaFuncSetAttribute(bf::encoder_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                      bf::kSmemRequest));
         d.scratch = ptr;
         d.sm_count = prop.multiProcessorCount;
@@ -1396,7 +1426,7 @@ int bf_forward_noalloc(int device, const void* blob_dev, size_t blob_bytes, cons
     p.prof = nullptr;
     const int n_tiles = (n + 3) / 4;
     const int grid = n_tiles < d->sm_count ? n_tiles : d->sm_count;
-    bf::encoder_kernel<<<grid, bf::kThreads, bf::kSmemRequest, static_cast<cudaStream_t>(stream)>>>(p);
+    bf::encoder_kernel<false><<<grid, bf::kThreads, bf::kSmemRequest, static_cast<cudaStream_t>(stream)>>>(p);
     BF_CUDA(cudaGetLastError());
     return BF_OK;
 }

@@ -95,8 +95,9 @@ int bf_forward_capture(bf_handle* h, const uint16_t* boards, const int16_t* cont
                        int32_t* acc, void* stream);
 
 /* End-to-end call with HOST buffers (pinned for best speed): copies the inputs to the
- * device, runs `bf_forward`, copies the three outputs back and synchronises.  Device
- * staging buffers are owned by the handle and grow to the largest `n` seen. */
+ * device, runs the evaluator as launches of one full wave of tiles each, copies each wave's
+ * three outputs back on a second stream while the next wave computes, and synchronises.
+ * Device staging buffers are owned by the handle and grow to the largest `n` seen. */
 int bf_forward_host(bf_handle* h, const uint16_t* boards, const int16_t* control,
                     const uint8_t* rep, const uint64_t* legal, int n, void* policy,
                     void* promo, float* value);

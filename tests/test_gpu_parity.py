@@ -350,6 +350,6 @@ def test_phase_profile_hooks(encoders, pos256):
     prof = enc.read_profile()
     enc.set_profile(False)
     assert np.array_equal(base.view(np.uint16), got.view(np.uint16))
-    assert set(prof) >= {"layernorm_quantise", "wait_mma", "attention", "ff1_epilogue", "heads"}
+    assert set(prof) >= {"layernorm_quantise", "wait_mma_ff1", "attention", "ff1_epilogue", "heads"}
     assert all(v >= 0 for v in prof.values()) and prof["ff1_epilogue"] > 0 and prof["attention"] > 0
     enc.check_status()
