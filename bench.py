@@ -44,10 +44,35 @@ WORKLOAD = ("8-layer d256 h8 ff1024 int8 evaluator, N(0,0.02) seed-0 weights, se
 def load_positions(n: int):
     """``n`` positions: the committed 4096 random-playout positions, tiled when more are
     asked for (a tile keeps the distribution of piece counts, clocks and side to move)."""
-    z = np.load(os.path.join(ROOT, "tests", "golden", "positions_4096_seed1.npz"))
-    reps = (n + 4095) // 4096
-    take = lambda a: np.ascontiguousarray(np.concatenate([a] * reps)[:n])
-    return take(z["boards"]), take(z["control"]), take(z["rep"]), take(z["legal"])
+    from brokefish_b200.positions import tiled
+    return tiled(n)
+
+
+def sweep(enc, dev, batches=(1, 64, 512, 4096, 16384, 65536), steps=10, warmup=3):
+    """Batch sweep with piece counts uniform in 2..32 and side to move 50/50: one JSON line
+    per batch size (latency-bound at the small end, throughput-bound at the large end)."""
+    from brokefish_b200.positions import varied
+    flush = torch.empty(256 << 20, dtype=torch.uint8, device=dev)
+    for n in batches:
+        b, c, r, _ = varied(n, seed=2)
+        d_b, d_c, d_r = (torch.from_numpy(a).to(dev) for a in (b, c, r))
+        for _ in range(warmup):
+            enc.forward_full(d_b, d_c, d_r)
+        torch.cuda.synchronize(dev)
+        ms = []
+        for i in range(steps):
+            flush.fill_(i & 0xFF)
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record()
+            enc.forward_full(d_b, d_c, d_r)
+            e1.record()
+            torch.cuda.synchronize(dev)
+            ms.append(e0.elapsed_time(e1))
+        enc.check_status()
+        t = float(np.median(ms))
+        print(json.dumps({"sweep_batch": n, "ms_per_launch_median": t, "positions_per_s": n / t * 1e3,
+                          "int8_TOPs": n * OPS_PER_POSITION / t / 1e9, "tiles": (n + 3) // 4,
+                          "data": "synthetic: piece counts U{2..32}, side to move 50/50, seed 2"}))
 
 
 def peaks():
@@ -128,6 +153,7 @@ def main() -> int:
     ap.add_argument("--total", type=int, default=0,
                     help="fixed number of positions per step split across the GPUs")
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--sweep", action="store_true", help="print one line per batch size 1..65536 and exit")
     args = ap.parse_args()
     rank = int(os.environ.get("RANK", "0"))
     world = int(os.environ.get("WORLD_SIZE", "1"))
@@ -165,6 +191,11 @@ def main() -> int:
         net.load_state_dict(seeded_state(seed=0, std=0.02))
     ev = ShardedEvaluator(net, rank, world, local)        # one broadcast of the packed blob
     enc = ev.encoder
+
+    if args.sweep:
+        if rank == 0:
+            sweep(enc, dev)
+        return 0
 
     if args.total:
         lo, hi = shard_bounds(args.total, world, rank)

@@ -80,6 +80,8 @@ struct Params {
     const uint8_t* lparams;
     const __half* emb;
     const __half* tail;
+    const __half* rj;           // re-injection coefficients [sites][8] or null
+    int rj_mode;                // 0 none, 1 attention norms, 2 both norms
     __half* policy;
     __half* promo;
     float* value;
@@ -104,6 +106,8 @@ struct RowCtx {
     uint32_t full0, full1;      // accumulator slots consumed so far
     long grow;                  // global token row = board * 32 + token
     bool valid;                 // board < n
+    uint32_t word;              // this token's piece word
+    int stm, clk, rp;           // board-level embedding indices (side to move, clock, repetition)
     bool prof_on;               // this thread keeps the CTA's phase clock
     long long t_last;
 };
@@ -252,9 +256,46 @@ __device__ __forceinline__ void store_words(void* dst, const uint32_t* w) {
 // x -> x_hat is monotone (every rounding in it is), so amax(x_hat) is reached at the row's
 // largest or smallest x and needs no second pass: the row minimum and maximum travel in the
 // same exchange as the sums.
-template <bool kDbg>
+// Per-layer input re-injection (csrc/encoder.cu:384-416, 439-583): what the LayerNorm is given
+// is `x + sum_k c[site][k] * E_k` with the five embedding rows of this token, in the
+// reference's fp16 order: pb = fma(c_clk, clock, c_rep * rep); cs = fma(c_ct, color_turn by
+// *slot* colour, pb); then fma(c_ts, type_special, fma(c_sq, square, x)) + cs.  The residual
+// stream itself is not touched.  32 columns starting at `col`.
+__device__ __forceinline__ void reinject32(const RowCtx& c, const Params& p, int site, int col,
+                                           uint32_t (&x)[16]) {
+    const uint4 cf = __ldg(reinterpret_cast<const uint4*>(p.rj + site * 8));
+    const __half2 c_sq = __half2half2(__low2half(as_h2(cf.x))), c_ts = __half2half2(__high2half(as_h2(cf.x)));
+    const __half2 c_ct = __half2half2(__low2half(as_h2(cf.y))), c_ck = __half2half2(__high2half(as_h2(cf.y)));
+    const __half2 c_rp = __half2half2(__low2half(as_h2(cf.z)));
+    const int sq = c.word & 63;
+    const int ts = min(static_cast<int>(((c.word >> 6) & 7) * 2 + ((c.word >> 9) & 1)), kNTypeSpecial - 1);
+    const int ct = (c.lane >> 4) * 2 + c.stm;
+    const uint4* e_sq = reinterpret_cast<const uint4*>(p.emb + (EMB_SQUARE + sq) * kD + col);
+    const uint4* e_ts = reinterpret_cast<const uint4*>(p.emb + (EMB_TS + ts) * kD + col);
+    const uint4* e_ct = reinterpret_cast<const uint4*>(p.emb + (EMB_CT + ct) * kD + col);
+    const uint4* e_ck = reinterpret_cast<const uint4*>(p.emb + (EMB_CLOCK + c.clk) * kD + col);
+    const uint4* e_rp = reinterpret_cast<const uint4*>(p.emb + (EMB_REP + c.rp) * kD + col);
+#pragma unroll
+    for (int k = 0; k < 4; ++k) {
+        const uint4 a = __ldg(e_sq + k), b = __ldg(e_ts + k), d = __ldg(e_ct + k);
+        const uint4 e = __ldg(e_ck + k), f = __ldg(e_rp + k);
+        const uint32_t aw[4] = {a.x, a.y, a.z, a.w}, bw[4] = {b.x, b.y, b.z, b.w};
+        const uint32_t dw[4] = {d.x, d.y, d.z, d.w}, ew[4] = {e.x, e.y, e.z, e.w};
+        const uint32_t fw[4] = {f.x, f.y, f.z, f.w};
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+            const __half2 pb = __hfma2(c_ck, as_h2(ew[j]), __hmul2(c_rp, as_h2(fw[j])));
+            const __half2 cs = __hfma2(c_ct, as_h2(dw[j]), pb);
+            __half2 t = __hfma2(c_sq, as_h2(aw[j]), as_h2(x[4 * k + j]));
+            t = __hfma2(c_ts, as_h2(bw[j]), t);
+            x[4 * k + j] = as_u32(__hadd2(t, cs));
+        }
+    }
+}
+
+template <bool kDbg, bool kRJ>
 __device__ __forceinline__ float ln_stage(RowCtx& c, const Params& p, bool final_norm, bool dump_x,
-                                          bool dump_xn, bool capture) {
+                                          bool dump_xn, bool capture, int site) {
     uint64_t sum2 = pk2(0.f, 0.f), sq2 = pk2(0.f, 0.f);      // (even, odd) column lanes
     __half2 mn = __float2half2_rn(65504.0f), mx = __float2half2_rn(-65504.0f);
 #pragma unroll 1
@@ -263,6 +304,7 @@ __device__ __forceinline__ float ln_stage(RowCtx& c, const Params& p, bool final
         tmem_ld16(c.tm + TM_X + 64 * u + 16 * c.qt, x);
         tmem_wait_ld();
         if (kDbg && dump_x && c.valid) store_words<16>(p.y + c.grow * kD + 128 * u + 32 * c.qt, x);
+        if (kRJ && site >= 0) reinject32(c, p, site, 128 * u + 32 * c.qt, x);
 #pragma unroll
         for (int i = 0; i < 16; ++i) {
             const __half2 h = as_h2(x[i]);
@@ -299,6 +341,7 @@ __device__ __forceinline__ float ln_stage(RowCtx& c, const Params& p, bool final
         tmem_ld16(c.tm + TM_X + 64 * u + 16 * c.qt, x);
         tmem_wait_ld();
         const int col = 128 * u + 32 * c.qt;
+        if (kRJ && site >= 0) reinject32(c, p, site, col, x);
         if (!final_norm) {
 #pragma unroll
             for (int i = 0; i < 16; ++i) x[i] = f2_to_h2(mul2(add2(h2_to_f2(x[i]), nmean2), rstd2));
@@ -608,7 +651,7 @@ __device__ __forceinline__ void ffn_block(RowCtx& c, const Params& p, const Laye
     }
 }
 
-template <bool kDbg>
+template <bool kDbg, bool kRJ>
 __device__ __forceinline__ void row_warps_tile(RowCtx& c, const Params& p, int tile) {
     const int board = tile * 4 + c.q;
     c.valid = board < p.n;
@@ -624,6 +667,7 @@ __device__ __forceinline__ void row_warps_tile(RowCtx& c, const Params& p, int t
         const int stm = ctl < 0;
         const int clk = min(max((ctl < 0 ? -ctl : ctl) - 1, 0), kNClock - 1);
         const int rp = min(c.valid ? static_cast<int>(p.rep[board]) : 0, kNRep - 1);
+        c.word = word; c.stm = stm; c.clk = clk; c.rp = rp;
         const int sq = word & 63;
         const int ts = min(static_cast<int>(((word >> 6) & 7) * 2 + ((word >> 9) & 1)), kNTypeSpecial - 1);
         const int ct = ((word >> 10) & 1) * 2 + stm;
@@ -666,13 +710,15 @@ __device__ __forceinline__ void row_warps_tile(RowCtx& c, const Params& p, int t
         const bool dump_x = (dbg == 9 && ph == 0) || (dbg == 2 && odd && dbgl) ||
                             (dbg == 10 && !odd && ph > 0 && layer - 1 == p.debug_layer);
         if (ph == n_ph) {
-            ln_stage<kDbg>(c, p, true, dump_x, dbg == 8, false);
+            ln_stage<kDbg, kRJ>(c, p, true, dump_x, dbg == 8, false, -1);
             row_publish(c, B_A_READY);
             break;
         }
         const bool cap = layer == p.cap_layer;
-        const float sa = ln_stage<kDbg>(c, p, false, dump_x, dbgl && dbg == (odd ? 3 : 1),
-                                  cap && p.cap_op == (odd ? BF_OP_FF1 : BF_OP_QKV));
+        // re-injection site of this norm: every norm when both inject, attention norms only else
+        const int site = !kRJ ? -1 : (p.rj_mode == 2 ? ph : (odd ? -1 : layer));
+        const float sa = ln_stage<kDbg, kRJ>(c, p, false, dump_x, dbgl && dbg == (odd ? 3 : 1),
+                                           cap && p.cap_op == (odd ? BF_OP_FF1 : BF_OP_QKV), site);
         row_publish(c, B_A_READY);
 
         const uint8_t* lpb = p.lparams + static_cast<size_t>(layer) * kLparamStride;
@@ -887,7 +933,7 @@ __device__ __forceinline__ void mma_loop(uint32_t smem, uint32_t tmem, volatile 
 }
 
 // ------------------------------------------------------------------------------------------
-template <bool kDbg>
+template <bool kDbg, bool kRJ>
 __global__ void __launch_bounds__(kThreads, 1) encoder_kernel(const Params p) {
     extern __shared__ uint8_t smem_raw[];
     uint8_t* sm = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
@@ -923,7 +969,7 @@ __global__ void __launch_bounds__(kThreads, 1) encoder_kernel(const Params p) {
         c.abort_flag = abort_flag; c.xpar = 0; c.full0 = c.full1 = 0;
         c.prof_on = kDbg && p.prof != nullptr && threadIdx.x == 0;
         c.t_last = c.prof_on ? clock64() : 0;
-        for (int tile = blockIdx.x; tile < n_tiles; tile += gridDim.x) row_warps_tile<kDbg>(c, p, tile);
+        for (int tile = blockIdx.x; tile < n_tiles; tile += gridDim.x) row_warps_tile<kDbg, kRJ>(c, p, tile);
     } else if (warp == kProducerWarp) {
         if (lane == 0) producer_loop(smem, abort_flag, p, blockIdx.x, gridDim.x, n_tiles);
     } else {
@@ -1030,8 +1076,8 @@ int fail(int code, const std::string& msg) {
 struct BlobHeader {
     uint32_t magic, version, n_layers, n_value, vmode;
     float eps;
-    uint32_t reserved[2];
-    uint64_t off_w, bytes_w, off_lp, bytes_lp, off_emb, bytes_emb, off_tail, bytes_tail, total;
+    uint32_t rj_mode, reserved;
+    uint64_t off_w, bytes_w, off_lp, bytes_lp, off_emb, bytes_emb, off_tail, bytes_tail, off_rj, bytes_rj, total;
 };
 
 }  // namespace
@@ -1074,6 +1120,8 @@ int launch(bf_handle* h, const uint16_t* boards, const int16_t* control, const u
     p.lparams = h->blob + h->hdr.off_lp;
     p.emb = reinterpret_cast<const __half*>(h->blob + h->hdr.off_emb);
     p.tail = reinterpret_cast<const __half*>(h->blob + h->hdr.off_tail);
+    p.rj_mode = static_cast<int>(h->hdr.rj_mode);
+    p.rj = p.rj_mode ? reinterpret_cast<const __half*>(h->blob + h->hdr.off_rj) : nullptr;
     p.policy = static_cast<__half*>(policy); p.promo = static_cast<__half*>(promo); p.value = value;
     p.y = static_cast<__half*>(y); p.debug_stage = stage; p.debug_layer = stage_layer;
     p.cap_layer = cap_layer; p.cap_op = cap_op; p.cap_a = cap_a; p.cap_acc = cap_acc;
@@ -1082,10 +1130,14 @@ int launch(bf_handle* h, const uint16_t* boards, const int16_t* control, const u
     const int n_tiles = (n + 3) / 4;
     const int grid = n_tiles < h->sm_count ? n_tiles : h->sm_count;
     // the instrumented instantiation only when a dump, a capture or the phase clock is asked for
-    if (stage != 0 || cap_layer >= 0 || p.prof != nullptr)
-        bf::encoder_kernel<true><<<grid, bf::kThreads, bf::kSmemRequest, stream>>>(p);
-    else
-        bf::encoder_kernel<false><<<grid, bf::kThreads, bf::kSmemRequest, stream>>>(p);
+    const bool dbg = stage != 0 || cap_layer >= 0 || p.prof != nullptr;
+    if (p.rj_mode != 0) {
+        if (dbg) bf::encoder_kernel<true, true><<<grid, bf::kThreads, bf::kSmemRequest, stream>>>(p);
+        else     bf::encoder_kernel<false, true><<<grid, bf::kThreads, bf::kSmemRequest, stream>>>(p);
+    } else {
+        if (dbg) bf::encoder_kernel<true, false><<<grid, bf::kThreads, bf::kSmemRequest, stream>>>(p);
+        else     bf::encoder_kernel<false, false><<<grid, bf::kThreads, bf::kSmemRequest, stream>>>(p);
+    }
     BF_CUDA(cudaGetLastError());
     h->launches++;
     return BF_OK;
@@ -1112,12 +1164,14 @@ int bf_create(const void* blob, size_t blob_bytes, int device, bf_handle** out) 
     if (hdr.n_layers < 1 || hdr.n_layers > 64) return fail(BF_EINVAL, "n_layers out of range");
     if (hdr.bytes_w != static_cast<uint64_t>(hdr.n_layers) * bf::kLayerStreamBytes + 4 * bf::kHeadStage ||
         hdr.bytes_lp != static_cast<uint64_t>(hdr.n_layers) * bf::kLparamStride ||
-        hdr.bytes_emb != 184u * 256u * 2u || hdr.bytes_tail != 1024u)
+        hdr.bytes_emb != 184u * 256u * 2u || hdr.bytes_tail != 2560u || hdr.rj_mode > 2 ||
+        hdr.bytes_rj != (hdr.rj_mode ? static_cast<uint64_t>(hdr.n_layers) * hdr.rj_mode * 16u : 0u))
         return fail(BF_EINVAL, "blob section sizes do not match this build");
-    if ((hdr.off_w | hdr.off_lp | hdr.off_emb | hdr.off_tail) & 255u)
+    if ((hdr.off_w | hdr.off_lp | hdr.off_emb | hdr.off_tail | hdr.off_rj) & 255u)
         return fail(BF_EINVAL, "blob sections must be 256-byte aligned");
     if (hdr.off_w + hdr.bytes_w > blob_bytes || hdr.off_lp + hdr.bytes_lp > blob_bytes ||
-        hdr.off_emb + hdr.bytes_emb > blob_bytes || hdr.off_tail + hdr.bytes_tail > blob_bytes)
+        hdr.off_emb + hdr.bytes_emb > blob_bytes || hdr.off_tail + hdr.bytes_tail > blob_bytes ||
+        hdr.off_rj + hdr.bytes_rj > blob_bytes)
         return fail(BF_EINVAL, "blob section outside the blob");
     if (hdr.n_value != 1 && hdr.n_value != 3) return fail(BF_EINVAL, "n_value must be 1 or 3");
     if (hdr.vmode > 1) return fail(BF_ENOTSUP, "the prenorm value head is not built");
@@ -1136,10 +1190,16 @@ int bf_create(const void* blob, size_t blob_bytes, int device, bf_handle** out) 
     if (e == cudaSuccess) e = cudaStreamCreateWithFlags(&h->copy_stream, cudaStreamNonBlocking);
     if (e == cudaSuccess) e = cudaEventCreateWithFlags(&h->chunk_done, cudaEventDisableTiming);
     if (e == cudaSuccess)
-        e = cudaFuncSetAttribute(bf::encoder_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+        e = cudaFuncSetAttribute(bf::encoder_kernel<false, false>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                  bf::kSmemRequest);
     if (e == cudaSuccess)
-        e = cudaFuncSetAttribute(bf::encoder_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+        e = cudaFuncSetAttribute(bf::encoder_kernel<true, false>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                 bf::kSmemRequest);
+    if (e == cudaSuccess)
+        e = cudaFuncSetAttribute(bf::encoder_kernel<false, true>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                 bf::kSmemRequest);
+    if (e == cudaSuccess)
+        e = cudaFuncSetAttribute(bf::encoder_kernel<true, true>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                  bf::kSmemRequest);
     if (e != cudaSuccess) {
         bf_destroy(h);
@@ -1362,7 +1422,7 @@ int noalloc_setup(int device, NoAllocDevice** out) {
         void* ptr = nullptr;
         BF_CUDA(cudaGetSymbolAddress(&ptr, bf::g_noalloc_scratch));
         BF_CUDA(cudaMemset(ptr, 0, bf::kNoAllocScratchBytes));
-        BF_CUDA(cudaFuncSetAttribute(bf::encoder_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+        BF_CUDA(cudaFuncSetAttribute(bf::encoder_kernel<false, false>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                      bf::kSmemRequest));
         d.scratch = ptr;
         d.sm_count = prop.multiProcessorCount;
@@ -1397,13 +1457,14 @@ int bf_forward_noalloc(int device, const void* blob_dev, size_t blob_bytes, cons
         if (hdr.n_layers < 1 || hdr.n_layers > 64 ||
             hdr.bytes_w != static_cast<uint64_t>(hdr.n_layers) * bf::kLayerStreamBytes + 4 * bf::kHeadStage ||
             hdr.bytes_lp != static_cast<uint64_t>(hdr.n_layers) * bf::kLparamStride ||
-            hdr.bytes_emb != 184u * 256u * 2u || hdr.bytes_tail != 1024u ||
+            hdr.bytes_emb != 184u * 256u * 2u || hdr.bytes_tail != 2560u || hdr.rj_mode != 0 ||
             ((hdr.off_w | hdr.off_lp | hdr.off_emb | hdr.off_tail) & 255u) ||
             hdr.off_w + hdr.bytes_w > blob_bytes || hdr.off_lp + hdr.bytes_lp > blob_bytes ||
             hdr.off_emb + hdr.bytes_emb > blob_bytes || hdr.off_tail + hdr.bytes_tail > blob_bytes)
             return fail(BF_EINVAL, "blob sections do not match this build");
         if ((hdr.n_value != 1 && hdr.n_value != 3) || hdr.vmode > 1)
             return fail(BF_ENOTSUP, "value head variant not built");
+        if (hdr.rj_mode != 0) return fail(BF_ENOTSUP, "re-injecting networks need a handle (bf_create)");
         if (reinterpret_cast<uintptr_t>(blob_dev) & 255u)
             return fail(BF_EINVAL, "the device blob must be 256-byte aligned");
         d->hdr = hdr; d->blob = blob_dev; d->blob_bytes = blob_bytes;
@@ -1419,6 +1480,7 @@ int bf_forward_noalloc(int device, const void* blob_dev, size_t blob_bytes, cons
     p.lparams = base + d->hdr.off_lp;
     p.emb = reinterpret_cast<const __half*>(base + d->hdr.off_emb);
     p.tail = reinterpret_cast<const __half*>(base + d->hdr.off_tail);
+    p.rj = nullptr; p.rj_mode = 0;
     p.policy = static_cast<__half*>(policy); p.promo = static_cast<__half*>(promo); p.value = value;
     p.y = nullptr; p.debug_stage = 0; p.debug_layer = 0;
     p.cap_layer = -1; p.cap_op = -1; p.cap_a = nullptr; p.cap_acc = nullptr;
@@ -1426,7 +1488,7 @@ int bf_forward_noalloc(int device, const void* blob_dev, size_t blob_bytes, cons
     p.prof = nullptr;
     const int n_tiles = (n + 3) / 4;
     const int grid = n_tiles < d->sm_count ? n_tiles : d->sm_count;
-    bf::encoder_kernel<false><<<grid, bf::kThreads, bf::kSmemRequest, static_cast<cudaStream_t>(stream)>>>(p);
+    bf::encoder_kernel<false, false><<<grid, bf::kThreads, bf::kSmemRequest, static_cast<cudaStream_t>(stream)>>>(p);
     BF_CUDA(cudaGetLastError());
     return BF_OK;
 }

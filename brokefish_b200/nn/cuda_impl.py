@@ -46,6 +46,7 @@ class FusedEncoder:
     NHEAD = 96
     VALUE_ROW = N_POLICY + N_PROMO
     VMODE = {"king": 0, "pooled": 1, "prenorm": 2}
+    RJMODE = {"none": 0, "ln1": 1, "both": 2}
     n_value = 1
     vmode = 0
     rj_mode = 0
@@ -103,8 +104,7 @@ class FusedEncoder:
             self.device = torch.cuda.current_device() if device is None else int(device)
             self.n_value = int(net.value.weight.shape[0])
             self.vmode = self.VMODE[getattr(net, "value_head", "king")]
-            if getattr(net, "reinject", "none") != "none":
-                raise NotImplementedError("input re-injection is not built")
+            self.rj_mode = self.RJMODE[getattr(net, "reinject", "none")]
             self.blob = pack_blob(net)
             self._create(self.blob)
 

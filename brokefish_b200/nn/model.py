@@ -27,6 +27,8 @@ VALUE_CLASSES = (1, 3)
 VALUE_HEADS = ("king", "pooled", "prenorm")
 VALUE_MODE_ID = {"pooled": 1, "prenorm": 2}
 REINJECT_MODES = ("none", "ln1", "both")
+REINJECT_MODE_ID = {"ln1": 1, "both": 2}
+N_SOURCES = 5
 
 EMB_TABLES = ("emb_square", "emb_type_special", "emb_color_turn", "emb_clock", "emb_rep")
 
@@ -61,12 +63,24 @@ def value_head_of(state: dict) -> str:
     raise ValueError(f"unknown value_mode {got}")
 
 
+def reinject_of(state: dict) -> str:
+    """Which per-layer input re-injection a ``state_dict`` was written with; absence of the
+    marker means none (brokefish/nn/model.py:210-225)."""
+    if "reinject_mode" not in state:
+        return "none"
+    got = int(state["reinject_mode"])
+    for name, i in REINJECT_MODE_ID.items():
+        if i == got:
+            return name
+    raise ValueError(f"unknown reinject_mode {got}")
+
+
 def net_for_state(state: dict, **kw) -> "BrokefishNet":
     """An empty network shaped to hold ``state`` (brokefish/nn/model.py:243-248)."""
-    if "reinject_mode" in state or "rule_features_mode" in state:
-        raise NotImplementedError(
-            "re-injection and rule-feature networks are not supported by this build")
-    return BrokefishNet(n_value=n_value_of(state), value_head=value_head_of(state), **kw)
+    if "rule_features_mode" in state:
+        raise NotImplementedError("rule-feature networks are not supported by this build")
+    return BrokefishNet(n_value=n_value_of(state), value_head=value_head_of(state),
+                        reinject=reinject_of(state), **kw)
 
 
 class BrokefishNet(nn.Module):
@@ -83,11 +97,12 @@ class BrokefishNet(nn.Module):
             raise ValueError(f"value_head must be one of {VALUE_HEADS}, got {value_head!r}")
         if reinject not in REINJECT_MODES:
             raise ValueError(f"reinject must be one of {REINJECT_MODES}, got {reinject!r}")
-        if reinject != "none" or rule_features:
-            raise NotImplementedError(
-                "per-layer re-injection and rule-derived inputs are not built here")
+        if rule_features:
+            raise NotImplementedError("rule-derived inputs are a torch-only prototype of the "
+                                      "reference and are not built here")
         self.d_model, self.n_layers, self.n_value = d_model, n_layers, n_value
-        self.value_head, self.reinject, self.rule_features = value_head, "none", False
+        self.value_head, self.reinject, self.rule_features = value_head, reinject, False
+        self.n_sites = 0 if reinject == "none" else n_layers * (2 if reinject == "both" else 1)
 
         self.emb_square = nn.Embedding(N_SQUARE, d_model)
         self.emb_type_special = nn.Embedding(N_TYPE_SPECIAL, d_model)
@@ -106,6 +121,11 @@ class BrokefishNet(nn.Module):
         if value_head in VALUE_MODE_ID:
             self.register_buffer("value_mode",
                                  torch.tensor(VALUE_MODE_ID[value_head], dtype=torch.int64))
+        if reinject in REINJECT_MODE_ID:
+            # zero-initialised: an untrained re-injecting network is the plain one exactly
+            self.reinject_c = nn.Parameter(torch.zeros(self.n_sites, N_SOURCES))
+            self.register_buffer("reinject_mode",
+                                 torch.tensor(REINJECT_MODE_ID[reinject], dtype=torch.int64))
         std = d_model ** -0.5
         for mod in (self.emb_square, self.emb_type_special, self.emb_color_turn,
                     self.emb_clock, self.emb_rep, self.policy, self.promo, self.value):
@@ -115,9 +135,11 @@ class BrokefishNet(nn.Module):
     def embed_indices(self, boards, control, rep):
         captured, color, special, ptype, square = decode_boards(boards)
         stm = (control < 0).long()
+        slot_color = (torch.arange(T, device=boards.device) >= T // 2).long()
         idx = (square, ptype * 2 + special, color * 2 + stm[:, None],
                (control.abs().long() - 1).clamp_(0, N_CLOCK - 1),
-               rep.long().clamp_(0, N_REP - 1))
+               rep.long().clamp_(0, N_REP - 1),
+               slot_color[None, :] * 2 + stm[:, None])     # re-injection's colour row: by slot
         return idx, captured == 0
 
     def embed(self, boards, control, rep):
@@ -132,8 +154,35 @@ class BrokefishNet(nn.Module):
         x = x + per_board[:, None, :]
         return x, alive
 
-    def encode(self, x, alive):
-        return self.encoder(x, src_key_padding_mask=~alive)
+    def mix(self, idx, c: torch.Tensor) -> torch.Tensor:
+        """``sum_k c[k] * E_k`` for one re-injection site, ``[N, 32, d]``; the colour row is
+        chosen by the *slot* (0-15 white, 16-31 black), not by the decoded word
+        (brokefish/nn/model.py:481-509)."""
+        F = nn.functional
+        m = F.embedding(idx[0], c[0] * self.emb_square.weight)
+        m = m + F.embedding(idx[1], c[1] * self.emb_type_special.weight)
+        m = m + F.embedding(idx[5], c[2] * self.emb_color_turn.weight)
+        per_board = (F.embedding(idx[3], c[3] * self.emb_clock.weight)
+                     + F.embedding(idx[4], c[4] * self.emb_rep.weight))
+        return m + per_board[:, None, :]
+
+    def encode(self, x, alive, idx=None):
+        """The encoder stack; with re-injection every block's LayerNorm sees
+        ``h + mix`` while the residual stream itself is untouched
+        (brokefish/nn/model.py:511-538)."""
+        if self.reinject == "none":
+            return self.encoder(x, src_key_padding_mask=~alive)
+        if idx is None:
+            raise ValueError("reinject needs the embedding indices")
+        pad = ~alive
+        both = self.reinject == "both"
+        for i, lay in enumerate(self.encoder.layers):
+            site = i * 2 if both else i
+            x = x + lay._sa_block(lay.norm1(x + self.mix(idx, self.reinject_c[site])), None, pad,
+                                  is_causal=False)
+            n2 = lay.norm2(x + self.mix(idx, self.reinject_c[site + 1])) if both else lay.norm2(x)
+            x = x + lay._ff_block(n2)
+        return x
 
     @property
     def value_absolute(self) -> bool:
@@ -162,13 +211,15 @@ class BrokefishNet(nn.Module):
 
     def forward(self, boards, control, rep, with_logits: bool = False, mask=None):
         x, alive = self.embed(boards, control, rep)
-        h = self.encode(x, alive)
+        idx, _ = self.embed_indices(boards, control, rep)
+        h = self.encode(x, alive, idx)
         return self.heads(self.norm_f(h), control, alive=alive,
                           with_logits=with_logits, h_raw=h)
 
 
 def seeded_state(seed: int = 0, std: Optional[float] = 0.02, perturb_norms: bool = False,
-                 n_value: int = 1, value_head: str = "king") -> dict:
+                 n_value: int = 1, value_head: str = "king", reinject: str = "none",
+                 reinject_scale: float = 0.5) -> dict:
     """A reproducible ``state_dict``, independent of module construction order.
 
     Keys are visited in sorted order and each tensor is drawn from its own
@@ -179,9 +230,10 @@ def seeded_state(seed: int = 0, std: Optional[float] = 0.02, perturb_norms: bool
     gammas are 1 and every bias / beta is 0.  ``std=None``: matrices are
     N(0, 1/16) (tables and heads) or N(0, 1/sqrt(fan_in)) (projections).
     ``perturb_norms``: LayerNorm gamma/beta and all biases get N(1, .1) / N(0, .1), so
-    the LayerNorm folds and the bias paths carry signal.
+    the LayerNorm folds and the bias paths carry signal.  ``reinject``: the coefficient
+    matrix is N(0, reinject_scale).
     """
-    net = BrokefishNet(n_value=n_value, value_head=value_head)
+    net = BrokefishNet(n_value=n_value, value_head=value_head, reinject=reinject)
     state = net.state_dict()
     out = {}
     for i, key in enumerate(sorted(state)):
@@ -190,7 +242,9 @@ def seeded_state(seed: int = 0, std: Optional[float] = 0.02, perturb_norms: bool
             out[key] = t.clone()
             continue
         g = torch.Generator(device="cpu").manual_seed(seed * 100003 + i)
-        if t.dim() >= 2:
+        if key == "reinject_c":
+            out[key] = reinject_scale * torch.randn(t.shape, generator=g)
+        elif t.dim() >= 2:
             s = std if std is not None else (
                 1.0 / 16 if (key.startswith("emb_") or key.split(".")[0] in
                              ("policy", "promo", "value")) else t.shape[-1] ** -0.5)

@@ -17,7 +17,8 @@ What happens here, once per weight snapshot (the reference does the same work in
 Blob layout (all offsets 256-byte aligned, little endian; mirrored by
 ``include/brokefish_b200.h``):
 
-    header   256 B   magic, version, n_layers, n_value, vmode, eps, section table
+    header   256 B   magic, version, n_layers, n_value, vmode, eps, rj_mode, section table
+                     (offset, bytes of wstream, lparams, emb, tail, rj), total bytes
     wstream  n_layers * 786432 + 49152 B
                      per layer 8 QKV stages [192 rows x 128 B], then 36 stages
                      [128 rows x 128 B]: out-proj (2 units) and the FFN units in
@@ -27,7 +28,11 @@ Blob layout (all offsets 256-byte aligned, little endian; mirrored by
                      to 128 B) then fp16 biases: qkv (chunk order) 768, out 256,
                      ff1 1024, ff2 256
     emb      184 * 256 fp16: square, type_special, color_turn, clock, rep tables
-    tail     512 fp16: norm_f gamma, beta
+    tail     1280 fp16: norm_f gamma, beta, then the value head's rows as three plain
+             row-major vectors (zero rows beyond n_value)
+    rj       (only with per-layer input re-injection) sites * 8 fp16: five coefficients per
+             site (square, type_special, color_turn, clock, rep), padded to 8; 16 sites
+             when both norms of a layer inject, 8 when only the attention norm does
 
 A QKV "chunk" j (0..3) holds heads 2j and 2j+1: rows 0-63 are their Q rows, 64-127
 their K rows, 128-191 their V rows.  A stage image stores row r's 16-byte group c at
@@ -44,11 +49,11 @@ import numpy as np
 import torch
 
 from brokefish_b200.nn.model import (BrokefishNet, EMB_TABLES, N_POLICY, N_PROMO,
-                                     VALUE_MODE_ID)
+                                     REINJECT_MODE_ID, VALUE_MODE_ID)
 from brokefish_b200.nn.quant import quantise_weights_int8_bytes
 
 MAGIC = 0x38424642          # "BFB8"
-VERSION = 1
+VERSION = 2
 HEADER_BYTES = 256
 D, DFF, H, DH, T = 256, 1024, 8, 32, 32
 NHEAD = 96                   # head matrix rows: 64 policy, 4 promo, 1-3 value, zero pad
@@ -204,10 +209,19 @@ def pack_blob(net: BrokefishNet) -> np.ndarray:
     lparams = np.concatenate([_layer_params(fl) for fl in layers])
     emb = np.concatenate([getattr(net, n).weight.detach().half().cpu().numpy().reshape(-1)
                           for n in EMB_TABLES]).astype("<f2").view(np.uint8)
+    val = np.zeros((3, D), dtype=np.float16)
+    val[:int(net.value.weight.shape[0])] = net.value.weight.detach().half().cpu().numpy()
     tail = np.concatenate([net.norm_f.weight.detach().half().cpu().numpy(),
-                           net.norm_f.bias.detach().half().cpu().numpy()]
+                           net.norm_f.bias.detach().half().cpu().numpy(), val.reshape(-1)]
                           ).astype("<f2").view(np.uint8)
-    sections = [wstream, lparams, emb, tail]
+    rj_mode = REINJECT_MODE_ID.get(getattr(net, "reinject", "none"), 0)
+    rj = np.zeros(0, dtype=np.uint8)
+    if rj_mode:
+        coef = net.reinject_c.detach().float().half().cpu().numpy()          # [sites, 5]
+        slab = np.zeros((coef.shape[0], 8), dtype=np.float16)
+        slab[:, :coef.shape[1]] = coef
+        rj = slab.reshape(-1).astype("<f2").view(np.uint8)
+    sections = [wstream, lparams, emb, tail, rj]
     offs, cur = [], HEADER_BYTES
     for sec in sections:
         offs.append(cur)
@@ -215,7 +229,7 @@ def pack_blob(net: BrokefishNet) -> np.ndarray:
     total = cur
     vmode = VALUE_MODE_ID.get(getattr(net, "value_head", "king"), 0)
     header = struct.pack("<IIIIIfII", MAGIC, VERSION, len(layers),
-                         int(net.value.weight.shape[0]), vmode, float(first.norm1.eps), 0, 0)
+                         int(net.value.weight.shape[0]), vmode, float(first.norm1.eps), rj_mode, 0)
     for off, sec in zip(offs, sections):
         header += struct.pack("<QQ", off, sec.size)
     header += struct.pack("<Q", total)

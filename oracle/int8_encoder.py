@@ -91,6 +91,8 @@ class Weights:
     head: np.ndarray                      # [96, 256] fp16
     n_value: int
     vmode: int
+    rj_mode: int = 0                      # 0 none, 1 attention norms, 2 both norms
+    rj_coef: Optional[np.ndarray] = None  # [sites, 5] fp16
 
 
 def prepare(state: Dict[str, np.ndarray]) -> Weights:
@@ -130,7 +132,10 @@ def prepare(state: Dict[str, np.ndarray]) -> Weights:
     emb = {k: f16(s[k + ".weight"]) for k in
            ("emb_square", "emb_type_special", "emb_color_turn", "emb_clock", "emb_rep")}
     vmode = int(s["value_mode"]) if "value_mode" in s else 0
-    return Weights(layers, emb, f16(s["norm_f.weight"]), f16(s["norm_f.bias"]), head, nv, vmode)
+    rj_mode = int(s["reinject_mode"]) if "reinject_mode" in s else 0
+    rj_coef = f16(s["reinject_c"]) if rj_mode else None
+    return Weights(layers, emb, f16(s["norm_f.weight"]), f16(s["norm_f.bias"]), head, nv, vmode,
+                   rj_mode, rj_coef)
 
 
 # ---------------------------------------------------------------------------
@@ -152,6 +157,37 @@ def embed(w: Weights, boards: np.ndarray, control: np.ndarray, rep: np.ndarray):
     x = add_f16(x, w.emb["emb_color_turn"][ct])
     x = add_f16(x, per_board[:, None, :])
     return x, ((wd >> 11) & 1) == 0
+
+
+def fma_f16(a, b, c) -> np.ndarray:
+    """fp16 fused multiply-add, rounded once (float64 holds a*b + c exactly)."""
+    return (np.asarray(a).astype(np.float64) * np.asarray(b).astype(np.float64)
+            + np.asarray(c).astype(np.float64)).astype(F16)
+
+
+def reinject(w: Weights, x16: np.ndarray, boards, control, rep, site: int) -> np.ndarray:
+    """What a block's LayerNorm is given under per-layer input re-injection:
+    ``x + sum_k c[site, k] * E_k`` in the reference kernel's fp16 order
+    (csrc/encoder.cu:439-583): ``pb = fma(c_clk, clock, c_rep * rep)``,
+    ``cs = fma(c_ct, color_turn[slot colour], pb)``, then per token
+    ``fma(c_ts, type_special, fma(c_sq, square, x)) + cs``.  The colour row is chosen by the
+    slot index (0-15 white, 16-31 black), not by the decoded word."""
+    n = boards.shape[0]
+    c = w.rj_coef[site]
+    wd = boards.astype(np.int64) & 0xFFFF
+    ctl = control.astype(np.int64)
+    stm = (ctl < 0).astype(np.int64)
+    sq = wd & 63
+    ts = np.minimum(((wd >> 6) & 7) * 2 + ((wd >> 9) & 1), N_TYPE_SPECIAL - 1)
+    clk = np.clip(np.abs(ctl) - 1, 0, N_CLOCK - 1)
+    rp = np.minimum(rep.astype(np.int64), N_REP - 1)
+    slot_col = (np.arange(T) >= T // 2).astype(np.int64)
+    pb = fma_f16(c[3], w.emb["emb_clock"][clk], (c[4].astype(np.float64)
+                                                 * w.emb["emb_rep"][rp].astype(np.float64)).astype(F16))
+    cs = fma_f16(c[2], w.emb["emb_color_turn"][slot_col[None, :] * 2 + stm[:, None]], pb[:, None, :])
+    t = fma_f16(c[0], w.emb["emb_square"][sq], x16.reshape(n, T, D))
+    t = fma_f16(c[1], w.emb["emb_type_special"][ts], t)
+    return add_f16(t, cs).reshape(n * T, D)
 
 
 def _seq_sum(a: np.ndarray) -> np.ndarray:
@@ -269,7 +305,8 @@ def forward(w: Weights, boards, control, rep, legal=None, trace: Optional[Trace]
 
     for li, lw in enumerate(w.layers):
         first = li == 0 and trace is not None
-        xn = layernorm(x)
+        site1 = li * 2 if w.rj_mode == 2 else li
+        xn = layernorm(reinject(w, x, boards, control, rep, site1) if w.rj_mode else x)
         if first:
             trace.stages[1] = xn.reshape(n, T, D).copy()
         qa, sa = quantise_rows(xn)
@@ -292,7 +329,7 @@ def forward(w: Weights, boards, control, rep, legal=None, trace: Optional[Trace]
             trace.by_layer[(li, 2)] = x.reshape(n, T, D).copy()
         if first:
             trace.stages[2] = x.reshape(n, T, D).copy()
-        xn = layernorm(x)
+        xn = layernorm(reinject(w, x, boards, control, rep, li * 2 + 1) if w.rj_mode == 2 else x)
         if first:
             trace.stages[3] = xn.reshape(n, T, D).copy()
         qa, sa = quantise_rows(xn)

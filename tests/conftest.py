@@ -11,6 +11,8 @@ GOLDEN = os.path.join(ROOT, "tests", "golden")
 
 WEIGHT_SETS = {"A": dict(seed=0, std=0.02, perturb_norms=False),
                "B": dict(seed=0, std=None, perturb_norms=True)}
+#: Per-layer input re-injection at both norms with nonzero coefficients.
+REINJECT_SET = dict(seed=7, std=None, perturb_norms=True, reinject="both")
 
 
 def pytest_configure(config):

@@ -15,6 +15,8 @@ next to this script:
 * ``ref_outputs_A.npz``, ``ref_outputs_B.npz`` -- for two seeded weight sets, the
   reference network's fp32 outputs, its int8-emulated outputs, its fp16 embedding and
   digests of its folded + quantised weights;
+* ``ref_outputs_C.npz`` -- the reference fp32 network's outputs for a network with per-layer
+  input re-injection at both norms and nonzero coefficients;
 * ``scheme_kats.npz`` -- known answers of the reference's int8 scheme functions.
 
 The fixtures are what ``tests/test_oracle_golden.py`` pins the CPU oracle against; the
@@ -150,6 +152,20 @@ def main() -> int:
         out["folded_b_qkv"] = np.stack(fb_qkv)
         out["folded_b_ff1"] = np.stack(fb_ff1)
         np.savez_compressed(os.path.join(HERE, f"ref_outputs_{name}.npz"), **out)
+
+    # per-layer input re-injection (both norms), nonzero coefficients: fp32 reference outputs
+    print("weight set C (re-injection)", flush=True)
+    kw = dict(seed=7, std=None, perturb_norms=True, reinject="both")
+    state = seeded_state(**kw)
+    net = RefNet(reinject="both").eval()
+    net.load_state_dict(state, strict=True)
+    with torch.no_grad():
+        p, pr, v = net(boards[:32], control[:32], rep[:32])
+    np.savez_compressed(os.path.join(HERE, "ref_outputs_C.npz"),
+                        state_sha=sha(np.concatenate([state[k].numpy().reshape(-1).astype(np.float32)
+                                                      for k in sorted(state)])),
+                        fp32_policy=p.numpy().astype(np.float16), fp32_promo=pr.numpy().astype(np.float16),
+                        fp32_value=v.numpy().astype(np.float32))
 
     print("scheme known answers", flush=True)
     g = torch.Generator().manual_seed(1234)

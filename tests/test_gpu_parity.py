@@ -353,3 +353,44 @@ def test_phase_profile_hooks(encoders, pos256):
     assert set(prof) >= {"layernorm_quantise", "wait_mma_ff1", "attention", "ff1_epilogue", "heads"}
     assert all(v >= 0 for v in prof.values()) and prof["ff1_epilogue"] > 0 and prof["attention"] > 0
     enc.check_status()
+
+
+@pytest.mark.parametrize("mode", ["ln1", "both"])
+def test_reinjection(mode, pos256):
+    """Per-layer input re-injection (the reference's tests/test_b2.py:734-754): layer-0 LN1
+    output and Q/K/V bit-identical to the oracle, logits within the relative tolerance, and with
+    all-zero coefficients bit-identical to the same network without injection, odd batch."""
+    from brokefish_b200.nn import encoder_impl
+    from brokefish_b200.nn.model import net_for_state, seeded_state
+    st = seeded_state(seed=7, std=None, perturb_norms=True, reinject=mode)
+    net = net_for_state(st).eval()
+    net.load_state_dict(st)
+    enc = encoder_impl("cuda")(net)
+    assert enc.rj_mode == {"ln1": 1, "both": 2}[mode]
+    w = aligned_oracle({"X": O.prepare({k: v.numpy() for k, v in st.items()})}, "X", enc)
+    sl = slice(0, 48)
+    tr = O.Trace()
+    opol, _, oval = O.forward(w, pos256["boards"][sl], pos256["control"][sl], pos256["rep"][sl], trace=tr)
+    for stage in (1, 5, 6, 7):
+        got = enc.forward_stage(*inputs(pos256, sl), stage).cpu().numpy()
+        assert np.array_equal(got.view(np.uint16), tr.stages[stage].view(np.uint16)), stage
+    pol, _, val = (t.cpu().numpy() for t in enc.forward_full(*inputs(pos256, sl)))
+    assert np.abs(pol.astype(np.float32) - opol.astype(np.float32)).max() <= logit_tol("B", opol)
+    assert np.abs(val - oval).max() <= 3e-2
+    enc.check_status()
+    enc.close()
+    # zero coefficients == no injection, bit for bit, on an odd batch
+    st0 = {k: (torch.zeros_like(v) if k == "reinject_c" else v) for k, v in st.items()}
+    net0 = net_for_state(st0).eval()
+    net0.load_state_dict(st0)
+    plain_state = {k: v for k, v in st0.items() if not k.startswith("reinject")}
+    plain = net_for_state(plain_state).eval()
+    plain.load_state_dict(plain_state)
+    e0, e1 = encoder_impl("cuda")(net0), encoder_impl("cuda")(plain)
+    odd = slice(3, 3 + 131)
+    a = [t.cpu().numpy().copy() for t in e0.forward_full(*inputs(pos256, odd))]
+    b = [t.cpu().numpy().copy() for t in e1.forward_full(*inputs(pos256, odd))]
+    for x, y in zip(a, b):
+        assert np.array_equal(x.view(np.uint8), y.view(np.uint8))
+    e0.close()
+    e1.close()

@@ -79,7 +79,10 @@ def test_state_dict_round_trip_and_variants():
     with pytest.raises(ValueError):
         BrokefishNet(n_value=2)
     with pytest.raises(NotImplementedError):
-        BrokefishNet(reinject="ln1")
+        BrokefishNet(rule_features=True)
+    rj = seeded_state(seed=3, reinject="both")
+    assert rj["reinject_c"].shape == (16, 5) and int(rj["reinject_mode"]) == 2
+    assert net_for_state(rj).reinject == "both" and net_for_state(rj).n_sites == 16
 
 
 def test_scheme_functions_against_reference_answers():

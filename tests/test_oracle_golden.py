@@ -137,3 +137,31 @@ def test_fp32_port_matches_reference_fp32(name, states, pos256):
     assert np.abs(p.numpy() - g["fp32_policy"]).max() < 1e-4
     assert np.abs(pr.numpy() - g["fp32_promo"]).max() < 1e-4
     assert np.abs(v.numpy() - g["fp32_value"]).max() < 1e-4
+
+
+def test_reinjection_against_reference_fp32(pos256):
+    """A re-injecting network (both norms, nonzero coefficients): the oracle's int8 path
+    against the reference's fp32 outputs at the reference's 8 % bar; with all-zero
+    coefficients the injecting path is bit-identical to the plain one."""
+    import copy
+    from conftest import REINJECT_SET
+    from brokefish_b200.nn.model import seeded_state
+    g = np.load(os.path.join(GOLDEN, "ref_outputs_C.npz"))
+    st = seeded_state(**REINJECT_SET)
+    flat = np.concatenate([st[k].numpy().reshape(-1).astype(np.float32) for k in sorted(st)])
+    assert sha(flat) == str(g["state_sha"])
+    w = O.prepare({k: v.numpy() for k, v in st.items()})
+    assert w.rj_mode == 2 and w.rj_coef.shape == (16, 5)
+    n = g["fp32_policy"].shape[0]
+    pol, pro, val = O.forward(w, pos256["boards"][:n], pos256["control"][:n], pos256["rep"][:n])
+    top = np.abs(g["fp32_policy"].astype(np.float32)).max()
+    assert np.abs(pol.astype(np.float32) - g["fp32_policy"].astype(np.float32)).max() <= 0.08 * top
+    assert np.abs(val - g["fp32_value"]).max() <= 0.08
+    plain = copy.deepcopy(w)
+    plain.rj_mode = 0
+    differs = O.forward(plain, pos256["boards"][:4], pos256["control"][:4], pos256["rep"][:4])[0]
+    assert not np.array_equal(differs, pol[:4])              # the injection does something
+    zero = copy.deepcopy(w)
+    zero.rj_coef = np.zeros_like(w.rj_coef)
+    same = O.forward(zero, pos256["boards"][:4], pos256["control"][:4], pos256["rep"][:4])[0]
+    assert np.array_equal(same.view(np.uint16), differs.view(np.uint16))

@@ -51,9 +51,10 @@ def test_blob_layout_decodes_back(nets, folded):
     net, fl = nets["B"], folded["B"]
     blob = pack.pack_blob(net)
     magic, ver, nl, nv, vm, eps = struct.unpack_from("<IIIIIf", blob, 0)
-    assert (magic, ver, nl, nv, vm) == (pack.MAGIC, 1, 8, 1, 0) and abs(eps - 1e-5) < 1e-12
-    offs = struct.unpack_from("<9Q", blob, 32)
-    off_w, bytes_w, off_lp, bytes_lp, off_emb, bytes_emb, off_tail, bytes_tail, total = offs
+    assert (magic, ver, nl, nv, vm) == (pack.MAGIC, 2, 8, 1, 0) and abs(eps - 1e-5) < 1e-12
+    offs = struct.unpack_from("<11Q", blob, 32)
+    off_w, bytes_w, off_lp, bytes_lp, off_emb, bytes_emb, off_tail, bytes_tail, off_rj, bytes_rj, total = offs
+    assert bytes_rj == 0 and bytes_tail == 2560
     assert total == blob.size and bytes_w == 8 * 786432 + 49152 and bytes_lp == 8 * 4736
     assert all(o % 256 == 0 for o in (off_w, off_lp, off_emb, off_tail))
     # layer 3, FFN unit 9 = ff2, hidden chunk 1, output half 1; its K-slab 1
