@@ -651,6 +651,70 @@ __device__ __forceinline__ void ffn_block(RowCtx& c, const Params& p, const Laye
     }
 }
 
+// The "prenorm" value head (csrc/encoder.cu:1008-1057; nn/model.py:576-584): the raw residual
+// stream is averaged over the board's live tokens, that one vector goes through the final
+// LayerNorm (with affine) and is dotted with the value rows, all in fp32.  Written as one pass
+// over this thread's 64 columns: with a = the column means, the k-th logit is
+// rstd * (sum a*g*w_k - mean * sum g*w_k) + sum b*w_k, so no vector has to be kept.
+// Every thread of the board returns the same three logits.
+__device__ __forceinline__ void prenorm_value(RowCtx& c, const Params& p, uint32_t alive, float (&logit)[3]) {
+    const bool live = (alive >> c.lane) & 1u;
+    const int nlive = __popc(alive);
+    const float inv_live = 1.0f / static_cast<float>(nlive > 0 ? nlive : 1);
+    float s = 0.f, q = 0.f, s1[3] = {0.f, 0.f, 0.f}, s2[3] = {0.f, 0.f, 0.f}, s3[3] = {0.f, 0.f, 0.f};
+#pragma unroll 1
+    for (int u = 0; u < 2; ++u) {
+        uint32_t x[16];
+        tmem_ld16(c.tm + TM_X + 64 * u + 16 * c.qt, x);
+        tmem_wait_ld();
+        const int col = 128 * u + 32 * c.qt;
+#pragma unroll 1
+        for (int i = 0; i < 16; ++i) {
+            const float2 f = __half22float2(as_h2(x[i]));
+            float a0 = live ? f.x : 0.f, a1 = live ? f.y : 0.f;
+#pragma unroll
+            for (int off = 16; off; off >>= 1) {
+                a0 += __shfl_xor_sync(0xffffffffu, a0, off);
+                a1 += __shfl_xor_sync(0xffffffffu, a1, off);
+            }
+            a0 *= inv_live; a1 *= inv_live;
+            s += a0 + a1;
+            q += a0 * a0 + a1 * a1;
+            const float2 g = __half22float2(as_h2(__ldg(reinterpret_cast<const uint32_t*>(p.tail + col) + i)));
+            const float2 b = __half22float2(as_h2(__ldg(reinterpret_cast<const uint32_t*>(p.tail + kD + col) + i)));
+#pragma unroll
+            for (int k = 0; k < 3; ++k) {
+                const float2 w = __half22float2(
+                    as_h2(__ldg(reinterpret_cast<const uint32_t*>(p.tail + 2 * kD + k * kD + col) + i)));
+                s1[k] += a0 * g.x * w.x + a1 * g.y * w.y;
+                s2[k] += g.x * w.x + g.y * w.y;
+                s3[k] += b.x * w.x + b.y * w.y;
+            }
+        }
+    }
+    float4 all[4];
+    exchange4(c, make_float4(s, q, 0.f, 0.f), all);
+    const float tot = (all[0].x + all[1].x) + (all[2].x + all[3].x);
+    const float totq = (all[0].y + all[1].y) + (all[2].y + all[3].y);
+    const float mean = tot * (1.0f / 256.0f);
+    const float rstd = rsqrtf(fmaxf(totq * (1.0f / 256.0f) - mean * mean, 0.f) + p.eps);
+    float t1[3], t2[3], t3[3];
+    exchange4(c, make_float4(s1[0], s1[1], s1[2], 0.f), all);
+    t1[0] = (all[0].x + all[1].x) + (all[2].x + all[3].x);
+    t1[1] = (all[0].y + all[1].y) + (all[2].y + all[3].y);
+    t1[2] = (all[0].z + all[1].z) + (all[2].z + all[3].z);
+    exchange4(c, make_float4(s2[0], s2[1], s2[2], 0.f), all);
+    t2[0] = (all[0].x + all[1].x) + (all[2].x + all[3].x);
+    t2[1] = (all[0].y + all[1].y) + (all[2].y + all[3].y);
+    t2[2] = (all[0].z + all[1].z) + (all[2].z + all[3].z);
+    exchange4(c, make_float4(s3[0], s3[1], s3[2], 0.f), all);
+    t3[0] = (all[0].x + all[1].x) + (all[2].x + all[3].x);
+    t3[1] = (all[0].y + all[1].y) + (all[2].y + all[3].y);
+    t3[2] = (all[0].z + all[1].z) + (all[2].z + all[3].z);
+#pragma unroll
+    for (int k = 0; k < 3; ++k) logit[k] = rstd * (t1[k] - mean * t2[k]) + t3[k];
+}
+
 template <bool kDbg, bool kRJ>
 __device__ __forceinline__ void row_warps_tile(RowCtx& c, const Params& p, int tile) {
     const int board = tile * 4 + c.q;
@@ -737,6 +801,8 @@ __device__ __forceinline__ void row_warps_tile(RowCtx& c, const Params& p, int t
 
     // ---- heads: fp16 GEMM [128 x 256] x [96 x 256]^T, fp32 accumulate, rounded to fp16
     //      (encoder.cu:894-1079; the reference accumulates in fp16) -------------------------
+    float pre[3] = {0.f, 0.f, 0.f};
+    if (p.vmode == 2) prenorm_value(c, p, c.valid ? alive : 0xffffffffu, pre);
     row_wait_acc<kDbg>(c, 0, PH_LN);
     {
         uint32_t acc[16], aux[16];
@@ -778,7 +844,8 @@ __device__ __forceinline__ void row_warps_tile(RowCtx& c, const Params& p, int t
                 const float inv = 1.0f / static_cast<float>(nlive > 0 ? nlive : 1);
                 a *= inv; b *= inv; d *= inv;
             }
-            const bool writer = p.vmode == 1 ? c.lane == 0 : c.lane == (ctl < 0 ? 31 : 15);
+            if (p.vmode == 2) { a = pre[0]; b = pre[1]; d = pre[2]; }
+            const bool writer = p.vmode != 0 ? c.lane == 0 : c.lane == (ctl < 0 ? 31 : 15);
             if (writer && c.valid && p.value != nullptr) {
                 float v;
                 if (p.n_value == 1) {
@@ -1174,7 +1241,7 @@ int bf_create(const void* blob, size_t blob_bytes, int device, bf_handle** out) 
         hdr.off_rj + hdr.bytes_rj > blob_bytes)
         return fail(BF_EINVAL, "blob section outside the blob");
     if (hdr.n_value != 1 && hdr.n_value != 3) return fail(BF_EINVAL, "n_value must be 1 or 3");
-    if (hdr.vmode > 1) return fail(BF_ENOTSUP, "the prenorm value head is not built");
+    if (hdr.vmode > 2) return fail(BF_EINVAL, "unknown value mode");
     cudaDeviceProp prop;
     BF_CUDA(cudaGetDeviceProperties(&prop, device));
     if (prop.major != 10)

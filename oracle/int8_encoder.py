@@ -366,7 +366,16 @@ def forward(w: Weights, boards, control, rep, legal=None, trace: Optional[Trace]
         raw = (vcols * m[:, :, None]).sum(axis=1, dtype=F32) / np.maximum(
             m.sum(axis=1, dtype=F32), F32(1))[:, None]
     else:
-        raise NotImplementedError("the prenorm value head is not restated here")
+        # "prenorm": mean of the raw residual over live tokens, final LayerNorm with affine,
+        # value rows, all fp32 (csrc/encoder.cu:1008-1057; nn/model.py:576-584)
+        m = alive.astype(F32)
+        xr = x.reshape(n, T, D).astype(F32)
+        pooled = (xr * m[:, :, None]).sum(axis=1, dtype=F32) / np.maximum(m.sum(axis=1, dtype=F32), F32(1))[:, None]
+        mu = pooled.mean(axis=1, dtype=F32)
+        var = np.maximum((pooled * pooled).mean(axis=1, dtype=F32) - mu * mu, F32(0))
+        rs = (F32(1) / np.sqrt(var + EPS)).astype(F32)
+        nv = ((pooled - mu[:, None]) * rs[:, None] * w.lnf_w.astype(F32)[None, :] + w.lnf_b.astype(F32)[None, :])
+        raw = (nv.astype(F32) @ w.head[68:68 + w.n_value].astype(F32).T).astype(F32)
     if w.n_value == 1:
         value = np.tanh(raw[:, 0]).astype(F32)
     else:

@@ -312,7 +312,7 @@ def test_value_head_variants(pos256):
     """Win/draw/loss rows and the pooled head (the reference's tests/test_b2.py:404-690)."""
     from brokefish_b200.nn import encoder_impl
     from brokefish_b200.nn.model import BrokefishNet, seeded_state
-    for nv, head in ((3, "king"), (1, "pooled"), (3, "pooled")):
+    for nv, head in ((3, "king"), (1, "pooled"), (3, "pooled"), (1, "prenorm"), (3, "prenorm")):
         st = seeded_state(seed=5, std=None, perturb_norms=True, n_value=nv, value_head=head)
         net = BrokefishNet(n_value=nv, value_head=head).eval()
         net.load_state_dict(st)
