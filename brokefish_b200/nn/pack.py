@@ -17,7 +17,7 @@ What happens here, once per weight snapshot (the reference does the same work in
 Blob layout (all offsets 256-byte aligned, little endian; mirrored by
 ``include/brokefish_b200.h``):
 
-    header   256 B   magic, version, n_layers, n_value, vmode, eps, rj_mode, section table
+    header   256 B   magic, version, n_layers, n_value, vmode, eps, rj_mode, quant, section table
                      (offset, bytes of wstream, lparams, emb, tail, rj), total bytes
     wstream  n_layers * 786432 + 49152 B
                      per layer 8 QKV stages [192 rows x 128 B], then 36 stages
@@ -50,7 +50,7 @@ import torch
 
 from brokefish_b200.nn.model import (BrokefishNet, EMB_TABLES, N_POLICY, N_PROMO,
                                      REINJECT_MODE_ID, VALUE_MODE_ID)
-from brokefish_b200.nn.quant import quantise_weights_int8_bytes
+from brokefish_b200.nn.quant import Q_MAX, quantise_weights_bytes, quantise_weights_int8_bytes
 
 MAGIC = 0x38424642          # "BFB8"
 VERSION = 2
@@ -59,6 +59,10 @@ D, DFF, H, DH, T = 256, 1024, 8, 32, 32
 NHEAD = 96                   # head matrix rows: 64 policy, 4 promo, 1-3 value, zero pad
 VALUE_ROW = N_POLICY + N_PROMO
 LAYER_STREAM_BYTES = 786432
+LAYER_STREAM_BYTES_E4M3 = 1048576
+#: Arithmetic of a blob, by the reference's kernel mode number: 3 = int8 on all four
+#: matmuls, 1 = e4m3 on the two FFN matmuls with fp16 QKV and out-projection.
+QUANT_INT8, QUANT_E4M3 = 3, 1
 HEAD_STREAM_BYTES = 4 * NHEAD * 128
 LPARAM_STRIDE = 4736
 LP_SW_QKV, LP_SW_O, LP_SW_FF1, LP_SW_FF2 = 0, 24, 32, 64
@@ -101,15 +105,21 @@ def sw128_image(tile: np.ndarray) -> np.ndarray:
 
 @dataclass
 class FoldedLayer:
-    """One layer after folding and quantisation (natural row order, no layout yet)."""
+    """One layer after folding and quantisation (natural row order, no layout yet).  In the
+    e4m3 arithmetic ``q_qkv`` / ``q_o`` are the fp16 matrices viewed as bytes ``[N, 512]``
+    and their scales are ones."""
     q_qkv: np.ndarray; s_qkv: np.ndarray; b_qkv: np.ndarray     # [768,256] u8, [6], [768] f16
     q_o: np.ndarray; s_o: np.ndarray; b_o: np.ndarray
     q_ff1: np.ndarray; s_ff1: np.ndarray; b_ff1: np.ndarray
     q_ff2: np.ndarray; s_ff2: np.ndarray; b_ff2: np.ndarray
 
 
-def fold_and_quantise(net: BrokefishNet) -> List[FoldedLayer]:
-    """The per-layer folded s8 matrices, scales and fp16 biases."""
+def fold_and_quantise(net: BrokefishNet, fmt: str = "int8") -> List[FoldedLayer]:
+    """The per-layer folded matrices, scales and fp16 biases.  ``fmt="int8"``: all four
+    matrices s8.  ``fmt="e4m3"``: the two FFN matrices e4m3 with ``amax/8`` scales, QKV and
+    out-projection fp16 (brokefish/nn/cuda_impl.py:303-337)."""
+    if fmt not in ("int8", "e4m3"):
+        raise ValueError(f"fmt must be 'int8' or 'e4m3', got {fmt!r}")
     out = []
     scale = DH ** -0.5
     for lay in net.encoder.layers:
@@ -123,7 +133,14 @@ def fold_and_quantise(net: BrokefishNet) -> List[FoldedLayer]:
         mats = {}
         for name, w in (("qkv", w_qkv), ("o", lay.self_attn.out_proj.weight.detach()),
                         ("ff1", w_ff1), ("ff2", lay.linear2.weight.detach())):
-            qb, sc = quantise_weights_int8_bytes(w.float())
+            if fmt == "int8":
+                qb, sc = quantise_weights_int8_bytes(w.float())
+            elif name in ("ff1", "ff2"):
+                qb, sc = quantise_weights_bytes(w.float(), Q_MAX, tile_k=w.shape[1])
+                sc = sc.reshape(-1)
+            else:
+                qb = w.float().half().contiguous().view(torch.uint8).reshape(w.shape[0], -1)
+                sc = torch.ones(w.shape[0] // 128)
             mats[name] = (qb.cpu().numpy(), sc.cpu().numpy().astype(np.float32))
 
         def f16(v):
@@ -149,12 +166,13 @@ def head_matrix(net: BrokefishNet) -> np.ndarray:
 def _layer_stream(fl: FoldedLayer) -> np.ndarray:
     parts = []
     rows = qkv_chunk_rows()
+    slabs = fl.q_qkv.shape[1] // 128          # 2 for s8 (K = 256 bytes), 4 for fp16 (512 bytes)
     for j in range(4):
-        chunk = fl.q_qkv[rows[j]]                                   # [192, 256]
-        for s in range(2):
+        chunk = fl.q_qkv[rows[j]]                                   # [192, K bytes]
+        for s in range(slabs):
             parts.append(sw128_image(np.ascontiguousarray(chunk[:, 128 * s:128 * s + 128])))
     for u in range(2):
-        for s in range(2):
+        for s in range(slabs):
             parts.append(sw128_image(np.ascontiguousarray(
                 fl.q_o[128 * u:128 * u + 128, 128 * s:128 * s + 128])))
     for kind, c, j in FFN_UNITS:
@@ -167,7 +185,7 @@ def _layer_stream(fl: FoldedLayer) -> np.ndarray:
                                256 * c + 128 * s:256 * c + 128 * s + 128]
             parts.append(sw128_image(np.ascontiguousarray(blk)))
     stream = np.concatenate(parts)
-    assert stream.size == LAYER_STREAM_BYTES
+    assert stream.size == (LAYER_STREAM_BYTES if slabs == 2 else LAYER_STREAM_BYTES_E4M3)
     return stream
 
 
@@ -189,8 +207,10 @@ def _align(n: int, a: int = 256) -> int:
     return (n + a - 1) // a * a
 
 
-def pack_blob(net: BrokefishNet) -> np.ndarray:
-    """The whole device blob for ``net`` as a ``uint8`` array."""
+def pack_blob(net: BrokefishNet, fmt: str = "int8") -> np.ndarray:
+    """The whole device blob for ``net`` as a ``uint8`` array, in the int8 arithmetic or in
+    the e4m3-FFN arithmetic (in which a layer's stream is 16 QKV stages and 8 out-projection
+    stages of fp16 followed by the 32 FFN stages of e4m3 bytes: 1,048,576 B per layer)."""
     if (net.d_model, len(net.encoder.layers)) != (D, net.n_layers):
         raise ValueError("unexpected network shape")
     first = net.encoder.layers[0]
@@ -200,7 +220,9 @@ def pack_blob(net: BrokefishNet) -> np.ndarray:
             f"kernel is compiled for d_model={D}, d_ff={DFF}, heads={H}; got "
             f"{first.self_attn.embed_dim}, {first.linear1.out_features}, "
             f"{first.self_attn.num_heads}")
-    layers = fold_and_quantise(net)
+    layers = fold_and_quantise(net, fmt)
+    if fmt == "e4m3" and getattr(net, "reinject", "none") != "none":
+        raise NotImplementedError("input re-injection is built for the int8 arithmetic only")
     head = head_matrix(net).view(np.uint8).reshape(NHEAD, 512)
     wstream = np.concatenate(
         [_layer_stream(fl) for fl in layers]
@@ -229,7 +251,8 @@ def pack_blob(net: BrokefishNet) -> np.ndarray:
     total = cur
     vmode = VALUE_MODE_ID.get(getattr(net, "value_head", "king"), 0)
     header = struct.pack("<IIIIIfII", MAGIC, VERSION, len(layers),
-                         int(net.value.weight.shape[0]), vmode, float(first.norm1.eps), rj_mode, 0)
+                         int(net.value.weight.shape[0]), vmode, float(first.norm1.eps), rj_mode,
+                         QUANT_INT8 if fmt == "int8" else QUANT_E4M3)
     for off, sec in zip(offs, sections):
         header += struct.pack("<QQ", off, sec.size)
     header += struct.pack("<Q", total)

@@ -24,6 +24,15 @@ Q_MAX_S8 = 127.0
 Q_MAX_U8 = 255.0
 
 
+#: e4m3 as NVIDIA defines it (no infinities, maximum 448).
+E4M3 = torch.float8_e4m3fn
+E4M3_MAX = 448.0
+#: What a row's (or a weight block's) maximum is mapped to in the e4m3 arithmetic.  The
+#: reference fixes 8 because its kernel accumulates 256 products in fp16; the value is kept so
+#: that both implementations quantise to the same grid (brokefish/nn/quant.py:97-110).
+Q_MAX = 8.0
+
+
 def _scale_for(amax: torch.Tensor, q_max: float) -> torch.Tensor:
     """``amax / q_max`` in fp32, with 1 for an all-zero group so nothing divides by 0."""
     one = torch.ones((), dtype=amax.dtype, device=amax.device)
@@ -70,3 +79,20 @@ def int8_linear(x: torch.Tensor, w: torch.Tensor, bias: Optional[torch.Tensor],
     if bias is not None:
         y = y + bias.float()
     return y.reshape(*lead, w.shape[0]).to(x.dtype)
+
+
+def quantise_weights_bytes(w: torch.Tensor, q_max: float = Q_MAX, tile_k: Optional[int] = None,
+                           block_n: int = BLOCK_N):
+    """``[N, K]`` -> ``(e4m3 bytes [N, K] uint8, scale [N // block_n, K // tile_k] fp32)``.
+
+    One scale per ``block_n`` output rows and ``tile_k`` reduction columns (``tile_k=None``:
+    the whole of K, which is what the evaluator's single descale needs); values are divided by
+    the scale, clamped to +-448 and rounded to e4m3 (brokefish/nn/quant.py:208-224)."""
+    n, k = w.shape
+    tile_k = k if tile_k is None else tile_k
+    if n % block_n or k % tile_k:
+        raise ValueError(f"weight {tuple(w.shape)} does not tile into {block_n}x{tile_k} blocks")
+    blocks = w.float().reshape(n // block_n, block_n, k // tile_k, tile_k)
+    scale = _scale_for(blocks.abs().amax(dim=(1, 3), keepdim=True), q_max)
+    q = (blocks / scale).clamp(-E4M3_MAX, E4M3_MAX).to(E4M3).reshape(n, k)
+    return q.view(torch.uint8), scale.reshape(n // block_n, k // tile_k).contiguous()

@@ -64,6 +64,35 @@ def add_f16(a: np.ndarray, b: np.ndarray) -> np.ndarray:
 # weights
 # ---------------------------------------------------------------------------
 
+def round_e4m3(x) -> np.ndarray:
+    """Round to the e4m3 grid (4 exponent bits, bias 7, 3 mantissa bits, no infinities),
+    nearest-even, saturating at +-448; returned as float32 values."""
+    x = np.asarray(x).astype(np.float64)
+    a = np.minimum(np.abs(x), 448.0)
+    e = np.maximum(np.floor(np.log2(np.maximum(a, 2.0 ** -9))), -6.0)
+    step = 2.0 ** (e - 3.0)
+    return (np.sign(x) * np.rint(a / step) * step).astype(F32)
+
+
+def decode_e4m3(b) -> np.ndarray:
+    """e4m3 bytes -> float32 values."""
+    b = np.asarray(b).astype(np.int64)
+    e, m = (b >> 3) & 15, b & 7
+    mag = np.where(e == 0, m * 2.0 ** -9, (1.0 + m / 8.0) * 2.0 ** (e - 7.0))
+    return np.where(b >> 7, -mag, mag).astype(F32)
+
+
+def quantise_weights_e4m3(w: np.ndarray):
+    """``[N, K]`` fp32 -> ``(values on the e4m3 grid [N, K] fp32, scale [N/128] fp32)``: one
+    scale ``amax/8`` per 128 output rows over all of K (brokefish/nn/quant.py:208-224 with
+    ``q_max=8, tile_k=K``; brokefish/nn/cuda_impl.py:323-335)."""
+    n, k = w.shape
+    b = w.astype(F32).reshape(n // 128, 128 * k)
+    amax = np.abs(b).max(axis=1)
+    scale = np.where(amax > 0, amax / F32(8.0), F32(1.0)).astype(F32)
+    return round_e4m3((b / scale[:, None]).astype(F32)).reshape(n, k), scale
+
+
 def quantise_weights_s8(w: np.ndarray):
     """``[N, K]`` fp32 -> ``(q [N, K] int8, scale [N/128] fp32)``; one scale per 128
     output rows over all of K, ``amax/127``, round-half-even, clamp +-127."""
@@ -93,10 +122,15 @@ class Weights:
     vmode: int
     rj_mode: int = 0                      # 0 none, 1 attention norms, 2 both norms
     rj_coef: Optional[np.ndarray] = None  # [sites, 5] fp16
+    #: "int8": the four matmuls in s8/u8.  "e4m3": the two FFN matmuls in e4m3 (q_* hold grid
+    #: values as fp32), QKV and out-projection in fp16 (q_* hold the fp16 matrices, scales 1).
+    fmt: str = "int8"
 
 
-def prepare(state: Dict[str, np.ndarray]) -> Weights:
+def prepare(state: Dict[str, np.ndarray], fmt: str = "int8") -> Weights:
     """Fold, quantise and round a fp32 ``state_dict`` (numpy arrays)."""
+    if fmt not in ("int8", "e4m3"):
+        raise ValueError(fmt)
     s = {k: np.asarray(v) for k, v in state.items()}
     n_layers = 1 + max(int(k.split(".")[2]) for k in s if k.startswith("encoder.layers."))
     layers = []
@@ -116,10 +150,16 @@ def prepare(state: Dict[str, np.ndarray]) -> Weights:
         g2, e2 = s[p + "norm2.weight"].astype(F32), s[p + "norm2.bias"].astype(F32)
         b_ff1 = (b_ff1.astype(np.float64) + w_ff1.astype(np.float64) @ e2.astype(np.float64)).astype(F32)
         w_ff1 = w_ff1 * g2[None, :]
-        q_qkv, s_qkv = quantise_weights_s8(w_qkv)
-        q_o, s_o = quantise_weights_s8(s[p + "self_attn.out_proj.weight"])
-        q_ff1, s_ff1 = quantise_weights_s8(w_ff1)
-        q_ff2, s_ff2 = quantise_weights_s8(s[p + "linear2.weight"])
+        if fmt == "int8":
+            q_qkv, s_qkv = quantise_weights_s8(w_qkv)
+            q_o, s_o = quantise_weights_s8(s[p + "self_attn.out_proj.weight"])
+            q_ff1, s_ff1 = quantise_weights_s8(w_ff1)
+            q_ff2, s_ff2 = quantise_weights_s8(s[p + "linear2.weight"])
+        else:
+            q_qkv, s_qkv = f16(w_qkv), np.ones(6, dtype=F32)
+            q_o, s_o = f16(s[p + "self_attn.out_proj.weight"]), np.ones(2, dtype=F32)
+            q_ff1, s_ff1 = quantise_weights_e4m3(w_ff1)
+            q_ff2, s_ff2 = quantise_weights_e4m3(s[p + "linear2.weight"].astype(F32))
         layers.append(LayerW(q_qkv, s_qkv, f16(b_qkv), q_o, s_o,
                              f16(s[p + "self_attn.out_proj.bias"]),
                              q_ff1, s_ff1, f16(b_ff1), q_ff2, s_ff2,
@@ -135,7 +175,7 @@ def prepare(state: Dict[str, np.ndarray]) -> Weights:
     rj_mode = int(s["reinject_mode"]) if "reinject_mode" in s else 0
     rj_coef = f16(s["reinject_c"]) if rj_mode else None
     return Weights(layers, emb, f16(s["norm_f.weight"]), f16(s["norm_f.bias"]), head, nv, vmode,
-                   rj_mode, rj_coef)
+                   rj_mode, rj_coef, fmt)
 
 
 # ---------------------------------------------------------------------------
@@ -241,9 +281,22 @@ def quantise_rows(x16: np.ndarray, unsigned: bool = False):
     return q, sc
 
 
+def quantise_rows_e4m3(x16: np.ndarray):
+    """fp16 rows -> (values on the e4m3 grid as fp32, per-row fp32 scale ``amax/8``); the
+    scaled value is rounded to fp16 before the e4m3 conversion, as the reference's
+    quantiser does (csrc/fp8_gemm.cuh:147-208)."""
+    x = x16.astype(F32)
+    amax = np.abs(x).max(axis=1)
+    sc = np.where(amax > 0, (amax / F32(8.0)).astype(F32), F32(1.0)).astype(F32)
+    inv = (F32(1.0) / sc).astype(F32)
+    return round_e4m3((x * inv[:, None]).astype(F32).astype(F16)), sc
+
+
 def gemm_int(q_a: np.ndarray, q_w: np.ndarray) -> np.ndarray:
-    """Exact integer product ``A @ W^T`` as float32.  Every partial sum is below
-    2^24 (255 * 127 * 256 = 8.29e6), so fp32 accumulation is exact in any order."""
+    """``A @ W^T`` in float32.  For int8 operands this is the exact integer product: every
+    partial sum is below 2^24 (255 * 127 * 256 = 8.29e6), so fp32 accumulation is exact in
+    any order.  For e4m3 operands it is an fp32-accumulated product (the tensor cores'
+    summation order is not reproduced)."""
     return q_a.astype(F32) @ q_w.astype(F32).T
 
 
@@ -309,20 +362,27 @@ def forward(w: Weights, boards, control, rep, legal=None, trace: Optional[Trace]
         xn = layernorm(reinject(w, x, boards, control, rep, site1) if w.rj_mode else x)
         if first:
             trace.stages[1] = xn.reshape(n, T, D).copy()
-        qa, sa = quantise_rows(xn)
-        acc = gemm_int(qa, lw.q_qkv)
-        cap(li, "qkv", qa, acc)
-        qkv = add_f16(descale(acc, sa, lw.s_qkv).astype(F16), lw.b_qkv[None, :])
+        e4 = w.fmt == "e4m3"
+        if e4:       # fp16 QKV, fp32 accumulate (the reference accumulates in fp16)
+            qkv = add_f16((xn.astype(F32) @ lw.q_qkv.astype(F32).T).astype(F16), lw.b_qkv[None, :])
+        else:
+            qa, sa = quantise_rows(xn)
+            acc = gemm_int(qa, lw.q_qkv)
+            cap(li, "qkv", qa, acc)
+            qkv = add_f16(descale(acc, sa, lw.s_qkv).astype(F16), lw.b_qkv[None, :])
         q16, k16, v16 = (qkv[:, i * D:(i + 1) * D].reshape(n, T, D) for i in range(3))
         if first:
             trace.stages[5], trace.stages[6], trace.stages[7] = q16.copy(), k16.copy(), v16.copy()
         o = attention(q16, k16, v16, alive)
         if first:
             trace.stages[4] = o.copy()
-        qa, sa = quantise_rows(o.reshape(n * T, D))
-        acc = gemm_int(qa, lw.q_o)
-        cap(li, "out", qa, acc)
-        y = add_f16(descale(acc, sa, lw.s_o).astype(F16), lw.b_o[None, :])
+        if e4:
+            y = add_f16((o.reshape(n * T, D).astype(F32) @ lw.q_o.astype(F32).T).astype(F16), lw.b_o[None, :])
+        else:
+            qa, sa = quantise_rows(o.reshape(n * T, D))
+            acc = gemm_int(qa, lw.q_o)
+            cap(li, "out", qa, acc)
+            y = add_f16(descale(acc, sa, lw.s_o).astype(F16), lw.b_o[None, :])
         x = add_f16(x, y)
         if trace is not None:
             trace.by_layer[(li, 4)] = o.copy()
@@ -332,17 +392,19 @@ def forward(w: Weights, boards, control, rep, legal=None, trace: Optional[Trace]
         xn = layernorm(reinject(w, x, boards, control, rep, li * 2 + 1) if w.rj_mode == 2 else x)
         if first:
             trace.stages[3] = xn.reshape(n, T, D).copy()
-        qa, sa = quantise_rows(xn)
+        qa, sa = quantise_rows_e4m3(xn) if e4 else quantise_rows(xn)
         run = np.zeros((n * T, D), dtype=F16)
         for c in range(DFF // 256):
             acc = gemm_int(qa, lw.q_ff1[256 * c:256 * c + 256])
-            cap(li, f"ff1_{c}", qa, acc)
+            if not e4:
+                cap(li, f"ff1_{c}", qa, acc)
             hid = add_f16(descale(acc, sa, lw.s_ff1, n0=256 * c).astype(F16),
                           lw.b_ff1[None, 256 * c:256 * c + 256])
             hid = np.maximum(hid, F16(0))
-            qh, sh = quantise_rows(hid, unsigned=True)
+            qh, sh = quantise_rows_e4m3(hid) if e4 else quantise_rows(hid, unsigned=True)
             acc2 = gemm_int(qh, lw.q_ff2[:, 256 * c:256 * c + 256])
-            cap(li, f"ff2_{c}", qh, acc2)
+            if not e4:
+                cap(li, f"ff2_{c}", qh, acc2)
             o32 = (descale(acc2, sh, lw.s_ff2) + run.astype(F32)).astype(F32)
             run = o32.astype(F16)
         y = add_f16(run, lw.b_ff2[None, :])
