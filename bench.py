@@ -154,6 +154,8 @@ def main() -> int:
                     help="fixed number of positions per step split across the GPUs")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--sweep", action="store_true", help="print one line per batch size 1..65536 and exit")
+    ap.add_argument("--fp8", action="store_true",
+                    help="time the e4m3-FFN arithmetic instead of int8 (a separate line; not the headline)")
     args = ap.parse_args()
     rank = int(os.environ.get("RANK", "0"))
     world = int(os.environ.get("WORLD_SIZE", "1"))
@@ -189,7 +191,7 @@ def main() -> int:
     if rank == 0 or world == 1:
         net = BrokefishNet().eval()
         net.load_state_dict(seeded_state(seed=0, std=0.02))
-    ev = ShardedEvaluator(net, rank, world, local)        # one broadcast of the packed blob
+    ev = ShardedEvaluator(net, rank, world, local, fp8=args.fp8)   # one broadcast of the packed blob
     enc = ev.encoder
 
     if args.sweep:
@@ -268,7 +270,8 @@ def main() -> int:
     line = {
         "metric": METRIC, "value": value, "unit": "positions/s", "n_gpus": world,
         "steps": args.steps, "warmup": warmup, "ms_per_step": dev_ms / args.steps,
-        "higher_is_better": True, "scaling": scaling, "vs_baseline": None, "dtype": "s8",
+        "higher_is_better": True, "scaling": scaling, "vs_baseline": None,
+        "dtype": "e4m3 (FFN) + f16" if args.fp8 else "s8",
         "data": "synthetic",
         "config": {"workload": WORKLOAD, "positions_per_step": n_global, "parallelism": f"dp{world}",
                    "l2": "flushed between timed iterations (256 MiB fill)",

@@ -41,24 +41,33 @@ using namespace bfptx;
 
 constexpr int kD = 256, kDFF = 1024, kT = 32, kRows = 128;
 constexpr int kRowWarps = 16, kProducerWarp = 16, kMmaWarp = 17, kThreads = 576;
-constexpr int kLayerStreamBytes = 786432, kLparamStride = 4736;
+constexpr int kLparamStride = 4736;
 constexpr int LP_SW_QKV = 0, LP_SW_O = 24, LP_SW_FF1 = 32, LP_SW_FF2 = 64;
 constexpr int LP_B_QKV = 128, LP_B_O = 1664, LP_B_FF1 = 2176, LP_B_FF2 = 4224;
 constexpr int EMB_SQUARE = 0, EMB_TS = 64, EMB_CT = 76, EMB_CLOCK = 80, EMB_REP = 181;
 constexpr int kNClock = 101, kNRep = 3, kNTypeSpecial = 12;
 
 // ---- shared memory map (offsets from a 1024-byte aligned base) ----------------------
-constexpr uint32_t SM_A = 0;            // s8 A operand, 2 K-slabs of [128 rows][128 B]
-constexpr uint32_t SM_R = 32768;        // 64 KB: Q/K/V staging (3 x 16 KB) | hidden u8
-                                        // A operand x2 (2 x 32 KB) | fp16 head A (4 x 16 KB)
-constexpr uint32_t SM_RING = 98304;     // 112 KB weight ring: 4 x 24 KB or 7 x 16 KB
+// The front of the map depends on the arithmetic.  int8: the A operand is 32 KB of bytes and
+// the weight ring has 112 KB.  e4m3-FFN: QKV and out-projection run in fp16, so the A operand
+// is 64 KB (4 K-slabs of 64 halves) and the ring gives up two slots.
+template <bool kFP8>
+struct Cfg {
+    static constexpr uint32_t SM_A = 0;     // A operand: K-slabs of [128 rows][128 B]
+    static constexpr uint32_t SM_R = kFP8 ? 65536 : 32768;   // 64 KB: Q/K/V staging (3 x 16 KB) |
+                                            // hidden operand x2 (2 x 32 KB) | fp16 head A (4 x 16 KB)
+    static constexpr uint32_t SM_RING = SM_R + 65536;        // weight ring up to SM_XCH
+    static constexpr int kQSlots = kFP8 ? 3 : 4;             // 24 KB QKV stages
+    static constexpr int kRSlots = kFP8 ? 5 : 7;             // 16 KB stages
+    static constexpr int kAttnSlabs = kFP8 ? 4 : 2;          // K-slabs of a QKV / out-proj unit
+    static constexpr int kLayerStream = kFP8 ? 1048576 : 786432;
+};
 constexpr uint32_t SM_XCH = 212992;     // 16 KB: float4 [2 parity][4 quarter][128 rows]
 constexpr uint32_t SM_BAR = 229376;     // mbarriers
 constexpr uint32_t SM_MISC = SM_BAR + 256;
 constexpr uint32_t SM_PROF = SM_MISC + 64;     // 16 x int64 phase cycle counters
 constexpr uint32_t SM_BYTES = SM_PROF + 128;
 constexpr uint32_t kSmemRequest = SM_BYTES + 1024;
-constexpr int kQSlots = 4, kRSlots = 7;
 constexpr uint32_t kQStage = 24576, kRStage = 16384, kHeadStage = 12288;
 // barrier indices
 constexpr int B_WQ_FULL = 0, B_WQ_EMPTY = 4, B_WR_FULL = 8, B_WR_EMPTY = 15, B_ACC_FULL = 22,
@@ -75,6 +84,7 @@ struct Params {
     const uint8_t* rep;
     const uint64_t* legal;
     int n, n_layers, n_value, vmode;
+    int quant;                  // 3 = int8 on all four matmuls, 1 = e4m3 FFN with fp16 attention GEMMs
     float eps;
     const uint8_t* wstream;
     const uint8_t* lparams;
@@ -99,6 +109,7 @@ struct Params {
 struct RowCtx {
     int lane, q, qt, row;       // q: board within the tile, qt: which quarter of the columns
     uint32_t smem;              // shared base (shared-space address)
+    uint32_t sm_a, sm_r;        // A operand and the 64 KB staging / hidden / head-operand region
     uint8_t* smem_gen;          // shared base (generic pointer)
     uint32_t tm;                // TMEM base address with this warp's lane offset
     volatile int* abort_flag;
@@ -192,6 +203,24 @@ __device__ __forceinline__ uint4 quant16(const uint32_t* h, float inv) {
     }
     return make_uint4(o[0], o[1], o[2], o[3]);
 }
+// The e4m3 twin: the scaled value is rounded to fp16 first, then to e4m3, as the reference's
+// quantiser does (csrc/fp8_gemm.cuh:186-199); low half to the low byte.
+__device__ __forceinline__ uint4 quant16_e4m3(const uint32_t* h, float inv) {
+    const uint64_t inv2 = pk2(inv, inv);
+    uint32_t o[4];
+#pragma unroll
+    for (int k = 0; k < 4; ++k) {
+        const uint32_t lo = e4m3x2_from_h2(f2_to_h2(mul2(h2_to_f2(h[2 * k]), inv2)));
+        const uint32_t hi = e4m3x2_from_h2(f2_to_h2(mul2(h2_to_f2(h[2 * k + 1]), inv2)));
+        o[k] = lo | (hi << 16);
+    }
+    return make_uint4(o[0], o[1], o[2], o[3]);
+}
+template <bool kFP8>
+__device__ __forceinline__ uint4 quant16_any(const uint32_t* h, float inv) {
+    if (kFP8) return quant16_e4m3(h, inv);
+    return quant16(h, inv);
+}
 // Address of 16-byte group `chunk` of row `row` in a [rows][128 B] swizzled tile.
 __device__ __forceinline__ uint32_t sw_off(int row, int chunk) {
     return static_cast<uint32_t>(row) * 128u + (static_cast<uint32_t>(chunk ^ (row & 7)) << 4);
@@ -199,7 +228,11 @@ __device__ __forceinline__ uint32_t sw_off(int row, int chunk) {
 
 // `(float(acc) * sa) * sw` -> fp16, + fp16 bias, optional ReLU; kN columns -> kN/2 pairs
 // (int8_gemm.cuh:276-297, encoder.cu:631-644, 1482-1489).
-template <int kN, bool kRelu>
+// kAcc says what the accumulator holds: kAccInt = s32 with the two scales, kAccFloat = fp32
+// with the two scales (e4m3 GEMMs; csrc/fp8_gemm.cuh:288-310), kAccPlain = fp32 of an fp16 GEMM,
+// no scales (the reference's un-quantised QKV / out-projection).
+enum { kAccInt = 0, kAccFloat = 1, kAccPlain = 2 };
+template <int kN, bool kRelu, int kAcc = kAccInt>
 __device__ __forceinline__ void descale(const uint32_t* acc, float sa, float sw, const __half* bias,
                                         uint32_t* out) {
     const uint4* b4 = reinterpret_cast<const uint4*>(bias);
@@ -214,9 +247,14 @@ __device__ __forceinline__ void descale(const uint32_t* acc, float sa, float sw,
             // exact s32 -> f32 on the conversion unit (otherwise idle here; the integer-add
             // form measured 6 % slower because it loads the FMA pipe, which is the busy one),
             // then the two fp32 multiplies, both lanes at once
-            const uint64_t f = pk2(static_cast<float>(static_cast<int>(acc[2 * i])),
-                                   static_cast<float>(static_cast<int>(acc[2 * i + 1])));
-            __half2 h = __hadd2(as_h2(f2_to_h2(mul2(mul2(f, sa2), sw2))), as_h2(bw[k]));
+            uint64_t f;
+            if (kAcc == kAccInt)
+                f = pk2(static_cast<float>(static_cast<int>(acc[2 * i])),
+                        static_cast<float>(static_cast<int>(acc[2 * i + 1])));
+            else
+                f = pk2(__uint_as_float(acc[2 * i]), __uint_as_float(acc[2 * i + 1]));
+            if (kAcc != kAccPlain) f = mul2(mul2(f, sa2), sw2);
+            __half2 h = __hadd2(as_h2(f2_to_h2(f)), as_h2(bw[k]));
             if (kRelu) h = __hmax2(h, __float2half2_rn(0.0f));
             out[i] = as_u32(h);
         }
@@ -293,9 +331,13 @@ __device__ __forceinline__ void reinject32(const RowCtx& c, const Params& p, int
     }
 }
 
-template <bool kDbg, bool kRJ>
+//
+// In the e4m3 arithmetic (kFP8) the attention norm is not quantised at all: x_hat goes out as
+// the fp16 A operand of the fp16 QKV GEMM (`f16_out`); the FFN norm is quantised to e4m3 with
+// scale amax/8 (csrc/fp8_gemm.cuh:147-208).
+template <bool kDbg, bool kRJ, bool kFP8>
 __device__ __forceinline__ float ln_stage(RowCtx& c, const Params& p, bool final_norm, bool dump_x,
-                                          bool dump_xn, bool capture, int site) {
+                                          bool dump_xn, bool capture, int site, bool f16_out = false) {
     uint64_t sum2 = pk2(0.f, 0.f), sq2 = pk2(0.f, 0.f);      // (even, odd) column lanes
     __half2 mn = __float2half2_rn(65504.0f), mx = __float2half2_rn(-65504.0f);
 #pragma unroll 1
@@ -332,7 +374,7 @@ __device__ __forceinline__ float ln_stage(RowCtx& c, const Params& p, bool final
     const float e_lo = __half2float(__float2half_rn(__fmul_rn(__fsub_rn(xmin, mean), rstd)));
     const float e_hi = __half2float(__float2half_rn(__fmul_rn(__fsub_rn(xmax, mean), rstd)));
     const float amax = fmaxf(fabsf(e_lo), fabsf(e_hi));
-    const float sc = amax > 0.f ? __fdiv_rn(amax, 127.0f) : 1.0f;
+    const float sc = amax > 0.f ? __fdiv_rn(amax, kFP8 ? 8.0f : 127.0f) : 1.0f;
     const float inv = __fdiv_rn(1.0f, sc);
     const uint64_t nmean2 = pk2(-mean, -mean), rstd2 = pk2(rstd, rstd);
 #pragma unroll 1
@@ -345,11 +387,20 @@ __device__ __forceinline__ float ln_stage(RowCtx& c, const Params& p, bool final
         if (!final_norm) {
 #pragma unroll
             for (int i = 0; i < 16; ++i) x[i] = f2_to_h2(mul2(add2(h2_to_f2(x[i]), nmean2), rstd2));
+            if (kFP8 && f16_out) {
+                // fp16 A operand: 4 K-slabs of [128 rows][64 halves]; this thread's 32 columns
+                // are half of slab col / 64
 #pragma unroll
-            for (int v = 0; v < 2; ++v) {
-                const uint4 qv = quant16(&x[8 * v], inv);
-                sts128(c.smem + SM_A + u * 16384 + sw_off(c.row, 2 * c.qt + v), qv);
-                if (kDbg && capture && c.valid) *reinterpret_cast<uint4*>(p.cap_a + c.grow * kD + col + 16 * v) = qv;
+                for (int v = 0; v < 4; ++v)
+                    sts128(c.sm_a + (2 * u + (c.qt >> 1)) * 16384 + sw_off(c.row, 4 * (c.qt & 1) + v),
+                           make_uint4(x[4 * v], x[4 * v + 1], x[4 * v + 2], x[4 * v + 3]));
+            } else {
+#pragma unroll
+                for (int v = 0; v < 2; ++v) {
+                    const uint4 qv = quant16_any<kFP8>(&x[8 * v], inv);
+                    sts128(c.sm_a + u * 16384 + sw_off(c.row, 2 * c.qt + v), qv);
+                    if (kDbg && capture && c.valid) *reinterpret_cast<uint4*>(p.cap_a + c.grow * kD + col + 16 * v) = qv;
+                }
             }
         } else {
             // norm_f with affine: fp16(fma(x_hat, gamma, beta)) (encoder.cu:609-611), written as
@@ -365,7 +416,7 @@ __device__ __forceinline__ float ln_stage(RowCtx& c, const Params& p, bool final
                     x[4 * v + j] = f2_to_h2(fma2(mul2(add2(h2_to_f2(x[4 * v + j]), nmean2), rstd2),
                                                  h2_to_f2(gw[j]), h2_to_f2(bw[j])));
                 // head A slab = col / 64 = 2u + qt/2; 16-byte group within the 64-column slab
-                sts128(c.smem + SM_R + (2 * u + (c.qt >> 1)) * 16384 + sw_off(c.row, 4 * (c.qt & 1) + v),
+                sts128(c.sm_r + (2 * u + (c.qt >> 1)) * 16384 + sw_off(c.row, 4 * (c.qt & 1) + v),
                        make_uint4(x[4 * v], x[4 * v + 1], x[4 * v + 2], x[4 * v + 3]));
             }
         }
@@ -381,7 +432,7 @@ __device__ __forceinline__ float ln_stage(RowCtx& c, const Params& p, bool final
 // qt & 1 of the pair and query rows 16 * (qt >> 1) .. +15; the result overwrites its own
 // block of Q.
 __device__ __forceinline__ void attention_unit(const RowCtx& c, uint32_t alive) {
-    const uint32_t qs = c.smem + SM_R, ks = qs + 16384, vs = qs + 32768;
+    const uint32_t qs = c.sm_r, ks = qs + 16384, vs = qs + 32768;
     const int hh = c.qt & 1, r0 = 32 * c.q, rq = r0 + 16 * (c.qt >> 1);
     const int lane = c.lane, g = lane >> 2, t = lane & 3;
     uint32_t qa[2][4];
@@ -476,7 +527,7 @@ struct LayerParams {
 // QKV in four head-pair chunks with attention per chunk, then the attention output is
 // quantised into A, then out-projection + residual into the residual stream (TMEM).
 // `sa` is the scale of the row in A on entry.
-template <bool kDbg>
+template <bool kDbg, bool kFP8>
 __device__ __forceinline__ void attention_block(RowCtx& c, const Params& p, const LayerParams& lp,
                                                 float sa, uint32_t alive, bool cap, bool dbgl) {
     const int dbg = p.debug_stage;
@@ -492,10 +543,11 @@ __device__ __forceinline__ void attention_block(RowCtx& c, const Params& p, cons
             tmem_ld16(c.tm + TM_ACC + c0, acc);
             tmem_wait_ld();
             if (kDbg && cap && p.cap_op == BF_OP_QKV && c.valid) store_words<16>(p.cap_acc + c.grow * 768 + j * 192 + c0, acc);
-            descale<16, false>(acc, sa, __ldg(lp.sw_qkv + m * 2 + (j >> 1)), lp.b_qkv + j * 192 + c0, h);
+            descale<16, false, kFP8 ? kAccPlain : kAccInt>(acc, sa, __ldg(lp.sw_qkv + m * 2 + (j >> 1)),
+                                                            lp.b_qkv + j * 192 + c0, h);
 #pragma unroll
             for (int k = 0; k < 2; ++k)
-                sts128(c.smem + SM_R + m * 16384 + sw_off(c.row, (cm >> 3) + k),
+                sts128(c.sm_r + m * 16384 + sw_off(c.row, (cm >> 3) + k),
                        make_uint4(h[4 * k], h[4 * k + 1], h[4 * k + 2], h[4 * k + 3]));
             if (kDbg && dbgl && dbg == 5 + m && c.valid) store_words<8>(p.y + c.grow * kD + 64 * j + cm, h);
         }
@@ -511,7 +563,7 @@ __device__ __forceinline__ void attention_block(RowCtx& c, const Params& p, cons
             uint32_t oh[8];
 #pragma unroll
             for (int k = 0; k < 2; ++k) {
-                const uint4 v = lds128(c.smem + SM_R + sw_off(c.row, 2 * c.qt + k));
+                const uint4 v = lds128(c.sm_r + sw_off(c.row, 2 * c.qt + k));
                 oh[4 * k] = v.x; oh[4 * k + 1] = v.y; oh[4 * k + 2] = v.z; oh[4 * k + 3] = v.w;
             }
             o_amax = fmaxf(o_amax, amax_h2<8>(oh, true));
@@ -524,8 +576,20 @@ __device__ __forceinline__ void attention_block(RowCtx& c, const Params& p, cons
     tmem_wait_st();
     prof_mark<kDbg>(c, PH_PAIR_BAR);
 
-    // quantise the attention output into A (s8, per-row scale)
-    {
+    // the attention output becomes the A operand of the out-projection: quantised to s8 with a
+    // per-row scale, or (e4m3 arithmetic) copied as fp16 into the four fp16 K-slabs
+    if (kFP8) {
+#pragma unroll 1
+        for (int j = 0; j < 4; ++j) {
+            uint32_t oh[8];
+            tmem_ld8(c.tm + TM_OY + 32 * j + 8 * c.qt, oh);
+            tmem_wait_ld();
+            // columns 64j + 16qt .. +15 of the fp16 operand: slab j, 16-byte groups 2qt, 2qt+1
+            sts128(c.sm_a + j * 16384 + sw_off(c.row, 2 * c.qt), make_uint4(oh[0], oh[1], oh[2], oh[3]));
+            sts128(c.sm_a + j * 16384 + sw_off(c.row, 2 * c.qt + 1), make_uint4(oh[4], oh[5], oh[6], oh[7]));
+        }
+        row_publish(c, B_A_READY);
+    } else {
         const float amax = exchange_max(c, o_amax);
         sa = amax > 0.f ? __fdiv_rn(amax, 127.0f) : 1.0f;
         const float inv = __fdiv_rn(1.0f, sa);
@@ -536,7 +600,7 @@ __device__ __forceinline__ void attention_block(RowCtx& c, const Params& p, cons
             tmem_ld8(c.tm + TM_OY + 32 * j + 8 * c.qt, oh);
             tmem_wait_ld();
             const uint4 v = quant16(oh, inv);
-            sts128(c.smem + SM_A + (j >> 1) * 16384 + sw_off(c.row, 4 * (j & 1) + c.qt), v);
+            sts128(c.sm_a + (j >> 1) * 16384 + sw_off(c.row, 4 * (j & 1) + c.qt), v);
             if (capo) *reinterpret_cast<uint4*>(p.cap_a + c.grow * kD + 64 * j + 16 * c.qt) = v;
         }
         row_publish(c, B_A_READY);
@@ -553,7 +617,7 @@ __device__ __forceinline__ void attention_block(RowCtx& c, const Params& p, cons
         tmem_wait_ld();
         row_release_acc(c, u);
         if (kDbg && cap && p.cap_op == BF_OP_OUT && c.valid) store_words<32>(p.cap_acc + c.grow * 256 + col, acc);
-        descale<32, false>(acc, sa, __ldg(lp.sw_o + u), lp.b_o + col, y);
+        descale<32, false, kFP8 ? kAccPlain : kAccInt>(acc, sa, __ldg(lp.sw_o + u), lp.b_o + col, y);
 #pragma unroll
         for (int i = 0; i < 16; ++i) xo[i] = as_u32(__hadd2(as_h2(xo[i]), as_h2(y[i])));
         tmem_st16(c.tm + TM_X + (col >> 1), xo);
@@ -564,7 +628,7 @@ __device__ __forceinline__ void attention_block(RowCtx& c, const Params& p, cons
 
 // FFN: four hidden chunks of 256; ff1 -> ReLU -> per-row u8 -> ff2 with an fp16 running
 // total (encoder.cu:1431-1556).  The eight steps follow the MMA issue order.
-template <bool kDbg>
+template <bool kDbg, bool kFP8>
 __device__ __forceinline__ void ffn_block(RowCtx& c, const Params& p, const LayerParams& lp,
                                           float sa, bool cap) {
     float sa2_0 = 1.f, sa2_1 = 1.f;
@@ -584,11 +648,12 @@ __device__ __forceinline__ void ffn_block(RowCtx& c, const Params& p, const Laye
                 row_release_acc(c, jh);
                 const int col = 256 * ch + 128 * jh + 32 * c.qt;
                 if (kDbg && cap && p.cap_op == BF_OP_FF1 && c.valid) store_words<32>(p.cap_acc + c.grow * 1024 + col, acc);
-                descale<32, true>(acc, sa, __ldg(lp.sw_ff1 + 2 * ch + jh), lp.b_ff1 + col, &hid[16 * jh]);
+                descale<32, true, kFP8 ? kAccFloat : kAccInt>(acc, sa, __ldg(lp.sw_ff1 + 2 * ch + jh), lp.b_ff1 + col,
+                                                              &hid[16 * jh]);
             }
             // per-row u8 scale over the 256-wide chunk (encoder.cu:1510-1517)
             const float amax = exchange_max(c, amax_h2<32>(hid, false));
-            const float sc = amax > 0.f ? __fdiv_rn(amax, 255.0f) : 1.0f;
+            const float sc = amax > 0.f ? __fdiv_rn(amax, kFP8 ? 8.0f : 255.0f) : 1.0f;
             const float inv = __fdiv_rn(1.0f, sc);
             if (ch & 1) sa2_1 = sc; else sa2_0 = sc;
             const bool caph = kDbg && cap && p.cap_op == BF_OP_FF2 + ch && c.valid;
@@ -596,8 +661,8 @@ __device__ __forceinline__ void ffn_block(RowCtx& c, const Params& p, const Laye
             for (int jh = 0; jh < 2; ++jh)
 #pragma unroll
                 for (int k = 0; k < 2; ++k) {
-                    const uint4 v = quant16(&hid[16 * jh + 8 * k], inv);
-                    sts128(c.smem + SM_R + (ch & 1) * 32768 + jh * 16384 + sw_off(c.row, 2 * c.qt + k), v);
+                    const uint4 v = quant16_any<kFP8>(&hid[16 * jh + 8 * k], inv);
+                    sts128(c.sm_r + (ch & 1) * 32768 + jh * 16384 + sw_off(c.row, 2 * c.qt + k), v);
                     if (caph) *reinterpret_cast<uint4*>(p.cap_a + c.grow * kD + 128 * jh + 32 * c.qt + 16 * k) = v;
                 }
             row_publish(c, B_A2_READY + (ch & 1));
@@ -618,8 +683,10 @@ __device__ __forceinline__ void ffn_block(RowCtx& c, const Params& p, const Laye
                 const uint64_t s1_2 = pk2(s1, s1), s2_2 = pk2(s2, s2);
 #pragma unroll
                 for (int i = 0; i < 16; ++i) {
-                    uint64_t f = mul2(mul2(pk2(static_cast<float>(static_cast<int>(acc[2 * i])),
-                                               static_cast<float>(static_cast<int>(acc[2 * i + 1]))), s1_2), s2_2);
+                    uint64_t f = kFP8 ? pk2(__uint_as_float(acc[2 * i]), __uint_as_float(acc[2 * i + 1]))
+                                      : pk2(static_cast<float>(static_cast<int>(acc[2 * i])),
+                                            static_cast<float>(static_cast<int>(acc[2 * i + 1])));
+                    f = mul2(mul2(f, s1_2), s2_2);
                     if (ch > 0) f = add2_after_mul(f, h2_to_f2(run[i]));
                     run[i] = f2_to_h2(f);
                 }
@@ -715,7 +782,7 @@ __device__ __forceinline__ void prenorm_value(RowCtx& c, const Params& p, uint32
     for (int k = 0; k < 3; ++k) logit[k] = rstd * (t1[k] - mean * t2[k]) + t3[k];
 }
 
-template <bool kDbg, bool kRJ>
+template <bool kDbg, bool kRJ, bool kFP8>
 __device__ __forceinline__ void row_warps_tile(RowCtx& c, const Params& p, int tile) {
     const int board = tile * 4 + c.q;
     c.valid = board < p.n;
@@ -774,15 +841,16 @@ __device__ __forceinline__ void row_warps_tile(RowCtx& c, const Params& p, int t
         const bool dump_x = (dbg == 9 && ph == 0) || (dbg == 2 && odd && dbgl) ||
                             (dbg == 10 && !odd && ph > 0 && layer - 1 == p.debug_layer);
         if (ph == n_ph) {
-            ln_stage<kDbg, kRJ>(c, p, true, dump_x, dbg == 8, false, -1);
+            ln_stage<kDbg, kRJ, kFP8>(c, p, true, dump_x, dbg == 8, false, -1);
             row_publish(c, B_A_READY);
             break;
         }
         const bool cap = layer == p.cap_layer;
         // re-injection site of this norm: every norm when both inject, attention norms only else
         const int site = !kRJ ? -1 : (p.rj_mode == 2 ? ph : (odd ? -1 : layer));
-        const float sa = ln_stage<kDbg, kRJ>(c, p, false, dump_x, dbgl && dbg == (odd ? 3 : 1),
-                                           cap && p.cap_op == (odd ? BF_OP_FF1 : BF_OP_QKV), site);
+        const float sa = ln_stage<kDbg, kRJ, kFP8>(c, p, false, dump_x, dbgl && dbg == (odd ? 3 : 1),
+                                                 cap && p.cap_op == (odd ? BF_OP_FF1 : BF_OP_QKV), site,
+                                                 kFP8 && !odd);
         row_publish(c, B_A_READY);
 
         const uint8_t* lpb = p.lparams + static_cast<size_t>(layer) * kLparamStride;
@@ -795,8 +863,8 @@ __device__ __forceinline__ void row_warps_tile(RowCtx& c, const Params& p, int t
         lp.b_o = reinterpret_cast<const __half*>(lpb + LP_B_O);
         lp.b_ff1 = reinterpret_cast<const __half*>(lpb + LP_B_FF1);
         lp.b_ff2 = reinterpret_cast<const __half*>(lpb + LP_B_FF2);
-        if (!odd) attention_block<kDbg>(c, p, lp, sa, c.valid ? alive : 0xffffffffu, cap, dbgl);
-        else      ffn_block<kDbg>(c, p, lp, sa, cap);
+        if (!odd) attention_block<kDbg, kFP8>(c, p, lp, sa, c.valid ? alive : 0xffffffffu, cap, dbgl);
+        else      ffn_block<kDbg, kFP8>(c, p, lp, sa, cap);
     }
 
     // ---- heads: fp16 GEMM [128 x 256] x [96 x 256]^T, fp32 accumulate, rounded to fp16
@@ -870,8 +938,11 @@ __device__ __forceinline__ uint32_t uses(uint32_t cnt, uint32_t slots, uint32_t 
     return (cnt + slots - 1 - s) / slots;
 }
 
+template <bool kFP8>
 __device__ __forceinline__ void producer_loop(uint32_t smem, volatile int* abort_flag, const Params& p,
                                            int first_tile, int tile_step, int n_tiles) {
+    using C = Cfg<kFP8>;
+    constexpr uint32_t kQS = C::kQSlots, kRS = C::kRSlots;
     uint32_t qi = 0, ri = 0;   // stages issued into the QKV ring / the 16 KB ring
     for (int tile = first_tile; tile < n_tiles; tile += tile_step) {
         const uint8_t* src = p.wstream;
@@ -879,25 +950,26 @@ __device__ __forceinline__ void producer_loop(uint32_t smem, volatile int* abort
             const bool head = layer == p.n_layers;
             if (!head) {
                 // the two rings share memory: the 16 KB ring must be drained first
-                for (uint32_t s = 0; s < kRSlots; ++s)
-                    mbar_wait(bar_addr(smem, B_WR_EMPTY + s), (uses(ri, kRSlots, s) - 1u) & 1u, abort_flag, kErrProducer);
-                for (int st = 0; st < 8; ++st, ++qi) {
-                    const uint32_t s = qi % kQSlots;
-                    mbar_wait(bar_addr(smem, B_WQ_EMPTY + s), (qi / kQSlots - 1u) & 1u, abort_flag, kErrProducer);
+                for (uint32_t s = 0; s < kRS; ++s)
+                    mbar_wait(bar_addr(smem, B_WR_EMPTY + s), (uses(ri, kRS, s) - 1u) & 1u, abort_flag, kErrProducer);
+                for (int st = 0; st < 4 * C::kAttnSlabs; ++st, ++qi) {
+                    const uint32_t s = qi % kQS;
+                    mbar_wait(bar_addr(smem, B_WQ_EMPTY + s), (qi / kQS - 1u) & 1u, abort_flag, kErrProducer);
                     mbar_arrive_expect_tx(bar_addr(smem, B_WQ_FULL + s), kQStage);
-                    bulk_g2s(smem + SM_RING + s * kQStage, src, kQStage, bar_addr(smem, B_WQ_FULL + s));
+                    bulk_g2s(smem + C::SM_RING + s * kQStage, src, kQStage, bar_addr(smem, B_WQ_FULL + s));
                     src += kQStage;
                 }
-                for (uint32_t s = 0; s < kQSlots; ++s)
-                    mbar_wait(bar_addr(smem, B_WQ_EMPTY + s), (uses(qi, kQSlots, s) - 1u) & 1u, abort_flag, kErrProducer);
+                for (uint32_t s = 0; s < kQS; ++s)
+                    mbar_wait(bar_addr(smem, B_WQ_EMPTY + s), (uses(qi, kQS, s) - 1u) & 1u, abort_flag, kErrProducer);
             }
-            const int n_st = head ? 4 : 36;
+            // out-projection (2 units) and the 16 FFN units (2 K-slabs each), or the 4 head slabs
+            const int n_st = head ? 4 : 2 * C::kAttnSlabs + 32;
             const uint32_t bytes = head ? kHeadStage : kRStage;
             for (int st = 0; st < n_st; ++st, ++ri) {
-                const uint32_t s = ri % kRSlots;
-                mbar_wait(bar_addr(smem, B_WR_EMPTY + s), (ri / kRSlots - 1u) & 1u, abort_flag, kErrProducer);
+                const uint32_t s = ri % kRS;
+                mbar_wait(bar_addr(smem, B_WR_EMPTY + s), (ri / kRS - 1u) & 1u, abort_flag, kErrProducer);
                 mbar_arrive_expect_tx(bar_addr(smem, B_WR_FULL + s), bytes);
-                bulk_g2s(smem + SM_RING + s * kRStage, src, bytes, bar_addr(smem, B_WR_FULL + s));
+                bulk_g2s(smem + C::SM_RING + s * kRStage, src, bytes, bar_addr(smem, B_WR_FULL + s));
                 src += bytes;
             }
         }
@@ -919,34 +991,37 @@ struct MmaState {
     uint32_t accn[2];         // units issued into each accumulator slot
     uint32_t aready, a2n[2];  // operand-ready phases consumed
 };
+enum { kKindI8 = 0, kKindF16 = 1, kKindF8 = 2 };
 
 // One GEMM unit: `n_stages` K-slabs of 128 bytes, 4 MMAs each.
+template <bool kFP8>
 __device__ __forceinline__ void mma_unit(uint32_t smem, volatile int* abort_flag, MmaState& st,
                                          uint32_t tmem_d, int slot, uint32_t a_base, bool qring,
-                                         int n_stages, uint32_t idesc, bool f16) {
+                                         int n_stages, uint32_t idesc, int kind) {
+    using C = Cfg<kFP8>;
     mbar_wait(bar_addr(smem, B_ACC_EMPTY + slot), (st.accn[slot] - 1u) & 1u, abort_flag, kErrMmaAcc);
     tc_fence_after();
     for (int s = 0; s < n_stages; ++s) {
-        uint32_t w_full, w_empty, w_addr;
+        uint32_t w_empty, w_addr;
         if (qring) {
-            const uint32_t k = st.qc % kQSlots;
-            mbar_wait(bar_addr(smem, B_WQ_FULL + k), (st.qc / kQSlots) & 1u, abort_flag, kErrMmaWeights);
-            w_full = k; w_empty = bar_addr(smem, B_WQ_EMPTY + k); w_addr = smem + SM_RING + k * kQStage;
+            const uint32_t k = st.qc % C::kQSlots;
+            mbar_wait(bar_addr(smem, B_WQ_FULL + k), (st.qc / C::kQSlots) & 1u, abort_flag, kErrMmaWeights);
+            w_empty = bar_addr(smem, B_WQ_EMPTY + k); w_addr = smem + C::SM_RING + k * kQStage;
             st.qc++;
         } else {
-            const uint32_t k = st.rc % kRSlots;
-            mbar_wait(bar_addr(smem, B_WR_FULL + k), (st.rc / kRSlots) & 1u, abort_flag, kErrMmaWeights);
-            w_full = k; w_empty = bar_addr(smem, B_WR_EMPTY + k); w_addr = smem + SM_RING + k * kRStage;
+            const uint32_t k = st.rc % C::kRSlots;
+            mbar_wait(bar_addr(smem, B_WR_FULL + k), (st.rc / C::kRSlots) & 1u, abort_flag, kErrMmaWeights);
+            w_empty = bar_addr(smem, B_WR_EMPTY + k); w_addr = smem + C::SM_RING + k * kRStage;
             st.rc++;
         }
-        (void)w_full;
         tc_fence_after();
         const uint64_t ad = umma_desc_k128(a_base + s * 16384), bd = umma_desc_k128(w_addr);
 #pragma unroll
         for (int k = 0; k < 4; ++k) {
             const uint32_t accumulate = (s > 0 || k > 0) ? 1u : 0u;
-            if (f16) umma_f16(tmem_d, ad + 2 * k, bd + 2 * k, idesc, accumulate);
-            else     umma_i8(tmem_d, ad + 2 * k, bd + 2 * k, idesc, accumulate);
+            if (kind == kKindF16)     umma_f16(tmem_d, ad + 2 * k, bd + 2 * k, idesc, accumulate);
+            else if (kind == kKindF8) umma_f8(tmem_d, ad + 2 * k, bd + 2 * k, idesc, accumulate);
+            else                      umma_i8(tmem_d, ad + 2 * k, bd + 2 * k, idesc, accumulate);
         }
         tc_commit(w_empty);
     }
@@ -961,22 +1036,33 @@ __device__ __forceinline__ void mma_wait_operand(uint32_t smem, volatile int* ab
     tc_fence_after();
 }
 
+template <bool kFP8>
 __device__ __forceinline__ void mma_loop(uint32_t smem, uint32_t tmem, volatile int* abort_flag,
                                       const Params& p, int first_tile, int tile_step, int n_tiles) {
+    using C = Cfg<kFP8>;
     MmaState st = {0, 0, {0, 0}, 0, {0, 0}};
-    constexpr uint32_t kI_QKV = umma_idesc(kAccS32, kFmtS8, kFmtS8, 128, 192);
-    constexpr uint32_t kI_S8 = umma_idesc(kAccS32, kFmtS8, kFmtS8, 128, 128);
-    constexpr uint32_t kI_U8 = umma_idesc(kAccS32, kFmtU8, kFmtS8, 128, 128);
+    // int8: every weight GEMM is s8/u8 x s8.  e4m3: QKV and out-projection are fp16 x fp16,
+    // the FFN is e4m3 x e4m3; both accumulate in fp32.
+    constexpr uint32_t kI_QKV = kFP8 ? umma_idesc(kAccF32, kFmtF16, kFmtF16, 128, 192)
+                                     : umma_idesc(kAccS32, kFmtS8, kFmtS8, 128, 192);
+    constexpr uint32_t kI_OUT = kFP8 ? umma_idesc(kAccF32, kFmtF16, kFmtF16, 128, 128)
+                                     : umma_idesc(kAccS32, kFmtS8, kFmtS8, 128, 128);
+    constexpr uint32_t kI_FF1 = kFP8 ? umma_idesc(kAccF32, kFmtE4M3, kFmtE4M3, 128, 128)
+                                     : umma_idesc(kAccS32, kFmtS8, kFmtS8, 128, 128);
+    constexpr uint32_t kI_FF2 = kFP8 ? umma_idesc(kAccF32, kFmtE4M3, kFmtE4M3, 128, 128)
+                                     : umma_idesc(kAccS32, kFmtU8, kFmtS8, 128, 128);
     constexpr uint32_t kI_HEAD = umma_idesc(kAccF32, kFmtF16, kFmtF16, 128, 96);
+    constexpr int kAttnKind = kFP8 ? kKindF16 : kKindI8, kFfnKind = kFP8 ? kKindF8 : kKindI8;
     const uint32_t acc0 = tmem + TM_ACC, acc1 = tmem + TM_ACC + 128;
+    const uint32_t sm_a = smem + C::SM_A, sm_r = smem + C::SM_R;
     for (int tile = first_tile; tile < n_tiles; tile += tile_step) {
         for (int layer = 0; layer < p.n_layers; ++layer) {
             mma_wait_operand(smem, abort_flag, B_A_READY, st.aready);          // LN1 output
             for (int j = 0; j < 4; ++j)
-                mma_unit(smem, abort_flag, st, acc0, 0, smem + SM_A, true, 2, kI_QKV, false);
+                mma_unit<kFP8>(smem, abort_flag, st, acc0, 0, sm_a, true, C::kAttnSlabs, kI_QKV, kAttnKind);
             mma_wait_operand(smem, abort_flag, B_A_READY, st.aready);          // attention output
-            mma_unit(smem, abort_flag, st, acc0, 0, smem + SM_A, false, 2, kI_S8, false);
-            mma_unit(smem, abort_flag, st, acc1, 1, smem + SM_A, false, 2, kI_S8, false);
+            mma_unit<kFP8>(smem, abort_flag, st, acc0, 0, sm_a, false, C::kAttnSlabs, kI_OUT, kAttnKind);
+            mma_unit<kFP8>(smem, abort_flag, st, acc1, 1, sm_a, false, C::kAttnSlabs, kI_OUT, kAttnKind);
             mma_wait_operand(smem, abort_flag, B_A_READY, st.aready);          // LN2 output
             // FFN units in the order the weight stream was packed (pack.py: FFN_UNITS)
 #pragma unroll 1
@@ -987,20 +1073,20 @@ __device__ __forceinline__ void mma_loop(uint32_t smem, uint32_t tmem, volatile 
                 const int ch = kind2 ? ((0x32010000u >> (4 * pr)) & 0xF) : ((0x00302010u >> (4 * pr)) & 0xF);
                 if (kind2) {
                     if (jh == 0) mma_wait_operand(smem, abort_flag, B_A2_READY + (ch & 1), st.a2n[ch & 1]);
-                    mma_unit(smem, abort_flag, st, jh ? acc1 : acc0, jh, smem + SM_R + (ch & 1) * 32768,
-                             false, 2, kI_U8, false);
+                    mma_unit<kFP8>(smem, abort_flag, st, jh ? acc1 : acc0, jh, sm_r + (ch & 1) * 32768,
+                                   false, 2, kI_FF2, kFfnKind);
                 } else {
-                    mma_unit(smem, abort_flag, st, jh ? acc1 : acc0, jh, smem + SM_A, false, 2, kI_S8, false);
+                    mma_unit<kFP8>(smem, abort_flag, st, jh ? acc1 : acc0, jh, sm_a, false, 2, kI_FF1, kFfnKind);
                 }
             }
         }
         mma_wait_operand(smem, abort_flag, B_A_READY, st.aready);              // final norm output
-        mma_unit(smem, abort_flag, st, acc0, 0, smem + SM_R, false, 4, kI_HEAD, true);
+        mma_unit<kFP8>(smem, abort_flag, st, acc0, 0, sm_r, false, 4, kI_HEAD, kKindF16);
     }
 }
 
 // ------------------------------------------------------------------------------------------
-template <bool kDbg, bool kRJ>
+template <bool kDbg, bool kRJ, bool kFP8>
 __global__ void __launch_bounds__(kThreads, 1) encoder_kernel(const Params p) {
     extern __shared__ uint8_t smem_raw[];
     uint8_t* sm = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
@@ -1032,15 +1118,16 @@ __global__ void __launch_bounds__(kThreads, 1) encoder_kernel(const Params p) {
         RowCtx c;
         c.lane = lane; c.q = warp & 3; c.qt = warp >> 2; c.row = 32 * c.q + lane;
         c.smem = smem; c.smem_gen = sm;
+        c.sm_a = smem + Cfg<kFP8>::SM_A; c.sm_r = smem + Cfg<kFP8>::SM_R;
         c.tm = tmem + (static_cast<uint32_t>(32 * c.q) << 16);
         c.abort_flag = abort_flag; c.xpar = 0; c.full0 = c.full1 = 0;
         c.prof_on = kDbg && p.prof != nullptr && threadIdx.x == 0;
         c.t_last = c.prof_on ? clock64() : 0;
-        for (int tile = blockIdx.x; tile < n_tiles; tile += gridDim.x) row_warps_tile<kDbg, kRJ>(c, p, tile);
+        for (int tile = blockIdx.x; tile < n_tiles; tile += gridDim.x) row_warps_tile<kDbg, kRJ, kFP8>(c, p, tile);
     } else if (warp == kProducerWarp) {
-        if (lane == 0) producer_loop(smem, abort_flag, p, blockIdx.x, gridDim.x, n_tiles);
+        if (lane == 0) producer_loop<kFP8>(smem, abort_flag, p, blockIdx.x, gridDim.x, n_tiles);
     } else {
-        if (lane == 0) mma_loop(smem, tmem, abort_flag, p, blockIdx.x, gridDim.x, n_tiles);
+        if (lane == 0) mma_loop<kFP8>(smem, tmem, abort_flag, p, blockIdx.x, gridDim.x, n_tiles);
     }
     __syncwarp();
     tc_fence_before();
@@ -1094,12 +1181,14 @@ __global__ void __launch_bounds__(128, 1) selftest_kernel(int mode, const uint8_
         const uint32_t idesc = mode == 0 ? umma_idesc(kAccS32, kFmtS8, kFmtS8, 128, 128)
                              : mode == 1 ? umma_idesc(kAccS32, kFmtU8, kFmtS8, 128, 128)
                              : mode == 2 ? umma_idesc(kAccS32, kFmtS8, kFmtS8, 128, 192)
-                                         : umma_idesc(kAccF32, kFmtF16, kFmtF16, 128, 96);
+                             : mode == 3 ? umma_idesc(kAccF32, kFmtF16, kFmtF16, 128, 96)
+                                         : umma_idesc(kAccF32, kFmtE4M3, kFmtE4M3, 128, 128);
         for (int s = 0; s < slabs; ++s) {
             const uint64_t ad = umma_desc_k128(smem + s * 16384), bd = umma_desc_k128(smem + kW + s * w_stage);
             for (int k = 0; k < 4; ++k) {
-                if (mode == 3) umma_f16(tmem, ad + 2 * k, bd + 2 * k, idesc, (s | k) ? 1u : 0u);
-                else           umma_i8(tmem, ad + 2 * k, bd + 2 * k, idesc, (s | k) ? 1u : 0u);
+                if (mode == 3)      umma_f16(tmem, ad + 2 * k, bd + 2 * k, idesc, (s | k) ? 1u : 0u);
+                else if (mode == 4) umma_f8(tmem, ad + 2 * k, bd + 2 * k, idesc, (s | k) ? 1u : 0u);
+                else                umma_i8(tmem, ad + 2 * k, bd + 2 * k, idesc, (s | k) ? 1u : 0u);
             }
         }
         tc_commit(smem + kBar + 8);
@@ -1143,7 +1232,7 @@ int fail(int code, const std::string& msg) {
 struct BlobHeader {
     uint32_t magic, version, n_layers, n_value, vmode;
     float eps;
-    uint32_t rj_mode, reserved;
+    uint32_t rj_mode, quant;      // quant: 3 = int8 all four matmuls, 1 = e4m3 FFN
     uint64_t off_w, bytes_w, off_lp, bytes_lp, off_emb, bytes_emb, off_tail, bytes_tail, off_rj, bytes_rj, total;
 };
 
@@ -1182,6 +1271,7 @@ int launch(bf_handle* h, const uint16_t* boards, const int16_t* control, const u
     p.boards = boards; p.control = control; p.rep = rep; p.legal = legal;
     p.n = n; p.n_layers = static_cast<int>(h->hdr.n_layers);
     p.n_value = static_cast<int>(h->hdr.n_value); p.vmode = static_cast<int>(h->hdr.vmode);
+    p.quant = static_cast<int>(h->hdr.quant);
     p.eps = h->hdr.eps;
     p.wstream = h->blob + h->hdr.off_w;
     p.lparams = h->blob + h->hdr.off_lp;
@@ -1198,12 +1288,16 @@ int launch(bf_handle* h, const uint16_t* boards, const int16_t* control, const u
     const int grid = n_tiles < h->sm_count ? n_tiles : h->sm_count;
     // the instrumented instantiation only when a dump, a capture or the phase clock is asked for
     const bool dbg = stage != 0 || cap_layer >= 0 || p.prof != nullptr;
-    if (p.rj_mode != 0) {
-        if (dbg) bf::encoder_kernel<true, true><<<grid, bf::kThreads, bf::kSmemRequest, stream>>>(p);
-        else     bf::encoder_kernel<false, true><<<grid, bf::kThreads, bf::kSmemRequest, stream>>>(p);
+    if (p.quant == 1) {
+        if (cap_layer >= 0) return fail(BF_ENOTSUP, "operand capture is for the int8 arithmetic");
+        if (dbg) bf::encoder_kernel<true, false, true><<<grid, bf::kThreads, bf::kSmemRequest, stream>>>(p);
+        else     bf::encoder_kernel<false, false, true><<<grid, bf::kThreads, bf::kSmemRequest, stream>>>(p);
+    } else if (p.rj_mode != 0) {
+        if (dbg) bf::encoder_kernel<true, true, false><<<grid, bf::kThreads, bf::kSmemRequest, stream>>>(p);
+        else     bf::encoder_kernel<false, true, false><<<grid, bf::kThreads, bf::kSmemRequest, stream>>>(p);
     } else {
-        if (dbg) bf::encoder_kernel<true, false><<<grid, bf::kThreads, bf::kSmemRequest, stream>>>(p);
-        else     bf::encoder_kernel<false, false><<<grid, bf::kThreads, bf::kSmemRequest, stream>>>(p);
+        if (dbg) bf::encoder_kernel<true, false, false><<<grid, bf::kThreads, bf::kSmemRequest, stream>>>(p);
+        else     bf::encoder_kernel<false, false, false><<<grid, bf::kThreads, bf::kSmemRequest, stream>>>(p);
     }
     BF_CUDA(cudaGetLastError());
     h->launches++;
@@ -1229,7 +1323,10 @@ int bf_create(const void* blob, size_t blob_bytes, int device, bf_handle** out) 
     if (hdr.version != BF_BLOB_VERSION) return fail(BF_EINVAL, "blob version mismatch");
     if (hdr.total != blob_bytes) return fail(BF_EINVAL, "blob size does not match its header");
     if (hdr.n_layers < 1 || hdr.n_layers > 64) return fail(BF_EINVAL, "n_layers out of range");
-    if (hdr.bytes_w != static_cast<uint64_t>(hdr.n_layers) * bf::kLayerStreamBytes + 4 * bf::kHeadStage ||
+    if (hdr.quant != 3 && hdr.quant != 1) return fail(BF_EINVAL, "blob arithmetic must be 3 (int8) or 1 (e4m3 FFN)");
+    if (hdr.quant == 1 && hdr.rj_mode != 0) return fail(BF_ENOTSUP, "re-injection is built for the int8 arithmetic only");
+    const uint64_t layer_stream = hdr.quant == 1 ? bf::Cfg<true>::kLayerStream : bf::Cfg<false>::kLayerStream;
+    if (hdr.bytes_w != static_cast<uint64_t>(hdr.n_layers) * layer_stream + 4 * bf::kHeadStage ||
         hdr.bytes_lp != static_cast<uint64_t>(hdr.n_layers) * bf::kLparamStride ||
         hdr.bytes_emb != 184u * 256u * 2u || hdr.bytes_tail != 2560u || hdr.rj_mode > 2 ||
         hdr.bytes_rj != (hdr.rj_mode ? static_cast<uint64_t>(hdr.n_layers) * hdr.rj_mode * 16u : 0u))
@@ -1256,18 +1353,15 @@ int bf_create(const void* blob, size_t blob_bytes, int device, bf_handle** out) 
     if (e == cudaSuccess) e = cudaStreamCreateWithFlags(&h->stream, cudaStreamNonBlocking);
     if (e == cudaSuccess) e = cudaStreamCreateWithFlags(&h->copy_stream, cudaStreamNonBlocking);
     if (e == cudaSuccess) e = cudaEventCreateWithFlags(&h->chunk_done, cudaEventDisableTiming);
-    if (e == cudaSuccess)
-        e = cudaFuncSetAttribute(bf::encoder_kernel<false, false>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                 bf::kSmemRequest);
-    if (e == cudaSuccess)
-        e = cudaFuncSetAttribute(bf::encoder_kernel<true, false>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                 bf::kSmemRequest);
-    if (e == cudaSuccess)
-        e = cudaFuncSetAttribute(bf::encoder_kernel<false, true>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                 bf::kSmemRequest);
-    if (e == cudaSuccess)
-        e = cudaFuncSetAttribute(bf::encoder_kernel<true, true>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                 bf::kSmemRequest);
+    const void* kernels[6] = {
+        reinterpret_cast<const void*>(&bf::encoder_kernel<false, false, false>),
+        reinterpret_cast<const void*>(&bf::encoder_kernel<true, false, false>),
+        reinterpret_cast<const void*>(&bf::encoder_kernel<false, true, false>),
+        reinterpret_cast<const void*>(&bf::encoder_kernel<true, true, false>),
+        reinterpret_cast<const void*>(&bf::encoder_kernel<false, false, true>),
+        reinterpret_cast<const void*>(&bf::encoder_kernel<true, false, true>)};
+    for (int i = 0; i < 6 && e == cudaSuccess; ++i)
+        e = cudaFuncSetAttribute(kernels[i], cudaFuncAttributeMaxDynamicSharedMemorySize, bf::kSmemRequest);
     if (e != cudaSuccess) {
         bf_destroy(h);
         return fail(BF_ECUDA, std::string("bf_create: ") + cudaGetErrorString(e));
@@ -1421,7 +1515,7 @@ const char* bf_profile_phases(void) {
 }
 
 int bf_selftest_umma(int device, int mode, const void* a, const void* w_image, void* out) {
-    if (mode < 0 || mode > 3 || a == nullptr || w_image == nullptr || out == nullptr)
+    if (mode < 0 || mode > 4 || a == nullptr || w_image == nullptr || out == nullptr)
         return fail(BF_EINVAL, "bad self-test argument");
     BF_CUDA(cudaSetDevice(device));
     int* status = nullptr;
@@ -1489,7 +1583,7 @@ int noalloc_setup(int device, NoAllocDevice** out) {
         void* ptr = nullptr;
         BF_CUDA(cudaGetSymbolAddress(&ptr, bf::g_noalloc_scratch));
         BF_CUDA(cudaMemset(ptr, 0, bf::kNoAllocScratchBytes));
-        BF_CUDA(cudaFuncSetAttribute(bf::encoder_kernel<false, false>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+        BF_CUDA(cudaFuncSetAttribute(bf::encoder_kernel<false, false, false>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                      bf::kSmemRequest));
         d.scratch = ptr;
         d.sm_count = prop.multiProcessorCount;
@@ -1522,7 +1616,8 @@ int bf_forward_noalloc(int device, const void* blob_dev, size_t blob_bytes, cons
         if (hdr.magic != BF_BLOB_MAGIC || hdr.version != BF_BLOB_VERSION || hdr.total != blob_bytes)
             return fail(BF_EINVAL, "blob header does not match (magic, version or size)");
         if (hdr.n_layers < 1 || hdr.n_layers > 64 ||
-            hdr.bytes_w != static_cast<uint64_t>(hdr.n_layers) * bf::kLayerStreamBytes + 4 * bf::kHeadStage ||
+            hdr.quant != 3 ||
+            hdr.bytes_w != static_cast<uint64_t>(hdr.n_layers) * bf::Cfg<false>::kLayerStream + 4 * bf::kHeadStage ||
             hdr.bytes_lp != static_cast<uint64_t>(hdr.n_layers) * bf::kLparamStride ||
             hdr.bytes_emb != 184u * 256u * 2u || hdr.bytes_tail != 2560u || hdr.rj_mode != 0 ||
             ((hdr.off_w | hdr.off_lp | hdr.off_emb | hdr.off_tail) & 255u) ||
@@ -1542,6 +1637,7 @@ int bf_forward_noalloc(int device, const void* blob_dev, size_t blob_bytes, cons
     p.boards = boards; p.control = control; p.rep = rep; p.legal = legal;
     p.n = n; p.n_layers = static_cast<int>(d->hdr.n_layers);
     p.n_value = static_cast<int>(d->hdr.n_value); p.vmode = static_cast<int>(d->hdr.vmode);
+    p.quant = 3;
     p.eps = d->hdr.eps;
     p.wstream = base + d->hdr.off_w;
     p.lparams = base + d->hdr.off_lp;
@@ -1555,7 +1651,7 @@ int bf_forward_noalloc(int device, const void* blob_dev, size_t blob_bytes, cons
     p.prof = nullptr;
     const int n_tiles = (n + 3) / 4;
     const int grid = n_tiles < d->sm_count ? n_tiles : d->sm_count;
-    bf::encoder_kernel<false, false><<<grid, bf::kThreads, bf::kSmemRequest, static_cast<cudaStream_t>(stream)>>>(p);
+    bf::encoder_kernel<false, false, false><<<grid, bf::kThreads, bf::kSmemRequest, static_cast<cudaStream_t>(stream)>>>(p);
     BF_CUDA(cudaGetLastError());
     return BF_OK;
 }

@@ -211,7 +211,7 @@ __device__ __forceinline__ uint64_t umma_desc_k128(uint32_t saddr) {
 
 // Instruction descriptor fields: D format [4,6), A format [7,10), B format [10,13),
 // N>>3 [17,23), M>>4 [24,29); A and B both K-major, dense, no negate.
-constexpr uint32_t kFmtU8 = 0, kFmtS8 = 1, kFmtF16 = 0;
+constexpr uint32_t kFmtU8 = 0, kFmtS8 = 1, kFmtF16 = 0, kFmtE4M3 = 0;
 constexpr uint32_t kAccF32 = 1, kAccS32 = 2;
 __host__ __device__ constexpr uint32_t umma_idesc(uint32_t acc, uint32_t afmt, uint32_t bfmt,
                                                   uint32_t m, uint32_t n) {
@@ -235,6 +235,22 @@ __device__ __forceinline__ void umma_f16(uint32_t d_tmem, uint64_t adesc, uint64
         "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}"
         ::"r"(d_tmem), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate)
         : "memory");
+}
+
+__device__ __forceinline__ void umma_f8(uint32_t d_tmem, uint64_t adesc, uint64_t bdesc,
+                                        uint32_t idesc, uint32_t accumulate) {
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "setp.ne.b32 p, %4, 0;\n\t"
+        "tcgen05.mma.cta_group::1.kind::f8f6f4 [%0], %1, %2, %3, p;\n\t}"
+        ::"r"(d_tmem), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate)
+        : "memory");
+}
+// Two fp16 values -> two e4m3 bytes (low half to the low byte), saturating at +-448.
+__device__ __forceinline__ uint32_t e4m3x2_from_h2(uint32_t h2) {
+    uint32_t r;
+    asm("{ .reg .b16 t; cvt.rn.satfinite.e4m3x2.f16x2 t, %1; cvt.u32.u16 %0, t; }" : "=r"(r) : "r"(h2));
+    return r;
 }
 
 // ---------------------------------------------------------------- warp-level mma (attention)

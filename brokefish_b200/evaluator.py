@@ -61,19 +61,19 @@ class ShardedEvaluator:
     rank's GPU; ``shard`` tells the caller which slice of a global batch is this rank's.
     """
 
-    def __init__(self, net, rank: int, world: int, device_index: int):
+    def __init__(self, net, rank: int, world: int, device_index: int, fp8: bool = False):
         import torch.distributed as dist
         from brokefish_b200.nn.cuda_impl import FusedEncoder
         from brokefish_b200.nn.pack import pack_blob
         self.rank, self.world = rank, world
         dev = torch.device("cuda", device_index)
         if world > 1:
-            blob = pack_blob(net) if rank == 0 else None
+            blob = pack_blob(net, "e4m3" if fp8 else "int8") if rank == 0 else None
             blob_dev = broadcast_blob(blob, dev, src=0)
             torch.cuda.synchronize(dev)
             self.encoder = FusedEncoder.from_blob(blob_dev, device=device_index)
         else:
-            self.encoder = FusedEncoder(net, device=device_index)
+            self.encoder = FusedEncoder(net, device=device_index, fp8=fp8)
 
     def shard(self, n: int) -> Tuple[int, int]:
         return shard_bounds(n, self.world, self.rank)

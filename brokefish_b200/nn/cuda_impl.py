@@ -5,10 +5,12 @@ Same constructor, attributes, methods and errors as the reference's CUDA impleme
 ``include/brokefish_b200.h``.  PyTorch is used for device memory and the current stream
 only.
 
-What is built here is the int8 arithmetic of the reference's ``int8=True`` path (scheme
-``"all"``: QKV, out-projection and both FFN matmuls in int8, heads and attention in
-fp16).  The fp16 and e4m3 arithmetics of the reference are not built: asking for them
-raises ``NotImplementedError`` instead of silently running something else.
+Two arithmetics are built: the reference's ``int8=True`` path (scheme ``"all"``: QKV,
+out-projection and both FFN matmuls in int8, heads and attention in fp16), which is the
+default here, and its ``fp8=True`` path (the two FFN matmuls in e4m3 with ``amax/8`` scales,
+QKV and out-projection in fp16).  The plain fp16 arithmetic and the partial int8 schemes
+are not built: asking for them raises ``NotImplementedError`` instead of silently running
+something else.
 
 The weights are a *snapshot*: folded, quantised and uploaded once in the constructor.
 After a weight update, build a new ``FusedEncoder``.
@@ -76,19 +78,21 @@ class FusedEncoder:
                 f"kernel is compiled for d_model={self.D}, d_ff={self.DFF}, heads={self.H}; "
                 f"got {self.d_model}, {self.d_ff}, {self.n_heads}")
         self.fp8 = bool(fp8)
-        self.int8 = True if int8 is None else bool(int8)
-        if self.fp8 and self.int8 and int8 is not None:
+        self.int8 = (not self.fp8) if int8 is None else bool(int8)
+        if self.fp8 and self.int8:
             raise ValueError("fp8 and int8 quantise the same two matmuls; pick one")
         if int8_scheme not in SCHEMES:
             raise ValueError(f"int8_scheme must be one of {sorted(SCHEMES)}, got {int8_scheme!r}")
         if self.fp8:
-            raise NotImplementedError("the e4m3 FFN arithmetic is not built; use int8")
-        if not self.int8:
-            raise NotImplementedError("the fp16 arithmetic is not built; use int8 (the default)")
-        if int8_scheme != "all":
+            self.int8 = False
+        elif not self.int8:
+            raise NotImplementedError("the fp16 arithmetic is not built; use int8 (the default) "
+                                      "or fp8=True")
+        if self.int8 and int8_scheme != "all":
             raise NotImplementedError("only the 'all' int8 scheme is built")
         self.int8_scheme = int8_scheme
-        self.quant = SCHEMES[int8_scheme]
+        # the reference's kernel mode numbers: 3 = int8 on all four matmuls, 1 = e4m3 FFN
+        self.quant = 1 if self.fp8 else SCHEMES[int8_scheme]
         # Kept for callers that read it; the number of boards sharing a CTA never changes
         # a board's arithmetic, here as in the reference.
         self.two_boards = True if two_boards is None else bool(two_boards)
@@ -105,7 +109,9 @@ class FusedEncoder:
             self.n_value = int(net.value.weight.shape[0])
             self.vmode = self.VMODE[getattr(net, "value_head", "king")]
             self.rj_mode = self.RJMODE[getattr(net, "reinject", "none")]
-            self.blob = pack_blob(net)
+            if self.fp8 and self.rj_mode:
+                raise NotImplementedError("input re-injection is built for the int8 arithmetic only")
+            self.blob = pack_blob(net, "e4m3" if self.fp8 else "int8")
             self._create(self.blob)
 
     # -- construction helpers --------------------------------------------------
@@ -138,6 +144,9 @@ class FusedEncoder:
         nl, nv, vm = ctypes.c_int(0), ctypes.c_int(0), ctypes.c_int(0)
         _native.check(L.bf_info(h, ctypes.byref(nl), ctypes.byref(nv), ctypes.byref(vm)), "bf_info")
         self.n_layers, self.n_value, self.vmode = nl.value, nv.value, vm.value
+        head = blob[:32].cpu().numpy() if isinstance(blob, torch.Tensor) else np.asarray(blob[:32])
+        self.rj_mode, self.quant = (int(v) for v in head.view(np.uint32)[6:8])
+        self.fp8, self.int8 = self.quant == 1, self.quant != 1
         self.eps = 1e-5
         self._from_blob = True
         return self
@@ -156,7 +165,8 @@ class FusedEncoder:
     @property
     def label(self) -> str:
         """What this instance runs, for a bench header or a run log."""
-        return "int8 FFN+QKV+out_proj, 4 boards/CTA, tcgen05 (sm_100a)"
+        base = "e4m3 FFN" if self.quant == 1 else "int8 FFN+QKV+out_proj"
+        return base + ", 4 boards/CTA, tcgen05 (sm_100a)"
 
     @property
     def launches(self) -> int:

@@ -51,7 +51,8 @@ const char* bf_version(void);
 const char* bf_last_error(void);
 
 /* Create an evaluator on CUDA device `device` from a packed weight blob (host or device
- * memory; layout in brokefish_b200/nn/pack.py).  The blob is copied; the caller may free
+ * memory; layout in brokefish_b200/nn/pack.py; its header says whether it carries the int8
+ * arithmetic or the e4m3-FFN arithmetic, and the matching kernel arm runs).  The blob is copied; the caller may free
  * it afterwards.  Replaces the weight slabs `FusedEncoder.__init__` uploads
  * (brokefish/nn/cuda_impl.py:228, 370-371, 382-406). */
 int bf_create(const void* blob, size_t blob_bytes, int device, bf_handle** out);
@@ -153,9 +154,10 @@ int bf_noalloc_status(int device, int* status);
 /* Tensor-core self test (no network): one 128-row tile times a packed weight tile.
  *   mode 0: s8 x s8, N=128, K=256     mode 1: u8 x s8, N=128, K=256
  *   mode 2: s8 x s8, N=192, K=256     mode 3: f16 x f16 -> f32, N=96, K=256
+ *   mode 4: e4m3 x e4m3 -> f32, N=128, K=256
  *   a        device, [128, K] row-major (1 byte or 2 bytes per element)
  *   w_image  device, K/ (128 B) stage images of [N, 128 B] (pack.py: sw128_image)
- *   out      device, [128, N] s32 (modes 0-2) or f32 (mode 3)
+ *   out      device, [128, N] s32 (modes 0-2) or f32 (modes 3, 4)
  * Follows the exact-integer method of the reference's csrc/tests/tint8.cu:268-337. */
 int bf_selftest_umma(int device, int mode, const void* a, const void* w_image, void* out);
 

@@ -122,6 +122,14 @@ def main() -> int:
             out["emu_policy"] = p.numpy().astype(np.float32)
             out["emu_promo"] = pr.numpy().astype(np.float32)
             out["emu_value"] = v.numpy().astype(np.float32)
+            # the reference's e4m3 arithmetic as its kernel ships it: the two FFN matmuls,
+            # weights and activations, q_max 8, one scale over the whole 256-deep reduction
+            cfg8 = rq.QuantConfig(fmt="e4m3", weights=True, activations=True, acc16=False,
+                                  q_max=rq.Q_MAX, tile_k=rq.ROW_K)
+            p, pr, v = rq.emulated_forward(net, cfg8, which=("ffn1", "ffn2"))(
+                boards[:n_emu], control[:n_emu], rep[:n_emu])
+            out["e4m3_policy"] = p.numpy().astype(np.float16)
+            out["e4m3_value"] = v.numpy().astype(np.float32)
             half = RefNet().eval()
             half.load_state_dict(state, strict=True)
             half = half.half()
@@ -178,12 +186,14 @@ def main() -> int:
     acts16 = acts.half().float()
     qs, ss = rq.quantise_activations_int8(acts16)
     qu, su = rq.quantise_activations_int8(acts16.relu(), unsigned=True)
+    qb8, sc8 = rq.quantise_weights_bytes(wmat, rq.Q_MAX, tile_k=wmat.shape[1])
     lin = rq.int8_linear(acts16, wmat, torch.linspace(-1, 1, 256))
     np.savez_compressed(os.path.join(HERE, "scheme_kats.npz"),
                         w=wmat.numpy(), w_q=qb.numpy(), w_s=sc.numpy(),
                         acts=acts16.numpy(), q_s8=qs.numpy(), s_s8=ss.numpy(),
                         q_u8=qu.numpy(), s_u8=su.numpy(), lin=lin.numpy(),
-                        q_max=np.array([rq.Q_MAX_S8, rq.Q_MAX_U8]))
+                        q_max=np.array([rq.Q_MAX_S8, rq.Q_MAX_U8]),
+                        w_e4m3=qb8.numpy(), w_e4m3_s=sc8.numpy(), q_max_e4m3=np.array([rq.Q_MAX]))
     print("done")
     return 0
 

@@ -28,10 +28,12 @@ def test_constructor_refusals(nets):
         FusedEncoder(net, acc_dtype="bf16")
     with pytest.raises(NotImplementedError):
         FusedEncoder(net, acc_dtype="fp32")
-    with pytest.raises(NotImplementedError):
-        FusedEncoder(net, fp8=True, int8=False)
+    with pytest.raises(ValueError):
+        FusedEncoder(net, fp8=True, int8=True)
     with pytest.raises(NotImplementedError):
         FusedEncoder(net, int8=False)
+    with pytest.raises(NotImplementedError):
+        FusedEncoder(net, int8_scheme="ffn")
     with pytest.raises(ValueError):
         FusedEncoder(net, int8_scheme="nope")
     with pytest.raises(ValueError):

@@ -165,3 +165,24 @@ def test_reinjection_against_reference_fp32(pos256):
     zero.rj_coef = np.zeros_like(w.rj_coef)
     same = O.forward(zero, pos256["boards"][:4], pos256["control"][:4], pos256["rep"][:4])[0]
     assert np.array_equal(same.view(np.uint16), differs.view(np.uint16))
+
+
+def test_e4m3_scheme_against_reference(kats, states, pos256):
+    """The e4m3 FFN arithmetic: weight bytes and scales equal the reference's
+    `quantise_weights_bytes(q_max=8, tile_k=K)`; end to end, the oracle stays within 12 % of
+    max|logit| of the reference fp32 network and of the reference's own e4m3 emulation (which
+    itself is 7-8 % from fp32 on these networks: three mantissa bits)."""
+    q, s = O.quantise_weights_e4m3(kats["w"])
+    assert np.array_equal(O.decode_e4m3(kats["w_e4m3"]), q)
+    assert np.array_equal(s, kats["w_e4m3_s"].reshape(-1)) and kats["q_max_e4m3"][0] == 8.0
+    grid = O.round_e4m3(np.array([0.0, 448.0, 500.0, -600.0, 2.0 ** -9, 2.0 ** -10, 3 * 2.0 ** -10, 0.0145], np.float32))
+    assert list(grid) == [0.0, 448.0, 448.0, -448.0, 2.0 ** -9, 0.0, 2.0 ** -8, 0.013671875]
+    for name in ("A", "B"):
+        g = np.load(os.path.join(GOLDEN, f"ref_outputs_{name}.npz"))
+        w = O.prepare({k: v.numpy() for k, v in states[name].items()}, fmt="e4m3")
+        n = g["e4m3_policy"].shape[0]
+        pol, _, val = O.forward(w, pos256["boards"][:n], pos256["control"][:n], pos256["rep"][:n])
+        top = np.abs(g["fp32_policy"]).max()
+        assert np.abs(pol.astype(np.float32) - g["fp32_policy"][:n]).max() <= 0.12 * top
+        assert np.abs(pol.astype(np.float32) - g["e4m3_policy"].astype(np.float32)).max() <= 0.12 * top
+        assert np.abs(val - g["fp32_value"][:n]).max() <= 0.15
