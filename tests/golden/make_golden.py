@@ -2,7 +2,7 @@
 
 Run in a container that holds the reference checkout (read-only), from the repo root:
 
-    PYTHONDONTWRITEBYTECODE=1 python tests/golden/make_golden.py --reference /root/reference
+    PYTHONDONTWRITEBYTECODE=1 python tests/golden/make_golden.py --reference <reference checkout>
 
 It imports the reference (``brokefish.nn.model``, ``brokefish.nn.quant``,
 ``brokefish.nn.cuda_impl._fold_norm``, ``brokefish.env.torch_impl``) on CPU and writes,

@@ -1,0 +1,200 @@
+"""The product against the reference's OWN kernel, both on the same GPU.
+
+``oracle/build_ref.py`` compiles the reference's ``csrc/encoder.cu`` for sm_100a from the
+reference checkout and saves the weight slabs the reference's constructor derives; this file
+runs that kernel (``oracle/ref_kernel.py``) and the product on identical seeded positions and
+weights.  Skipped when the built reference is not present (it is not part of the history).
+
+The reference kernel and the product round differently inside a layer (the reference
+accumulates attention in fp16 on ``mma.sync``; its LayerNorm statistics come from warp
+shuffles in another order), and a single differing fp16 rounding moves an int8 operand by a
+step, so three implementations of the same scheme -- this kernel, the reference kernel and
+the numpy oracle -- sit about 1.5-2 % of max|logit| from one another after eight layers
+(measured on 4096 positions, set A: product vs reference kernel 0.0239, oracle vs reference
+kernel 0.0198, oracle vs product 0.0146, max|logit| 1.22).  The bars here are therefore:
+logits within 3 % of max(1, max|logit|) (measured 2.0 % A, 2.1 % B), value within 5e-2
+(measured 1.5e-2 A, 4.2e-2 B), masked argmax agreement >= 97 % (measured 97.8 % / 97.6 % of
+4043 playable positions) with EVERY disagreement a near tie by the reference kernel's own
+logits, and the product no further from the reference's fp32 network than the reference
+kernel is (x1.25).  The embedding, which involves no arithmetic order, is bit-identical.
+"""
+import os
+
+import numpy as np
+import pytest
+import torch
+
+from conftest import GOLDEN
+
+from oracle import int8_encoder as O
+from oracle import ref_kernel as R
+
+pytestmark = [pytest.mark.gpu,
+              pytest.mark.skipif(not R.available(), reason="oracle/_ref not built")]
+
+SETS = {"A": dict(seed=0, std=0.02, perturb_norms=False),
+        "B": dict(seed=0, std=None, perturb_norms=True)}
+
+
+def dev(a):
+    return torch.from_numpy(np.ascontiguousarray(a)).cuda()
+
+
+def inputs(pos, sl):
+    return dev(pos["boards"][sl]), dev(pos["control"][sl]), dev(pos["rep"][sl])
+
+
+def product(state_kw, **enc_kw):
+    from brokefish_b200.nn import encoder_impl
+    from brokefish_b200.nn.model import net_for_state, seeded_state
+    st = seeded_state(**state_kw)
+    net = net_for_state(st).eval()
+    net.load_state_dict(st)
+    return encoder_impl("cuda")(net, **enc_kw)
+
+
+def run_both(enc, ref, pos, sl):
+    mine = [t.cpu().numpy().copy() for t in enc.forward_full(*inputs(pos, sl))]
+    enc.check_status()
+    theirs = [t.cpu().numpy().copy() for t in ref.forward_full(*inputs(pos, sl))]
+    torch.cuda.synchronize()
+    return mine, theirs
+
+
+def rel_tol(theirs_pol, frac):
+    return frac * max(1.0, float(np.abs(theirs_pol.astype(np.float32)).max()))
+
+
+def check_argmax(pol, rpol, legal, floor, tol):
+    mine, theirs = O.masked_argmax(pol, legal), O.masked_argmax(rpol, legal)
+    playable = theirs >= 0
+    assert (mine[playable] == theirs[playable]).mean() >= floor
+    flat = rpol.astype(np.float32).reshape(rpol.shape[0], -1)
+    for i in np.where(playable & (mine != theirs))[0]:
+        assert flat[i, theirs[i]] - flat[i, mine[i]] <= tol
+
+
+@pytest.mark.parametrize("name", ["A", "B"])
+def test_int8_path_against_reference_kernel(name, pos256):
+    if not R.available(f"{name}_int8"):
+        pytest.skip("slabs missing")
+    enc, ref = product(SETS[name]), R.RefKernel(f"{name}_int8")
+    assert (ref.quant, ref.two_boards) == (3, 1)
+    sl = slice(0, 256)
+    (pol, pro, val), (rpol, rpro, rval) = run_both(enc, ref, pos256, sl)
+    tol = rel_tol(rpol, 3e-2)
+    assert np.abs(pol.astype(np.float32) - rpol.astype(np.float32)).max() <= tol
+    assert np.abs(pro.astype(np.float32) - rpro.astype(np.float32)).max() <= tol
+    assert np.abs(val - rval).max() <= 5e-2
+    check_argmax(pol, rpol, pos256["legal"][sl], 0.97, tol)
+    # against the reference's fp32 network (committed golden outputs): the product is not
+    # further from it than the reference's own kernel
+    g = np.load(os.path.join(GOLDEN, f"ref_outputs_{name}.npz"))
+    n = g["fp32_policy"].shape[0]
+    mine = np.abs(pol[:n].astype(np.float32) - g["fp32_policy"]).max()
+    theirs = np.abs(rpol[:n].astype(np.float32) - g["fp32_policy"]).max()
+    print(f"set {name}: max|logit - fp32| product {mine:.4f}, reference kernel {theirs:.4f}")
+    assert mine <= 1.25 * theirs
+    enc.close()
+
+
+def test_int8_full_batch_against_reference_kernel(pos4096):
+    if not R.available("A_int8"):
+        pytest.skip("slabs missing")
+    enc, ref = product(SETS["A"]), R.RefKernel("A_int8")
+    sl = slice(0, 4096)
+    (pol, pro, val), (rpol, rpro, rval) = run_both(enc, ref, pos4096, sl)
+    tol = rel_tol(rpol, 3e-2)
+    assert np.abs(pol.astype(np.float32) - rpol.astype(np.float32)).max() <= tol
+    assert np.abs(val - rval).max() <= 5e-2
+    check_argmax(pol, rpol, pos4096["legal"][sl], 0.97, tol)
+    enc.close()
+
+
+def test_embedding_equals_reference_kernel_bitwise(pos256):
+    if not R.available("B_int8"):
+        pytest.skip("slabs missing")
+    enc, ref = product(SETS["B"]), R.RefKernel("B_int8")
+    sl = slice(0, 200)
+    got = enc.forward_stage(*inputs(pos256, sl), 9).cpu().numpy()
+    want = ref.forward_stage(*inputs(pos256, sl), 9).cpu().numpy()
+    assert np.array_equal(got.view(np.uint16), want.view(np.uint16))
+    enc.close()
+
+
+def test_e4m3_path_against_reference_kernel(pos256):
+    if not R.available("A_e4m3"):
+        pytest.skip("slabs missing")
+    enc, ref = product(SETS["A"], fp8=True), R.RefKernel("A_e4m3")
+    assert ref.quant == 1
+    sl = slice(0, 128)
+    (pol, pro, val), (rpol, rpro, rval) = run_both(enc, ref, pos256, sl)
+    # two e4m3 implementations (measured 7.1 % of max|logit| on 4096 positions): the
+    # reference's own bar for a quantised path is 8 % of max|logit| against fp32
+    tol = rel_tol(rpol, 10e-2)
+    assert np.abs(pol.astype(np.float32) - rpol.astype(np.float32)).max() <= tol
+    assert np.abs(val - rval).max() <= 8e-2
+    enc.close()
+
+
+def test_reinjection_against_reference_kernel(pos256):
+    if not R.available("C_int8_rj"):
+        pytest.skip("slabs missing")
+    kw = dict(seed=7, std=None, perturb_norms=True, reinject="both")
+    enc, ref = product(kw), R.RefKernel("C_int8_rj")
+    assert ref.rj_mode == 2 and enc.rj_mode == 2
+    sl = slice(0, 96)
+    (pol, pro, val), (rpol, rpro, rval) = run_both(enc, ref, pos256, sl)
+    tol = rel_tol(rpol, 3e-2)
+    assert np.abs(pol.astype(np.float32) - rpol.astype(np.float32)).max() <= tol
+    assert np.abs(val - rval).max() <= 5e-2
+    enc.close()
+
+
+def test_pooled_wdl_value_against_reference_kernel(pos256):
+    if not R.available("V_int8_wdl"):
+        pytest.skip("slabs missing")
+    kw = dict(seed=3, std=0.02, perturb_norms=True, n_value=3, value_head="pooled")
+    enc, ref = product(kw), R.RefKernel("V_int8_wdl")
+    assert (ref.n_value, ref.vmode) == (3, 1)
+    sl = slice(0, 96)
+    (pol, pro, val), (rpol, rpro, rval) = run_both(enc, ref, pos256, sl)
+    assert np.abs(pol.astype(np.float32) - rpol.astype(np.float32)).max() <= rel_tol(rpol, 3e-2)
+    assert np.abs(val - rval).max() <= 5e-2
+    enc.close()
+
+
+def test_timing_report(pos4096):
+    """Not a bar: prints both kernels' device time on the 4096-position batch (CUDA events, 5
+    warm-ups, 20 timed launches each) so the summary under profiles/ can be reproduced with
+    ``pytest tests/test_gpu_reference_kernel.py -m gpu -s -k timing``."""
+    if not R.available("A_int8"):
+        pytest.skip("slabs missing")
+    args = inputs(pos4096, slice(0, 4096))
+
+    def ms(fn, n=20):
+        for _ in range(5):
+            fn()
+        torch.cuda.synchronize()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for _ in range(n):
+            fn()
+        e1.record()
+        torch.cuda.synchronize()
+        return e0.elapsed_time(e1) / n
+
+    enc = product(SETS["A"])
+    rows = [("product int8", ms(lambda: enc.forward_full(*args)))]
+    enc.close()
+    enc = product(SETS["A"], fp8=True)
+    rows.append(("product e4m3 FFN", ms(lambda: enc.forward_full(*args))))
+    enc.close()
+    for tag, label in (("A_int8", "reference kernel int8 (all four GEMMs, two boards per CTA)"),
+                       ("A_f16", "reference kernel fp16"), ("A_e4m3", "reference kernel e4m3 FFN")):
+        if R.available(tag):
+            ref = R.RefKernel(tag)
+            rows.append((label, ms(lambda: ref.forward_full(*args))))
+    for label, t in rows:
+        print(f"{label:64s} {t:7.3f} ms / 4096 positions  {4096 / t * 1e3:12.0f} pos/s")
+    assert all(t > 0 for _, t in rows)
