@@ -68,7 +68,11 @@ constexpr uint32_t SM_MISC = SM_BAR + 256;
 constexpr uint32_t SM_PROF = SM_MISC + 64;     // 16 x int64 phase cycle counters
 constexpr uint32_t SM_BYTES = SM_PROF + 128;
 constexpr uint32_t kSmemRequest = SM_BYTES + 1024;
-constexpr uint32_t kQStage = 24576, kRStage = 16384, kHeadStage = 12288;
+constexpr uint32_t kQStage = 24576, kRStage = 16384;
+// tail section: gamma, beta, three value rows (1280 halves), then the [96 x 256] head matrix in
+// mma.sync B-fragment order: uint4 [12 n-tiles][8 k-step pairs][32 lanes]
+constexpr int kTailHeadFrag = 1280;
+constexpr uint32_t kTailBytes = 2560u + 96u * 256u * 2u;
 // barrier indices
 constexpr int B_WQ_FULL = 0, B_WQ_EMPTY = 4, B_WR_FULL = 8, B_WR_EMPTY = 15, B_ACC_FULL = 22,
               B_ACC_EMPTY = 24, B_A_READY = 26, B_A2_READY = 27, B_COUNT = 29;
@@ -85,7 +89,10 @@ struct Params {
     const uint64_t* legal;
     int n, n_layers, n_value, vmode;
     int quant;                  // 3 = int8 on all four matmuls, 1 = e4m3 FFN with fp16 attention GEMMs
+    int rsqrt_rn;               // 1: correctly rounded 1/sqrt in the norms (what a CPU can reproduce);
+                                // 0: the hardware approximation, as the reference's rsqrtf (encoder.cu:597)
     float eps;
+    float one;                  // 1.0f (see quant16)
     const uint8_t* wstream;
     const uint8_t* lparams;
     const __half* emb;
@@ -114,6 +121,7 @@ struct RowCtx {
     uint32_t tm;                // TMEM base address with this warp's lane offset
     volatile int* abort_flag;
     int xpar;                   // exchange buffer parity
+    uint64_t one2;              // (1.0f, 1.0f) from the launch parameters, opaque to the compiler
     uint32_t full0, full1;      // accumulator slots consumed so far
     long grow;                  // global token row = board * 32 + token
     bool valid;                 // board < n
@@ -191,14 +199,17 @@ __device__ __forceinline__ uint32_t pack4(uint32_t a, uint32_t b, uint32_t c, ui
 }
 // 8 packed fp16 pairs (16 values) -> 16 quantised bytes: fp32 multiply by 1/scale, then the
 // rounding add, two lanes at a time.
-__device__ __forceinline__ uint4 quant16(const uint32_t* h, float inv) {
+// `one2` is 1.0 in both lanes, read from the launch parameters so that the compiler cannot see
+// its value: the rounding add is written as fma(x, 1, magic), and with a literal 1 the product
+// `x = h * inv` was fused into it, skipping the rounding of the product the scheme specifies.
+__device__ __forceinline__ uint4 quant16(const uint32_t* h, float inv, uint64_t one2) {
     const uint64_t inv2 = pk2(inv, inv), magic2 = pk2(12582912.0f, 12582912.0f);
     uint32_t o[4];
 #pragma unroll
     for (int k = 0; k < 4; ++k) {
         float a0, a1, b0, b1;
-        upk2(add2_after_mul(mul2(h2_to_f2(h[2 * k]), inv2), magic2), a0, a1);
-        upk2(add2_after_mul(mul2(h2_to_f2(h[2 * k + 1]), inv2), magic2), b0, b1);
+        upk2(fma2(mul2(h2_to_f2(h[2 * k]), inv2), one2, magic2), a0, a1);
+        upk2(fma2(mul2(h2_to_f2(h[2 * k + 1]), inv2), one2, magic2), b0, b1);
         o[k] = pack4(__float_as_uint(a0), __float_as_uint(a1), __float_as_uint(b0), __float_as_uint(b1));
     }
     return make_uint4(o[0], o[1], o[2], o[3]);
@@ -217,9 +228,9 @@ __device__ __forceinline__ uint4 quant16_e4m3(const uint32_t* h, float inv) {
     return make_uint4(o[0], o[1], o[2], o[3]);
 }
 template <bool kFP8>
-__device__ __forceinline__ uint4 quant16_any(const uint32_t* h, float inv) {
+__device__ __forceinline__ uint4 quant16_any(const uint32_t* h, float inv, uint64_t one2) {
     if (kFP8) return quant16_e4m3(h, inv);
-    return quant16(h, inv);
+    return quant16(h, inv, one2);
 }
 // Address of 16-byte group `chunk` of row `row` in a [rows][128 B] swizzled tile.
 __device__ __forceinline__ uint32_t sw_off(int row, int chunk) {
@@ -284,11 +295,11 @@ __device__ __forceinline__ void store_words(void* dst, const uint32_t* w) {
 // quantisation into the A operand (returns the row scale) or, for the final norm, by the
 // affine and the fp16 store into the head GEMM's A operand.
 //
-// Statistics: fp32, one pass, variance clamped at zero (encoder.cu:584-598); summation order
-// (mirrored by the CPU oracle): within a quarter even and odd columns accumulate separately
-// and sequentially, then even + odd; the quarters combine as (q0 + q1) + (q2 + q3).  1/sqrt
-// is correctly rounded where the reference uses the hardware approximation.
-// x_hat = fp16((x - mean) * rstd).
+// Statistics: fp32, one pass, variance clamped at zero, in the reference's own summation
+// order (encoder.cu:566-598; the CPU oracle mirrors it): eight contiguous columns summed one
+// after the other, then the 32 partial sums combined by the butterfly 16, 8, 4, 2, 1.  1/sqrt
+// is the hardware approximation the reference uses, or correctly rounded when the launch asks
+// for it (`rsqrt_rn`, the only form a CPU can reproduce).  x_hat = fp16((x - mean) * rstd).
 //
 // Quantisation (int8_gemm.cuh:159-199): scale = amax(x_hat)/127, all-zero row -> 1.  The map
 // x -> x_hat is monotone (every rounding in it is), so amax(x_hat) is reached at the row's
@@ -338,7 +349,13 @@ __device__ __forceinline__ void reinject32(const RowCtx& c, const Params& p, int
 template <bool kDbg, bool kRJ, bool kFP8>
 __device__ __forceinline__ float ln_stage(RowCtx& c, const Params& p, bool final_norm, bool dump_x,
                                           bool dump_xn, bool capture, int site, bool f16_out = false) {
-    uint64_t sum2 = pk2(0.f, 0.f), sq2 = pk2(0.f, 0.f);      // (even, odd) column lanes
+    // Partial sums in the reference's order (encoder.cu:566-583): "lane" l of the reference
+    // owns columns 8l..8l+7 and adds them one after the other, then lanes combine by the
+    // butterfly 16, 8, 4, 2, 1.  This thread's 64 columns are lanes 4qt..4qt+3 and their
+    // partners 16 + 4qt..: it forms P[l] + P[l+16] for its four l (level 16); levels 8 and 4
+    // pair it with the other three quarters of the row, levels 2 and 1 are local again.
+    // Two lanes ride in one packed register: (x[l][j], x[l+1][j]).
+    uint64_t as0 = 0, as1 = 0, aq0 = 0, aq1 = 0;
     __half2 mn = __float2half2_rn(65504.0f), mx = __float2half2_rn(-65504.0f);
 #pragma unroll 1
     for (int u = 0; u < 2; ++u) {
@@ -347,30 +364,80 @@ __device__ __forceinline__ float ln_stage(RowCtx& c, const Params& p, bool final
         tmem_wait_ld();
         if (kDbg && dump_x && c.valid) store_words<16>(p.y + c.grow * kD + 128 * u + 32 * c.qt, x);
         if (kRJ && site >= 0) reinject32(c, p, site, 128 * u + 32 * c.qt, x);
+        uint64_t s2[2], q2[2];
+#pragma unroll
+        for (int pr = 0; pr < 2; ++pr) {
+            s2[pr] = pk2(0.f, 0.f);
+            q2[pr] = pk2(0.f, 0.f);
+#pragma unroll
+            for (int k = 0; k < 4; ++k) {
+                const uint32_t wa = x[8 * pr + k], wb = x[8 * pr + 4 + k];
+                uint64_t f = h2_to_f2(__byte_perm(wa, wb, 0x5410));
+                s2[pr] = add2(s2[pr], f);
+                q2[pr] = fma2(f, f, q2[pr]);
+                f = h2_to_f2(__byte_perm(wa, wb, 0x7632));
+                s2[pr] = add2(s2[pr], f);
+                q2[pr] = fma2(f, f, q2[pr]);
+            }
+        }
 #pragma unroll
         for (int i = 0; i < 16; ++i) {
-            const __half2 h = as_h2(x[i]);
-            const uint64_t f = h2_to_f2(x[i]);
-            sum2 = add2(sum2, f);
-            sq2 = fma2(f, f, sq2);
-            mn = __hmin2(mn, h);
-            mx = __hmax2(mx, h);
+            mn = __hmin2(mn, as_h2(x[i]));
+            mx = __hmax2(mx, as_h2(x[i]));
+        }
+        if (u == 0) {
+            as0 = s2[0]; as1 = s2[1]; aq0 = q2[0]; aq1 = q2[1];
+        } else {
+            as0 = add2(as0, s2[0]); as1 = add2(as1, s2[1]);
+            aq0 = add2(aq0, q2[0]); aq1 = add2(aq1, q2[1]);
         }
     }
-    float s_lo, s_hi, q_lo, q_hi;
-    upk2(sum2, s_lo, s_hi);
-    upk2(sq2, q_lo, q_hi);
-    float4 all[4];
-    exchange4(c, make_float4(__fadd_rn(s_lo, s_hi), __fadd_rn(q_lo, q_hi),
-                             fminf(__low2float(mn), __high2float(mn)),
-                             fmaxf(__low2float(mx), __high2float(mx))), all);
-    const float tot = __fadd_rn(__fadd_rn(all[0].x, all[1].x), __fadd_rn(all[2].x, all[3].x));
-    const float totq = __fadd_rn(__fadd_rn(all[0].y, all[1].y), __fadd_rn(all[2].y, all[3].y));
-    const float xmin = fminf(fminf(all[0].z, all[1].z), fminf(all[2].z, all[3].z));
-    const float xmax = fmaxf(fmaxf(all[0].w, all[1].w), fmaxf(all[2].w, all[3].w));
+    // Exchange among the row's four threads through this board's slice of the staging region
+    // (idle between the MMAs that last read it and the next staging write; the second barrier
+    // keeps a fast warp from overwriting it): [sums | squares] in the first 16 KB block,
+    // [min, max] in the second.
+    float tot, totq, xmin, xmax;
+    {
+        const uint32_t xb = c.sm_r + 4096u * c.q, slot = 16u * (32 * c.qt + c.lane);
+        float f0, f1, f2, f3;
+        upk2(as0, f0, f1); upk2(as1, f2, f3);
+        sts_f4(xb + slot, make_float4(f0, f1, f2, f3));
+        upk2(aq0, f0, f1); upk2(aq1, f2, f3);
+        sts_f4(xb + 2048u + slot, make_float4(f0, f1, f2, f3));
+        sts_f4(xb + 16384u + slot, make_float4(fminf(__low2float(mn), __high2float(mn)),
+                                               fmaxf(__low2float(mx), __high2float(mx)), 0.f, 0.f));
+        board_sync(c);
+        float4 S[4], Q[4], M[4];
+#pragma unroll
+        for (int k = 0; k < 4; ++k) {
+            S[k] = lds_f4(xb + 16u * (32 * k + c.lane));
+            Q[k] = lds_f4(xb + 2048u + 16u * (32 * k + c.lane));
+            M[k] = lds_f4(xb + 16384u + 16u * (32 * k + c.lane));
+        }
+        board_sync(c);
+        // levels 8 and 4: (A_q0 + A_q2) + (A_q1 + A_q3) for each of the four lanes; level 2:
+        // lanes (0,2) and (1,3); level 1: the last add
+        const uint64_t c01 = add2(add2(pk2(S[0].x, S[0].y), pk2(S[2].x, S[2].y)),
+                                  add2(pk2(S[1].x, S[1].y), pk2(S[3].x, S[3].y)));
+        const uint64_t c23 = add2(add2(pk2(S[0].z, S[0].w), pk2(S[2].z, S[2].w)),
+                                  add2(pk2(S[1].z, S[1].w), pk2(S[3].z, S[3].w)));
+        const uint64_t d01 = add2(add2(pk2(Q[0].x, Q[0].y), pk2(Q[2].x, Q[2].y)),
+                                  add2(pk2(Q[1].x, Q[1].y), pk2(Q[3].x, Q[3].y)));
+        const uint64_t d23 = add2(add2(pk2(Q[0].z, Q[0].w), pk2(Q[2].z, Q[2].w)),
+                                  add2(pk2(Q[1].z, Q[1].w), pk2(Q[3].z, Q[3].w)));
+        float a, b;
+        upk2(add2(c01, c23), a, b);
+        tot = __fadd_rn(a, b);
+        upk2(add2(d01, d23), a, b);
+        totq = __fadd_rn(a, b);
+        xmin = fminf(fminf(M[0].x, M[1].x), fminf(M[2].x, M[3].x));
+        xmax = fmaxf(fmaxf(M[0].y, M[1].y), fmaxf(M[2].y, M[3].y));
+    }
     const float mean = __fmul_rn(tot, 1.0f / 256.0f);
-    const float var = fmaxf(__fmaf_rn(-mean, mean, __fmul_rn(totq, 1.0f / 256.0f)), 0.f);
-    const float rstd = __frsqrt_rn(__fadd_rn(var, p.eps));
+    // `sq / Dm - mean * mean` (encoder.cu:596): the product is rounded on its own, the
+    // scaling by 1/256 is exact
+    const float var = fmaxf(__fsub_rn(__fmul_rn(totq, 1.0f / 256.0f), __fmul_rn(mean, mean)), 0.f);
+    const float rstd = p.rsqrt_rn ? __frsqrt_rn(__fadd_rn(var, p.eps)) : rsqrtf(__fadd_rn(var, p.eps));
     const float e_lo = __half2float(__float2half_rn(__fmul_rn(__fsub_rn(xmin, mean), rstd)));
     const float e_hi = __half2float(__float2half_rn(__fmul_rn(__fsub_rn(xmax, mean), rstd)));
     const float amax = fmaxf(fabsf(e_lo), fabsf(e_hi));
@@ -397,7 +464,7 @@ __device__ __forceinline__ float ln_stage(RowCtx& c, const Params& p, bool final
             } else {
 #pragma unroll
                 for (int v = 0; v < 2; ++v) {
-                    const uint4 qv = quant16_any<kFP8>(&x[8 * v], inv);
+                    const uint4 qv = quant16_any<kFP8>(&x[8 * v], inv, c.one2);
                     sts128(c.sm_a + u * 16384 + sw_off(c.row, 2 * c.qt + v), qv);
                     if (kDbg && capture && c.valid) *reinterpret_cast<uint4*>(p.cap_a + c.grow * kD + col + 16 * v) = qv;
                 }
@@ -426,9 +493,10 @@ __device__ __forceinline__ float ln_stage(RowCtx& c, const Params& p, bool final
 }
 
 // Half of one (board, head) attention unit: 16 query rows against the board's 32 keys, on the
-// staged fp16 Q/K/V of a head pair.  S = Q K^T (scale pre-folded), dead keys -inf, fp32
-// softmax with the hardware 2^x, P rounded to fp16, O = P V; both products accumulate in fp32
-// where the reference accumulates in fp16 (encoder.cu:715-797).  Warp (q, qt) takes head
+// staged fp16 Q/K/V of a head pair, instruction for instruction what the reference does
+// (encoder.cu:715-797): S = Q K^T (scale pre-folded) on m16n8k16 with fp16 accumulators, dims
+// 0-15 before 16-31; dead keys -inf; row max; __expf(s - max); the row sum in the reference's
+// order; P = fp16(p * (1 / sum)); O = P V on the same instruction, keys 0-15 before 16-31.  Warp (q, qt) takes head
 // qt & 1 of the pair and query rows 16 * (qt >> 1) .. +15; the result overwrites its own
 // block of Q.
 __device__ __forceinline__ void attention_unit(const RowCtx& c, uint32_t alive) {
@@ -441,77 +509,66 @@ __device__ __forceinline__ void attention_unit(const RowCtx& c, uint32_t alive) 
         const int row = rq + (lane & 15);
         ldmatrix_x4(qa[kk], qs + sw_off(row, 4 * hh + 2 * kk + (lane >> 4)));
     }
-    float s[4][4];
-#pragma unroll
-    for (int nt = 0; nt < 4; ++nt)
-#pragma unroll
-        for (int k = 0; k < 4; ++k) s[nt][k] = 0.f;
+    // s[nt] = {row g, row g + 8} x key columns 8 nt + 2t, +1, as packed fp16 pairs
+    uint32_t s[4][2];
 #pragma unroll
     for (int nt = 0; nt < 4; ++nt) {
+        s[nt][0] = s[nt][1] = 0u;
         uint32_t kb[4];
         const int row = r0 + 8 * nt + (lane & 7);
         ldmatrix_x4(kb, ks + sw_off(row, 4 * hh + (lane >> 3)));
-        mma_f16_f32(s[nt], qa[0], kb[0], kb[1]);
-        mma_f16_f32(s[nt], qa[1], kb[2], kb[3]);
+        mma_f16_f16(s[nt], qa[0], kb[0], kb[1]);      // dims 0-15, then 16-31
+        mma_f16_f16(s[nt], qa[1], kb[2], kb[3]);
     }
-    // dead keys get -inf added; this lane's eight key columns are 8*nt + 2*t + {0,1}
-    float kb_mask[4][2];
-#pragma unroll
-    for (int nt = 0; nt < 4; ++nt)
-#pragma unroll
-        for (int k = 0; k < 2; ++k) kb_mask[nt][k] = ((alive >> (8 * nt + 2 * t + k)) & 1u) ? 0.f : -INFINITY;
-    uint32_t pa[2][4];
 #pragma unroll
     for (int hi = 0; hi < 2; ++hi) {
+        float pv[4][2];
         float mx = -INFINITY;
 #pragma unroll
-        for (int nt = 0; nt < 4; ++nt)
-#pragma unroll
-            for (int k = 0; k < 2; ++k) {
-                float& v = s[nt][2 * hi + k];
-                v += kb_mask[nt][k];
-                mx = fmaxf(mx, v);
-            }
+        for (int nt = 0; nt < 4; ++nt) {
+            const __half2 val = as_h2(s[nt][hi]);
+            const int col = 8 * nt + 2 * t;
+            pv[nt][0] = ((alive >> col) & 1u) ? __low2float(val) : -INFINITY;
+            pv[nt][1] = ((alive >> (col + 1)) & 1u) ? __high2float(val) : -INFINITY;
+            mx = fmaxf(mx, fmaxf(pv[nt][0], pv[nt][1]));
+        }
         mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 1));
         mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 2));
-        // exp(v - mx) = 2^(v*log2e - mx*log2e); an all-dead row keeps the reference's NaN
-        const float nmx = -mx * 1.4426950408889634f;
         float sum = 0.f;
 #pragma unroll
-        for (int nt = 0; nt < 4; ++nt)
-#pragma unroll
-            for (int k = 0; k < 2; ++k) {
-                float& v = s[nt][2 * hi + k];
-                v = ex2_approx(__fmaf_rn(v, 1.4426950408889634f, nmx));
-                sum += v;
-            }
+        for (int nt = 0; nt < 4; ++nt) {
+            pv[nt][0] = __expf(pv[nt][0] - mx);       // an all-dead row keeps the reference's NaN
+            pv[nt][1] = __expf(pv[nt][1] - mx);
+            sum += pv[nt][0] + pv[nt][1];
+        }
         sum += __shfl_xor_sync(0xffffffffu, sum, 1);
         sum += __shfl_xor_sync(0xffffffffu, sum, 2);
         const float inv = 1.0f / sum;
 #pragma unroll
-        for (int kk = 0; kk < 2; ++kk) {
-            pa[kk][hi] = pack_h2(s[2 * kk][2 * hi] * inv, s[2 * kk][2 * hi + 1] * inv);
-            pa[kk][2 + hi] = pack_h2(s[2 * kk + 1][2 * hi] * inv, s[2 * kk + 1][2 * hi + 1] * inv);
-        }
+        for (int nt = 0; nt < 4; ++nt) s[nt][hi] = pack_h2(pv[nt][0] * inv, pv[nt][1] * inv);
     }
-    float o[4][4];
+    // P's accumulator fragments are already A fragments: keys 16 kk .. +15 are n-tiles 2kk, 2kk+1
+    uint32_t pa[2][4];
 #pragma unroll
-    for (int nt = 0; nt < 4; ++nt)
-#pragma unroll
-        for (int k = 0; k < 4; ++k) o[nt][k] = 0.f;
+    for (int kk = 0; kk < 2; ++kk) {
+        pa[kk][0] = s[2 * kk][0];     pa[kk][1] = s[2 * kk][1];
+        pa[kk][2] = s[2 * kk + 1][0]; pa[kk][3] = s[2 * kk + 1][1];
+    }
+    uint32_t o[4][2];
 #pragma unroll
     for (int nt = 0; nt < 4; ++nt) {
+        o[nt][0] = o[nt][1] = 0u;
         uint32_t vb[4];
         ldmatrix_x4_trans(vb, vs + sw_off(r0 + lane, 4 * hh + nt));
-        mma_f16_f32(o[nt], pa[0], vb[0], vb[1]);
-        mma_f16_f32(o[nt], pa[1], vb[2], vb[3]);
+        mma_f16_f16(o[nt], pa[0], vb[0], vb[1]);      // keys 0-15, then 16-31
+        mma_f16_f16(o[nt], pa[1], vb[2], vb[3]);
     }
     __syncwarp();   // every lane's Q fragments are in registers before Q is overwritten
 #pragma unroll
     for (int nt = 0; nt < 4; ++nt) {
         const int row = rq + g;
-        sts32(qs + sw_off(row, 4 * hh + nt) + 4 * t, pack_h2(o[nt][0], o[nt][1]));
-        sts32(qs + sw_off(row + 8, 4 * hh + nt) + 4 * t, pack_h2(o[nt][2], o[nt][3]));
+        sts32(qs + sw_off(row, 4 * hh + nt) + 4 * t, o[nt][0]);
+        sts32(qs + sw_off(row + 8, 4 * hh + nt) + 4 * t, o[nt][1]);
     }
 }
 
@@ -599,7 +656,7 @@ __device__ __forceinline__ void attention_block(RowCtx& c, const Params& p, cons
             uint32_t oh[8];
             tmem_ld8(c.tm + TM_OY + 32 * j + 8 * c.qt, oh);
             tmem_wait_ld();
-            const uint4 v = quant16(oh, inv);
+            const uint4 v = quant16(oh, inv, c.one2);
             sts128(c.sm_a + (j >> 1) * 16384 + sw_off(c.row, 4 * (j & 1) + c.qt), v);
             if (capo) *reinterpret_cast<uint4*>(p.cap_a + c.grow * kD + 64 * j + 16 * c.qt) = v;
         }
@@ -661,7 +718,7 @@ __device__ __forceinline__ void ffn_block(RowCtx& c, const Params& p, const Laye
             for (int jh = 0; jh < 2; ++jh)
 #pragma unroll
                 for (int k = 0; k < 2; ++k) {
-                    const uint4 v = quant16_any<kFP8>(&hid[16 * jh + 8 * k], inv);
+                    const uint4 v = quant16_any<kFP8>(&hid[16 * jh + 8 * k], inv, c.one2);
                     sts128(c.sm_r + (ch & 1) * 32768 + jh * 16384 + sw_off(c.row, 2 * c.qt + k), v);
                     if (caph) *reinterpret_cast<uint4*>(p.cap_a + c.grow * kD + 128 * jh + 32 * c.qt + 16 * k) = v;
                 }
@@ -686,8 +743,10 @@ __device__ __forceinline__ void ffn_block(RowCtx& c, const Params& p, const Laye
                     uint64_t f = kFP8 ? pk2(__uint_as_float(acc[2 * i]), __uint_as_float(acc[2 * i + 1]))
                                       : pk2(static_cast<float>(static_cast<int>(acc[2 * i])),
                                             static_cast<float>(static_cast<int>(acc[2 * i + 1])));
-                    f = mul2(mul2(f, s1_2), s2_2);
-                    if (ch > 0) f = add2_after_mul(f, h2_to_f2(run[i]));
+                    // `float(acc) * sa * sw + float(run)` (int8_gemm.cuh:285-294): the compiler
+                    // fuses the second product with the sum in the reference, so it is one fma here
+                    f = mul2(f, s1_2);
+                    f = ch > 0 ? fma2(f, s2_2, h2_to_f2(run[i])) : mul2(f, s2_2);
                     run[i] = f2_to_h2(f);
                 }
                 if (ch < 3) {
@@ -764,7 +823,7 @@ __device__ __forceinline__ void prenorm_value(RowCtx& c, const Params& p, uint32
     const float tot = (all[0].x + all[1].x) + (all[2].x + all[3].x);
     const float totq = (all[0].y + all[1].y) + (all[2].y + all[3].y);
     const float mean = tot * (1.0f / 256.0f);
-    const float rstd = rsqrtf(fmaxf(totq * (1.0f / 256.0f) - mean * mean, 0.f) + p.eps);
+    const float rstd = rsqrtf(fmaxf(__fsub_rn(totq * (1.0f / 256.0f), __fmul_rn(mean, mean)), 0.f) + p.eps);
     float t1[3], t2[3], t3[3];
     exchange4(c, make_float4(s1[0], s1[1], s1[2], 0.f), all);
     t1[0] = (all[0].x + all[1].x) + (all[2].x + all[3].x);
@@ -842,7 +901,6 @@ __device__ __forceinline__ void row_warps_tile(RowCtx& c, const Params& p, int t
                             (dbg == 10 && !odd && ph > 0 && layer - 1 == p.debug_layer);
         if (ph == n_ph) {
             ln_stage<kDbg, kRJ, kFP8>(c, p, true, dump_x, dbg == 8, false, -1);
-            row_publish(c, B_A_READY);
             break;
         }
         const bool cap = layer == p.cap_layer;
@@ -867,24 +925,80 @@ __device__ __forceinline__ void row_warps_tile(RowCtx& c, const Params& p, int t
         else      ffn_block<kDbg, kFP8>(c, p, lp, sa, cap);
     }
 
-    // ---- heads: fp16 GEMM [128 x 256] x [96 x 256]^T, fp32 accumulate, rounded to fp16
-    //      (encoder.cu:894-1079; the reference accumulates in fp16) -------------------------
+    // ---- heads: fp16 product [32 x 256] x [96 x 256]^T per board on the row warps, with
+    //      mma.sync m16n8k16 and fp16 accumulators, k-steps in rising order, as the reference
+    //      computes it (encoder.cu:309-352, 918-927), so the logits carry its roundings.
+    //      Warp qt of the board takes output columns 24 qt .. 24 qt + 23 (three n-tiles) of
+    //      both 16-row tiles; the fragments go through a staging tile in the (idle) A-operand
+    //      region so that each thread then finds its own row's 16 policy columns. ----
     float pre[3] = {0.f, 0.f, 0.f};
     if (p.vmode == 2) prenorm_value(c, p, c.valid ? alive : 0xffffffffu, pre);
-    row_wait_acc<kDbg>(c, 0, PH_LN);
+    prof_mark<kDbg>(c, PH_LN);
+    constexpr uint32_t kHeadPitch = 208;                 // bytes per staged row: 96 halves + pad
+    const uint32_t stage = c.sm_a + 8192u * c.q;
+    board_sync(c);                                       // this board's rows of the operand are written
     {
-        uint32_t acc[16], aux[16];
-        tmem_ld16(c.tm + TM_ACC + 16 * c.qt, acc);
-        if (c.qt == 0) tmem_ld16(c.tm + TM_ACC + 64, aux);
-        tmem_wait_ld();
-        row_release_acc(c, 0);
+        const uint4* hf = reinterpret_cast<const uint4*>(p.tail + kTailHeadFrag) + c.lane;
+        uint32_t acc[3][2][2];
+#pragma unroll
+        for (int jj = 0; jj < 3; ++jj)
+#pragma unroll
+            for (int m = 0; m < 2; ++m) acc[jj][m][0] = acc[jj][m][1] = 0u;
+        uint4 bw[3];
+#pragma unroll
+        for (int jj = 0; jj < 3; ++jj) bw[jj] = __ldg(hf + ((3 * c.qt + jj) * 8) * 32);
+#pragma unroll 1
+        for (int kp = 0; kp < 8; ++kp) {
+            uint4 nx[3];
+            const int kn = kp < 7 ? kp + 1 : kp;
+#pragma unroll
+            for (int jj = 0; jj < 3; ++jj) nx[jj] = __ldg(hf + ((3 * c.qt + jj) * 8 + kn) * 32);
+#pragma unroll
+            for (int h = 0; h < 2; ++h) {
+                const int ks = 2 * kp + h;
+#pragma unroll
+                for (int m = 0; m < 2; ++m) {
+                    uint32_t af[4];
+                    ldmatrix_x4(af, c.sm_r + (ks >> 2) * 16384 +
+                                        sw_off(32 * c.q + 16 * m + (c.lane & 15), 2 * (ks & 3) + (c.lane >> 4)));
+#pragma unroll
+                    for (int jj = 0; jj < 3; ++jj)
+                        mma_f16_f16(acc[jj][m], af, h ? bw[jj].z : bw[jj].x, h ? bw[jj].w : bw[jj].y);
+                }
+            }
+#pragma unroll
+            for (int jj = 0; jj < 3; ++jj) bw[jj] = nx[jj];
+        }
+        const int g = c.lane >> 2, t = c.lane & 3;
+#pragma unroll
+        for (int jj = 0; jj < 3; ++jj)
+#pragma unroll
+            for (int m = 0; m < 2; ++m) {
+                const uint32_t at = stage + (16 * m + g) * kHeadPitch + (8 * (3 * c.qt + jj) + 2 * t) * 2;
+                sts32(at, acc[jj][m][0]);
+                sts32(at + 8 * kHeadPitch, acc[jj][m][1]);
+            }
+    }
+    board_sync(c);                                       // the board's 32 x 96 logits are staged
+    {
+        uint32_t lgw[8], aux[4] = {0u, 0u, 0u, 0u};
+        {
+            const uint4 v0 = lds128(stage + c.lane * kHeadPitch + 32 * c.qt);
+            const uint4 v1 = lds128(stage + c.lane * kHeadPitch + 32 * c.qt + 16);
+            lgw[0] = v0.x; lgw[1] = v0.y; lgw[2] = v0.z; lgw[3] = v0.w;
+            lgw[4] = v1.x; lgw[5] = v1.y; lgw[6] = v1.z; lgw[7] = v1.w;
+            if (c.qt == 0) {
+                const uint4 va = lds128(stage + c.lane * kHeadPitch + 128);   // columns 64..71
+                aux[0] = va.x; aux[1] = va.y; aux[2] = va.z; aux[3] = va.w;
+            }
+        }
         uint32_t lg[8];
         unsigned long long lw = ~0ull;
         if (p.legal != nullptr && c.valid) lw = p.legal[c.grow];
         const uint32_t bits = static_cast<uint32_t>(lw >> (16 * c.qt)) & 0xffffu;
 #pragma unroll
         for (int i = 0; i < 8; ++i) {
-            uint32_t v = pack_h2(__uint_as_float(acc[2 * i]), __uint_as_float(acc[2 * i + 1]));
+            uint32_t v = lgw[i];
             if (!((bits >> (2 * i)) & 1u)) v = (v & 0xffff0000u) | 0xfc00u;
             if (!((bits >> (2 * i + 1)) & 1u)) v = (v & 0x0000ffffu) | 0xfc000000u;
             lg[i] = v;
@@ -892,22 +1006,20 @@ __device__ __forceinline__ void row_warps_tile(RowCtx& c, const Params& p, int t
         if (c.valid && p.policy != nullptr) store_words<8>(p.policy + c.grow * 64 + 16 * c.qt, lg);
         if (c.qt == 0) {
             if (c.valid && p.promo != nullptr)
-                *reinterpret_cast<uint2*>(p.promo + c.grow * 4) =
-                    make_uint2(pack_h2(__uint_as_float(aux[0]), __uint_as_float(aux[1])),
-                               pack_h2(__uint_as_float(aux[2]), __uint_as_float(aux[3])));
-            // value logits are read after their fp16 rounding, as the reference does
-            float a = __half2float(__float2half_rn(__uint_as_float(aux[4])));
-            float b = __half2float(__float2half_rn(__uint_as_float(aux[5])));
-            float d = __half2float(__float2half_rn(__uint_as_float(aux[6])));
+                *reinterpret_cast<uint2*>(p.promo + c.grow * 4) = make_uint2(aux[0], aux[1]);
+            // value logits: the fp16 head outputs in columns 68, 69, 70
+            float a = __low2float(as_h2(aux[2])), b = __high2float(as_h2(aux[2]));
+            float d = __low2float(as_h2(aux[3]));
             if (p.vmode == 1) {
-                const bool live = (alive >> c.lane) & 1u;
-                a = live ? a : 0.f; b = live ? b : 0.f; d = live ? d : 0.f;
-#pragma unroll
-                for (int off = 16; off; off >>= 1) {
-                    a += __shfl_xor_sync(0xffffffffu, a, off);
-                    b += __shfl_xor_sync(0xffffffffu, b, off);
-                    d += __shfl_xor_sync(0xffffffffu, d, off);
+                // live tokens in slot order, one after the other (encoder.cu:1040-1057)
+                float ta = 0.f, tb = 0.f, td = 0.f;
+#pragma unroll 1
+                for (int tt = 0; tt < kT; ++tt) {
+                    const float at = __shfl_sync(0xffffffffu, a, tt), bt = __shfl_sync(0xffffffffu, b, tt);
+                    const float dt = __shfl_sync(0xffffffffu, d, tt);
+                    if ((alive >> tt) & 1u) { ta += at; tb += bt; td += dt; }
                 }
+                a = ta; b = tb; d = td;
                 const int nlive = __popc(alive);
                 const float inv = 1.0f / static_cast<float>(nlive > 0 ? nlive : 1);
                 a *= inv; b *= inv; d *= inv;
@@ -946,9 +1058,8 @@ __device__ __forceinline__ void producer_loop(uint32_t smem, volatile int* abort
     uint32_t qi = 0, ri = 0;   // stages issued into the QKV ring / the 16 KB ring
     for (int tile = first_tile; tile < n_tiles; tile += tile_step) {
         const uint8_t* src = p.wstream;
-        for (int layer = 0; layer <= p.n_layers; ++layer) {
-            const bool head = layer == p.n_layers;
-            if (!head) {
+        for (int layer = 0; layer < p.n_layers; ++layer) {
+            {
                 // the two rings share memory: the 16 KB ring must be drained first
                 for (uint32_t s = 0; s < kRS; ++s)
                     mbar_wait(bar_addr(smem, B_WR_EMPTY + s), (uses(ri, kRS, s) - 1u) & 1u, abort_flag, kErrProducer);
@@ -962,9 +1073,9 @@ __device__ __forceinline__ void producer_loop(uint32_t smem, volatile int* abort
                 for (uint32_t s = 0; s < kQS; ++s)
                     mbar_wait(bar_addr(smem, B_WQ_EMPTY + s), (uses(qi, kQS, s) - 1u) & 1u, abort_flag, kErrProducer);
             }
-            // out-projection (2 units) and the 16 FFN units (2 K-slabs each), or the 4 head slabs
-            const int n_st = head ? 4 : 2 * C::kAttnSlabs + 32;
-            const uint32_t bytes = head ? kHeadStage : kRStage;
+            // out-projection (2 units) and the 16 FFN units (2 K-slabs each)
+            const int n_st = 2 * C::kAttnSlabs + 32;
+            const uint32_t bytes = kRStage;
             for (int st = 0; st < n_st; ++st, ++ri) {
                 const uint32_t s = ri % kRS;
                 mbar_wait(bar_addr(smem, B_WR_EMPTY + s), (ri / kRS - 1u) & 1u, abort_flag, kErrProducer);
@@ -1051,7 +1162,6 @@ __device__ __forceinline__ void mma_loop(uint32_t smem, uint32_t tmem, volatile 
                                      : umma_idesc(kAccS32, kFmtS8, kFmtS8, 128, 128);
     constexpr uint32_t kI_FF2 = kFP8 ? umma_idesc(kAccF32, kFmtE4M3, kFmtE4M3, 128, 128)
                                      : umma_idesc(kAccS32, kFmtU8, kFmtS8, 128, 128);
-    constexpr uint32_t kI_HEAD = umma_idesc(kAccF32, kFmtF16, kFmtF16, 128, 96);
     constexpr int kAttnKind = kFP8 ? kKindF16 : kKindI8, kFfnKind = kFP8 ? kKindF8 : kKindI8;
     const uint32_t acc0 = tmem + TM_ACC, acc1 = tmem + TM_ACC + 128;
     const uint32_t sm_a = smem + C::SM_A, sm_r = smem + C::SM_R;
@@ -1080,8 +1190,6 @@ __device__ __forceinline__ void mma_loop(uint32_t smem, uint32_t tmem, volatile 
                 }
             }
         }
-        mma_wait_operand(smem, abort_flag, B_A_READY, st.aready);              // final norm output
-        mma_unit<kFP8>(smem, abort_flag, st, acc0, 0, sm_r, false, 4, kI_HEAD, kKindF16);
     }
 }
 
@@ -1121,6 +1229,7 @@ __global__ void __launch_bounds__(kThreads, 1) encoder_kernel(const Params p) {
         c.sm_a = smem + Cfg<kFP8>::SM_A; c.sm_r = smem + Cfg<kFP8>::SM_R;
         c.tm = tmem + (static_cast<uint32_t>(32 * c.q) << 16);
         c.abort_flag = abort_flag; c.xpar = 0; c.full0 = c.full1 = 0;
+        c.one2 = pk2(p.one, p.one);
         c.prof_on = kDbg && p.prof != nullptr && threadIdx.x == 0;
         c.t_last = c.prof_on ? clock64() : 0;
         for (int tile = blockIdx.x; tile < n_tiles; tile += gridDim.x) row_warps_tile<kDbg, kRJ, kFP8>(c, p, tile);
@@ -1245,6 +1354,7 @@ struct bf_handle {
     int* status = nullptr;
     unsigned long long* prof = nullptr;
     bool prof_on = false;
+    bool rsqrt_rn = false;        // BF_OPT_RSQRT_RN
     int sm_count = 0;
     long long launches = 0;
     // staging for bf_forward_host
@@ -1272,7 +1382,9 @@ int launch(bf_handle* h, const uint16_t* boards, const int16_t* control, const u
     p.n = n; p.n_layers = static_cast<int>(h->hdr.n_layers);
     p.n_value = static_cast<int>(h->hdr.n_value); p.vmode = static_cast<int>(h->hdr.vmode);
     p.quant = static_cast<int>(h->hdr.quant);
+    p.rsqrt_rn = h->rsqrt_rn ? 1 : 0;
     p.eps = h->hdr.eps;
+    p.one = 1.0f;
     p.wstream = h->blob + h->hdr.off_w;
     p.lparams = h->blob + h->hdr.off_lp;
     p.emb = reinterpret_cast<const __half*>(h->blob + h->hdr.off_emb);
@@ -1326,9 +1438,9 @@ int bf_create(const void* blob, size_t blob_bytes, int device, bf_handle** out) 
     if (hdr.quant != 3 && hdr.quant != 1) return fail(BF_EINVAL, "blob arithmetic must be 3 (int8) or 1 (e4m3 FFN)");
     if (hdr.quant == 1 && hdr.rj_mode != 0) return fail(BF_ENOTSUP, "re-injection is built for the int8 arithmetic only");
     const uint64_t layer_stream = hdr.quant == 1 ? bf::Cfg<true>::kLayerStream : bf::Cfg<false>::kLayerStream;
-    if (hdr.bytes_w != static_cast<uint64_t>(hdr.n_layers) * layer_stream + 4 * bf::kHeadStage ||
+    if (hdr.bytes_w != static_cast<uint64_t>(hdr.n_layers) * layer_stream ||
         hdr.bytes_lp != static_cast<uint64_t>(hdr.n_layers) * bf::kLparamStride ||
-        hdr.bytes_emb != 184u * 256u * 2u || hdr.bytes_tail != 2560u || hdr.rj_mode > 2 ||
+        hdr.bytes_emb != 184u * 256u * 2u || hdr.bytes_tail != bf::kTailBytes || hdr.rj_mode > 2 ||
         hdr.bytes_rj != (hdr.rj_mode ? static_cast<uint64_t>(hdr.n_layers) * hdr.rj_mode * 16u : 0u))
         return fail(BF_EINVAL, "blob section sizes do not match this build");
     if ((hdr.off_w | hdr.off_lp | hdr.off_emb | hdr.off_tail | hdr.off_rj) & 255u)
@@ -1471,6 +1583,12 @@ int bf_forward_host(bf_handle* h, const uint16_t* boards, const int16_t* control
     BF_CUDA(cudaStreamSynchronize(s));
     BF_CUDA(cudaStreamSynchronize(c));
     return BF_OK;
+}
+
+int bf_set_option(bf_handle* h, int option, int value) {
+    if (h == nullptr) return fail(BF_EINVAL, "null handle");
+    if (option == BF_OPT_RSQRT_RN) { h->rsqrt_rn = value != 0; return BF_OK; }
+    return fail(BF_EINVAL, "unknown option");
 }
 
 int bf_status(bf_handle* h, int* status) {
@@ -1617,9 +1735,9 @@ int bf_forward_noalloc(int device, const void* blob_dev, size_t blob_bytes, cons
             return fail(BF_EINVAL, "blob header does not match (magic, version or size)");
         if (hdr.n_layers < 1 || hdr.n_layers > 64 ||
             hdr.quant != 3 ||
-            hdr.bytes_w != static_cast<uint64_t>(hdr.n_layers) * bf::Cfg<false>::kLayerStream + 4 * bf::kHeadStage ||
+            hdr.bytes_w != static_cast<uint64_t>(hdr.n_layers) * bf::Cfg<false>::kLayerStream ||
             hdr.bytes_lp != static_cast<uint64_t>(hdr.n_layers) * bf::kLparamStride ||
-            hdr.bytes_emb != 184u * 256u * 2u || hdr.bytes_tail != 2560u || hdr.rj_mode != 0 ||
+            hdr.bytes_emb != 184u * 256u * 2u || hdr.bytes_tail != bf::kTailBytes || hdr.rj_mode != 0 ||
             ((hdr.off_w | hdr.off_lp | hdr.off_emb | hdr.off_tail) & 255u) ||
             hdr.off_w + hdr.bytes_w > blob_bytes || hdr.off_lp + hdr.bytes_lp > blob_bytes ||
             hdr.off_emb + hdr.bytes_emb > blob_bytes || hdr.off_tail + hdr.bytes_tail > blob_bytes)
@@ -1639,6 +1757,7 @@ int bf_forward_noalloc(int device, const void* blob_dev, size_t blob_bytes, cons
     p.n_value = static_cast<int>(d->hdr.n_value); p.vmode = static_cast<int>(d->hdr.vmode);
     p.quant = 3;
     p.eps = d->hdr.eps;
+    p.one = 1.0f;
     p.wstream = base + d->hdr.off_w;
     p.lparams = base + d->hdr.off_lp;
     p.emb = reinterpret_cast<const __half*>(base + d->hdr.off_emb);

@@ -275,6 +275,17 @@ __device__ __forceinline__ void mma_f16_f32(float (&d)[4], const uint32_t (&a)[4
         : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3])
         : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
 }
+// D(16x8, f16) += A(16x16, f16) * B(16x8, f16): fp16 accumulators (two packed pairs: row g
+// and row g + 8 of this lane's two columns), the form the reference's attention and head
+// products use (csrc/mma.cuh), so the same operands give the same bits.
+__device__ __forceinline__ void mma_f16_f16(uint32_t (&d)[2], const uint32_t (&a)[4], uint32_t b0,
+                                            uint32_t b1) {
+    asm volatile(
+        "mma.sync.aligned.m16n8k16.row.col.f16.f16.f16.f16 "
+        "{%0, %1}, {%2, %3, %4, %5}, {%6, %7}, {%0, %1};"
+        : "+r"(d[0]), "+r"(d[1])
+        : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
+}
 
 // ---------------------------------------------------------------- packed fp32 (sm_100 f32x2)
 // Two fp32 lanes in one 64-bit register; each lane rounds exactly as the scalar op does.
@@ -301,11 +312,10 @@ __device__ __forceinline__ uint64_t fma2(uint64_t a, uint64_t b, uint64_t c) {
     asm("fma.rn.f32x2 %0, %1, %2, %3;" : "=l"(d) : "l"(a), "l"(b), "l"(c));
     return d;
 }
-// a + b rounded once, written as fma(a, 1, b) so that the assembler cannot contract a
-// preceding packed multiply into it (the two-step rounding is part of the arithmetic).
-__device__ __forceinline__ uint64_t add2_after_mul(uint64_t a, uint64_t b) {
-    return fma2(a, pk2(1.0f, 1.0f), b);
-}
+// Note on two-step roundings: a packed multiply followed by a packed add (also when the add is
+// written as fma(x, 1.0, b) with a literal 1.0) may come out of the assembler as one fused
+// multiply-add.  Where the product must be rounded on its own, feed the add an fma whose unit
+// multiplier is a run-time value (see `quant16` in bf_encoder.cu).
 __device__ __forceinline__ uint64_t h2_to_f2(uint32_t h) {
     const float2 f = __half22float2(*reinterpret_cast<__half2*>(&h));
     return pk2(f.x, f.y);

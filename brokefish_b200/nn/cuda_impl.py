@@ -99,6 +99,7 @@ class FusedEncoder:
         self.debug_stage = 0
         self.net = net
         self._handle = ctypes.c_void_p(0)
+        self._exact_rsqrt = False
         self._buffered = 0
         self._buffered_full = 0
         if net is not None:
@@ -131,6 +132,7 @@ class FusedEncoder:
         self.int8_scheme, self.quant, self.two_boards, self.debug_stage = "all", 3, True, 0
         self.d_model, self.d_ff, self.n_heads, self.d_head = cls.D, cls.DFF, cls.H, 32
         self.net = None
+        self._exact_rsqrt = False
         self._buffered = self._buffered_full = 0
         self.device = torch.cuda.current_device() if device is None else int(device)
         L = _native.lib()
@@ -298,6 +300,17 @@ class FusedEncoder:
         _native.check(_native.lib().bf_profile_read(self._handle, buf, 16), "bf_profile_read")
         names = _native.lib().bf_profile_phases().decode().split(",")
         return {n: int(buf[i]) for i, n in enumerate(names)}
+
+    # -- 1/sqrt of the norms: hardware approximation (default, as the reference kernel's
+    #    rsqrtf, csrc/encoder.cu:597) or correctly rounded (what a CPU can reproduce) ------
+    @property
+    def exact_rsqrt(self) -> bool:
+        return self._exact_rsqrt
+
+    @exact_rsqrt.setter
+    def exact_rsqrt(self, on: bool) -> None:
+        _native.check(_native.lib().bf_set_option(self._handle, 1, int(bool(on))), "bf_set_option")
+        self._exact_rsqrt = bool(on)
 
     def check_status(self) -> None:
         """Synchronise and raise if any launch hit a device-side time-out."""

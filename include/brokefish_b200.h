@@ -34,7 +34,7 @@ extern "C" {
 #define BF_EDEVICE (-4)  /* a device-side bounded wait ran out */
 
 #define BF_BLOB_MAGIC 0x38424642u /* "BFB8" */
-#define BF_BLOB_VERSION 2u
+#define BF_BLOB_VERSION 3u
 
 /* GEMM selectors for bf_forward_capture. */
 #define BF_OP_QKV 0 /* A: LN1 output s8 [rows,256]; acc [rows,768] in chunk order        */
@@ -102,6 +102,15 @@ int bf_forward_capture(bf_handle* h, const uint16_t* boards, const int16_t* cont
 int bf_forward_host(bf_handle* h, const uint16_t* boards, const int16_t* control,
                     const uint8_t* rep, const uint64_t* legal, int n, void* policy,
                     void* promo, float* value);
+
+/* Options of a handle; no counterpart in the reference.
+ *   BF_OPT_RSQRT_RN  0 (default): the LayerNorms take 1/sqrt from the hardware approximation,
+ *                    as the reference kernel's `rsqrtf` does (csrc/encoder.cu:597), so outputs
+ *                    follow that kernel bit for bit through the encoder body;
+ *                    1: correctly rounded 1/sqrt, the only form a CPU restatement can
+ *                    reproduce bit for bit (the parity tests against the numpy oracle use it). */
+#define BF_OPT_RSQRT_RN 1
+int bf_set_option(bf_handle* h, int option, int value);
 
 /* Read (and clear) the device status word; 0 = every launch since the last call ran
  * clean.  Synchronises the device. */

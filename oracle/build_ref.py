@@ -49,6 +49,8 @@ SETS = {
     "C_int8_rj": (dict(seed=7, std=None, perturb_norms=True, reinject="both"), dict(int8=True)),
     "V_int8_wdl": (dict(seed=3, std=0.02, perturb_norms=True, n_value=3, value_head="pooled"),
                    dict(int8=True)),
+    "P_int8_prenorm": (dict(seed=5, std=None, perturb_norms=True, n_value=3, value_head="prenorm"),
+                       dict(int8=True)),
 }
 
 

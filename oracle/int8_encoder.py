@@ -26,9 +26,10 @@ committed under ``tests/golden/`` with the generating script.
 
 Where the reference's GPU arithmetic cannot be reproduced bit for bit on a CPU
 (``rsqrtf``, ``__expf``, the internal order of tensor-core accumulation), this file
-uses correctly rounded fp32 (``1/sqrt`` rounded once, ``exp``), fp32 accumulation for
-the two attention products and the head product, and a fixed sequential summation
-order for the LayerNorm statistics; every other rounding point is the reference's.
+uses correctly rounded fp32 (``1/sqrt`` rounded once, ``exp``), models the attention
+products as fp16 accumulation in two steps of 16 with an exact sum inside a step, and
+accumulates the head product in fp32; the LayerNorm statistics follow the reference
+kernel's own summation order; every other rounding point is the reference's.
 """
 
 from __future__ import annotations
@@ -44,11 +45,10 @@ N_POLICY, N_PROMO = 64, 4
 EPS = np.float32(1e-5)
 F32, F16 = np.float32, np.float16
 
-#: Column ownership of the four quarters of a row in the statistics' summation order:
-#: quarter q sums columns 32q..32q+31 then 128+32q..128+32q+31; within a quarter even and
-#: odd columns accumulate separately, sequentially, then even + odd; the quarters combine
-#: as (q0 + q1) + (q2 + q3).
-_QUARTER_COLS = [np.r_[32 * q:32 * q + 32, 128 + 32 * q:128 + 32 * q + 32] for q in range(4)]
+#: The statistics' summation order is the reference kernel's (csrc/encoder.cu:566-583): lane l
+#: of a warp owns columns 8l..8l+7 and adds them one after the other; the 32 partial sums are
+#: then combined by the butterfly 16, 8, 4, 2, 1 (every lane ends with the same total).
+_LANES, _LANE_COLS = 32, 8
 
 
 def f16(x) -> np.ndarray:
@@ -230,21 +230,19 @@ def reinject(w: Weights, x16: np.ndarray, boards, control, rep, site: int) -> np
     return add_f16(t, cs).reshape(n * T, D)
 
 
-def _seq_sum(a: np.ndarray) -> np.ndarray:
-    return np.add.accumulate(a, axis=1, dtype=F32)[:, -1]
-
-
 def ln_stats(x16: np.ndarray):
     """Row mean and 1/std of fp16 rows ``[M, 256]`` in the fixed summation order."""
-    x = x16.astype(F32)
-    s_part, q_part = [], []
-    for cols in _QUARTER_COLS:
-        v = x[:, cols]
-        sq = v * v                                 # exact: fp16 squares fit fp32
-        s_part.append((_seq_sum(v[:, 0::2]) + _seq_sum(v[:, 1::2])).astype(F32))
-        q_part.append((_seq_sum(sq[:, 0::2]) + _seq_sum(sq[:, 1::2])).astype(F32))
-    tot = ((s_part[0] + s_part[1]).astype(F32) + (s_part[2] + s_part[3]).astype(F32)).astype(F32)
-    totq = ((q_part[0] + q_part[1]).astype(F32) + (q_part[2] + q_part[3]).astype(F32)).astype(F32)
+    v = x16.astype(F32).reshape(-1, _LANES, _LANE_COLS)
+    tot = np.zeros(v.shape[:2], dtype=F32)
+    totq = np.zeros(v.shape[:2], dtype=F32)
+    for j in range(_LANE_COLS):
+        tot = (tot + v[:, :, j]).astype(F32)
+        totq = (totq + v[:, :, j] * v[:, :, j]).astype(F32)    # the square of an fp16 is exact in fp32
+    while tot.shape[1] > 1:
+        h = tot.shape[1] // 2
+        tot = (tot[:, :h] + tot[:, h:]).astype(F32)
+        totq = (totq[:, :h] + totq[:, h:]).astype(F32)
+    tot, totq = tot[:, 0], totq[:, 0]
     mean = (tot * F32(1.0 / 256)).astype(F32)
     t = (totq * F32(1.0 / 256)).astype(F32)
     var = (t.astype(np.float64) - mean.astype(np.float64) ** 2).astype(F32)   # one fma
@@ -307,20 +305,36 @@ def descale(acc: np.ndarray, sa: np.ndarray, sw_blocks: np.ndarray, n0: int = 0)
     return ((acc.astype(F32) * sa[:, None]).astype(F32) * sw[None, :]).astype(F32)
 
 
+def _mma_f16acc(a: np.ndarray, b: np.ndarray) -> np.ndarray:
+    """``a @ b`` for fp16 operands with the contraction cut into steps of 16 and an fp16
+    accumulator between the steps, the shape of the reference's ``mma.sync m16n8k16`` with
+    fp16 accumulators (csrc/mma.cuh:68-75).  Inside a step the sum is taken exactly and rounded
+    once; the hardware's own order inside a step is not documented, so this is a model of it,
+    not a transcript."""
+    acc = None
+    for k0 in range(0, a.shape[-1], 16):
+        part = np.matmul(a[..., k0:k0 + 16].astype(np.float64), b[..., k0:k0 + 16, :].astype(np.float64))
+        acc = part.astype(F16) if acc is None else (acc.astype(np.float64) + part).astype(F16)
+    return acc
+
+
 def attention(q16, k16, v16, alive):
-    """``[n,32,256]`` fp16 Q, K, V (scale pre-folded) -> ``[n,32,256]`` fp16."""
+    """``[n,32,256]`` fp16 Q, K, V (scale pre-folded) -> ``[n,32,256]`` fp16, in the
+    reference's arithmetic (csrc/encoder.cu:715-797): both products accumulate in fp16 in two
+    steps of 16, the softmax is fp32 (``exp`` here where the kernel has the hardware
+    ``__expf``; the row sum's order is not mirrored)."""
     n = q16.shape[0]
-    q = q16.astype(F32).reshape(n, T, H, DH).transpose(0, 2, 1, 3)
-    k = k16.astype(F32).reshape(n, T, H, DH).transpose(0, 2, 1, 3)
-    v = v16.astype(F32).reshape(n, T, H, DH).transpose(0, 2, 1, 3)
-    s = np.matmul(q, k.transpose(0, 1, 3, 2)).astype(F32)            # [n,H,32,32]
+    q = q16.reshape(n, T, H, DH).transpose(0, 2, 1, 3)
+    k = k16.reshape(n, T, H, DH).transpose(0, 2, 1, 3)
+    v = v16.reshape(n, T, H, DH).transpose(0, 2, 1, 3)
+    s = _mma_f16acc(q, k.transpose(0, 1, 3, 2)).astype(F32)          # [n,H,32,32]
     s = np.where(alive[:, None, None, :], s, F32(-np.inf))
     with np.errstate(invalid="ignore"):
         mx = s.max(axis=-1, keepdims=True)
         p = np.exp((s - mx).astype(F32)).astype(F32)
         inv = (F32(1.0) / p.sum(axis=-1, keepdims=True, dtype=F32)).astype(F32)
         pn = (p * inv).astype(F16)
-    o = np.matmul(pn.astype(F32), v).astype(F32)
+        o = _mma_f16acc(pn, v)
     return o.transpose(0, 2, 1, 3).reshape(n, T, D).astype(F16)
 
 
@@ -405,7 +419,11 @@ def forward(w: Weights, boards, control, rep, legal=None, trace: Optional[Trace]
             acc2 = gemm_int(qh, lw.q_ff2[:, 256 * c:256 * c + 256])
             if not e4:
                 cap(li, f"ff2_{c}", qh, acc2)
-            o32 = (descale(acc2, sh, lw.s_ff2) + run.astype(F32)).astype(F32)
+            # `float(acc) * sa * sw + float(run)` (csrc/int8_gemm.cuh:285-294): the compiler fuses
+            # the second product with the sum, so it is one fma (float64 holds it exactly)
+            sw2 = lw.s_ff2[np.arange(D) // 128].astype(np.float64)
+            prod = (acc2.astype(F32) * sh[:, None]).astype(F32)
+            o32 = (prod.astype(np.float64) * sw2[None, :] + run.astype(np.float64)).astype(F32)
             run = o32.astype(F16)
         y = add_f16(run, lw.b_ff2[None, :])
         x = add_f16(x, y)
@@ -415,7 +433,7 @@ def forward(w: Weights, boards, control, rep, legal=None, trace: Optional[Trace]
     hn = layernorm(x, w.lnf_w, w.lnf_b)
     if trace is not None:
         trace.stages[8] = hn.reshape(n, T, D).copy()
-    logits = (hn.astype(F32) @ w.head.astype(F32).T).astype(F16).reshape(n, T, 96)
+    logits = _mma_f16acc(hn, w.head.T).reshape(n, T, 96)        # fp16 accumulators, 16 steps of 16
     policy = logits[:, :, :N_POLICY].copy()
     promo = logits[:, :, N_POLICY:N_POLICY + N_PROMO].copy()
     vcols = logits[:, :, 68:68 + w.n_value].astype(F32)

@@ -46,6 +46,20 @@ def inputs(pos, sl):
 
 @pytest.fixture(scope="module")
 def encoders(nets):
+    """The product with correctly rounded 1/sqrt in the norms, the form the numpy oracle can
+    reproduce; the default (the hardware approximation, as the reference kernel) is what
+    `encoders_hw` and tests/test_gpu_reference_kernel.py run."""
+    from brokefish_b200.nn import encoder_impl
+    out = {k: encoder_impl("cuda")(n) for k, n in nets.items()}
+    for e in out.values():
+        e.exact_rsqrt = True
+    yield out
+    for e in out.values():
+        e.close()
+
+
+@pytest.fixture(scope="module")
+def encoders_hw(nets):
     from brokefish_b200.nn import encoder_impl
     out = {k: encoder_impl("cuda")(n) for k, n in nets.items()}
     yield out
@@ -198,9 +212,11 @@ def test_layer0_operands_equal_the_oracles(name, encoders, oracle_weights, pos25
 
 
 # ---------------------------------------------------------------- outputs
+@pytest.mark.parametrize("hw_rsqrt", [False, True])
 @pytest.mark.parametrize("name", ["A", "B"])
-def test_logits_value_and_argmax(name, encoders, oracle_weights, pos256):
-    enc = encoders[name]
+def test_logits_value_and_argmax(name, hw_rsqrt, encoders, encoders_hw, oracle_weights, pos256):
+    enc = (encoders_hw if hw_rsqrt else encoders)[name]
+    assert enc.exact_rsqrt == (not hw_rsqrt)
     w = aligned_oracle(oracle_weights, name, enc)
     sl = slice(0, 256)
     pol, pro, val = (t.cpu().numpy() for t in enc.forward_full(*inputs(pos256, sl)))
@@ -327,6 +343,7 @@ def test_value_head_variants(pos256):
         net = BrokefishNet(n_value=nv, value_head=head).eval()
         net.load_state_dict(st)
         enc = encoder_impl("cuda")(net)
+        enc.exact_rsqrt = True
         w = O.prepare({k: v.numpy() for k, v in st.items()})
         sl = slice(0, 48)
         val = enc.forward_full(*inputs(pos256, sl))[2].cpu().numpy()
@@ -376,6 +393,7 @@ def test_reinjection(mode, pos256):
     net = net_for_state(st).eval()
     net.load_state_dict(st)
     enc = encoder_impl("cuda")(net)
+    enc.exact_rsqrt = True
     assert enc.rj_mode == {"ln1": 1, "both": 2}[mode]
     w = aligned_oracle({"X": O.prepare({k: v.numpy() for k, v in st.items()})}, "X", enc)
     sl = slice(0, 48)
@@ -418,6 +436,7 @@ def test_e4m3_ffn_arithmetic(name, nets, states, pos256):
     from conftest import GOLDEN
     from brokefish_b200.nn import encoder_impl
     enc = encoder_impl("cuda")(nets[name], fp8=True)
+    enc.exact_rsqrt = True
     assert enc.quant == 1 and enc.label.startswith("e4m3")
     w = O.prepare({k: v.numpy() for k, v in states[name].items()}, fmt="e4m3")
     sl = slice(0, 64)

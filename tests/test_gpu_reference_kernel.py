@@ -5,18 +5,17 @@ reference checkout and saves the weight slabs the reference's constructor derive
 runs that kernel (``oracle/ref_kernel.py``) and the product on identical seeded positions and
 weights.  Skipped when the built reference is not present (it is not part of the history).
 
-The reference kernel and the product round differently inside a layer (the reference
-accumulates attention in fp16 on ``mma.sync``; its LayerNorm statistics come from warp
-shuffles in another order), and a single differing fp16 rounding moves an int8 operand by a
-step, so three implementations of the same scheme -- this kernel, the reference kernel and
-the numpy oracle -- sit about 1.5-2 % of max|logit| from one another after eight layers
-(measured on 4096 positions, set A: product vs reference kernel 0.0239, oracle vs reference
-kernel 0.0198, oracle vs product 0.0146, max|logit| 1.22).  The bars here are therefore:
-logits within 3 % of max(1, max|logit|) (measured 2.0 % A, 2.1 % B), value within 5e-2
-(measured 1.5e-2 A, 4.2e-2 B), masked argmax agreement >= 97 % (measured 97.8 % / 97.6 % of
-4043 playable positions) with EVERY disagreement a near tie by the reference kernel's own
-logits, and the product no further from the reference's fp32 network than the reference
-kernel is (x1.5: both are one draw of the same quantisation noise).  The embedding, which involves no arithmetic order, is bit-identical.
+Bar for the int8 arithmetic (the path the metric is quoted on): BIT IDENTITY.  The product
+keeps the reference kernel's own rounding points and summation orders -- LayerNorm partial
+sums and butterfly, hardware 1/sqrt, fp16-accumulate ``mma.sync`` for the attention and head
+products, ``__expf`` softmax, the fused multiply-add in the ff2 running total -- and moves
+only the exact-integer GEMMs to tcgen05, so every layer-0 debug stage, the final norm after
+eight layers, policy, promo and value come out equal to the bit (measured on 2048 positions
+for four weight sets: 0 differing elements, value difference 0.0, argmax agreement 100 %).
+
+The e4m3-FFN arithmetic is a tolerance: there the product accumulates its fp16 and e4m3
+tcgen05 GEMMs in fp32 where the reference accumulates in fp16 (measured 6.3 % of max|logit|;
+the reference's own bar for a quantised path is 8 % of max|logit| against fp32).
 """
 import os
 
@@ -74,51 +73,93 @@ def check_argmax(pol, rpol, legal, floor, tol):
         assert flat[i, theirs[i]] - flat[i, mine[i]] <= tol
 
 
+def same_bits(a, b):
+    return np.array_equal(np.ascontiguousarray(a).view(np.uint8), np.ascontiguousarray(b).view(np.uint8))
+
+
 @pytest.mark.parametrize("name", ["A", "B"])
-def test_int8_path_against_reference_kernel(name, pos256):
+def test_int8_outputs_are_bit_identical_to_the_reference_kernel(name, pos256):
     if not R.available(f"{name}_int8"):
         pytest.skip("slabs missing")
     enc, ref = product(SETS[name]), R.RefKernel(f"{name}_int8")
-    assert (ref.quant, ref.two_boards) == (3, 1)
+    assert (ref.quant, ref.two_boards) == (3, 1) and not enc.exact_rsqrt
     sl = slice(0, 256)
     (pol, pro, val), (rpol, rpro, rval) = run_both(enc, ref, pos256, sl)
-    tol = rel_tol(rpol, 3e-2)
-    assert np.abs(pol.astype(np.float32) - rpol.astype(np.float32)).max() <= tol
-    assert np.abs(pro.astype(np.float32) - rpro.astype(np.float32)).max() <= tol
-    assert np.abs(val - rval).max() <= 5e-2
-    check_argmax(pol, rpol, pos256["legal"][sl], 0.95, tol)      # 250 positions: +-1 % sampling
-    # against the reference's fp32 network (committed golden outputs): the product is not
-    # further from it than the reference's own kernel
-    g = np.load(os.path.join(GOLDEN, f"ref_outputs_{name}.npz"))
-    n = g["fp32_policy"].shape[0]
-    mine = np.abs(pol[:n].astype(np.float32) - g["fp32_policy"]).max()
-    theirs = np.abs(rpol[:n].astype(np.float32) - g["fp32_policy"]).max()
-    print(f"set {name}: max|logit - fp32| product {mine:.4f}, reference kernel {theirs:.4f}")
-    assert mine <= 1.5 * theirs
+    assert same_bits(pol, rpol) and same_bits(pro, rpro)
+    assert np.abs(val - rval).max() <= 1e-6
+    # an odd batch, so the reference's spare board slot and the product's partial tile are hit
+    odd = slice(5, 5 + 77)
+    (pol, pro, val), (rpol, rpro, rval) = run_both(enc, ref, pos256, odd)
+    assert same_bits(pol, rpol) and same_bits(pro, rpro) and np.abs(val - rval).max() <= 1e-6
     enc.close()
 
 
-def test_int8_full_batch_against_reference_kernel(pos4096):
+@pytest.mark.parametrize("name", ["A", "B"])
+def test_every_debug_stage_is_bit_identical(name, pos256):
+    """Stage 9 embedding; layer 0: 1 LN1, 5/6/7 Q/K/V, 4 attention output, 2 residual after
+    attention, 3 LN2; 8 the final norm after all eight layers (the reference's stage numbers,
+    csrc/encoder.cu:1315-1596)."""
+    if not R.available(f"{name}_int8"):
+        pytest.skip("slabs missing")
+    enc, ref = product(SETS[name]), R.RefKernel(f"{name}_int8")
+    sl = slice(0, 200)
+    for stage in (9, 1, 5, 6, 7, 4, 2, 3, 8):
+        got = enc.forward_stage(*inputs(pos256, sl), stage).cpu().numpy()
+        want = ref.forward_stage(*inputs(pos256, sl), stage).cpu().numpy()
+        assert same_bits(got, want), stage
+    enc.close()
+
+
+def test_int8_full_batch_is_bit_identical(pos4096):
     if not R.available("A_int8"):
         pytest.skip("slabs missing")
     enc, ref = product(SETS["A"]), R.RefKernel("A_int8")
     sl = slice(0, 4096)
     (pol, pro, val), (rpol, rpro, rval) = run_both(enc, ref, pos4096, sl)
-    tol = rel_tol(rpol, 3e-2)
-    assert np.abs(pol.astype(np.float32) - rpol.astype(np.float32)).max() <= tol
-    assert np.abs(val - rval).max() <= 5e-2
-    check_argmax(pol, rpol, pos4096["legal"][sl], 0.97, tol)
+    assert same_bits(pol, rpol) and same_bits(pro, rpro)
+    assert np.abs(val - rval).max() <= 1e-6
+    mine, theirs = O.masked_argmax(pol, pos4096["legal"][sl]), O.masked_argmax(rpol, pos4096["legal"][sl])
+    assert np.array_equal(mine, theirs)
     enc.close()
 
 
-def test_embedding_equals_reference_kernel_bitwise(pos256):
-    if not R.available("B_int8"):
+def test_reinjection_is_bit_identical(pos256):
+    if not R.available("C_int8_rj"):
         pytest.skip("slabs missing")
-    enc, ref = product(SETS["B"]), R.RefKernel("B_int8")
-    sl = slice(0, 200)
-    got = enc.forward_stage(*inputs(pos256, sl), 9).cpu().numpy()
-    want = ref.forward_stage(*inputs(pos256, sl), 9).cpu().numpy()
-    assert np.array_equal(got.view(np.uint16), want.view(np.uint16))
+    kw = dict(seed=7, std=None, perturb_norms=True, reinject="both")
+    enc, ref = product(kw), R.RefKernel("C_int8_rj")
+    assert ref.rj_mode == 2 and enc.rj_mode == 2
+    sl = slice(0, 96)
+    (pol, pro, val), (rpol, rpro, rval) = run_both(enc, ref, pos256, sl)
+    assert same_bits(pol, rpol) and same_bits(pro, rpro) and np.abs(val - rval).max() <= 1e-6
+    enc.close()
+
+
+def test_pooled_wdl_value_is_bit_identical(pos256):
+    if not R.available("V_int8_wdl"):
+        pytest.skip("slabs missing")
+    kw = dict(seed=3, std=0.02, perturb_norms=True, n_value=3, value_head="pooled")
+    enc, ref = product(kw), R.RefKernel("V_int8_wdl")
+    assert (ref.n_value, ref.vmode) == (3, 1)
+    sl = slice(0, 96)
+    (pol, pro, val), (rpol, rpro, rval) = run_both(enc, ref, pos256, sl)
+    assert same_bits(pol, rpol) and same_bits(pro, rpro) and np.abs(val - rval).max() <= 1e-6
+    enc.close()
+
+
+def test_prenorm_wdl_value_against_reference_kernel(pos256):
+    """The prenorm value head pools the raw residual and norms it once; the product sums in
+    another order than the reference's one warp (csrc/encoder.cu:1008-1057), all in fp32, so the
+    value is held to 1e-5 while policy and promo stay bit-identical."""
+    if not R.available("P_int8_prenorm"):
+        pytest.skip("slabs missing")
+    kw = dict(seed=5, std=None, perturb_norms=True, n_value=3, value_head="prenorm")
+    enc, ref = product(kw), R.RefKernel("P_int8_prenorm")
+    assert (ref.n_value, ref.vmode) == (3, 2)
+    sl = slice(0, 96)
+    (pol, pro, val), (rpol, rpro, rval) = run_both(enc, ref, pos256, sl)
+    assert same_bits(pol, rpol) and same_bits(pro, rpro)
+    assert np.abs(val - rval).max() <= 1e-5
     enc.close()
 
 
@@ -129,38 +170,11 @@ def test_e4m3_path_against_reference_kernel(pos256):
     assert ref.quant == 1
     sl = slice(0, 128)
     (pol, pro, val), (rpol, rpro, rval) = run_both(enc, ref, pos256, sl)
-    # two e4m3 implementations (measured 7.1 % of max|logit| on 4096 positions): the
-    # reference's own bar for a quantised path is 8 % of max|logit| against fp32
+    # two e4m3 implementations with different accumulator widths (measured 6.3 % of
+    # max|logit| on 2048 positions)
     tol = rel_tol(rpol, 10e-2)
     assert np.abs(pol.astype(np.float32) - rpol.astype(np.float32)).max() <= tol
     assert np.abs(val - rval).max() <= 8e-2
-    enc.close()
-
-
-def test_reinjection_against_reference_kernel(pos256):
-    if not R.available("C_int8_rj"):
-        pytest.skip("slabs missing")
-    kw = dict(seed=7, std=None, perturb_norms=True, reinject="both")
-    enc, ref = product(kw), R.RefKernel("C_int8_rj")
-    assert ref.rj_mode == 2 and enc.rj_mode == 2
-    sl = slice(0, 96)
-    (pol, pro, val), (rpol, rpro, rval) = run_both(enc, ref, pos256, sl)
-    tol = rel_tol(rpol, 3e-2)
-    assert np.abs(pol.astype(np.float32) - rpol.astype(np.float32)).max() <= tol
-    assert np.abs(val - rval).max() <= 5e-2
-    enc.close()
-
-
-def test_pooled_wdl_value_against_reference_kernel(pos256):
-    if not R.available("V_int8_wdl"):
-        pytest.skip("slabs missing")
-    kw = dict(seed=3, std=0.02, perturb_norms=True, n_value=3, value_head="pooled")
-    enc, ref = product(kw), R.RefKernel("V_int8_wdl")
-    assert (ref.n_value, ref.vmode) == (3, 1)
-    sl = slice(0, 96)
-    (pol, pro, val), (rpol, rpro, rval) = run_both(enc, ref, pos256, sl)
-    assert np.abs(pol.astype(np.float32) - rpol.astype(np.float32)).max() <= rel_tol(rpol, 3e-2)
-    assert np.abs(val - rval).max() <= 5e-2
     enc.close()
 
 
