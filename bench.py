@@ -36,6 +36,9 @@ import torch
 
 OPS_PER_POSITION = 402653184          # int8 ops of the 32 weight GEMMs of one position
 BYTES_IN, BYTES_OUT = 67, 4356        # boards+control+rep ; policy+promo+value
+#: DRAM bytes one launch of 4096 positions moved under ncu (read 6.92 MB: the weight blob once
+#: plus inputs; written 0.02 MB: the 17.8 MB of outputs were still in L2 when the launch ended)
+NCU_DRAM_BYTES_PER_LAUNCH = 6.94e6
 METRIC = "positions evaluated/sec at batch 4096 int8"
 WORKLOAD = ("8-layer d256 h8 ff1024 int8 evaluator, N(0,0.02) seed-0 weights, seeded "
             "random-playout positions, batch 4096 per GPU")
@@ -87,7 +90,11 @@ class ClockSampler:
     """Samples SM clock and throttle reasons with nvidia-smi while the timed region runs."""
 
     def __init__(self, index: int):
-        self.rows, self.proc, self.index = [], None, index
+        self.rows, self.proc, self.index, self.first = [], None, index, 0
+
+    def mark(self):
+        """The timed region starts here: earlier samples (warm-up) are not reported."""
+        self.first = len(self.rows)
 
     def start(self):
         q = ("clocks.sm,clocks.max.sm,clocks_event_reasons.hw_slowdown,"
@@ -96,7 +103,7 @@ class ClockSampler:
         try:
             self.proc = subprocess.Popen(
                 ["nvidia-smi", f"--id={self.index}", f"--query-gpu={q}", "--format=csv,noheader,nounits",
-                 "-lms", "100"], stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+                 "-lms", "50"], stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
             threading.Thread(target=self._read, daemon=True).start()
         except OSError:
             self.proc = None
@@ -113,11 +120,12 @@ class ClockSampler:
             self.proc.wait(timeout=5)
         except Exception:
             pass
-        sm = [float(r[0]) for r in self.rows if len(r) >= 6 and r[0].replace(".", "").isdigit()]
-        mx = [float(r[1]) for r in self.rows if len(r) >= 6 and r[1].replace(".", "").isdigit()]
+        rows = self.rows[self.first:] or self.rows
+        sm = [float(r[0]) for r in rows if len(r) >= 6 and r[0].replace(".", "").isdigit()]
+        mx = [float(r[1]) for r in rows if len(r) >= 6 and r[1].replace(".", "").isdigit()]
         names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
         reasons = [nm for i, nm in enumerate(names)
-                   if any(len(r) >= 6 and r[2 + i].lower().startswith("active") for r in self.rows)]
+                   if any(len(r) >= 6 and r[2 + i].lower().startswith("active") for r in rows)]
         return {"sm_mhz": float(np.median(sm)) if sm else None,
                 "sm_max_mhz": max(mx) if mx else None, "reasons": reasons, "samples": len(sm)}
 
@@ -154,6 +162,8 @@ def main() -> int:
                     help="fixed number of positions per step split across the GPUs")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--sweep", action="store_true", help="print one line per batch size 1..65536 and exit")
+    ap.add_argument("--phases", action="store_true",
+                    help="add the in-kernel phase split (cycles per phase over 5 extra launches) to the line")
     ap.add_argument("--fp8", action="store_true",
                     help="time the e4m3-FFN arithmetic instead of int8 (a separate line; not the headline)")
     args = ap.parse_args()
@@ -214,16 +224,17 @@ def main() -> int:
             dist.barrier()
         torch.cuda.synchronize(dev)
 
-    for _ in range(warmup):
-        enc.forward_full(d_b, d_c, d_r)
-    barrier()
     sampler = ClockSampler(local)
     if rank == 0:
         sampler.start()
+    for _ in range(warmup):
+        enc.forward_full(d_b, d_c, d_r)
+    barrier()
     starts = [torch.cuda.Event(enable_timing=True) for _ in range(args.steps)]
     stops = [torch.cuda.Event(enable_timing=True) for _ in range(args.steps)]
     launches0 = enc.launches
     barrier()
+    sampler.mark()
     t_wall = time.perf_counter()
     for i in range(args.steps):
         flush.fill_(i & 0xFF)                      # L2 flush between timed iterations
@@ -252,6 +263,14 @@ def main() -> int:
     torch.cuda.synchronize(dev)
     e2e_ms = (time.perf_counter() - t0) * 1e3
     clocks = sampler.stop() if rank == 0 else None
+    phases = None
+    if args.phases and rank == 0:
+        enc.set_profile(True)
+        enc.read_profile()
+        for _ in range(5):
+            enc.forward_full(d_b, d_c, d_r)
+        phases = {k: v / 5 for k, v in enc.read_profile().items() if k}
+        enc.set_profile(False)
 
     times = torch.tensor([dev_ms, e2e_ms], dtype=torch.float64, device=dev)
     if world > 1:
@@ -279,12 +298,16 @@ def main() -> int:
                    "wall_ms_incl_flush": t_wall * 1e3},
         "roofline": {"bound": "tensor", "achieved": achieved, "peak": peak, "unit": "TFLOP/s",
                      "frac": achieved / peak, "peak_source": peak_src + "; int8 dense nominal 4500",
-                     "traffic": None,
+                     "traffic": NCU_DRAM_BYTES_PER_LAUNCH if (n_local == 4096 and not args.fp8) else None,
+                     "traffic_source": "ncu dram__bytes_read.sum + dram__bytes_write.sum of one launch at "
+                                       "batch 4096 (profiles/encoder_kernel_batch4096_ncu_full.md)",
                      "hbm_algorithmic_GBps": n_local * (BYTES_IN + BYTES_OUT) / (kern_avg_ms * 1e-3) / 1e9},
         "e2e": {"value": e2e, "unit": "positions/s", "h2d_bytes_per_step": n_local * BYTES_IN,
                 "d2h_bytes_per_step": n_local * BYTES_OUT},
         "gpu_launches": launches, "clocks": clocks,
     }
+    if phases is not None:
+        line["phases_cycles_per_launch"] = phases
     if world == 1 and not args.no_cpu_baseline:
         cv, cms, info = cpu_reference(25, 3)
         line["cpu_baseline"] = dict(info, value=cv, unit="positions/s")
