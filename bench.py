@@ -308,6 +308,20 @@ def main() -> int:
     }
     if phases is not None:
         line["phases_cycles_per_launch"] = phases
+    if world == 1:
+        # the tensor pipe's own int8 rate on this GPU (a tcgen05 kind::i8 loop on resident
+        # operands) is the denominator when it can be measured; the fractions of 2 x the measured
+        # bf16 rate and of the nominal int8 rate are kept beside it
+        import ctypes
+        from brokefish_b200 import _native
+        tops, ms = ctypes.c_double(0), ctypes.c_double(0)
+        rf = line["roofline"]
+        rf["frac_of_2x_bf16_measured"], rf["frac_of_nominal_4500"] = achieved / peak, achieved / 4500.0
+        if _native.lib().bf_measure_i8_peak(local, 16384, ctypes.byref(tops), ctypes.byref(ms)) == 0:
+            rf["peak"], rf["frac"] = tops.value, achieved / tops.value
+            rf["peak_source"] = ("measured on this GPU in this run: tcgen05.mma kind::i8 loop on resident "
+                                 "operands (bf_measure_i8_peak); 2 x measured dense bf16 burst "
+                                 "(MEASURED_PEAKS.json) = %.0f; int8 dense nominal 4500" % peak)
     if world == 1 and not args.no_cpu_baseline:
         cv, cms, info = cpu_reference(25, 3)
         line["cpu_baseline"] = dict(info, value=cv, unit="positions/s")

@@ -1250,6 +1250,58 @@ __global__ void __launch_bounds__(kThreads, 1) encoder_kernel(const Params p) {
 }
 
 // ------------------------------------------------------------------------------------------
+// Tensor-pipe probe: what `tcgen05.mma kind::i8` sustains when nothing else is in the way.
+// One CTA per SM; operands (pseudo-random bytes) sit in shared memory, accumulators in tensor
+// memory; one thread issues `iters` groups of four M=128, N=256, K=32 MMAs back to back into two
+// alternating accumulators, commits once and waits (bounded).  The counterpart of the
+// reference's register-resident mma loop (csrc/fp8_loop.cu), used as the measured int8
+// denominator of the roofline.
+// ------------------------------------------------------------------------------------------
+__global__ void __launch_bounds__(128, 1) i8_peak_kernel(int iters, int* status) {
+    extern __shared__ uint8_t smem_raw[];
+    uint8_t* sm = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+    const uint32_t smem = smem_u32(sm);
+    // layout: A [128 rows][128 B] at 0, B [256 rows][128 B] at 16384, barrier at 49152
+    constexpr uint32_t kB = 16384, kBar = 49152;
+    volatile int* abort_flag = reinterpret_cast<volatile int*>(sm + kBar + 64);
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(sm + kBar + 68);
+    if (threadIdx.x == 0) {
+        mbar_init(smem + kBar, 1);
+        *abort_flag = 0;
+        fence_barrier_init();
+    }
+    if ((threadIdx.x >> 5) == 0) { tmem_alloc(smem + kBar + 68, 512); tmem_relinquish(); }
+    uint32_t h = 0x9E3779B9u * (threadIdx.x + 1u) + blockIdx.x;
+    for (uint32_t i = threadIdx.x; i < (kB + 32768u) / 4u; i += blockDim.x) {
+        h = h * 1664525u + 1013904223u;
+        reinterpret_cast<uint32_t*>(sm)[i] = h ^ (h >> 13);
+    }
+    fence_proxy_async_smem();
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t tmem = *tmem_slot;
+    if (threadIdx.x == 0) {
+        const uint32_t idesc = umma_idesc(kAccS32, kFmtS8, kFmtS8, 128, 256);
+        const uint64_t ad = umma_desc_k128(smem), bd = umma_desc_k128(smem + kB);
+        for (int it = 0; it < iters; ++it) {
+            const uint32_t d = tmem + ((it & 1) ? 256u : 0u);
+#pragma unroll
+            for (int k = 0; k < 4; ++k) umma_i8(d, ad + 2 * k, bd + 2 * k, idesc, (it > 1 || k > 0) ? 1u : 0u);
+        }
+        tc_commit(smem + kBar);
+        mbar_wait(smem + kBar, 0, abort_flag, kErrMmaAcc);
+        tc_fence_after();
+    }
+    __syncwarp();
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    if ((threadIdx.x >> 5) == 0) tmem_dealloc(tmem, 512);
+    if (threadIdx.x == 0 && *abort_flag != 0) atomicCAS(status, 0, *abort_flag);
+}
+
+// ------------------------------------------------------------------------------------------
 // Tensor-core self test: one tile, one GEMM, no network.
 // ------------------------------------------------------------------------------------------
 __global__ void __launch_bounds__(128, 1) selftest_kernel(int mode, const uint8_t* a, const uint8_t* w,
@@ -1630,6 +1682,43 @@ const char* bf_profile_phases(void) {
     return "embed,layernorm_quantise,wait_mma_qkv_heads,qkv_epilogue,pair_barrier,attention,attn_readback,"
            "attn_quantise,out_proj_epilogue,ff1_epilogue,ff2_epilogue,heads,wait_mma_out,wait_mma_ff1,"
            "wait_mma_ff2";
+}
+
+int bf_measure_i8_peak(int device, int iters, double* tops, double* ms) {
+    if (tops == nullptr || iters < 2 || iters > (1 << 22)) return fail(BF_EINVAL, "tops is null or iters out of range");
+    BF_CUDA(cudaSetDevice(device));
+    cudaDeviceProp prop;
+    BF_CUDA(cudaGetDeviceProperties(&prop, device));
+    if (prop.major != 10) return fail(BF_ENOTSUP, "this library needs a compute capability 10.x (sm_100a) device");
+    constexpr int kSmem = 49152 + 256 + 1024;
+    BF_CUDA(cudaFuncSetAttribute(bf::i8_peak_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmem));
+    int* status = nullptr;
+    BF_CUDA(cudaMalloc(&status, sizeof(int)));
+    cudaEvent_t e0 = nullptr, e1 = nullptr;
+    cudaError_t e = cudaMemset(status, 0, sizeof(int));
+    if (e == cudaSuccess) e = cudaEventCreate(&e0);
+    if (e == cudaSuccess) e = cudaEventCreate(&e1);
+    float best = 0.f;
+    int st = 0;
+    for (int rep = 0; rep < 4 && e == cudaSuccess; ++rep) {      // first repetition warms up
+        cudaEventRecord(e0);
+        bf::i8_peak_kernel<<<prop.multiProcessorCount, 128, kSmem>>>(iters, status);
+        cudaEventRecord(e1);
+        e = cudaEventSynchronize(e1);
+        float t = 0.f;
+        if (e == cudaSuccess) e = cudaEventElapsedTime(&t, e0, e1);
+        if (rep > 0 && (best == 0.f || t < best)) best = t;
+    }
+    if (e == cudaSuccess) e = cudaMemcpy(&st, status, sizeof(int), cudaMemcpyDeviceToHost);
+    if (e0) cudaEventDestroy(e0);
+    if (e1) cudaEventDestroy(e1);
+    cudaFree(status);
+    if (e != cudaSuccess) return fail(BF_ECUDA, cudaGetErrorString(e));
+    if (st != 0) return fail(BF_EDEVICE, "the probe's bounded wait ran out");
+    const double ops = 2.0 * 128 * 256 * 32 * 4.0 * iters * prop.multiProcessorCount;
+    *tops = ops / (best * 1e-3) / 1e12;
+    if (ms != nullptr) *ms = best;
+    return BF_OK;
 }
 
 int bf_selftest_umma(int device, int mode, const void* a, const void* w_image, void* out) {

@@ -160,6 +160,13 @@ int bf_forward_noalloc(int device, const void* blob_dev, size_t blob_bytes, cons
  * share; 0 = clean.  No counterpart in the reference. */
 int bf_noalloc_status(int device, int* status);
 
+/* Measure what the tensor pipe sustains on `tcgen05.mma kind::i8` alone: one CTA per SM issues
+ * `iters` groups of four M=128, N=256, K=32 MMAs on operands resident in shared memory, timed
+ * with CUDA events (best of three after a warm-up).  `*tops` = int8 TOP/s of the whole device,
+ * `*ms` (may be NULL) the duration.  The method of the reference's peak probe
+ * (csrc/fp8_loop.cu; docs/ledger/perf.md:616-647), for the roofline's denominator. */
+int bf_measure_i8_peak(int device, int iters, double* tops, double* ms);
+
 /* Tensor-core self test (no network): one 128-row tile times a packed weight tile.
  *   mode 0: s8 x s8, N=128, K=256     mode 1: u8 x s8, N=128, K=256
  *   mode 2: s8 x s8, N=192, K=256     mode 3: f16 x f16 -> f32, N=96, K=256

@@ -464,3 +464,44 @@ def test_e4m3_ffn_arithmetic(name, nets, states, pos256):
     with pytest.raises(NotImplementedError):
         enc.capture_gemm(*inputs(pos256, slice(0, 4)), layer=0, op=0)
     enc.close()
+
+
+def test_divergence_report(encoders, encoders_hw, oracle_weights, pos256):
+    """Not a bar: prints, layer by layer, how far the kernel and the numpy oracle are apart
+    (`pytest tests/test_gpu_parity.py -m gpu -s -k divergence_report`), for both 1/sqrt modes.
+    Stage 4 = attention output, 2 = residual after the attention block, 10 = residual at the end
+    of the layer."""
+    sl = slice(0, 256)
+    for mode, encs in (("correctly rounded 1/sqrt", encoders), ("hardware 1/sqrt", encoders_hw)):
+        enc = encs["A"]
+        w = aligned_oracle(oracle_weights, "A", enc)
+        tr = O.Trace()
+        opol, _, oval = O.forward(w, pos256["boards"][sl], pos256["control"][sl], pos256["rep"][sl], trace=tr)
+        print(f"\nset A, {mode}: layer | stage 4 max / exact | stage 2 max / exact | stage 10 max / exact")
+        for layer in range(8):
+            cells = []
+            for stage in (4, 2, 10):
+                got = enc.forward_stage(*inputs(pos256, sl), stage, layer=layer).cpu().numpy()
+                want = tr.by_layer[(layer, stage)].reshape(got.shape)
+                d = np.abs(got.astype(np.float32) - want.astype(np.float32)).max()
+                same = (got.view(np.uint16) == want.view(np.uint16)).mean()
+                cells.append(f"{d:.4f} / {same:.4f}")
+            print(f"  {layer} | " + " | ".join(cells))
+        pol, _, val = (t.cpu().numpy() for t in enc.forward_full(*inputs(pos256, sl)))
+        d = np.abs(pol.astype(np.float32) - opol.astype(np.float32))
+        same = (pol.view(np.uint16) == opol.view(np.uint16)).mean()
+        am, ao = O.masked_argmax(pol, pos256["legal"][sl]), O.masked_argmax(opol, pos256["legal"][sl])
+        ok = ao >= 0
+        print(f"  logits max {d.max():.4f}, {same:.3f} bit-identical, value max {np.abs(val - oval).max():.4f}, "
+              f"masked argmax {(am[ok] == ao[ok]).sum()} / {ok.sum()}")
+
+
+def test_int8_peak_probe_runs_and_is_plausible():
+    """The tcgen05 kind::i8 loop used as the roofline's measured denominator: runs clean and
+    lands between half of and a little above the nominal dense int8 rate (4500 TOP/s)."""
+    from brokefish_b200 import _native
+    tops, ms = ctypes.c_double(0), ctypes.c_double(0)
+    rc = _native.lib().bf_measure_i8_peak(0, 4096, ctypes.byref(tops), ctypes.byref(ms))
+    assert rc == 0, _native.lib().bf_last_error()
+    assert 2000.0 < tops.value < 5500.0, (tops.value, ms.value)
+    assert _native.lib().bf_measure_i8_peak(0, 1, ctypes.byref(tops), None) != 0     # iters out of range
