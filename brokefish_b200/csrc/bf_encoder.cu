@@ -265,9 +265,13 @@ __device__ __forceinline__ void descale(const uint32_t* acc, float sa, float sw,
             else
                 f = pk2(__uint_as_float(acc[2 * i]), __uint_as_float(acc[2 * i + 1]));
             if (kAcc != kAccPlain) f = mul2(mul2(f, sa2), sw2);
-            __half2 h = __hadd2(as_h2(f2_to_h2(f)), as_h2(bw[k]));
-            if (kRelu) h = __hmax2(h, __float2half2_rn(0.0f));
-            out[i] = as_u32(h);
+            if (kRelu) {
+                // relu(x + b) in one instruction: x * 1 is exact, so the sum is rounded once
+                // exactly as the fp16 add is, and the clamp is part of the same operation
+                out[i] = hfma2_relu(f2_to_h2(f), 0x3C003C00u, bw[k]);
+            } else {
+                out[i] = as_u32(__hadd2(as_h2(f2_to_h2(f)), as_h2(bw[k])));
+            }
         }
     }
 }
@@ -592,21 +596,30 @@ __device__ __forceinline__ void attention_block(RowCtx& c, const Params& p, cons
 #pragma unroll 1
     for (int j = 0; j < 4; ++j) {
         row_wait_acc<kDbg>(c, 0, j == 0 ? PH_LN : PH_PAIR_BAR);
-        // this thread's 48 of the chunk's 192 columns, 16 at a time
-#pragma unroll 1
-        for (int g = 0; g < 3; ++g) {
-            const int c0 = 48 * c.qt + 16 * g, m = c0 >> 6, cm = c0 & 63;
-            uint32_t acc[16], h[8];
-            tmem_ld16(c.tm + TM_ACC + c0, acc);
+        // this thread's 48 of the chunk's 192 columns, 16 at a time; the load of the next group
+        // is in flight while a group is descaled and staged
+        {
+            uint32_t pa[16], pb[16];
+            tmem_ld16(c.tm + TM_ACC + 48 * c.qt, pa);
             tmem_wait_ld();
-            if (kDbg && cap && p.cap_op == BF_OP_QKV && c.valid) store_words<16>(p.cap_acc + c.grow * 768 + j * 192 + c0, acc);
-            descale<16, false, kFP8 ? kAccPlain : kAccInt>(acc, sa, __ldg(lp.sw_qkv + m * 2 + (j >> 1)),
-                                                            lp.b_qkv + j * 192 + c0, h);
 #pragma unroll
-            for (int k = 0; k < 2; ++k)
-                sts128(c.sm_r + m * 16384 + sw_off(c.row, (cm >> 3) + k),
-                       make_uint4(h[4 * k], h[4 * k + 1], h[4 * k + 2], h[4 * k + 3]));
-            if (kDbg && dbgl && dbg == 5 + m && c.valid) store_words<8>(p.y + c.grow * kD + 64 * j + cm, h);
+            for (int g = 0; g < 3; ++g) {
+                uint32_t* cur = (g & 1) ? pb : pa;
+                uint32_t* nxt = (g & 1) ? pa : pb;
+                if (g < 2) tmem_ld16(c.tm + TM_ACC + 48 * c.qt + 16 * (g + 1), *reinterpret_cast<uint32_t(*)[16]>(nxt));
+                const int c0 = 48 * c.qt + 16 * g, m = c0 >> 6, cm = c0 & 63;
+                uint32_t h[8];
+                if (kDbg && cap && p.cap_op == BF_OP_QKV && c.valid)
+                    store_words<16>(p.cap_acc + c.grow * 768 + j * 192 + c0, cur);
+                descale<16, false, kFP8 ? kAccPlain : kAccInt>(cur, sa, __ldg(lp.sw_qkv + m * 2 + (j >> 1)),
+                                                                lp.b_qkv + j * 192 + c0, h);
+#pragma unroll
+                for (int k = 0; k < 2; ++k)
+                    sts128(c.sm_r + m * 16384 + sw_off(c.row, (cm >> 3) + k),
+                           make_uint4(h[4 * k], h[4 * k + 1], h[4 * k + 2], h[4 * k + 3]));
+                if (kDbg && dbgl && dbg == 5 + m && c.valid) store_words<8>(p.y + c.grow * kD + 64 * j + cm, h);
+                if (g < 2) tmem_wait_ld();
+            }
         }
         row_release_acc(c, 0);
         prof_mark<kDbg>(c, PH_QKV_EPI);
@@ -695,18 +708,34 @@ __device__ __forceinline__ void ffn_block(RowCtx& c, const Params& p, const Laye
         const int kind2 = (0xD4 >> st) & 1;
         const int ch = kind2 ? ((0x32010000u >> (4 * st)) & 0xF) : ((0x00302010u >> (4 * st)) & 0xF);
         if (!kind2) {
+            // 64 columns in four 16-column pieces (two per accumulator slot); the tensor-memory
+            // load of a piece is in flight while the piece before it is descaled
             uint32_t hid[32];
-#pragma unroll
-            for (int jh = 0; jh < 2; ++jh) {
-                row_wait_acc<kDbg>(c, jh, PH_FF1_EPI, PH_WAIT_FF1);
-                uint32_t acc[32];
-                tmem_ld32(c.tm + TM_ACC + 128 * jh + 32 * c.qt, acc);
+            {
+                constexpr int kA = kFP8 ? kAccFloat : kAccInt;
+                const bool capf = kDbg && cap && p.cap_op == BF_OP_FF1 && c.valid;
+                const int col0 = 256 * ch + 32 * c.qt;                 // + 128 jh + 16 half
+                const uint32_t t0 = c.tm + TM_ACC + 32 * c.qt;
+                const float sw0 = __ldg(lp.sw_ff1 + 2 * ch), sw1 = __ldg(lp.sw_ff1 + 2 * ch + 1);
+                uint32_t pa[16], pb[16];
+                row_wait_acc<kDbg>(c, 0, PH_FF1_EPI, PH_WAIT_FF1);
+                tmem_ld16(t0, pa);
                 tmem_wait_ld();
-                row_release_acc(c, jh);
-                const int col = 256 * ch + 128 * jh + 32 * c.qt;
-                if (kDbg && cap && p.cap_op == BF_OP_FF1 && c.valid) store_words<32>(p.cap_acc + c.grow * 1024 + col, acc);
-                descale<32, true, kFP8 ? kAccFloat : kAccInt>(acc, sa, __ldg(lp.sw_ff1 + 2 * ch + jh), lp.b_ff1 + col,
-                                                              &hid[16 * jh]);
+                tmem_ld16(t0 + 16, pb);
+                if (capf) store_words<16>(p.cap_acc + c.grow * 1024 + col0, pa);
+                descale<16, true, kA>(pa, sa, sw0, lp.b_ff1 + col0, &hid[0]);
+                row_release_acc(c, 0);                                 // waits for the load of pb
+                row_wait_acc<kDbg>(c, 1, PH_FF1_EPI, PH_WAIT_FF1);
+                tmem_ld16(t0 + 128, pa);
+                if (capf) store_words<16>(p.cap_acc + c.grow * 1024 + col0 + 16, pb);
+                descale<16, true, kA>(pb, sa, sw0, lp.b_ff1 + col0 + 16, &hid[8]);
+                tmem_wait_ld();
+                tmem_ld16(t0 + 128 + 16, pb);
+                if (capf) store_words<16>(p.cap_acc + c.grow * 1024 + col0 + 128, pa);
+                descale<16, true, kA>(pa, sa, sw1, lp.b_ff1 + col0 + 128, &hid[16]);
+                row_release_acc(c, 1);
+                if (capf) store_words<16>(p.cap_acc + c.grow * 1024 + col0 + 144, pb);
+                descale<16, true, kA>(pb, sa, sw1, lp.b_ff1 + col0 + 144, &hid[24]);
             }
             // per-row u8 scale over the 256-wide chunk (encoder.cu:1510-1517)
             const float amax = exchange_max(c, amax_h2<32>(hid, false));
@@ -730,24 +759,36 @@ __device__ __forceinline__ void ffn_block(RowCtx& c, const Params& p, const Laye
             for (int jh = 0; jh < 2; ++jh) {
                 row_wait_acc<kDbg>(c, jh, PH_FF2_EPI, PH_WAIT_FF2);
                 const float s2 = __ldg(lp.sw_ff2 + jh);
-                uint32_t acc[32], run[16];
+                // 32 columns as two 16-column pieces: the second piece's loads are in flight
+                // while the first is accumulated
+                uint32_t pa[16], pb[16], run[16];
                 const int col = 128 * jh + 32 * c.qt;
-                tmem_ld32(c.tm + TM_ACC + col, acc);
-                if (ch > 0) tmem_ld16(c.tm + TM_OY + (col >> 1), run);
-                tmem_wait_ld();
-                row_release_acc(c, jh);
-                if (kDbg && cap && p.cap_op == BF_OP_FF2 + ch && c.valid) store_words<32>(p.cap_acc + c.grow * 256 + col, acc);
+                const bool capf = kDbg && cap && p.cap_op == BF_OP_FF2 + ch && c.valid;
                 const uint64_t s1_2 = pk2(s1, s1), s2_2 = pk2(s2, s2);
+                tmem_ld16(c.tm + TM_ACC + col, pa);
+                if (ch > 0) tmem_ld8(c.tm + TM_OY + (col >> 1), *reinterpret_cast<uint32_t(*)[8]>(&run[0]));
+                tmem_wait_ld();
+                tmem_ld16(c.tm + TM_ACC + col + 16, pb);
+                if (ch > 0) tmem_ld8(c.tm + TM_OY + (col >> 1) + 8, *reinterpret_cast<uint32_t(*)[8]>(&run[8]));
+                if (capf) store_words<16>(p.cap_acc + c.grow * 256 + col, pa);
 #pragma unroll
-                for (int i = 0; i < 16; ++i) {
-                    uint64_t f = kFP8 ? pk2(__uint_as_float(acc[2 * i]), __uint_as_float(acc[2 * i + 1]))
-                                      : pk2(static_cast<float>(static_cast<int>(acc[2 * i])),
-                                            static_cast<float>(static_cast<int>(acc[2 * i + 1])));
-                    // `float(acc) * sa * sw + float(run)` (int8_gemm.cuh:285-294): the compiler
-                    // fuses the second product with the sum in the reference, so it is one fma here
-                    f = mul2(f, s1_2);
-                    f = ch > 0 ? fma2(f, s2_2, h2_to_f2(run[i])) : mul2(f, s2_2);
-                    run[i] = f2_to_h2(f);
+                for (int half = 0; half < 2; ++half) {
+                    if (half == 1) {
+                        row_release_acc(c, jh);                        // waits for the second piece
+                        if (capf) store_words<16>(p.cap_acc + c.grow * 256 + col + 16, pb);
+                    }
+                    const uint32_t* acc = half ? pb : pa;
+#pragma unroll
+                    for (int i = 0; i < 8; ++i) {
+                        uint64_t f = kFP8 ? pk2(__uint_as_float(acc[2 * i]), __uint_as_float(acc[2 * i + 1]))
+                                          : pk2(static_cast<float>(static_cast<int>(acc[2 * i])),
+                                                static_cast<float>(static_cast<int>(acc[2 * i + 1])));
+                        // `float(acc) * sa * sw + float(run)` (int8_gemm.cuh:285-294): the compiler
+                        // fuses the second product with the sum in the reference, so it is one fma here
+                        f = mul2(f, s1_2);
+                        f = ch > 0 ? fma2(f, s2_2, h2_to_f2(run[8 * half + i])) : mul2(f, s2_2);
+                        run[8 * half + i] = f2_to_h2(f);
+                    }
                 }
                 if (ch < 3) {
                     tmem_st16(c.tm + TM_OY + (col >> 1), run);

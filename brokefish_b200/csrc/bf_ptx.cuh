@@ -328,6 +328,12 @@ __device__ __forceinline__ uint32_t f2_to_h2(uint64_t v) {
 }
 
 // 2^x, hardware approximation (what `__expf` uses after its multiply by log2 e)
+// relu(a * b + c) on packed fp16 pairs, one rounding
+__device__ __forceinline__ uint32_t hfma2_relu(uint32_t a, uint32_t b, uint32_t c) {
+    uint32_t d;
+    asm("fma.rn.relu.f16x2 %0, %1, %2, %3;" : "=r"(d) : "r"(a), "r"(b), "r"(c));
+    return d;
+}
 __device__ __forceinline__ float ex2_approx(float x) {
     float y;
     asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
