@@ -17,6 +17,10 @@ next to this script:
   digests of its folded + quantised weights;
 * ``ref_outputs_C.npz`` -- the reference fp32 network's outputs for a network with per-layer
   input re-injection at both norms and nonzero coefficients;
+* ``ref_priors.npz`` -- priors, move labels and edge counts that the reference's search
+  (``Search.root_init`` -> ``_expand``) derives from its fp32 network's fp16 logits on 160
+  non-terminal positions, at edge caps 96 and 12, and the reference validator's metrics on a
+  perturbed copy of those logits;
 * ``scheme_kats.npz`` -- known answers of the reference's int8 scheme functions.
 
 The fixtures are what ``tests/test_oracle_golden.py`` pins the CPU oracle against; the
@@ -174,6 +178,38 @@ def main() -> int:
                                                       for k in sorted(state)])),
                         fp32_policy=p.numpy().astype(np.float16), fp32_promo=pr.numpy().astype(np.float16),
                         fp32_value=v.numpy().astype(np.float32))
+
+    # the search's own expansion step on reference logits: priors, move labels and edge counts
+    # (brokefish/nn/validate.py:248-280 run_priors -> Search.root_init -> Search._expand), with
+    # the default edge cap and with a small one so that the truncation branch is exercised
+    print("priors through the reference search", flush=True)
+    from brokefish.nn.validate import compare as ref_compare, run_priors      # reference
+    legal_words = torch.from_numpy(pos["legal"].view(np.int64).copy())
+    rows = (legal_words != 0).any(-1).nonzero(as_tuple=True)[0][:160]
+    state = seeded_state(**sets["B"])
+    net = RefNet().eval()
+    net.load_state_dict(state, strict=True)
+    with torch.no_grad():
+        pol, pro, val = net(boards[rows], control[rows], rep[rows])
+    pol16, pro16 = pol.half(), pro.half()
+    out = {"rows": rows.numpy(), "policy": pol16.numpy(), "promo": pro16.numpy(), "value": val.numpy()}
+    for cap in (96, 12):
+        pri, mov, ne = run_priors(boards[rows], control[rows], pol16, pro16, val, cap)
+        out[f"prior_{cap}"] = pri.numpy().astype(np.float16)
+        out[f"move_{cap}"] = mov.numpy()
+        out[f"nedges_{cap}"] = ne.numpy()
+    # the reference's metrics on a perturbed copy of the logits, as known answers for compare()
+    g = torch.Generator().manual_seed(99)
+    pol_b = (pol16.float() + 0.05 * torch.randn(pol16.shape, generator=g)).half()
+    ref_b = (*run_priors(boards[rows], control[rows], pol16, pro16, val, 96), pol16, pro16, val)
+    got_b = (*run_priors(boards[rows], control[rows], pol_b, pro16, val + 0.01, 96), pol_b, pro16, val + 0.01)
+    dl = ref_compare("perturbed", ref_b, got_b)
+    out["policy_perturbed"] = pol_b.numpy()
+    out["delta_perturbed"] = np.array([dl.max_abs, dl.p95_abs, dl.max_rel, dl.max_kl, dl.mean_kl,
+                                       dl.top1_disagree, dl.top3_miss, dl.flip_risk, dl.flushed,
+                                       dl.edge_set_differs, dl.max_abs_logit, dl.nonfinite,
+                                       dl.max_abs_value], dtype=np.float64)
+    np.savez_compressed(os.path.join(HERE, "ref_priors.npz"), **out)
 
     print("scheme known answers", flush=True)
     g = torch.Generator().manual_seed(1234)

@@ -1,0 +1,128 @@
+"""The prior-space validator (brokefish_b200/validate.py) against the reference's own search:
+``expand_priors`` must reproduce, bit for bit, the priors, move labels and edge counts that
+``Search.root_init`` -> ``Search._expand`` derives from the same logits (committed under
+tests/golden/ref_priors.npz by make_golden.py), and ``compare`` must reproduce the reference
+validator's metrics on the same pair of logit sets."""
+import os
+
+import numpy as np
+import pytest
+import torch
+
+from conftest import GOLDEN
+from brokefish_b200 import validate as V
+
+
+@pytest.fixture(scope="module")
+def gold():
+    z = np.load(os.path.join(GOLDEN, "ref_priors.npz"))
+    return {k: z[k] for k in z.files}
+
+
+@pytest.fixture(scope="module")
+def nodes(gold, pos256):
+    rows = gold["rows"]
+    t = lambda a: torch.from_numpy(np.ascontiguousarray(a))
+    return (t(pos256["boards"][rows]), t(pos256["control"][rows]),
+            t(pos256["legal"][rows].view(np.int64).copy()))
+
+
+@pytest.mark.parametrize("cap", [96, 12])
+def test_expand_priors_equals_the_reference_search(cap, gold, nodes):
+    boards, control, legal = nodes
+    pri, mov, ne = V.expand_priors(boards, control, legal, torch.from_numpy(gold["policy"]),
+                                   torch.from_numpy(gold["promo"]), cap)
+    assert np.array_equal(ne.numpy(), gold[f"nedges_{cap}"])
+    assert np.array_equal(mov.numpy(), gold[f"move_{cap}"])
+    assert np.array_equal(pri.numpy().astype(np.float16).view(np.uint16), gold[f"prior_{cap}"].view(np.uint16))
+    if cap == 12:
+        assert (gold["nedges_96"] > 12).any() and ne.max() == 12      # the truncation branch ran
+    # a distribution over the kept edges, canonical order, promotion types only on promotions
+    live = torch.arange(cap)[None, :] < ne[:, None]
+    assert torch.allclose(pri.masked_fill(~live, 0).sum(-1), torch.ones(len(ne)), atol=2e-3)
+    field = (mov.long() & 2047)[live]
+    assert (field >= 0).all() and (field < 2048).all()
+    flat = (mov.long() & 2047) * 4 + (mov.long() >> 11)
+    assert ((flat[:, 1:] > flat[:, :-1]) | ~live[:, 1:]).all()
+
+
+def test_compare_reproduces_the_reference_metrics(gold, nodes):
+    boards, control, legal = nodes
+    pol, pro, val = (torch.from_numpy(gold[k]) for k in ("policy", "promo", "value"))
+    pol_b = torch.from_numpy(gold["policy_perturbed"])
+    ref = (*V.expand_priors(boards, control, legal, pol, pro, 96), pol, pro, val)
+    got = (*V.expand_priors(boards, control, legal, pol_b, pro, 96), pol_b, pro, val + 0.01)
+    d = V.compare("perturbed", ref, got)
+    mine = np.array([d.max_abs, d.p95_abs, d.max_rel, d.max_kl, d.mean_kl, d.top1_disagree, d.top3_miss,
+                     d.flip_risk, d.flushed, d.edge_set_differs, d.max_abs_logit, d.nonfinite,
+                     d.max_abs_value], dtype=np.float64)
+    assert np.allclose(mine, gold["delta_perturbed"], rtol=1e-5, atol=1e-9), (mine, gold["delta_perturbed"])
+    same = V.compare("same", ref, ref)
+    assert same.max_abs == 0.0 and same.top1_disagree == 0.0 and same.edge_set_differs == 0
+
+
+def test_compare_reports_inf_when_nothing_is_comparable(gold, nodes):
+    """A variant that changes every position's edge set leaves nothing to difference: the
+    maxima read inf, never a perfect 0 (brokefish/nn/validate.py:337-344)."""
+    boards, control, legal = nodes
+    pol, pro, val = (torch.from_numpy(gold[k]) for k in ("policy", "promo", "value"))
+    ref = (*V.expand_priors(boards, control, legal, pol, pro, 96), pol, pro, val)
+    other = (ref[0], ref[1], ref[2] + 1, pol, pro, val)
+    d = V.compare("shifted", ref, other)
+    assert d.edge_set_differs == len(ref[2]) and d.max_abs == float("inf") and d.p95_abs == float("inf")
+
+
+def test_validate_on_cpu_scores_an_injected_error(pos256):
+    """The suite bites: an evaluator whose policy logits are shifted on one slot moves the
+    priors, an exact copy of the fp32 network does not (the method of the reference's
+    tests/test_validate.py)."""
+    from brokefish_b200.nn.model import BrokefishNet, seeded_state
+    net = BrokefishNet().eval()
+    net.load_state_dict(seeded_state(seed=0, std=None, perturb_norms=True))
+    net = net.half().float()
+    n = 48
+    t = lambda a: torch.from_numpy(np.ascontiguousarray(a[:n]))
+    boards, control, rep = t(pos256["boards"]), t(pos256["control"]), t(pos256["rep"])
+    legal = torch.from_numpy(pos256["legal"][:n].view(np.int64).copy())
+
+    def exact(b, c, r):
+        with torch.no_grad():
+            p, q, v = net(b, c, r)
+        return p.half(), q.half(), v
+
+    def bumped(b, c, r):
+        p, q, v = exact(b, c, r)
+        p = p.clone()
+        p[:, 3] += 0.5
+        return p, q, v
+
+    out = V.validate(net, boards, control, rep, legal, {"exact": exact, "bumped": bumped}, verbose=False)
+    assert out["exact"].max_abs == out["store"].max_abs and out["exact"].top1_disagree == 0.0
+    assert out["bumped"].max_abs > 10 * max(out["store"].max_abs, 1e-4)
+    assert not out["exact"].aliases_across_calls
+
+
+@pytest.mark.gpu
+def test_b200_evaluator_in_prior_space(pos4096):
+    """The int8 kernel against the fp32 network where the search looks: the reference's own
+    acceptance quantities.  Random-init weights (the only ones available): max |dp| within 0.05,
+    no flushed prior, no non-finite output, top-1 moves on fewer than 3 % of positions, and the
+    outputs are reused buffers (as the reference's)."""
+    from brokefish_b200.nn import encoder_impl
+    from brokefish_b200.nn.model import BrokefishNet, seeded_state
+    net = BrokefishNet().eval()
+    net.load_state_dict(seeded_state(seed=0, std=None, perturb_norms=True))
+    net = net.half().float()
+    dev = torch.device("cuda")
+    n = 2048
+    t = lambda a: torch.from_numpy(np.ascontiguousarray(a[:n])).to(dev)
+    boards, control, rep = t(pos4096["boards"]), t(pos4096["control"]), t(pos4096["rep"])
+    legal = torch.from_numpy(pos4096["legal"][:n].view(np.int64).copy()).to(dev)
+    enc = encoder_impl("cuda")(net)
+    out = V.validate(net, boards, control, rep, legal, {"b200-int8": enc.forward_full}, verbose=True)
+    d = out["b200-int8"]
+    assert d.nonfinite == 0 and d.flushed == 0 and d.edge_set_differs == 0
+    assert d.max_abs <= 0.05 and d.top1_disagree <= 0.03 and d.max_abs_value <= 0.08
+    assert d.aliases_across_calls
+    assert out["store"].max_abs <= d.max_abs
+    enc.close()
