@@ -103,6 +103,11 @@ struct Params {
     __half* promo;
     float* value;
     __half* y;
+    // fused expansion (optional): per position up to `e_cap` edges in canonical order
+    __half* prior;              // [n, e_cap] fp16 priors, zero beyond the edge count
+    int16_t* move;              // [n, e_cap] labels: slot * 64 + square | promotion type << 11
+    int* nedges;                // [n] edges written
+    int e_cap;
     int debug_stage, debug_layer;
     int cap_layer, cap_op;
     uint8_t* cap_a;
@@ -818,6 +823,144 @@ __device__ __forceinline__ void ffn_block(RowCtx& c, const Params& p, const Laye
     }
 }
 
+// ------------------------------------------------------------------------------------------
+// Fused expansion: the node's legal edges and their priors straight from the staged logits,
+// what the reference's search does in a kernel of its own after reading the logits back
+// (Search._expand, brokefish/search/torch_impl.py:962-1033; csrc/search.cuh:593-798).  One warp
+// per board, lane = piece slot.  A candidate is a legal (slot, square), four times over
+// (N B R Q) when a pawn reaches its last rank; its logit is the policy logit plus, for a
+// promotion, log_softmax of the slot's promotion logits, evaluated as (x - max) - log(sum);
+// the prior is exp(logit - max) / sum over the kept candidates, stored as fp16.  More than
+// `e_cap` candidates: the e_cap largest logits stay, ties to the earlier candidate.  Edges are
+// written in canonical order (slot, square, type) whatever their prior.
+// ------------------------------------------------------------------------------------------
+__device__ __forceinline__ uint32_t order_key(float v) {
+    // unsigned keys that sort like the floats; -0 and +0 share a key
+    uint32_t b = __float_as_uint(v);
+    if (b == 0x80000000u) b = 0u;
+    return (b & 0x80000000u) ? ~b : (b ^ 0x80000000u);
+}
+template <typename F>
+__device__ __forceinline__ void each_candidate(unsigned long long legal, unsigned long long promos,
+                                               uint32_t row_smem, uint32_t row_xor, const float (&type_lp)[4],
+                                               F&& visit) {
+    for (unsigned long long rest = legal; rest != 0ull; rest &= rest - 1ull) {
+        const int sq = __ffsll(static_cast<long long>(rest)) - 1;
+        uint16_t raw;
+        asm volatile("ld.shared.u16 %0, [%1];"
+                     : "=h"(raw)
+                     : "r"(row_smem + (((static_cast<uint32_t>(sq) >> 3) ^ row_xor) << 4) + 2u * (sq & 7)));
+        const float base = __half2float(__ushort_as_half(raw));
+        if ((promos >> sq) & 1ull) {
+#pragma unroll
+            for (int t = 0; t < 4; ++t) visit(sq, t, __fadd_rn(base, type_lp[t]));
+        } else {
+            visit(sq, 0, base);
+        }
+    }
+}
+__device__ __forceinline__ int warp_prefix(int mine, int lane, int& total) {
+    int inc = mine;
+#pragma unroll
+    for (int off = 1; off < 32; off <<= 1) {
+        const int up = __shfl_up_sync(0xffffffffu, inc, off);
+        if (lane >= off) inc += up;
+    }
+    total = __shfl_sync(0xffffffffu, inc, 31);
+    return inc - mine;
+}
+__device__ __forceinline__ float warp_sum_to_all(float v) {
+#pragma unroll
+    for (int off = 16; off > 0; off >>= 1) v = __fadd_rn(v, __shfl_down_sync(0xffffffffu, v, off));
+    return __shfl_sync(0xffffffffu, v, 0);
+}
+__device__ __forceinline__ void expand_board(const Params& p, int board, int lane, bool valid, uint32_t word,
+                                             int ctl, unsigned long long legal, uint32_t stage_pol,
+                                             uint32_t stage_aux, int row) {
+    // the staged row of this slot: 16-byte group g of the row lives at sw_off(row, g)
+    const uint32_t row_smem = stage_pol + static_cast<uint32_t>(row) * 128u;
+    const uint32_t row_xor = static_cast<uint32_t>(row & 7);
+    const bool pawn = ((word >> 11) & 1u) == 0u && ((word >> 6) & 7u) == 0u;
+    const unsigned long long last = ctl < 0 ? 0xffull : (0xffull << 56);
+    const unsigned long long promos = pawn ? (legal & last) : 0ull;
+    float type_lp[4] = {0.f, 0.f, 0.f, 0.f};
+    if (promos != 0ull) {
+        uint32_t w0, w1;
+        asm volatile("ld.shared.v2.b32 {%0, %1}, [%2];" : "=r"(w0), "=r"(w1) : "r"(stage_aux + sw_off(row, 0)));
+        const float x[4] = {__low2float(as_h2(w0)), __high2float(as_h2(w0)), __low2float(as_h2(w1)),
+                            __high2float(as_h2(w1))};
+        const float top = fmaxf(fmaxf(x[0], x[1]), fmaxf(x[2], x[3]));
+        float z = 0.f;
+#pragma unroll
+        for (int t = 0; t < 4; ++t) z = __fadd_rn(z, expf(__fsub_rn(x[t], top)));
+        const float lz = logf(z);
+#pragma unroll
+        for (int t = 0; t < 4; ++t) type_lp[t] = __fsub_rn(__fsub_rn(x[t], top), lz);
+    }
+    const int e_cap = p.e_cap;
+    int total = 0;
+    const int mine = __popcll(legal) + 3 * __popcll(promos);
+    int first = warp_prefix(mine, lane, total);          // this slot's first edge index
+    // threshold of a truncating node: the e_cap-th largest key, found bit by bit
+    const bool cut = total > e_cap;
+    uint32_t thr = 0u;
+    int ties_wanted = 0, tie_rank0 = 0;
+    if (cut) {
+#pragma unroll 1
+        for (int bit = 31; bit >= 0; --bit) {
+            const uint32_t trial = thr | (1u << bit);
+            int at_least = 0;
+            each_candidate(legal, promos, row_smem, row_xor, type_lp, [&](int, int, float lg) { at_least += order_key(lg) >= trial; });
+            if (__reduce_add_sync(0xffffffffu, static_cast<unsigned>(at_least)) >= static_cast<unsigned>(e_cap)) thr = trial;
+        }
+        int above = 0, equal = 0;
+        each_candidate(legal, promos, row_smem, row_xor, type_lp, [&](int, int, float lg) {
+            const uint32_t k = order_key(lg);
+            above += k > thr;
+            equal += k == thr;
+        });
+        int above_all = 0, equal_all = 0;
+        const int above_before = warp_prefix(above, lane, above_all);
+        tie_rank0 = warp_prefix(equal, lane, equal_all);
+        ties_wanted = e_cap - above_all;
+        first = above_before + min(tie_rank0, ties_wanted);
+    }
+    // a candidate stays when it beats the threshold, or ties with it early enough
+    int tie_rank = tie_rank0;
+    auto stays = [&](float lg) -> bool {
+        if (!cut) return true;
+        const uint32_t k = order_key(lg);
+        if (k > thr) return true;
+        if (k < thr) return false;
+        return tie_rank++ < ties_wanted;
+    };
+    float top = -INFINITY;
+    each_candidate(legal, promos, row_smem, row_xor, type_lp, [&](int, int, float lg) { if (stays(lg)) top = fmaxf(top, lg); });
+#pragma unroll
+    for (int off = 16; off > 0; off >>= 1) top = fmaxf(top, __shfl_xor_sync(0xffffffffu, top, off));
+    tie_rank = tie_rank0;
+    float part = 0.f;
+    each_candidate(legal, promos, row_smem, row_xor, type_lp, [&](int, int, float lg) {
+        if (stays(lg)) part = __fadd_rn(part, expf(__fsub_rn(lg, top)));
+    });
+    const float z = warp_sum_to_all(part);
+    const int kept = cut ? e_cap : total;
+    if (valid) {
+        __half* out_p = p.prior + static_cast<size_t>(board) * e_cap;
+        int16_t* out_m = p.move + static_cast<size_t>(board) * e_cap;
+        tie_rank = tie_rank0;
+        int at = first;
+        each_candidate(legal, promos, row_smem, row_xor, type_lp, [&](int sq, int t, float lg) {
+            if (!stays(lg)) return;
+            out_p[at] = __float2half_rn(__fdiv_rn(expf(__fsub_rn(lg, top)), z));
+            out_m[at] = static_cast<int16_t>((lane * 64 + sq) | (t << 11));
+            ++at;
+        });
+        for (int i = kept + lane; i < e_cap; i += 32) { out_p[i] = __float2half_rn(0.f); out_m[i] = 0; }
+        if (lane == 0) p.nedges[board] = kept;
+    }
+}
+
 // The "prenorm" value head (csrc/encoder.cu:1008-1057; nn/model.py:576-584): the raw residual
 // stream is averaged over the board's live tokens, that one vector goes through the final
 // LayerNorm (with affine) and is dotted with the value rows, all in fp32.  Written as one pass
@@ -975,8 +1118,10 @@ __device__ __forceinline__ void row_warps_tile(RowCtx& c, const Params& p, int t
     float pre[3] = {0.f, 0.f, 0.f};
     if (p.vmode == 2) prenorm_value(c, p, c.valid ? alive : 0xffffffffu, pre);
     prof_mark<kDbg>(c, PH_LN);
-    constexpr uint32_t kHeadPitch = 208;                 // bytes per staged row: 96 halves + pad
-    const uint32_t stage = c.sm_a + 8192u * c.q;
+    // Staging uses only this board's own rows of the A-operand slabs (another board may already
+    // be writing its rows for the next tile): policy columns 0-63 in K-slab 0 at the operand's
+    // swizzled row address, the 32 aux columns in K-slab 1.
+    const uint32_t stage_pol = c.sm_a, stage_aux = c.sm_a + 16384u;
     board_sync(c);                                       // this board's rows of the operand are written
     {
         const uint4* hf = reinterpret_cast<const uint4*>(p.tail + kTailHeadFrag) + c.lane;
@@ -1015,21 +1160,22 @@ __device__ __forceinline__ void row_warps_tile(RowCtx& c, const Params& p, int t
         for (int jj = 0; jj < 3; ++jj)
 #pragma unroll
             for (int m = 0; m < 2; ++m) {
-                const uint32_t at = stage + (16 * m + g) * kHeadPitch + (8 * (3 * c.qt + jj) + 2 * t) * 2;
-                sts32(at, acc[jj][m][0]);
-                sts32(at + 8 * kHeadPitch, acc[jj][m][1]);
+                const int j = 3 * c.qt + jj, r0 = 32 * c.q + 16 * m + g;
+                const uint32_t base = j < 8 ? stage_pol : stage_aux;
+                sts32(base + sw_off(r0, j & 7) + 4 * t, acc[jj][m][0]);
+                sts32(base + sw_off(r0 + 8, j & 7) + 4 * t, acc[jj][m][1]);
             }
     }
     board_sync(c);                                       // the board's 32 x 96 logits are staged
     {
         uint32_t lgw[8], aux[4] = {0u, 0u, 0u, 0u};
         {
-            const uint4 v0 = lds128(stage + c.lane * kHeadPitch + 32 * c.qt);
-            const uint4 v1 = lds128(stage + c.lane * kHeadPitch + 32 * c.qt + 16);
+            const uint4 v0 = lds128(stage_pol + sw_off(c.row, 2 * c.qt));
+            const uint4 v1 = lds128(stage_pol + sw_off(c.row, 2 * c.qt + 1));
             lgw[0] = v0.x; lgw[1] = v0.y; lgw[2] = v0.z; lgw[3] = v0.w;
             lgw[4] = v1.x; lgw[5] = v1.y; lgw[6] = v1.z; lgw[7] = v1.w;
             if (c.qt == 0) {
-                const uint4 va = lds128(stage + c.lane * kHeadPitch + 128);   // columns 64..71
+                const uint4 va = lds128(stage_aux + sw_off(c.row, 0));        // columns 64..71
                 aux[0] = va.x; aux[1] = va.y; aux[2] = va.z; aux[3] = va.w;
             }
         }
@@ -1045,6 +1191,9 @@ __device__ __forceinline__ void row_warps_tile(RowCtx& c, const Params& p, int t
             lg[i] = v;
         }
         if (c.valid && p.policy != nullptr) store_words<8>(p.policy + c.grow * 64 + 16 * c.qt, lg);
+        if (p.prior != nullptr && c.qt == 1)
+            expand_board(p, board, c.lane, c.valid, word, ctl, p.legal != nullptr && c.valid ? lw : 0ull,
+                         stage_pol, stage_aux, c.row);
         if (c.qt == 0) {
             if (c.valid && p.promo != nullptr)
                 *reinterpret_cast<uint2*>(p.promo + c.grow * 4) = make_uint2(aux[0], aux[1]);
@@ -1461,9 +1610,17 @@ struct bf_handle {
 
 namespace {
 
+struct PriorOut {
+    void* prior;
+    int16_t* move;
+    int* nedges;
+    int e_cap;
+};
+
 int launch(bf_handle* h, const uint16_t* boards, const int16_t* control, const uint8_t* rep,
            const uint64_t* legal, int n, void* policy, void* promo, float* value, void* y, int stage,
-           int stage_layer, int cap_layer, int cap_op, uint8_t* cap_a, int32_t* cap_acc, cudaStream_t stream) {
+           int stage_layer, int cap_layer, int cap_op, uint8_t* cap_a, int32_t* cap_acc, cudaStream_t stream,
+           const PriorOut* po = nullptr) {
     if (h == nullptr) return fail(BF_EINVAL, "null handle");
     if (n < 0) return fail(BF_EINVAL, "n must be >= 0");
     if (n == 0) return BF_OK;
@@ -1489,6 +1646,9 @@ int launch(bf_handle* h, const uint16_t* boards, const int16_t* control, const u
     p.cap_layer = cap_layer; p.cap_op = cap_op; p.cap_a = cap_a; p.cap_acc = cap_acc;
     p.status = h->status;
     p.prof = h->prof_on ? h->prof : nullptr;
+    if (po != nullptr) {
+        p.prior = static_cast<__half*>(po->prior); p.move = po->move; p.nedges = po->nedges; p.e_cap = po->e_cap;
+    }
     const int n_tiles = (n + 3) / 4;
     const int grid = n_tiles < h->sm_count ? n_tiles : h->sm_count;
     // the instrumented instantiation only when a dump, a capture or the phase clock is asked for
@@ -1598,6 +1758,17 @@ int bf_forward(bf_handle* h, const uint16_t* boards, const int16_t* control, con
                const uint64_t* legal, int n, void* policy, void* promo, float* value, void* stream) {
     return launch(h, boards, control, rep, legal, n, policy, promo, value, nullptr, 0, 0, -1, -1, nullptr,
                   nullptr, static_cast<cudaStream_t>(stream));
+}
+
+int bf_forward_priors(bf_handle* h, const uint16_t* boards, const int16_t* control, const uint8_t* rep,
+                      const uint64_t* legal, int n, int e_cap, void* prior, int16_t* move, int* nedges,
+                      float* value, void* policy, void* promo, void* stream) {
+    if (legal == nullptr) return fail(BF_EINVAL, "the fused expansion needs the legal-move words");
+    if (prior == nullptr || move == nullptr || nedges == nullptr) return fail(BF_EINVAL, "prior, move and nedges must be non-null");
+    if (e_cap < 1 || e_cap > 255) return fail(BF_EINVAL, "e_cap must be in 1..255");
+    const PriorOut po{prior, move, nedges, e_cap};
+    return launch(h, boards, control, rep, legal, n, policy, promo, value, nullptr, 0, 0, -1, -1, nullptr,
+                  nullptr, static_cast<cudaStream_t>(stream), &po);
 }
 
 int bf_forward_stage_at(bf_handle* h, const uint16_t* boards, const int16_t* control,

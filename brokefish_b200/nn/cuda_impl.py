@@ -237,6 +237,37 @@ class FusedEncoder:
             _ptr(self.promo_out), _ptr(self.value_out), stream), "bf_forward")
         return self.policy_out, self.promo_out, self.value_out
 
+    def forward_priors(self, boards, control, rep, legal, e_cap: int = 96, logits: bool = False):
+        """Evaluate and expand in one launch: ``(prior [n,e_cap] fp16, move [n,e_cap] int16,
+        nedges [n] int32, value [n] fp32)`` — the edges of each position's search node in
+        canonical order with their priors, what the reference's search computes from the
+        logits in ``Search._expand`` (brokefish/search/torch_impl.py:962-1033).  ``legal`` is
+        the ``[n,32]`` int64 legality words.  With ``logits=True`` the masked policy and the
+        promotion logits are written as well (``self.policy_out``, ``self.promo_out``).
+        Returns views on internal buffers, which the next call overwrites."""
+        self._require_net("forward_priors")
+        n = self._check_inputs(boards, control, rep)
+        self._check_device(boards, control, rep, legal)
+        if legal is None or tuple(legal.shape) != (n, self.T) or legal.dtype is not torch.int64:
+            raise ValueError(f"legal must be [{n}, 32] int64")
+        if not 1 <= int(e_cap) <= 255:
+            raise ValueError(f"e_cap must be in 1..255, got {e_cap}")
+        self._ensure_full_buffers(n)
+        dev = torch.device("cuda", self.device)
+        if getattr(self, "_prior_shape", None) != (n, int(e_cap)):
+            self.prior_out = torch.zeros(n, int(e_cap), device=dev, dtype=torch.half)
+            self.move_out = torch.zeros(n, int(e_cap), device=dev, dtype=torch.int16)
+            self.nedges_out = torch.zeros(n, device=dev, dtype=torch.int32)
+            self._prior_shape = (n, int(e_cap))
+        b, c, r, lg = boards.contiguous(), control.contiguous(), rep.contiguous(), legal.contiguous()
+        stream = ctypes.c_void_p(torch.cuda.current_stream(self.device).cuda_stream)
+        _native.check(_native.lib().bf_forward_priors(
+            self._handle, _ptr(b), _ptr(c), _ptr(r), _ptr(lg), n, int(e_cap), _ptr(self.prior_out),
+            _ptr(self.move_out), _ptr(self.nedges_out), _ptr(self.value_out),
+            _ptr(self.policy_out) if logits else None, _ptr(self.promo_out) if logits else None, stream),
+            "bf_forward_priors")
+        return self.prior_out, self.move_out, self.nedges_out, self.value_out
+
     def forward_stage(self, boards, control, rep, stage: int, layer: int = 0):
         """Activations ``[n,32,256]`` fp16 at an intermediate stage: 9 embedding; layer 0:
         1 LN1, 5/6/7 Q/K/V, 4 attention output, 2 residual after attention, 3 LN2; 8 final

@@ -73,6 +73,24 @@ int bf_forward(bf_handle* h, const uint16_t* boards, const int16_t* control,
                const uint8_t* rep, const uint64_t* legal, int n, void* policy, void* promo,
                float* value, void* stream);
 
+/* Evaluate and expand in one launch: besides (optionally) the logits, write for every position
+ * the edges of its search node and their priors, which the reference's search derives in a
+ * kernel of its own from the logits (`Search._expand`, brokefish/search/torch_impl.py:962-1033;
+ * `expand_node`, csrc/search.cuh:593-798).  `legal` [n,32] is required (bit s of word p: the
+ * piece in slot p may move to square s).  Outputs, caller-owned device memory:
+ *   prior  [n, e_cap] fp16   softmax over the node's candidates (policy logit, plus for a pawn
+ *                            reaching its last rank log_softmax of its four promotion logits);
+ *                            more than e_cap candidates: the e_cap largest stay (ties to the
+ *                            earlier candidate) and are renormalised; zero beyond the edge count
+ *   move   [n, e_cap] int16  slot * 64 + square | promotion type << 11, canonical order
+ *   nedges [n] int32         edges written (0 for a position without a legal move)
+ *   value  [n] fp32          as bf_forward; policy / promo may be NULL to skip the 4.3 KB per
+ *                            position logit stream (when given, policy carries the legality AND)
+ * e_cap is 1..255 (the reference's search uses 96). */
+int bf_forward_priors(bf_handle* h, const uint16_t* boards, const int16_t* control, const uint8_t* rep,
+                      const uint64_t* legal, int n, int e_cap, void* prior, int16_t* move, int* nedges,
+                      float* value, void* policy, void* promo, void* stream);
+
 /* Activations at an intermediate stage as [n,32,256] fp16.  Replaces
  * `model_forward(..., debug_stage=stage)` (csrc/encoder.cu:1315-1427, 1575-1598):
  * 9 embedding; layer 0: 1 LN1 out, 5/6/7 Q/K/V after bias, 4 attention out,
