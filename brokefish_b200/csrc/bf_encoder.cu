@@ -3,11 +3,12 @@
 // What one launch computes (per position): embedding of 32 piece words, 8 pre-norm
 // encoder layers of width 256 (8 heads of 32, FFN 1024) with every weight GEMM in
 // s8/u8 x s8 -> s32 on the tcgen05 tensor cores, a final LayerNorm, and the fp16 head
-// GEMM giving 32x64 policy logits, 32x4 promotion logits and the value.  It follows the
-// arithmetic of the reference kernel (csrc/encoder.cu:1225-1599 with int8_gemm.cuh) at
-// every rounding point that can be reproduced exactly; the places where it differs
-// (fp32 instead of fp16 accumulation in attention and heads, correctly rounded 1/sqrt)
-// are listed beside the code.
+// product giving 32x64 policy logits, 32x4 promotion logits and the value; optionally the
+// search node's edges and priors straight from the epilogue.  The int8 arithmetic follows
+// the reference kernel (csrc/encoder.cu:1225-1599 with int8_gemm.cuh) at every rounding
+// point, the hardware-approximate ones included (summation order and 1/sqrt of the norms,
+// fp16-accumulate mma.sync for the attention and head products, __expf), so that its
+// outputs equal that kernel's bit for bit; only the exact-integer GEMMs run on tcgen05.
 //
 // Shape of the kernel
 //   * persistent grid, one CTA per SM, each CTA loops over tiles of 128 token rows
