@@ -262,6 +262,20 @@ def main() -> int:
         enc.forward_host(h_b, h_c, h_r, h_pol, h_pro, h_val)
     torch.cuda.synchronize(dev)
     e2e_ms = (time.perf_counter() - t0) * 1e3
+    # the same end-to-end step with the expansion fused in: edge lists back instead of logits
+    h_lg = torch.from_numpy(np.ascontiguousarray(lg).view(np.int64).copy()).pin_memory()
+    e_cap = 96
+    h_pri = torch.empty(n_local, e_cap, dtype=torch.half).pin_memory()
+    h_mov = torch.empty(n_local, e_cap, dtype=torch.int16).pin_memory()
+    h_ne = torch.empty(n_local, dtype=torch.int32).pin_memory()
+    for _ in range(3):
+        enc.forward_priors_host(h_b, h_c, h_r, h_lg, h_pri, h_mov, h_ne, h_val)
+    barrier()
+    t0 = time.perf_counter()
+    for _ in range(e2e_steps):
+        enc.forward_priors_host(h_b, h_c, h_r, h_lg, h_pri, h_mov, h_ne, h_val)
+    torch.cuda.synchronize(dev)
+    e2e_pri_ms = (time.perf_counter() - t0) * 1e3
     clocks = sampler.stop() if rank == 0 else None
     phases = None
     if args.phases and rank == 0:
@@ -272,10 +286,10 @@ def main() -> int:
         phases = {k: v / 5 for k, v in enc.read_profile().items() if k}
         enc.set_profile(False)
 
-    times = torch.tensor([dev_ms, e2e_ms], dtype=torch.float64, device=dev)
+    times = torch.tensor([dev_ms, e2e_ms, e2e_pri_ms], dtype=torch.float64, device=dev)
     if world > 1:
         dist.all_reduce(times, op=dist.ReduceOp.MAX)
-    dev_ms, e2e_ms = float(times[0]), float(times[1])
+    dev_ms, e2e_ms, e2e_pri_ms = float(times[0]), float(times[1]), float(times[2])
     if rank != 0:
         if world > 1:
             dist.destroy_process_group()
@@ -304,6 +318,11 @@ def main() -> int:
                      "hbm_algorithmic_GBps": n_local * (BYTES_IN + BYTES_OUT) / (kern_avg_ms * 1e-3) / 1e9},
         "e2e": {"value": e2e, "unit": "positions/s", "h2d_bytes_per_step": n_local * BYTES_IN,
                 "d2h_bytes_per_step": n_local * BYTES_OUT},
+        "e2e_fused_expansion": {"value": n_global * e2e_steps / (e2e_pri_ms * 1e-3), "unit": "positions/s",
+                                "what": "the same step through forward_priors_host: legality words in, "
+                                        "edge lists (fp16 priors, move labels, counts) and values out",
+                                "h2d_bytes_per_step": n_local * (BYTES_IN + 256),
+                                "d2h_bytes_per_step": n_local * (e_cap * 4 + 8)},
         "gpu_launches": launches, "clocks": clocks,
     }
     if phases is not None:

@@ -1850,6 +1850,61 @@ int bf_forward_host(bf_handle* h, const uint16_t* boards, const int16_t* control
     return BF_OK;
 }
 
+int bf_forward_priors_host(bf_handle* h, const uint16_t* boards, const int16_t* control, const uint8_t* rep,
+                           const uint64_t* legal, int n, int e_cap, void* prior, int16_t* move, int* nedges,
+                           float* value) {
+    if (h == nullptr) return fail(BF_EINVAL, "null handle");
+    if (n < 0) return fail(BF_EINVAL, "n must be >= 0");
+    if (n == 0) return BF_OK;
+    if (boards == nullptr || control == nullptr || rep == nullptr || legal == nullptr)
+        return fail(BF_EINVAL, "boards, control, rep and legal must be non-null");
+    if (prior == nullptr || move == nullptr || nedges == nullptr) return fail(BF_EINVAL, "prior, move and nedges must be non-null");
+    if (e_cap < 1 || e_cap > 255) return fail(BF_EINVAL, "e_cap must be in 1..255");
+    BF_CUDA(cudaSetDevice(h->device));
+    if (n > h->cap_n) {
+        cudaFree(h->d_in); cudaFree(h->d_out);
+        h->d_in = h->d_out = nullptr; h->cap_n = 0;
+        BF_CUDA(cudaMalloc(&h->d_in, static_cast<size_t>(n) * (64 + 2 + 1 + 256) + 1024));
+        BF_CUDA(cudaMalloc(&h->d_out, static_cast<size_t>(n) * (4096 + 256 + 4) + 1024));
+        h->cap_n = n;
+    }
+    const size_t N = static_cast<size_t>(h->cap_n), E = static_cast<size_t>(e_cap);
+    uint8_t* d_legal = h->d_in;
+    uint8_t* d_boards = d_legal + N * 256;
+    uint8_t* d_control = d_boards + N * 64;
+    uint8_t* d_rep = d_control + N * 2;
+    // the output staging (sized for the logits) holds the much smaller edge lists
+    uint8_t* d_nedges = h->d_out;
+    uint8_t* d_value = d_nedges + N * 4;
+    uint8_t* d_prior = d_value + N * 4;
+    uint8_t* d_move = d_prior + N * E * 2;
+    cudaStream_t s = h->stream, c = h->copy_stream;
+    BF_CUDA(cudaMemcpyAsync(d_boards, boards, static_cast<size_t>(n) * 64, cudaMemcpyHostToDevice, s));
+    BF_CUDA(cudaMemcpyAsync(d_control, control, static_cast<size_t>(n) * 2, cudaMemcpyHostToDevice, s));
+    BF_CUDA(cudaMemcpyAsync(d_rep, rep, static_cast<size_t>(n), cudaMemcpyHostToDevice, s));
+    BF_CUDA(cudaMemcpyAsync(d_legal, legal, static_cast<size_t>(n) * 256, cudaMemcpyHostToDevice, s));
+    const int wave = h->sm_count * 4;
+    for (int lo = 0; lo < n; lo += wave) {
+        const int m = n - lo < wave ? n - lo : wave;
+        const size_t o = static_cast<size_t>(lo), M = static_cast<size_t>(m);
+        const PriorOut po{d_prior + o * E * 2, reinterpret_cast<int16_t*>(d_move + o * E * 2),
+                          reinterpret_cast<int*>(d_nedges) + o, e_cap};
+        int rc = launch(h, reinterpret_cast<uint16_t*>(d_boards) + o * 32, reinterpret_cast<int16_t*>(d_control) + o,
+                        d_rep + o, reinterpret_cast<uint64_t*>(d_legal) + o * 32, m, nullptr, nullptr,
+                        reinterpret_cast<float*>(d_value) + o, nullptr, 0, 0, -1, -1, nullptr, nullptr, s, &po);
+        if (rc != BF_OK) return rc;
+        BF_CUDA(cudaEventRecord(h->chunk_done, s));
+        BF_CUDA(cudaStreamWaitEvent(c, h->chunk_done, 0));
+        BF_CUDA(cudaMemcpyAsync(static_cast<uint8_t*>(prior) + o * E * 2, d_prior + o * E * 2, M * E * 2, cudaMemcpyDeviceToHost, c));
+        BF_CUDA(cudaMemcpyAsync(reinterpret_cast<uint8_t*>(move) + o * E * 2, d_move + o * E * 2, M * E * 2, cudaMemcpyDeviceToHost, c));
+        BF_CUDA(cudaMemcpyAsync(nedges + o, d_nedges + o * 4, M * 4, cudaMemcpyDeviceToHost, c));
+        if (value) BF_CUDA(cudaMemcpyAsync(value + o, d_value + o * 4, M * 4, cudaMemcpyDeviceToHost, c));
+    }
+    BF_CUDA(cudaStreamSynchronize(s));
+    BF_CUDA(cudaStreamSynchronize(c));
+    return BF_OK;
+}
+
 int bf_set_option(bf_handle* h, int option, int value) {
     if (h == nullptr) return fail(BF_EINVAL, "null handle");
     if (option == BF_OPT_RSQRT_RN) { h->rsqrt_rn = value != 0; return BF_OK; }

@@ -321,6 +321,28 @@ class FusedEncoder:
             _ptr(promo), _ptr(value)), "bf_forward_host")
         return policy, promo, value
 
+    def forward_priors_host(self, boards, control, rep, legal, prior, move, nedges, value):
+        """``forward_priors`` end to end on HOST tensors (pinned for speed): ``prior [n,E]``
+        fp16, ``move [n,E]`` int16, ``nedges [n]`` int32 and ``value [n]`` fp32 are filled;
+        ``E = prior.shape[1]``."""
+        self._require_net("forward_priors_host")
+        n = self._check_inputs(boards, control, rep)
+        for t in (boards, control, rep, legal, prior, move, nedges, value):
+            if t.is_cuda or not t.is_contiguous():
+                raise ValueError("forward_priors_host takes contiguous CPU tensors")
+        e_cap = int(prior.shape[1])
+        if (tuple(legal.shape) != (n, self.T) or legal.dtype is not torch.int64
+                or tuple(move.shape) != (n, e_cap) or move.dtype is not torch.int16
+                or prior.dtype is not torch.half or tuple(nedges.shape) != (n,)
+                or nedges.dtype is not torch.int32 or tuple(value.shape) != (n,)
+                or value.dtype is not torch.float32):
+            raise ValueError("forward_priors_host: legal [n,32] int64, prior [n,E] fp16, move [n,E] int16, "
+                             "nedges [n] int32, value [n] fp32")
+        _native.check(_native.lib().bf_forward_priors_host(
+            self._handle, _ptr(boards), _ptr(control), _ptr(rep), _ptr(legal), n, e_cap, _ptr(prior),
+            _ptr(move), _ptr(nedges), _ptr(value)), "bf_forward_priors_host")
+        return prior, move, nedges, value
+
     # -- in-kernel phase accounting (the reference's set_profile / read_profile hooks) ----
     def set_profile(self, on: bool) -> None:
         _native.check(_native.lib().bf_profile(self._handle, int(bool(on))), "bf_profile")

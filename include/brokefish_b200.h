@@ -121,6 +121,14 @@ int bf_forward_host(bf_handle* h, const uint16_t* boards, const int16_t* control
                     const uint8_t* rep, const uint64_t* legal, int n, void* policy,
                     void* promo, float* value);
 
+/* bf_forward_priors with HOST buffers, end to end like bf_forward_host: inputs (the legality
+ * words included) go to the device, the evaluator runs wave by wave, and each wave's edge
+ * lists and values come back on a second stream while the next wave computes; about 11 times
+ * fewer bytes return to the host than with the logits (392 B per position at e_cap 96). */
+int bf_forward_priors_host(bf_handle* h, const uint16_t* boards, const int16_t* control, const uint8_t* rep,
+                           const uint64_t* legal, int n, int e_cap, void* prior, int16_t* move, int* nedges,
+                           float* value);
+
 /* Options of a handle; no counterpart in the reference.
  *   BF_OPT_RSQRT_RN  0 (default): the LayerNorms take 1/sqrt from the hardware approximation,
  *                    as the reference kernel's `rsqrtf` does (csrc/encoder.cu:597), so outputs

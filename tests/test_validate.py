@@ -172,3 +172,28 @@ def test_fused_expansion_equals_the_expansion_of_its_own_logits(cap, pos4096):
     with pytest.raises(ValueError):
         enc.forward_priors(boards, control, rep, legal, 0)
     enc.close()
+
+
+@pytest.mark.gpu
+def test_fused_expansion_host_call_matches_the_device_call(pos256):
+    from brokefish_b200.nn import encoder_impl
+    from brokefish_b200.nn.model import BrokefishNet, seeded_state
+    net = BrokefishNet().eval()
+    net.load_state_dict(seeded_state(seed=0, std=0.02))
+    enc = encoder_impl("cuda")(net)
+    n, cap = 253, 96
+    t = lambda a: torch.from_numpy(np.ascontiguousarray(a[:n]))
+    boards, control, rep = t(pos256["boards"]), t(pos256["control"]), t(pos256["rep"])
+    legal = torch.from_numpy(pos256["legal"][:n].view(np.int64).copy())
+    dp, dm, dn, dv = (x.cpu().clone() for x in enc.forward_priors(boards.cuda(), control.cuda(), rep.cuda(),
+                                                                  legal.cuda(), cap))
+    hp = torch.empty(n, cap, dtype=torch.half).pin_memory()
+    hm = torch.empty(n, cap, dtype=torch.int16).pin_memory()
+    hn = torch.empty(n, dtype=torch.int32).pin_memory()
+    hv = torch.empty(n, dtype=torch.float32).pin_memory()
+    for _ in range(2):                                         # twice: staging buffers are reused
+        enc.forward_priors_host(boards, control, rep, legal, hp, hm, hn, hv)
+        assert torch.equal(hp.view(torch.int16), dp.view(torch.int16)) and torch.equal(hm, dm)
+        assert torch.equal(hn, dn) and torch.equal(hv, dv)
+    enc.check_status()
+    enc.close()
