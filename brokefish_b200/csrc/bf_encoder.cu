@@ -303,7 +303,7 @@ __device__ __forceinline__ void store_words(void* dst, const uint32_t* w) {
 // One LayerNorm of the residual stream (TMEM) for this thread's quarter row (columns
 // 32*qt + [0,32) and 128 + 32*qt + [0,32)), in two passes, followed either by the s8
 // quantisation into the A operand (returns the row scale) or, for the final norm, by the
-// affine and the fp16 store into the head GEMM's A operand.
+// affine and the fp16 store into the head product's A operand.
 //
 // Statistics: fp32, one pass, variance clamped at zero, in the reference's own summation
 // order (encoder.cu:566-598; the CPU oracle mirrors it): eight contiguous columns summed one
@@ -481,7 +481,7 @@ __device__ __forceinline__ float ln_stage(RowCtx& c, const Params& p, bool final
             }
         } else {
             // norm_f with affine: fp16(fma(x_hat, gamma, beta)) (encoder.cu:609-611), written as
-            // the fp16 A operand of the head GEMM: 4 K-slabs of [128 rows][64 halves]
+            // the fp16 A operand of the head product: 4 K-slabs of [128 rows][64 halves]
             const uint4* g4 = reinterpret_cast<const uint4*>(p.tail + col);
             const uint4* b4 = reinterpret_cast<const uint4*>(p.tail + kD + col);
 #pragma unroll

@@ -7,7 +7,8 @@ only.
 
 Two arithmetics are built: the reference's ``int8=True`` path (scheme ``"all"``: QKV,
 out-projection and both FFN matmuls in int8, heads and attention in fp16), which is the
-default here, and its ``fp8=True`` path (the two FFN matmuls in e4m3 with ``amax/8`` scales,
+default here and whose outputs equal the reference kernel's bit for bit, and its
+``fp8=True`` path (the two FFN matmuls in e4m3 with ``amax/8`` scales,
 QKV and out-projection in fp16).  The plain fp16 arithmetic and the partial int8 schemes
 are not built: asking for them raises ``NotImplementedError`` instead of silently running
 something else.
@@ -64,8 +65,9 @@ class FusedEncoder:
             raise ValueError(f"acc_dtype must be one of {self.ACC_DTYPES}, got {acc_dtype!r}")
         if acc_dtype == "fp32":
             raise NotImplementedError(
-                "acc_dtype='fp32' is not a mode of this kernel: the weight GEMMs accumulate "
-                "exactly in s32 and attention / heads already accumulate in fp32")
+                "acc_dtype='fp32' is not built: the weight GEMMs accumulate exactly in s32, and "
+                "the attention and head products keep the fp16 accumulators of the reference's "
+                "shipped kernel so that outputs equal that kernel's bit for bit")
         self.acc_dtype = acc_dtype
         self.n_layers = len(layers)
         self.d_model = first.self_attn.embed_dim
