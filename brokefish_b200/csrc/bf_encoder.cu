@@ -246,8 +246,10 @@ __device__ __forceinline__ uint32_t sw_off(int row, int chunk) {
 // `(float(acc) * sa) * sw` -> fp16, + fp16 bias, optional ReLU; kN columns -> kN/2 pairs
 // (int8_gemm.cuh:276-297, encoder.cu:631-644, 1482-1489).
 // kAcc says what the accumulator holds: kAccInt = s32 with the two scales, kAccFloat = fp32
-// with the two scales (e4m3 GEMMs; csrc/fp8_gemm.cuh:288-310), kAccPlain = fp32 of an fp16 GEMM,
-// no scales (the reference's un-quantised QKV / out-projection).
+// with the two scales (e4m3 GEMMs; csrc/fp8_gemm.cuh:288-310), kAccPlain = the fp16 accumulator
+// of an fp16 GEMM, one value in the low half of each word, no scales (the reference's
+// un-quantised QKV / out-projection, whose mma.sync accumulates in fp16; tcgen05 kind::f16 with
+// fp16 accumulators gives the same bits).
 enum { kAccInt = 0, kAccFloat = 1, kAccPlain = 2 };
 template <int kN, bool kRelu, int kAcc = kAccInt>
 __device__ __forceinline__ void descale(const uint32_t* acc, float sa, float sw, const __half* bias,
@@ -264,13 +266,18 @@ __device__ __forceinline__ void descale(const uint32_t* acc, float sa, float sw,
             // exact s32 -> f32 on the conversion unit (otherwise idle here; the integer-add
             // form measured 6 % slower because it loads the FMA pipe, which is the busy one),
             // then the two fp32 multiplies, both lanes at once
+            if (kAcc == kAccPlain) {
+                const uint32_t h = __byte_perm(acc[2 * i], acc[2 * i + 1], 0x5410);
+                out[i] = as_u32(__hadd2(as_h2(h), as_h2(bw[k])));
+                continue;
+            }
             uint64_t f;
             if (kAcc == kAccInt)
                 f = pk2(static_cast<float>(static_cast<int>(acc[2 * i])),
                         static_cast<float>(static_cast<int>(acc[2 * i + 1])));
             else
                 f = pk2(__uint_as_float(acc[2 * i]), __uint_as_float(acc[2 * i + 1]));
-            if (kAcc != kAccPlain) f = mul2(mul2(f, sa2), sw2);
+            f = mul2(mul2(f, sa2), sw2);
             if (kRelu) {
                 // relu(x + b) in one instruction: x * 1 is exact, so the sum is rounded once
                 // exactly as the fp16 add is, and the clamp is part of the same operation
@@ -1343,11 +1350,12 @@ __device__ __forceinline__ void mma_loop(uint32_t smem, uint32_t tmem, volatile 
                                       const Params& p, int first_tile, int tile_step, int n_tiles) {
     using C = Cfg<kFP8>;
     MmaState st = {0, 0, {0, 0}, 0, {0, 0}};
-    // int8: every weight GEMM is s8/u8 x s8.  e4m3: QKV and out-projection are fp16 x fp16,
-    // the FFN is e4m3 x e4m3; both accumulate in fp32.
-    constexpr uint32_t kI_QKV = kFP8 ? umma_idesc(kAccF32, kFmtF16, kFmtF16, 128, 192)
+    // int8: every weight GEMM is s8/u8 x s8.  e4m3: QKV and out-projection are fp16 x fp16 with
+    // fp16 accumulators (the bits of the reference's mma.sync), the FFN is e4m3 x e4m3 with fp32
+    // accumulators (the reference's fp16-accumulate e4m3 mma.sync has no bit-equal on tcgen05).
+    constexpr uint32_t kI_QKV = kFP8 ? umma_idesc(kAccF16, kFmtF16, kFmtF16, 128, 192)
                                      : umma_idesc(kAccS32, kFmtS8, kFmtS8, 128, 192);
-    constexpr uint32_t kI_OUT = kFP8 ? umma_idesc(kAccF32, kFmtF16, kFmtF16, 128, 128)
+    constexpr uint32_t kI_OUT = kFP8 ? umma_idesc(kAccF16, kFmtF16, kFmtF16, 128, 128)
                                      : umma_idesc(kAccS32, kFmtS8, kFmtS8, 128, 128);
     constexpr uint32_t kI_FF1 = kFP8 ? umma_idesc(kAccF32, kFmtE4M3, kFmtE4M3, 128, 128)
                                      : umma_idesc(kAccS32, kFmtS8, kFmtS8, 128, 128);

@@ -212,7 +212,7 @@ __device__ __forceinline__ uint64_t umma_desc_k128(uint32_t saddr) {
 // Instruction descriptor fields: D format [4,6), A format [7,10), B format [10,13),
 // N>>3 [17,23), M>>4 [24,29); A and B both K-major, dense, no negate.
 constexpr uint32_t kFmtU8 = 0, kFmtS8 = 1, kFmtF16 = 0, kFmtE4M3 = 0;
-constexpr uint32_t kAccF32 = 1, kAccS32 = 2;
+constexpr uint32_t kAccF16 = 0, kAccF32 = 1, kAccS32 = 2;
 __host__ __device__ constexpr uint32_t umma_idesc(uint32_t acc, uint32_t afmt, uint32_t bfmt,
                                                   uint32_t m, uint32_t n) {
     return (acc << 4) | (afmt << 7) | (bfmt << 10) | ((n >> 3) << 17) | ((m >> 4) << 24);

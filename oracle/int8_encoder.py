@@ -377,8 +377,8 @@ def forward(w: Weights, boards, control, rep, legal=None, trace: Optional[Trace]
         if first:
             trace.stages[1] = xn.reshape(n, T, D).copy()
         e4 = w.fmt == "e4m3"
-        if e4:       # fp16 QKV, fp32 accumulate (the reference accumulates in fp16)
-            qkv = add_f16((xn.astype(F32) @ lw.q_qkv.astype(F32).T).astype(F16), lw.b_qkv[None, :])
+        if e4:       # fp16 QKV with fp16 accumulators, 16 steps of 16 (csrc/encoder.cu:1366-1368)
+            qkv = add_f16(_mma_f16acc(xn, lw.q_qkv.astype(F16).T), lw.b_qkv[None, :])
         else:
             qa, sa = quantise_rows(xn)
             acc = gemm_int(qa, lw.q_qkv)
@@ -391,7 +391,7 @@ def forward(w: Weights, boards, control, rep, legal=None, trace: Optional[Trace]
         if first:
             trace.stages[4] = o.copy()
         if e4:
-            y = add_f16((o.reshape(n * T, D).astype(F32) @ lw.q_o.astype(F32).T).astype(F16), lw.b_o[None, :])
+            y = add_f16(_mma_f16acc(o.reshape(n * T, D), lw.q_o.astype(F16).T), lw.b_o[None, :])
         else:
             qa, sa = quantise_rows(o.reshape(n * T, D))
             acc = gemm_int(qa, lw.q_o)

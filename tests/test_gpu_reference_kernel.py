@@ -164,16 +164,27 @@ def test_prenorm_wdl_value_against_reference_kernel(pos256):
 
 
 def test_e4m3_path_against_reference_kernel(pos256):
+    """The e4m3-FFN arithmetic.  Its fp16 GEMMs (QKV, out-projection) run on tcgen05 with fp16
+    accumulators, which carry the bits of the reference's fp16-accumulate mma.sync, so layer 0 is
+    bit-identical up to the FFN input: LN1, Q, K, V, attention output, residual, LN2.  The FFN
+    itself accumulates e4m3 products in fp32 where the reference accumulates in fp16 (no tcgen05
+    form reproduces that instruction's roundings), so the outputs are a tolerance: 10 % of
+    max|logit| (measured about 6 %)."""
     if not R.available("A_e4m3"):
         pytest.skip("slabs missing")
     enc, ref = product(SETS["A"], fp8=True), R.RefKernel("A_e4m3")
     assert ref.quant == 1
     sl = slice(0, 128)
+    for stage in (9, 1, 5, 6, 7, 4, 2, 3):
+        got = enc.forward_stage(*inputs(pos256, sl), stage).cpu().numpy()
+        want = ref.forward_stage(*inputs(pos256, sl), stage).cpu().numpy()
+        assert same_bits(got, want), stage
     (pol, pro, val), (rpol, rpro, rval) = run_both(enc, ref, pos256, sl)
-    # two e4m3 implementations with different accumulator widths (measured 6.3 % of
-    # max|logit| on 2048 positions)
     tol = rel_tol(rpol, 10e-2)
-    assert np.abs(pol.astype(np.float32) - rpol.astype(np.float32)).max() <= tol
+    d = np.abs(pol.astype(np.float32) - rpol.astype(np.float32)).max()
+    print(f"e4m3 arm vs reference e4m3 kernel: max|dlogit| {d:.4f} of max|logit| "
+          f"{np.abs(rpol.astype(np.float32)).max():.3f}, value {np.abs(val - rval).max():.4f}")
+    assert d <= tol
     assert np.abs(val - rval).max() <= 8e-2
     enc.close()
 
