@@ -141,7 +141,8 @@ struct RowCtx {
 // csrc/encoder.cu:1110-1177): one thread per CTA charges the cycles since its previous mark to
 // a phase.  Off (one predictable branch per mark) unless the launch carries a counter buffer.
 enum { PH_EMBED = 0, PH_LN, PH_WAIT_MMA, PH_QKV_EPI, PH_PAIR_BAR, PH_ATTENTION, PH_O_READBACK, PH_O_QUANT,
-       PH_OUT_EPI, PH_FF1_EPI, PH_FF2_EPI, PH_HEAD, PH_WAIT_OUT, PH_WAIT_FF1, PH_WAIT_FF2, PH_COUNT };
+       PH_OUT_EPI, PH_FF1_EPI, PH_FF2_EPI, PH_HEAD, PH_WAIT_OUT, PH_WAIT_FF1, PH_WAIT_FF2, PH_WAIT_FF1_FIRST,
+       PH_COUNT };
 template <bool kDbg>
 __device__ __forceinline__ void prof_mark(RowCtx& c, int phase) {
     if (kDbg && c.prof_on) {
@@ -731,7 +732,7 @@ __device__ __forceinline__ void ffn_block(RowCtx& c, const Params& p, const Laye
                 const uint32_t t0 = c.tm + TM_ACC + 32 * c.qt;
                 const float sw0 = __ldg(lp.sw_ff1 + 2 * ch), sw1 = __ldg(lp.sw_ff1 + 2 * ch + 1);
                 uint32_t pa[16], pb[16];
-                row_wait_acc<kDbg>(c, 0, PH_FF1_EPI, PH_WAIT_FF1);
+                row_wait_acc<kDbg>(c, 0, PH_FF1_EPI, ch == 0 ? PH_WAIT_FF1_FIRST : PH_WAIT_FF1);
                 tmem_ld16(t0, pa);
                 tmem_wait_ld();
                 tmem_ld16(t0 + 16, pb);
@@ -1955,9 +1956,9 @@ int bf_profile_read(bf_handle* h, long long* cycles, int n) {
 }
 
 const char* bf_profile_phases(void) {
-    return "embed,layernorm_quantise,wait_mma_qkv_heads,qkv_epilogue,pair_barrier,attention,attn_readback,"
+    return "embed,layernorm_quantise,wait_mma_qkv,qkv_epilogue,pair_barrier,attention,attn_readback,"
            "attn_quantise,out_proj_epilogue,ff1_epilogue,ff2_epilogue,heads,wait_mma_out,wait_mma_ff1,"
-           "wait_mma_ff2";
+           "wait_mma_ff2,wait_mma_ff1_first";
 }
 
 int bf_measure_i8_peak(int device, int iters, double* tops, double* ms) {
