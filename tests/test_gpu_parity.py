@@ -149,6 +149,25 @@ def test_embedding_is_bit_exact(name, encoders, oracle_weights, pos256):
     enc.check_status()
 
 
+def test_embedding_over_every_clock_sign_and_repetition(encoders, oracle_weights, nets, pos256):
+    """Every half-move-clock row (1..101, and the clamp beyond), both signs of the control word
+    and every repetition value including the clamp (the reference's tests/test_b2.py:110-133),
+    bit-exact against the oracle and against the torch module in fp16."""
+    enc = encoders["B"]
+    clocks = np.arange(1, 111)
+    control = np.concatenate([clocks, -clocks]).astype(np.int16)
+    grid_c = np.repeat(control, 5)
+    grid_r = np.tile(np.arange(5, dtype=np.uint8), len(control))
+    boards = np.tile(pos256["boards"][7][None, :], (len(grid_c), 1))
+    got = enc.forward_stage(dev(boards), dev(grid_c), dev(grid_r), 9).cpu().numpy()
+    want, _ = O.embed(oracle_weights["B"], boards, grid_c, grid_r)
+    assert np.array_equal(got.view(np.uint16), want.view(np.uint16))
+    half = __import__("copy").deepcopy(nets["B"]).half()
+    with torch.no_grad():
+        x, _ = half.embed(torch.from_numpy(boards), torch.from_numpy(grid_c), torch.from_numpy(grid_r))
+    assert np.array_equal(got.view(np.uint16), x.numpy().view(np.uint16))
+
+
 @pytest.mark.parametrize("name", ["A", "B"])
 def test_layer0_stages(name, encoders, oracle_weights, pos256):
     """LN1, Q/K/V and LN2-side stages of layer 0.  LN1 and Q/K/V are reproducible exactly;
@@ -316,6 +335,32 @@ def test_full_size_batch_properties(encoders, oracle_weights, pos4096):
     ok = theirs >= 0
     assert (mine[ok] == theirs[ok]).mean() >= ARGMAX_MIN["A"]
     assert_disagreements_are_near_ties(opol, legal, mine, theirs, LOGIT_TOL)
+
+
+def test_largest_configured_batch_is_a_tiling_of_the_4096_batch(encoders_hw, pos4096):
+    """131,072 positions in one launch (the largest step size of the configurations; the 4096
+    fixture tiled 32 times, shifted by 5 positions so that copies straddle tiles differently):
+    every copy's outputs equal the 4096-position launch's bit for bit — an evaluation does not
+    depend on its index in the batch, on what shares its tile, or on the batch size."""
+    enc = encoders_hw["A"]
+    base = [t.clone() for t in enc.forward_full(*inputs(pos4096, slice(0, 4096)))]
+    reps, shift = 32, 5
+    big = []
+    for key in ("boards", "control", "rep"):
+        a = np.roll(pos4096[key], shift, axis=0)
+        big.append(dev(np.concatenate([a] * reps, axis=0)))
+    pol, pro, val = enc.forward_full(*big)
+    enc.check_status()
+    assert pol.shape[0] == 131072
+    want = [torch.roll(t, shift, dims=0) for t in base]
+    for k in (0, 1, 17, 31):
+        lo = 4096 * k
+        assert torch.equal(pol[lo:lo + 4096].view(torch.int16), want[0].view(torch.int16))
+        assert torch.equal(pro[lo:lo + 4096].view(torch.int16), want[1].view(torch.int16))
+        assert torch.equal(val[lo:lo + 4096].view(torch.int32), want[2].view(torch.int32))
+    # a checksum over all copies: the remaining 28 agree with the first as well
+    folded = pol.view(torch.int16).to(torch.int32).reshape(reps, -1)
+    assert bool((folded == folded[0]).all())
 
 
 def test_end_to_end_host_call_matches_device_call(encoders, pos256):
