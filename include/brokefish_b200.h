@@ -124,7 +124,8 @@ int bf_forward_host(bf_handle* h, const uint16_t* boards, const int16_t* control
 /* bf_forward_priors with HOST buffers, end to end like bf_forward_host: inputs (the legality
  * words included) go to the device, the evaluator runs wave by wave, and each wave's edge
  * lists and values come back on a second stream while the next wave computes; about 11 times
- * fewer bytes return to the host than with the logits (392 B per position at e_cap 96). */
+ * fewer bytes return to the host than with the logits (392 B per position at e_cap 96).  When
+ * the outputs are pinned, device-mapped host memory the kernel writes them there directly. */
 int bf_forward_priors_host(bf_handle* h, const uint16_t* boards, const int16_t* control, const uint8_t* rep,
                            const uint64_t* legal, int n, int e_cap, void* prior, int16_t* move, int* nedges,
                            float* value);

@@ -363,15 +363,19 @@ def test_largest_configured_batch_is_a_tiling_of_the_4096_batch(encoders_hw, pos
     assert bool((folded == folded[0]).all())
 
 
-def test_end_to_end_host_call_matches_device_call(encoders, pos256):
+@pytest.mark.parametrize("pinned", [True, False])
+def test_end_to_end_host_call_matches_device_call(pinned, encoders, pos4096):
+    """Pinned and pageable host buffers; more positions than one wave (592 on a 148-SM part) and
+    not a multiple of it, so that several wave-sized launches and their overlapped copies run."""
     enc = encoders["A"]
-    n = 200
-    b = torch.from_numpy(pos256["boards"][:n].copy()).pin_memory()
-    c = torch.from_numpy(pos256["control"][:n].copy()).pin_memory()
-    r = torch.from_numpy(pos256["rep"][:n].copy()).pin_memory()
-    pol = torch.empty(n, 32, 64, dtype=torch.half).pin_memory()
-    pro = torch.empty(n, 32, 4, dtype=torch.half).pin_memory()
-    val = torch.empty(n, dtype=torch.float).pin_memory()
+    n = 1500
+    pin = (lambda t: t.pin_memory()) if pinned else (lambda t: t)
+    b = pin(torch.from_numpy(pos4096["boards"][:n].copy()))
+    c = pin(torch.from_numpy(pos4096["control"][:n].copy()))
+    r = pin(torch.from_numpy(pos4096["rep"][:n].copy()))
+    pol = pin(torch.zeros(n, 32, 64, dtype=torch.half))
+    pro = pin(torch.zeros(n, 32, 4, dtype=torch.half))
+    val = pin(torch.zeros(n, dtype=torch.float))
     enc.forward_host(b, c, r, pol, pro, val)
     dpol, dpro, dval = (t.cpu() for t in enc.forward_full(b.cuda(), c.cuda(), r.cuda()))
     assert torch.equal(pol.view(torch.int16), dpol.view(torch.int16))

@@ -175,7 +175,10 @@ def test_fused_expansion_equals_the_expansion_of_its_own_logits(cap, pos4096):
 
 
 @pytest.mark.gpu
-def test_fused_expansion_host_call_matches_the_device_call(pos256):
+@pytest.mark.parametrize("pinned", [True, False])
+def test_fused_expansion_host_call_matches_the_device_call(pinned, pos256):
+    """Pinned outputs are written by the kernel straight into host memory; pageable ones go
+    through the staged path (wave-sized launches, copies on a second stream)."""
     from brokefish_b200.nn import encoder_impl
     from brokefish_b200.nn.model import BrokefishNet, seeded_state
     net = BrokefishNet().eval()
@@ -187,10 +190,11 @@ def test_fused_expansion_host_call_matches_the_device_call(pos256):
     legal = torch.from_numpy(pos256["legal"][:n].view(np.int64).copy())
     dp, dm, dn, dv = (x.cpu().clone() for x in enc.forward_priors(boards.cuda(), control.cuda(), rep.cuda(),
                                                                   legal.cuda(), cap))
-    hp = torch.empty(n, cap, dtype=torch.half).pin_memory()
-    hm = torch.empty(n, cap, dtype=torch.int16).pin_memory()
-    hn = torch.empty(n, dtype=torch.int32).pin_memory()
-    hv = torch.empty(n, dtype=torch.float32).pin_memory()
+    pin = (lambda t: t.pin_memory()) if pinned else (lambda t: t)
+    hp = pin(torch.zeros(n, cap, dtype=torch.half))
+    hm = pin(torch.zeros(n, cap, dtype=torch.int16))
+    hn = pin(torch.zeros(n, dtype=torch.int32))
+    hv = pin(torch.zeros(n, dtype=torch.float32))
     for _ in range(2):                                         # twice: staging buffers are reused
         enc.forward_priors_host(boards, control, rep, legal, hp, hm, hn, hv)
         assert torch.equal(hp.view(torch.int16), dp.view(torch.int16)) and torch.equal(hm, dm)
