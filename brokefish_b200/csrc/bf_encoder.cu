@@ -1502,6 +1502,39 @@ __global__ void __launch_bounds__(128, 1) i8_peak_kernel(int iters, int* status)
 }
 
 // ------------------------------------------------------------------------------------------
+// Time-out self test: one thread waits on an mbarrier that nothing ever arrives on, through the
+// same bounded wait every role of the evaluator uses.  The wait gives up after its cycle limit,
+// the abort flag carries the code, the kernel returns normally and the host reads the status:
+// the path a lost arrival takes in the real kernel, exercised without faulting anything.
+// ------------------------------------------------------------------------------------------
+__global__ void __launch_bounds__(64, 1) timeout_kernel(int code, int* status, long long* waited) {
+    __shared__ __align__(8) unsigned long long bar;
+    __shared__ int abort_flag;
+    const uint32_t b = smem_u32(&bar);
+    if (threadIdx.x == 0) {
+        mbar_init(b, 1);
+        abort_flag = 0;
+        fence_barrier_init();
+    }
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        const long long t0 = clock64();
+        const bool ok = mbar_wait(b, 0, &abort_flag, code);
+        *waited = clock64() - t0;
+        if (ok) atomicCAS(status, 0, -1);          // cannot happen: nothing arrives
+    }
+    // a second waiter sees the flag and returns at once instead of waiting its own limit out
+    __syncthreads();
+    if (threadIdx.x == 32) {
+        const long long t0 = clock64();
+        mbar_wait(b, 0, &abort_flag, code + 100);
+        waited[1] = clock64() - t0;
+    }
+    __syncthreads();
+    if (threadIdx.x == 0 && abort_flag != 0) atomicCAS(status, 0, abort_flag);
+}
+
+// ------------------------------------------------------------------------------------------
 // Tensor-core self test: one tile, one GEMM, no network.
 // ------------------------------------------------------------------------------------------
 __global__ void __launch_bounds__(128, 1) selftest_kernel(int mode, const uint8_t* a, const uint8_t* w,
@@ -2022,6 +2055,29 @@ int bf_measure_i8_peak(int device, int iters, double* tops, double* ms) {
     const double ops = 2.0 * 128 * 256 * 32 * 4.0 * iters * prop.multiProcessorCount;
     *tops = ops / (best * 1e-3) / 1e12;
     if (ms != nullptr) *ms = best;
+    return BF_OK;
+}
+
+int bf_selftest_timeout(int device, int code, int* status, long long* waited_cycles) {
+    if (status == nullptr || code < 1 || code > 99) return fail(BF_EINVAL, "status is null or code not in 1..99");
+    BF_CUDA(cudaSetDevice(device));
+    int* d_status = nullptr;
+    long long* d_waited = nullptr;
+    BF_CUDA(cudaMalloc(&d_status, sizeof(int)));
+    cudaError_t e = cudaMalloc(&d_waited, 2 * sizeof(long long));
+    if (e == cudaSuccess) e = cudaMemset(d_status, 0, sizeof(int));
+    if (e == cudaSuccess) e = cudaMemset(d_waited, 0, 2 * sizeof(long long));
+    if (e == cudaSuccess) {
+        bf::timeout_kernel<<<1, 64>>>(code, d_status, d_waited);
+        e = cudaDeviceSynchronize();
+    }
+    long long w[2] = {0, 0};
+    if (e == cudaSuccess) e = cudaMemcpy(status, d_status, sizeof(int), cudaMemcpyDeviceToHost);
+    if (e == cudaSuccess) e = cudaMemcpy(w, d_waited, sizeof(w), cudaMemcpyDeviceToHost);
+    cudaFree(d_status);
+    cudaFree(d_waited);
+    if (e != cudaSuccess) return fail(BF_ECUDA, cudaGetErrorString(e));
+    if (waited_cycles != nullptr) { waited_cycles[0] = w[0]; waited_cycles[1] = w[1]; }
     return BF_OK;
 }
 

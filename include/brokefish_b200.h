@@ -194,6 +194,14 @@ int bf_noalloc_status(int device, int* status);
  * (csrc/fp8_loop.cu; docs/ledger/perf.md:616-647), for the roofline's denominator. */
 int bf_measure_i8_peak(int device, int iters, double* tops, double* ms);
 
+/* Time-out self test; no counterpart in the reference.  A small kernel waits, through the same
+ * bounded wait the evaluator's roles use, on an mbarrier that nothing arrives on.  The wait runs
+ * out after its cycle limit (about 0.2 s), the kernel returns normally and `*status` receives
+ * `code` (1..99), which is how a lost arrival would surface from the evaluator through
+ * bf_status().  `waited_cycles` (may be NULL): [0] cycles the first waiter spent, [1] cycles a
+ * second waiter spent after the flag was set (it returns at once).  Nothing faults or hangs. */
+int bf_selftest_timeout(int device, int code, int* status, long long* waited_cycles);
+
 /* Tensor-core self test (no network): one 128-row tile times a packed weight tile.
  *   mode 0: s8 x s8, N=128, K=256     mode 1: u8 x s8, N=128, K=256
  *   mode 2: s8 x s8, N=192, K=256     mode 3: f16 x f16 -> f32, N=96, K=256

@@ -554,3 +554,20 @@ def test_int8_peak_probe_runs_and_is_plausible():
     assert rc == 0, _native.lib().bf_last_error()
     assert 2000.0 < tops.value < 5500.0, (tops.value, ms.value)
     assert _native.lib().bf_measure_i8_peak(0, 1, ctypes.byref(tops), None) != 0     # iters out of range
+
+
+def test_a_wait_that_nothing_satisfies_times_out_and_reports():
+    """Failure detection without a fault: the bounded wait gives up after its limit, the kernel
+    returns, the status word carries the code, a later waiter returns at once, and the device
+    keeps working afterwards."""
+    from brokefish_b200 import _native
+    L = _native.lib()
+    status = ctypes.c_int(0)
+    waited = (ctypes.c_longlong * 2)()
+    assert L.bf_selftest_timeout(0, 7, ctypes.byref(status), waited) == 0, L.bf_last_error()
+    assert status.value == 7
+    assert waited[0] >= 400_000_000 and waited[0] < 4_000_000_000      # the limit, not forever
+    assert waited[1] < 10_000_000                                      # the second waiter saw the flag
+    assert L.bf_selftest_timeout(0, 0, ctypes.byref(status), None) != 0
+    x = torch.ones(8, device="cuda")
+    assert float(x.sum()) == 8.0
