@@ -1653,6 +1653,18 @@ struct bf_handle {
 
 namespace {
 
+// Device staging of the host-buffer calls: inputs (boards, control, rep, legality words) and
+// outputs (sized for the logits, the largest output set), grown to the largest n seen.
+int ensure_staging(bf_handle* h, int n) {
+    if (n <= h->cap_n) return BF_OK;
+    cudaFree(h->d_in); cudaFree(h->d_out);
+    h->d_in = h->d_out = nullptr; h->cap_n = 0;
+    BF_CUDA(cudaMalloc(&h->d_in, static_cast<size_t>(n) * (64 + 2 + 1 + 256) + 1024));
+    BF_CUDA(cudaMalloc(&h->d_out, static_cast<size_t>(n) * (4096 + 256 + 4) + 1024));
+    h->cap_n = n;
+    return BF_OK;
+}
+
 // The device-side alias of a pinned, mapped host allocation, or null for any other pointer.
 void* mapped_host(const void* p) {
     if (p == nullptr) return nullptr;
@@ -1856,13 +1868,7 @@ int bf_forward_host(bf_handle* h, const uint16_t* boards, const int16_t* control
     if (boards == nullptr || control == nullptr || rep == nullptr)
         return fail(BF_EINVAL, "boards, control and rep must be non-null");
     BF_CUDA(cudaSetDevice(h->device));
-    if (n > h->cap_n) {
-        cudaFree(h->d_in); cudaFree(h->d_out);
-        h->d_in = h->d_out = nullptr; h->cap_n = 0;
-        BF_CUDA(cudaMalloc(&h->d_in, static_cast<size_t>(n) * (64 + 2 + 1 + 256) + 1024));
-        BF_CUDA(cudaMalloc(&h->d_out, static_cast<size_t>(n) * (4096 + 256 + 4) + 1024));
-        h->cap_n = n;
-    }
+    { const int rc = ensure_staging(h, n); if (rc != BF_OK) return rc; }
     const size_t N = static_cast<size_t>(h->cap_n);
     uint8_t* d_legal = h->d_in;                         // 8-byte aligned first
     uint8_t* d_boards = d_legal + N * 256;
@@ -1913,13 +1919,7 @@ int bf_forward_priors_host(bf_handle* h, const uint16_t* boards, const int16_t* 
     if (prior == nullptr || move == nullptr || nedges == nullptr) return fail(BF_EINVAL, "prior, move and nedges must be non-null");
     if (e_cap < 1 || e_cap > 255) return fail(BF_EINVAL, "e_cap must be in 1..255");
     BF_CUDA(cudaSetDevice(h->device));
-    if (n > h->cap_n) {
-        cudaFree(h->d_in); cudaFree(h->d_out);
-        h->d_in = h->d_out = nullptr; h->cap_n = 0;
-        BF_CUDA(cudaMalloc(&h->d_in, static_cast<size_t>(n) * (64 + 2 + 1 + 256) + 1024));
-        BF_CUDA(cudaMalloc(&h->d_out, static_cast<size_t>(n) * (4096 + 256 + 4) + 1024));
-        h->cap_n = n;
-    }
+    { const int rc = ensure_staging(h, n); if (rc != BF_OK) return rc; }
     const size_t N = static_cast<size_t>(h->cap_n), E = static_cast<size_t>(e_cap);
     uint8_t* d_legal = h->d_in;
     uint8_t* d_boards = d_legal + N * 256;
