@@ -49,19 +49,26 @@ constexpr int EMB_SQUARE = 0, EMB_TS = 64, EMB_CT = 76, EMB_CLOCK = 80, EMB_REP 
 constexpr int kNClock = 101, kNRep = 3, kNTypeSpecial = 12;
 
 // ---- shared memory map (offsets from a 1024-byte aligned base) ----------------------
+// Arithmetic of a kernel arm: which formats the weight GEMMs run in.
+//   kArInt8  every weight GEMM s8/u8 x s8 -> s32 (the reference's int8 "all" scheme)
+//   kArE4M3  FFN e4m3 x e4m3, QKV and out-projection fp16 x fp16 (the reference's fp8 path)
+//   kArF16   every weight GEMM fp16 x fp16 with fp16 accumulators (the reference's default path)
+enum { kArInt8 = 0, kArE4M3 = 1, kArF16 = 2 };
 // The front of the map depends on the arithmetic.  int8: the A operand is 32 KB of bytes and
-// the weight ring has 112 KB.  e4m3-FFN: QKV and out-projection run in fp16, so the A operand
-// is 64 KB (4 K-slabs of 64 halves) and the ring gives up two slots.
-template <bool kFP8>
+// the weight ring has 112 KB.  With fp16 attention GEMMs (e4m3, fp16 arms) the A operand is 64 KB
+// (4 K-slabs of 64 halves) and the ring gives up two slots.
+template <int kAr>
 struct Cfg {
+    static constexpr bool kHalfA = kAr != kArInt8;           // fp16 A operand for QKV / out-proj
     static constexpr uint32_t SM_A = 0;     // A operand: K-slabs of [128 rows][128 B]
-    static constexpr uint32_t SM_R = kFP8 ? 65536 : 32768;   // 64 KB: Q/K/V staging (3 x 16 KB) |
-                                            // hidden operand x2 (2 x 32 KB) | fp16 head A (4 x 16 KB)
+    static constexpr uint32_t SM_R = kHalfA ? 65536 : 32768; // 64 KB: Q/K/V staging (3 x 16 KB) |
+                                            // hidden operand(s) | fp16 head A (4 x 16 KB)
     static constexpr uint32_t SM_RING = SM_R + 65536;        // weight ring up to SM_XCH
-    static constexpr int kQSlots = kFP8 ? 3 : 4;             // 24 KB QKV stages
-    static constexpr int kRSlots = kFP8 ? 5 : 7;             // 16 KB stages
-    static constexpr int kAttnSlabs = kFP8 ? 4 : 2;          // K-slabs of a QKV / out-proj unit
-    static constexpr int kLayerStream = kFP8 ? 1048576 : 786432;
+    static constexpr int kQSlots = kHalfA ? 3 : 4;           // 24 KB QKV stages
+    static constexpr int kRSlots = kHalfA ? 5 : 7;           // 16 KB stages
+    static constexpr int kAttnSlabs = kHalfA ? 4 : 2;        // K-slabs of a QKV / out-proj unit
+    static constexpr int kFfnSlabs = kAr == kArF16 ? 4 : 2;  // K-slabs of an FFN unit
+    static constexpr int kLayerStream = kAr == kArF16 ? 1572864 : (kAr == kArE4M3 ? 1048576 : 786432);
 };
 constexpr uint32_t SM_XCH = 212992;     // 16 KB: float4 [2 parity][4 quarter][128 rows]
 constexpr uint32_t SM_BAR = 229376;     // mbarriers
@@ -269,7 +276,7 @@ __device__ __forceinline__ void descale(const uint32_t* acc, float sa, float sw,
             // then the two fp32 multiplies, both lanes at once
             if (kAcc == kAccPlain) {
                 const uint32_t h = __byte_perm(acc[2 * i], acc[2 * i + 1], 0x5410);
-                out[i] = as_u32(__hadd2(as_h2(h), as_h2(bw[k])));
+                out[i] = kRelu ? hfma2_relu(h, 0x3C003C00u, bw[k]) : as_u32(__hadd2(as_h2(h), as_h2(bw[k])));
                 continue;
             }
             uint64_t f;
@@ -361,12 +368,13 @@ __device__ __forceinline__ void reinject32(const RowCtx& c, const Params& p, int
 }
 
 //
-// In the e4m3 arithmetic (kFP8) the attention norm is not quantised at all: x_hat goes out as
-// the fp16 A operand of the fp16 QKV GEMM (`f16_out`); the FFN norm is quantised to e4m3 with
-// scale amax/8 (csrc/fp8_gemm.cuh:147-208).
-template <bool kDbg, bool kRJ, bool kFP8>
+// In the e4m3 arithmetic the attention norm is not quantised at all: x_hat goes out as the fp16
+// A operand of the fp16 QKV GEMM (`f16_out`); the FFN norm is quantised to e4m3 with scale
+// amax/8 (csrc/fp8_gemm.cuh:147-208).  In the fp16 arithmetic both norms go out as fp16.
+template <bool kDbg, bool kRJ, int kAr>
 __device__ __forceinline__ float ln_stage(RowCtx& c, const Params& p, bool final_norm, bool dump_x,
                                           bool dump_xn, bool capture, int site, bool f16_out = false) {
+    constexpr bool kFP8 = kAr == kArE4M3, kHalfA = kAr != kArInt8;
     // Partial sums in the reference's order (encoder.cu:566-583): "lane" l of the reference
     // owns columns 8l..8l+7 and adds them one after the other, then lanes combine by the
     // butterfly 16, 8, 4, 2, 1.  This thread's 64 columns are lanes 4qt..4qt+3 and their
@@ -472,7 +480,7 @@ __device__ __forceinline__ float ln_stage(RowCtx& c, const Params& p, bool final
         if (!final_norm) {
 #pragma unroll
             for (int i = 0; i < 16; ++i) x[i] = f2_to_h2(mul2(add2(h2_to_f2(x[i]), nmean2), rstd2));
-            if (kFP8 && f16_out) {
+            if (kHalfA && f16_out) {
                 // fp16 A operand: 4 K-slabs of [128 rows][64 halves]; this thread's 32 columns
                 // are half of slab col / 64
 #pragma unroll
@@ -602,9 +610,10 @@ struct LayerParams {
 // QKV in four head-pair chunks with attention per chunk, then the attention output is
 // quantised into A, then out-projection + residual into the residual stream (TMEM).
 // `sa` is the scale of the row in A on entry.
-template <bool kDbg, bool kFP8>
+template <bool kDbg, int kAr>
 __device__ __forceinline__ void attention_block(RowCtx& c, const Params& p, const LayerParams& lp,
                                                 float sa, uint32_t alive, bool cap, bool dbgl) {
+    constexpr bool kHalfA = kAr != kArInt8;
     const int dbg = p.debug_stage;
     float o_amax = 0.f;
 #pragma unroll 1
@@ -625,7 +634,7 @@ __device__ __forceinline__ void attention_block(RowCtx& c, const Params& p, cons
                 uint32_t h[8];
                 if (kDbg && cap && p.cap_op == BF_OP_QKV && c.valid)
                     store_words<16>(p.cap_acc + c.grow * 768 + j * 192 + c0, cur);
-                descale<16, false, kFP8 ? kAccPlain : kAccInt>(cur, sa, __ldg(lp.sw_qkv + m * 2 + (j >> 1)),
+                descale<16, false, kHalfA ? kAccPlain : kAccInt>(cur, sa, __ldg(lp.sw_qkv + m * 2 + (j >> 1)),
                                                                 lp.b_qkv + j * 192 + c0, h);
 #pragma unroll
                 for (int k = 0; k < 2; ++k)
@@ -661,8 +670,8 @@ __device__ __forceinline__ void attention_block(RowCtx& c, const Params& p, cons
     prof_mark<kDbg>(c, PH_PAIR_BAR);
 
     // the attention output becomes the A operand of the out-projection: quantised to s8 with a
-    // per-row scale, or (e4m3 arithmetic) copied as fp16 into the four fp16 K-slabs
-    if (kFP8) {
+    // per-row scale, or (e4m3 and fp16 arithmetics) copied as fp16 into the four fp16 K-slabs
+    if (kHalfA) {
 #pragma unroll 1
         for (int j = 0; j < 4; ++j) {
             uint32_t oh[8];
@@ -701,7 +710,7 @@ __device__ __forceinline__ void attention_block(RowCtx& c, const Params& p, cons
         tmem_wait_ld();
         row_release_acc(c, u);
         if (kDbg && cap && p.cap_op == BF_OP_OUT && c.valid) store_words<32>(p.cap_acc + c.grow * 256 + col, acc);
-        descale<32, false, kFP8 ? kAccPlain : kAccInt>(acc, sa, __ldg(lp.sw_o + u), lp.b_o + col, y);
+        descale<32, false, kHalfA ? kAccPlain : kAccInt>(acc, sa, __ldg(lp.sw_o + u), lp.b_o + col, y);
 #pragma unroll
         for (int i = 0; i < 16; ++i) xo[i] = as_u32(__hadd2(as_h2(xo[i]), as_h2(y[i])));
         tmem_st16(c.tm + TM_X + (col >> 1), xo);
@@ -712,9 +721,11 @@ __device__ __forceinline__ void attention_block(RowCtx& c, const Params& p, cons
 
 // FFN: four hidden chunks of 256; ff1 -> ReLU -> per-row u8 -> ff2 with an fp16 running
 // total (encoder.cu:1431-1556).  The eight steps follow the MMA issue order.
-template <bool kDbg, bool kFP8>
+template <bool kDbg, int kAr>
 __device__ __forceinline__ void ffn_block(RowCtx& c, const Params& p, const LayerParams& lp,
                                           float sa, bool cap) {
+    constexpr bool kFP8 = kAr == kArE4M3;
+    static_assert(kAr != kArF16, "the fp16 arithmetic has its own FFN block");
     float sa2_0 = 1.f, sa2_1 = 1.f;
     prof_mark<kDbg>(c, PH_LN);
 #pragma unroll 1
@@ -970,6 +981,58 @@ __device__ __forceinline__ void expand_board(const Params& p, int board, int lan
     }
 }
 
+// FFN of the fp16 arithmetic (the reference's default path, csrc/encoder.cu:1431-1556 with
+// Q8 = false): ff1 per 256-wide hidden chunk as an fp16 GEMM with fp16 accumulators, + bias, ReLU
+// in fp16; the chunk goes out as the fp16 A operand of ff2, whose fp16 accumulators run on
+// through all four chunks (K = 1024 in 64 steps of 16) before bias and residual are added.
+// One hidden buffer (the whole 64 KB staging region): a chunk may be written only when the ff2
+// units of the chunk before it have completed, which the MMA issuer signals on accumulator
+// barrier 1 once per chunk.  ff1 units use accumulator slot 0; the ff2 accumulators are the
+// (idle) attention-output columns for output half 0 and slot 1 for half 1.
+template <bool kDbg>
+__device__ __forceinline__ void ffn_block_f16(RowCtx& c, const Params& p, const LayerParams& lp) {
+    prof_mark<kDbg>(c, PH_LN);
+#pragma unroll 1
+    for (int ch = 0; ch < 4; ++ch) {
+#pragma unroll 1
+        for (int jh = 0; jh < 2; ++jh) {
+            row_wait_acc<kDbg>(c, 0, PH_FF1_EPI, ch == 0 && jh == 0 ? PH_WAIT_FF1_FIRST : PH_WAIT_FF1);
+            uint32_t acc[32], hid[16];
+            tmem_ld32(c.tm + TM_ACC + 32 * c.qt, acc);
+            tmem_wait_ld();
+            row_release_acc(c, 0);
+            descale<32, true, kAccPlain>(acc, 1.f, 1.f, lp.b_ff1 + 256 * ch + 128 * jh + 32 * c.qt, hid);
+            // the ff2 units of the previous chunk must be done with the hidden buffer
+            if (ch > 0 && jh == 0) row_wait_acc<kDbg>(c, 1, PH_FF1_EPI, PH_WAIT_FF2);
+            // columns 128 jh + 32 qt .. +31 of the chunk: K-slab 2 jh + qt / 2, 16-byte groups
+            // 4 (qt & 1) .. +3
+#pragma unroll
+            for (int v = 0; v < 4; ++v)
+                sts128(c.sm_r + (2 * jh + (c.qt >> 1)) * 16384 + sw_off(c.row, 4 * (c.qt & 1) + v),
+                       make_uint4(hid[4 * v], hid[4 * v + 1], hid[4 * v + 2], hid[4 * v + 3]));
+        }
+        row_publish(c, B_A2_READY);
+        prof_mark<kDbg>(c, PH_FF1_EPI);
+    }
+    // all four chunks accumulated: + b_ff2, residual (encoder.cu:1548-1556)
+    row_wait_acc<kDbg>(c, 1, PH_FF1_EPI, PH_WAIT_FF2);
+#pragma unroll 1
+    for (int jh = 0; jh < 2; ++jh) {
+        uint32_t acc[32], y[16], xo[16];
+        const int col = 128 * jh + 32 * c.qt;
+        tmem_ld32(c.tm + (jh ? TM_ACC + 128 : TM_OY) + 32 * c.qt, acc);
+        tmem_ld16(c.tm + TM_X + (col >> 1), xo);
+        tmem_wait_ld();
+        descale<32, false, kAccPlain>(acc, 1.f, 1.f, lp.b_ff2 + col, y);
+#pragma unroll
+        for (int i = 0; i < 16; ++i) xo[i] = as_u32(__hadd2(as_h2(xo[i]), as_h2(y[i])));
+        tmem_st16(c.tm + TM_X + (col >> 1), xo);
+    }
+    row_release_acc(c, 1);
+    tmem_wait_st();
+    prof_mark<kDbg>(c, PH_FF2_EPI);
+}
+
 // The "prenorm" value head (csrc/encoder.cu:1008-1057; nn/model.py:576-584): the raw residual
 // stream is averaged over the board's live tokens, that one vector goes through the final
 // LayerNorm (with affine) and is dotted with the value rows, all in fp32.  Written as one pass
@@ -1034,7 +1097,7 @@ __device__ __forceinline__ void prenorm_value(RowCtx& c, const Params& p, uint32
     for (int k = 0; k < 3; ++k) logit[k] = rstd * (t1[k] - mean * t2[k]) + t3[k];
 }
 
-template <bool kDbg, bool kRJ, bool kFP8>
+template <bool kDbg, bool kRJ, int kAr>
 __device__ __forceinline__ void row_warps_tile(RowCtx& c, const Params& p, int tile) {
     const int board = tile * 4 + c.q;
     c.valid = board < p.n;
@@ -1093,15 +1156,15 @@ __device__ __forceinline__ void row_warps_tile(RowCtx& c, const Params& p, int t
         const bool dump_x = (dbg == 9 && ph == 0) || (dbg == 2 && odd && dbgl) ||
                             (dbg == 10 && !odd && ph > 0 && layer - 1 == p.debug_layer);
         if (ph == n_ph) {
-            ln_stage<kDbg, kRJ, kFP8>(c, p, true, dump_x, dbg == 8, false, -1);
+            ln_stage<kDbg, kRJ, kAr>(c, p, true, dump_x, dbg == 8, false, -1);
             break;
         }
         const bool cap = layer == p.cap_layer;
         // re-injection site of this norm: every norm when both inject, attention norms only else
         const int site = !kRJ ? -1 : (p.rj_mode == 2 ? ph : (odd ? -1 : layer));
-        const float sa = ln_stage<kDbg, kRJ, kFP8>(c, p, false, dump_x, dbgl && dbg == (odd ? 3 : 1),
-                                                 cap && p.cap_op == (odd ? BF_OP_FF1 : BF_OP_QKV), site,
-                                                 kFP8 && !odd);
+        const float sa = ln_stage<kDbg, kRJ, kAr>(c, p, false, dump_x, dbgl && dbg == (odd ? 3 : 1),
+                                                cap && p.cap_op == (odd ? BF_OP_FF1 : BF_OP_QKV), site,
+                                                kAr == kArF16 || (kAr == kArE4M3 && !odd));
         row_publish(c, B_A_READY);
 
         const uint8_t* lpb = p.lparams + static_cast<size_t>(layer) * kLparamStride;
@@ -1114,8 +1177,9 @@ __device__ __forceinline__ void row_warps_tile(RowCtx& c, const Params& p, int t
         lp.b_o = reinterpret_cast<const __half*>(lpb + LP_B_O);
         lp.b_ff1 = reinterpret_cast<const __half*>(lpb + LP_B_FF1);
         lp.b_ff2 = reinterpret_cast<const __half*>(lpb + LP_B_FF2);
-        if (!odd) attention_block<kDbg, kFP8>(c, p, lp, sa, c.valid ? alive : 0xffffffffu, cap, dbgl);
-        else      ffn_block<kDbg, kFP8>(c, p, lp, sa, cap);
+        if (!odd) attention_block<kDbg, kAr>(c, p, lp, sa, c.valid ? alive : 0xffffffffu, cap, dbgl);
+        else if constexpr (kAr == kArF16) ffn_block_f16<kDbg>(c, p, lp);
+        else      ffn_block<kDbg, kAr>(c, p, lp, sa, cap);
     }
 
     // ---- heads: fp16 product [32 x 256] x [96 x 256]^T per board on the row warps, with
@@ -1249,10 +1313,10 @@ __device__ __forceinline__ uint32_t uses(uint32_t cnt, uint32_t slots, uint32_t 
     return (cnt + slots - 1 - s) / slots;
 }
 
-template <bool kFP8>
+template <int kAr>
 __device__ __forceinline__ void producer_loop(uint32_t smem, volatile int* abort_flag, const Params& p,
                                            int first_tile, int tile_step, int n_tiles) {
-    using C = Cfg<kFP8>;
+    using C = Cfg<kAr>;
     constexpr uint32_t kQS = C::kQSlots, kRS = C::kRSlots;
     uint32_t qi = 0, ri = 0;   // stages issued into the QKV ring / the 16 KB ring
     for (int tile = first_tile; tile < n_tiles; tile += tile_step) {
@@ -1272,8 +1336,8 @@ __device__ __forceinline__ void producer_loop(uint32_t smem, volatile int* abort
                 for (uint32_t s = 0; s < kQS; ++s)
                     mbar_wait(bar_addr(smem, B_WQ_EMPTY + s), (uses(qi, kQS, s) - 1u) & 1u, abort_flag, kErrProducer);
             }
-            // out-projection (2 units) and the 16 FFN units (2 K-slabs each)
-            const int n_st = 2 * C::kAttnSlabs + 32;
+            // out-projection (2 units) and the 16 FFN units
+            const int n_st = 2 * C::kAttnSlabs + 16 * C::kFfnSlabs;
             const uint32_t bytes = kRStage;
             for (int st = 0; st < n_st; ++st, ++ri) {
                 const uint32_t s = ri % kRS;
@@ -1304,11 +1368,11 @@ struct MmaState {
 enum { kKindI8 = 0, kKindF16 = 1, kKindF8 = 2 };
 
 // One GEMM unit: `n_stages` K-slabs of 128 bytes, 4 MMAs each.
-template <bool kFP8>
+template <int kAr>
 __device__ __forceinline__ void mma_unit(uint32_t smem, volatile int* abort_flag, MmaState& st,
                                          uint32_t tmem_d, int slot, uint32_t a_base, bool qring,
                                          int n_stages, uint32_t idesc, int kind) {
-    using C = Cfg<kFP8>;
+    using C = Cfg<kAr>;
     mbar_wait(bar_addr(smem, B_ACC_EMPTY + slot), (st.accn[slot] - 1u) & 1u, abort_flag, kErrMmaAcc);
     tc_fence_after();
     for (int s = 0; s < n_stages; ++s) {
@@ -1346,34 +1410,72 @@ __device__ __forceinline__ void mma_wait_operand(uint32_t smem, volatile int* ab
     tc_fence_after();
 }
 
-template <bool kFP8>
+template <int kAr>
 __device__ __forceinline__ void mma_loop(uint32_t smem, uint32_t tmem, volatile int* abort_flag,
                                       const Params& p, int first_tile, int tile_step, int n_tiles) {
-    using C = Cfg<kFP8>;
+    using C = Cfg<kAr>;
     MmaState st = {0, 0, {0, 0}, 0, {0, 0}};
     // int8: every weight GEMM is s8/u8 x s8.  e4m3: QKV and out-projection are fp16 x fp16 with
     // fp16 accumulators (the bits of the reference's mma.sync), the FFN is e4m3 x e4m3 with fp32
     // accumulators (the reference's fp16-accumulate e4m3 mma.sync has no bit-equal on tcgen05).
-    constexpr uint32_t kI_QKV = kFP8 ? umma_idesc(kAccF16, kFmtF16, kFmtF16, 128, 192)
-                                     : umma_idesc(kAccS32, kFmtS8, kFmtS8, 128, 192);
-    constexpr uint32_t kI_OUT = kFP8 ? umma_idesc(kAccF16, kFmtF16, kFmtF16, 128, 128)
-                                     : umma_idesc(kAccS32, kFmtS8, kFmtS8, 128, 128);
-    constexpr uint32_t kI_FF1 = kFP8 ? umma_idesc(kAccF32, kFmtE4M3, kFmtE4M3, 128, 128)
-                                     : umma_idesc(kAccS32, kFmtS8, kFmtS8, 128, 128);
-    constexpr uint32_t kI_FF2 = kFP8 ? umma_idesc(kAccF32, kFmtE4M3, kFmtE4M3, 128, 128)
-                                     : umma_idesc(kAccS32, kFmtU8, kFmtS8, 128, 128);
-    constexpr int kAttnKind = kFP8 ? kKindF16 : kKindI8, kFfnKind = kFP8 ? kKindF8 : kKindI8;
+    constexpr bool kHalfA = kAr != kArInt8;
+    constexpr uint32_t kI_H128 = umma_idesc(kAccF16, kFmtF16, kFmtF16, 128, 128);
+    constexpr uint32_t kI_QKV = kHalfA ? umma_idesc(kAccF16, kFmtF16, kFmtF16, 128, 192)
+                                       : umma_idesc(kAccS32, kFmtS8, kFmtS8, 128, 192);
+    constexpr uint32_t kI_OUT = kHalfA ? kI_H128 : umma_idesc(kAccS32, kFmtS8, kFmtS8, 128, 128);
+    constexpr uint32_t kI_FF1 = kAr == kArE4M3 ? umma_idesc(kAccF32, kFmtE4M3, kFmtE4M3, 128, 128)
+                              : kAr == kArF16 ? kI_H128 : umma_idesc(kAccS32, kFmtS8, kFmtS8, 128, 128);
+    constexpr uint32_t kI_FF2 = kAr == kArE4M3 ? umma_idesc(kAccF32, kFmtE4M3, kFmtE4M3, 128, 128)
+                              : kAr == kArF16 ? kI_H128 : umma_idesc(kAccS32, kFmtU8, kFmtS8, 128, 128);
+    constexpr int kAttnKind = kHalfA ? kKindF16 : kKindI8;
+    constexpr int kFfnKind = kAr == kArE4M3 ? kKindF8 : (kAr == kArF16 ? kKindF16 : kKindI8);
     const uint32_t acc0 = tmem + TM_ACC, acc1 = tmem + TM_ACC + 128;
     const uint32_t sm_a = smem + C::SM_A, sm_r = smem + C::SM_R;
     for (int tile = first_tile; tile < n_tiles; tile += tile_step) {
         for (int layer = 0; layer < p.n_layers; ++layer) {
             mma_wait_operand(smem, abort_flag, B_A_READY, st.aready);          // LN1 output
             for (int j = 0; j < 4; ++j)
-                mma_unit<kFP8>(smem, abort_flag, st, acc0, 0, sm_a, true, C::kAttnSlabs, kI_QKV, kAttnKind);
+                mma_unit<kAr>(smem, abort_flag, st, acc0, 0, sm_a, true, C::kAttnSlabs, kI_QKV, kAttnKind);
             mma_wait_operand(smem, abort_flag, B_A_READY, st.aready);          // attention output
-            mma_unit<kFP8>(smem, abort_flag, st, acc0, 0, sm_a, false, C::kAttnSlabs, kI_OUT, kAttnKind);
-            mma_unit<kFP8>(smem, abort_flag, st, acc1, 1, sm_a, false, C::kAttnSlabs, kI_OUT, kAttnKind);
+            mma_unit<kAr>(smem, abort_flag, st, acc0, 0, sm_a, false, C::kAttnSlabs, kI_OUT, kAttnKind);
+            mma_unit<kAr>(smem, abort_flag, st, acc1, 1, sm_a, false, C::kAttnSlabs, kI_OUT, kAttnKind);
             mma_wait_operand(smem, abort_flag, B_A_READY, st.aready);          // LN2 output
+            if constexpr (kAr == kArF16) {
+                // fp16 FFN: per hidden chunk two ff1 units into slot 0, then, once the rows
+                // have written the chunk, the two ff2 units, whose accumulators (the idle
+                // attention-output columns for half 0, slot 1 for half 1) run on through all
+                // four chunks; one commit per chunk on accumulator barrier 1 tells the rows
+                // that the hidden buffer is free again, the last one that the sums are done
+#pragma unroll 1
+                for (int ch = 0; ch < 4; ++ch) {
+                    mma_unit<kAr>(smem, abort_flag, st, acc0, 0, sm_a, false, 4, kI_FF1, kKindF16);
+                    mma_unit<kAr>(smem, abort_flag, st, acc0, 0, sm_a, false, 4, kI_FF1, kKindF16);
+                    mma_wait_operand(smem, abort_flag, B_A2_READY, st.a2n[0]);
+                    if (ch == 0) {
+                        mbar_wait(bar_addr(smem, B_ACC_EMPTY + 1), (st.accn[1] - 1u) & 1u, abort_flag, kErrMmaAcc);
+                        tc_fence_after();
+                    }
+#pragma unroll 1
+                    for (int jh = 0; jh < 2; ++jh) {
+                        const uint32_t dst = jh ? acc1 : tmem + TM_OY;
+#pragma unroll 1
+                        for (int sl = 0; sl < 4; ++sl) {
+                            const uint32_t k = st.rc % C::kRSlots;
+                            mbar_wait(bar_addr(smem, B_WR_FULL + k), (st.rc / C::kRSlots) & 1u, abort_flag, kErrMmaWeights);
+                            st.rc++;
+                            tc_fence_after();
+                            const uint64_t ad = umma_desc_k128(sm_r + sl * 16384);
+                            const uint64_t bd = umma_desc_k128(smem + C::SM_RING + k * kRStage);
+#pragma unroll
+                            for (int kk = 0; kk < 4; ++kk)
+                                umma_f16(dst, ad + 2 * kk, bd + 2 * kk, kI_FF2, (ch > 0 || sl > 0 || kk > 0) ? 1u : 0u);
+                            tc_commit(bar_addr(smem, B_WR_EMPTY + k));
+                        }
+                    }
+                    tc_commit(bar_addr(smem, B_ACC_FULL + 1));
+                }
+                st.accn[1]++;
+            } else {
             // FFN units in the order the weight stream was packed (pack.py: FFN_UNITS)
 #pragma unroll 1
             for (int u = 0; u < 16; ++u) {
@@ -1383,18 +1485,19 @@ __device__ __forceinline__ void mma_loop(uint32_t smem, uint32_t tmem, volatile 
                 const int ch = kind2 ? ((0x32010000u >> (4 * pr)) & 0xF) : ((0x00302010u >> (4 * pr)) & 0xF);
                 if (kind2) {
                     if (jh == 0) mma_wait_operand(smem, abort_flag, B_A2_READY + (ch & 1), st.a2n[ch & 1]);
-                    mma_unit<kFP8>(smem, abort_flag, st, jh ? acc1 : acc0, jh, sm_r + (ch & 1) * 32768,
+                    mma_unit<kAr>(smem, abort_flag, st, jh ? acc1 : acc0, jh, sm_r + (ch & 1) * 32768,
                                    false, 2, kI_FF2, kFfnKind);
                 } else {
-                    mma_unit<kFP8>(smem, abort_flag, st, jh ? acc1 : acc0, jh, sm_a, false, 2, kI_FF1, kFfnKind);
+                    mma_unit<kAr>(smem, abort_flag, st, jh ? acc1 : acc0, jh, sm_a, false, 2, kI_FF1, kFfnKind);
                 }
+            }
             }
         }
     }
 }
 
 // ------------------------------------------------------------------------------------------
-template <bool kDbg, bool kRJ, bool kFP8>
+template <bool kDbg, bool kRJ, int kAr>
 __global__ void __launch_bounds__(kThreads, 1) encoder_kernel(const Params p) {
     extern __shared__ uint8_t smem_raw[];
     uint8_t* sm = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
@@ -1426,17 +1529,17 @@ __global__ void __launch_bounds__(kThreads, 1) encoder_kernel(const Params p) {
         RowCtx c;
         c.lane = lane; c.q = warp & 3; c.qt = warp >> 2; c.row = 32 * c.q + lane;
         c.smem = smem; c.smem_gen = sm;
-        c.sm_a = smem + Cfg<kFP8>::SM_A; c.sm_r = smem + Cfg<kFP8>::SM_R;
+        c.sm_a = smem + Cfg<kAr>::SM_A; c.sm_r = smem + Cfg<kAr>::SM_R;
         c.tm = tmem + (static_cast<uint32_t>(32 * c.q) << 16);
         c.abort_flag = abort_flag; c.xpar = 0; c.full0 = c.full1 = 0;
         c.one2 = pk2(p.one, p.one);
         c.prof_on = kDbg && p.prof != nullptr && threadIdx.x == 0;
         c.t_last = c.prof_on ? clock64() : 0;
-        for (int tile = blockIdx.x; tile < n_tiles; tile += gridDim.x) row_warps_tile<kDbg, kRJ, kFP8>(c, p, tile);
+        for (int tile = blockIdx.x; tile < n_tiles; tile += gridDim.x) row_warps_tile<kDbg, kRJ, kAr>(c, p, tile);
     } else if (warp == kProducerWarp) {
-        if (lane == 0) producer_loop<kFP8>(smem, abort_flag, p, blockIdx.x, gridDim.x, n_tiles);
+        if (lane == 0) producer_loop<kAr>(smem, abort_flag, p, blockIdx.x, gridDim.x, n_tiles);
     } else {
-        if (lane == 0) mma_loop<kFP8>(smem, tmem, abort_flag, p, blockIdx.x, gridDim.x, n_tiles);
+        if (lane == 0) mma_loop<kAr>(smem, tmem, abort_flag, p, blockIdx.x, gridDim.x, n_tiles);
     }
     __syncwarp();
     tc_fence_before();
@@ -1716,16 +1819,20 @@ int launch(bf_handle* h, const uint16_t* boards, const int16_t* control, const u
     const int grid = n_tiles < h->sm_count ? n_tiles : h->sm_count;
     // the instrumented instantiation only when a dump, a capture or the phase clock is asked for
     const bool dbg = stage != 0 || cap_layer >= 0 || p.prof != nullptr;
-    if (p.quant == 1) {
+    if (p.quant == 0) {
         if (cap_layer >= 0) return fail(BF_ENOTSUP, "operand capture is for the int8 arithmetic");
-        if (dbg) bf::encoder_kernel<true, false, true><<<grid, bf::kThreads, bf::kSmemRequest, stream>>>(p);
-        else     bf::encoder_kernel<false, false, true><<<grid, bf::kThreads, bf::kSmemRequest, stream>>>(p);
+        if (dbg) bf::encoder_kernel<true, false, bf::kArF16><<<grid, bf::kThreads, bf::kSmemRequest, stream>>>(p);
+        else     bf::encoder_kernel<false, false, bf::kArF16><<<grid, bf::kThreads, bf::kSmemRequest, stream>>>(p);
+    } else if (p.quant == 1) {
+        if (cap_layer >= 0) return fail(BF_ENOTSUP, "operand capture is for the int8 arithmetic");
+        if (dbg) bf::encoder_kernel<true, false, bf::kArE4M3><<<grid, bf::kThreads, bf::kSmemRequest, stream>>>(p);
+        else     bf::encoder_kernel<false, false, bf::kArE4M3><<<grid, bf::kThreads, bf::kSmemRequest, stream>>>(p);
     } else if (p.rj_mode != 0) {
-        if (dbg) bf::encoder_kernel<true, true, false><<<grid, bf::kThreads, bf::kSmemRequest, stream>>>(p);
-        else     bf::encoder_kernel<false, true, false><<<grid, bf::kThreads, bf::kSmemRequest, stream>>>(p);
+        if (dbg) bf::encoder_kernel<true, true, bf::kArInt8><<<grid, bf::kThreads, bf::kSmemRequest, stream>>>(p);
+        else     bf::encoder_kernel<false, true, bf::kArInt8><<<grid, bf::kThreads, bf::kSmemRequest, stream>>>(p);
     } else {
-        if (dbg) bf::encoder_kernel<true, false, false><<<grid, bf::kThreads, bf::kSmemRequest, stream>>>(p);
-        else     bf::encoder_kernel<false, false, false><<<grid, bf::kThreads, bf::kSmemRequest, stream>>>(p);
+        if (dbg) bf::encoder_kernel<true, false, bf::kArInt8><<<grid, bf::kThreads, bf::kSmemRequest, stream>>>(p);
+        else     bf::encoder_kernel<false, false, bf::kArInt8><<<grid, bf::kThreads, bf::kSmemRequest, stream>>>(p);
     }
     BF_CUDA(cudaGetLastError());
     h->launches++;
@@ -1751,9 +1858,12 @@ int bf_create(const void* blob, size_t blob_bytes, int device, bf_handle** out) 
     if (hdr.version != BF_BLOB_VERSION) return fail(BF_EINVAL, "blob version mismatch");
     if (hdr.total != blob_bytes) return fail(BF_EINVAL, "blob size does not match its header");
     if (hdr.n_layers < 1 || hdr.n_layers > 64) return fail(BF_EINVAL, "n_layers out of range");
-    if (hdr.quant != 3 && hdr.quant != 1) return fail(BF_EINVAL, "blob arithmetic must be 3 (int8) or 1 (e4m3 FFN)");
-    if (hdr.quant == 1 && hdr.rj_mode != 0) return fail(BF_ENOTSUP, "re-injection is built for the int8 arithmetic only");
-    const uint64_t layer_stream = hdr.quant == 1 ? bf::Cfg<true>::kLayerStream : bf::Cfg<false>::kLayerStream;
+    if (hdr.quant != 3 && hdr.quant != 1 && hdr.quant != 0)
+        return fail(BF_EINVAL, "blob arithmetic must be 3 (int8), 1 (e4m3 FFN) or 0 (fp16)");
+    if (hdr.quant != 3 && hdr.rj_mode != 0) return fail(BF_ENOTSUP, "re-injection is built for the int8 arithmetic only");
+    const uint64_t layer_stream = hdr.quant == 1 ? bf::Cfg<bf::kArE4M3>::kLayerStream
+                                : hdr.quant == 0 ? bf::Cfg<bf::kArF16>::kLayerStream
+                                                 : bf::Cfg<bf::kArInt8>::kLayerStream;
     if (hdr.bytes_w != static_cast<uint64_t>(hdr.n_layers) * layer_stream ||
         hdr.bytes_lp != static_cast<uint64_t>(hdr.n_layers) * bf::kLparamStride ||
         hdr.bytes_emb != 184u * 256u * 2u || hdr.bytes_tail != bf::kTailBytes || hdr.rj_mode > 2 ||
@@ -1781,14 +1891,16 @@ int bf_create(const void* blob, size_t blob_bytes, int device, bf_handle** out) 
     if (e == cudaSuccess) e = cudaStreamCreateWithFlags(&h->stream, cudaStreamNonBlocking);
     if (e == cudaSuccess) e = cudaStreamCreateWithFlags(&h->copy_stream, cudaStreamNonBlocking);
     if (e == cudaSuccess) e = cudaEventCreateWithFlags(&h->chunk_done, cudaEventDisableTiming);
-    const void* kernels[6] = {
-        reinterpret_cast<const void*>(&bf::encoder_kernel<false, false, false>),
-        reinterpret_cast<const void*>(&bf::encoder_kernel<true, false, false>),
-        reinterpret_cast<const void*>(&bf::encoder_kernel<false, true, false>),
-        reinterpret_cast<const void*>(&bf::encoder_kernel<true, true, false>),
-        reinterpret_cast<const void*>(&bf::encoder_kernel<false, false, true>),
-        reinterpret_cast<const void*>(&bf::encoder_kernel<true, false, true>)};
-    for (int i = 0; i < 6 && e == cudaSuccess; ++i)
+    const void* kernels[8] = {
+        reinterpret_cast<const void*>(&bf::encoder_kernel<false, false, bf::kArInt8>),
+        reinterpret_cast<const void*>(&bf::encoder_kernel<true, false, bf::kArInt8>),
+        reinterpret_cast<const void*>(&bf::encoder_kernel<false, true, bf::kArInt8>),
+        reinterpret_cast<const void*>(&bf::encoder_kernel<true, true, bf::kArInt8>),
+        reinterpret_cast<const void*>(&bf::encoder_kernel<false, false, bf::kArE4M3>),
+        reinterpret_cast<const void*>(&bf::encoder_kernel<true, false, bf::kArE4M3>),
+        reinterpret_cast<const void*>(&bf::encoder_kernel<false, false, bf::kArF16>),
+        reinterpret_cast<const void*>(&bf::encoder_kernel<true, false, bf::kArF16>)};
+    for (int i = 0; i < 8 && e == cudaSuccess; ++i)
         e = cudaFuncSetAttribute(kernels[i], cudaFuncAttributeMaxDynamicSharedMemorySize, bf::kSmemRequest);
     if (e != cudaSuccess) {
         bf_destroy(h);
@@ -2150,7 +2262,7 @@ int noalloc_setup(int device, NoAllocDevice** out) {
         void* ptr = nullptr;
         BF_CUDA(cudaGetSymbolAddress(&ptr, bf::g_noalloc_scratch));
         BF_CUDA(cudaMemset(ptr, 0, bf::kNoAllocScratchBytes));
-        BF_CUDA(cudaFuncSetAttribute(bf::encoder_kernel<false, false, false>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+        BF_CUDA(cudaFuncSetAttribute(bf::encoder_kernel<false, false, bf::kArInt8>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                      bf::kSmemRequest));
         d.scratch = ptr;
         d.sm_count = prop.multiProcessorCount;
@@ -2184,7 +2296,7 @@ int bf_forward_noalloc(int device, const void* blob_dev, size_t blob_bytes, cons
             return fail(BF_EINVAL, "blob header does not match (magic, version or size)");
         if (hdr.n_layers < 1 || hdr.n_layers > 64 ||
             hdr.quant != 3 ||
-            hdr.bytes_w != static_cast<uint64_t>(hdr.n_layers) * bf::Cfg<false>::kLayerStream ||
+            hdr.bytes_w != static_cast<uint64_t>(hdr.n_layers) * bf::Cfg<bf::kArInt8>::kLayerStream ||
             hdr.bytes_lp != static_cast<uint64_t>(hdr.n_layers) * bf::kLparamStride ||
             hdr.bytes_emb != 184u * 256u * 2u || hdr.bytes_tail != bf::kTailBytes || hdr.rj_mode != 0 ||
             ((hdr.off_w | hdr.off_lp | hdr.off_emb | hdr.off_tail) & 255u) ||
@@ -2219,7 +2331,7 @@ int bf_forward_noalloc(int device, const void* blob_dev, size_t blob_bytes, cons
     p.prof = nullptr;
     const int n_tiles = (n + 3) / 4;
     const int grid = n_tiles < d->sm_count ? n_tiles : d->sm_count;
-    bf::encoder_kernel<false, false, false><<<grid, bf::kThreads, bf::kSmemRequest, static_cast<cudaStream_t>(stream)>>>(p);
+    bf::encoder_kernel<false, false, bf::kArInt8><<<grid, bf::kThreads, bf::kSmemRequest, static_cast<cudaStream_t>(stream)>>>(p);
     BF_CUDA(cudaGetLastError());
     return BF_OK;
 }

@@ -57,23 +57,26 @@ class ShardedEvaluator:
     """Position-sharded evaluation: this rank evaluates its slice of every batch.
 
     ``net`` is needed on rank 0 only (other ranks may pass ``None``); the packed weights
-    travel as one blob.  ``forward_shard`` evaluates positions that already live on this
+    travel as one blob (int8 by default; ``fp8=True`` the e4m3-FFN arithmetic, ``int8=False`` the
+    fp16 arithmetic).  ``forward_shard`` evaluates positions that already live on this
     rank's GPU; ``shard`` tells the caller which slice of a global batch is this rank's.
     """
 
-    def __init__(self, net, rank: int, world: int, device_index: int, fp8: bool = False):
+    def __init__(self, net, rank: int, world: int, device_index: int, fp8: bool = False,
+                 int8: bool = True):
         import torch.distributed as dist
         from brokefish_b200.nn.cuda_impl import FusedEncoder
         from brokefish_b200.nn.pack import pack_blob
         self.rank, self.world = rank, world
         dev = torch.device("cuda", device_index)
         if world > 1:
-            blob = pack_blob(net, "e4m3" if fp8 else "int8") if rank == 0 else None
+            fmt = "e4m3" if fp8 else ("int8" if int8 else "f16")
+            blob = pack_blob(net, fmt) if rank == 0 else None
             blob_dev = broadcast_blob(blob, dev, src=0)
             torch.cuda.synchronize(dev)
             self.encoder = FusedEncoder.from_blob(blob_dev, device=device_index)
         else:
-            self.encoder = FusedEncoder(net, device=device_index, fp8=fp8)
+            self.encoder = FusedEncoder(net, device=device_index, fp8=fp8, int8=None if fp8 else int8)
 
     def shard(self, n: int) -> Tuple[int, int]:
         return shard_bounds(n, self.world, self.rank)

@@ -5,13 +5,14 @@ Same constructor, attributes, methods and errors as the reference's CUDA impleme
 ``include/brokefish_b200.h``.  PyTorch is used for device memory and the current stream
 only.
 
-Two arithmetics are built: the reference's ``int8=True`` path (scheme ``"all"``: QKV,
+Three arithmetics are built: the reference's ``int8=True`` path (scheme ``"all"``: QKV,
 out-projection and both FFN matmuls in int8, heads and attention in fp16), which is the
 default here and whose outputs equal the reference kernel's bit for bit, and its
 ``fp8=True`` path (the two FFN matmuls in e4m3 with ``amax/8`` scales,
-QKV and out-projection in fp16).  The plain fp16 arithmetic and the partial int8 schemes
-are not built: asking for them raises ``NotImplementedError`` instead of silently running
-something else.
+QKV and out-projection in fp16), and the plain fp16 arithmetic (``int8=False``: the reference's
+own default; every weight GEMM fp16 with fp16 accumulators on tcgen05, which carry the bits of
+the reference's ``mma.sync``).  The partial int8 schemes are not built: asking for them raises
+``NotImplementedError`` instead of silently running something else.
 
 The weights are a *snapshot*: folded, quantised and uploaded once in the constructor.
 After a weight update, build a new ``FusedEncoder``.
@@ -87,14 +88,12 @@ class FusedEncoder:
             raise ValueError(f"int8_scheme must be one of {sorted(SCHEMES)}, got {int8_scheme!r}")
         if self.fp8:
             self.int8 = False
-        elif not self.int8:
-            raise NotImplementedError("the fp16 arithmetic is not built; use int8 (the default) "
-                                      "or fp8=True")
         if self.int8 and int8_scheme != "all":
             raise NotImplementedError("only the 'all' int8 scheme is built")
         self.int8_scheme = int8_scheme
-        # the reference's kernel mode numbers: 3 = int8 on all four matmuls, 1 = e4m3 FFN
-        self.quant = 1 if self.fp8 else SCHEMES[int8_scheme]
+        # the reference's kernel mode numbers: 3 = int8 on all four matmuls, 1 = e4m3 FFN,
+        # 0 = the plain fp16 arithmetic (the reference's default; here `int8=False`)
+        self.quant = 1 if self.fp8 else (SCHEMES[int8_scheme] if self.int8 else 0)
         # Kept for callers that read it; the number of boards sharing a CTA never changes
         # a board's arithmetic, here as in the reference.
         self.two_boards = True if two_boards is None else bool(two_boards)
@@ -112,9 +111,9 @@ class FusedEncoder:
             self.n_value = int(net.value.weight.shape[0])
             self.vmode = self.VMODE[getattr(net, "value_head", "king")]
             self.rj_mode = self.RJMODE[getattr(net, "reinject", "none")]
-            if self.fp8 and self.rj_mode:
+            if self.quant != 3 and self.rj_mode:
                 raise NotImplementedError("input re-injection is built for the int8 arithmetic only")
-            self.blob = pack_blob(net, "e4m3" if self.fp8 else "int8")
+            self.blob = pack_blob(net, {3: "int8", 1: "e4m3", 0: "f16"}[self.quant])
             self._create(self.blob)
 
     # -- construction helpers --------------------------------------------------
@@ -150,7 +149,7 @@ class FusedEncoder:
         self.n_layers, self.n_value, self.vmode = nl.value, nv.value, vm.value
         head = blob[:32].cpu().numpy() if isinstance(blob, torch.Tensor) else np.asarray(blob[:32])
         self.rj_mode, self.quant = (int(v) for v in head.view(np.uint32)[6:8])
-        self.fp8, self.int8 = self.quant == 1, self.quant != 1
+        self.fp8, self.int8 = self.quant == 1, self.quant == 3
         self.eps = 1e-5
         self._from_blob = True
         return self
@@ -169,7 +168,7 @@ class FusedEncoder:
     @property
     def label(self) -> str:
         """What this instance runs, for a bench header or a run log."""
-        base = "e4m3 FFN" if self.quant == 1 else "int8 FFN+QKV+out_proj"
+        base = {1: "e4m3 FFN", 0: "fp16", 3: "int8 FFN+QKV+out_proj"}[self.quant]
         return base + ", 4 boards/CTA, tcgen05 (sm_100a)"
 
     @property

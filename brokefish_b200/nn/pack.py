@@ -62,9 +62,10 @@ NHEAD = 96                   # head matrix rows: 64 policy, 4 promo, 1-3 value, 
 VALUE_ROW = N_POLICY + N_PROMO
 LAYER_STREAM_BYTES = 786432
 LAYER_STREAM_BYTES_E4M3 = 1048576
+LAYER_STREAM_BYTES_F16 = 1572864
 #: Arithmetic of a blob, by the reference's kernel mode number: 3 = int8 on all four
 #: matmuls, 1 = e4m3 on the two FFN matmuls with fp16 QKV and out-projection.
-QUANT_INT8, QUANT_E4M3 = 3, 1
+QUANT_INT8, QUANT_E4M3, QUANT_F16 = 3, 1, 0
 HEAD_STREAM_BYTES = 4 * NHEAD * 128
 LPARAM_STRIDE = 4736
 LP_SW_QKV, LP_SW_O, LP_SW_FF1, LP_SW_FF2 = 0, 24, 32, 64
@@ -119,9 +120,10 @@ class FoldedLayer:
 def fold_and_quantise(net: BrokefishNet, fmt: str = "int8") -> List[FoldedLayer]:
     """The per-layer folded matrices, scales and fp16 biases.  ``fmt="int8"``: all four
     matrices s8.  ``fmt="e4m3"``: the two FFN matrices e4m3 with ``amax/8`` scales, QKV and
-    out-projection fp16 (brokefish/nn/cuda_impl.py:303-337)."""
-    if fmt not in ("int8", "e4m3"):
-        raise ValueError(f"fmt must be 'int8' or 'e4m3', got {fmt!r}")
+    out-projection fp16 (brokefish/nn/cuda_impl.py:303-337).  ``fmt="f16"``: all four fp16, the
+    folded fp32 matrices rounded once (cuda_impl.py:194-228)."""
+    if fmt not in ("int8", "e4m3", "f16"):
+        raise ValueError(f"fmt must be 'int8', 'e4m3' or 'f16', got {fmt!r}")
     out = []
     scale = DH ** -0.5
     for lay in net.encoder.layers:
@@ -137,7 +139,7 @@ def fold_and_quantise(net: BrokefishNet, fmt: str = "int8") -> List[FoldedLayer]
                         ("ff1", w_ff1), ("ff2", lay.linear2.weight.detach())):
             if fmt == "int8":
                 qb, sc = quantise_weights_int8_bytes(w.float())
-            elif name in ("ff1", "ff2"):
+            elif fmt == "e4m3" and name in ("ff1", "ff2"):
                 qb, sc = quantise_weights_bytes(w.float(), Q_MAX, tile_k=w.shape[1])
                 sc = sc.reshape(-1)
             else:
@@ -198,17 +200,32 @@ def _layer_stream(fl: FoldedLayer) -> np.ndarray:
         for s in range(slabs):
             parts.append(sw128_image(np.ascontiguousarray(
                 fl.q_o[128 * u:128 * u + 128, 128 * s:128 * s + 128])))
-    for kind, c, j in FFN_UNITS:
-        for s in range(2):
-            if kind == 1:
-                blk = fl.q_ff1[256 * c + 128 * j:256 * c + 128 * j + 128,
-                               128 * s:128 * s + 128]
-            else:
-                blk = fl.q_ff2[128 * j:128 * j + 128,
-                               256 * c + 128 * s:256 * c + 128 * s + 128]
-            parts.append(sw128_image(np.ascontiguousarray(blk)))
+    if fl.q_ff1.shape[1] == 512:
+        # fp16 FFN: per hidden chunk the two ff1 units then the two ff2 units, 4 K-slabs of 64
+        # halves each (the ff2 accumulators run on through the chunks, so its units follow the
+        # chunk order)
+        for c in range(4):
+            for j in range(2):
+                for s in range(4):
+                    parts.append(sw128_image(np.ascontiguousarray(
+                        fl.q_ff1[256 * c + 128 * j:256 * c + 128 * j + 128, 128 * s:128 * s + 128])))
+            for j in range(2):
+                for s in range(4):
+                    parts.append(sw128_image(np.ascontiguousarray(
+                        fl.q_ff2[128 * j:128 * j + 128, 512 * c + 128 * s:512 * c + 128 * s + 128])))
+    else:
+        for kind, c, j in FFN_UNITS:
+            for s in range(2):
+                if kind == 1:
+                    blk = fl.q_ff1[256 * c + 128 * j:256 * c + 128 * j + 128,
+                                   128 * s:128 * s + 128]
+                else:
+                    blk = fl.q_ff2[128 * j:128 * j + 128,
+                                   256 * c + 128 * s:256 * c + 128 * s + 128]
+                parts.append(sw128_image(np.ascontiguousarray(blk)))
     stream = np.concatenate(parts)
-    assert stream.size == (LAYER_STREAM_BYTES if slabs == 2 else LAYER_STREAM_BYTES_E4M3)
+    assert stream.size == (LAYER_STREAM_BYTES_F16 if fl.q_ff1.shape[1] == 512 else
+                           LAYER_STREAM_BYTES if slabs == 2 else LAYER_STREAM_BYTES_E4M3)
     return stream
 
 
@@ -231,9 +248,10 @@ def _align(n: int, a: int = 256) -> int:
 
 
 def pack_blob(net: BrokefishNet, fmt: str = "int8") -> np.ndarray:
-    """The whole device blob for ``net`` as a ``uint8`` array, in the int8 arithmetic or in
-    the e4m3-FFN arithmetic (in which a layer's stream is 16 QKV stages and 8 out-projection
-    stages of fp16 followed by the 32 FFN stages of e4m3 bytes: 1,048,576 B per layer)."""
+    """The whole device blob for ``net`` as a ``uint8`` array, in the int8 arithmetic, in the
+    e4m3-FFN arithmetic (a layer's stream is 16 QKV stages and 8 out-projection stages of fp16
+    followed by the 32 FFN stages of e4m3 bytes: 1,048,576 B per layer) or in the fp16
+    arithmetic (``fmt="f16"``: 16 + 8 + 64 stages of fp16, 1,572,864 B per layer)."""
     if (net.d_model, len(net.encoder.layers)) != (D, net.n_layers):
         raise ValueError("unexpected network shape")
     first = net.encoder.layers[0]
@@ -244,7 +262,7 @@ def pack_blob(net: BrokefishNet, fmt: str = "int8") -> np.ndarray:
             f"{first.self_attn.embed_dim}, {first.linear1.out_features}, "
             f"{first.self_attn.num_heads}")
     layers = fold_and_quantise(net, fmt)
-    if fmt == "e4m3" and getattr(net, "reinject", "none") != "none":
+    if fmt != "int8" and getattr(net, "reinject", "none") != "none":
         raise NotImplementedError("input re-injection is built for the int8 arithmetic only")
     wstream = np.concatenate([_layer_stream(fl) for fl in layers])
     lparams = np.concatenate([_layer_params(fl) for fl in layers])
@@ -272,7 +290,7 @@ def pack_blob(net: BrokefishNet, fmt: str = "int8") -> np.ndarray:
     vmode = VALUE_MODE_ID.get(getattr(net, "value_head", "king"), 0)
     header = struct.pack("<IIIIIfII", MAGIC, VERSION, len(layers),
                          int(net.value.weight.shape[0]), vmode, float(first.norm1.eps), rj_mode,
-                         QUANT_INT8 if fmt == "int8" else QUANT_E4M3)
+                         {"int8": QUANT_INT8, "e4m3": QUANT_E4M3, "f16": QUANT_F16}[fmt])
     for off, sec in zip(offs, sections):
         header += struct.pack("<QQ", off, sec.size)
     header += struct.pack("<Q", total)

@@ -129,7 +129,7 @@ class Weights:
 
 def prepare(state: Dict[str, np.ndarray], fmt: str = "int8") -> Weights:
     """Fold, quantise and round a fp32 ``state_dict`` (numpy arrays)."""
-    if fmt not in ("int8", "e4m3"):
+    if fmt not in ("int8", "e4m3", "f16"):
         raise ValueError(fmt)
     s = {k: np.asarray(v) for k, v in state.items()}
     n_layers = 1 + max(int(k.split(".")[2]) for k in s if k.startswith("encoder.layers."))
@@ -158,8 +158,12 @@ def prepare(state: Dict[str, np.ndarray], fmt: str = "int8") -> Weights:
         else:
             q_qkv, s_qkv = f16(w_qkv), np.ones(6, dtype=F32)
             q_o, s_o = f16(s[p + "self_attn.out_proj.weight"]), np.ones(2, dtype=F32)
-            q_ff1, s_ff1 = quantise_weights_e4m3(w_ff1)
-            q_ff2, s_ff2 = quantise_weights_e4m3(s[p + "linear2.weight"].astype(F32))
+            if fmt == "e4m3":
+                q_ff1, s_ff1 = quantise_weights_e4m3(w_ff1)
+                q_ff2, s_ff2 = quantise_weights_e4m3(s[p + "linear2.weight"].astype(F32))
+            else:               # the reference's default arithmetic: every matrix fp16
+                q_ff1, s_ff1 = f16(w_ff1), np.ones(8, dtype=F32)
+                q_ff2, s_ff2 = f16(s[p + "linear2.weight"]), np.ones(2, dtype=F32)
         layers.append(LayerW(q_qkv, s_qkv, f16(b_qkv), q_o, s_o,
                              f16(s[p + "self_attn.out_proj.bias"]),
                              q_ff1, s_ff1, f16(b_ff1), q_ff2, s_ff2,
@@ -305,13 +309,12 @@ def descale(acc: np.ndarray, sa: np.ndarray, sw_blocks: np.ndarray, n0: int = 0)
     return ((acc.astype(F32) * sa[:, None]).astype(F32) * sw[None, :]).astype(F32)
 
 
-def _mma_f16acc(a: np.ndarray, b: np.ndarray) -> np.ndarray:
+def _mma_f16acc(a: np.ndarray, b: np.ndarray, acc: Optional[np.ndarray] = None) -> np.ndarray:
     """``a @ b`` for fp16 operands with the contraction cut into steps of 16 and an fp16
     accumulator between the steps, the shape of the reference's ``mma.sync m16n8k16`` with
     fp16 accumulators (csrc/mma.cuh:68-75).  Inside a step the sum is taken exactly and rounded
     once; the hardware's own order inside a step is not documented, so this is a model of it,
     not a transcript."""
-    acc = None
     for k0 in range(0, a.shape[-1], 16):
         part = np.matmul(a[..., k0:k0 + 16].astype(np.float64), b[..., k0:k0 + 16, :].astype(np.float64))
         acc = part.astype(F16) if acc is None else (acc.astype(np.float64) + part).astype(F16)
@@ -376,7 +379,7 @@ def forward(w: Weights, boards, control, rep, legal=None, trace: Optional[Trace]
         xn = layernorm(reinject(w, x, boards, control, rep, site1) if w.rj_mode else x)
         if first:
             trace.stages[1] = xn.reshape(n, T, D).copy()
-        e4 = w.fmt == "e4m3"
+        e4 = w.fmt in ("e4m3", "f16")       # fp16 attention GEMMs
         if e4:       # fp16 QKV with fp16 accumulators, 16 steps of 16 (csrc/encoder.cu:1366-1368)
             qkv = add_f16(_mma_f16acc(xn, lw.q_qkv.astype(F16).T), lw.b_qkv[None, :])
         else:
@@ -406,8 +409,22 @@ def forward(w: Weights, boards, control, rep, legal=None, trace: Optional[Trace]
         xn = layernorm(reinject(w, x, boards, control, rep, li * 2 + 1) if w.rj_mode == 2 else x)
         if first:
             trace.stages[3] = xn.reshape(n, T, D).copy()
-        qa, sa = quantise_rows_e4m3(xn) if e4 else quantise_rows(xn)
+        if w.fmt == "f16":
+            # fp16 FFN (csrc/encoder.cu:1431-1556 without quantisation): ff1 per chunk with fp16
+            # accumulators, + bias, ReLU; the ff2 accumulators run on through all four chunks
+            ff = None
+            for c in range(DFF // 256):
+                hid = add_f16(_mma_f16acc(xn, lw.q_ff1[256 * c:256 * c + 256].astype(F16).T),
+                              lw.b_ff1[None, 256 * c:256 * c + 256])
+                hid = np.maximum(hid, F16(0))
+                ff = _mma_f16acc(hid, lw.q_ff2[:, 256 * c:256 * c + 256].astype(F16).T, acc=ff)
+            x = add_f16(x, add_f16(ff, lw.b_ff2[None, :]))
+            if trace is not None:
+                trace.by_layer[(li, 10)] = x.reshape(n, T, D).copy()
+            continue
+        qa, sa = quantise_rows_e4m3(xn) if w.fmt == "e4m3" else quantise_rows(xn)
         run = np.zeros((n * T, D), dtype=F16)
+        e4 = w.fmt == "e4m3"
         for c in range(DFF // 256):
             acc = gemm_int(qa, lw.q_ff1[256 * c:256 * c + 256])
             if not e4:

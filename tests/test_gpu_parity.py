@@ -571,3 +571,34 @@ def test_a_wait_that_nothing_satisfies_times_out_and_reports():
     assert L.bf_selftest_timeout(0, 0, ctypes.byref(status), None) != 0
     x = torch.ones(8, device="cuda")
     assert float(x.sum()) == 8.0
+
+
+def test_fp16_arithmetic_against_the_oracle_and_the_fp32_network(nets, states, pos256):
+    """`FusedEncoder(net, int8=False)` against the oracle's fp16 restatement (same roundings up
+    to the hardware's exp and the order inside a tensor-core step): logits within 1 % of
+    max|logit|; and within 1 % of the reference fp32 network's committed outputs (fp16 arithmetic
+    has no quantisation noise)."""
+    import os
+    from conftest import GOLDEN
+    from brokefish_b200.nn import encoder_impl
+    enc = encoder_impl("cuda")(nets["A"], int8=False)
+    enc.exact_rsqrt = True
+    w = O.prepare({k: v.numpy() for k, v in states["A"].items()}, fmt="f16")
+    sl = slice(0, 64)
+    tr = O.Trace()
+    opol, opro, oval = O.forward(w, pos256["boards"][sl], pos256["control"][sl], pos256["rep"][sl], trace=tr)
+    got = enc.forward_stage(*inputs(pos256, sl), 1).cpu().numpy()
+    assert np.array_equal(got.view(np.uint16), tr.stages[1].view(np.uint16))
+    pol, pro, val = (t.cpu().numpy() for t in enc.forward_full(*inputs(pos256, sl)))
+    enc.check_status()
+    top = float(np.abs(opol.astype(np.float32)).max())
+    assert np.abs(pol.astype(np.float32) - opol.astype(np.float32)).max() <= 0.01 * max(1.0, top)
+    assert np.abs(val - oval).max() <= 5e-3
+    g = np.load(os.path.join(GOLDEN, "ref_outputs_A.npz"))
+    n = g["fp32_policy"].shape[0]
+    assert np.abs(pol[:n].astype(np.float32) - g["fp32_policy"]).max() <= 0.01 * np.abs(g["fp32_policy"]).max()
+    # determinism and independence of what shares the launch
+    a = enc.forward_full(*inputs(pos256, slice(5, 5 + 33)))[0].cpu().numpy().copy()
+    b = enc.forward_full(*inputs(pos256, slice(0, 64)))[0].cpu().numpy()[5:38]
+    assert np.array_equal(a.view(np.uint16), b.view(np.uint16))
+    enc.close()

@@ -189,6 +189,26 @@ def test_e4m3_path_against_reference_kernel(pos256):
     enc.close()
 
 
+def test_fp16_arithmetic_is_bit_identical_to_the_reference_kernel(pos256, pos4096):
+    """`FusedEncoder(net, int8=False)`: the reference's default arithmetic, every weight GEMM fp16
+    x fp16.  tcgen05 `kind::f16` with fp16 accumulators carries the bits of the reference's
+    fp16-accumulate mma.sync, and the ff2 accumulators run through the four hidden chunks as the
+    reference's do, so every stage and every output is equal to the bit."""
+    if not R.available("A_f16"):
+        pytest.skip("slabs missing")
+    enc, ref = product(SETS["A"], int8=False), R.RefKernel("A_f16")
+    assert ref.quant == 0 and enc.quant == 0 and enc.label.startswith("fp16")
+    sl = slice(0, 200)
+    for stage in (9, 1, 5, 6, 7, 4, 2, 3, 8):
+        got = enc.forward_stage(*inputs(pos256, sl), stage).cpu().numpy()
+        want = ref.forward_stage(*inputs(pos256, sl), stage).cpu().numpy()
+        assert same_bits(got, want), stage
+    for pos, sl in ((pos256, slice(3, 3 + 77)), (pos4096, slice(0, 4096))):
+        (pol, pro, val), (rpol, rpro, rval) = run_both(enc, ref, pos, sl)
+        assert same_bits(pol, rpol) and same_bits(pro, rpro) and np.abs(val - rval).max() <= 1e-6
+    enc.close()
+
+
 def test_timing_report(pos4096):
     """Not a bar: prints both kernels' device time on the 4096-position batch (CUDA events, 5
     warm-ups, 20 timed launches each) so the summary under profiles/ can be reproduced with
@@ -214,6 +234,9 @@ def test_timing_report(pos4096):
     enc.close()
     enc = product(SETS["A"], fp8=True)
     rows.append(("product e4m3 FFN", ms(lambda: enc.forward_full(*args))))
+    enc.close()
+    enc = product(SETS["A"], int8=False)
+    rows.append(("product fp16", ms(lambda: enc.forward_full(*args))))
     enc.close()
     for tag, label in (("A_int8", "reference kernel int8 (all four GEMMs, two boards per CTA)"),
                        ("A_f16", "reference kernel fp16"), ("A_e4m3", "reference kernel e4m3 FFN")):

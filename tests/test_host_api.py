@@ -31,8 +31,6 @@ def test_constructor_refusals(nets):
     with pytest.raises(ValueError):
         FusedEncoder(net, fp8=True, int8=True)
     with pytest.raises(NotImplementedError):
-        FusedEncoder(net, int8=False)
-    with pytest.raises(NotImplementedError):
         FusedEncoder(net, int8_scheme="ffn")
     with pytest.raises(ValueError):
         FusedEncoder(net, int8_scheme="nope")
