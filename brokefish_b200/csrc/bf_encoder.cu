@@ -1441,15 +1441,19 @@ __device__ __forceinline__ void mma_loop(uint32_t smem, uint32_t tmem, volatile 
             mma_unit<kAr>(smem, abort_flag, st, acc1, 1, sm_a, false, C::kAttnSlabs, kI_OUT, kAttnKind);
             mma_wait_operand(smem, abort_flag, B_A_READY, st.aready);          // LN2 output
             if constexpr (kAr == kArF16) {
-                // fp16 FFN: per hidden chunk two ff1 units into slot 0, then, once the rows
-                // have written the chunk, the two ff2 units, whose accumulators (the idle
+                // fp16 FFN: ff1 units go into slot 0; once the rows have written a hidden chunk,
+                // its two ff2 units follow, whose accumulators (the idle
                 // attention-output columns for half 0, slot 1 for half 1) run on through all
                 // four chunks; one commit per chunk on accumulator barrier 1 tells the rows
                 // that the hidden buffer is free again, the last one that the sums are done
+                // issue order (= the packed weight order): F1 c0 j0, F1 c0 j1, then per chunk c:
+                // F1 c+1 j0 (so that it runs under the rows' epilogue of F1 c j1), F2 c j0, F2 c j1,
+                // F1 c+1 j1
+                mma_unit<kAr>(smem, abort_flag, st, acc0, 0, sm_a, false, 4, kI_FF1, kKindF16);
+                mma_unit<kAr>(smem, abort_flag, st, acc0, 0, sm_a, false, 4, kI_FF1, kKindF16);
 #pragma unroll 1
                 for (int ch = 0; ch < 4; ++ch) {
-                    mma_unit<kAr>(smem, abort_flag, st, acc0, 0, sm_a, false, 4, kI_FF1, kKindF16);
-                    mma_unit<kAr>(smem, abort_flag, st, acc0, 0, sm_a, false, 4, kI_FF1, kKindF16);
+                    if (ch < 3) mma_unit<kAr>(smem, abort_flag, st, acc0, 0, sm_a, false, 4, kI_FF1, kKindF16);
                     mma_wait_operand(smem, abort_flag, B_A2_READY, st.a2n[0]);
                     if (ch == 0) {
                         mbar_wait(bar_addr(smem, B_ACC_EMPTY + 1), (st.accn[1] - 1u) & 1u, abort_flag, kErrMmaAcc);
@@ -1473,6 +1477,7 @@ __device__ __forceinline__ void mma_loop(uint32_t smem, uint32_t tmem, volatile 
                         }
                     }
                     tc_commit(bar_addr(smem, B_ACC_FULL + 1));
+                    if (ch < 3) mma_unit<kAr>(smem, abort_flag, st, acc0, 0, sm_a, false, 4, kI_FF1, kKindF16);
                 }
                 st.accn[1]++;
             } else {

@@ -201,18 +201,25 @@ def _layer_stream(fl: FoldedLayer) -> np.ndarray:
             parts.append(sw128_image(np.ascontiguousarray(
                 fl.q_o[128 * u:128 * u + 128, 128 * s:128 * s + 128])))
     if fl.q_ff1.shape[1] == 512:
-        # fp16 FFN: per hidden chunk the two ff1 units then the two ff2 units, 4 K-slabs of 64
-        # halves each (the ff2 accumulators run on through the chunks, so its units follow the
-        # chunk order)
+        # fp16 FFN: units of 4 K-slabs of 64 halves each; the ff2 accumulators run on through
+        # the chunks, so its units follow the chunk order
+        def ff1_unit(c, j):
+            return [sw128_image(np.ascontiguousarray(
+                fl.q_ff1[256 * c + 128 * j:256 * c + 128 * j + 128, 128 * s:128 * s + 128])) for s in range(4)]
+
+        def ff2_unit(c, j):
+            return [sw128_image(np.ascontiguousarray(
+                fl.q_ff2[128 * j:128 * j + 128, 512 * c + 128 * s:512 * c + 128 * s + 128])) for s in range(4)]
+
+        # issue order of the MMA schedule: F1 c0 j0, F1 c0 j1, then per chunk c: F1 c+1 j0,
+        # F2 c j0, F2 c j1, F1 c+1 j1
+        parts += ff1_unit(0, 0) + ff1_unit(0, 1)
         for c in range(4):
-            for j in range(2):
-                for s in range(4):
-                    parts.append(sw128_image(np.ascontiguousarray(
-                        fl.q_ff1[256 * c + 128 * j:256 * c + 128 * j + 128, 128 * s:128 * s + 128])))
-            for j in range(2):
-                for s in range(4):
-                    parts.append(sw128_image(np.ascontiguousarray(
-                        fl.q_ff2[128 * j:128 * j + 128, 512 * c + 128 * s:512 * c + 128 * s + 128])))
+            if c < 3:
+                parts += ff1_unit(c + 1, 0)
+            parts += ff2_unit(c, 0) + ff2_unit(c, 1)
+            if c < 3:
+                parts += ff1_unit(c + 1, 1)
     else:
         for kind, c, j in FFN_UNITS:
             for s in range(2):
