@@ -602,3 +602,34 @@ def test_fp16_arithmetic_against_the_oracle_and_the_fp32_network(nets, states, p
     b = enc.forward_full(*inputs(pos256, slice(0, 64)))[0].cpu().numpy()[5:38]
     assert np.array_equal(a.view(np.uint16), b.view(np.uint16))
     enc.close()
+
+
+def test_the_parity_checks_bite(nets, pos256):
+    """A validator nobody has watched fail is an assertion, not a measurement (the reference's
+    tests/test_validate.py): flip one weight byte, one scale bit or one bias bit in the packed
+    blob and the outputs must move; an untouched copy of the blob must reproduce them exactly."""
+    import struct
+    from brokefish_b200.nn.cuda_impl import FusedEncoder
+    from brokefish_b200.nn.pack import pack_blob
+    blob = pack_blob(nets["A"])
+    args = inputs(pos256, slice(0, 64))
+    base_enc = FusedEncoder.from_blob(blob.copy())
+    base = [t.clone() for t in base_enc.forward_full(*args)]
+    base_enc.close()
+    off_w, bytes_w, off_lp = struct.unpack_from("<QQQ", blob, 32)
+    mutants = {"weight byte, layer 5": off_w + 5 * 786432 + 123457,
+               "weight scale, layer 2 ff1": off_lp + 2 * 4736 + 32 + 2,
+               "bias, layer 7 ff2": off_lp + 7 * 4736 + 4224 + 11}
+    for what, at in mutants.items():
+        m = blob.copy()
+        m[at] ^= 0x10
+        enc = FusedEncoder.from_blob(m)
+        pol = enc.forward_full(*args)[0]
+        assert not torch.equal(pol.view(torch.int16), base[0].view(torch.int16)), what
+        enc.close()
+    again = FusedEncoder.from_blob(blob.copy())
+    out = again.forward_full(*args)
+    assert all(torch.equal(a.view(torch.int32) if a.dtype == torch.float32 else a.view(torch.int16),
+                           b.view(torch.int32) if b.dtype == torch.float32 else b.view(torch.int16))
+               for a, b in zip(out, base))
+    again.close()
