@@ -35,6 +35,7 @@
 #include <string>
 
 #include "../../include/brokefish_b200.h"
+#include "bf_movegen.cuh"
 #include "bf_ptx.cuh"
 
 namespace bf {
@@ -1264,9 +1265,15 @@ __device__ __forceinline__ void row_warps_tile(RowCtx& c, const Params& p, int t
             lg[i] = v;
         }
         if (c.valid && p.policy != nullptr) store_words<8>(p.policy + c.grow * 64 + 16 * c.qt, lg);
-        if (p.prior != nullptr && c.qt == 1)
-            expand_board(p, board, c.lane, c.valid, word, ctl, p.legal != nullptr && c.valid ? lw : 0ull,
-                         stage_pol, stage_aux, c.row);
+        if (p.prior != nullptr && c.qt == 1) {
+            // without legality words from the caller the warp generates them itself (lane = slot)
+            unsigned long long moves = 0ull;
+            if (c.valid) {
+                bool in_check;
+                moves = p.legal != nullptr ? lw : bfmg::legal_word(word, ctl, in_check);
+            }
+            expand_board(p, board, c.lane, c.valid, word, ctl, moves, stage_pol, stage_aux, c.row);
+        }
         if (c.qt == 0) {
             if (c.valid && p.promo != nullptr)
                 *reinterpret_cast<uint2*>(p.promo + c.grow * 4) = make_uint2(aux[0], aux[1]);
@@ -1943,12 +1950,26 @@ int bf_forward(bf_handle* h, const uint16_t* boards, const int16_t* control, con
 int bf_forward_priors(bf_handle* h, const uint16_t* boards, const int16_t* control, const uint8_t* rep,
                       const uint64_t* legal, int n, int e_cap, void* prior, int16_t* move, int* nedges,
                       float* value, void* policy, void* promo, void* stream) {
-    if (legal == nullptr) return fail(BF_EINVAL, "the fused expansion needs the legal-move words");
     if (prior == nullptr || move == nullptr || nedges == nullptr) return fail(BF_EINVAL, "prior, move and nedges must be non-null");
     if (e_cap < 1 || e_cap > 255) return fail(BF_EINVAL, "e_cap must be in 1..255");
+    if (legal == nullptr && policy != nullptr)
+        return fail(BF_EINVAL, "the masked policy needs the legality words; pass them or leave policy null");
     const PriorOut po{prior, move, nedges, e_cap};
     return launch(h, boards, control, rep, legal, n, policy, promo, value, nullptr, 0, 0, -1, -1, nullptr,
                   nullptr, static_cast<cudaStream_t>(stream), &po);
+}
+
+int bf_movegen(int device, const uint16_t* boards, const int16_t* control, int n, uint64_t* mask,
+               unsigned char* in_check, void* stream) {
+    if (n < 0) return fail(BF_EINVAL, "n must be >= 0");
+    if (n == 0) return BF_OK;
+    if (boards == nullptr || control == nullptr || mask == nullptr)
+        return fail(BF_EINVAL, "boards, control and mask must be non-null");
+    BF_CUDA(cudaSetDevice(device));
+    bfmg::movegen_kernel<<<(n + 3) / 4, 128, 0, static_cast<cudaStream_t>(stream)>>>(
+        boards, control, n, reinterpret_cast<unsigned long long*>(mask), in_check);
+    BF_CUDA(cudaGetLastError());
+    return BF_OK;
 }
 
 int bf_forward_stage_at(bf_handle* h, const uint16_t* boards, const int16_t* control,

@@ -243,14 +243,17 @@ class FusedEncoder:
         nedges [n] int32, value [n] fp32)`` — the edges of each position's search node in
         canonical order with their priors, what the reference's search computes from the
         logits in ``Search._expand`` (brokefish/search/torch_impl.py:962-1033).  ``legal`` is
-        the ``[n,32]`` int64 legality words.  With ``logits=True`` the masked policy and the
+        the ``[n,32]`` int64 legality words, or ``None`` to let the kernel generate the legal
+        moves itself (the rules of :func:`brokefish_b200.env.movegen`).  With ``logits=True`` the masked policy and the
         promotion logits are written as well (``self.policy_out``, ``self.promo_out``).
         Returns views on internal buffers, which the next call overwrites."""
         self._require_net("forward_priors")
         n = self._check_inputs(boards, control, rep)
         self._check_device(boards, control, rep, legal)
-        if legal is None or tuple(legal.shape) != (n, self.T) or legal.dtype is not torch.int64:
-            raise ValueError(f"legal must be [{n}, 32] int64")
+        if legal is not None and (tuple(legal.shape) != (n, self.T) or legal.dtype is not torch.int64):
+            raise ValueError(f"legal must be [{n}, 32] int64 or None")
+        if legal is None and logits:
+            raise ValueError("the masked policy needs the legality words; pass them or leave logits off")
         if not 1 <= int(e_cap) <= 255:
             raise ValueError(f"e_cap must be in 1..255, got {e_cap}")
         self._ensure_full_buffers(n)
@@ -260,7 +263,8 @@ class FusedEncoder:
             self.move_out = torch.zeros(n, int(e_cap), device=dev, dtype=torch.int16)
             self.nedges_out = torch.zeros(n, device=dev, dtype=torch.int32)
             self._prior_shape = (n, int(e_cap))
-        b, c, r, lg = boards.contiguous(), control.contiguous(), rep.contiguous(), legal.contiguous()
+        b, c, r = boards.contiguous(), control.contiguous(), rep.contiguous()
+        lg = legal.contiguous() if legal is not None else None
         stream = ctypes.c_void_p(torch.cuda.current_stream(self.device).cuda_stream)
         _native.check(_native.lib().bf_forward_priors(
             self._handle, _ptr(b), _ptr(c), _ptr(r), _ptr(lg), n, int(e_cap), _ptr(self.prior_out),

@@ -76,8 +76,8 @@ int bf_forward(bf_handle* h, const uint16_t* boards, const int16_t* control,
 /* Evaluate and expand in one launch: besides (optionally) the logits, write for every position
  * the edges of its search node and their priors, which the reference's search derives in a
  * kernel of its own from the logits (`Search._expand`, brokefish/search/torch_impl.py:962-1033;
- * `expand_node`, csrc/search.cuh:593-798).  `legal` [n,32] is required (bit s of word p: the
- * piece in slot p may move to square s).  Outputs, caller-owned device memory:
+ * `expand_node`, csrc/search.cuh:593-798).  `legal` [n,32]: bit s of word p says the piece in
+ * slot p may move to square s.  Outputs, caller-owned device memory:
  *   prior  [n, e_cap] fp16   softmax over the node's candidates (policy logit, plus for a pawn
  *                            reaching its last rank log_softmax of its four promotion logits);
  *                            more than e_cap candidates: the e_cap largest stay (ties to the
@@ -86,10 +86,21 @@ int bf_forward(bf_handle* h, const uint16_t* boards, const int16_t* control,
  *   nedges [n] int32         edges written (0 for a position without a legal move)
  *   value  [n] fp32          as bf_forward; policy / promo may be NULL to skip the 4.3 KB per
  *                            position logit stream (when given, policy carries the legality AND)
- * e_cap is 1..255 (the reference's search uses 96). */
+ * e_cap is 1..255 (the reference's search uses 96).  `legal` may be NULL: the kernel then
+ * generates the legal moves itself from the boards (bf_movegen's rules), policy must be NULL. */
 int bf_forward_priors(bf_handle* h, const uint16_t* boards, const int16_t* control, const uint8_t* rep,
                       const uint64_t* legal, int n, int e_cap, void* prior, int16_t* move, int* nedges,
                       float* value, void* policy, void* promo, void* stream);
+
+/* Legal-move generation for `n` boards (device pointers): `mask` [n,32] 64-bit words, bit s of
+ * word p set when the piece in slot p may legally move to square s (a promotion is one bit,
+ * castling the king's two-square move, en passant a pawn's diagonal move to an empty square);
+ * `in_check` [n] (may be NULL) for the side to move.  The engine contract of the reference's
+ * `movegen` (brokefish/env/torch_impl.py:254-291; csrc/movegen.cuh): the input generator of the
+ * evaluator's legality words and of the search's node masks.  One warp per board, one launch on
+ * `stream`; needs no handle. */
+int bf_movegen(int device, const uint16_t* boards, const int16_t* control, int n, uint64_t* mask,
+               unsigned char* in_check, void* stream);
 
 /* Activations at an intermediate stage as [n,32,256] fp16.  Replaces
  * `model_forward(..., debug_stage=stage)` (csrc/encoder.cu:1315-1427, 1575-1598):

@@ -21,6 +21,9 @@ next to this script:
   (``Search.root_init`` -> ``_expand``) derives from its fp32 network's fp16 logits on 160
   non-terminal positions, at edge caps 96 and 12, and the reference validator's metrics on a
   perturbed copy of those logits;
+* ``ref_movegen.npz`` -- the reference move generator's legal words and check flags on 17
+  hand-picked positions (its adversarial FENs, castling, en passant, pins, mates), and its check
+  flags for the two playout sets;
 * ``scheme_kats.npz`` -- known answers of the reference's int8 scheme functions.
 
 The fixtures are what ``tests/test_oracle_golden.py`` pins the CPU oracle against; the
@@ -210,6 +213,37 @@ def main() -> int:
                                        dl.edge_set_differs, dl.max_abs_logit, dl.nonfinite,
                                        dl.max_abs_value], dtype=np.float64)
     np.savez_compressed(os.path.join(HERE, "ref_priors.npz"), **out)
+
+    # the engine's move generator on positions no random playout reaches (the adversarial FENs
+    # of brokefish/nn/validate.py:81-87 plus castling, en passant, pins and checks) and the check
+    # flag of the two playout sets (their legal words are already in the position files)
+    print("movegen known answers", flush=True)
+    fens = [f for _, f in __import__("brokefish.nn.validate", fromlist=["ADVERSARIAL"]).ADVERSARIAL] + [
+        "r3k2r/pppppppp/8/8/8/8/PPPPPPPP/R3K2R w KQkq - 0 1",
+        "r3k2r/8/8/8/8/8/8/R3K2R b KQkq - 0 1",
+        "r3k2r/8/8/8/8/8/6r1/R3K2R w KQkq - 0 1",          # g1 / f1 covered: no short castle
+        "4k3/8/8/8/8/8/8/R3K2r w Q - 0 1",                  # in check: no castle
+        "rnbqkbnr/ppp1p1pp/8/3pPp2/8/8/PPPP1PPP/RNBQKBNR w KQkq f6 0 3",   # en passant available
+        "8/8/8/8/k2Pp2Q/8/8/4K3 b - d3 0 1",                # en passant would expose the king
+        "4k3/8/8/8/8/4r3/4B3/4K3 w - - 0 1",                # pinned bishop
+        "4k3/8/8/8/8/8/3n4/4K3 w - - 0 1",                  # knight check
+        "7k/5Q2/6K1/8/8/8/8/8 b - - 0 1",                   # stalemate
+        "7k/6Q1/6K1/8/8/8/8/8 b - - 0 1",                   # checkmate
+        "8/2P5/8/8/8/8/5p2/K2k4 w - - 0 1",                 # promotions for both sides
+        "8/2P5/8/8/8/8/5p2/K2k4 b - - 0 1",
+    ]
+    fb, fc = zip(*(env.from_fen(f) for f in fens))
+    fb, fc = torch.cat(fb), torch.cat(fc)
+    fm, fchk = env.movegen(fb, fc)
+    out = {"fen_boards": fb.numpy().astype(np.int16), "fen_control": fc.numpy().astype(np.int16),
+           "fen_legal": fm.numpy().astype(np.int64).view(np.uint64), "fen_in_check": fchk.numpy(),
+           "fens": np.array(fens)}
+    for n_pos, seed in ((256, 0), (4096, 1)):
+        z = np.load(os.path.join(HERE, f"positions_{n_pos}_seed{seed}.npz"))
+        m, chk = env.movegen(torch.from_numpy(z["boards"]), torch.from_numpy(z["control"]))
+        assert np.array_equal(m.numpy().astype(np.int64).view(np.uint64), z["legal"])
+        out[f"in_check_{n_pos}"] = chk.numpy()
+    np.savez_compressed(os.path.join(HERE, "ref_movegen.npz"), **out)
 
     print("scheme known answers", flush=True)
     g = torch.Generator().manual_seed(1234)

@@ -1,0 +1,91 @@
+"""The move generator (brokefish_b200/csrc/bf_movegen.cuh, C ABI bf_movegen) against the
+reference engine's own answers, committed under tests/golden/ by make_golden.py: the legal words
+of 4352 random-playout positions (0-120 plies: captures, castling, en passant, promotions,
+checks, mates) and of 17 hand-picked positions, and the check flags.  Bit-exact."""
+import os
+
+import numpy as np
+import pytest
+import torch
+
+from conftest import GOLDEN
+
+
+@pytest.fixture(scope="module")
+def gold():
+    z = np.load(os.path.join(GOLDEN, "ref_movegen.npz"))
+    return {k: z[k] for k in z.files}
+
+
+def popcount(words):
+    return np.array([bin(int(w)).count("1") for w in np.asarray(words).reshape(-1)]).reshape(np.asarray(words).shape)
+
+
+def test_golden_answers_are_the_known_move_counts(gold):
+    """The fixture itself: 218 moves in the maximum-mobility position, 20 from the start
+    position, mate and stalemate have none, and the hand-picked cases say what they should."""
+    counts = popcount(gold["fen_legal"]).sum(-1)
+    fens = list(gold["fens"])
+    by = {f.split()[0] + " " + f.split()[1]: int(c) for f, c in zip(fens, counts)}
+    assert by["R6R/3Q4/1Q4Q1/4Q3/2Q4Q/Q4Q2/pp1Q4/kBNN1KB1 w"] == 218
+    assert by["rnbqkbnr/pppppppp/8/8/8/8/PPPPPPPP/RNBQKBNR w"] == 20
+    assert by["7k/5Q2/6K1/8/8/8/8/8 b"] == 0 and by["7k/6Q1/6K1/8/8/8/8/8 b"] == 0
+    chk = dict(zip(fens, gold["fen_in_check"]))
+    assert not chk["7k/5Q2/6K1/8/8/8/8/8 b - - 0 1"] and chk["7k/6Q1/6K1/8/8/8/8/8 b - - 0 1"]
+    # white castles both ways from the bare position: the king's word has bits 2 and 6 set
+    i = fens.index("r3k2r/pppppppp/8/8/8/8/PPPPPPPP/R3K2R w KQkq - 0 1")
+    king = gold["fen_legal"][i][15]
+    assert (int(king) >> 6) & 1 and (int(king) >> 2) & 1
+    # rook on g2 covers g1 and f1... the short castle is gone, the long one stays
+    i = fens.index("r3k2r/8/8/8/8/8/6r1/R3K2R w KQkq - 0 1")
+    king = gold["fen_legal"][i][15]
+    assert not (int(king) >> 6) & 1 and (int(king) >> 2) & 1
+    # the en passant capture that would expose the king is not there
+    i = fens.index("8/8/8/8/k2Pp2Q/8/8/4K3 b - d3 0 1")
+    assert all(not (int(w) >> 19) & 1 for w in gold["fen_legal"][i])
+
+
+@pytest.mark.gpu
+def test_movegen_equals_the_reference_engine(gold, pos256, pos4096):
+    from brokefish_b200.env import movegen
+    cases = [(gold["fen_boards"], gold["fen_control"], gold["fen_legal"], gold["fen_in_check"]),
+             (pos256["boards"], pos256["control"], pos256["legal"], gold["in_check_256"]),
+             (pos4096["boards"], pos4096["control"], pos4096["legal"], gold["in_check_4096"])]
+    for boards, control, legal, in_check in cases:
+        b = torch.from_numpy(np.ascontiguousarray(boards)).cuda()
+        c = torch.from_numpy(np.ascontiguousarray(control)).cuda()
+        mask, chk = movegen(b, c)
+        got = mask.cpu().numpy().view(np.uint64)
+        bad = np.argwhere(got != legal)
+        assert bad.size == 0, (bad[:5], [hex(int(got[tuple(i)])) for i in bad[:3]], [hex(int(legal[tuple(i)])) for i in bad[:3]])
+        assert np.array_equal(chk.cpu().numpy(), in_check.astype(bool))
+    assert in_check.any() and (popcount(pos256["legal"]).sum(-1) == 0).any()      # checks and mates occur
+    # an empty batch and wrong inputs
+    m, k = movegen(b[:0], c[:0])
+    assert m.shape == (0, 32) and k.shape == (0,)
+    with pytest.raises(ValueError):
+        movegen(b.cpu(), c.cpu())
+
+
+@pytest.mark.gpu
+def test_fused_expansion_generates_its_own_moves(pos4096):
+    """`forward_priors` without legality words: the kernel's expansion warp generates them (lane
+    = slot) and the result equals the call that was given the engine's words."""
+    from brokefish_b200.nn import encoder_impl
+    from brokefish_b200.nn.model import BrokefishNet, seeded_state
+    net = BrokefishNet().eval()
+    net.load_state_dict(seeded_state(seed=0, std=None, perturb_norms=True))
+    n = 1111
+    t = lambda a: torch.from_numpy(np.ascontiguousarray(a[:n])).cuda()
+    boards, control, rep = t(pos4096["boards"]), t(pos4096["control"]), t(pos4096["rep"])
+    legal = torch.from_numpy(pos4096["legal"][:n].view(np.int64).copy()).cuda()
+    enc = encoder_impl("cuda")(net)
+    for cap in (96, 12):
+        want = [x.clone() for x in enc.forward_priors(boards, control, rep, legal, cap)]
+        got = [x.clone() for x in enc.forward_priors(boards, control, rep, None, cap)]
+        assert torch.equal(got[0].view(torch.int16), want[0].view(torch.int16))
+        assert torch.equal(got[1], want[1]) and torch.equal(got[2], want[2]) and torch.equal(got[3], want[3])
+    enc.check_status()
+    with pytest.raises(ValueError):
+        enc.forward_priors(boards, control, rep, None, 96, logits=True)
+    enc.close()
