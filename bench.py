@@ -160,6 +160,9 @@ def main() -> int:
     ap.add_argument("--batch", type=int, default=4096, help="positions per GPU per step")
     ap.add_argument("--total", type=int, default=0,
                     help="fixed number of positions per step split across the GPUs")
+    ap.add_argument("--playouts", action="store_true",
+                    help="play this rank's positions on the device (random games from the start position, "
+                         "seed 100 + rank) instead of tiling the committed 4096")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--sweep", action="store_true", help="print one line per batch size 1..65536 and exit")
     ap.add_argument("--phases", action="store_true",
@@ -218,6 +221,13 @@ def main() -> int:
     else:
         n_local, n_global, scaling = args.batch, args.batch * world, "weak"
         b, c, r, lg = load_positions(args.batch)
+    data = "synthetic"
+    if args.playouts:
+        from brokefish_b200.env import random_playouts
+        pb, pc, pr, pl, _ = random_playouts(n_local, 100 + rank, device=dev)
+        b, c, r = pb.cpu().numpy(), pc.cpu().numpy(), pr.cpu().numpy()
+        lg = pl.cpu().numpy().view(np.uint64)
+        data = f"synthetic: {n_local} random-playout positions per rank played on the device, seed 100 + rank"
     d_b, d_c, d_r = (torch.from_numpy(np.ascontiguousarray(a)).to(dev) for a in (b, c, r))
     flush = torch.empty(256 << 20, dtype=torch.uint8, device=dev)     # > 126 MB L2
 
@@ -307,7 +317,7 @@ def main() -> int:
         "steps": args.steps, "warmup": warmup, "ms_per_step": dev_ms / args.steps,
         "higher_is_better": True, "scaling": scaling, "vs_baseline": None,
         "dtype": "e4m3 (FFN) + f16" if args.fp8 else ("f16" if args.f16 else "s8"),
-        "data": "synthetic",
+        "data": data,
         "config": {"workload": WORKLOAD, "positions_per_step": n_global, "parallelism": f"dp{world}",
                    "l2": "flushed between timed iterations (256 MiB fill)",
                    "timing": "CUDA events per launch on the launching stream, summed; max over ranks",

@@ -28,7 +28,7 @@ EXPORTS = ["bf_version", "bf_last_error", "bf_create", "bf_destroy", "bf_info", 
            "bf_forward_stage", "bf_forward_stage_at", "bf_forward_capture", "bf_forward_host", "bf_status",
            "bf_launch_count", "bf_profile", "bf_profile_read", "bf_profile_phases",
            "bf_forward_noalloc", "bf_noalloc_status", "bf_selftest_umma", "bf_set_option", "bf_measure_i8_peak", "bf_forward_priors",
-           "bf_forward_priors_host", "bf_selftest_timeout", "bf_movegen"]
+           "bf_forward_priors_host", "bf_selftest_timeout", "bf_movegen", "bf_step", "bf_random_ply"]
 
 
 def nvcc_path() -> str:
@@ -89,6 +89,8 @@ def lib() -> ctypes.CDLL:
     L.bf_forward_priors.argtypes = [vp, vp, vp, vp, vp, i32, i32, vp, vp, vp, vp, vp, vp, vp]
     L.bf_selftest_timeout.argtypes = [i32, i32, ctypes.POINTER(i32), ctypes.POINTER(ctypes.c_longlong)]
     L.bf_movegen.argtypes = [i32, vp, vp, i32, vp, vp, vp]
+    L.bf_random_ply.argtypes = [i32, vp, vp, vp, vp, vp, i32, vp, vp]
+    L.bf_step.argtypes = [i32, vp, vp, vp, vp, i32, vp, vp, vp, vp, vp, vp]
     L.bf_forward_priors_host.argtypes = [vp, vp, vp, vp, vp, i32, i32, vp, vp, vp, vp]
     L.bf_measure_i8_peak.argtypes = [i32, i32, ctypes.POINTER(ctypes.c_double), ctypes.POINTER(ctypes.c_double)]
     L.bf_launch_count.argtypes = [vp]

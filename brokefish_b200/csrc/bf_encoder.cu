@@ -1972,6 +1972,34 @@ int bf_movegen(int device, const uint16_t* boards, const int16_t* control, int n
     return BF_OK;
 }
 
+int bf_step(int device, const uint16_t* boards, const int16_t* control, const int* move,
+            const signed char* promo, int n, uint16_t* boards_out, int16_t* control_out,
+            unsigned char* irreversible, uint64_t* mask, unsigned char* in_check, void* stream) {
+    if (n < 0) return fail(BF_EINVAL, "n must be >= 0");
+    if (n == 0) return BF_OK;
+    if (boards == nullptr || control == nullptr || move == nullptr || boards_out == nullptr || control_out == nullptr)
+        return fail(BF_EINVAL, "boards, control, move, boards_out and control_out must be non-null");
+    BF_CUDA(cudaSetDevice(device));
+    bfmg::step_kernel<<<(n + 3) / 4, 128, 0, static_cast<cudaStream_t>(stream)>>>(
+        boards, control, move, promo, n, boards_out, control_out, irreversible,
+        reinterpret_cast<unsigned long long*>(mask), in_check);
+    BF_CUDA(cudaGetLastError());
+    return BF_OK;
+}
+
+int bf_random_ply(int device, uint16_t* boards, int16_t* control, uint64_t* mask, const float* r,
+                  const signed char* promo, int n, int* move, void* stream) {
+    if (n < 0) return fail(BF_EINVAL, "n must be >= 0");
+    if (n == 0) return BF_OK;
+    if (boards == nullptr || control == nullptr || mask == nullptr || r == nullptr)
+        return fail(BF_EINVAL, "boards, control, mask and r must be non-null");
+    BF_CUDA(cudaSetDevice(device));
+    bfmg::random_ply_kernel<<<(n + 3) / 4, 128, 0, static_cast<cudaStream_t>(stream)>>>(
+        boards, control, reinterpret_cast<unsigned long long*>(mask), r, promo, n, move);
+    BF_CUDA(cudaGetLastError());
+    return BF_OK;
+}
+
 int bf_forward_stage_at(bf_handle* h, const uint16_t* boards, const int16_t* control,
                         const uint8_t* rep, int n, int layer, int stage, void* y, void* stream) {
     if (h == nullptr) return fail(BF_EINVAL, "null handle");

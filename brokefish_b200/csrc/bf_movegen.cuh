@@ -179,6 +179,141 @@ __device__ __forceinline__ unsigned long long legal_word(unsigned word, int cont
     return legal;
 }
 
+// Castling rights of a board in FEN order KQkq as four bits (torch_impl.py:294-318): the king
+// and that corner's rook are alive and have never moved.  Warp-collective.
+__device__ __forceinline__ unsigned castling_bits(unsigned word) {
+    const bool intact = ((word >> 11) & 1u) == 0u && ((word >> 9) & 1u) == 0u;
+    const bool is_black = (word >> 10) & 1u;
+    const int type = (word >> 6) & 7, sq = word & 63;
+    const unsigned wk = __ballot_sync(kFull, intact && type == KING && !is_black) != 0u;
+    const unsigned bk = __ballot_sync(kFull, intact && type == KING && is_black) != 0u;
+    const bool rook = intact && type == ROOK;
+    const unsigned k = __ballot_sync(kFull, rook && !is_black && sq == 7) != 0u;
+    const unsigned q = __ballot_sync(kFull, rook && !is_black && sq == 0) != 0u;
+    const unsigned k2 = __ballot_sync(kFull, rook && is_black && sq == 63) != 0u;
+    const unsigned q2 = __ballot_sync(kFull, rook && is_black && sq == 56) != 0u;
+    return (wk & k) | ((wk & q) << 1) | ((bk & k2) << 2) | ((bk & q2) << 3);
+}
+
+// Apply one move (`move` = slot * 64 + target, -1 = no move; `promo` 0..3 = N B R Q, negative =
+// queen) to a board, lane = slot: the reference's `step` without its hash
+// (brokefish/env/torch_impl.py:412-548).  Returns this slot's new word; `new_control` and
+// `irreversible` (capture, pawn move or a change of castling rights) are the same on every lane.
+__device__ __forceinline__ unsigned step_word(unsigned word, int control, int move, int promo, int lane,
+                                              int& new_control, bool& irreversible) {
+    new_control = control;
+    irreversible = false;
+    if (move < 0) return word;
+    const int source = move >> 6, target = move & 63;
+    const bool white = control > 0;
+    const unsigned mover = __shfl_sync(kFull, word, source);
+    const int mtype = (mover >> 6) & 7, from = mover & 63;
+    const bool is_pawn = mtype == PAWN;
+    const unsigned rights_before = castling_bits(word);
+    // capture: a live piece on the target square, or for a pawn the en passant victim, which
+    // carries the double-step flag and stands beside the target's file neighbour, not on it
+    const bool live = ((word >> 11) & 1u) == 0u;
+    const unsigned victim_word = ((white ? 3u : 1u) << 9) + static_cast<unsigned>(target + (white ? -8 : 8));
+    const bool hit = (live && static_cast<int>(word & 63u) == target) || (is_pawn && word == victim_word);
+    const unsigned hits = __ballot_sync(kFull, hit);
+    const bool has_capture = hits != 0u;
+    unsigned w = word;
+    if (has_capture && lane == __ffs(hits) - 1) w = 1u << 11;
+    // castling: the rook on the king's side corner jumps over (found before any square changes)
+    const int dx = target - from;
+    const bool castling = mtype == KING && (dx == 2 || dx == -2);
+    const int corner = (white ? 0 : 56) + (dx > 0 ? 7 : 0);
+    const unsigned rooks = __ballot_sync(kFull, ((w >> 6) & 7u) == ROOK && static_cast<int>(word & 63u) == corner);
+    if (lane == source) {
+        w = (w & ~63u & 0xFFFu) + static_cast<unsigned>(target);
+        if (is_pawn && (target >> 3) == (white ? 7 : 0))
+            w += static_cast<unsigned>(promo < 0 ? QUEEN : promo + KNIGHT) << 6;
+        if (mtype == KING || mtype == ROOK) w |= 1u << 9;
+    }
+    if (castling && rooks != 0u && lane == __ffs(rooks) - 1)
+        w = (w & ~63u & 0xFFFu) + static_cast<unsigned>((white ? 0 : 56) + (dx > 0 ? 5 : 3));
+    // the en passant flag lives for one ply: clear every pawn's, set the double-stepper's
+    if (((w >> 6) & 7u) == PAWN) w &= ~(1u << 9) & 0xFFFu;
+    if (lane == source && is_pawn && (dx == 16 || dx == -16)) w |= 1u << 9;
+    const int mag = (has_capture || is_pawn) ? 1 : (control < 0 ? -control : control) + 1;
+    new_control = white ? -mag : mag;
+    irreversible = has_capture || is_pawn || castling_bits(w) != rights_before;
+    return w;
+}
+
+// One warp per board: play `move` (with `promo`), then generate the legal moves of the result.
+__global__ void __launch_bounds__(128) step_kernel(const uint16_t* __restrict__ boards,
+                                                   const int16_t* __restrict__ control,
+                                                   const int* __restrict__ move, const signed char* __restrict__ promo,
+                                                   int n, uint16_t* __restrict__ boards_out,
+                                                   int16_t* __restrict__ control_out,
+                                                   unsigned char* __restrict__ irreversible,
+                                                   unsigned long long* __restrict__ mask,
+                                                   unsigned char* __restrict__ in_check) {
+    const int board = blockIdx.x * 4 + (threadIdx.x >> 5), lane = threadIdx.x & 31;
+    if (board >= n) return;
+    int nc;
+    bool irr;
+    const unsigned w = step_word(boards[static_cast<size_t>(board) * 32 + lane], control[board], move[board],
+                                 promo != nullptr ? promo[board] : -1, lane, nc, irr);
+    boards_out[static_cast<size_t>(board) * 32 + lane] = static_cast<uint16_t>(w);
+    if (lane == 0) {
+        control_out[board] = static_cast<int16_t>(nc);
+        if (irreversible != nullptr) irreversible[board] = irr ? 1 : 0;
+    }
+    if (mask != nullptr) {
+        bool chk;
+        const unsigned long long m = legal_word(w, nc, chk);
+        mask[static_cast<size_t>(board) * 32 + lane] = m;
+        if (in_check != nullptr && lane == 0) in_check[board] = chk ? 1 : 0;
+    }
+}
+
+// One warp per board: one ply of a uniform-random playout, in place.  The move is the
+// floor(r * count)-th legal move in (slot, square) order (r in [0,1), product in fp32), the board
+// is stepped and its new legal moves replace `mask`; a board without legal moves stays as it is
+// and reports move -1.
+__global__ void __launch_bounds__(128) random_ply_kernel(uint16_t* __restrict__ boards, int16_t* __restrict__ control,
+                                                         unsigned long long* __restrict__ mask,
+                                                         const float* __restrict__ r,
+                                                         const signed char* __restrict__ promo, int n,
+                                                         int* __restrict__ move_out) {
+    const int board = blockIdx.x * 4 + (threadIdx.x >> 5), lane = threadIdx.x & 31;
+    if (board >= n) return;
+    unsigned long long m = mask[static_cast<size_t>(board) * 32 + lane];
+    const int cnt = __popcll(m);
+    int incl = cnt;
+#pragma unroll
+    for (int d = 1; d < 32; d <<= 1) {
+        const int v = __shfl_up_sync(kFull, incl, d);
+        if (lane >= d) incl += v;
+    }
+    const int total = __shfl_sync(kFull, incl, 31);
+    int move = -1;
+    if (total > 0) {
+        int pick = static_cast<int>(__fmul_rn(r[board], static_cast<float>(total)));
+        pick = pick < total - 1 ? pick : total - 1;
+        const int k = pick - (incl - cnt);
+        const unsigned owners = __ballot_sync(kFull, k >= 0 && k < cnt);
+        const int owner = __ffs(owners) - 1;
+        int bit = 0;
+        if (lane == owner) {
+            for (int i = 0; i < k; ++i) m &= m - 1ull;
+            bit = __ffsll(static_cast<long long>(m)) - 1;
+        }
+        move = owner * 64 + __shfl_sync(kFull, bit, owner);
+    }
+    if (move_out != nullptr && lane == 0) move_out[board] = move;
+    if (move < 0) return;
+    int nc;
+    bool irr, chk;
+    const unsigned w = step_word(boards[static_cast<size_t>(board) * 32 + lane], control[board], move,
+                                 promo != nullptr ? promo[board] : -1, lane, nc, irr);
+    boards[static_cast<size_t>(board) * 32 + lane] = static_cast<uint16_t>(w);
+    if (lane == 0) control[board] = static_cast<int16_t>(nc);
+    mask[static_cast<size_t>(board) * 32 + lane] = legal_word(w, nc, chk);
+}
+
 // One warp per board.
 __global__ void __launch_bounds__(128) movegen_kernel(const uint16_t* __restrict__ boards,
                                                       const int16_t* __restrict__ control, int n,

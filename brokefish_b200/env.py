@@ -3,8 +3,11 @@
 ``movegen(boards, control) -> (mask, in_check)`` with the reference's contract
 (brokefish/env/torch_impl.py:254-291): ``mask [n,32]`` int64, bit ``s`` of word ``p`` set when
 the piece in slot ``p`` may legally move to square ``s``; ``in_check [n]`` bool for the side
-to move.  One warp per board in ``libbrokefish_b200`` (C ABI ``bf_movegen``); CUDA tensors in,
-CUDA tensors out, on the current stream.  There is no CPU path.
+to move.  ``step`` and ``play`` apply a move per board (torch_impl.py:412-548, 680-685; the
+position hash is not tracked), ``initial_boards`` is the start position (torch_impl.py:692-697)
+and ``random_playouts`` plays uniform-random games to make evaluator inputs.  One warp per board
+in ``libbrokefish_b200`` (C ABI ``bf_movegen``, ``bf_step``, ``bf_random_ply``); CUDA tensors
+in, CUDA tensors out, on the current stream.  There is no CPU path.
 """
 
 from __future__ import annotations
@@ -34,3 +37,91 @@ def movegen(boards: torch.Tensor, control: torch.Tensor):
             dev.index or 0, ctypes.c_void_p(b.data_ptr()), ctypes.c_void_p(c.data_ptr()), n,
             ctypes.c_void_p(mask.data_ptr()), ctypes.c_void_p(in_check.data_ptr()), stream), "bf_movegen")
     return mask, in_check.bool()
+
+
+def _ptr(t):
+    return ctypes.c_void_p(t.data_ptr()) if t is not None else None
+
+
+def _check_position(boards, control):
+    n = boards.shape[0]
+    if boards.dim() != 2 or boards.shape[1] != 32 or boards.dtype is not torch.int16:
+        raise ValueError(f"boards must be [n, 32] int16, got {tuple(boards.shape)} {boards.dtype}")
+    if tuple(control.shape) != (n,) or control.dtype is not torch.int16:
+        raise ValueError(f"control must be [{n}] int16, got {tuple(control.shape)} {control.dtype}")
+    if not (boards.is_cuda and control.is_cuda and boards.device == control.device):
+        raise ValueError("the engine kernels take CUDA tensors on one device; there is no CPU path")
+    return n
+
+
+def initial_boards(n: int = 1, device="cuda"):
+    """``n`` copies of the start position, white to move (brokefish/env/torch_impl.py:692-697).
+    Slots: white pawns a-h, knights, bishops, rooks, queen, king, then black in the same order."""
+    squares = list(range(8, 16)) + [1, 6, 2, 5, 0, 7, 3, 4]
+    types = [0] * 8 + [1, 1, 2, 2, 3, 3, 4, 5]
+    white = [(t << 6) | s for t, s in zip(types, squares)]
+    black = [(1 << 10) | (t << 6) | (s ^ 56) for t, s in zip(types, squares)]
+    start = torch.tensor(white + black, dtype=torch.int16, device=device)
+    return start.unsqueeze(0).expand(n, -1).clone(), torch.ones(n, dtype=torch.int16, device=device)
+
+
+def step(boards, control, move, promo=None, with_moves: bool = False):
+    """Apply ``move [n]`` (``slot * 64 + target``, -1 = no move) with ``promo [n]`` (0..3 =
+    N B R Q, default queen): ``(boards, control, None, irreversible)`` as the reference's
+    ``step`` returns them when no hash is tracked (brokefish/env/torch_impl.py:412-548).  With
+    ``with_moves`` the new positions' ``(mask, in_check)`` are generated in the same launch and
+    appended.  Moves are not checked for legality."""
+    n = _check_position(boards, control)
+    dev = boards.device
+    if tuple(move.shape) != (n,) or not move.is_cuda:
+        raise ValueError(f"move must be a CUDA tensor of shape [{n}]")
+    mv = move.to(torch.int32).contiguous()
+    pr = promo.to(device=dev, dtype=torch.int8).contiguous() if promo is not None else None
+    if pr is not None and tuple(pr.shape) != (n,):
+        raise ValueError(f"promo must have shape [{n}]")
+    nb = torch.empty(n, 32, dtype=torch.int16, device=dev)
+    nc = torch.empty(n, dtype=torch.int16, device=dev)
+    irr = torch.zeros(n, dtype=torch.uint8, device=dev)
+    mask = torch.zeros(n, 32, dtype=torch.int64, device=dev) if with_moves else None
+    chk = torch.zeros(n, dtype=torch.uint8, device=dev) if with_moves else None
+    if n:
+        b, c = boards.contiguous(), control.contiguous()
+        stream = ctypes.c_void_p(torch.cuda.current_stream(dev).cuda_stream)
+        _native.check(_native.lib().bf_step(dev.index or 0, _ptr(b), _ptr(c), _ptr(mv), _ptr(pr), n, _ptr(nb),
+                                            _ptr(nc), _ptr(irr), _ptr(mask), _ptr(chk), stream), "bf_step")
+    out = (nb, nc, None, irr.bool())
+    return out + (mask, chk.bool()) if with_moves else out
+
+
+def play(boards, control, move, promo=None):
+    """``step`` then ``movegen`` in one launch: ``(boards, control, mask, in_check)``
+    (brokefish/env/torch_impl.py:680-685)."""
+    nb, nc, _, _, mask, chk = step(boards, control, move, promo, with_moves=True)
+    return nb, nc, mask, chk
+
+
+def random_playouts(n: int, seed: int, max_plies: int = 120, device="cuda"):
+    """``n`` uniform-random legal games from the start position, game ``i`` stopped after
+    ``plies[i]`` moves (uniform in 0..max_plies) or at its end: ``(boards, control, rep, legal,
+    plies)`` with ``rep = i % 3``.  The random draws come from a CPU generator seeded with
+    ``seed`` in a fixed order (plies; then per ply one fp32 uniform and one promotion type per
+    game), so the positions depend on ``seed`` alone; the rules run on the GPU, one launch per
+    ply."""
+    dev = torch.device(device)
+    gen = torch.Generator(device="cpu").manual_seed(seed)
+    plies = torch.randint(0, max_plies + 1, (n,), generator=gen)
+    boards, control = initial_boards(n, dev)
+    mask, _ = movegen(boards, control)
+    left = plies.to(dev)
+    out_b, out_c, out_m = boards.clone(), control.clone(), mask.clone()
+    lib, stream = _native.lib(), ctypes.c_void_p(torch.cuda.current_stream(dev).cuda_stream)
+    for ply in range(max_plies):
+        r = torch.rand(n, generator=gen).to(dev)
+        promo = torch.randint(0, 4, (n,), generator=gen).to(device=dev, dtype=torch.int8)
+        if n:
+            _native.check(lib.bf_random_ply(dev.index or 0, _ptr(boards), _ptr(control), _ptr(mask), _ptr(r),
+                                            _ptr(promo), n, None, stream), "bf_random_ply")
+        snap = left == ply + 1
+        out_b[snap], out_c[snap], out_m[snap] = boards[snap], control[snap], mask[snap]
+    rep = (torch.arange(n, device=dev) % 3).to(torch.uint8)
+    return out_b, out_c, rep, out_m, plies

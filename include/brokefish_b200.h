@@ -102,6 +102,29 @@ int bf_forward_priors(bf_handle* h, const uint16_t* boards, const int16_t* contr
 int bf_movegen(int device, const uint16_t* boards, const int16_t* control, int n, uint64_t* mask,
                unsigned char* in_check, void* stream);
 
+/* Play one move per board (device pointers): `move` [n] int32 = slot * 64 + target square, -1
+ * leaves the board as it is; `promo` [n] int8 (may be NULL = queen) 0..3 = knight, bishop, rook,
+ * queen.  Writes the new piece words (in place when boards_out == boards), the new control word
+ * (side flipped; magnitude = the fifty-move counter, 1 after a capture or pawn move) and, when
+ * non-NULL, `irreversible` [n] (capture, pawn move or a change of castling rights) -- the
+ * reference's `step` without its position hash (brokefish/env/torch_impl.py:412-548;
+ * csrc/movegen.cuh).  When `mask` is non-NULL the legal moves of the NEW position follow in the
+ * same launch (bf_movegen's outputs), which is one ply of a self-play loop.  Moves are not
+ * checked for legality.  One warp per board; needs no handle. */
+int bf_step(int device, const uint16_t* boards, const int16_t* control, const int* move,
+            const signed char* promo, int n, uint16_t* boards_out, int16_t* control_out,
+            unsigned char* irreversible, uint64_t* mask, unsigned char* in_check, void* stream);
+
+/* One ply of a uniform-random playout, in place (device pointers): from `mask` (the legal moves
+ * of `boards`, bf_movegen's output) the floor(r[i] * count)-th legal move in (slot, square) order
+ * is played with promotion type `promo[i]` (may be NULL = queen), and `mask` becomes the legal
+ * moves of the new position; a board without legal moves is left alone.  `move` [n] int32 (may
+ * be NULL) receives the move played or -1.  No single counterpart: the body of the reference's
+ * random-playout loops (tests and benchmarks drive `movegen` + `play`,
+ * brokefish/env/torch_impl.py:254-291, 412-548), here the generator of benchmark positions. */
+int bf_random_ply(int device, uint16_t* boards, int16_t* control, uint64_t* mask, const float* r,
+                  const signed char* promo, int n, int* move, void* stream);
+
 /* Activations at an intermediate stage as [n,32,256] fp16.  Replaces
  * `model_forward(..., debug_stage=stage)` (csrc/encoder.cu:1315-1427, 1575-1598):
  * 9 embedding; layer 0: 1 LN1 out, 5/6/7 Q/K/V after bias, 4 attention out,

@@ -81,16 +81,80 @@ def playout_positions(env, n: int, seed: int, max_plies: int = 120):
             rep.numpy(), out_m.numpy().astype(np.int64).view(np.uint64), plies.numpy())
 
 
+def step_answers(env) -> None:
+    """The engine's `step` / `play` on one random legal move (random promotion type) from each of
+    the 4096 playout positions -- every 16th board gets the null move -- and on hand-picked
+    castling, en passant and promotion moves: new words, control, the irreversible flag and the
+    next position's legal words and check flag."""
+    z = np.load(os.path.join(HERE, "positions_4096_seed1.npz"))
+    boards, control = torch.from_numpy(z["boards"]), torch.from_numpy(z["control"])
+    mask = torch.from_numpy(z["legal"].view(np.int64))
+    n = boards.shape[0]
+    gen = torch.Generator(device="cpu").manual_seed(7)
+    legal = env.bitset_to_bool(mask).reshape(n, 32 * 64)
+    counts = legal.sum(dim=1)
+    pick = torch.minimum((torch.rand(n, generator=gen) * counts.clamp(min=1).float()).long(), (counts - 1).clamp(min=0))
+    move = (legal.cumsum(dim=1) > pick[:, None]).float().argmax(dim=1)
+    move = torch.where((counts > 0) & (torch.arange(n) % 16 != 5), move, torch.full_like(move, -1))
+    promo = torch.randint(0, 4, (n,), generator=gen)
+    nb, nc, _, irr = env.step(boards, control, move, promo=promo)
+    nm, chk = env.movegen(nb, nc)
+    out = {"move": move.numpy().astype(np.int32), "promo": promo.numpy().astype(np.int8),
+           "boards": nb.numpy().astype(np.int16), "control": nc.numpy().astype(np.int16),
+           "irreversible": irr.numpy(), "legal": nm.numpy().astype(np.int64).view(np.uint64),
+           "in_check": chk.numpy()}
+    # hand-picked: (FEN, from, to, promotion type or -1 for the default)
+    sq = lambda name: (ord(name[0]) - 97) + 8 * (int(name[1]) - 1)
+    cases = [("r3k2r/pppppppp/8/8/8/8/PPPPPPPP/R3K2R w KQkq - 0 1", "e1", "g1", -1),
+             ("r3k2r/pppppppp/8/8/8/8/PPPPPPPP/R3K2R w KQkq - 0 1", "e1", "c1", -1),
+             ("r3k2r/8/8/8/8/8/8/R3K2R b KQkq - 0 1", "e8", "g8", -1),
+             ("r3k2r/8/8/8/8/8/8/R3K2R b KQkq - 0 1", "e8", "c8", -1),
+             ("r3k2r/8/8/8/8/8/8/R3K2R b KQkq - 5 9", "a8", "a1", -1),       # rook takes rook: both lose rights
+             ("r3k2r/8/8/8/8/8/8/R3K2R w KQkq - 5 9", "h1", "h4", -1),       # quiet rook move: a right goes
+             ("rnbqkbnr/ppp1p1pp/8/3pPp2/8/8/PPPP1PPP/RNBQKBNR w KQkq f6 0 3", "e5", "f6", -1),
+             ("rnbqkbnr/ppp1p1pp/8/3pPp2/8/8/PPPP1PPP/RNBQKBNR w KQkq f6 0 3", "e5", "e6", -1),
+             ("rnbqkbnr/pppppppp/8/8/8/8/PPPPPPPP/RNBQKBNR w KQkq - 0 1", "e2", "e4", -1),
+             ("rnbqkbnr/pppppppp/8/8/8/8/PPPPPPPP/RNBQKBNR w KQkq - 0 1", "g1", "f3", -1),
+             ("8/2P5/8/8/8/8/5p2/K2k4 w - - 0 1", "c7", "c8", -1),
+             ("8/2P5/8/8/8/8/5p2/K2k4 w - - 0 1", "c7", "c8", 0),
+             ("8/2P5/8/8/8/8/5p2/K2k4 w - - 0 1", "c7", "c8", 1),
+             ("8/2P5/8/8/8/8/5p2/K2k4 b - - 0 1", "f2", "f1", 2),
+             ("8/2P5/8/8/8/8/5p2/K2k4 b - - 0 1", "f2", "f1", 3),
+             ("4k3/8/8/8/8/8/8/4K2R w K - 12 30", "e1", "e2", -1)]           # quiet king move: the counter goes up
+    fb, fc, fmv, fpr = [], [], [], []
+    for fen, a, b, pr in cases:
+        bb, cc = env.from_fen(fen)
+        slot = int((((bb[0] & 63) == sq(a)) & ((bb[0] >> 11) == 0)).int().argmax())
+        fb.append(bb); fc.append(cc); fmv.append(slot * 64 + sq(b)); fpr.append(3 if pr < 0 else pr)
+    fb, fc = torch.cat(fb), torch.cat(fc)
+    fmv, fpr = torch.tensor(fmv), torch.tensor(fpr)
+    legal_before, _ = env.movegen(fb, fc)
+    ok = (legal_before[torch.arange(len(cases)), fmv // 64] >> (fmv % 64)) & 1
+    assert bool(ok.all()), "a hand-picked move is not legal"
+    hb, hc, _, hirr = env.step(fb, fc, fmv, promo=fpr)
+    hm, hchk = env.movegen(hb, hc)
+    out.update({"case_boards_in": fb.numpy().astype(np.int16), "case_control_in": fc.numpy().astype(np.int16),
+                "case_move": fmv.numpy().astype(np.int32), "case_promo": fpr.numpy().astype(np.int8),
+                "case_boards": hb.numpy().astype(np.int16), "case_control": hc.numpy().astype(np.int16),
+                "case_irreversible": hirr.numpy(), "case_legal": hm.numpy().astype(np.int64).view(np.uint64),
+                "case_in_check": hchk.numpy(), "cases": np.array([f"{f} {a}{b}" for f, a, b, _ in cases])})
+    np.savez_compressed(os.path.join(HERE, "ref_step.npz"), **out)
+
+
 def main() -> int:
     ap = argparse.ArgumentParser()
     ap.add_argument("--reference", default="/root/reference")
     ap.add_argument("--skip-positions", action="store_true")
+    ap.add_argument("--only-step", action="store_true", help="write ref_step.npz and stop")
     args = ap.parse_args()
     sys.path.insert(0, args.reference)
     sys.dont_write_bytecode = True
     torch.manual_seed(0)
 
     from brokefish.env import torch_impl as env                      # reference
+    if args.only_step:
+        step_answers(env)
+        return 0
     from brokefish.nn import quant as rq                             # reference
     from brokefish.nn.cuda_impl import _fold_norm                    # reference
     from brokefish.nn.model import BrokefishNet as RefNet            # reference
@@ -244,6 +308,9 @@ def main() -> int:
         assert np.array_equal(m.numpy().astype(np.int64).view(np.uint64), z["legal"])
         out[f"in_check_{n_pos}"] = chk.numpy()
     np.savez_compressed(os.path.join(HERE, "ref_movegen.npz"), **out)
+
+    print("step known answers", flush=True)
+    step_answers(env)
 
     print("scheme known answers", flush=True)
     g = torch.Generator().manual_seed(1234)

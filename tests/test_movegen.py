@@ -89,3 +89,71 @@ def test_fused_expansion_generates_its_own_moves(pos4096):
     with pytest.raises(ValueError):
         enc.forward_priors(boards, control, rep, None, 96, logits=True)
     enc.close()
+
+
+@pytest.fixture(scope="module")
+def gold_step():
+    z = np.load(os.path.join(GOLDEN, "ref_step.npz"))
+    return {k: z[k] for k in z.files}
+
+
+def test_step_fixture_covers_the_special_moves(gold_step, pos4096):
+    """The reference's answers themselves: castling moves the rook too, en passant removes the
+    pawn beside the target, promotions take the asked type, the null move changes nothing."""
+    g = gold_step
+    cases = list(g["cases"])
+    i = cases.index("r3k2r/pppppppp/8/8/8/8/PPPPPPPP/R3K2R w KQkq - 0 1 e1g1")
+    assert (g["case_boards"][i][15] & 63) == 6 and (g["case_boards"][i][13] & 63) == 5
+    i = cases.index("rnbqkbnr/ppp1p1pp/8/3pPp2/8/8/PPPP1PPP/RNBQKBNR w KQkq f6 0 3 e5f6")
+    assert (g["case_boards"][i] == 0x800).sum() == (g["case_boards_in"][i] == 0x800).sum() + 1
+    types = [(int(g["case_boards"][i][g["case_move"][i] >> 6]) >> 6) & 7
+             for i, c in enumerate(cases) if c.endswith("w - - 0 1 c7c8")]
+    assert types == [4, 1, 2]
+    null = g["move"] < 0
+    assert null.sum() > 200 and np.array_equal(g["boards"][null], pos4096["boards"][null])
+    assert not g["irreversible"][null].any() and 0.2 < g["irreversible"].mean() < 0.5
+    assert not g["case_irreversible"][cases.index("rnbqkbnr/pppppppp/8/8/8/8/PPPPPPPP/RNBQKBNR w KQkq - 0 1 g1f3")]
+
+
+@pytest.mark.gpu
+def test_step_and_play_equal_the_reference_engine(gold_step, pos4096):
+    from brokefish_b200.env import play, step
+    g = gold_step
+    cu = lambda a: torch.from_numpy(np.ascontiguousarray(a)).cuda()
+    sets = [(pos4096["boards"], pos4096["control"], g["move"], g["promo"], g["boards"], g["control"],
+             g["irreversible"], g["legal"], g["in_check"]),
+            (g["case_boards_in"], g["case_control_in"], g["case_move"], g["case_promo"], g["case_boards"],
+             g["case_control"], g["case_irreversible"], g["case_legal"], g["case_in_check"])]
+    for b0, c0, mv, pr, b1, c1, irr, legal, chk in sets:
+        nb, nc, h, ir = step(cu(b0), cu(c0), cu(mv), cu(pr))
+        assert h is None
+        assert np.array_equal(nb.cpu().numpy(), b1) and np.array_equal(nc.cpu().numpy(), c1)
+        assert np.array_equal(ir.cpu().numpy(), irr.astype(bool))
+        pb, pc, pm, pk = play(cu(b0), cu(c0), cu(mv).long(), cu(pr))
+        assert torch.equal(pb, nb) and torch.equal(pc, nc)
+        assert np.array_equal(pm.cpu().numpy().view(np.uint64), legal)
+        assert np.array_equal(pk.cpu().numpy(), chk.astype(bool))
+    # the default promotion is the queen (the hand-picked set asks for 3 where it wants the default)
+    q = g["case_promo"] == 3
+    nb2, _, _, _ = step(cu(g["case_boards_in"][q]), cu(g["case_control_in"][q]), cu(g["case_move"][q]))
+    assert np.array_equal(nb2.cpu().numpy(), g["case_boards"][q])
+    with pytest.raises(ValueError):
+        step(cu(b0), cu(c0), cu(mv)[:3])
+
+
+@pytest.mark.gpu
+def test_random_playouts_on_the_gpu_reproduce_the_reference_made_position_files(pos256, pos4096):
+    """Up to 120 plies of movegen -> pick -> step chained on the device, with the random draws of
+    the fixture script: the positions and their legal words come out equal to the files the
+    reference engine wrote, and the start position is the reference's."""
+    from brokefish_b200.env import initial_boards, random_playouts
+    for pos, n, seed in ((pos256, 256, 0), (pos4096, 4096, 1)):
+        b, c, rep, legal, plies = random_playouts(n, seed)
+        assert np.array_equal(plies.numpy(), pos["plies"])
+        assert np.array_equal(b.cpu().numpy(), pos["boards"])
+        assert np.array_equal(c.cpu().numpy(), pos["control"])
+        assert np.array_equal(rep.cpu().numpy(), pos["rep"])
+        assert np.array_equal(legal.cpu().numpy().view(np.uint64), pos["legal"])
+    i = int(np.argmax(pos256["plies"] == 0))
+    sb, sc = initial_boards(2)
+    assert np.array_equal(sb[1].cpu().numpy(), pos256["boards"][i]) and int(sc[0]) == 1
