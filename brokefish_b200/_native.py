@@ -18,7 +18,7 @@ ROOT = os.path.dirname(PKG_DIR)
 #: The in-tree library; ``BROKEFISH_B200_LIB`` points the loader at another build of it.
 LIB_PATH = os.environ.get("BROKEFISH_B200_LIB") or os.path.join(PKG_DIR, "libbrokefish_b200.so")
 SOURCES = [os.path.join(PKG_DIR, "csrc", "bf_encoder.cu")]
-DEPS = SOURCES + [os.path.join(PKG_DIR, "csrc", "bf_ptx.cuh"),
+DEPS = SOURCES + [os.path.join(PKG_DIR, "csrc", "bf_ptx.cuh"), os.path.join(PKG_DIR, "csrc", "bf_movegen.cuh"),
                   os.path.join(ROOT, "include", "brokefish_b200.h")]
 NVCC_FLAGS = ["-gencode", "arch=compute_100a,code=sm_100a", "-O3", "-lineinfo", "-std=c++17",
               "-Xcompiler", "-fPIC", "-shared", "-diag-suppress", "177,550"]
@@ -28,7 +28,8 @@ EXPORTS = ["bf_version", "bf_last_error", "bf_create", "bf_destroy", "bf_info", 
            "bf_forward_stage", "bf_forward_stage_at", "bf_forward_capture", "bf_forward_host", "bf_status",
            "bf_launch_count", "bf_profile", "bf_profile_read", "bf_profile_phases",
            "bf_forward_noalloc", "bf_noalloc_status", "bf_selftest_umma", "bf_set_option", "bf_measure_i8_peak", "bf_forward_priors",
-           "bf_forward_priors_host", "bf_selftest_timeout", "bf_movegen", "bf_step", "bf_random_ply"]
+           "bf_forward_priors_host", "bf_selftest_timeout", "bf_movegen", "bf_step", "bf_random_ply",
+           "bf_forward_leaves"]
 
 
 def nvcc_path() -> str:
@@ -89,6 +90,7 @@ def lib() -> ctypes.CDLL:
     L.bf_forward_priors.argtypes = [vp, vp, vp, vp, vp, i32, i32, vp, vp, vp, vp, vp, vp, vp]
     L.bf_selftest_timeout.argtypes = [i32, i32, ctypes.POINTER(i32), ctypes.POINTER(ctypes.c_longlong)]
     L.bf_movegen.argtypes = [i32, vp, vp, i32, vp, vp, vp]
+    L.bf_forward_leaves.argtypes = [vp] * 7 + [i32] + [vp] * 3 + [i32] + [vp] * 4
     L.bf_random_ply.argtypes = [i32, vp, vp, vp, vp, vp, i32, vp, vp]
     L.bf_step.argtypes = [i32, vp, vp, vp, vp, i32, vp, vp, vp, vp, vp, vp]
     L.bf_forward_priors_host.argtypes = [vp, vp, vp, vp, vp, i32, i32, vp, vp, vp, vp]

@@ -121,6 +121,10 @@ struct Params {
     int cap_layer, cap_op;
     uint8_t* cap_a;
     int32_t* cap_acc;
+    // compacted leaf list (optional): evaluate positions leaf_index[0 .. *leaf_count) of the
+    // staged arrays; `n` is then the capacity (the most the list can hold) the grid was sized for
+    const int* leaf_index;
+    const int* leaf_count;
     int* status;
     unsigned long long* prof;   // 16 phase counters (cycles of warp 0, lane 0 of every CTA) or null
 };
@@ -138,7 +142,8 @@ struct RowCtx {
     uint64_t one2;              // (1.0f, 1.0f) from the launch parameters, opaque to the compiler
     uint32_t full0, full1;      // accumulator slots consumed so far
     long grow;                  // global token row = board * 32 + token
-    bool valid;                 // board < n
+    int n;                      // positions this launch evaluates (the leaf count when a list is given)
+    bool valid;                 // this warp's board exists
     uint32_t word;              // this token's piece word
     int stm, clk, rp;           // board-level embedding indices (side to move, clock, repetition)
     bool prof_on;               // this thread keeps the CTA's phase clock
@@ -1100,8 +1105,11 @@ __device__ __forceinline__ void prenorm_value(RowCtx& c, const Params& p, uint32
 
 template <bool kDbg, bool kRJ, int kAr>
 __device__ __forceinline__ void row_warps_tile(RowCtx& c, const Params& p, int tile) {
-    const int board = tile * 4 + c.q;
-    c.valid = board < p.n;
+    const int item = tile * 4 + c.q;
+    c.valid = item < c.n;
+    // with a leaf list the board is read from, and its outputs written to, its own place in the
+    // staged arrays
+    const int board = (c.valid && p.leaf_index != nullptr) ? __ldg(p.leaf_index + item) : item;
     c.grow = static_cast<long>(board) * kT + c.lane;
     const uint32_t word = c.valid ? p.boards[c.grow] : 0u;
     const uint32_t alive = __ballot_sync(0xffffffffu, ((word >> 11) & 1u) == 0u);
@@ -1536,9 +1544,14 @@ __global__ void __launch_bounds__(kThreads, 1) encoder_kernel(const Params p) {
     tc_fence_after();
     const uint32_t tmem = *tmem_slot;
 
-    const int n_tiles = (p.n + 3) / 4;
+    // the number of positions: the launch's own, or what the device-side leaf count says now
+    // (clamped to the capacity the grid was sized for); every role reads the same word
+    int n_eval = p.n;
+    if (p.leaf_count != nullptr) n_eval = min(max(__ldg(p.leaf_count), 0), p.n);
+    const int n_tiles = (n_eval + 3) / 4;
     if (warp < kRowWarps) {
         RowCtx c;
+        c.n = n_eval;
         c.lane = lane; c.q = warp & 3; c.qt = warp >> 2; c.row = 32 * c.q + lane;
         c.smem = smem; c.smem_gen = sm;
         c.sm_a = smem + Cfg<kAr>::SM_A; c.sm_r = smem + Cfg<kAr>::SM_R;
@@ -1794,11 +1807,15 @@ struct PriorOut {
     int* nedges;
     int e_cap;
 };
+struct LeafList {
+    const int* index;           // device: positions to evaluate, as places in the staged arrays
+    const int* count;           // device: how many of them (read by the kernel when it starts)
+};
 
 int launch(bf_handle* h, const uint16_t* boards, const int16_t* control, const uint8_t* rep,
            const uint64_t* legal, int n, void* policy, void* promo, float* value, void* y, int stage,
            int stage_layer, int cap_layer, int cap_op, uint8_t* cap_a, int32_t* cap_acc, cudaStream_t stream,
-           const PriorOut* po = nullptr) {
+           const PriorOut* po = nullptr, const LeafList* leaves = nullptr) {
     if (h == nullptr) return fail(BF_EINVAL, "null handle");
     if (n < 0) return fail(BF_EINVAL, "n must be >= 0");
     if (n == 0) return BF_OK;
@@ -1827,6 +1844,7 @@ int launch(bf_handle* h, const uint16_t* boards, const int16_t* control, const u
     if (po != nullptr) {
         p.prior = static_cast<__half*>(po->prior); p.move = po->move; p.nedges = po->nedges; p.e_cap = po->e_cap;
     }
+    if (leaves != nullptr) { p.leaf_index = leaves->index; p.leaf_count = leaves->count; }
     const int n_tiles = (n + 3) / 4;
     const int grid = n_tiles < h->sm_count ? n_tiles : h->sm_count;
     // the instrumented instantiation only when a dump, a capture or the phase clock is asked for
@@ -1957,6 +1975,25 @@ int bf_forward_priors(bf_handle* h, const uint16_t* boards, const int16_t* contr
     const PriorOut po{prior, move, nedges, e_cap};
     return launch(h, boards, control, rep, legal, n, policy, promo, value, nullptr, 0, 0, -1, -1, nullptr,
                   nullptr, static_cast<cudaStream_t>(stream), &po);
+}
+
+int bf_forward_leaves(bf_handle* h, const uint16_t* boards, const int16_t* control, const uint8_t* rep,
+                      const uint64_t* legal, const int* leaf_index, const int* leaf_count, int capacity,
+                      void* policy, void* promo, float* value, int e_cap, void* prior, int16_t* move,
+                      int* nedges, void* stream) {
+    if (leaf_index == nullptr || leaf_count == nullptr) return fail(BF_EINVAL, "leaf_index and leaf_count must be non-null");
+    const bool priors = prior != nullptr || move != nullptr || nedges != nullptr;
+    if (priors) {
+        if (prior == nullptr || move == nullptr || nedges == nullptr)
+            return fail(BF_EINVAL, "prior, move and nedges go together");
+        if (e_cap < 1 || e_cap > 255) return fail(BF_EINVAL, "e_cap must be in 1..255");
+        if (legal == nullptr && policy != nullptr)
+            return fail(BF_EINVAL, "the masked policy needs the legality words; pass them or leave policy null");
+    }
+    const PriorOut po{prior, move, nedges, e_cap};
+    const LeafList ll{leaf_index, leaf_count};
+    return launch(h, boards, control, rep, legal, capacity, policy, promo, value, nullptr, 0, 0, -1, -1, nullptr,
+                  nullptr, static_cast<cudaStream_t>(stream), priors ? &po : nullptr, &ll);
 }
 
 int bf_movegen(int device, const uint16_t* boards, const int16_t* control, int n, uint64_t* mask,

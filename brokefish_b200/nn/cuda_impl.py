@@ -273,6 +273,54 @@ class FusedEncoder:
             "bf_forward_priors")
         return self.prior_out, self.move_out, self.nedges_out, self.value_out
 
+    def forward_leaves(self, boards, control, rep, leaf_index, leaf_count, legal=None, e_cap: int = 0):
+        """Evaluate a compacted leaf list: positions ``leaf_index[: leaf_count]`` of the staged
+        arrays, where ``leaf_count`` is a one-element int32 CUDA tensor the kernel reads when it
+        starts (no host synchronisation; clamped to ``len(leaf_index)``) -- the staging interface
+        the reference's retrospective asks for in place of "all B staged leaves, active or not"
+        (brokefish/search/cuda_impl.py:304-320).  A short list runs short: CTAs beyond the
+        count's tiles leave at once.  Returns ``(policy, promo, value)`` sized like the staged
+        arrays, rows not in the list untouched since the last call; with ``e_cap > 0`` the fused
+        expansion runs as well and ``(prior, move, nedges, value)`` is returned (``legal`` words
+        optional as in :meth:`forward_priors`, and the masked policy is written when they are
+        given).  Views on internal buffers."""
+        self._require_net("forward_leaves")
+        n = self._check_inputs(boards, control, rep)
+        self._check_device(boards, control, rep, legal, leaf_index, leaf_count)
+        if leaf_index.dim() != 1 or leaf_index.dtype is not torch.int32 or leaf_index.shape[0] > n:
+            raise ValueError(f"leaf_index must be int32 [k], k <= {n}")
+        if leaf_count.dtype is not torch.int32 or leaf_count.numel() != 1:
+            raise ValueError("leaf_count must be a one-element int32 tensor")
+        if legal is not None and (tuple(legal.shape) != (n, self.T) or legal.dtype is not torch.int64):
+            raise ValueError(f"legal must be [{n}, 32] int64 or None")
+        e_cap = int(e_cap)
+        if not 0 <= e_cap <= 255:
+            raise ValueError(f"e_cap must be in 0..255, got {e_cap}")
+        self._ensure_full_buffers(n)
+        dev = torch.device("cuda", self.device)
+        if e_cap and getattr(self, "_prior_shape", None) != (n, e_cap):
+            self.prior_out = torch.zeros(n, e_cap, device=dev, dtype=torch.half)
+            self.move_out = torch.zeros(n, e_cap, device=dev, dtype=torch.int16)
+            self.nedges_out = torch.zeros(n, device=dev, dtype=torch.int32)
+            self._prior_shape = (n, e_cap)
+        capacity = int(leaf_index.shape[0])
+        if capacity == 0:
+            return ((self.prior_out, self.move_out, self.nedges_out, self.value_out) if e_cap
+                    else (self.policy_out, self.promo_out, self.value_out))
+        b, c, r, li = boards.contiguous(), control.contiguous(), rep.contiguous(), leaf_index.contiguous()
+        lg = legal.contiguous() if legal is not None else None
+        want_policy = not e_cap or lg is not None
+        stream = ctypes.c_void_p(torch.cuda.current_stream(self.device).cuda_stream)
+        _native.check(_native.lib().bf_forward_leaves(
+            self._handle, _ptr(b), _ptr(c), _ptr(r), _ptr(lg), _ptr(li), _ptr(leaf_count), capacity,
+            _ptr(self.policy_out) if want_policy else None, _ptr(self.promo_out) if want_policy else None,
+            _ptr(self.value_out), e_cap, _ptr(self.prior_out) if e_cap else None,
+            _ptr(self.move_out) if e_cap else None, _ptr(self.nedges_out) if e_cap else None, stream),
+            "bf_forward_leaves")
+        if e_cap:
+            return self.prior_out, self.move_out, self.nedges_out, self.value_out
+        return self.policy_out, self.promo_out, self.value_out
+
     def forward_stage(self, boards, control, rep, stage: int, layer: int = 0):
         """Activations ``[n,32,256]`` fp16 at an intermediate stage: 9 embedding; layer 0:
         1 LN1, 5/6/7 Q/K/V, 4 attention output, 2 residual after attention, 3 LN2; 8 final

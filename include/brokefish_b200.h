@@ -92,6 +92,23 @@ int bf_forward_priors(bf_handle* h, const uint16_t* boards, const int16_t* contr
                       const uint64_t* legal, int n, int e_cap, void* prior, int16_t* move, int* nedges,
                       float* value, void* policy, void* promo, void* stream);
 
+/* Evaluate a compacted leaf list: positions leaf_index[0 .. *leaf_count) of the staged arrays
+ * (`boards`, `control`, `rep`, `legal` indexed by place), the count read ON THE DEVICE when the
+ * kernel starts, so the caller needs no host synchronisation to know it.  `capacity` is the most
+ * the list can hold (the grid is sized for it; a larger count is clamped, a negative one is 0);
+ * CTAs beyond the count's tiles leave at once, so a short list runs short.  Every output is
+ * written at the position's own place in the staged arrays (policy [place,32,64], value [place],
+ * prior [place,e_cap] ...); places not in the list are not touched.  Any of policy / promo /
+ * value may be NULL; pass prior, move and nedges (all three, else all NULL) for the fused
+ * expansion of bf_forward_priors.  Two list entries naming the same place race on its outputs
+ * (same values).  No counterpart in the reference, whose search hands the evaluator all B staged
+ * leaves whether active or not (brokefish/search/cuda_impl.py:304-320); this is the interface its
+ * retrospective asks for (docs/journal/2026-08-09-kernel-design-retrospective.md, item 4). */
+int bf_forward_leaves(bf_handle* h, const uint16_t* boards, const int16_t* control, const uint8_t* rep,
+                      const uint64_t* legal, const int* leaf_index, const int* leaf_count, int capacity,
+                      void* policy, void* promo, float* value, int e_cap, void* prior, int16_t* move,
+                      int* nedges, void* stream);
+
 /* Legal-move generation for `n` boards (device pointers): `mask` [n,32] 64-bit words, bit s of
  * word p set when the piece in slot p may legally move to square s (a promotion is one bit,
  * castling the king's two-square move, en passant a pawn's diagonal move to an empty square);
