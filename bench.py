@@ -353,6 +353,28 @@ def main() -> int:
             rf["peak_source"] = ("measured on this GPU in this run: tcgen05.mma kind::i8 loop on resident "
                                  "operands (bf_measure_i8_peak); 2 x measured dense bf16 burst "
                                  "(MEASURED_PEAKS.json) = %.0f; int8 dense nominal 4500" % peak)
+        # the second roof: the time the element-wise arithmetic between the GEMMs needs on the
+        # CUDA cores at the rate the row warps' own device functions reach in isolation
+        # (per position and layer: 32 rows x the widths below; attention, heads and embedding
+        # are not counted, so the floor is an underestimate)
+        if not args.f16 and not args.fp8:
+            widths = {0: 1024, 1: 768 + 256, 2: 1024, 3: 2 * 256, 4: 2 * 256, 5: 256}
+            rates, floor_s = {}, 0.0
+            for block, width in widths.items():
+                eps = ctypes.c_double(0)
+                if _native.lib().bf_measure_elementwise(local, block, 4000, ctypes.byref(eps), None) != 0:
+                    rates = None
+                    break
+                rates[block] = eps.value
+                floor_s += n_local * 8 * 32 * width / eps.value
+            if rates:
+                names = ["ff1_epilogue", "descale_bias", "ff2_step", "norm_statistics", "normalise_quantise", "quantise"]
+                rf["cuda_core_floor"] = {
+                    "ms": floor_s * 1e3, "frac_of_step": floor_s * 1e3 / kern_avg_ms,
+                    "elements_per_ns_per_sm": {names[b]: r / 1e9 / 148 for b, r in rates.items()},
+                    "what": "sum over the element-wise blocks of elements per launch / isolated rate "
+                            "(bf_measure_elementwise: same device functions, operands in shared memory, "
+                            "16 warps per SM, no tensor-memory loads, exchanges or barriers)"}
     if world == 1 and not args.no_cpu_baseline:
         cv, cms, info = cpu_reference(25, 3)
         line["cpu_baseline"] = dict(info, value=cv, unit="positions/s")

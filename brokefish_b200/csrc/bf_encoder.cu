@@ -389,11 +389,16 @@ __device__ __forceinline__ float ln_stage(RowCtx& c, const Params& p, bool final
     // Two lanes ride in one packed register: (x[l][j], x[l+1][j]).
     uint64_t as0 = 0, as1 = 0, aq0 = 0, aq1 = 0;
     __half2 mn = __float2half2_rn(65504.0f), mx = __float2half2_rn(-65504.0f);
-#pragma unroll 1
+    // both halves' loads are issued before the first is used: the second is in flight while
+    // the first is summed
+    uint32_t xa[16], xb2[16];
+    tmem_ld16(c.tm + TM_X + 16 * c.qt, xa);
+    tmem_wait_ld();
+    tmem_ld16(c.tm + TM_X + 64 + 16 * c.qt, xb2);
+#pragma unroll
     for (int u = 0; u < 2; ++u) {
-        uint32_t x[16];
-        tmem_ld16(c.tm + TM_X + 64 * u + 16 * c.qt, x);
-        tmem_wait_ld();
+        if (u == 1) tmem_wait_ld();
+        uint32_t(&x)[16] = u ? xb2 : xa;
         if (kDbg && dump_x && c.valid) store_words<16>(p.y + c.grow * kD + 128 * u + 32 * c.qt, x);
         if (kRJ && site >= 0) reinject32(c, p, site, 128 * u + 32 * c.qt, x);
         uint64_t s2[2], q2[2];
@@ -438,6 +443,8 @@ __device__ __forceinline__ float ln_stage(RowCtx& c, const Params& p, bool final
         sts_f4(xb + 2048u + slot, make_float4(f0, f1, f2, f3));
         sts_f4(xb + 16384u + slot, make_float4(fminf(__low2float(mn), __high2float(mn)),
                                                fmaxf(__low2float(mx), __high2float(mx)), 0.f, 0.f));
+        // the second pass's first half is fetched while the exchange is under way
+        tmem_ld16(c.tm + TM_X + 16 * c.qt, xa);
         board_sync(c);
         float4 S[4], Q[4], M[4];
 #pragma unroll
@@ -476,11 +483,12 @@ __device__ __forceinline__ float ln_stage(RowCtx& c, const Params& p, bool final
     const float sc = amax > 0.f ? __fdiv_rn(amax, kFP8 ? 8.0f : 127.0f) : 1.0f;
     const float inv = __fdiv_rn(1.0f, sc);
     const uint64_t nmean2 = pk2(-mean, -mean), rstd2 = pk2(rstd, rstd);
-#pragma unroll 1
+    tmem_wait_ld();
+    tmem_ld16(c.tm + TM_X + 64 + 16 * c.qt, xb2);
+#pragma unroll
     for (int u = 0; u < 2; ++u) {
-        uint32_t x[16];
-        tmem_ld16(c.tm + TM_X + 64 * u + 16 * c.qt, x);
-        tmem_wait_ld();
+        if (u == 1) tmem_wait_ld();
+        uint32_t(&x)[16] = u ? xb2 : xa;
         const int col = 128 * u + 32 * c.qt;
         if (kRJ && site >= 0) reinject32(c, p, site, col, x);
         if (!final_norm) {
@@ -1578,6 +1586,88 @@ __global__ void __launch_bounds__(kThreads, 1) encoder_kernel(const Params p) {
 }
 
 // ------------------------------------------------------------------------------------------
+// CUDA-core probe: what one SM sustains on the element-wise building blocks of the row warps when
+// nothing else is in the way -- operands in shared memory, sixteen warps resident as in the
+// evaluator, no tensor-memory loads, no exchanges, no barriers.  The same device functions the
+// evaluator calls.  Block 0: ff1 epilogue (s32 -> descale -> bias + ReLU -> row maximum -> u8);
+// 1: descale + bias -> fp16 (QKV and out-projection epilogues); 2: ff2 step (descale, fused add
+// to the fp16 running total); 3: norm statistics (sum, sum of squares, minimum, maximum); 4:
+// normalise -> fp16 -> s8; 5: fp16 -> int8 quantisation alone.  32 elements per thread and pass.
+// The host entry also runs block 0 with eight and with thirty-two warps resident (its blocks 6
+// and 7), which shows how much a different number of row warps could change.
+// ------------------------------------------------------------------------------------------
+template <int kBlock, int kProbeThreads>
+__global__ void __launch_bounds__(kProbeThreads, 1) elementwise_probe_kernel(const __half* bias, float sa, float sw,
+                                                                              float one, int iters, float* out) {
+    extern __shared__ uint32_t probe_sm[];
+    const int tid = threadIdx.x;
+    for (int i = tid; i < 32 * kProbeThreads; i += kProbeThreads) probe_sm[i] = 0x3c003800u + ((i * 2654435761u) >> 20);
+    __syncthreads();
+    const uint64_t one2 = pk2(one, one), sa2 = pk2(sa, sa), sw2 = pk2(sw, sw);
+    float m = 0.f;
+    uint32_t keep = 0;
+    uint64_t sum2 = pk2(0.f, 0.f), sq2 = pk2(0.f, 0.f);
+    __half2 mn = __float2half2_rn(65504.0f), mx = __float2half2_rn(-65504.0f);
+    uint32_t run[16];
+#pragma unroll
+    for (int i = 0; i < 16; ++i) run[i] = 0;
+    for (int it = 0; it < iters; ++it) {
+        uint32_t acc[32], o[16];
+        if (kBlock <= 2) {
+#pragma unroll
+            for (int k = 0; k < 32; ++k) acc[k] = probe_sm[k * kProbeThreads + tid] + it;
+        } else {
+#pragma unroll
+            for (int k = 0; k < 16; ++k) o[k] = probe_sm[k * kProbeThreads + tid] ^ (it & 1);
+        }
+        if (kBlock == 0) {
+            descale<32, true, kAccInt>(acc, sa, sw, bias, o);
+            const float am = amax_h2<16>(o, false);
+            m = fmaxf(m, am);
+            const float inv = 255.0f / fmaxf(am, 1e-3f);
+            const uint4 a = quant16(&o[0], inv, one2), b = quant16(&o[8], inv, one2);
+            keep ^= a.x ^ a.y ^ a.z ^ a.w ^ b.x ^ b.y ^ b.z ^ b.w;
+        } else if (kBlock == 1) {
+            descale<32, false, kAccInt>(acc, sa, sw, bias, o);
+#pragma unroll
+            for (int k = 0; k < 16; ++k) probe_sm[(16 + k) * kProbeThreads + tid] = o[k];
+        } else if (kBlock == 2) {
+#pragma unroll
+            for (int i = 0; i < 16; ++i) {
+                uint64_t f = pk2(static_cast<float>(static_cast<int>(acc[2 * i])),
+                                 static_cast<float>(static_cast<int>(acc[2 * i + 1])));
+                f = fma2(mul2(f, sa2), sw2, h2_to_f2(run[i]));
+                run[i] = f2_to_h2(f);
+            }
+        } else if (kBlock == 3) {
+#pragma unroll
+            for (int i = 0; i < 16; ++i) {
+                const uint64_t f = h2_to_f2(o[i]);
+                sum2 = add2(sum2, f);
+                sq2 = fma2(f, f, sq2);
+                mn = __hmin2(mn, as_h2(o[i]));
+                mx = __hmax2(mx, as_h2(o[i]));
+            }
+        } else if (kBlock == 4) {
+#pragma unroll
+            for (int i = 0; i < 16; ++i) o[i] = f2_to_h2(mul2(add2(h2_to_f2(o[i]), sa2), sw2));
+            const uint4 a = quant16(&o[0], sa, one2), b = quant16(&o[8], sa, one2);
+            keep ^= a.x ^ a.y ^ a.z ^ a.w ^ b.x ^ b.y ^ b.z ^ b.w;
+        } else {
+            const uint4 a = quant16(&o[0], sa, one2), b = quant16(&o[8], sa, one2);
+            keep ^= a.x ^ a.y ^ a.z ^ a.w ^ b.x ^ b.y ^ b.z ^ b.w;
+        }
+    }
+    float a, b, c, d;
+    upk2(sum2, a, b);
+    upk2(sq2, c, d);
+#pragma unroll
+    for (int i = 0; i < 16; ++i) keep ^= run[i];
+    out[blockIdx.x * kProbeThreads + tid] =
+        m + a + b + c + d + __low2float(mn) + __high2float(mx) + __uint_as_float(keep & 0xffu);
+}
+
+// ------------------------------------------------------------------------------------------
 // Tensor-pipe probe: what `tcgen05.mma kind::i8` sustains when nothing else is in the way.
 // One CTA per SM; operands (pseudo-random bytes) sit in shared memory, accumulators in tensor
 // memory; one thread issues `iters` groups of four M=128, N=256, K=32 MMAs back to back into two
@@ -2257,6 +2347,50 @@ int bf_measure_i8_peak(int device, int iters, double* tops, double* ms) {
     if (st != 0) return fail(BF_EDEVICE, "the probe's bounded wait ran out");
     const double ops = 2.0 * 128 * 256 * 32 * 4.0 * iters * prop.multiProcessorCount;
     *tops = ops / (best * 1e-3) / 1e12;
+    if (ms != nullptr) *ms = best;
+    return BF_OK;
+}
+
+int bf_measure_elementwise(int device, int block, int iters, double* elements_per_s, double* ms) {
+    if (elements_per_s == nullptr || iters < 1 || iters > (1 << 22) || block < 0 || block > 7)
+        return fail(BF_EINVAL, "elements_per_s is null, block not in 0..7 or iters out of range");
+    BF_CUDA(cudaSetDevice(device));
+    cudaDeviceProp prop;
+    BF_CUDA(cudaGetDeviceProperties(&prop, device));
+    if (prop.major != 10) return fail(BF_ENOTSUP, "this library needs a compute capability 10.x (sm_100a) device");
+    using Kernel = void (*)(const __half*, float, float, float, int, float*);
+    static const Kernel kernels[8] = {bf::elementwise_probe_kernel<0, 512>, bf::elementwise_probe_kernel<1, 512>,
+                                      bf::elementwise_probe_kernel<2, 512>, bf::elementwise_probe_kernel<3, 512>,
+                                      bf::elementwise_probe_kernel<4, 512>, bf::elementwise_probe_kernel<5, 512>,
+                                      bf::elementwise_probe_kernel<0, 256>, bf::elementwise_probe_kernel<0, 1024>};
+    const int threads = block == 6 ? 256 : (block == 7 ? 1024 : 512);
+    const int kSmem = 32 * threads * 4;
+    BF_CUDA(cudaFuncSetAttribute(kernels[block], cudaFuncAttributeMaxDynamicSharedMemorySize, kSmem));
+    const int sms = prop.multiProcessorCount;
+    __half* bias = nullptr;
+    float* out = nullptr;
+    BF_CUDA(cudaMalloc(&bias, 256));
+    cudaError_t e = cudaMalloc(&out, static_cast<size_t>(sms) * threads * sizeof(float));
+    if (e == cudaSuccess) e = cudaMemset(bias, 0, 256);
+    cudaEvent_t e0 = nullptr, e1 = nullptr;
+    if (e == cudaSuccess) e = cudaEventCreate(&e0);
+    if (e == cudaSuccess) e = cudaEventCreate(&e1);
+    float best = 0.f;
+    for (int rep = 0; rep < 4 && e == cudaSuccess; ++rep) {      // first repetition warms up
+        cudaEventRecord(e0);
+        kernels[block]<<<sms, threads, kSmem>>>(bias, 0.01f, 0.02f, 1.0f, iters, out);
+        cudaEventRecord(e1);
+        e = cudaEventSynchronize(e1);
+        float t = 0.f;
+        if (e == cudaSuccess) e = cudaEventElapsedTime(&t, e0, e1);
+        if (rep > 0 && (best == 0.f || t < best)) best = t;
+    }
+    if (e0) cudaEventDestroy(e0);
+    if (e1) cudaEventDestroy(e1);
+    cudaFree(bias);
+    if (out) cudaFree(out);
+    if (e != cudaSuccess) return fail(BF_ECUDA, cudaGetErrorString(e));
+    *elements_per_s = 32.0 * threads * iters * sms / (best * 1e-3);
     if (ms != nullptr) *ms = best;
     return BF_OK;
 }

@@ -245,6 +245,19 @@ int bf_noalloc_status(int device, int* status);
  * (csrc/fp8_loop.cu; docs/ledger/perf.md:616-647), for the roofline's denominator. */
 int bf_measure_i8_peak(int device, int iters, double* tops, double* ms);
 
+/* The CUDA-core counterpart of bf_measure_i8_peak: elements per second, summed over the SMs, that
+ * the evaluator's own element-wise device functions sustain in isolation (operands in shared
+ * memory, sixteen warps per SM as in the evaluator, no tensor-memory loads, exchanges or
+ * barriers).  `block`: 0 ff1 epilogue (descale, bias + ReLU, row maximum, u8 quantise), 1 descale
+ * + bias to fp16 (QKV / out-projection epilogue), 2 ff2 step (descale + fused add to the fp16
+ * running total), 3 norm statistics, 4 normalise + s8 quantise, 5 fp16 -> int8 quantise alone;
+ * 6 and 7: block 0 again with eight and with thirty-two warps per SM.
+ * With the element counts of one position these give the time the reference's element-wise
+ * arithmetic needs on this GPU however it is scheduled -- the second roof of this kernel.  No
+ * counterpart in the reference beyond its wish for a benchmark that reports achieved against
+ * measured ceilings (docs/journal/2026-08-09-kernel-design-retrospective.md, item 6). */
+int bf_measure_elementwise(int device, int block, int iters, double* elements_per_s, double* ms);
+
 /* Time-out self test; no counterpart in the reference.  A small kernel waits, through the same
  * bounded wait the evaluator's roles use, on an mbarrier that nothing arrives on.  The wait runs
  * out after its cycle limit (about 0.2 s), the kernel returns normally and `*status` receives

@@ -556,6 +556,33 @@ def test_int8_peak_probe_runs_and_is_plausible():
     assert _native.lib().bf_measure_i8_peak(0, 1, ctypes.byref(tops), None) != 0     # iters out of range
 
 
+def test_elementwise_probe_gives_the_cuda_core_roof():
+    """The second roof: the row warps' own element-wise functions in isolation.  The ff1
+    epilogue is the slowest block per element, the norm statistics the fastest, and the time
+    they imply for a 4096-position launch is below the launch's measured time."""
+    from brokefish_b200 import _native
+    L = _native.lib()
+    rate = {}
+    for block in range(6):
+        eps, ms = ctypes.c_double(0), ctypes.c_double(0)
+        assert L.bf_measure_elementwise(0, block, 2000, ctypes.byref(eps), ctypes.byref(ms)) == 0, L.bf_last_error()
+        rate[block] = eps.value / 1e9 / 148                    # elements per ns per SM
+        assert 3.0 < rate[block] < 400.0, (block, rate[block], ms.value)
+    assert rate[0] == min(rate.values()) and rate[3] == max(rate.values()), rate
+    widths = {0: 1024, 1: 1024, 2: 1024, 3: 512, 4: 512, 5: 256}
+    floor_ms = sum(4096 * 8 * 32 * w / (rate[b] * 148 * 1e9) for b, w in widths.items()) * 1e3
+    print(f"\nelements/ns/SM {dict((b, round(r, 1)) for b, r in rate.items())}; floor for 4096 positions {floor_ms:.3f} ms")
+    assert 0.4 < floor_ms < 2.0
+    # the ff1 epilogue with 8 and with 32 warps per SM: sixteen are within 10 % of thirty-two
+    for block in (6, 7):
+        assert L.bf_measure_elementwise(0, block, 2000, ctypes.byref(eps), None) == 0, L.bf_last_error()
+        rate[block] = eps.value / 1e9 / 148
+    print(f"ff1 epilogue, elements/ns/SM at 8 / 16 / 32 warps: {rate[6]:.1f} / {rate[0]:.1f} / {rate[7]:.1f}")
+    assert rate[6] < rate[0] * 1.02 and rate[0] > 0.9 * rate[7]
+    assert L.bf_measure_elementwise(0, 8, 100, ctypes.byref(eps), None) != 0
+    assert L.bf_measure_elementwise(0, 0, 0, ctypes.byref(eps), None) != 0
+
+
 def test_a_wait_that_nothing_satisfies_times_out_and_reports():
     """Failure detection without a fault: the bounded wait gives up after its limit, the kernel
     returns, the status word carries the code, a later waiter returns at once, and the device
