@@ -697,16 +697,18 @@ __device__ __forceinline__ void attention_block(RowCtx& c, const Params& p, cons
         }
         row_publish(c, B_A_READY);
     } else {
+        // the four pieces' loads go out together, ahead of the row maximum's exchange
+        uint32_t oh[4][8];
+#pragma unroll
+        for (int j = 0; j < 4; ++j) tmem_ld8(c.tm + TM_OY + 32 * j + 8 * c.qt, oh[j]);
         const float amax = exchange_max(c, o_amax);
         sa = amax > 0.f ? __fdiv_rn(amax, 127.0f) : 1.0f;
         const float inv = __fdiv_rn(1.0f, sa);
         const bool capo = kDbg && cap && p.cap_op == BF_OP_OUT && c.valid;
-#pragma unroll 1
+        tmem_wait_ld();
+#pragma unroll
         for (int j = 0; j < 4; ++j) {
-            uint32_t oh[8];
-            tmem_ld8(c.tm + TM_OY + 32 * j + 8 * c.qt, oh);
-            tmem_wait_ld();
-            const uint4 v = quant16(oh, inv, c.one2);
+            const uint4 v = quant16(oh[j], inv, c.one2);
             sts128(c.sm_a + (j >> 1) * 16384 + sw_off(c.row, 4 * (j & 1) + c.qt), v);
             if (capo) *reinterpret_cast<uint4*>(p.cap_a + c.grow * kD + 64 * j + 16 * c.qt) = v;
         }
