@@ -430,8 +430,8 @@ __device__ __forceinline__ float ln_stage(RowCtx& c, const Params& p, bool final
         }
     }
     // Exchange among the row's four threads through this board's slice of the staging region
-    // (idle between the MMAs that last read it and the next staging write; the second barrier
-    // keeps a fast warp from overwriting it): [sums | squares] in the first 16 KB block,
+    // (idle between the MMAs that last read it and the next staging write): [sums | squares]
+    // in the first 16 KB block,
     // [min, max] in the second.
     float tot, totq, xmin, xmax;
     {
@@ -453,7 +453,11 @@ __device__ __forceinline__ float ln_stage(RowCtx& c, const Params& p, bool final
             Q[k] = lds_f4(xb + 2048u + 16u * (32 * k + c.lane));
             M[k] = lds_f4(xb + 16384u + 16u * (32 * k + c.lane));
         }
-        board_sync(c);
+        // The final norm writes its output over these slots right away, so every warp must have
+        // read first.  After the other norms the next writer of this slice is an epilogue that
+        // waits for a GEMM which itself waits for all sixteen warps' operand rows, written
+        // after these reads: no second barrier is needed.
+        if (final_norm) board_sync(c);
         // levels 8 and 4: (A_q0 + A_q2) + (A_q1 + A_q3) for each of the four lanes; level 2:
         // lanes (0,2) and (1,3); level 1: the last add
         const uint64_t c01 = add2(add2(pk2(S[0].x, S[0].y), pk2(S[2].x, S[2].y)),
