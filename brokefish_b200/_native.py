@@ -29,7 +29,7 @@ EXPORTS = ["bf_version", "bf_last_error", "bf_create", "bf_destroy", "bf_info", 
            "bf_launch_count", "bf_profile", "bf_profile_read", "bf_profile_phases",
            "bf_forward_noalloc", "bf_noalloc_status", "bf_selftest_umma", "bf_set_option", "bf_measure_i8_peak", "bf_forward_priors",
            "bf_forward_priors_host", "bf_selftest_timeout", "bf_movegen", "bf_step", "bf_random_ply",
-           "bf_forward_leaves", "bf_measure_elementwise"]
+           "bf_forward_leaves", "bf_measure_elementwise", "bf_forward_backbone"]
 
 
 def nvcc_path() -> str:
@@ -92,6 +92,7 @@ def lib() -> ctypes.CDLL:
     L.bf_movegen.argtypes = [i32, vp, vp, i32, vp, vp, vp]
     L.bf_forward_leaves.argtypes = [vp] * 7 + [i32] + [vp] * 3 + [i32] + [vp] * 4
     L.bf_measure_elementwise.argtypes = [i32, i32, i32, ctypes.POINTER(ctypes.c_double), ctypes.POINTER(ctypes.c_double)]
+    L.bf_forward_backbone.argtypes = [vp, vp, vp, i32, vp, vp]
     L.bf_random_ply.argtypes = [i32, vp, vp, vp, vp, vp, i32, vp, vp]
     L.bf_step.argtypes = [i32, vp, vp, vp, vp, i32, vp, vp, vp, vp, vp, vp]
     L.bf_forward_priors_host.argtypes = [vp, vp, vp, vp, vp, i32, i32, vp, vp, vp, vp]

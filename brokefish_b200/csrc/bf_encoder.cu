@@ -121,6 +121,10 @@ struct Params {
     int cap_layer, cap_op;
     uint8_t* cap_a;
     int32_t* cap_acc;
+    // backbone-only entry (instrumented arm): activations in instead of the embedding, optional
+    // per-token alive flags instead of the piece words' captured bit
+    const __half* x_in;
+    const int8_t* alive_in;
     // compacted leaf list (optional): evaluate positions leaf_index[0 .. *leaf_count) of the
     // staged arrays; `n` is then the capacity (the most the list can hold) the grid was sized for
     const int* leaf_index;
@@ -1125,17 +1129,37 @@ __device__ __forceinline__ void row_warps_tile(RowCtx& c, const Params& p, int t
     // staged arrays
     const int board = (c.valid && p.leaf_index != nullptr) ? __ldg(p.leaf_index + item) : item;
     c.grow = static_cast<long>(board) * kT + c.lane;
-    const uint32_t word = c.valid ? p.boards[c.grow] : 0u;
-    const uint32_t alive = __ballot_sync(0xffffffffu, ((word >> 11) & 1u) == 0u);
-    const int ctl = c.valid ? static_cast<int>(p.control[board]) : 1;
+    const bool backbone = kDbg && p.x_in != nullptr;
+    const uint32_t word = (c.valid && !backbone) ? p.boards[c.grow] : 0u;
+    uint32_t alive = __ballot_sync(0xffffffffu, ((word >> 11) & 1u) == 0u);
+    if (backbone && p.alive_in != nullptr)
+        alive = __ballot_sync(0xffffffffu, c.valid ? p.alive_in[c.grow] != 0 : true);
+    const int ctl = (c.valid && !backbone) ? static_cast<int>(p.control[board]) : 1;
     const int dbg = p.debug_stage;
 
+    if (backbone) {
+        // activations in (the reference's `encoder_forward`, encoder.cu:1752-1767): this token's
+        // row of x becomes the residual stream as it is
+        c.word = 0u; c.stm = 0; c.clk = 0; c.rp = 0;
+#pragma unroll 1
+        for (int u = 0; u < 2; ++u) {
+            uint32_t e16[16];
+            const uint4* src = reinterpret_cast<const uint4*>(p.x_in + c.grow * kD + 128 * u + 32 * c.qt);
+#pragma unroll
+            for (int k = 0; k < 4; ++k) {
+                const uint4 v = c.valid ? __ldg(src + k) : make_uint4(0u, 0u, 0u, 0u);
+                e16[4 * k] = v.x; e16[4 * k + 1] = v.y; e16[4 * k + 2] = v.z; e16[4 * k + 3] = v.w;
+            }
+            tmem_st16(c.tm + TM_X + 64 * u + 16 * c.qt, e16);
+        }
+        tmem_wait_st();
+    } else
     // ---- embedding: ((square + type_special) + color_turn) + (clock + rep), fp16
     //      (encoder.cu:817-889; nn/model.py:383-397), written to the residual stream ----
     {
         const int stm = ctl < 0;
         const int clk = min(max((ctl < 0 ? -ctl : ctl) - 1, 0), kNClock - 1);
-        const int rp = min(c.valid ? static_cast<int>(p.rep[board]) : 0, kNRep - 1);
+        const int rp = min((c.valid && !backbone) ? static_cast<int>(p.rep[board]) : 0, kNRep - 1);
         c.word = word; c.stm = stm; c.clk = clk; c.rp = rp;
         const int sq = word & 63;
         const int ts = min(static_cast<int>(((word >> 6) & 7) * 2 + ((word >> 9) & 1)), kNTypeSpecial - 1);
@@ -1903,6 +1927,10 @@ struct PriorOut {
     int* nedges;
     int e_cap;
 };
+struct Backbone {
+    const void* x;              // device: activations in, [n,32,256] fp16
+    const int8_t* alive;        // device: per-token alive flags [n,32] or null (all alive)
+};
 struct LeafList {
     const int* index;           // device: positions to evaluate, as places in the staged arrays
     const int* count;           // device: how many of them (read by the kernel when it starts)
@@ -1911,11 +1939,11 @@ struct LeafList {
 int launch(bf_handle* h, const uint16_t* boards, const int16_t* control, const uint8_t* rep,
            const uint64_t* legal, int n, void* policy, void* promo, float* value, void* y, int stage,
            int stage_layer, int cap_layer, int cap_op, uint8_t* cap_a, int32_t* cap_acc, cudaStream_t stream,
-           const PriorOut* po = nullptr, const LeafList* leaves = nullptr) {
+           const PriorOut* po = nullptr, const LeafList* leaves = nullptr, const Backbone* bb = nullptr) {
     if (h == nullptr) return fail(BF_EINVAL, "null handle");
     if (n < 0) return fail(BF_EINVAL, "n must be >= 0");
     if (n == 0) return BF_OK;
-    if (boards == nullptr || control == nullptr || rep == nullptr)
+    if (bb == nullptr && (boards == nullptr || control == nullptr || rep == nullptr))
         return fail(BF_EINVAL, "boards, control and rep must be non-null");
     BF_CUDA(cudaSetDevice(h->device));
     bf::Params p{};
@@ -1941,6 +1969,7 @@ int launch(bf_handle* h, const uint16_t* boards, const int16_t* control, const u
         p.prior = static_cast<__half*>(po->prior); p.move = po->move; p.nedges = po->nedges; p.e_cap = po->e_cap;
     }
     if (leaves != nullptr) { p.leaf_index = leaves->index; p.leaf_count = leaves->count; }
+    if (bb != nullptr) { p.x_in = static_cast<const __half*>(bb->x); p.alive_in = bb->alive; }
     const int n_tiles = (n + 3) / 4;
     const int grid = n_tiles < h->sm_count ? n_tiles : h->sm_count;
     // the instrumented instantiation only when a dump, a capture or the phase clock is asked for
@@ -2131,6 +2160,19 @@ int bf_random_ply(int device, uint16_t* boards, int16_t* control, uint64_t* mask
         boards, control, reinterpret_cast<unsigned long long*>(mask), r, promo, n, move);
     BF_CUDA(cudaGetLastError());
     return BF_OK;
+}
+
+int bf_forward_backbone(bf_handle* h, const void* x, const int8_t* alive, int n, void* y, void* stream) {
+    if (h == nullptr) return fail(BF_EINVAL, "null handle");
+    if (n == 0) return BF_OK;
+    if (x == nullptr || y == nullptr) return fail(BF_EINVAL, "x and y must be non-null");
+    if (h->hdr.quant != 0)
+        return fail(BF_ENOTSUP, "the backbone-only entry runs the fp16 arithmetic only, as the reference's does");
+    const Backbone bb{x, alive};
+    // the residual stream at the end of the last layer, through the instrumented arm's dump
+    return launch(h, nullptr, nullptr, nullptr, nullptr, n, nullptr, nullptr, nullptr, y, 10,
+                  static_cast<int>(h->hdr.n_layers) - 1, -1, -1, nullptr, nullptr,
+                  static_cast<cudaStream_t>(stream), nullptr, nullptr, &bb);
 }
 
 int bf_forward_stage_at(bf_handle* h, const uint16_t* boards, const int16_t* control,

@@ -99,6 +99,8 @@ class FusedEncoder:
         self.two_boards = True if two_boards is None else bool(two_boards)
         self.debug_stage = 0
         self.net = net
+        self._source_encoder = encoder
+        self._bb_handle = None
         self._handle = ctypes.c_void_p(0)
         self._exact_rsqrt = False
         self._buffered = 0
@@ -158,6 +160,9 @@ class FusedEncoder:
         if getattr(self, "_handle", None) and self._handle.value:
             _native.lib().bf_destroy(self._handle)
             self._handle = ctypes.c_void_p(0)
+        if getattr(self, "_bb_handle", None) is not None and self._bb_handle.value:
+            _native.lib().bf_destroy(self._bb_handle)
+            self._bb_handle = None
 
     def __del__(self):
         try:
@@ -181,11 +186,74 @@ class FusedEncoder:
                 f"{what} needs the whole model: build this from a BrokefishNet, not from a "
                 "bare nn.TransformerEncoder")
 
-    # -- the backbone-only path of the reference is not built -------------------------
+    # -- the backbone-only path: activations in, activations out ------------------------
+    def _backbone_handle(self):
+        """The handle the backbone entry runs on: this instance's own when it carries the fp16
+        arithmetic, else a second one packed from the same weights on first use (the reference
+        keeps an fp16 slab beside the quantised ones for the same purpose,
+        brokefish/nn/cuda_impl.py:228, 460)."""
+        if self.quant == 0 and self._handle.value:
+            return self._handle
+        if getattr(self, "_bb_handle", None) is not None and self._bb_handle.value:
+            return self._bb_handle
+        if getattr(self, "_from_blob", False):
+            raise NotImplementedError("an encoder built from a packed blob has no weights to pack the fp16 "
+                                      "backbone from; build it from the network")
+        net = self.net
+        if net is None:
+            # a bare nn.TransformerEncoder: the stack is all there is; embeddings, final norm and
+            # heads of a throw-away network fill the blob's other sections and are never read
+            if not torch.cuda.is_available():
+                raise RuntimeError("FusedEncoder needs a CUDA device (sm_100a); there is no CPU fallback")
+            if not hasattr(self, "device"):
+                self.device = torch.cuda.current_device()
+            net = BrokefishNet(n_layers=self.n_layers, eps=self.eps)
+            net.encoder = self._source_encoder
+        blob = pack_blob(net, "f16")
+        h = ctypes.c_void_p(0)
+        _native.check(_native.lib().bf_create(ctypes.c_void_p(blob.ctypes.data), blob.size, self.device,
+                                              ctypes.byref(h)), "bf_create")
+        self._bb_handle = h
+        return h
+
     def forward(self, x, alive=None, out=None):
-        raise NotImplementedError(
-            "the backbone-only entry point (activations in, activations out) is not built; "
-            "use forward_full(boards, control, rep)")
+        """Backbone only (brokefish/nn/cuda_impl.py:447-463): ``x [n,32,256]`` fp16 through the
+        encoder layers, no embedding, no final norm, no heads; ``alive [n,32]`` bool or int8
+        masks dead tokens as attention keys.  Always the fp16 arithmetic, as in the reference.
+        Returns ``out`` (or an internal buffer the next call overwrites)."""
+        if x.dim() != 3:
+            raise ValueError(f"x must be [n, 32, {self.D}], got {tuple(x.shape)}")
+        n_boards, seq_len, d_model = x.shape
+        if d_model != self.d_model:
+            raise ValueError(f"expected d_model={self.d_model}, got {d_model}")
+        if seq_len != self.T:
+            raise ValueError(f"expected {self.T} tokens per board, got {seq_len}")
+        if not x.is_cuda or x.dtype is not torch.half:
+            raise ValueError("x must be a CUDA fp16 tensor")
+        alive_arg = None
+        if alive is not None:
+            if tuple(alive.shape) != (n_boards, seq_len):
+                raise ValueError(f"alive must be [{n_boards}, {seq_len}], got {tuple(alive.shape)}")
+            if alive.dtype is torch.bool:
+                alive = alive.view(torch.int8)
+            elif alive.dtype is not torch.int8:
+                raise ValueError(f"alive must be bool or int8, got {alive.dtype}")
+            alive_arg = alive.contiguous()
+        h = self._backbone_handle()
+        self._check_device(x, alive_arg, out)
+        if out is None:
+            if self._buffered != n_boards:
+                self.state = torch.empty(n_boards, seq_len, d_model, dtype=torch.half,
+                                         device=torch.device("cuda", self.device))
+                self._buffered = n_boards
+            out = self.state
+        elif tuple(out.shape) != tuple(x.shape) or out.dtype is not torch.half or not out.is_contiguous():
+            raise ValueError("out must be a contiguous fp16 tensor of x's shape")
+        xin = x.contiguous()
+        stream = ctypes.c_void_p(torch.cuda.current_stream(self.device).cuda_stream)
+        _native.check(_native.lib().bf_forward_backbone(h, _ptr(xin), _ptr(alive_arg), n_boards, _ptr(out), stream),
+                      "bf_forward_backbone")
+        return out
 
     __call__ = forward
 

@@ -142,6 +142,15 @@ int bf_step(int device, const uint16_t* boards, const int16_t* control, const in
 int bf_random_ply(int device, uint16_t* boards, int16_t* control, uint64_t* mask, const float* r,
                   const signed char* promo, int n, int* move, void* stream);
 
+/* Backbone only: activations in, activations out.  `x` [n,32,256] fp16 goes through the encoder
+ * layers (no embedding, no final norm, no heads) and the residual stream after the last layer is
+ * written to `y` [n,32,256] fp16 (y == x is allowed: a board's rows are read before they are
+ * written); `alive` [n,32] int8 (may be NULL = all alive) masks dead tokens as attention keys.
+ * Replaces `encoder_forward(y, weights, alive, n_layers, eps, 0)` (csrc/encoder.cu:1752-1767),
+ * which the reference keeps on its fp16 arithmetic only; so does this: a handle whose blob
+ * carries another arithmetic is refused with BF_ENOTSUP. */
+int bf_forward_backbone(bf_handle* h, const void* x, const int8_t* alive, int n, void* y, void* stream);
+
 /* Activations at an intermediate stage as [n,32,256] fp16.  Replaces
  * `model_forward(..., debug_stage=stage)` (csrc/encoder.cu:1315-1427, 1575-1598):
  * 9 embedding; layer 0: 1 LN1 out, 5/6/7 Q/K/V after bias, 4 attention out,

@@ -88,3 +88,14 @@ class RefKernel:
                             self.n_layers, self.eps, int(stage), self.wq8, self.sq8, self.quant,
                             self.two_boards, self.n_value, self.vmode, self.rj, self.rj_mode)
         return y
+
+    def encoder_forward(self, x, alive=None):
+        """The reference's backbone-only entry (``encoder_forward`` of ``csrc/encoder.cu:1752``,
+        the call ``brokefish/nn/cuda_impl.py:447-461`` makes): ``x [n,32,256]`` fp16 in, the
+        residual stream after the last layer out; ``alive [n,32]`` int8 or ``None``."""
+        import torch
+        out = x.contiguous().clone()
+        a = alive.contiguous() if alive is not None else torch.empty(0, dtype=torch.int8, device=self.device)
+        ext().encoder_forward(out, self.weights, a, self.n_layers, self.eps, 0)
+        return out
+

@@ -41,8 +41,10 @@ def test_constructor_refusals(nets):
     z = torch.zeros(1, 32, dtype=torch.int16)
     with pytest.raises(ValueError):
         bare.forward_full(z, torch.ones(1, dtype=torch.int16), torch.zeros(1, dtype=torch.uint8))
-    with pytest.raises(NotImplementedError):
-        bare(torch.zeros(1, 32, 256))
+    with pytest.raises(ValueError):
+        bare(torch.zeros(1, 32, 256))                       # the backbone entry takes CUDA fp16 tensors
+    with pytest.raises(ValueError):
+        bare(torch.zeros(1, 32, 128))
 
 
 def test_input_checks():
