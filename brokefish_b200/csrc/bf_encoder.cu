@@ -1976,7 +1976,10 @@ int launch(bf_handle* h, const uint16_t* boards, const int16_t* control, const u
     const bool dbg = stage != 0 || cap_layer >= 0 || p.prof != nullptr;
     if (p.quant == 0) {
         if (cap_layer >= 0) return fail(BF_ENOTSUP, "operand capture is for the int8 arithmetic");
-        if (dbg) bf::encoder_kernel<true, false, bf::kArF16><<<grid, bf::kThreads, bf::kSmemRequest, stream>>>(p);
+        if (p.rj_mode != 0) {
+            if (dbg) bf::encoder_kernel<true, true, bf::kArF16><<<grid, bf::kThreads, bf::kSmemRequest, stream>>>(p);
+            else     bf::encoder_kernel<false, true, bf::kArF16><<<grid, bf::kThreads, bf::kSmemRequest, stream>>>(p);
+        } else if (dbg) bf::encoder_kernel<true, false, bf::kArF16><<<grid, bf::kThreads, bf::kSmemRequest, stream>>>(p);
         else     bf::encoder_kernel<false, false, bf::kArF16><<<grid, bf::kThreads, bf::kSmemRequest, stream>>>(p);
     } else if (p.quant == 1) {
         if (cap_layer >= 0) return fail(BF_ENOTSUP, "operand capture is for the int8 arithmetic");
@@ -2015,7 +2018,8 @@ int bf_create(const void* blob, size_t blob_bytes, int device, bf_handle** out) 
     if (hdr.n_layers < 1 || hdr.n_layers > 64) return fail(BF_EINVAL, "n_layers out of range");
     if (hdr.quant != 3 && hdr.quant != 1 && hdr.quant != 0)
         return fail(BF_EINVAL, "blob arithmetic must be 3 (int8), 1 (e4m3 FFN) or 0 (fp16)");
-    if (hdr.quant != 3 && hdr.rj_mode != 0) return fail(BF_ENOTSUP, "re-injection is built for the int8 arithmetic only");
+    if (hdr.quant == 1 && hdr.rj_mode != 0)
+        return fail(BF_ENOTSUP, "re-injection is built for the int8 and fp16 arithmetics, as in the reference");
     const uint64_t layer_stream = hdr.quant == 1 ? bf::Cfg<bf::kArE4M3>::kLayerStream
                                 : hdr.quant == 0 ? bf::Cfg<bf::kArF16>::kLayerStream
                                                  : bf::Cfg<bf::kArInt8>::kLayerStream;
@@ -2046,7 +2050,9 @@ int bf_create(const void* blob, size_t blob_bytes, int device, bf_handle** out) 
     if (e == cudaSuccess) e = cudaStreamCreateWithFlags(&h->stream, cudaStreamNonBlocking);
     if (e == cudaSuccess) e = cudaStreamCreateWithFlags(&h->copy_stream, cudaStreamNonBlocking);
     if (e == cudaSuccess) e = cudaEventCreateWithFlags(&h->chunk_done, cudaEventDisableTiming);
-    const void* kernels[8] = {
+    const void* kernels[10] = {
+        reinterpret_cast<const void*>(&bf::encoder_kernel<false, true, bf::kArF16>),
+        reinterpret_cast<const void*>(&bf::encoder_kernel<true, true, bf::kArF16>),
         reinterpret_cast<const void*>(&bf::encoder_kernel<false, false, bf::kArInt8>),
         reinterpret_cast<const void*>(&bf::encoder_kernel<true, false, bf::kArInt8>),
         reinterpret_cast<const void*>(&bf::encoder_kernel<false, true, bf::kArInt8>),
@@ -2055,7 +2061,7 @@ int bf_create(const void* blob, size_t blob_bytes, int device, bf_handle** out) 
         reinterpret_cast<const void*>(&bf::encoder_kernel<true, false, bf::kArE4M3>),
         reinterpret_cast<const void*>(&bf::encoder_kernel<false, false, bf::kArF16>),
         reinterpret_cast<const void*>(&bf::encoder_kernel<true, false, bf::kArF16>)};
-    for (int i = 0; i < 8 && e == cudaSuccess; ++i)
+    for (int i = 0; i < 10 && e == cudaSuccess; ++i)
         e = cudaFuncSetAttribute(kernels[i], cudaFuncAttributeMaxDynamicSharedMemorySize, bf::kSmemRequest);
     if (e != cudaSuccess) {
         bf_destroy(h);

@@ -113,8 +113,10 @@ class FusedEncoder:
             self.n_value = int(net.value.weight.shape[0])
             self.vmode = self.VMODE[getattr(net, "value_head", "king")]
             self.rj_mode = self.RJMODE[getattr(net, "reinject", "none")]
-            if self.quant != 3 and self.rj_mode:
-                raise NotImplementedError("input re-injection is built for the int8 arithmetic only")
+            if self.quant == 1 and self.rj_mode:
+                raise NotImplementedError("input re-injection is built for the int8 and the fp16 arithmetic "
+                                          "(as in the reference, brokefish/nn/cuda_impl.py:413-420); this "
+                                          "encoder is " + self.label)
             self.blob = pack_blob(net, {3: "int8", 1: "e4m3", 0: "f16"}[self.quant])
             self._create(self.blob)
 

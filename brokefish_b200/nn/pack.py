@@ -269,8 +269,8 @@ def pack_blob(net: BrokefishNet, fmt: str = "int8") -> np.ndarray:
             f"{first.self_attn.embed_dim}, {first.linear1.out_features}, "
             f"{first.self_attn.num_heads}")
     layers = fold_and_quantise(net, fmt)
-    if fmt != "int8" and getattr(net, "reinject", "none") != "none":
-        raise NotImplementedError("input re-injection is built for the int8 arithmetic only")
+    if fmt == "e4m3" and getattr(net, "reinject", "none") != "none":
+        raise NotImplementedError("input re-injection is built for the int8 and fp16 arithmetics only")
     wstream = np.concatenate([_layer_stream(fl) for fl in layers])
     lparams = np.concatenate([_layer_params(fl) for fl in layers])
     emb = np.concatenate([getattr(net, n).weight.detach().half().cpu().numpy().reshape(-1)

@@ -47,6 +47,8 @@ SETS = {
     "A_e4m3": (dict(seed=0, std=0.02, perturb_norms=False), dict(fp8=True)),
     "A_f16": (dict(seed=0, std=0.02, perturb_norms=False), dict()),
     "C_int8_rj": (dict(seed=7, std=None, perturb_norms=True, reinject="both"), dict(int8=True)),
+    "C_f16_rj": (dict(seed=7, std=None, perturb_norms=True, reinject="both"), dict()),
+    "D_f16_rj1": (dict(seed=8, std=0.02, perturb_norms=True, reinject="ln1"), dict()),
     "V_int8_wdl": (dict(seed=3, std=0.02, perturb_norms=True, n_value=3, value_head="pooled"),
                    dict(int8=True)),
     "P_int8_prenorm": (dict(seed=5, std=None, perturb_norms=True, n_value=3, value_head="prenorm"),

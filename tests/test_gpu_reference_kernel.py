@@ -135,6 +135,28 @@ def test_reinjection_is_bit_identical(pos256):
     enc.close()
 
 
+@pytest.mark.parametrize("name,kw,mode", [
+    ("C_f16_rj", dict(seed=7, std=None, perturb_norms=True, reinject="both"), 2),
+    ("D_f16_rj1", dict(seed=8, std=0.02, perturb_norms=True, reinject="ln1"), 1)])
+def test_reinjection_on_the_fp16_arithmetic_is_bit_identical(name, kw, mode, pos256):
+    """The reference builds re-injection for its int8 and its fp16 kernel
+    (brokefish/nn/cuda_impl.py:413-420); so does this library, both modes."""
+    if not R.available(name):
+        pytest.skip("slabs missing")
+    enc, ref = product(kw, int8=False), R.RefKernel(name)
+    assert ref.rj_mode == mode and enc.rj_mode == mode and ref.quant == 0 and enc.quant == 0
+    sl = slice(0, 96)
+    for stage in (1, 3, 8):
+        got = enc.forward_stage(*inputs(pos256, sl), stage).cpu().numpy()
+        want = ref.forward_stage(*inputs(pos256, sl), stage).cpu().numpy()
+        assert same_bits(got, want), stage
+    (pol, pro, val), (rpol, rpro, rval) = run_both(enc, ref, pos256, sl)
+    assert same_bits(pol, rpol) and same_bits(pro, rpro) and np.abs(val - rval).max() <= 1e-6
+    enc.close()
+    with pytest.raises(NotImplementedError):
+        product(kw, fp8=True)
+
+
 def test_pooled_wdl_value_is_bit_identical(pos256):
     if not R.available("V_int8_wdl"):
         pytest.skip("slabs missing")
