@@ -29,7 +29,8 @@ EXPORTS = ["bf_version", "bf_last_error", "bf_create", "bf_destroy", "bf_info", 
            "bf_launch_count", "bf_profile", "bf_profile_read", "bf_profile_phases",
            "bf_forward_noalloc", "bf_noalloc_status", "bf_selftest_umma", "bf_set_option", "bf_measure_i8_peak", "bf_forward_priors",
            "bf_forward_priors_host", "bf_selftest_timeout", "bf_movegen", "bf_step", "bf_random_ply",
-           "bf_forward_leaves", "bf_measure_elementwise", "bf_forward_backbone"]
+           "bf_forward_leaves", "bf_measure_elementwise", "bf_forward_backbone", "bf_int8_q_max",
+           "bf_fp8_q_max"]
 
 
 def nvcc_path() -> str:
@@ -93,6 +94,10 @@ def lib() -> ctypes.CDLL:
     L.bf_forward_leaves.argtypes = [vp] * 7 + [i32] + [vp] * 3 + [i32] + [vp] * 4
     L.bf_measure_elementwise.argtypes = [i32, i32, i32, ctypes.POINTER(ctypes.c_double), ctypes.POINTER(ctypes.c_double)]
     L.bf_forward_backbone.argtypes = [vp, vp, vp, i32, vp, vp]
+    L.bf_int8_q_max.argtypes = [ctypes.POINTER(ctypes.c_int), ctypes.POINTER(ctypes.c_int)]
+    L.bf_int8_q_max.restype = None
+    L.bf_fp8_q_max.argtypes = []
+    L.bf_fp8_q_max.restype = ctypes.c_double
     L.bf_random_ply.argtypes = [i32, vp, vp, vp, vp, vp, i32, vp, vp]
     L.bf_step.argtypes = [i32, vp, vp, vp, vp, i32, vp, vp, vp, vp, vp, vp]
     L.bf_forward_priors_host.argtypes = [vp, vp, vp, vp, vp, i32, i32, vp, vp, vp, vp]
@@ -107,7 +112,8 @@ def lib() -> ctypes.CDLL:
     L.bf_selftest_umma.argtypes = [i32, i32, vp, vp, vp]
     for name in EXPORTS:
         fn = getattr(L, name)
-        if name not in ("bf_version", "bf_last_error", "bf_launch_count", "bf_profile_phases"):
+        if name not in ("bf_version", "bf_last_error", "bf_launch_count", "bf_profile_phases",
+                        "bf_int8_q_max", "bf_fp8_q_max"):
             fn.restype = ctypes.c_int
     _LIB = L
     return L

@@ -91,6 +91,11 @@ constexpr uint32_t TM_X = 0, TM_OY = 128, TM_ACC = 256, TM_COLS = 512;
 // time-out codes written to the status word (which wait gave up)
 enum { kErrProducer = 1, kErrMmaOperand = 2, kErrMmaWeights = 3, kErrMmaAcc = 4, kErrRowAcc = 5 };
 
+// Ranges of the quantised operands: a row's (or a 128-output weight block's) scale is its
+// largest magnitude over these (int8_gemm.cuh:26-30, 98, 166: signed 127, unsigned 255;
+// fp8_gemm.cuh: the e4m3 operands are scaled into +-8).
+constexpr float kQMaxS8 = 127.0f, kQMaxU8 = 255.0f, kQMaxE4M3 = 8.0f;
+
 struct Params {
     const uint16_t* boards;
     const int16_t* control;
@@ -488,7 +493,7 @@ __device__ __forceinline__ float ln_stage(RowCtx& c, const Params& p, bool final
     const float e_lo = __half2float(__float2half_rn(__fmul_rn(__fsub_rn(xmin, mean), rstd)));
     const float e_hi = __half2float(__float2half_rn(__fmul_rn(__fsub_rn(xmax, mean), rstd)));
     const float amax = fmaxf(fabsf(e_lo), fabsf(e_hi));
-    const float sc = amax > 0.f ? __fdiv_rn(amax, kFP8 ? 8.0f : 127.0f) : 1.0f;
+    const float sc = amax > 0.f ? __fdiv_rn(amax, kFP8 ? kQMaxE4M3 : kQMaxS8) : 1.0f;
     const float inv = __fdiv_rn(1.0f, sc);
     const uint64_t nmean2 = pk2(-mean, -mean), rstd2 = pk2(rstd, rstd);
     tmem_wait_ld();
@@ -710,7 +715,7 @@ __device__ __forceinline__ void attention_block(RowCtx& c, const Params& p, cons
 #pragma unroll
         for (int j = 0; j < 4; ++j) tmem_ld8(c.tm + TM_OY + 32 * j + 8 * c.qt, oh[j]);
         const float amax = exchange_max(c, o_amax);
-        sa = amax > 0.f ? __fdiv_rn(amax, 127.0f) : 1.0f;
+        sa = amax > 0.f ? __fdiv_rn(amax, kQMaxS8) : 1.0f;
         const float inv = __fdiv_rn(1.0f, sa);
         const bool capo = kDbg && cap && p.cap_op == BF_OP_OUT && c.valid;
         tmem_wait_ld();
@@ -788,7 +793,7 @@ __device__ __forceinline__ void ffn_block(RowCtx& c, const Params& p, const Laye
             }
             // per-row u8 scale over the 256-wide chunk (encoder.cu:1510-1517)
             const float amax = exchange_max(c, amax_h2<32>(hid, false));
-            const float sc = amax > 0.f ? __fdiv_rn(amax, kFP8 ? 8.0f : 255.0f) : 1.0f;
+            const float sc = amax > 0.f ? __fdiv_rn(amax, kFP8 ? kQMaxE4M3 : kQMaxU8) : 1.0f;
             const float inv = __fdiv_rn(1.0f, sc);
             if (ch & 1) sa2_1 = sc; else sa2_0 = sc;
             const bool caph = kDbg && cap && p.cap_op == BF_OP_FF2 + ch && c.valid;
@@ -2167,6 +2172,12 @@ int bf_random_ply(int device, uint16_t* boards, int16_t* control, uint64_t* mask
     BF_CUDA(cudaGetLastError());
     return BF_OK;
 }
+
+void bf_int8_q_max(int* signed_max, int* unsigned_max) {
+    if (signed_max != nullptr) *signed_max = static_cast<int>(bf::kQMaxS8);
+    if (unsigned_max != nullptr) *unsigned_max = static_cast<int>(bf::kQMaxU8);
+}
+double bf_fp8_q_max(void) { return static_cast<double>(bf::kQMaxE4M3); }
 
 int bf_forward_backbone(bf_handle* h, const void* x, const int8_t* alive, int n, void* y, void* stream) {
     if (h == nullptr) return fail(BF_EINVAL, "null handle");

@@ -142,6 +142,12 @@ int bf_step(int device, const uint16_t* boards, const int16_t* control, const in
 int bf_random_ply(int device, uint16_t* boards, int16_t* control, uint64_t* mask, const float* r,
                   const signed char* promo, int n, int* move, void* stream);
 
+/* The kernel's own quantisation ranges, for a host-side packer to check its constants against:
+ * signed and unsigned int8 (127, 255) and the e4m3 operand range (8).  Replace the extension's
+ * `fp8_q_max()` and `int8_q_max()` (csrc/encoder.cu:1906, 1926-1929). */
+void bf_int8_q_max(int* signed_max, int* unsigned_max);
+double bf_fp8_q_max(void);
+
 /* Backbone only: activations in, activations out.  `x` [n,32,256] fp16 goes through the encoder
  * layers (no embedding, no final norm, no heads) and the residual stream after the last layer is
  * written to `y` [n,32,256] fp16 (y == x is allowed: a board's rows are read before they are

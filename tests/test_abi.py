@@ -32,3 +32,15 @@ def test_argument_errors_need_no_gpu():
     assert L.bf_forward(None, None, None, None, None, 4, None, None, None, None) == -1
     assert L.bf_destroy(None) == 0
     assert L.bf_launch_count(None) == 0
+
+
+def test_kernel_constants_match_the_packer():
+    """The quantisation ranges compiled into the kernel equal the host packer's (the reference
+    checks the same pair of facts, tests/test_quant.py:233-269)."""
+    from brokefish_b200.nn import quant
+    L = _native.lib()
+    s, u = ctypes.c_int(0), ctypes.c_int(0)
+    L.bf_int8_q_max(ctypes.byref(s), ctypes.byref(u))
+    assert (s.value, u.value) == (127, 255) == (int(quant.Q_MAX_S8), int(quant.Q_MAX_U8))
+    assert L.bf_fp8_q_max() == 8.0 == quant.Q_MAX
+    L.bf_int8_q_max(None, None)                              # null outputs are allowed
