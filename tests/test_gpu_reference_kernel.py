@@ -123,6 +123,29 @@ def test_int8_full_batch_is_bit_identical(pos4096):
     enc.close()
 
 
+def test_every_batch_size_of_the_sweep_is_bit_identical():
+    """Batch sizes 1 .. 65536 of the batch-sweep configuration (piece counts uniform in 2..32 by
+    extra captures, side to move flipped on half the boards, seed 2), with the sizes around a
+    tile (4 boards) and around one wave (148 CTAs x 4 boards) added: ragged last tiles, CTAs
+    without work, and many waves all give the reference kernel's bits."""
+    if not R.available("B_int8"):
+        pytest.skip("slabs missing")
+    from brokefish_b200.positions import varied
+    enc, ref = product(SETS["B"]), R.RefKernel("B_int8")
+    b, c, r, _ = varied(65536, seed=2)
+    pieces = ((b.view(np.uint16) >> 11) & 1) == 0
+    assert pieces.sum(1).min() == 2 and pieces.sum(1).max() == 32 and 0.4 < (c < 0).mean() < 0.6
+    for n in (1, 2, 3, 4, 5, 63, 64, 65, 511, 512, 513, 591, 592, 593, 4096, 16384, 65536):
+        lo = 0 if n == 65536 else 65536 - n - 7
+        args = [dev(a[lo:lo + n]) for a in (b, c, r)]
+        pol, pro, val = [t.cpu().numpy().copy() for t in enc.forward_full(*args)]
+        rpol, rpro, rval = [t.cpu().numpy().copy() for t in ref.forward_full(*args)]
+        assert same_bits(pol, rpol) and same_bits(pro, rpro), n
+        assert np.abs(val - rval).max() <= 1e-6, n
+    enc.check_status()
+    enc.close()
+
+
 def test_reinjection_is_bit_identical(pos256):
     if not R.available("C_int8_rj"):
         pytest.skip("slabs missing")
