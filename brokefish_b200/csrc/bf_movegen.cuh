@@ -11,12 +11,15 @@
 // pawn: has just made its double step), bit 10 colour (1 black), bit 11 captured.  The control
 // word's sign is the side to move (negative: black).
 //
-// Method: pseudo-legal targets from bitboards built with warp-wide OR reductions, then every
-// candidate is tested by removing / adding the squares it changes and asking whether the
-// mover's king square is attacked (rays from the king outwards, knight / king / pawn patterns),
-// which decides exactly what the reference decides by replaying each move and building the
-// opponent's control map (torch_impl.py:266-290).  Castling tests the king's start, crossed and
-// landing squares in the position after the move, as the reference does.
+// Method: bitboards built with warp-wide OR reductions; every enemy lane contributes the squares
+// its piece attacks with the mover's king lifted off the board (king moves and castling avoid
+// their union); the enemy lanes that attack the king are the checkers (one checker: the other
+// pieces may only capture it or step between; two: only the king moves); every lane walks the
+// line from the king to its own piece, which finds the pieces that shield the king from a slider
+// (they move only along that line) and, for a checking slider, the squares between.  Only en
+// passant, which takes two pieces off one rank at once, is tested on the position after the
+// move.  This decides what the reference decides by replaying each move and building the
+// opponent's control map (torch_impl.py:266-290).
 #pragma once
 #include <stdint.h>
 
@@ -111,23 +114,91 @@ __device__ __forceinline__ unsigned long long legal_word(unsigned word, int cont
     const unsigned long long fresh_rooks = warp_or(mine && type == ROOK && !special ? bb : 0ull);
     const unsigned long long my_king = warp_or(mine && type == KING ? bb : 0ull);
     const int king_sq = my_king ? __ffsll(static_cast<long long>(my_king)) - 1 : 0;
-    in_check = my_king != 0ull && attacked(king_sq, occ, e);
+    const int rank = sq >> 3, file = sq & 7;
+
+    // ---- what the opponent attacks, with the mover's king lifted off the board (so that a
+    //      square behind the king on a checking line counts as attacked) ----
+    unsigned long long att = 0ull;
+    if (theirs) {
+        const unsigned long long occ_nk = occ & ~my_king;
+        if (type == PAWN)
+            att = is_black ? (((bb >> 9) & ~kFileH) | ((bb >> 7) & ~kFileA))
+                           : (((bb << 7) & ~kFileH) | ((bb << 9) & ~kFileA));
+        else if (type == KNIGHT) att = knight_pattern(bb);
+        else if (type == KING) att = king_pattern(bb);
+        else {
+            if (type == BISHOP || type == QUEEN) att |= rays(sq, occ_nk, true);
+            if (type == ROOK || type == QUEEN) att |= rays(sq, occ_nk, false);
+        }
+    }
+    const unsigned long long danger = warp_or(att);
+    in_check = (danger & my_king) != 0ull;
+    const unsigned checkers = __ballot_sync(kFull, theirs && (att & my_king) != 0ull);
+
+    // ---- the line from the king to this piece, when the piece is the first one met on a rank,
+    //      file or diagonal through the king: `line_to_me` = squares after the king up to and
+    //      including the piece, `beyond` = the next piece on the same ray, `line` = everything
+    //      walked, from the king's neighbour to that next piece ----
+    unsigned long long line = 0ull, line_to_me = 0ull, beyond = 0ull;
+    bool first_on_ray = false, ray_diag = false;
+    if (live && my_king != 0ull && bb != my_king) {
+        const int kr = king_sq >> 3, kf = king_sq & 7;
+        const int dr = rank - kr, df = file - kf;
+        const bool aligned = (dr == 0) != (df == 0) || (dr != 0 && (dr == df || dr == -df));
+        if (aligned) {
+            const int sr = (dr > 0) - (dr < 0), sf = (df > 0) - (df < 0);
+            ray_diag = sr != 0 && sf != 0;
+            int r = kr + sr, f = kf + sf;
+            bool past = false;
+            while (r >= 0 && r < 8 && f >= 0 && f < 8) {
+                const unsigned long long bit = 1ull << (r * 8 + f);
+                line |= bit;
+                if (!past) line_to_me |= bit;
+                if (occ & bit) {
+                    if (!past) {
+                        if (bit != bb) break;          // something stands between the king and this piece
+                        past = first_on_ray = true;
+                    } else {
+                        beyond = bit;
+                        break;
+                    }
+                }
+                r += sr; f += sf;
+            }
+        }
+    }
+    // one checker: the other pieces may only capture it or step between it and the king
+    unsigned long long target_mask = ~0ull;
+    const int n_checkers = __popc(checkers);
+    {
+        const bool slider = type == BISHOP || type == ROOK || type == QUEEN;
+        const unsigned long long blk = (slider && first_on_ray) ? line_to_me : bb;
+        const int c = checkers ? __ffs(checkers) - 1 : 0;
+        const unsigned lo = __shfl_sync(kFull, static_cast<unsigned>(blk), c);
+        const unsigned hi = __shfl_sync(kFull, static_cast<unsigned>(blk >> 32), c);
+        if (n_checkers == 1) target_mask = (static_cast<unsigned long long>(hi) << 32) | lo;
+        else if (n_checkers > 1) target_mask = 0ull;
+    }
     if (!mine) return 0ull;
 
     // ---- pseudo-legal targets ----
-    const int rank = sq >> 3, file = sq & 7;
     unsigned long long cand = 0ull, ep_target = 0ull;
     if (type == KNIGHT) {
         cand = knight_pattern(bb);
     } else if (type == KING) {
-        cand = king_pattern(bb);
-        if (!special) {
+        cand = king_pattern(bb) & ~danger;
+        // castling: neither the king's square nor the one it crosses nor the one it lands on may
+        // be attacked (on the first rank nothing the rook's jump uncovers or covers changes that)
+        if (!special && !in_check) {
             const int row = black ? 56 : 0;
             if ((fresh_rooks >> (row + 7)) & 1ull)
-                if (((occ >> (row + 5)) & 3ull) == 0ull) cand |= 1ull << (row + 6);
+                if (((occ >> (row + 5)) & 3ull) == 0ull && ((danger >> (row + 5)) & 3ull) == 0ull)
+                    cand |= 1ull << (row + 6);
             if ((fresh_rooks >> row) & 1ull)
-                if (((occ >> (row + 1)) & 7ull) == 0ull) cand |= 1ull << (row + 2);
+                if (((occ >> (row + 1)) & 7ull) == 0ull && ((danger >> (row + 2)) & 3ull) == 0ull)
+                    cand |= 1ull << (row + 2);
         }
+        return cand & ~own;
     } else if (type == PAWN) {
         const int up = black ? -8 : 8;
         const int f1 = sq + up;
@@ -143,7 +214,6 @@ __device__ __forceinline__ unsigned long long legal_word(unsigned word, int cont
             if (rank == (black ? 3 : 4)) {
                 if (file > 0 && ((ep_pawns >> (sq - 1)) & 1ull)) ep_target |= 1ull << (f1 - 1);
                 if (file < 7 && ((ep_pawns >> (sq + 1)) & 1ull)) ep_target |= 1ull << (f1 + 1);
-                cand |= ep_target;
             }
         }
     } else {
@@ -151,30 +221,17 @@ __device__ __forceinline__ unsigned long long legal_word(unsigned word, int cont
         if (type == ROOK || type == QUEEN) cand |= rays(sq, occ, false);
     }
     cand &= ~own;
-
-    // ---- king safety, candidate by candidate ----
-    unsigned long long legal = 0ull;
-    for (unsigned long long rest = cand; rest != 0ull; rest &= rest - 1ull) {
+    if (my_king == 0ull) return cand | (ep_target & ~own);  // no king to protect
+    // a piece that shields the king from a slider moves only along the shielding line
+    const bool pinned = first_on_ray && (beyond & (ray_diag ? e.diag : e.line)) != 0ull;
+    unsigned long long legal = cand & target_mask & (pinned ? line : ~0ull);
+    // en passant takes two pieces off one rank at once: tested on the position after the move
+    for (unsigned long long rest = ep_target & ~own; rest != 0ull; rest &= rest - 1ull) {
         const int t = __ffsll(static_cast<long long>(rest)) - 1;
         const unsigned long long tb = 1ull << t;
-        bool ok;
-        if (type == KING && (t - sq == 2 || sq - t == 2)) {
-            // castling: the rook jumps over the king; the king's start, crossed and landing
-            // squares must not be attacked in the position after the move
-            const int row = sq & 56;
-            const bool kingside = t > sq;
-            const unsigned long long rook_from = 1ull << (kingside ? row + 7 : row);
-            const unsigned long long rook_to = 1ull << (kingside ? row + 5 : row + 3);
-            const unsigned long long after = (occ & ~bb & ~rook_from) | tb | rook_to;
-            const int lo = kingside ? sq : t;
-            ok = !attacked(lo, after, e) && !attacked(lo + 1, after, e) && !attacked(lo + 2, after, e);
-        } else {
-            unsigned long long gone = tb & opp;
-            if (type == PAWN && (ep_target & tb)) gone = 1ull << (t - (black ? -8 : 8));
-            const unsigned long long after = ((occ & ~bb) & ~gone) | tb;
-            ok = my_king == 0ull || !attacked(type == KING ? t : king_sq, after, without(e, gone));
-        }
-        if (ok) legal |= tb;
+        const unsigned long long gone = 1ull << (t - (black ? -8 : 8));
+        const unsigned long long after = ((occ & ~bb) & ~gone) | tb;
+        if (!attacked(king_sq, after, without(e, gone))) legal |= tb;
     }
     return legal;
 }
