@@ -78,6 +78,72 @@ def sweep(enc, dev, batches=(1, 64, 512, 4096, 16384, 65536), steps=10, warmup=3
                           "data": "synthetic: piece counts U{2..32}, side to move 50/50, seed 2"}))
 
 
+def engine(enc, dev, n=1 << 20, steps=10, warmup=3):
+    """The engine kernels beside the evaluator, one JSON line each: the legal-move generator
+    and `step` on `n` random-playout positions made on the device (HBM-bound by their
+    algorithmic bytes, 323 and 137 B per board; measured against the copy bandwidth), and the
+    evaluator's fused expansion with and without the legality words given."""
+    import ctypes
+    from brokefish_b200 import _native
+    from brokefish_b200.env import random_playouts
+    hbm = 6650.0
+    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(path):
+        hbm = float(json.load(open(path)).get("hbm_gbs", hbm))
+    b, c, r, lg, _ = random_playouts(n, 11, device=dev)
+    mask = torch.empty(n, 32, dtype=torch.int64, device=dev)
+    chk = torch.empty(n, dtype=torch.uint8, device=dev)
+    count = (lg != 0).any(dim=1)
+    first = (lg != 0).float().argmax(dim=1)
+    w = lg[torch.arange(n, device=dev), first]
+    low = w & -w
+    bit = torch.where(low < 0, torch.full_like(low, 63), torch.log2(low.abs().clamp(min=1).double()).long())
+    move = torch.where(count, first * 64 + bit, torch.full_like(first, -1)).to(torch.int32)
+    nb, nc = torch.empty_like(b), torch.empty_like(c)
+    irr = torch.empty(n, dtype=torch.uint8, device=dev)
+    L, stream = _native.lib(), ctypes.c_void_p(torch.cuda.current_stream(dev).cuda_stream)
+    ptr = lambda t: ctypes.c_void_p(t.data_ptr())
+    flush = torch.empty(256 << 20, dtype=torch.uint8, device=dev)
+
+    def timed(fn):
+        for _ in range(warmup):
+            fn()
+        ms = []
+        for i in range(steps):
+            flush.fill_(i & 0xFF)
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record()
+            fn()
+            e1.record()
+            torch.cuda.synchronize(dev)
+            ms.append(e0.elapsed_time(e1))
+        return float(np.median(ms))
+
+    idx = dev.index or 0
+    for name, bytes_per_board, fn in (
+            ("movegen", 64 + 2 + 256 + 1,
+             lambda: _native.check(L.bf_movegen(idx, ptr(b), ptr(c), n, ptr(mask), ptr(chk), stream), "bf_movegen")),
+            ("step", 64 + 2 + 4 + 64 + 2 + 1,
+             lambda: _native.check(L.bf_step(idx, ptr(b), ptr(c), ptr(move), None, n, ptr(nb), ptr(nc), ptr(irr),
+                                             None, None, stream), "bf_step")),
+            ("step+movegen (play)", 64 + 2 + 4 + 64 + 2 + 1 + 256 + 1,
+             lambda: _native.check(L.bf_step(idx, ptr(b), ptr(c), ptr(move), None, n, ptr(nb), ptr(nc), ptr(irr),
+                                             ptr(mask), ptr(chk), stream), "bf_step"))):
+        t = timed(fn)
+        gbs = n * bytes_per_board / t / 1e6
+        print(json.dumps({"engine_kernel": name, "boards": n, "ms_per_launch_median": t, "boards_per_s": n / t * 1e3,
+                          "roofline": {"bound": "hbm", "achieved": gbs, "peak": hbm, "unit": "GB/s",
+                                       "frac": gbs / hbm, "algorithmic_bytes_per_board": bytes_per_board},
+                          "data": "synthetic: random-playout positions played on the device, seed 11"}))
+    m = 4096
+    t_given = timed(lambda: enc.forward_priors(b[:m], c[:m], r[:m], lg[:m], 96))
+    t_own = timed(lambda: enc.forward_priors(b[:m], c[:m], r[:m], None, 96))
+    t_plain = timed(lambda: enc.forward_full(b[:m], c[:m], r[:m]))
+    enc.check_status()
+    print(json.dumps({"fused_expansion_batch": m, "ms_logits_only": t_plain, "ms_priors_legality_given": t_given,
+                      "ms_priors_moves_generated_in_kernel": t_own}))
+
+
 def peaks():
     path = os.path.join(ROOT, "MEASURED_PEAKS.json")
     if os.path.exists(path):
@@ -165,6 +231,8 @@ def main() -> int:
                          "seed 100 + rank) instead of tiling the committed 4096")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--sweep", action="store_true", help="print one line per batch size 1..65536 and exit")
+    ap.add_argument("--engine", action="store_true",
+                    help="time the engine kernels (movegen, step) and the fused expansion; print their lines and exit")
     ap.add_argument("--phases", action="store_true",
                     help="add the in-kernel phase split (cycles per phase over 5 extra launches) to the line")
     ap.add_argument("--f16", action="store_true",
@@ -212,6 +280,10 @@ def main() -> int:
     if args.sweep:
         if rank == 0:
             sweep(enc, dev)
+        return 0
+    if args.engine:
+        if rank == 0:
+            engine(enc, dev)
         return 0
 
     if args.total:
