@@ -2139,8 +2139,10 @@ int bf_movegen(int device, const uint16_t* boards, const int16_t* control, int n
     if (boards == nullptr || control == nullptr || mask == nullptr)
         return fail(BF_EINVAL, "boards, control and mask must be non-null");
     BF_CUDA(cudaSetDevice(device));
-    bfmg::movegen_kernel<<<(n + 3) / 4, 128, 0, static_cast<cudaStream_t>(stream)>>>(
-        boards, control, n, reinterpret_cast<unsigned long long*>(mask), in_check);
+    bfmg::engine_board_kernel<false, false><<<(n + bfmg::kTpbThreads - 1) / bfmg::kTpbThreads, bfmg::kTpbThreads,
+                                               bfmg::kTpbSmem, static_cast<cudaStream_t>(stream)>>>(
+        boards, control, nullptr, nullptr, nullptr, n, nullptr, nullptr, nullptr,
+        reinterpret_cast<unsigned long long*>(mask), in_check, nullptr);
     BF_CUDA(cudaGetLastError());
     return BF_OK;
 }
@@ -2153,9 +2155,10 @@ int bf_step(int device, const uint16_t* boards, const int16_t* control, const in
     if (boards == nullptr || control == nullptr || move == nullptr || boards_out == nullptr || control_out == nullptr)
         return fail(BF_EINVAL, "boards, control, move, boards_out and control_out must be non-null");
     BF_CUDA(cudaSetDevice(device));
-    bfmg::step_kernel<<<(n + 3) / 4, 128, 0, static_cast<cudaStream_t>(stream)>>>(
-        boards, control, move, promo, n, boards_out, control_out, irreversible,
-        reinterpret_cast<unsigned long long*>(mask), in_check);
+    bfmg::engine_board_kernel<true, false><<<(n + bfmg::kTpbThreads - 1) / bfmg::kTpbThreads, bfmg::kTpbThreads,
+                                              bfmg::kTpbSmem, static_cast<cudaStream_t>(stream)>>>(
+        boards, control, move, promo, nullptr, n, boards_out, control_out, irreversible,
+        reinterpret_cast<unsigned long long*>(mask), in_check, nullptr);
     BF_CUDA(cudaGetLastError());
     return BF_OK;
 }
@@ -2167,8 +2170,10 @@ int bf_random_ply(int device, uint16_t* boards, int16_t* control, uint64_t* mask
     if (boards == nullptr || control == nullptr || mask == nullptr || r == nullptr)
         return fail(BF_EINVAL, "boards, control, mask and r must be non-null");
     BF_CUDA(cudaSetDevice(device));
-    bfmg::random_ply_kernel<<<(n + 3) / 4, 128, 0, static_cast<cudaStream_t>(stream)>>>(
-        boards, control, reinterpret_cast<unsigned long long*>(mask), r, promo, n, move);
+    bfmg::engine_board_kernel<true, true><<<(n + bfmg::kTpbThreads - 1) / bfmg::kTpbThreads, bfmg::kTpbThreads,
+                                             bfmg::kTpbSmem, static_cast<cudaStream_t>(stream)>>>(
+        boards, control, nullptr, promo, r, n, boards, control, nullptr,
+        reinterpret_cast<unsigned long long*>(mask), nullptr, move);
     BF_CUDA(cudaGetLastError());
     return BF_OK;
 }

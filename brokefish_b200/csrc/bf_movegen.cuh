@@ -236,152 +236,374 @@ __device__ __forceinline__ unsigned long long legal_word(unsigned word, int cont
     return legal;
 }
 
-// Castling rights of a board in FEN order KQkq as four bits (torch_impl.py:294-318): the king
-// and that corner's rook are alive and have never moved.  Warp-collective.
-__device__ __forceinline__ unsigned castling_bits(unsigned word) {
-    const bool intact = ((word >> 11) & 1u) == 0u && ((word >> 9) & 1u) == 0u;
-    const bool is_black = (word >> 10) & 1u;
-    const int type = (word >> 6) & 7, sq = word & 63;
-    const unsigned wk = __ballot_sync(kFull, intact && type == KING && !is_black) != 0u;
-    const unsigned bk = __ballot_sync(kFull, intact && type == KING && is_black) != 0u;
-    const bool rook = intact && type == ROOK;
-    const unsigned k = __ballot_sync(kFull, rook && !is_black && sq == 7) != 0u;
-    const unsigned q = __ballot_sync(kFull, rook && !is_black && sq == 0) != 0u;
-    const unsigned k2 = __ballot_sync(kFull, rook && is_black && sq == 63) != 0u;
-    const unsigned q2 = __ballot_sync(kFull, rook && is_black && sq == 56) != 0u;
-    return (wk & k) | ((wk & q) << 1) | ((bk & k2) << 2) | ((bk & q2) << 3);
+// ------------------------------------------------------------------------------------------
+// One THREAD per board: the stand-alone generator.  A board is 64 bytes; with a warp per board
+// every bitboard costs warp-wide reductions over 32 lanes that hold one piece each, and the
+// kernel is bound by instruction issue far below the memory roof.  A thread that keeps the whole
+// board needs no reductions at all: attacks of all the opponent's sliders come out of eight
+// loop-free fills over the set of them at once, checkers and shielding pieces out of the same
+// fills started at the king, and only the mover's own pieces are visited one by one.  Slot p has
+// the same piece type on almost every board (promotions aside), so the threads of a warp take
+// the same branch as they walk the slots.  Boards come in and legal words go out through shared
+// memory so that global accesses stay coalesced.
+// ------------------------------------------------------------------------------------------
+template <int kShift>
+__device__ __forceinline__ unsigned long long fill_ray(unsigned long long gen, unsigned long long occ,
+                                                       unsigned long long wrap) {
+    // the pieces' bits spread over empty squares in doubling steps (1, 2, 4), then one more
+    // step lands on the first occupied square; `wrap` clears the file a step must not arrive on
+    unsigned long long pro = ~occ & wrap;
+    if constexpr (kShift > 0) {
+        gen |= pro & (gen << kShift);
+        pro &= pro << kShift;
+        gen |= pro & (gen << (2 * kShift));
+        pro &= pro << (2 * kShift);
+        gen |= pro & (gen << (4 * kShift));
+        return (gen << kShift) & wrap;
+    } else {
+        gen |= pro & (gen >> -kShift);
+        pro &= pro >> -kShift;
+        gen |= pro & (gen >> (-2 * kShift));
+        pro &= pro >> (-2 * kShift);
+        gen |= pro & (gen >> (-4 * kShift));
+        return (gen >> -kShift) & wrap;
+    }
+}
+// Squares seen from every piece of the set `b` along the bishop or the rook lines.
+__device__ __forceinline__ unsigned long long fill_diag(unsigned long long b, unsigned long long occ) {
+    return fill_ray<9>(b, occ, ~kFileA) | fill_ray<7>(b, occ, ~kFileH) | fill_ray<-7>(b, occ, ~kFileA) |
+           fill_ray<-9>(b, occ, ~kFileH);
+}
+__device__ __forceinline__ unsigned long long fill_line(unsigned long long b, unsigned long long occ) {
+    return fill_ray<8>(b, occ, ~0ull) | fill_ray<-8>(b, occ, ~0ull) | fill_ray<1>(b, occ, ~kFileA) |
+           fill_ray<-1>(b, occ, ~kFileH);
+}
+// Squares a set of pawns of one colour attacks.
+__device__ __forceinline__ unsigned long long pawn_attacks(unsigned long long b, bool black_pawns) {
+    return black_pawns ? (((b >> 9) & ~kFileH) | ((b >> 7) & ~kFileA)) : (((b << 7) & ~kFileH) | ((b << 9) & ~kFileA));
+}
+// The whole rank, file or diagonal through two aligned squares (0 when they are not aligned).
+__device__ __forceinline__ unsigned long long line_through(int a, int b) {
+    const int ra = a >> 3, fa = a & 7, rb = b >> 3, fb = b & 7;
+    if (ra == rb) return 0xFFull << (8 * ra);
+    if (fa == fb) return kFileA << fa;
+    if (ra - fa == rb - fb) {
+        const int d = ra - fa;                                   // the a1-h8 diagonal moved up or down
+        return d >= 0 ? 0x8040201008040201ull << (8 * d) : 0x8040201008040201ull >> (-8 * d);
+    }
+    if (ra + fa == rb + fb) {
+        const int d = ra + fa - 7;                               // the h1-a8 diagonal moved up or down
+        return d >= 0 ? 0x0102040810204080ull << (8 * d) : 0x0102040810204080ull >> (-8 * d);
+    }
+    return 0ull;
 }
 
+constexpr int kTpbThreads = 128;
+constexpr int kTpbInStride = 17;      // 32-bit words per board in shared memory (16 + 1: no bank conflicts)
+constexpr int kTpbOutStride = 33;     // 64-bit words per board in shared memory (32 + 1)
+constexpr int kTpbSmem = kTpbThreads * (kTpbInStride * 4 + kTpbOutStride * 8);
+
+// The legal words of one board held by one thread: `my` = the board's 32 piece words as 16
+// 32-bit words, `out[0..31]` receives the legal-target word of every slot.  Returns whether the
+// side to move is in check.
+__device__ __forceinline__ unsigned piece_word(const unsigned* my, int p) {
+    return (my[p >> 1] >> (16 * (p & 1))) & 0xFFFFu;
+}
+__device__ __forceinline__ bool board_moves(const unsigned* my, bool black, unsigned long long* out) {
+    // ---- pass 1: bitboards ----
+    unsigned long long occ = 0, own = 0, e_pawns = 0, e_knights = 0, e_diag = 0, e_line = 0, e_king = 0;
+    unsigned long long ep_pawns = 0, fresh_rooks = 0, my_king = 0;
+#pragma unroll 1
+    for (int p = 0; p < 32; ++p) {
+        const unsigned word = piece_word(my, p);
+        out[p] = 0ull;
+        if ((word >> 11) & 1u) continue;
+        const bool is_black = (word >> 10) & 1u, special = (word >> 9) & 1u;
+        const int type = (word >> 6) & 7;
+        const unsigned long long bb = 1ull << (word & 63u);
+        occ |= bb;
+        if (is_black == black) {
+            own |= bb;
+            if (type == KING) my_king |= bb;
+            if (type == ROOK && !special) fresh_rooks |= bb;
+        } else {
+            if (type == PAWN) { e_pawns |= bb; if (special) ep_pawns |= bb; }
+            else if (type == KNIGHT) e_knights |= bb;
+            else if (type == KING) e_king |= bb;
+            else {
+                if (type == BISHOP || type == QUEEN) e_diag |= bb;
+                if (type == ROOK || type == QUEEN) e_line |= bb;
+            }
+        }
+    }
+    const unsigned long long opp = occ & ~own;
+    const int king_sq = my_king ? __ffsll(static_cast<long long>(my_king)) - 1 : 0;
+    // ---- what the opponent attacks, with the mover's king lifted off the board ----
+    const unsigned long long occ_nk = occ & ~my_king;
+    const unsigned long long danger = pawn_attacks(e_pawns, !black) | knight_pattern(e_knights) |
+                                      king_pattern(e_king) | fill_diag(e_diag, occ_nk) | fill_line(e_line, occ_nk);
+    // ---- checkers and the squares that answer a single check ----
+    const unsigned long long k_diag = fill_diag(my_king, occ), k_line = fill_line(my_king, occ);
+    const unsigned long long checkers = (knight_pattern(my_king) & e_knights) | (pawn_attacks(my_king, black) & e_pawns) |
+                                        (k_diag & e_diag) | (k_line & e_line);
+    const bool chk = checkers != 0ull;
+    unsigned long long target_mask = ~0ull;
+    if (chk) {
+        if (checkers & (checkers - 1ull)) target_mask = 0ull;               // two checkers: only the king moves
+        else {
+            unsigned long long between = 0ull;
+            if (checkers & k_diag & e_diag) between = k_diag & fill_diag(checkers, occ);
+            else if (checkers & k_line & e_line) between = k_line & fill_line(checkers, occ);
+            target_mask = checkers | between;
+        }
+    }
+    // ---- pieces that shield the king from a slider: the first own piece on a ray from the
+    //      king, with an enemy slider of that ray's kind next behind it ----
+    unsigned long long pinned = 0ull;
+    if (my_king != 0ull) {
+        const unsigned long long shields = (k_diag | k_line) & own;
+        const unsigned long long occ2 = occ & ~shields;
+        const unsigned long long k_diag2 = fill_diag(my_king, occ2), k_line2 = fill_line(my_king, occ2);
+        for (unsigned long long pin = (k_diag2 & ~k_diag) & e_diag; pin != 0ull; pin &= pin - 1ull)
+            pinned |= k_diag2 & fill_diag(pin & (0ull - pin), occ2) & shields;
+        for (unsigned long long pin = (k_line2 & ~k_line) & e_line; pin != 0ull; pin &= pin - 1ull)
+            pinned |= k_line2 & fill_line(pin & (0ull - pin), occ2) & shields;
+    }
+    // ---- the mover's pieces, one by one ----
+#pragma unroll 1
+    for (int p = 0; p < 32; ++p) {
+        const unsigned word = piece_word(my, p);
+        if (((word >> 11) & 1u) || (((word >> 10) & 1u) != 0u) != black) continue;
+        const bool special = (word >> 9) & 1u;
+        const int type = (word >> 6) & 7, sq = word & 63;
+        const int rank = sq >> 3, file = sq & 7;
+        const unsigned long long bb = 1ull << sq;
+        unsigned long long cand = 0ull, ep_target = 0ull;
+        if (type == KING) {
+            cand = king_pattern(bb) & ~danger;
+            if (!special && !chk) {
+                const int row = black ? 56 : 0;
+                if ((fresh_rooks >> (row + 7)) & 1ull)
+                    if (((occ >> (row + 5)) & 3ull) == 0ull && ((danger >> (row + 5)) & 3ull) == 0ull)
+                        cand |= 1ull << (row + 6);
+                if ((fresh_rooks >> row) & 1ull)
+                    if (((occ >> (row + 1)) & 7ull) == 0ull && ((danger >> (row + 2)) & 3ull) == 0ull)
+                        cand |= 1ull << (row + 2);
+            }
+            out[p] = cand & ~own;
+            continue;
+        }
+        if (type == KNIGHT) {
+            cand = knight_pattern(bb);
+        } else if (type == PAWN) {
+            const int up = black ? -8 : 8;
+            const int f1 = sq + up;
+            if (f1 >= 0 && f1 < 64) {
+                if (!((occ >> f1) & 1ull)) {
+                    cand |= 1ull << f1;
+                    const bool start = black ? rank == 6 : rank == 1;
+                    if (start && !((occ >> (f1 + up)) & 1ull)) cand |= 1ull << (f1 + up);
+                }
+                if (file > 0) cand |= (1ull << (f1 - 1)) & opp;
+                if (file < 7) cand |= (1ull << (f1 + 1)) & opp;
+                if (rank == (black ? 3 : 4)) {
+                    if (file > 0 && ((ep_pawns >> (sq - 1)) & 1ull)) ep_target |= 1ull << (f1 - 1);
+                    if (file < 7 && ((ep_pawns >> (sq + 1)) & 1ull)) ep_target |= 1ull << (f1 + 1);
+                }
+            }
+        } else {
+            if (type == BISHOP || type == QUEEN) cand |= fill_diag(bb, occ);
+            if (type == ROOK || type == QUEEN) cand |= fill_line(bb, occ);
+        }
+        cand &= ~own;
+        ep_target &= ~own;
+        if (my_king == 0ull) { out[p] = cand | ep_target; continue; }       // no king to protect
+        unsigned long long legal = cand & target_mask;
+        if (bb & pinned) legal &= line_through(king_sq, sq);
+        // en passant takes two pieces off one rank at once: tested on the position after it
+        for (unsigned long long rest = ep_target; rest != 0ull; rest &= rest - 1ull) {
+            const unsigned long long tb = rest & (0ull - rest);
+            const unsigned long long gone = black ? tb << 8 : tb >> 8;
+            const unsigned long long after = ((occ & ~bb) & ~gone) | tb;
+            const bool hit = (knight_pattern(my_king) & e_knights) != 0ull ||
+                             (pawn_attacks(my_king, black) & (e_pawns & ~gone)) != 0ull ||
+                             (king_pattern(my_king) & e_king) != 0ull ||
+                             (fill_diag(my_king, after) & e_diag) != 0ull ||
+                             (fill_line(my_king, after) & e_line) != 0ull;
+            if (!hit) legal |= tb;
+        }
+        out[p] = legal;
+    }
+    return chk;
+}
+
+// Castling rights KQkq as four bits of a board held by one thread (torch_impl.py:294-318).
+__device__ __forceinline__ unsigned board_rights(const unsigned* my) {
+    bool wk = false, bk = false, k = false, q = false, k2 = false, q2 = false;
+#pragma unroll 1
+    for (int p = 0; p < 32; ++p) {
+        const unsigned word = piece_word(my, p);
+        if (((word >> 11) & 1u) || ((word >> 9) & 1u)) continue;
+        const bool is_black = (word >> 10) & 1u;
+        const int type = (word >> 6) & 7, sq = word & 63;
+        if (type == KING) { if (is_black) bk = true; else wk = true; }
+        if (type == ROOK) {
+            if (!is_black) { k |= sq == 7; q |= sq == 0; }
+            else { k2 |= sq == 63; q2 |= sq == 56; }
+        }
+    }
+    return (wk && k ? 1u : 0u) | (wk && q ? 2u : 0u) | (bk && k2 ? 4u : 0u) | (bk && q2 ? 8u : 0u);
+}
+__device__ __forceinline__ void set_piece(unsigned* my, int p, unsigned v) {
+    const int sh = 16 * (p & 1);
+    my[p >> 1] = (my[p >> 1] & ~(0xFFFFu << sh)) | ((v & 0xFFFFu) << sh);
+}
 // Apply one move (`move` = slot * 64 + target, -1 = no move; `promo` 0..3 = N B R Q, negative =
-// queen) to a board, lane = slot: the reference's `step` without its hash
-// (brokefish/env/torch_impl.py:412-548).  Returns this slot's new word; `new_control` and
-// `irreversible` (capture, pawn move or a change of castling rights) are the same on every lane.
-__device__ __forceinline__ unsigned step_word(unsigned word, int control, int move, int promo, int lane,
-                                              int& new_control, bool& irreversible) {
+// queen) to a board held by one thread: the reference's `step` without its hash
+// (brokefish/env/torch_impl.py:412-548).  Capture: the first live piece on the target square, or
+// for a pawn the en passant victim, which carries the double-step flag and stands beside the
+// target's file neighbour, not on it.  `irreversible`: capture, pawn move or a change of
+// castling rights.
+__device__ __forceinline__ void board_step(unsigned* my, int control, int move, int promo, int& new_control,
+                                           bool& irreversible) {
     new_control = control;
     irreversible = false;
-    if (move < 0) return word;
+    if (move < 0) return;
     const int source = move >> 6, target = move & 63;
     const bool white = control > 0;
-    const unsigned mover = __shfl_sync(kFull, word, source);
+    const unsigned mover = piece_word(my, source);
     const int mtype = (mover >> 6) & 7, from = mover & 63;
     const bool is_pawn = mtype == PAWN;
-    const unsigned rights_before = castling_bits(word);
-    // capture: a live piece on the target square, or for a pawn the en passant victim, which
-    // carries the double-step flag and stands beside the target's file neighbour, not on it
-    const bool live = ((word >> 11) & 1u) == 0u;
+    const unsigned rights_before = board_rights(my);
     const unsigned victim_word = ((white ? 3u : 1u) << 9) + static_cast<unsigned>(target + (white ? -8 : 8));
-    const bool hit = (live && static_cast<int>(word & 63u) == target) || (is_pawn && word == victim_word);
-    const unsigned hits = __ballot_sync(kFull, hit);
-    const bool has_capture = hits != 0u;
-    unsigned w = word;
-    if (has_capture && lane == __ffs(hits) - 1) w = 1u << 11;
-    // castling: the rook on the king's side corner jumps over (found before any square changes)
     const int dx = target - from;
     const bool castling = mtype == KING && (dx == 2 || dx == -2);
     const int corner = (white ? 0 : 56) + (dx > 0 ? 7 : 0);
-    const unsigned rooks = __ballot_sync(kFull, ((w >> 6) & 7u) == ROOK && static_cast<int>(word & 63u) == corner);
-    if (lane == source) {
-        w = (w & ~63u & 0xFFFu) + static_cast<unsigned>(target);
+    int captured = -1, rook = -1;
+#pragma unroll 1
+    for (int p = 0; p < 32; ++p) {
+        const unsigned word = piece_word(my, p);
+        const bool live = ((word >> 11) & 1u) == 0u;
+        if (captured < 0 && ((live && static_cast<int>(word & 63u) == target) || (is_pawn && word == victim_word)))
+            captured = p;
+    }
+    if (captured >= 0) set_piece(my, captured, 1u << 11);
+    // the corner rook is looked for by its square before anything moved, by its type after the capture
+    if (castling) {
+#pragma unroll 1
+        for (int p = 0; p < 32; ++p) {
+            const unsigned word = piece_word(my, p);
+            const unsigned square = p == captured ? static_cast<unsigned>(target) : (word & 63u);
+            if (rook < 0 && ((word >> 6) & 7u) == ROOK && static_cast<int>(square) == corner) rook = p;
+        }
+    }
+    {
+        unsigned w = (piece_word(my, source) & ~63u & 0xFFFu) + static_cast<unsigned>(target);
         if (is_pawn && (target >> 3) == (white ? 7 : 0))
             w += static_cast<unsigned>(promo < 0 ? QUEEN : promo + KNIGHT) << 6;
         if (mtype == KING || mtype == ROOK) w |= 1u << 9;
+        set_piece(my, source, w);
     }
-    if (castling && rooks != 0u && lane == __ffs(rooks) - 1)
-        w = (w & ~63u & 0xFFFu) + static_cast<unsigned>((white ? 0 : 56) + (dx > 0 ? 5 : 3));
+    if (rook >= 0)
+        set_piece(my, rook, (piece_word(my, rook) & ~63u & 0xFFFu) + static_cast<unsigned>((white ? 0 : 56) + (dx > 0 ? 5 : 3)));
     // the en passant flag lives for one ply: clear every pawn's, set the double-stepper's
-    if (((w >> 6) & 7u) == PAWN) w &= ~(1u << 9) & 0xFFFu;
-    if (lane == source && is_pawn && (dx == 16 || dx == -16)) w |= 1u << 9;
-    const int mag = (has_capture || is_pawn) ? 1 : (control < 0 ? -control : control) + 1;
+#pragma unroll 1
+    for (int p = 0; p < 32; ++p) {
+        const unsigned word = piece_word(my, p);
+        if (((word >> 6) & 7u) == PAWN && ((word >> 9) & 1u)) set_piece(my, p, word & ~(1u << 9) & 0xFFFu);
+    }
+    if (is_pawn && (dx == 16 || dx == -16)) set_piece(my, source, piece_word(my, source) | (1u << 9));
+    const int mag = (captured >= 0 || is_pawn) ? 1 : (control < 0 ? -control : control) + 1;
     new_control = white ? -mag : mag;
-    irreversible = has_capture || is_pawn || castling_bits(w) != rights_before;
-    return w;
+    irreversible = captured >= 0 || is_pawn || board_rights(my) != rights_before;
 }
 
-// One warp per board: play `move` (with `promo`), then generate the legal moves of the result.
-__global__ void __launch_bounds__(128) step_kernel(const uint16_t* __restrict__ boards,
-                                                   const int16_t* __restrict__ control,
-                                                   const int* __restrict__ move, const signed char* __restrict__ promo,
-                                                   int n, uint16_t* __restrict__ boards_out,
-                                                   int16_t* __restrict__ control_out,
-                                                   unsigned char* __restrict__ irreversible,
-                                                   unsigned long long* __restrict__ mask,
-                                                   unsigned char* __restrict__ in_check) {
-    const int board = blockIdx.x * 4 + (threadIdx.x >> 5), lane = threadIdx.x & 31;
-    if (board >= n) return;
-    int nc;
-    bool irr;
-    const unsigned w = step_word(boards[static_cast<size_t>(board) * 32 + lane], control[board], move[board],
-                                 promo != nullptr ? promo[board] : -1, lane, nc, irr);
-    boards_out[static_cast<size_t>(board) * 32 + lane] = static_cast<uint16_t>(w);
-    if (lane == 0) {
-        control_out[board] = static_cast<int16_t>(nc);
-        if (irreversible != nullptr) irreversible[board] = irr ? 1 : 0;
-    }
-    if (mask != nullptr) {
-        bool chk;
-        const unsigned long long m = legal_word(w, nc, chk);
-        mask[static_cast<size_t>(board) * 32 + lane] = m;
-        if (in_check != nullptr && lane == 0) in_check[board] = chk ? 1 : 0;
-    }
-}
-
-// One warp per board: one ply of a uniform-random playout, in place.  The move is the
-// floor(r * count)-th legal move in (slot, square) order (r in [0,1), product in fp32), the board
-// is stepped and its new legal moves replace `mask`; a board without legal moves stays as it is
-// and reports move -1.
-__global__ void __launch_bounds__(128) random_ply_kernel(uint16_t* __restrict__ boards, int16_t* __restrict__ control,
-                                                         unsigned long long* __restrict__ mask,
-                                                         const float* __restrict__ r,
-                                                         const signed char* __restrict__ promo, int n,
-                                                         int* __restrict__ move_out) {
-    const int board = blockIdx.x * 4 + (threadIdx.x >> 5), lane = threadIdx.x & 31;
-    if (board >= n) return;
-    unsigned long long m = mask[static_cast<size_t>(board) * 32 + lane];
-    const int cnt = __popcll(m);
-    int incl = cnt;
-#pragma unroll
-    for (int d = 1; d < 32; d <<= 1) {
-        const int v = __shfl_up_sync(kFull, incl, d);
-        if (lane >= d) incl += v;
-    }
-    const int total = __shfl_sync(kFull, incl, 31);
-    int move = -1;
-    if (total > 0) {
-        int pick = static_cast<int>(__fmul_rn(r[board], static_cast<float>(total)));
-        pick = pick < total - 1 ? pick : total - 1;
-        const int k = pick - (incl - cnt);
-        const unsigned owners = __ballot_sync(kFull, k >= 0 && k < cnt);
-        const int owner = __ffs(owners) - 1;
-        int bit = 0;
-        if (lane == owner) {
-            for (int i = 0; i < k; ++i) m &= m - 1ull;
-            bit = __ffsll(static_cast<long long>(m)) - 1;
+// One thread per board, boards and legal words staged through shared memory for coalescing.
+// kStep: play `move` first (or, with kPick, the floor(r * count)-th legal move of the incoming
+// `mask` in (slot, square) order; a board without legal moves stays as it is) and write the new
+// board, control word and irreversible flag; `mask` non-null: the legal words of the resulting
+// board follow.  In place (boards_out == boards) is safe: a block reads all its boards first.
+template <bool kStep, bool kPick>
+__global__ void __launch_bounds__(kTpbThreads) engine_board_kernel(
+        const uint16_t* __restrict__ boards, const int16_t* __restrict__ control, const int* __restrict__ move,
+        const signed char* __restrict__ promo, const float* __restrict__ r, int n, uint16_t* boards_out,
+        int16_t* control_out, unsigned char* __restrict__ irreversible, unsigned long long* mask,
+        unsigned char* __restrict__ in_check, int* __restrict__ move_out) {
+    extern __shared__ unsigned long long tpb_smem[];
+    unsigned long long* s_out = tpb_smem;                                        // [128][33]
+    unsigned* s_in = reinterpret_cast<unsigned*>(tpb_smem + kTpbThreads * kTpbOutStride);   // [128][17]
+    const int tid = threadIdx.x;
+    const long first = static_cast<long>(blockIdx.x) * kTpbThreads;
+    const int here = static_cast<int>(min(static_cast<long>(kTpbThreads), n - first));
+    {
+        // coalesced load: the block's boards are one contiguous run of 16-byte pieces
+        const uint4* src = reinterpret_cast<const uint4*>(boards + first * 32);
+        for (int j = tid; j < here * 4; j += kTpbThreads) {
+            const uint4 v = __ldg(src + j);
+            unsigned* d = s_in + (j >> 2) * kTpbInStride + (j & 3) * 4;
+            d[0] = v.x; d[1] = v.y; d[2] = v.z; d[3] = v.w;
         }
-        move = owner * 64 + __shfl_sync(kFull, bit, owner);
+        if (kPick)
+            for (int j = tid; j < here * 32; j += kTpbThreads)
+                s_out[(j >> 5) * kTpbOutStride + (j & 31)] = mask[first * 32 + j];
     }
-    if (move_out != nullptr && lane == 0) move_out[board] = move;
-    if (move < 0) return;
-    int nc;
-    bool irr, chk;
-    const unsigned w = step_word(boards[static_cast<size_t>(board) * 32 + lane], control[board], move,
-                                 promo != nullptr ? promo[board] : -1, lane, nc, irr);
-    boards[static_cast<size_t>(board) * 32 + lane] = static_cast<uint16_t>(w);
-    if (lane == 0) control[board] = static_cast<int16_t>(nc);
-    mask[static_cast<size_t>(board) * 32 + lane] = legal_word(w, nc, chk);
-}
-
-// One warp per board.
-__global__ void __launch_bounds__(128) movegen_kernel(const uint16_t* __restrict__ boards,
-                                                      const int16_t* __restrict__ control, int n,
-                                                      unsigned long long* __restrict__ mask,
-                                                      unsigned char* __restrict__ in_check) {
-    const int board = blockIdx.x * 4 + (threadIdx.x >> 5), lane = threadIdx.x & 31;
-    if (board >= n) return;
-    bool chk;
-    const unsigned long long w = legal_word(boards[static_cast<size_t>(board) * 32 + lane], control[board], chk);
-    mask[static_cast<size_t>(board) * 32 + lane] = w;
-    if (in_check != nullptr && lane == 0) in_check[board] = chk ? 1 : 0;
+    __syncthreads();
+    bool moved = false;
+    if (tid < here) {
+        unsigned* my = s_in + tid * kTpbInStride;
+        unsigned long long* out = s_out + tid * kTpbOutStride;
+        int ctl = control[first + tid];
+        bool generate = mask != nullptr;
+        if (kStep) {
+            int mv = kPick ? -1 : move[first + tid];
+            if (kPick) {
+                int total = 0;
+#pragma unroll 1
+                for (int p = 0; p < 32; ++p) total += __popcll(out[p]);
+                if (total > 0) {
+                    int pick = static_cast<int>(__fmul_rn(r[first + tid], static_cast<float>(total)));
+                    pick = pick < total - 1 ? pick : total - 1;
+#pragma unroll 1
+                    for (int p = 0; p < 32 && mv < 0; ++p) {
+                        unsigned long long m = out[p];
+                        const int cnt = __popcll(m);
+                        if (pick < cnt) {
+                            for (int i = 0; i < pick; ++i) m &= m - 1ull;
+                            mv = p * 64 + __ffsll(static_cast<long long>(m)) - 1;
+                        }
+                        pick -= cnt;
+                    }
+                }
+                if (move_out != nullptr) move_out[first + tid] = mv;
+                generate = mv >= 0;                   // a finished game keeps its (empty) legal words
+            }
+            int nc;
+            bool irr;
+            board_step(my, ctl, mv, promo != nullptr ? promo[first + tid] : -1, nc, irr);
+            moved = !kPick || mv >= 0;
+            if (moved) {
+                control_out[first + tid] = static_cast<int16_t>(nc);
+                if (irreversible != nullptr) irreversible[first + tid] = irr ? 1 : 0;
+            }
+            ctl = nc;
+        }
+        if (generate) {
+            const bool chk = board_moves(my, ctl < 0, out);
+            if (in_check != nullptr) in_check[first + tid] = chk ? 1 : 0;
+        }
+    }
+    __syncthreads();
+    if (kStep) {
+        // coalesced store of the block's boards (all of them: a board that did not move is rewritten as it was)
+        uint4* dst = reinterpret_cast<uint4*>(boards_out + first * 32);
+        for (int j = tid; j < here * 4; j += kTpbThreads) {
+            const unsigned* d = s_in + (j >> 2) * kTpbInStride + (j & 3) * 4;
+            dst[j] = make_uint4(d[0], d[1], d[2], d[3]);
+        }
+    }
+    if (mask != nullptr)
+        for (int j = tid; j < here * 32; j += kTpbThreads)
+            mask[first * 32 + j] = s_out[(j >> 5) * kTpbOutStride + (j & 31)];
 }
 
 }  // namespace bfmg
