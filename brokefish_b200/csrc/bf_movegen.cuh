@@ -1,4 +1,6 @@
-// Legal-move generation for the 32-slot piece-list board, one warp per board, lane = slot.
+// Legal-move generation and move application for the 32-slot piece-list board, in two forms:
+// `legal_word`, one warp per board with lane = slot (what the evaluator's expansion warp calls),
+// and the stand-alone kernels further down, one thread per board.
 //
 // The contract of the reference's engine (brokefish/env/torch_impl.py:254-291, csrc/movegen.cuh):
 // `mask [n,32]` 64-bit words, bit s of word p set when the piece in slot p may legally move to
@@ -11,7 +13,7 @@
 // pawn: has just made its double step), bit 10 colour (1 black), bit 11 captured.  The control
 // word's sign is the side to move (negative: black).
 //
-// Method: bitboards built with warp-wide OR reductions; every enemy lane contributes the squares
+// Method of the warp form: bitboards built with warp-wide OR reductions; every enemy lane contributes the squares
 // its piece attacks with the mover's king lifted off the board (king moves and castling avoid
 // their union); the enemy lanes that attack the king are the checkers (one checker: the other
 // pieces may only capture it or step between; two: only the king moves); every lane walks the

@@ -5,7 +5,7 @@
 the piece in slot ``p`` may legally move to square ``s``; ``in_check [n]`` bool for the side
 to move.  ``step`` and ``play`` apply a move per board (torch_impl.py:412-548, 680-685; the
 position hash is not tracked), ``initial_boards`` is the start position (torch_impl.py:692-697)
-and ``random_playouts`` plays uniform-random games to make evaluator inputs.  One warp per board
+and ``random_playouts`` plays uniform-random games to make evaluator inputs.  One thread per board
 in ``libbrokefish_b200`` (C ABI ``bf_movegen``, ``bf_step``, ``bf_random_ply``); CUDA tensors
 in, CUDA tensors out, on the current stream.  There is no CPU path.
 """

@@ -114,7 +114,7 @@ int bf_forward_leaves(bf_handle* h, const uint16_t* boards, const int16_t* contr
  * castling the king's two-square move, en passant a pawn's diagonal move to an empty square);
  * `in_check` [n] (may be NULL) for the side to move.  The engine contract of the reference's
  * `movegen` (brokefish/env/torch_impl.py:254-291; csrc/movegen.cuh): the input generator of the
- * evaluator's legality words and of the search's node masks.  One warp per board, one launch on
+ * evaluator's legality words and of the search's node masks.  One thread per board, one launch on
  * `stream`; needs no handle. */
 int bf_movegen(int device, const uint16_t* boards, const int16_t* control, int n, uint64_t* mask,
                unsigned char* in_check, void* stream);
@@ -127,7 +127,7 @@ int bf_movegen(int device, const uint16_t* boards, const int16_t* control, int n
  * reference's `step` without its position hash (brokefish/env/torch_impl.py:412-548;
  * csrc/movegen.cuh).  When `mask` is non-NULL the legal moves of the NEW position follow in the
  * same launch (bf_movegen's outputs), which is one ply of a self-play loop.  Moves are not
- * checked for legality.  One warp per board; needs no handle. */
+ * checked for legality.  One thread per board; needs no handle. */
 int bf_step(int device, const uint16_t* boards, const int16_t* control, const int* move,
             const signed char* promo, int n, uint16_t* boards_out, int16_t* control_out,
             unsigned char* irreversible, uint64_t* mask, unsigned char* in_check, void* stream);
