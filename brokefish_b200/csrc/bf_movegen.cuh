@@ -315,12 +315,14 @@ __device__ __forceinline__ bool board_moves(const unsigned* my, bool black, unsi
     // ---- pass 1: bitboards ----
     unsigned long long occ = 0, own = 0, e_pawns = 0, e_knights = 0, e_diag = 0, e_line = 0, e_king = 0;
     unsigned long long ep_pawns = 0, fresh_rooks = 0, my_king = 0;
+    bool by_slot = true;                 // white in slots 0-15, black in 16-31, as the engine keeps them
 #pragma unroll 1
     for (int p = 0; p < 32; ++p) {
         const unsigned word = piece_word(my, p);
         out[p] = 0ull;
         if ((word >> 11) & 1u) continue;
         const bool is_black = (word >> 10) & 1u, special = (word >> 9) & 1u;
+        by_slot &= is_black == (p >= 16);
         const int type = (word >> 6) & 7;
         const unsigned long long bb = 1ull << (word & 63u);
         occ |= bb;
@@ -371,9 +373,11 @@ __device__ __forceinline__ bool board_moves(const unsigned* my, bool black, unsi
         for (unsigned long long pin = (k_line2 & ~k_line) & e_line; pin != 0ull; pin &= pin - 1ull)
             pinned |= k_line2 & fill_line(pin & (0ull - pin), occ2) & shields;
     }
-    // ---- the mover's pieces, one by one ----
+    // ---- the mover's pieces, one by one: its sixteen slots (all thirty-two for a board that
+    //      does not keep the colours apart by slot) ----
+    const int p_lo = by_slot ? (black ? 16 : 0) : 0, p_hi = by_slot ? p_lo + 16 : 32;
 #pragma unroll 1
-    for (int p = 0; p < 32; ++p) {
+    for (int p = p_lo; p < p_hi; ++p) {
         const unsigned word = piece_word(my, p);
         if (((word >> 11) & 1u) || (((word >> 10) & 1u) != 0u) != black) continue;
         const bool special = (word >> 9) & 1u;
