@@ -300,6 +300,29 @@ __device__ __forceinline__ unsigned long long line_through(int a, int b) {
     return 0ull;
 }
 
+// One sliding piece along one line without loops or fills: on the line's squares other than the
+// piece's own, subtracting the piece's bit from the occupancy flips exactly the squares up to and
+// including the first occupied one above it; the same on the bit-reversed board gives the squares
+// below it.
+__device__ __forceinline__ unsigned long long line_attacks(unsigned long long s, unsigned long long occ,
+                                                           unsigned long long line_ex) {
+    const unsigned long long o = occ & line_ex;
+    const unsigned long long up = o - s;
+    const unsigned long long down = __brevll(__brevll(o) - __brevll(s));
+    return (up ^ down) & line_ex;
+}
+// The rank, file and two diagonals through a square, without the square itself.
+__device__ __forceinline__ unsigned long long rank_ex(int sq) { return (0xFFull << (sq & 56)) ^ (1ull << sq); }
+__device__ __forceinline__ unsigned long long file_ex(int sq) { return (kFileA << (sq & 7)) ^ (1ull << sq); }
+__device__ __forceinline__ unsigned long long diag_ex(int sq) {
+    const int d = (sq >> 3) - (sq & 7);
+    return (d >= 0 ? 0x8040201008040201ull << (8 * d) : 0x8040201008040201ull >> (-8 * d)) ^ (1ull << sq);
+}
+__device__ __forceinline__ unsigned long long anti_ex(int sq) {
+    const int d = (sq >> 3) + (sq & 7) - 7;
+    return (d >= 0 ? 0x0102040810204080ull << (8 * d) : 0x0102040810204080ull >> (-8 * d)) ^ (1ull << sq);
+}
+
 constexpr int kTpbThreads = 128;
 constexpr int kTpbInStride = 17;      // 32-bit words per board in shared memory (16 + 1: no bank conflicts)
 constexpr int kTpbOutStride = 33;     // 64-bit words per board in shared memory (32 + 1)
@@ -418,8 +441,10 @@ __device__ __forceinline__ bool board_moves(const unsigned* my, bool black, unsi
                 }
             }
         } else {
-            if (type == BISHOP || type == QUEEN) cand |= fill_diag(bb, occ);
-            if (type == ROOK || type == QUEEN) cand |= fill_line(bb, occ);
+            if (type == BISHOP || type == QUEEN)
+                cand |= line_attacks(bb, occ, diag_ex(sq)) | line_attacks(bb, occ, anti_ex(sq));
+            if (type == ROOK || type == QUEEN)
+                cand |= line_attacks(bb, occ, rank_ex(sq)) | line_attacks(bb, occ, file_ex(sq));
         }
         cand &= ~own;
         ep_target &= ~own;
