@@ -323,6 +323,16 @@ __device__ __forceinline__ unsigned long long anti_ex(int sq) {
     return (d >= 0 ? 0x0102040810204080ull << (8 * d) : 0x0102040810204080ull >> (-8 * d)) ^ (1ull << sq);
 }
 
+// Squares one piece `b` (a single bit) sees along the bishop or the rook lines.
+__device__ __forceinline__ unsigned long long piece_diag(unsigned long long b, unsigned long long occ) {
+    const int sq = __ffsll(static_cast<long long>(b)) - 1;
+    return line_attacks(b, occ, diag_ex(sq)) | line_attacks(b, occ, anti_ex(sq));
+}
+__device__ __forceinline__ unsigned long long piece_line(unsigned long long b, unsigned long long occ) {
+    const int sq = __ffsll(static_cast<long long>(b)) - 1;
+    return line_attacks(b, occ, rank_ex(sq)) | line_attacks(b, occ, file_ex(sq));
+}
+
 constexpr int kTpbThreads = 128;
 constexpr int kTpbInStride = 17;      // 32-bit words per board in shared memory (16 + 1: no bank conflicts)
 constexpr int kTpbOutStride = 33;     // 64-bit words per board in shared memory (32 + 1)
@@ -370,7 +380,10 @@ __device__ __forceinline__ bool board_moves(const unsigned* my, bool black, unsi
     const unsigned long long danger = pawn_attacks(e_pawns, !black) | knight_pattern(e_knights) |
                                       king_pattern(e_king) | fill_diag(e_diag, occ_nk) | fill_line(e_line, occ_nk);
     // ---- checkers and the squares that answer a single check ----
-    const unsigned long long k_diag = fill_diag(my_king, occ), k_line = fill_line(my_king, occ);
+    const unsigned long long kd_ex = diag_ex(king_sq), ka_ex = anti_ex(king_sq), kr_ex = rank_ex(king_sq),
+                             kf_ex = file_ex(king_sq);
+    const unsigned long long k_diag = line_attacks(my_king, occ, kd_ex) | line_attacks(my_king, occ, ka_ex);
+    const unsigned long long k_line = line_attacks(my_king, occ, kr_ex) | line_attacks(my_king, occ, kf_ex);
     const unsigned long long checkers = (knight_pattern(my_king) & e_knights) | (pawn_attacks(my_king, black) & e_pawns) |
                                         (k_diag & e_diag) | (k_line & e_line);
     const bool chk = checkers != 0ull;
@@ -379,8 +392,8 @@ __device__ __forceinline__ bool board_moves(const unsigned* my, bool black, unsi
         if (checkers & (checkers - 1ull)) target_mask = 0ull;               // two checkers: only the king moves
         else {
             unsigned long long between = 0ull;
-            if (checkers & k_diag & e_diag) between = k_diag & fill_diag(checkers, occ);
-            else if (checkers & k_line & e_line) between = k_line & fill_line(checkers, occ);
+            if (checkers & k_diag & e_diag) between = k_diag & piece_diag(checkers, occ);
+            else if (checkers & k_line & e_line) between = k_line & piece_line(checkers, occ);
             target_mask = checkers | between;
         }
     }
@@ -390,11 +403,12 @@ __device__ __forceinline__ bool board_moves(const unsigned* my, bool black, unsi
     if (my_king != 0ull) {
         const unsigned long long shields = (k_diag | k_line) & own;
         const unsigned long long occ2 = occ & ~shields;
-        const unsigned long long k_diag2 = fill_diag(my_king, occ2), k_line2 = fill_line(my_king, occ2);
+        const unsigned long long k_diag2 = line_attacks(my_king, occ2, kd_ex) | line_attacks(my_king, occ2, ka_ex);
+        const unsigned long long k_line2 = line_attacks(my_king, occ2, kr_ex) | line_attacks(my_king, occ2, kf_ex);
         for (unsigned long long pin = (k_diag2 & ~k_diag) & e_diag; pin != 0ull; pin &= pin - 1ull)
-            pinned |= k_diag2 & fill_diag(pin & (0ull - pin), occ2) & shields;
+            pinned |= k_diag2 & piece_diag(pin & (0ull - pin), occ2) & shields;
         for (unsigned long long pin = (k_line2 & ~k_line) & e_line; pin != 0ull; pin &= pin - 1ull)
-            pinned |= k_line2 & fill_line(pin & (0ull - pin), occ2) & shields;
+            pinned |= k_line2 & piece_line(pin & (0ull - pin), occ2) & shields;
     }
     // ---- the mover's pieces, one by one: its sixteen slots (all thirty-two for a board that
     //      does not keep the colours apart by slot) ----
@@ -459,8 +473,8 @@ __device__ __forceinline__ bool board_moves(const unsigned* my, bool black, unsi
             const bool hit = (knight_pattern(my_king) & e_knights) != 0ull ||
                              (pawn_attacks(my_king, black) & (e_pawns & ~gone)) != 0ull ||
                              (king_pattern(my_king) & e_king) != 0ull ||
-                             (fill_diag(my_king, after) & e_diag) != 0ull ||
-                             (fill_line(my_king, after) & e_line) != 0ull;
+                             ((line_attacks(my_king, after, kd_ex) | line_attacks(my_king, after, ka_ex)) & e_diag) != 0ull ||
+                             ((line_attacks(my_king, after, kr_ex) | line_attacks(my_king, after, kf_ex)) & e_line) != 0ull;
             if (!hit) legal |= tb;
         }
         out[p] = legal;

@@ -141,11 +141,43 @@ def step_answers(env) -> None:
     np.savez_compressed(os.path.join(HERE, "ref_step.npz"), **out)
 
 
+def shuffled_answers(env) -> None:
+    """The engine on boards whose slots do not keep the colours apart: 512 playout positions with
+    the thirty non-king slots permuted at random (the kings stay in slots 15 and 31), one random
+    legal move each.  Every rule reads colour, type and square from the word, so the reference's
+    answers are the same moves under the same permutation; a kernel that walks "its own sixteen
+    slots" must notice that it cannot here."""
+    z = np.load(os.path.join(HERE, "positions_4096_seed1.npz"))
+    n = 512
+    gen = torch.Generator(device="cpu").manual_seed(21)
+    boards, control = torch.from_numpy(z["boards"][:n]).clone(), torch.from_numpy(z["control"][:n])
+    others = torch.tensor([i for i in range(32) if i not in (15, 31)])
+    for i in range(n):
+        boards[i, others] = boards[i, others[torch.randperm(30, generator=gen)]]
+    mask, chk = env.movegen(boards, control)
+    legal = env.bitset_to_bool(mask).reshape(n, 32 * 64)
+    counts = legal.sum(dim=1)
+    pick = torch.minimum((torch.rand(n, generator=gen) * counts.clamp(min=1).float()).long(), (counts - 1).clamp(min=0))
+    move = (legal.cumsum(dim=1) > pick[:, None]).float().argmax(dim=1)
+    move = torch.where(counts > 0, move, torch.full_like(move, -1))
+    promo = torch.randint(0, 4, (n,), generator=gen)
+    nb, nc, _, irr = env.step(boards, control, move, promo=promo)
+    nm, nchk = env.movegen(nb, nc)
+    np.savez_compressed(os.path.join(HERE, "ref_shuffled.npz"),
+                        boards=boards.numpy().astype(np.int16), control=control.numpy().astype(np.int16),
+                        legal=mask.numpy().astype(np.int64).view(np.uint64), in_check=chk.numpy(),
+                        move=move.numpy().astype(np.int32), promo=promo.numpy().astype(np.int8),
+                        next_boards=nb.numpy().astype(np.int16), next_control=nc.numpy().astype(np.int16),
+                        irreversible=irr.numpy(), next_legal=nm.numpy().astype(np.int64).view(np.uint64),
+                        next_in_check=nchk.numpy())
+
+
 def main() -> int:
     ap = argparse.ArgumentParser()
     ap.add_argument("--reference", default="/root/reference")
     ap.add_argument("--skip-positions", action="store_true")
     ap.add_argument("--only-step", action="store_true", help="write ref_step.npz and stop")
+    ap.add_argument("--only-shuffled", action="store_true", help="write ref_shuffled.npz and stop")
     args = ap.parse_args()
     sys.path.insert(0, args.reference)
     sys.dont_write_bytecode = True
@@ -154,6 +186,9 @@ def main() -> int:
     from brokefish.env import torch_impl as env                      # reference
     if args.only_step:
         step_answers(env)
+        return 0
+    if args.only_shuffled:
+        shuffled_answers(env)
         return 0
     from brokefish.nn import quant as rq                             # reference
     from brokefish.nn.cuda_impl import _fold_norm                    # reference
@@ -311,6 +346,7 @@ def main() -> int:
 
     print("step known answers", flush=True)
     step_answers(env)
+    shuffled_answers(env)
 
     print("scheme known answers", flush=True)
     g = torch.Generator().manual_seed(1234)

@@ -157,3 +157,34 @@ def test_random_playouts_on_the_gpu_reproduce_the_reference_made_position_files(
     i = int(np.argmax(pos256["plies"] == 0))
     sb, sc = initial_boards(2)
     assert np.array_equal(sb[1].cpu().numpy(), pos256["boards"][i]) and int(sc[0]) == 1
+
+
+@pytest.mark.gpu
+def test_boards_that_do_not_keep_the_colours_apart_by_slot():
+    """512 positions with their thirty non-king slots permuted at random: the stand-alone kernels
+    (which normally walk only the mover's sixteen slots) and the evaluator's in-kernel generator
+    give the reference engine's legal words, check flags, moved boards and next legal words."""
+    from brokefish_b200.env import movegen, play
+    z = np.load(os.path.join(GOLDEN, "ref_shuffled.npz"))
+    cu = lambda a: torch.from_numpy(np.ascontiguousarray(a)).cuda()
+    b, c = cu(z["boards"]), cu(z["control"])
+    mask, chk = movegen(b, c)
+    assert np.array_equal(mask.cpu().numpy().view(np.uint64), z["legal"])
+    assert np.array_equal(chk.cpu().numpy(), z["in_check"].astype(bool))
+    nb, nc, nm, nk = play(b, c, cu(z["move"]), cu(z["promo"]))
+    assert np.array_equal(nb.cpu().numpy(), z["next_boards"]) and np.array_equal(nc.cpu().numpy(), z["next_control"])
+    assert np.array_equal(nm.cpu().numpy().view(np.uint64), z["next_legal"])
+    assert np.array_equal(nk.cpu().numpy(), z["next_in_check"].astype(bool))
+    # the warp-per-board form inside the evaluator: generated moves == given moves
+    from brokefish_b200.nn import encoder_impl
+    from brokefish_b200.nn.model import BrokefishNet, seeded_state
+    net = BrokefishNet().eval()
+    net.load_state_dict(seeded_state(seed=0, std=0.02))
+    enc = encoder_impl("cuda")(net)
+    rep = torch.zeros(b.shape[0], dtype=torch.uint8, device="cuda")
+    legal = torch.from_numpy(z["legal"].view(np.int64).copy()).cuda()
+    want = [x.clone() for x in enc.forward_priors(b, c, rep, legal, 96)]
+    got = enc.forward_priors(b, c, rep, None, 96)
+    assert torch.equal(got[1], want[1]) and torch.equal(got[2], want[2])
+    assert torch.equal(got[0].view(torch.int16), want[0].view(torch.int16))
+    enc.close()
