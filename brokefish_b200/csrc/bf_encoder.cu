@@ -2163,6 +2163,19 @@ int bf_step(int device, const uint16_t* boards, const int16_t* control, const in
     return BF_OK;
 }
 
+int bf_terminal(int device, const uint64_t* mask, const unsigned char* in_check, const int16_t* control,
+                const uint16_t* boards, int n, unsigned char* code, signed char* result, void* stream) {
+    if (n < 0) return fail(BF_EINVAL, "n must be >= 0");
+    if (n == 0) return BF_OK;
+    if (mask == nullptr || in_check == nullptr || control == nullptr || boards == nullptr || code == nullptr)
+        return fail(BF_EINVAL, "mask, in_check, control, boards and code must be non-null");
+    BF_CUDA(cudaSetDevice(device));
+    bfmg::terminal_kernel<<<(n + 127) / 128, 128, 0, static_cast<cudaStream_t>(stream)>>>(
+        reinterpret_cast<const unsigned long long*>(mask), in_check, control, boards, n, code, result);
+    BF_CUDA(cudaGetLastError());
+    return BF_OK;
+}
+
 int bf_random_ply(int device, uint16_t* boards, int16_t* control, uint64_t* mask, const float* r,
                   const signed char* promo, int n, int* move, void* stream) {
     if (n < 0) return fail(BF_EINVAL, "n must be >= 0");

@@ -651,4 +651,50 @@ __global__ void __launch_bounds__(kTpbThreads) engine_board_kernel(
             mask[first * 32 + j] = s_out[(j >> 5) * kTpbOutStride + (j & 31)];
 }
 
+// Why a game is over, one thread per board (brokefish/env/torch_impl.py:632-676 without the
+// repetition test, which needs the game's history): 1 checkmate, 2 stalemate (no legal move,
+// with or without check), else 3 when the control word's magnitude has reached 101 (fifty moves
+// without capture or pawn move), else 5 when neither side can mate -- no pawn, rook or queen and
+// either no knight and every bishop on one colour of squares, or one knight and no bishop
+// (torch_impl.py:604-629) -- else 0.  `result` is -1 for checkmate (the side to move lost), else 0.
+__global__ void __launch_bounds__(128) terminal_kernel(const unsigned long long* __restrict__ mask,
+                                                       const unsigned char* __restrict__ in_check,
+                                                       const int16_t* __restrict__ control,
+                                                       const uint16_t* __restrict__ boards, int n,
+                                                       unsigned char* __restrict__ code, signed char* __restrict__ result) {
+    const long board = static_cast<long>(blockIdx.x) * blockDim.x + threadIdx.x;
+    if (board >= n) return;
+    unsigned long long any = 0ull;
+    const ulonglong2* m2 = reinterpret_cast<const ulonglong2*>(mask + board * 32);
+#pragma unroll 4
+    for (int p = 0; p < 16; ++p) {
+        const ulonglong2 v = __ldg(m2 + p);
+        any |= v.x | v.y;
+    }
+    int heavy = 0, knights = 0, bishops = 0, dark = 0;
+    const uint4* b4 = reinterpret_cast<const uint4*>(boards + board * 32);
+#pragma unroll
+    for (int q = 0; q < 4; ++q) {
+        const uint4 v = __ldg(b4 + q);
+        const unsigned w[4] = {v.x, v.y, v.z, v.w};
+#pragma unroll
+        for (int k = 0; k < 8; ++k) {
+            const unsigned word = (w[k >> 1] >> (16 * (k & 1))) & 0xFFFFu;
+            if ((word >> 11) & 1u) continue;
+            const int type = (word >> 6) & 7, sq = word & 63;
+            heavy += type == PAWN || type == ROOK || type == QUEEN;
+            knights += type == KNIGHT;
+            bishops += type == BISHOP;
+            dark += type == BISHOP && (((sq & 7) + (sq >> 3)) & 1) == 0;
+        }
+    }
+    const int c = control[board];
+    int out = 0;
+    if (any == 0ull) out = in_check[board] ? 1 : 2;
+    else if ((c < 0 ? -c : c) >= 101) out = 3;
+    else if (heavy == 0 && ((knights == 0 && (dark == 0 || dark == bishops)) || (knights == 1 && bishops == 0))) out = 5;
+    code[board] = static_cast<unsigned char>(out);
+    if (result != nullptr) result[board] = out == 1 ? -1 : 0;
+}
+
 }  // namespace bfmg

@@ -100,6 +100,34 @@ def play(boards, control, move, promo=None):
     return nb, nc, mask, chk
 
 
+NONE, CHECKMATE, STALEMATE, FIFTY_MOVE, REPETITION, INSUFFICIENT = range(6)
+
+
+def terminal(mask, in_check, control, boards, hash=None, ring=None, length=None):
+    """``(code [n] uint8, result [n] int8)``: why each game is over (1 checkmate, 2 stalemate,
+    3 fifty-move rule, 5 insufficient material, 0 not over; the first that applies) and its result
+    for the side to move (-1 checkmate, else 0) -- the reference's ``terminal``
+    (brokefish/env/torch_impl.py:632-676) called without a history.  Threefold repetition (code
+    4) needs the game's hash ring, which is not kept here: passing one raises."""
+    if hash is not None or ring is not None or length is not None:
+        raise NotImplementedError("the repetition test needs the position hash and its ring, which are not built")
+    n = _check_position(boards, control)
+    dev = boards.device
+    if tuple(mask.shape) != (n, 32) or mask.dtype is not torch.int64 or not mask.is_cuda:
+        raise ValueError(f"mask must be a CUDA int64 tensor of shape [{n}, 32]")
+    if tuple(in_check.shape) != (n,) or not in_check.is_cuda:
+        raise ValueError(f"in_check must be a CUDA tensor of shape [{n}]")
+    chk = in_check.to(torch.uint8).contiguous()
+    code = torch.zeros(n, dtype=torch.uint8, device=dev)
+    result = torch.zeros(n, dtype=torch.int8, device=dev)
+    if n:
+        stream = ctypes.c_void_p(torch.cuda.current_stream(dev).cuda_stream)
+        _native.check(_native.lib().bf_terminal(dev.index or 0, _ptr(mask.contiguous()), _ptr(chk),
+                                                _ptr(control.contiguous()), _ptr(boards.contiguous()), n,
+                                                _ptr(code), _ptr(result), stream), "bf_terminal")
+    return code, result
+
+
 def random_playouts(n: int, seed: int, max_plies: int = 120, device="cuda"):
     """``n`` uniform-random legal games from the start position, game ``i`` stopped after
     ``plies[i]`` moves (uniform in 0..max_plies) or at its end: ``(boards, control, rep, legal,

@@ -132,6 +132,16 @@ int bf_step(int device, const uint16_t* boards, const int16_t* control, const in
             const signed char* promo, int n, uint16_t* boards_out, int16_t* control_out,
             unsigned char* irreversible, uint64_t* mask, unsigned char* in_check, void* stream);
 
+/* Why each of `n` games is over, from a position's legal words, check flag, control word and
+ * board (device pointers): `code` [n] uint8 = 1 checkmate, 2 stalemate, 3 fifty-move rule
+ * (control magnitude >= 101), 5 insufficient material, 0 not over -- the first that applies;
+ * `result` [n] int8 (may be NULL) = -1 for checkmate, else 0, from the side to move's point of
+ * view.  The reference's `terminal` called without a history
+ * (brokefish/env/torch_impl.py:632-676, 604-629); its code 4, threefold repetition, needs the
+ * game's hash ring, which this library does not keep. */
+int bf_terminal(int device, const uint64_t* mask, const unsigned char* in_check, const int16_t* control,
+                const uint16_t* boards, int n, unsigned char* code, signed char* result, void* stream);
+
 /* One ply of a uniform-random playout, in place (device pointers): from `mask` (the legal moves
  * of `boards`, bf_movegen's output) the floor(r[i] * count)-th legal move in (slot, square) order
  * is played with promotion type `promo[i]` (may be NULL = queen), and `mask` becomes the legal

@@ -172,12 +172,42 @@ def shuffled_answers(env) -> None:
                         next_in_check=nchk.numpy())
 
 
+def terminal_answers(env) -> None:
+    """The engine's `terminal` (no history) on the two playout sets and on hand-made positions:
+    bare kings, one minor piece, bishops on one and on two colours of squares, two knights, a
+    pawn, the fifty-move counter at and just under its limit, mate and stalemate (also with the
+    counter at its limit: mate comes first)."""
+    fens = ["8/8/8/4k3/8/8/8/4K3 w - - 0 1", "8/8/8/4k3/8/8/8/4KN2 w - - 0 1", "8/8/8/4k3/8/8/8/4KB2 b - - 0 1",
+            "8/8/8/4k3/8/8/8/2B1KB2 w - - 0 1", "8/8/8/4k3/8/8/2B5/4KB2 w - - 0 1", "8/8/8/3bk3/8/8/8/4KB2 w - - 0 1",
+            "8/8/8/2b1k3/8/8/8/4KB2 w - - 0 1", "8/8/8/4k3/8/8/8/3NKN2 w - - 0 1", "8/8/8/4k3/8/8/8/3NKB2 w - - 0 1",
+            "8/8/8/3nk3/8/8/8/4KN2 w - - 0 1", "8/8/8/4k3/8/8/4P3/4K3 w - - 0 1", "8/8/8/4k3/8/8/8/4KR2 b - - 0 1",
+            "8/8/8/4k3/8/8/4P3/4K3 w - - 100 80", "8/8/8/4k3/8/8/4P3/4K3 b - - 99 80", "8/8/8/4k3/8/8/4P3/4K3 b - - 120 90",
+            "7k/5Q2/6K1/8/8/8/8/8 b - - 0 1", "7k/6Q1/6K1/8/8/8/8/8 b - - 0 1", "7k/6Q1/6K1/8/8/8/8/8 b - - 100 70",
+            "7k/5Q2/6K1/8/8/8/8/8 b - - 100 70", "rnbqkbnr/pppppppp/8/8/8/8/PPPPPPPP/RNBQKBNR w KQkq - 0 1",
+            "1r1r2Rk/pp5p/4b2n/1P5P/n1Ppp3/R4P1p/1B1KP3/8 b - - 1 1"]
+    fb, fc = zip(*(env.from_fen(f) for f in fens))
+    fb, fc = torch.cat(fb), torch.cat(fc)
+    fm, fk = env.movegen(fb, fc)
+    code, result = env.terminal(fm, fk, fc, fb)
+    out = {"fens": np.array(fens), "fen_boards": fb.numpy().astype(np.int16), "fen_control": fc.numpy().astype(np.int16),
+           "fen_legal": fm.numpy().astype(np.int64).view(np.uint64), "fen_in_check": fk.numpy(),
+           "fen_code": code.numpy(), "fen_result": result.numpy()}
+    for n_pos, seed in ((256, 0), (4096, 1)):
+        z = np.load(os.path.join(HERE, f"positions_{n_pos}_seed{seed}.npz"))
+        b, c = torch.from_numpy(z["boards"]), torch.from_numpy(z["control"])
+        m, k = env.movegen(b, c)
+        code, result = env.terminal(m, k, c, b)
+        out[f"code_{n_pos}"], out[f"result_{n_pos}"] = code.numpy(), result.numpy()
+    np.savez_compressed(os.path.join(HERE, "ref_terminal.npz"), **out)
+
+
 def main() -> int:
     ap = argparse.ArgumentParser()
     ap.add_argument("--reference", default="/root/reference")
     ap.add_argument("--skip-positions", action="store_true")
     ap.add_argument("--only-step", action="store_true", help="write ref_step.npz and stop")
     ap.add_argument("--only-shuffled", action="store_true", help="write ref_shuffled.npz and stop")
+    ap.add_argument("--only-terminal", action="store_true", help="write ref_terminal.npz and stop")
     args = ap.parse_args()
     sys.path.insert(0, args.reference)
     sys.dont_write_bytecode = True
@@ -189,6 +219,9 @@ def main() -> int:
         return 0
     if args.only_shuffled:
         shuffled_answers(env)
+        return 0
+    if args.only_terminal:
+        terminal_answers(env)
         return 0
     from brokefish.nn import quant as rq                             # reference
     from brokefish.nn.cuda_impl import _fold_norm                    # reference
@@ -347,6 +380,7 @@ def main() -> int:
     print("step known answers", flush=True)
     step_answers(env)
     shuffled_answers(env)
+    terminal_answers(env)
 
     print("scheme known answers", flush=True)
     g = torch.Generator().manual_seed(1234)

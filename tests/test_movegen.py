@@ -188,3 +188,42 @@ def test_boards_that_do_not_keep_the_colours_apart_by_slot():
     assert torch.equal(got[1], want[1]) and torch.equal(got[2], want[2])
     assert torch.equal(got[0].view(torch.int16), want[0].view(torch.int16))
     enc.close()
+
+
+@pytest.fixture(scope="module")
+def gold_terminal():
+    z = np.load(os.path.join(GOLDEN, "ref_terminal.npz"))
+    return {k: z[k] for k in z.files}
+
+
+def test_terminal_fixture_says_what_the_rules_say(gold_terminal):
+    g = gold_terminal
+    by = dict(zip(g["fens"], zip(g["fen_code"], g["fen_result"])))
+    assert by["8/8/8/4k3/8/8/8/4K3 w - - 0 1"] == (5, 0) and by["8/8/8/4k3/8/8/8/3NKN2 w - - 0 1"] == (0, 0)
+    assert by["8/8/8/4k3/8/8/8/2B1KB2 w - - 0 1"] == (0, 0) and by["8/8/8/4k3/8/8/2B5/4KB2 w - - 0 1"] == (5, 0)
+    assert by["8/8/8/4k3/8/8/4P3/4K3 w - - 100 80"] == (3, 0) and by["8/8/8/4k3/8/8/4P3/4K3 b - - 99 80"] == (0, 0)
+    assert by["7k/6Q1/6K1/8/8/8/8/8 b - - 100 70"] == (1, -1) and by["7k/5Q2/6K1/8/8/8/8/8 b - - 100 70"] == (2, 0)
+    assert (g["code_4096"] == 1).sum() == 53 and (g["result_4096"] == -1).sum() == 53
+
+
+@pytest.mark.gpu
+def test_terminal_codes_equal_the_reference_engine(gold_terminal, pos256, pos4096):
+    """`env.terminal` on this library's own legal words and check flags: the reference's codes
+    and results on the hand-made positions and on both playout sets."""
+    from brokefish_b200.env import movegen, terminal
+    g = gold_terminal
+    cu = lambda a: torch.from_numpy(np.ascontiguousarray(a)).cuda()
+    for boards, control, code, result in ((g["fen_boards"], g["fen_control"], g["fen_code"], g["fen_result"]),
+                                          (pos256["boards"], pos256["control"], g["code_256"], g["result_256"]),
+                                          (pos4096["boards"], pos4096["control"], g["code_4096"], g["result_4096"])):
+        b, c = cu(boards), cu(control)
+        mask, chk = movegen(b, c)
+        got_code, got_result = terminal(mask, chk, c, b)
+        assert got_code.dtype is torch.uint8 and got_result.dtype is torch.int8
+        assert np.array_equal(got_code.cpu().numpy(), code) and np.array_equal(got_result.cpu().numpy(), result)
+    e = terminal(mask[:0], chk[:0], c[:0], b[:0])
+    assert e[0].shape == (0,)
+    with pytest.raises(NotImplementedError):
+        terminal(mask, chk, c, b, hash=torch.zeros(4096, dtype=torch.int64))
+    with pytest.raises(ValueError):
+        terminal(mask[:5], chk, c, b)
