@@ -231,6 +231,26 @@ def test_e4m3_path_against_reference_kernel(pos256):
           f"{np.abs(rpol.astype(np.float32)).max():.3f}, value {np.abs(val - rval).max():.4f}")
     assert d <= tol
     assert np.abs(val - rval).max() <= 8e-2
+    # the 16384-position configuration (piece counts 2..32, side to move flipped on half, seed 3):
+    # same tolerance, everything finite, and the masked argmax of the two kernels agrees on
+    # most positions that have a legal move (measured 95 %: with N(0, 0.02) weights the logits
+    # are nearly flat, and the two FFN accumulator widths differ by up to 6 % of the largest)
+    from brokefish_b200.positions import varied
+    b, c, r, lg = varied(16384, seed=3)
+    args = [dev(a) for a in (b, c, r)]
+    pol, pro, val = [t.cpu().numpy().copy() for t in enc.forward_full(*args)]
+    rpol, rpro, rval = [t.cpu().numpy().copy() for t in ref.forward_full(*args)]
+    enc.check_status()
+    assert np.isfinite(pol.astype(np.float32)).all() and np.isfinite(val).all()
+    d = np.abs(pol.astype(np.float32) - rpol.astype(np.float32)).max()
+    assert d <= rel_tol(rpol, 10e-2) and np.abs(val - rval).max() <= 8e-2
+    alive = ((b.view(np.uint16) >> 11) & 1) == 0
+    lg = np.where(alive, lg, 0)                       # captured pieces have no moves
+    has_move = lg.any(axis=1) & (c > 0)               # words are the mover's only where nothing was flipped
+    mine, theirs = O.masked_argmax(pol, lg), O.masked_argmax(rpol, lg)
+    agree = (mine == theirs)[has_move].mean()
+    print(f"e4m3, 16384 positions: max|dlogit| {d:.4f}, masked-argmax agreement {agree:.4f} on {has_move.sum()}")
+    assert agree >= 0.93
     enc.close()
 
 
