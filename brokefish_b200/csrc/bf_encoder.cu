@@ -54,7 +54,9 @@ constexpr int kNClock = 101, kNRep = 3, kNTypeSpecial = 12;
 //   kArInt8  every weight GEMM s8/u8 x s8 -> s32 (the reference's int8 "all" scheme)
 //   kArE4M3  FFN e4m3 x e4m3, QKV and out-projection fp16 x fp16 (the reference's fp8 path)
 //   kArF16   every weight GEMM fp16 x fp16 with fp16 accumulators (the reference's default path)
-enum { kArInt8 = 0, kArE4M3 = 1, kArF16 = 2 };
+//   kArI8Ffn FFN s8/u8 x s8 as in kArInt8, QKV and out-projection fp16 x fp16 as in kArF16 (the
+//            reference's "ffn" int8 scheme, quant 2)
+enum { kArInt8 = 0, kArE4M3 = 1, kArF16 = 2, kArI8Ffn = 3 };
 // The front of the map depends on the arithmetic.  int8: the A operand is 32 KB of bytes and
 // the weight ring has 112 KB.  With fp16 attention GEMMs (e4m3, fp16 arms) the A operand is 64 KB
 // (4 K-slabs of 64 halves) and the ring gives up two slots.
@@ -69,7 +71,8 @@ struct Cfg {
     static constexpr int kRSlots = kHalfA ? 5 : 7;           // 16 KB stages
     static constexpr int kAttnSlabs = kHalfA ? 4 : 2;        // K-slabs of a QKV / out-proj unit
     static constexpr int kFfnSlabs = kAr == kArF16 ? 4 : 2;  // K-slabs of an FFN unit
-    static constexpr int kLayerStream = kAr == kArF16 ? 1572864 : (kAr == kArE4M3 ? 1048576 : 786432);
+    static constexpr int kLayerStream = kAr == kArF16 ? 1572864
+                                      : (kAr == kArE4M3 || kAr == kArI8Ffn) ? 1048576 : 786432;
 };
 constexpr uint32_t SM_XCH = 212992;     // 16 KB: float4 [2 parity][4 quarter][128 rows]
 constexpr uint32_t SM_BAR = 229376;     // mbarriers
@@ -102,7 +105,7 @@ struct Params {
     const uint8_t* rep;
     const uint64_t* legal;
     int n, n_layers, n_value, vmode;
-    int quant;                  // 3 = int8 on all four matmuls, 1 = e4m3 FFN with fp16 attention GEMMs
+    int quant;                  // 3 = int8 on all four matmuls, 2 = int8 FFN only, 1 = e4m3 FFN, 0 = fp16
     int rsqrt_rn;               // 1: correctly rounded 1/sqrt in the norms (what a CPU can reproduce);
                                 // 0: the hardware approximation, as the reference's rsqrtf (encoder.cu:597)
     float eps;
@@ -1216,7 +1219,7 @@ __device__ __forceinline__ void row_warps_tile(RowCtx& c, const Params& p, int t
         const int site = !kRJ ? -1 : (p.rj_mode == 2 ? ph : (odd ? -1 : layer));
         const float sa = ln_stage<kDbg, kRJ, kAr>(c, p, false, dump_x, dbgl && dbg == (odd ? 3 : 1),
                                                 cap && p.cap_op == (odd ? BF_OP_FF1 : BF_OP_QKV), site,
-                                                kAr == kArF16 || (kAr == kArE4M3 && !odd));
+                                                kAr == kArF16 || ((kAr == kArE4M3 || kAr == kArI8Ffn) && !odd));
         row_publish(c, B_A_READY);
 
         const uint8_t* lpb = p.lparams + static_cast<size_t>(layer) * kLparamStride;
@@ -1986,6 +1989,10 @@ int launch(bf_handle* h, const uint16_t* boards, const int16_t* control, const u
             else     bf::encoder_kernel<false, true, bf::kArF16><<<grid, bf::kThreads, bf::kSmemRequest, stream>>>(p);
         } else if (dbg) bf::encoder_kernel<true, false, bf::kArF16><<<grid, bf::kThreads, bf::kSmemRequest, stream>>>(p);
         else     bf::encoder_kernel<false, false, bf::kArF16><<<grid, bf::kThreads, bf::kSmemRequest, stream>>>(p);
+    } else if (p.quant == 2) {
+        if (cap_layer >= 0) return fail(BF_ENOTSUP, "operand capture is for the int8 arithmetic");
+        if (dbg) bf::encoder_kernel<true, false, bf::kArI8Ffn><<<grid, bf::kThreads, bf::kSmemRequest, stream>>>(p);
+        else     bf::encoder_kernel<false, false, bf::kArI8Ffn><<<grid, bf::kThreads, bf::kSmemRequest, stream>>>(p);
     } else if (p.quant == 1) {
         if (cap_layer >= 0) return fail(BF_ENOTSUP, "operand capture is for the int8 arithmetic");
         if (dbg) bf::encoder_kernel<true, false, bf::kArE4M3><<<grid, bf::kThreads, bf::kSmemRequest, stream>>>(p);
@@ -2021,11 +2028,11 @@ int bf_create(const void* blob, size_t blob_bytes, int device, bf_handle** out) 
     if (hdr.version != BF_BLOB_VERSION) return fail(BF_EINVAL, "blob version mismatch");
     if (hdr.total != blob_bytes) return fail(BF_EINVAL, "blob size does not match its header");
     if (hdr.n_layers < 1 || hdr.n_layers > 64) return fail(BF_EINVAL, "n_layers out of range");
-    if (hdr.quant != 3 && hdr.quant != 1 && hdr.quant != 0)
-        return fail(BF_EINVAL, "blob arithmetic must be 3 (int8), 1 (e4m3 FFN) or 0 (fp16)");
-    if (hdr.quant == 1 && hdr.rj_mode != 0)
+    if (hdr.quant > 3)
+        return fail(BF_EINVAL, "blob arithmetic must be 3 (int8), 2 (int8 FFN only), 1 (e4m3 FFN) or 0 (fp16)");
+    if ((hdr.quant == 1 || hdr.quant == 2) && hdr.rj_mode != 0)
         return fail(BF_ENOTSUP, "re-injection is built for the int8 and fp16 arithmetics, as in the reference");
-    const uint64_t layer_stream = hdr.quant == 1 ? bf::Cfg<bf::kArE4M3>::kLayerStream
+    const uint64_t layer_stream = (hdr.quant == 1 || hdr.quant == 2) ? bf::Cfg<bf::kArE4M3>::kLayerStream
                                 : hdr.quant == 0 ? bf::Cfg<bf::kArF16>::kLayerStream
                                                  : bf::Cfg<bf::kArInt8>::kLayerStream;
     if (hdr.bytes_w != static_cast<uint64_t>(hdr.n_layers) * layer_stream ||
@@ -2055,7 +2062,9 @@ int bf_create(const void* blob, size_t blob_bytes, int device, bf_handle** out) 
     if (e == cudaSuccess) e = cudaStreamCreateWithFlags(&h->stream, cudaStreamNonBlocking);
     if (e == cudaSuccess) e = cudaStreamCreateWithFlags(&h->copy_stream, cudaStreamNonBlocking);
     if (e == cudaSuccess) e = cudaEventCreateWithFlags(&h->chunk_done, cudaEventDisableTiming);
-    const void* kernels[10] = {
+    const void* kernels[12] = {
+        reinterpret_cast<const void*>(&bf::encoder_kernel<false, false, bf::kArI8Ffn>),
+        reinterpret_cast<const void*>(&bf::encoder_kernel<true, false, bf::kArI8Ffn>),
         reinterpret_cast<const void*>(&bf::encoder_kernel<false, true, bf::kArF16>),
         reinterpret_cast<const void*>(&bf::encoder_kernel<true, true, bf::kArF16>),
         reinterpret_cast<const void*>(&bf::encoder_kernel<false, false, bf::kArInt8>),
@@ -2066,7 +2075,7 @@ int bf_create(const void* blob, size_t blob_bytes, int device, bf_handle** out) 
         reinterpret_cast<const void*>(&bf::encoder_kernel<true, false, bf::kArE4M3>),
         reinterpret_cast<const void*>(&bf::encoder_kernel<false, false, bf::kArF16>),
         reinterpret_cast<const void*>(&bf::encoder_kernel<true, false, bf::kArF16>)};
-    for (int i = 0; i < 10 && e == cudaSuccess; ++i)
+    for (int i = 0; i < 12 && e == cudaSuccess; ++i)
         e = cudaFuncSetAttribute(kernels[i], cudaFuncAttributeMaxDynamicSharedMemorySize, bf::kSmemRequest);
     if (e != cudaSuccess) {
         bf_destroy(h);
