@@ -56,23 +56,29 @@ constexpr int kNClock = 101, kNRep = 3, kNTypeSpecial = 12;
 //   kArF16   every weight GEMM fp16 x fp16 with fp16 accumulators (the reference's default path)
 //   kArI8Ffn FFN s8/u8 x s8 as in kArInt8, QKV and out-projection fp16 x fp16 as in kArF16 (the
 //            reference's "ffn" int8 scheme, quant 2)
-enum { kArInt8 = 0, kArE4M3 = 1, kArF16 = 2, kArI8Ffn = 3 };
+//   kArI8Qkv FFN and QKV s8 x s8, out-projection fp16 x fp16 (the reference's "ffn+qkv" int8
+//            scheme, quant 4)
+enum { kArInt8 = 0, kArE4M3 = 1, kArF16 = 2, kArI8Ffn = 3, kArI8Qkv = 4 };
 // The front of the map depends on the arithmetic.  int8: the A operand is 32 KB of bytes and
 // the weight ring has 112 KB.  With fp16 attention GEMMs (e4m3, fp16 arms) the A operand is 64 KB
 // (4 K-slabs of 64 halves) and the ring gives up two slots.
 template <int kAr>
 struct Cfg {
-    static constexpr bool kHalfA = kAr != kArInt8;           // fp16 A operand for QKV / out-proj
+    static constexpr bool kHalfA = kAr != kArInt8;           // the A operand region holds fp16 K-slabs
+    static constexpr bool kQkvF16 = kAr == kArE4M3 || kAr == kArF16 || kAr == kArI8Ffn;   // fp16 QKV GEMM
+    static constexpr bool kOutF16 = kHalfA;                  // fp16 out-projection GEMM
     static constexpr uint32_t SM_A = 0;     // A operand: K-slabs of [128 rows][128 B]
     static constexpr uint32_t SM_R = kHalfA ? 65536 : 32768; // 64 KB: Q/K/V staging (3 x 16 KB) |
                                             // hidden operand(s) | fp16 head A (4 x 16 KB)
     static constexpr uint32_t SM_RING = SM_R + 65536;        // weight ring up to SM_XCH
     static constexpr int kQSlots = kHalfA ? 3 : 4;           // 24 KB QKV stages
     static constexpr int kRSlots = kHalfA ? 5 : 7;           // 16 KB stages
-    static constexpr int kAttnSlabs = kHalfA ? 4 : 2;        // K-slabs of a QKV / out-proj unit
+    static constexpr int kQkvSlabs = kQkvF16 ? 4 : 2;        // K-slabs of a QKV unit
+    static constexpr int kOutSlabs = kOutF16 ? 4 : 2;        // K-slabs of an out-projection unit
     static constexpr int kFfnSlabs = kAr == kArF16 ? 4 : 2;  // K-slabs of an FFN unit
     static constexpr int kLayerStream = kAr == kArF16 ? 1572864
-                                      : (kAr == kArE4M3 || kAr == kArI8Ffn) ? 1048576 : 786432;
+                                      : (kAr == kArE4M3 || kAr == kArI8Ffn) ? 1048576
+                                      : kAr == kArI8Qkv ? 851968 : 786432;
 };
 constexpr uint32_t SM_XCH = 212992;     // 16 KB: float4 [2 parity][4 quarter][128 rows]
 constexpr uint32_t SM_BAR = 229376;     // mbarriers
@@ -105,7 +111,8 @@ struct Params {
     const uint8_t* rep;
     const uint64_t* legal;
     int n, n_layers, n_value, vmode;
-    int quant;                  // 3 = int8 on all four matmuls, 2 = int8 FFN only, 1 = e4m3 FFN, 0 = fp16
+    int quant;                  // 3 = int8 on all four matmuls, 2 = int8 FFN only, 4 = int8 FFN and QKV,
+                                // 1 = e4m3 FFN, 0 = fp16 (the reference's numbering)
     int rsqrt_rn;               // 1: correctly rounded 1/sqrt in the norms (what a CPU can reproduce);
                                 // 0: the hardware approximation, as the reference's rsqrtf (encoder.cu:597)
     float eps;
@@ -664,7 +671,7 @@ __device__ __forceinline__ void attention_block(RowCtx& c, const Params& p, cons
                 uint32_t h[8];
                 if (kDbg && cap && p.cap_op == BF_OP_QKV && c.valid)
                     store_words<16>(p.cap_acc + c.grow * 768 + j * 192 + c0, cur);
-                descale<16, false, kHalfA ? kAccPlain : kAccInt>(cur, sa, __ldg(lp.sw_qkv + m * 2 + (j >> 1)),
+                descale<16, false, Cfg<kAr>::kQkvF16 ? kAccPlain : kAccInt>(cur, sa, __ldg(lp.sw_qkv + m * 2 + (j >> 1)),
                                                                 lp.b_qkv + j * 192 + c0, h);
 #pragma unroll
                 for (int k = 0; k < 2; ++k)
@@ -742,7 +749,7 @@ __device__ __forceinline__ void attention_block(RowCtx& c, const Params& p, cons
         tmem_wait_ld();
         row_release_acc(c, u);
         if (kDbg && cap && p.cap_op == BF_OP_OUT && c.valid) store_words<32>(p.cap_acc + c.grow * 256 + col, acc);
-        descale<32, false, kHalfA ? kAccPlain : kAccInt>(acc, sa, __ldg(lp.sw_o + u), lp.b_o + col, y);
+        descale<32, false, Cfg<kAr>::kOutF16 ? kAccPlain : kAccInt>(acc, sa, __ldg(lp.sw_o + u), lp.b_o + col, y);
 #pragma unroll
         for (int i = 0; i < 16; ++i) xo[i] = as_u32(__hadd2(as_h2(xo[i]), as_h2(y[i])));
         tmem_st16(c.tm + TM_X + (col >> 1), xo);
@@ -1387,7 +1394,7 @@ __device__ __forceinline__ void producer_loop(uint32_t smem, volatile int* abort
                 // the two rings share memory: the 16 KB ring must be drained first
                 for (uint32_t s = 0; s < kRS; ++s)
                     mbar_wait(bar_addr(smem, B_WR_EMPTY + s), (uses(ri, kRS, s) - 1u) & 1u, abort_flag, kErrProducer);
-                for (int st = 0; st < 4 * C::kAttnSlabs; ++st, ++qi) {
+                for (int st = 0; st < 4 * C::kQkvSlabs; ++st, ++qi) {
                     const uint32_t s = qi % kQS;
                     mbar_wait(bar_addr(smem, B_WQ_EMPTY + s), (qi / kQS - 1u) & 1u, abort_flag, kErrProducer);
                     mbar_arrive_expect_tx(bar_addr(smem, B_WQ_FULL + s), kQStage);
@@ -1398,7 +1405,7 @@ __device__ __forceinline__ void producer_loop(uint32_t smem, volatile int* abort
                     mbar_wait(bar_addr(smem, B_WQ_EMPTY + s), (uses(qi, kQS, s) - 1u) & 1u, abort_flag, kErrProducer);
             }
             // out-projection (2 units) and the 16 FFN units
-            const int n_st = 2 * C::kAttnSlabs + 16 * C::kFfnSlabs;
+            const int n_st = 2 * C::kOutSlabs + 16 * C::kFfnSlabs;
             const uint32_t bytes = kRStage;
             for (int st = 0; st < n_st; ++st, ++ri) {
                 const uint32_t s = ri % kRS;
@@ -1481,14 +1488,14 @@ __device__ __forceinline__ void mma_loop(uint32_t smem, uint32_t tmem, volatile 
     // accumulators (the reference's fp16-accumulate e4m3 mma.sync has no bit-equal on tcgen05).
     constexpr bool kHalfA = kAr != kArInt8;
     constexpr uint32_t kI_H128 = umma_idesc(kAccF16, kFmtF16, kFmtF16, 128, 128);
-    constexpr uint32_t kI_QKV = kHalfA ? umma_idesc(kAccF16, kFmtF16, kFmtF16, 128, 192)
+    constexpr uint32_t kI_QKV = C::kQkvF16 ? umma_idesc(kAccF16, kFmtF16, kFmtF16, 128, 192)
                                        : umma_idesc(kAccS32, kFmtS8, kFmtS8, 128, 192);
-    constexpr uint32_t kI_OUT = kHalfA ? kI_H128 : umma_idesc(kAccS32, kFmtS8, kFmtS8, 128, 128);
+    constexpr uint32_t kI_OUT = C::kOutF16 ? kI_H128 : umma_idesc(kAccS32, kFmtS8, kFmtS8, 128, 128);
     constexpr uint32_t kI_FF1 = kAr == kArE4M3 ? umma_idesc(kAccF32, kFmtE4M3, kFmtE4M3, 128, 128)
                               : kAr == kArF16 ? kI_H128 : umma_idesc(kAccS32, kFmtS8, kFmtS8, 128, 128);
     constexpr uint32_t kI_FF2 = kAr == kArE4M3 ? umma_idesc(kAccF32, kFmtE4M3, kFmtE4M3, 128, 128)
                               : kAr == kArF16 ? kI_H128 : umma_idesc(kAccS32, kFmtU8, kFmtS8, 128, 128);
-    constexpr int kAttnKind = kHalfA ? kKindF16 : kKindI8;
+    constexpr int kQkvKind = C::kQkvF16 ? kKindF16 : kKindI8, kOutKind = C::kOutF16 ? kKindF16 : kKindI8;
     constexpr int kFfnKind = kAr == kArE4M3 ? kKindF8 : (kAr == kArF16 ? kKindF16 : kKindI8);
     const uint32_t acc0 = tmem + TM_ACC, acc1 = tmem + TM_ACC + 128;
     const uint32_t sm_a = smem + C::SM_A, sm_r = smem + C::SM_R;
@@ -1496,10 +1503,10 @@ __device__ __forceinline__ void mma_loop(uint32_t smem, uint32_t tmem, volatile 
         for (int layer = 0; layer < p.n_layers; ++layer) {
             mma_wait_operand(smem, abort_flag, B_A_READY, st.aready);          // LN1 output
             for (int j = 0; j < 4; ++j)
-                mma_unit<kAr>(smem, abort_flag, st, acc0, 0, sm_a, true, C::kAttnSlabs, kI_QKV, kAttnKind);
+                mma_unit<kAr>(smem, abort_flag, st, acc0, 0, sm_a, true, C::kQkvSlabs, kI_QKV, kQkvKind);
             mma_wait_operand(smem, abort_flag, B_A_READY, st.aready);          // attention output
-            mma_unit<kAr>(smem, abort_flag, st, acc0, 0, sm_a, false, C::kAttnSlabs, kI_OUT, kAttnKind);
-            mma_unit<kAr>(smem, abort_flag, st, acc1, 1, sm_a, false, C::kAttnSlabs, kI_OUT, kAttnKind);
+            mma_unit<kAr>(smem, abort_flag, st, acc0, 0, sm_a, false, C::kOutSlabs, kI_OUT, kOutKind);
+            mma_unit<kAr>(smem, abort_flag, st, acc1, 1, sm_a, false, C::kOutSlabs, kI_OUT, kOutKind);
             mma_wait_operand(smem, abort_flag, B_A_READY, st.aready);          // LN2 output
             if constexpr (kAr == kArF16) {
                 // fp16 FFN: ff1 units go into slot 0; once the rows have written a hidden chunk,
@@ -1989,6 +1996,10 @@ int launch(bf_handle* h, const uint16_t* boards, const int16_t* control, const u
             else     bf::encoder_kernel<false, true, bf::kArF16><<<grid, bf::kThreads, bf::kSmemRequest, stream>>>(p);
         } else if (dbg) bf::encoder_kernel<true, false, bf::kArF16><<<grid, bf::kThreads, bf::kSmemRequest, stream>>>(p);
         else     bf::encoder_kernel<false, false, bf::kArF16><<<grid, bf::kThreads, bf::kSmemRequest, stream>>>(p);
+    } else if (p.quant == 4) {
+        if (cap_layer >= 0) return fail(BF_ENOTSUP, "operand capture is for the int8 arithmetic");
+        if (dbg) bf::encoder_kernel<true, false, bf::kArI8Qkv><<<grid, bf::kThreads, bf::kSmemRequest, stream>>>(p);
+        else     bf::encoder_kernel<false, false, bf::kArI8Qkv><<<grid, bf::kThreads, bf::kSmemRequest, stream>>>(p);
     } else if (p.quant == 2) {
         if (cap_layer >= 0) return fail(BF_ENOTSUP, "operand capture is for the int8 arithmetic");
         if (dbg) bf::encoder_kernel<true, false, bf::kArI8Ffn><<<grid, bf::kThreads, bf::kSmemRequest, stream>>>(p);
@@ -2028,11 +2039,13 @@ int bf_create(const void* blob, size_t blob_bytes, int device, bf_handle** out) 
     if (hdr.version != BF_BLOB_VERSION) return fail(BF_EINVAL, "blob version mismatch");
     if (hdr.total != blob_bytes) return fail(BF_EINVAL, "blob size does not match its header");
     if (hdr.n_layers < 1 || hdr.n_layers > 64) return fail(BF_EINVAL, "n_layers out of range");
-    if (hdr.quant > 3)
-        return fail(BF_EINVAL, "blob arithmetic must be 3 (int8), 2 (int8 FFN only), 1 (e4m3 FFN) or 0 (fp16)");
-    if ((hdr.quant == 1 || hdr.quant == 2) && hdr.rj_mode != 0)
+    if (hdr.quant > 4)
+        return fail(BF_EINVAL, "blob arithmetic must be 3 (int8), 2 (int8 FFN only), 4 (int8 FFN and QKV), "
+                               "1 (e4m3 FFN) or 0 (fp16)");
+    if ((hdr.quant == 1 || hdr.quant == 2 || hdr.quant == 4) && hdr.rj_mode != 0)
         return fail(BF_ENOTSUP, "re-injection is built for the int8 and fp16 arithmetics, as in the reference");
     const uint64_t layer_stream = (hdr.quant == 1 || hdr.quant == 2) ? bf::Cfg<bf::kArE4M3>::kLayerStream
+                                : hdr.quant == 4 ? bf::Cfg<bf::kArI8Qkv>::kLayerStream
                                 : hdr.quant == 0 ? bf::Cfg<bf::kArF16>::kLayerStream
                                                  : bf::Cfg<bf::kArInt8>::kLayerStream;
     if (hdr.bytes_w != static_cast<uint64_t>(hdr.n_layers) * layer_stream ||
@@ -2062,7 +2075,9 @@ int bf_create(const void* blob, size_t blob_bytes, int device, bf_handle** out) 
     if (e == cudaSuccess) e = cudaStreamCreateWithFlags(&h->stream, cudaStreamNonBlocking);
     if (e == cudaSuccess) e = cudaStreamCreateWithFlags(&h->copy_stream, cudaStreamNonBlocking);
     if (e == cudaSuccess) e = cudaEventCreateWithFlags(&h->chunk_done, cudaEventDisableTiming);
-    const void* kernels[12] = {
+    const void* kernels[14] = {
+        reinterpret_cast<const void*>(&bf::encoder_kernel<false, false, bf::kArI8Qkv>),
+        reinterpret_cast<const void*>(&bf::encoder_kernel<true, false, bf::kArI8Qkv>),
         reinterpret_cast<const void*>(&bf::encoder_kernel<false, false, bf::kArI8Ffn>),
         reinterpret_cast<const void*>(&bf::encoder_kernel<true, false, bf::kArI8Ffn>),
         reinterpret_cast<const void*>(&bf::encoder_kernel<false, true, bf::kArF16>),
@@ -2075,7 +2090,7 @@ int bf_create(const void* blob, size_t blob_bytes, int device, bf_handle** out) 
         reinterpret_cast<const void*>(&bf::encoder_kernel<true, false, bf::kArE4M3>),
         reinterpret_cast<const void*>(&bf::encoder_kernel<false, false, bf::kArF16>),
         reinterpret_cast<const void*>(&bf::encoder_kernel<true, false, bf::kArF16>)};
-    for (int i = 0; i < 12 && e == cudaSuccess; ++i)
+    for (int i = 0; i < 14 && e == cudaSuccess; ++i)
         e = cudaFuncSetAttribute(kernels[i], cudaFuncAttributeMaxDynamicSharedMemorySize, bf::kSmemRequest);
     if (e != cudaSuccess) {
         bf_destroy(h);

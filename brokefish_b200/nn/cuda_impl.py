@@ -88,9 +88,6 @@ class FusedEncoder:
             raise ValueError(f"int8_scheme must be one of {sorted(SCHEMES)}, got {int8_scheme!r}")
         if self.fp8:
             self.int8 = False
-        if self.int8 and int8_scheme == "ffn+qkv":
-            raise NotImplementedError("the 'ffn+qkv' int8 scheme (int8 FFN and QKV, fp16 out-projection) is not "
-                                      "built; 'all' (the shipped one) and 'ffn' are")
         self.int8_scheme = int8_scheme
         # the reference's kernel mode numbers: 3 = int8 on all four matmuls, 1 = e4m3 FFN,
         # 0 = the plain fp16 arithmetic (the reference's default; here `int8=False`)
@@ -114,11 +111,11 @@ class FusedEncoder:
             self.n_value = int(net.value.weight.shape[0])
             self.vmode = self.VMODE[getattr(net, "value_head", "king")]
             self.rj_mode = self.RJMODE[getattr(net, "reinject", "none")]
-            if self.quant in (1, 2) and self.rj_mode:
+            if self.quant in (1, 2, 4) and self.rj_mode:
                 raise NotImplementedError("input re-injection is built for the int8 and the fp16 arithmetic "
                                           "(as in the reference, brokefish/nn/cuda_impl.py:413-420); this "
                                           "encoder is " + self.label)
-            self.blob = pack_blob(net, {3: "int8", 2: "int8_ffn", 1: "e4m3", 0: "f16"}[self.quant])
+            self.blob = pack_blob(net, {3: "int8", 2: "int8_ffn", 4: "int8_ffn_qkv", 1: "e4m3", 0: "f16"}[self.quant])
             self._create(self.blob)
 
     # -- construction helpers --------------------------------------------------
@@ -176,7 +173,7 @@ class FusedEncoder:
     @property
     def label(self) -> str:
         """What this instance runs, for a bench header or a run log."""
-        base = {1: "e4m3 FFN", 0: "fp16", 2: "int8 FFN", 3: "int8 FFN+QKV+out_proj"}[self.quant]
+        base = {1: "e4m3 FFN", 0: "fp16", 2: "int8 FFN", 3: "int8 FFN+QKV+out_proj", 4: "int8 FFN+QKV"}[self.quant]
         return base + ", 4 boards/CTA, tcgen05 (sm_100a)"
 
     @property

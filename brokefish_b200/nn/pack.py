@@ -63,9 +63,10 @@ VALUE_ROW = N_POLICY + N_PROMO
 LAYER_STREAM_BYTES = 786432
 LAYER_STREAM_BYTES_E4M3 = 1048576
 LAYER_STREAM_BYTES_F16 = 1572864
+LAYER_STREAM_BYTES_QKV8 = 851968      # s8 QKV, fp16 out-projection, s8 FFN
 #: Arithmetic of a blob, by the reference's kernel mode number: 3 = int8 on all four
 #: matmuls, 1 = e4m3 on the two FFN matmuls with fp16 QKV and out-projection.
-QUANT_INT8, QUANT_E4M3, QUANT_F16, QUANT_INT8_FFN = 3, 1, 0, 2
+QUANT_INT8, QUANT_E4M3, QUANT_F16, QUANT_INT8_FFN, QUANT_INT8_FFN_QKV = 3, 1, 0, 2, 4
 HEAD_STREAM_BYTES = 4 * NHEAD * 128
 LPARAM_STRIDE = 4736
 LP_SW_QKV, LP_SW_O, LP_SW_FF1, LP_SW_FF2 = 0, 24, 32, 64
@@ -122,9 +123,10 @@ def fold_and_quantise(net: BrokefishNet, fmt: str = "int8") -> List[FoldedLayer]
     matrices s8.  ``fmt="e4m3"``: the two FFN matrices e4m3 with ``amax/8`` scales, QKV and
     out-projection fp16 (brokefish/nn/cuda_impl.py:303-337).  ``fmt="f16"``: all four fp16, the
     folded fp32 matrices rounded once (cuda_impl.py:194-228).  ``fmt="int8_ffn"``: the reference's
-    "ffn" int8 scheme (quant 2): the two FFN matrices s8, QKV and out-projection fp16."""
-    if fmt not in ("int8", "e4m3", "f16", "int8_ffn"):
-        raise ValueError(f"fmt must be 'int8', 'int8_ffn', 'e4m3' or 'f16', got {fmt!r}")
+    "ffn" int8 scheme (quant 2): the two FFN matrices s8, QKV and out-projection fp16.
+    ``fmt="int8_ffn_qkv"``: its "ffn+qkv" scheme (quant 4): only the out-projection stays fp16."""
+    if fmt not in ("int8", "e4m3", "f16", "int8_ffn", "int8_ffn_qkv"):
+        raise ValueError(f"fmt must be 'int8', 'int8_ffn', 'int8_ffn_qkv', 'e4m3' or 'f16', got {fmt!r}")
     out = []
     scale = DH ** -0.5
     for lay in net.encoder.layers:
@@ -138,7 +140,8 @@ def fold_and_quantise(net: BrokefishNet, fmt: str = "int8") -> List[FoldedLayer]
         mats = {}
         for name, w in (("qkv", w_qkv), ("o", lay.self_attn.out_proj.weight.detach()),
                         ("ff1", w_ff1), ("ff2", lay.linear2.weight.detach())):
-            if fmt == "int8" or (fmt == "int8_ffn" and name in ("ff1", "ff2")):
+            if (fmt == "int8" or (fmt == "int8_ffn" and name in ("ff1", "ff2"))
+                    or (fmt == "int8_ffn_qkv" and name != "o")):
                 qb, sc = quantise_weights_int8_bytes(w.float())
             elif fmt == "e4m3" and name in ("ff1", "ff2"):
                 qb, sc = quantise_weights_bytes(w.float(), Q_MAX, tile_k=w.shape[1])
@@ -193,12 +196,13 @@ def _layer_stream(fl: FoldedLayer) -> np.ndarray:
     parts = []
     rows = qkv_chunk_rows()
     slabs = fl.q_qkv.shape[1] // 128          # 2 for s8 (K = 256 bytes), 4 for fp16 (512 bytes)
+    slabs_o = fl.q_o.shape[1] // 128
     for j in range(4):
         chunk = fl.q_qkv[rows[j]]                                   # [192, K bytes]
         for s in range(slabs):
             parts.append(sw128_image(np.ascontiguousarray(chunk[:, 128 * s:128 * s + 128])))
     for u in range(2):
-        for s in range(slabs):
+        for s in range(slabs_o):
             parts.append(sw128_image(np.ascontiguousarray(
                 fl.q_o[128 * u:128 * u + 128, 128 * s:128 * s + 128])))
     if fl.q_ff1.shape[1] == 512:
@@ -233,7 +237,8 @@ def _layer_stream(fl: FoldedLayer) -> np.ndarray:
                 parts.append(sw128_image(np.ascontiguousarray(blk)))
     stream = np.concatenate(parts)
     assert stream.size == (LAYER_STREAM_BYTES_F16 if fl.q_ff1.shape[1] == 512 else
-                           LAYER_STREAM_BYTES if slabs == 2 else LAYER_STREAM_BYTES_E4M3)
+                           LAYER_STREAM_BYTES_E4M3 if slabs == 4 else
+                           LAYER_STREAM_BYTES if slabs_o == 2 else LAYER_STREAM_BYTES_QKV8)
     return stream
 
 
@@ -270,7 +275,7 @@ def pack_blob(net: BrokefishNet, fmt: str = "int8") -> np.ndarray:
             f"{first.self_attn.embed_dim}, {first.linear1.out_features}, "
             f"{first.self_attn.num_heads}")
     layers = fold_and_quantise(net, fmt)
-    if fmt in ("e4m3", "int8_ffn") and getattr(net, "reinject", "none") != "none":
+    if fmt in ("e4m3", "int8_ffn", "int8_ffn_qkv") and getattr(net, "reinject", "none") != "none":
         raise NotImplementedError("input re-injection is built for the int8 and fp16 arithmetics only")
     wstream = np.concatenate([_layer_stream(fl) for fl in layers])
     lparams = np.concatenate([_layer_params(fl) for fl in layers])
@@ -298,7 +303,8 @@ def pack_blob(net: BrokefishNet, fmt: str = "int8") -> np.ndarray:
     vmode = VALUE_MODE_ID.get(getattr(net, "value_head", "king"), 0)
     header = struct.pack("<IIIIIfII", MAGIC, VERSION, len(layers),
                          int(net.value.weight.shape[0]), vmode, float(first.norm1.eps), rj_mode,
-                         {"int8": QUANT_INT8, "e4m3": QUANT_E4M3, "f16": QUANT_F16, "int8_ffn": QUANT_INT8_FFN}[fmt])
+                         {"int8": QUANT_INT8, "e4m3": QUANT_E4M3, "f16": QUANT_F16, "int8_ffn": QUANT_INT8_FFN,
+                          "int8_ffn_qkv": QUANT_INT8_FFN_QKV}[fmt])
     for off, sec in zip(offs, sections):
         header += struct.pack("<QQ", off, sec.size)
     header += struct.pack("<Q", total)

@@ -52,8 +52,10 @@ const char* bf_last_error(void);
 
 /* Create an evaluator on CUDA device `device` from a packed weight blob (host or device
  * memory; layout in brokefish_b200/nn/pack.py; its header says which of the reference's kernel
- * modes it carries — 3: int8 on all four matmuls, 1: e4m3 FFN with fp16 attention GEMMs, 0: plain
- * fp16 — and the matching kernel arm runs).  The blob is copied; the caller may free it afterwards.  Replaces the weight slabs `FusedEncoder.__init__` uploads
+ * modes it carries, in the reference's numbering (brokefish/nn/cuda_impl.py:95) — 3: int8 on all
+ * four matmuls, 2: int8 FFN only, 4: int8 FFN and QKV, 1: e4m3 FFN with fp16 attention GEMMs,
+ * 0: plain fp16 — and the matching kernel arm runs).  The blob is copied; the caller may free
+ * it afterwards.  Replaces the weight slabs `FusedEncoder.__init__` uploads
  * (brokefish/nn/cuda_impl.py:228, 370-371, 382-406). */
 int bf_create(const void* blob, size_t blob_bytes, int device, bf_handle** out);
 

@@ -47,6 +47,7 @@ SETS = {
     "A_e4m3": (dict(seed=0, std=0.02, perturb_norms=False), dict(fp8=True)),
     "A_f16": (dict(seed=0, std=0.02, perturb_norms=False), dict()),
     "B_int8_ffn": (dict(seed=0, std=None, perturb_norms=True), dict(int8=True, int8_scheme="ffn")),
+    "B_int8_ffn_qkv": (dict(seed=0, std=None, perturb_norms=True), dict(int8=True, int8_scheme="ffn+qkv")),
     "C_int8_rj": (dict(seed=7, std=None, perturb_norms=True, reinject="both"), dict(int8=True)),
     "C_f16_rj": (dict(seed=7, std=None, perturb_norms=True, reinject="both"), dict()),
     "D_f16_rj1": (dict(seed=8, std=0.02, perturb_norms=True, reinject="ln1"), dict()),

@@ -130,7 +130,7 @@ class Weights:
 
 def prepare(state: Dict[str, np.ndarray], fmt: str = "int8") -> Weights:
     """Fold, quantise and round a fp32 ``state_dict`` (numpy arrays)."""
-    if fmt not in ("int8", "e4m3", "f16", "int8_ffn"):
+    if fmt not in ("int8", "e4m3", "f16", "int8_ffn", "int8_ffn_qkv"):
         raise ValueError(fmt)
     s = {k: np.asarray(v) for k, v in state.items()}
     n_layers = 1 + max(int(k.split(".")[2]) for k in s if k.startswith("encoder.layers."))
@@ -159,7 +159,9 @@ def prepare(state: Dict[str, np.ndarray], fmt: str = "int8") -> Weights:
         else:
             q_qkv, s_qkv = f16(w_qkv), np.ones(6, dtype=F32)
             q_o, s_o = f16(s[p + "self_attn.out_proj.weight"]), np.ones(2, dtype=F32)
-            if fmt == "int8_ffn":      # the reference's "ffn" scheme: int8 FFN, fp16 QKV / out-projection
+            if fmt == "int8_ffn_qkv":  # the reference's "ffn+qkv" scheme: only the out-projection stays fp16
+                q_qkv, s_qkv = quantise_weights_s8(w_qkv)
+            if fmt in ("int8_ffn", "int8_ffn_qkv"):      # int8 FFN ("ffn": fp16 QKV and out-projection)
                 q_ff1, s_ff1 = quantise_weights_s8(w_ff1)
                 q_ff2, s_ff2 = quantise_weights_s8(s[p + "linear2.weight"])
             elif fmt == "e4m3":
@@ -383,8 +385,8 @@ def forward(w: Weights, boards, control, rep, legal=None, trace: Optional[Trace]
         xn = layernorm(reinject(w, x, boards, control, rep, site1) if w.rj_mode else x)
         if first:
             trace.stages[1] = xn.reshape(n, T, D).copy()
-        e4 = w.fmt in ("e4m3", "f16", "int8_ffn")       # fp16 attention GEMMs
-        if e4:       # fp16 QKV with fp16 accumulators, 16 steps of 16 (csrc/encoder.cu:1366-1368)
+        e4 = w.fmt in ("e4m3", "f16", "int8_ffn", "int8_ffn_qkv")       # fp16 out-projection
+        if e4 and w.fmt != "int8_ffn_qkv":       # fp16 QKV with fp16 accumulators, 16 steps of 16 (csrc/encoder.cu:1366-1368)
             qkv = add_f16(_mma_f16acc(xn, lw.q_qkv.astype(F16).T), lw.b_qkv[None, :])
         else:
             qa, sa = quantise_rows(xn)

@@ -274,14 +274,17 @@ def test_fp16_arithmetic_is_bit_identical_to_the_reference_kernel(pos256, pos409
     enc.close()
 
 
-def test_int8_ffn_scheme_is_bit_identical(pos256, pos4096):
+@pytest.mark.parametrize("scheme,name,quant,fmt", [("ffn", "B_int8_ffn", 2, "int8_ffn"),
+                                                   ("ffn+qkv", "B_int8_ffn_qkv", 4, "int8_ffn_qkv")])
+def test_partial_int8_schemes_are_bit_identical(scheme, name, quant, fmt, pos256, pos4096):
     """`int8_scheme="ffn"` (the reference's quant 2): the FFN in s8/u8 as in the shipped scheme,
-    QKV and out-projection in fp16 as in the default arithmetic.  Both halves carry the
-    reference's bits on their own, so does the mixture."""
-    if not R.available("B_int8_ffn"):
+    QKV and out-projection in fp16 as in the default arithmetic; `"ffn+qkv"` (quant 4): QKV in
+    s8 as well, only the out-projection in fp16.  Each GEMM carries the reference's bits on its
+    own, so do the mixtures."""
+    if not R.available(name):
         pytest.skip("slabs missing")
-    enc, ref = product(SETS["B"], int8=True, int8_scheme="ffn"), R.RefKernel("B_int8_ffn")
-    assert ref.quant == 2 and enc.quant == 2 and enc.label.startswith("int8 FFN,")
+    enc, ref = product(SETS["B"], int8=True, int8_scheme=scheme), R.RefKernel(name)
+    assert ref.quant == quant and enc.quant == quant and enc.label.startswith("int8 FFN")
     sl = slice(0, 200)
     for stage in (9, 1, 5, 6, 7, 4, 2, 3, 8):
         got = enc.forward_stage(*inputs(pos256, sl), stage).cpu().numpy()
@@ -292,17 +295,15 @@ def test_int8_ffn_scheme_is_bit_identical(pos256, pos4096):
         assert same_bits(pol, rpol) and same_bits(pro, rpro) and np.abs(val - rval).max() <= 1e-6
     # and against the CPU restatement of the same mixture, at the quantised-path tolerance
     from brokefish_b200.nn.model import seeded_state
-    w = O.prepare({k: v.numpy() for k, v in seeded_state(**SETS["B"]).items()}, fmt="int8_ffn")
+    w = O.prepare({k: v.numpy() for k, v in seeded_state(**SETS["B"]).items()}, fmt=fmt)
     n = 48
     opol, opro, oval = O.forward(w, pos256["boards"][:n], pos256["control"][:n], pos256["rep"][:n])[:3]
     enc.exact_rsqrt = True
     pol, pro, val = [t.cpu().numpy().copy() for t in enc.forward_full(*inputs(pos256, slice(0, n)))]
     d = np.abs(pol.astype(np.float32) - opol.astype(np.float32)).max()
-    print(f"int8-FFN arm vs CPU restatement: max|dlogit| {d:.4f} of {np.abs(opol.astype(np.float32)).max():.3f}")
+    print(f"{scheme} arm vs CPU restatement: max|dlogit| {d:.4f} of {np.abs(opol.astype(np.float32)).max():.3f}")
     assert d <= rel_tol(opol, 2e-2)
     enc.close()
-    with pytest.raises(NotImplementedError):
-        product(SETS["B"], int8=True, int8_scheme="ffn+qkv")
 
 
 def test_timing_report(pos4096):

@@ -30,8 +30,6 @@ def test_constructor_refusals(nets):
         FusedEncoder(net, acc_dtype="fp32")
     with pytest.raises(ValueError):
         FusedEncoder(net, fp8=True, int8=True)
-    with pytest.raises(NotImplementedError):
-        FusedEncoder(net, int8_scheme="ffn+qkv")
     with pytest.raises(ValueError):
         FusedEncoder(net, int8_scheme="nope")
     with pytest.raises(ValueError):
