@@ -7,8 +7,10 @@
 // search node's edges and priors straight from the epilogue.  The int8 arithmetic follows
 // the reference kernel (csrc/encoder.cu:1225-1599 with int8_gemm.cuh) at every rounding
 // point, the hardware-approximate ones included (summation order and 1/sqrt of the norms,
-// fp16-accumulate mma.sync for the attention and head products, __expf), so that its
-// outputs equal that kernel's bit for bit; only the exact-integer GEMMs run on tcgen05.
+// fp16 accumulation in the attention and head products, __expf), so that its outputs equal
+// that kernel's bit for bit.  The weight GEMMs and the head product run on tcgen05 (exact
+// integers; fp16 x fp16 with fp16 accumulators, which carries the bits of the reference's
+// fp16-accumulate mma.sync); the 32 x 32 attention products run as mma.sync on the row warps.
 //
 // Shape of the kernel
 //   * persistent grid, one CTA per SM, each CTA loops over tiles of 128 token rows
@@ -87,10 +89,10 @@ constexpr uint32_t SM_PROF = SM_MISC + 64;     // 16 x int64 phase cycle counter
 constexpr uint32_t SM_BYTES = SM_PROF + 128;
 constexpr uint32_t kSmemRequest = SM_BYTES + 1024;
 constexpr uint32_t kQStage = 24576, kRStage = 16384;
-// tail section: gamma, beta, three value rows (1280 halves), then the [96 x 256] head matrix in
-// mma.sync B-fragment order: uint4 [12 n-tiles][8 k-step pairs][32 lanes]
-constexpr int kTailHeadFrag = 1280;
-constexpr uint32_t kTailBytes = 2560u + 96u * 256u * 2u;
+// the weight stream ends with the [96 x 256] fp16 head matrix as 4 K-slabs of [96 rows][128 B]
+constexpr uint32_t kHeadStage = 12288, kHeadStages = 4;
+// tail section: gamma, beta and three value rows of the final norm / value head (1280 halves)
+constexpr uint32_t kTailBytes = 2560u;
 // barrier indices
 constexpr int B_WQ_FULL = 0, B_WQ_EMPTY = 4, B_WR_FULL = 8, B_WR_EMPTY = 15, B_ACC_FULL = 22,
               B_ACC_EMPTY = 24, B_A_READY = 26, B_A2_READY = 27, B_COUNT = 29;
@@ -1219,6 +1221,7 @@ __device__ __forceinline__ void row_warps_tile(RowCtx& c, const Params& p, int t
                             (dbg == 10 && !odd && ph > 0 && layer - 1 == p.debug_layer);
         if (ph == n_ph) {
             ln_stage<kDbg, kRJ, kAr>(c, p, true, dump_x, dbg == 8, false, -1);
+            row_publish(c, B_A_READY);                   // the head product's A operand
             break;
         }
         const bool cap = layer == p.cap_layer;
@@ -1244,12 +1247,12 @@ __device__ __forceinline__ void row_warps_tile(RowCtx& c, const Params& p, int t
         else      ffn_block<kDbg, kAr>(c, p, lp, sa, cap);
     }
 
-    // ---- heads: fp16 product [32 x 256] x [96 x 256]^T per board on the row warps, with
-    //      mma.sync m16n8k16 and fp16 accumulators, k-steps in rising order, as the reference
-    //      computes it (encoder.cu:309-352, 918-927), so the logits carry its roundings.
-    //      Warp qt of the board takes output columns 24 qt .. 24 qt + 23 (three n-tiles) of
-    //      both 16-row tiles; the fragments go through a staging tile in the (idle) A-operand
-    //      region so that each thread then finds its own row's 16 policy columns. ----
+    // ---- heads: fp16 product [128 x 256] x [96 x 256]^T on the tensor pipe (tcgen05 kind::f16
+    //      with fp16 accumulators, k-steps in rising order: the bits of the reference's
+    //      fp16-accumulate mma.sync product, encoder.cu:309-352, 918-927).  Warp qt of a board
+    //      reads its rows' output columns 24 qt .. 24 qt + 23; they go through a staging tile in
+    //      the (idle) A-operand region so that each thread then finds its own row's 16 policy
+    //      columns and the expansion warp whole rows. ----
     float pre[3] = {0.f, 0.f, 0.f};
     if (p.vmode == 2) prenorm_value(c, p, c.valid ? alive : 0xffffffffu, pre);
     prof_mark<kDbg>(c, PH_LN);
@@ -1257,49 +1260,26 @@ __device__ __forceinline__ void row_warps_tile(RowCtx& c, const Params& p, int t
     // be writing its rows for the next tile): policy columns 0-63 in K-slab 0 at the operand's
     // swizzled row address, the 32 aux columns in K-slab 1.
     const uint32_t stage_pol = c.sm_a, stage_aux = c.sm_a + 16384u;
-    board_sync(c);                                       // this board's rows of the operand are written
+    row_wait_acc<kDbg>(c, 0, PH_LN);
     {
-        const uint4* hf = reinterpret_cast<const uint4*>(p.tail + kTailHeadFrag) + c.lane;
-        uint32_t acc[3][2][2];
+        // this thread's row, output columns 24 qt .. 24 qt + 23 (three groups of eight), one fp16
+        // in the low half of each accumulator word; packed and staged so that every thread then
+        // finds its own row's 16 policy columns and the expansion warp whole rows
+        uint32_t acc[24];
 #pragma unroll
         for (int jj = 0; jj < 3; ++jj)
+            tmem_ld8(c.tm + TM_ACC + 24 * c.qt + 8 * jj, *reinterpret_cast<uint32_t(*)[8]>(&acc[8 * jj]));
+        row_release_acc(c, 0);                           // waits for the loads
 #pragma unroll
-            for (int m = 0; m < 2; ++m) acc[jj][m][0] = acc[jj][m][1] = 0u;
-        uint4 bw[3];
-#pragma unroll
-        for (int jj = 0; jj < 3; ++jj) bw[jj] = __ldg(hf + ((3 * c.qt + jj) * 8) * 32);
-#pragma unroll 1
-        for (int kp = 0; kp < 8; ++kp) {
-            uint4 nx[3];
-            const int kn = kp < 7 ? kp + 1 : kp;
-#pragma unroll
-            for (int jj = 0; jj < 3; ++jj) nx[jj] = __ldg(hf + ((3 * c.qt + jj) * 8 + kn) * 32);
-#pragma unroll
-            for (int h = 0; h < 2; ++h) {
-                const int ks = 2 * kp + h;
-#pragma unroll
-                for (int m = 0; m < 2; ++m) {
-                    uint32_t af[4];
-                    ldmatrix_x4(af, c.sm_r + (ks >> 2) * 16384 +
-                                        sw_off(32 * c.q + 16 * m + (c.lane & 15), 2 * (ks & 3) + (c.lane >> 4)));
-#pragma unroll
-                    for (int jj = 0; jj < 3; ++jj)
-                        mma_f16_f16(acc[jj][m], af, h ? bw[jj].z : bw[jj].x, h ? bw[jj].w : bw[jj].y);
-                }
-            }
-#pragma unroll
-            for (int jj = 0; jj < 3; ++jj) bw[jj] = nx[jj];
+        for (int jj = 0; jj < 3; ++jj) {
+            const int j = 3 * c.qt + jj;
+            const uint32_t base = j < 8 ? stage_pol : stage_aux;
+            sts128(base + sw_off(c.row, j & 7),
+                   make_uint4(__byte_perm(acc[8 * jj], acc[8 * jj + 1], 0x5410),
+                              __byte_perm(acc[8 * jj + 2], acc[8 * jj + 3], 0x5410),
+                              __byte_perm(acc[8 * jj + 4], acc[8 * jj + 5], 0x5410),
+                              __byte_perm(acc[8 * jj + 6], acc[8 * jj + 7], 0x5410)));
         }
-        const int g = c.lane >> 2, t = c.lane & 3;
-#pragma unroll
-        for (int jj = 0; jj < 3; ++jj)
-#pragma unroll
-            for (int m = 0; m < 2; ++m) {
-                const int j = 3 * c.qt + jj, r0 = 32 * c.q + 16 * m + g;
-                const uint32_t base = j < 8 ? stage_pol : stage_aux;
-                sts32(base + sw_off(r0, j & 7) + 4 * t, acc[jj][m][0]);
-                sts32(base + sw_off(r0 + 8, j & 7) + 4 * t, acc[jj][m][1]);
-            }
     }
     board_sync(c);                                       // the board's 32 x 96 logits are staged
     {
@@ -1414,6 +1394,14 @@ __device__ __forceinline__ void producer_loop(uint32_t smem, volatile int* abort
                 bulk_g2s(smem + C::SM_RING + s * kRStage, src, bytes, bar_addr(smem, B_WR_FULL + s));
                 src += bytes;
             }
+        }
+        // the head matrix: four K-slabs of 96 rows in 16 KB slots
+        for (uint32_t st = 0; st < kHeadStages; ++st, ++ri) {
+            const uint32_t s = ri % kRS;
+            mbar_wait(bar_addr(smem, B_WR_EMPTY + s), (ri / kRS - 1u) & 1u, abort_flag, kErrProducer);
+            mbar_arrive_expect_tx(bar_addr(smem, B_WR_FULL + s), kHeadStage);
+            bulk_g2s(smem + C::SM_RING + s * kRStage, src, kHeadStage, bar_addr(smem, B_WR_FULL + s));
+            src += kHeadStage;
         }
     }
     // Every copy issued has been waited for by the MMA issuer on the normal path.  After a
@@ -1566,6 +1554,12 @@ __device__ __forceinline__ void mma_loop(uint32_t smem, uint32_t tmem, volatile 
             }
             }
         }
+        // heads: [128 x 256] x [96 x 256]^T in fp16 with fp16 accumulators, sixteen steps of
+        // sixteen in rising order -- the bits of the reference's fp16-accumulate mma.sync head
+        // product (encoder.cu:309-352, 918-927); A is the final norm's output in the staging region
+        mma_wait_operand(smem, abort_flag, B_A_READY, st.aready);
+        mma_unit<kAr>(smem, abort_flag, st, acc0, 0, sm_r, false, kHeadStages,
+                      umma_idesc(kAccF16, kFmtF16, kFmtF16, 128, 96), kKindF16);
     }
 }
 
@@ -2048,7 +2042,7 @@ int bf_create(const void* blob, size_t blob_bytes, int device, bf_handle** out) 
                                 : hdr.quant == 4 ? bf::Cfg<bf::kArI8Qkv>::kLayerStream
                                 : hdr.quant == 0 ? bf::Cfg<bf::kArF16>::kLayerStream
                                                  : bf::Cfg<bf::kArInt8>::kLayerStream;
-    if (hdr.bytes_w != static_cast<uint64_t>(hdr.n_layers) * layer_stream ||
+    if (hdr.bytes_w != static_cast<uint64_t>(hdr.n_layers) * layer_stream + bf::kHeadStages * bf::kHeadStage ||
         hdr.bytes_lp != static_cast<uint64_t>(hdr.n_layers) * bf::kLparamStride ||
         hdr.bytes_emb != 184u * 256u * 2u || hdr.bytes_tail != bf::kTailBytes || hdr.rj_mode > 2 ||
         hdr.bytes_rj != (hdr.rj_mode ? static_cast<uint64_t>(hdr.n_layers) * hdr.rj_mode * 16u : 0u))
@@ -2628,7 +2622,8 @@ int bf_forward_noalloc(int device, const void* blob_dev, size_t blob_bytes, cons
             return fail(BF_EINVAL, "blob header does not match (magic, version or size)");
         if (hdr.n_layers < 1 || hdr.n_layers > 64 ||
             hdr.quant != 3 ||
-            hdr.bytes_w != static_cast<uint64_t>(hdr.n_layers) * bf::Cfg<bf::kArInt8>::kLayerStream ||
+            hdr.bytes_w != static_cast<uint64_t>(hdr.n_layers) * bf::Cfg<bf::kArInt8>::kLayerStream +
+                               bf::kHeadStages * bf::kHeadStage ||
             hdr.bytes_lp != static_cast<uint64_t>(hdr.n_layers) * bf::kLparamStride ||
             hdr.bytes_emb != 184u * 256u * 2u || hdr.bytes_tail != bf::kTailBytes || hdr.rj_mode != 0 ||
             ((hdr.off_w | hdr.off_lp | hdr.off_emb | hdr.off_tail) & 255u) ||

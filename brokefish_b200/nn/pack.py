@@ -19,19 +19,19 @@ Blob layout (all offsets 256-byte aligned, little endian; mirrored by
 
     header   256 B   magic, version, n_layers, n_value, vmode, eps, rj_mode, quant, section table
                      (offset, bytes of wstream, lparams, emb, tail, rj), total bytes
-    wstream  n_layers * 786432 B
+    wstream  n_layers * 786432 B + 49152 B
                      per layer 8 QKV stages [192 rows x 128 B], then 36 stages
                      [128 rows x 128 B]: out-proj (2 units) and the FFN units in
-                     issue order
+                     issue order; after the last layer the [96 x 256] fp16 head matrix
+                     (policy rows 0-63, promo 64-67, value from 68) as 4 stages
+                     [96 rows x 128 B], one per K-slab of 64 columns
     lparams  n_layers * 4736 B
                      per layer 18 fp32 weight scales (qkv 6, out 2, ff1 8, ff2 2; padded
                      to 128 B) then fp16 biases: qkv (chunk order) 768, out 256,
                      ff1 1024, ff2 256
     emb      184 * 256 fp16: square, type_special, color_turn, clock, rep tables
     tail     1280 fp16: norm_f gamma, beta, then the value head's rows as three plain
-             row-major vectors (zero rows beyond n_value); then the packed [96 x 256] fp16 head
-             matrix in ``mma.sync m16n8k16`` B-fragment order (49152 B, see
-             :func:`head_fragments`)
+             row-major vectors (zero rows beyond n_value)
     rj       (only with per-layer input re-injection) sites * 8 fp16: five coefficients per
              site (square, type_special, color_turn, clock, rep), padded to 8; 16 sites
              when both norms of a layer inject, 8 when only the attention norm does
@@ -55,7 +55,7 @@ from brokefish_b200.nn.model import (BrokefishNet, EMB_TABLES, N_POLICY, N_PROMO
 from brokefish_b200.nn.quant import Q_MAX, quantise_weights_bytes, quantise_weights_int8_bytes
 
 MAGIC = 0x38424642          # "BFB8"
-VERSION = 3
+VERSION = 4
 HEADER_BYTES = 256
 D, DFF, H, DH, T = 256, 1024, 8, 32, 32
 NHEAD = 96                   # head matrix rows: 64 policy, 4 promo, 1-3 value, zero pad
@@ -161,27 +161,6 @@ def fold_and_quantise(net: BrokefishNet, fmt: str = "int8") -> List[FoldedLayer]
     return out
 
 
-def head_fragments(head: np.ndarray) -> np.ndarray:
-    """``[96, 256]`` fp16 head matrix -> ``[12 n-tiles, 8 k-pairs, 32 lanes, 8]`` fp16: what
-    lane ``4 g + t`` feeds ``mma.sync.m16n8k16`` as the B operand for output columns
-    ``8 j .. 8 j + 7`` and the two k-steps ``2 kp, 2 kp + 1``, one 16-byte load:
-    ``W[8j+g][16 ks + 2t, +1]`` then ``W[8j+g][16 ks + 8 + 2t, +1]`` for each k-step ``ks``.
-    The head product runs on the row warps with fp16 accumulators, k-steps in rising order,
-    as the reference's does (csrc/encoder.cu:309-352, 918-927), so the logits carry the same
-    roundings."""
-    out = np.zeros((NHEAD // 8, 8, 32, 8), dtype=np.float16)
-    lane = np.arange(32)
-    g, t = lane >> 2, lane & 3
-    for j in range(NHEAD // 8):
-        rows = head[8 * j + g]                                    # [32 lanes, 256]
-        for kp in range(8):
-            for h in range(2):
-                k0 = 16 * (2 * kp + h)
-                for e, off in enumerate((0, 1, 8, 9)):
-                    out[j, kp, lane, 4 * h + e] = rows[lane, k0 + 2 * t + off]
-    return out
-
-
 def head_matrix(net: BrokefishNet) -> np.ndarray:
     """``[96, 256]`` fp16: policy rows 0-63, promo 64-67, value from 68, zeros after."""
     head = torch.zeros(NHEAD, D, dtype=torch.half)
@@ -277,15 +256,17 @@ def pack_blob(net: BrokefishNet, fmt: str = "int8") -> np.ndarray:
     layers = fold_and_quantise(net, fmt)
     if fmt in ("e4m3", "int8_ffn", "int8_ffn_qkv") and getattr(net, "reinject", "none") != "none":
         raise NotImplementedError("input re-injection is built for the int8 and fp16 arithmetics only")
-    wstream = np.concatenate([_layer_stream(fl) for fl in layers])
+    head_bytes = np.ascontiguousarray(head_matrix(net)).view(np.uint8).reshape(NHEAD, 2 * D)
+    wstream = np.concatenate([_layer_stream(fl) for fl in layers] +
+                             [sw128_image(np.ascontiguousarray(head_bytes[:, 128 * s:128 * s + 128]))
+                              for s in range(4)])
     lparams = np.concatenate([_layer_params(fl) for fl in layers])
     emb = np.concatenate([getattr(net, n).weight.detach().half().cpu().numpy().reshape(-1)
                           for n in EMB_TABLES]).astype("<f2").view(np.uint8)
     val = np.zeros((3, D), dtype=np.float16)
     val[:int(net.value.weight.shape[0])] = net.value.weight.detach().half().cpu().numpy()
     tail = np.concatenate([net.norm_f.weight.detach().half().cpu().numpy(),
-                           net.norm_f.bias.detach().half().cpu().numpy(), val.reshape(-1),
-                           head_fragments(head_matrix(net)).reshape(-1)]
+                           net.norm_f.bias.detach().half().cpu().numpy(), val.reshape(-1)]
                           ).astype("<f2").view(np.uint8)
     rj_mode = REINJECT_MODE_ID.get(getattr(net, "reinject", "none"), 0)
     rj = np.zeros(0, dtype=np.uint8)

@@ -34,7 +34,7 @@ extern "C" {
 #define BF_EDEVICE (-4)  /* a device-side bounded wait ran out */
 
 #define BF_BLOB_MAGIC 0x38424642u /* "BFB8" */
-#define BF_BLOB_VERSION 3u
+#define BF_BLOB_VERSION 4u
 
 /* GEMM selectors for bf_forward_capture. */
 #define BF_OP_QKV 0 /* A: LN1 output s8 [rows,256]; acc [rows,768] in chunk order        */

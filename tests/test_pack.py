@@ -51,11 +51,11 @@ def test_blob_layout_decodes_back(nets, folded):
     net, fl = nets["B"], folded["B"]
     blob = pack.pack_blob(net)
     magic, ver, nl, nv, vm, eps = struct.unpack_from("<IIIIIf", blob, 0)
-    assert (magic, ver, nl, nv, vm) == (pack.MAGIC, 3, 8, 1, 0) and abs(eps - 1e-5) < 1e-12
+    assert (magic, ver, nl, nv, vm) == (pack.MAGIC, 4, 8, 1, 0) and abs(eps - 1e-5) < 1e-12
     offs = struct.unpack_from("<11Q", blob, 32)
     off_w, bytes_w, off_lp, bytes_lp, off_emb, bytes_emb, off_tail, bytes_tail, off_rj, bytes_rj, total = offs
-    assert bytes_rj == 0 and bytes_tail == 2560 + 96 * 256 * 2
-    assert total == blob.size and bytes_w == 8 * 786432 and bytes_lp == 8 * 4736
+    assert bytes_rj == 0 and bytes_tail == 2560
+    assert total == blob.size and bytes_w == 8 * 786432 + 4 * 96 * 128 and bytes_lp == 8 * 4736
     assert all(o % 256 == 0 for o in (off_w, off_lp, off_emb, off_tail))
     # layer 3, FFN unit 9 = ff2, hidden chunk 1, output half 1; its K-slab 1
     layer, unit, slab = 3, 9, 1
@@ -77,15 +77,16 @@ def test_blob_layout_decodes_back(nets, folded):
     assert np.array_equal(lp[64:72].view("<f4"), fl[layer].s_ff2)
     bq = lp[128:128 + 1536].view("<f2")
     assert bq[2 * 192 + 130] == fl[layer].b_qkv[512 + 128 + 2]
-    # head matrix in mma B-fragment order behind the 1280 halves of norm / value rows: lane
-    # 4g + t of n-tile j, k-step ks holds W[8j+g][16ks+2t, +1] and W[8j+g][16ks+8+2t, +1]
+    # the head matrix closes the weight stream: 4 K-slabs of [96 rows][128 B], swizzled like
+    # every other stage; row 68 is the first value row
     head = pack.head_matrix(net)
-    frag = blob[off_tail + 2560:off_tail + bytes_tail].view("<f2").reshape(12, 8, 32, 8)
-    j, ks, g, t = 8, 5, 4, 3                      # row 68 = the first value row
-    got = frag[j, ks // 2, 4 * g + t, 4 * (ks % 2):4 * (ks % 2) + 4]
-    k0 = 16 * ks + 2 * t
-    assert np.array_equal(got, head[8 * j + g, [k0, k0 + 1, k0 + 8, k0 + 9]])
-    assert np.array_equal(np.sort(frag.reshape(-1)), np.sort(head.reshape(-1)))
+    slab, r, grp = 2, 68, 6
+    at = off_w + 8 * 786432 + slab * 96 * 128
+    got = blob[at + r * 128 + ((grp ^ (r & 7)) * 16):][:16].view("<f2")
+    assert np.array_equal(got, head[r, 64 * slab + 8 * grp:64 * slab + 8 * grp + 8])
+    tail = blob[off_tail:off_tail + bytes_tail].view("<f2")
+    assert np.array_equal(tail[:256], net.norm_f.weight.detach().half().numpy())
+    assert np.array_equal(tail[512:768], head[68])
 
 
 def test_packer_rejects_other_widths():
