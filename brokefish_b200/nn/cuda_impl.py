@@ -5,14 +5,14 @@ Same constructor, attributes, methods and errors as the reference's CUDA impleme
 ``include/brokefish_b200.h``.  PyTorch is used for device memory and the current stream
 only.
 
-Three arithmetics are built: the reference's ``int8=True`` path (scheme ``"all"``: QKV,
-out-projection and both FFN matmuls in int8, heads and attention in fp16), which is the
-default here and whose outputs equal the reference kernel's bit for bit, and its
-``fp8=True`` path (the two FFN matmuls in e4m3 with ``amax/8`` scales,
-QKV and out-projection in fp16), and the plain fp16 arithmetic (``int8=False``: the reference's
-own default; every weight GEMM fp16 with fp16 accumulators on tcgen05, which carry the bits of
-the reference's ``mma.sync``).  The partial int8 schemes are not built: asking for them raises
-``NotImplementedError`` instead of silently running something else.
+All five arithmetics of the reference are built: its ``int8=True`` path (scheme ``"all"``:
+QKV, out-projection and both FFN matmuls in int8, heads and attention in fp16), which is the
+default here and whose outputs equal the reference kernel's bit for bit; the partial schemes
+``int8_scheme="ffn"`` and ``"ffn+qkv"`` (the other GEMMs in fp16), bit for bit as well; its
+``fp8=True`` path (the two FFN matmuls in e4m3 with ``amax/8`` scales, QKV and out-projection
+in fp16), a tolerance; and the plain fp16 arithmetic (``int8=False``: the reference's own
+default; every weight GEMM fp16 with fp16 accumulators on tcgen05, which carry the bits of
+the reference's fp16-accumulate ``mma.sync``), bit for bit.
 
 The weights are a *snapshot*: folded, quantised and uploaded once in the constructor.
 After a weight update, build a new ``FusedEncoder``.

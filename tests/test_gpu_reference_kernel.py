@@ -7,9 +7,10 @@ weights.  Skipped when the built reference is not present (it is not part of the
 
 Bar for the int8 arithmetic (the path the metric is quoted on): BIT IDENTITY.  The product
 keeps the reference kernel's own rounding points and summation orders -- LayerNorm partial
-sums and butterfly, hardware 1/sqrt, fp16-accumulate ``mma.sync`` for the attention and head
-products, ``__expf`` softmax, the fused multiply-add in the ff2 running total -- and moves
-only the exact-integer GEMMs to tcgen05, so every layer-0 debug stage, the final norm after
+sums and butterfly, hardware 1/sqrt, fp16 accumulation in the attention products
+(``mma.sync``) and in the head product (tcgen05 with fp16 accumulators, which gives the same
+bits), ``__expf`` softmax, the fused multiply-add in the ff2 running total -- and runs the
+exact-integer GEMMs on tcgen05, so every layer-0 debug stage, the final norm after
 eight layers, policy, promo and value come out equal to the bit (measured on 2048 positions
 for four weight sets: 0 differing elements, value difference 0.0, argmax agreement 100 %).
 
