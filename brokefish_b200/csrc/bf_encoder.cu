@@ -1260,6 +1260,14 @@ __device__ __forceinline__ void row_warps_tile(RowCtx& c, const Params& p, int t
     // be writing its rows for the next tile): policy columns 0-63 in K-slab 0 at the operand's
     // swizzled row address, the 32 aux columns in K-slab 1.
     const uint32_t stage_pol = c.sm_a, stage_aux = c.sm_a + 16384u;
+    // while the head product runs: the legality words, given or (for the expansion warp, lane =
+    // slot) generated here
+    unsigned long long lw = ~0ull, moves = 0ull;
+    if (p.legal != nullptr && c.valid) lw = p.legal[c.grow];
+    if (p.prior != nullptr && c.qt == 1 && c.valid) {
+        bool in_check;
+        moves = p.legal != nullptr ? lw : bfmg::legal_word(word, ctl, in_check);
+    }
     row_wait_acc<kDbg>(c, 0, PH_LN);
     {
         // this thread's row, output columns 24 qt .. 24 qt + 23 (three groups of eight), one fp16
@@ -1295,8 +1303,6 @@ __device__ __forceinline__ void row_warps_tile(RowCtx& c, const Params& p, int t
             }
         }
         uint32_t lg[8];
-        unsigned long long lw = ~0ull;
-        if (p.legal != nullptr && c.valid) lw = p.legal[c.grow];
         const uint32_t bits = static_cast<uint32_t>(lw >> (16 * c.qt)) & 0xffffu;
 #pragma unroll
         for (int i = 0; i < 8; ++i) {
@@ -1307,12 +1313,6 @@ __device__ __forceinline__ void row_warps_tile(RowCtx& c, const Params& p, int t
         }
         if (c.valid && p.policy != nullptr) store_words<8>(p.policy + c.grow * 64 + 16 * c.qt, lg);
         if (p.prior != nullptr && c.qt == 1) {
-            // without legality words from the caller the warp generates them itself (lane = slot)
-            unsigned long long moves = 0ull;
-            if (c.valid) {
-                bool in_check;
-                moves = p.legal != nullptr ? lw : bfmg::legal_word(word, ctl, in_check);
-            }
             expand_board(p, board, c.lane, c.valid, word, ctl, moves, stage_pol, stage_aux, c.row);
         }
         if (c.qt == 0) {
