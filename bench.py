@@ -125,10 +125,10 @@ def engine(enc, dev, n=1 << 20, steps=10, warmup=3):
              lambda: _native.check(L.bf_movegen(idx, ptr(b), ptr(c), n, ptr(mask), ptr(chk), stream), "bf_movegen")),
             ("step", 64 + 2 + 4 + 64 + 2 + 1,
              lambda: _native.check(L.bf_step(idx, ptr(b), ptr(c), ptr(move), None, n, ptr(nb), ptr(nc), ptr(irr),
-                                             None, None, stream), "bf_step")),
+                                             None, None, None, stream), "bf_step")),
             ("step+movegen (play)", 64 + 2 + 4 + 64 + 2 + 1 + 256 + 1,
              lambda: _native.check(L.bf_step(idx, ptr(b), ptr(c), ptr(move), None, n, ptr(nb), ptr(nc), ptr(irr),
-                                             ptr(mask), ptr(chk), stream), "bf_step"))):
+                                             ptr(mask), ptr(chk), None, stream), "bf_step"))):
         t = timed(fn)
         gbs = n * bytes_per_board / t / 1e6
         print(json.dumps({"engine_kernel": name, "boards": n, "ms_per_launch_median": t, "boards_per_s": n / t * 1e3,

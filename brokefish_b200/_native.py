@@ -30,7 +30,8 @@ EXPORTS = ["bf_version", "bf_last_error", "bf_create", "bf_destroy", "bf_info", 
            "bf_forward_noalloc", "bf_noalloc_status", "bf_selftest_umma", "bf_set_option", "bf_measure_i8_peak", "bf_forward_priors",
            "bf_forward_priors_host", "bf_selftest_timeout", "bf_movegen", "bf_step", "bf_random_ply",
            "bf_forward_leaves", "bf_measure_elementwise", "bf_forward_backbone", "bf_int8_q_max",
-           "bf_fp8_q_max", "bf_terminal"]
+           "bf_fp8_q_max", "bf_terminal", "bf_hash", "bf_history_push",
+           "bf_repetition_count"]
 
 
 def nvcc_path() -> str:
@@ -98,9 +99,12 @@ def lib() -> ctypes.CDLL:
     L.bf_int8_q_max.restype = None
     L.bf_fp8_q_max.argtypes = []
     L.bf_fp8_q_max.restype = ctypes.c_double
-    L.bf_terminal.argtypes = [i32, vp, vp, vp, vp, i32, vp, vp, vp]
+    L.bf_terminal.argtypes = [i32, vp, vp, vp, vp, vp, i32, vp, vp, vp]
+    L.bf_hash.argtypes = [i32, vp, vp, i32, vp, vp]
+    L.bf_history_push.argtypes = [i32, vp, vp, vp, vp, i32, vp]
+    L.bf_repetition_count.argtypes = [i32, vp, vp, vp, i32, vp, vp]
     L.bf_random_ply.argtypes = [i32, vp, vp, vp, vp, vp, i32, vp, vp]
-    L.bf_step.argtypes = [i32, vp, vp, vp, vp, i32, vp, vp, vp, vp, vp, vp]
+    L.bf_step.argtypes = [i32, vp, vp, vp, vp, i32, vp, vp, vp, vp, vp, vp, vp]
     L.bf_forward_priors_host.argtypes = [vp, vp, vp, vp, vp, i32, i32, vp, vp, vp, vp]
     L.bf_measure_i8_peak.argtypes = [i32, i32, ctypes.POINTER(ctypes.c_double), ctypes.POINTER(ctypes.c_double)]
     L.bf_launch_count.argtypes = [vp]

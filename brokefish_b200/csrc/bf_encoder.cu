@@ -2160,14 +2160,56 @@ int bf_movegen(int device, const uint16_t* boards, const int16_t* control, int n
     bfmg::engine_board_kernel<false, false><<<(n + bfmg::kTpbThreads - 1) / bfmg::kTpbThreads, bfmg::kTpbThreads,
                                                bfmg::kTpbSmem, static_cast<cudaStream_t>(stream)>>>(
         boards, control, nullptr, nullptr, nullptr, n, nullptr, nullptr, nullptr,
-        reinterpret_cast<unsigned long long*>(mask), in_check, nullptr);
+        reinterpret_cast<unsigned long long*>(mask), in_check, nullptr, nullptr);
+    BF_CUDA(cudaGetLastError());
+    return BF_OK;
+}
+
+int bf_hash(int device, const uint16_t* boards, const int16_t* control, int n, uint64_t* hash, void* stream) {
+    if (n < 0) return fail(BF_EINVAL, "n must be >= 0");
+    if (n == 0) return BF_OK;
+    if (boards == nullptr || control == nullptr || hash == nullptr)
+        return fail(BF_EINVAL, "boards, control and hash must be non-null");
+    BF_CUDA(cudaSetDevice(device));
+    bfmg::engine_board_kernel<false, false><<<(n + bfmg::kTpbThreads - 1) / bfmg::kTpbThreads, bfmg::kTpbThreads,
+                                               bfmg::kTpbSmem, static_cast<cudaStream_t>(stream)>>>(
+        boards, control, nullptr, nullptr, nullptr, n, nullptr, nullptr, nullptr, nullptr, nullptr, nullptr,
+        reinterpret_cast<unsigned long long*>(hash));
+    BF_CUDA(cudaGetLastError());
+    return BF_OK;
+}
+
+int bf_history_push(int device, uint64_t* ring, long long* length, const uint64_t* hash,
+                    const unsigned char* irreversible, int n, void* stream) {
+    if (n < 0) return fail(BF_EINVAL, "n must be >= 0");
+    if (n == 0) return BF_OK;
+    if (ring == nullptr || length == nullptr || hash == nullptr || irreversible == nullptr)
+        return fail(BF_EINVAL, "ring, length, hash and irreversible must be non-null");
+    BF_CUDA(cudaSetDevice(device));
+    bfmg::history_push_kernel<<<(n + 127) / 128, 128, 0, static_cast<cudaStream_t>(stream)>>>(
+        reinterpret_cast<unsigned long long*>(ring), length, reinterpret_cast<const unsigned long long*>(hash),
+        irreversible, n);
+    BF_CUDA(cudaGetLastError());
+    return BF_OK;
+}
+
+int bf_repetition_count(int device, const uint64_t* hash, const uint64_t* ring, const long long* length, int n,
+                        int* count, void* stream) {
+    if (n < 0) return fail(BF_EINVAL, "n must be >= 0");
+    if (n == 0) return BF_OK;
+    if (ring == nullptr || length == nullptr || hash == nullptr || count == nullptr)
+        return fail(BF_EINVAL, "hash, ring, length and count must be non-null");
+    BF_CUDA(cudaSetDevice(device));
+    bfmg::repetition_kernel<<<(n + 127) / 128, 128, 0, static_cast<cudaStream_t>(stream)>>>(
+        reinterpret_cast<const unsigned long long*>(hash), reinterpret_cast<const unsigned long long*>(ring), length,
+        n, count);
     BF_CUDA(cudaGetLastError());
     return BF_OK;
 }
 
 int bf_step(int device, const uint16_t* boards, const int16_t* control, const int* move,
             const signed char* promo, int n, uint16_t* boards_out, int16_t* control_out,
-            unsigned char* irreversible, uint64_t* mask, unsigned char* in_check, void* stream) {
+            unsigned char* irreversible, uint64_t* mask, unsigned char* in_check, uint64_t* hash, void* stream) {
     if (n < 0) return fail(BF_EINVAL, "n must be >= 0");
     if (n == 0) return BF_OK;
     if (boards == nullptr || control == nullptr || move == nullptr || boards_out == nullptr || control_out == nullptr)
@@ -2176,20 +2218,21 @@ int bf_step(int device, const uint16_t* boards, const int16_t* control, const in
     bfmg::engine_board_kernel<true, false><<<(n + bfmg::kTpbThreads - 1) / bfmg::kTpbThreads, bfmg::kTpbThreads,
                                               bfmg::kTpbSmem, static_cast<cudaStream_t>(stream)>>>(
         boards, control, move, promo, nullptr, n, boards_out, control_out, irreversible,
-        reinterpret_cast<unsigned long long*>(mask), in_check, nullptr);
+        reinterpret_cast<unsigned long long*>(mask), in_check, nullptr, reinterpret_cast<unsigned long long*>(hash));
     BF_CUDA(cudaGetLastError());
     return BF_OK;
 }
 
 int bf_terminal(int device, const uint64_t* mask, const unsigned char* in_check, const int16_t* control,
-                const uint16_t* boards, int n, unsigned char* code, signed char* result, void* stream) {
+                const uint16_t* boards, const int* rep_count, int n, unsigned char* code, signed char* result,
+                void* stream) {
     if (n < 0) return fail(BF_EINVAL, "n must be >= 0");
     if (n == 0) return BF_OK;
     if (mask == nullptr || in_check == nullptr || control == nullptr || boards == nullptr || code == nullptr)
         return fail(BF_EINVAL, "mask, in_check, control, boards and code must be non-null");
     BF_CUDA(cudaSetDevice(device));
     bfmg::terminal_kernel<<<(n + 127) / 128, 128, 0, static_cast<cudaStream_t>(stream)>>>(
-        reinterpret_cast<const unsigned long long*>(mask), in_check, control, boards, n, code, result);
+        reinterpret_cast<const unsigned long long*>(mask), in_check, control, boards, rep_count, n, code, result);
     BF_CUDA(cudaGetLastError());
     return BF_OK;
 }
@@ -2204,7 +2247,7 @@ int bf_random_ply(int device, uint16_t* boards, int16_t* control, uint64_t* mask
     bfmg::engine_board_kernel<true, true><<<(n + bfmg::kTpbThreads - 1) / bfmg::kTpbThreads, bfmg::kTpbThreads,
                                              bfmg::kTpbSmem, static_cast<cudaStream_t>(stream)>>>(
         boards, control, nullptr, promo, r, n, boards, control, nullptr,
-        reinterpret_cast<unsigned long long*>(mask), nullptr, move);
+        reinterpret_cast<unsigned long long*>(mask), nullptr, move, nullptr);
     BF_CUDA(cudaGetLastError());
     return BF_OK;
 }

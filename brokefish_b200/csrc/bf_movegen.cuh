@@ -563,7 +563,77 @@ __device__ __forceinline__ void board_step(unsigned* my, int control, int move, 
     irreversible = captured >= 0 || is_pawn || board_rights(my) != rights_before;
 }
 
+// Position keys.  The reference hashes a position with a table of random 64-bit keys indexed by
+// (colour, type, square), side to move, the four castling rights and the file of a LEGAL en
+// passant capture (brokefish/env/torch_impl.py:374-401, 321-371); only equality of hashes is
+// ever used (repetition), so the keys here are this library's own: a 64-bit mix of the index.
+__device__ __forceinline__ unsigned long long zobrist_key(int index) {
+    unsigned long long x = 0x9E3779B97F4A7C15ull * static_cast<unsigned long long>(index + 1);
+    x = (x ^ (x >> 30)) * 0xBF58476D1CE4E5B9ull;
+    x = (x ^ (x >> 27)) * 0x94D049BB133111EBull;
+    return x ^ (x >> 31);
+}
+enum { ZOBRIST_SIDE = 768, ZOBRIST_CASTLE = 769, ZOBRIST_EP = 773 };
+
+// Hash of a board held by one thread.  The en passant file counts only when a capture is really
+// available: a pawn of the mover stands beside the pawn that has just made its double step, and
+// taking it does not leave the mover's king attacked.
+__device__ __forceinline__ unsigned long long board_hash(const unsigned* my, bool black) {
+    unsigned long long h = black ? zobrist_key(ZOBRIST_SIDE) : 0ull;
+    unsigned long long occ = 0, my_pawns = 0, my_king = 0, flagged = 0;
+    unsigned long long e_pawns = 0, e_knights = 0, e_diag = 0, e_line = 0, e_king = 0;
+#pragma unroll 1
+    for (int p = 0; p < 32; ++p) {
+        const unsigned word = piece_word(my, p);
+        if ((word >> 11) & 1u) continue;
+        const bool is_black = (word >> 10) & 1u, special = (word >> 9) & 1u;
+        const int type = (word >> 6) & 7, sq = word & 63;
+        const unsigned long long bb = 1ull << sq;
+        h ^= zobrist_key(((is_black ? 6 : 0) + type) * 64 + sq);
+        occ |= bb;
+        if (is_black == black) {
+            if (type == PAWN) my_pawns |= bb;
+            if (type == KING) my_king |= bb;
+        } else {
+            if (type == PAWN) { e_pawns |= bb; if (special) flagged |= bb; }
+            else if (type == KNIGHT) e_knights |= bb;
+            else if (type == KING) e_king |= bb;
+            else {
+                if (type == BISHOP || type == QUEEN) e_diag |= bb;
+                if (type == ROOK || type == QUEEN) e_line |= bb;
+            }
+        }
+    }
+    const unsigned rights = board_rights(my);
+#pragma unroll
+    for (int i = 0; i < 4; ++i)
+        if ((rights >> i) & 1u) h ^= zobrist_key(ZOBRIST_CASTLE + i);
+    if (flagged != 0ull) {
+        const unsigned long long victim = flagged & (0ull - flagged);
+        const int vsq = __ffsll(static_cast<long long>(victim)) - 1, vfile = vsq & 7;
+        const unsigned long long target = black ? victim >> 8 : victim << 8;
+        const int ksq = my_king ? __ffsll(static_cast<long long>(my_king)) - 1 : 0;
+        bool legal = false;
+#pragma unroll
+        for (int side = 0; side < 2; ++side) {
+            const unsigned long long capturer = side ? ((victim << 1) & ~kFileA) : ((victim >> 1) & ~kFileH);
+            if ((capturer & my_pawns) == 0ull) continue;
+            const unsigned long long after = ((occ & ~capturer) & ~victim) | target;
+            const bool hit = my_king != 0ull &&
+                             ((knight_pattern(my_king) & e_knights) != 0ull ||
+                              (pawn_attacks(my_king, black) & (e_pawns & ~victim)) != 0ull ||
+                              (king_pattern(my_king) & e_king) != 0ull ||
+                              ((line_attacks(my_king, after, diag_ex(ksq)) | line_attacks(my_king, after, anti_ex(ksq))) & e_diag) != 0ull ||
+                              ((line_attacks(my_king, after, rank_ex(ksq)) | line_attacks(my_king, after, file_ex(ksq))) & e_line) != 0ull);
+            legal |= !hit;
+        }
+        if (legal) h ^= zobrist_key(ZOBRIST_EP + vfile);
+    }
+    return h;
+}
+
 // One thread per board, boards and legal words staged through shared memory for coalescing.
+// `hash_out` non-null: the position key of the resulting board.
 // kStep: play `move` first (or, with kPick, the floor(r * count)-th legal move of the incoming
 // `mask` in (slot, square) order; a board without legal moves stays as it is) and write the new
 // board, control word and irreversible flag; `mask` non-null: the legal words of the resulting
@@ -573,7 +643,7 @@ __global__ void __launch_bounds__(kTpbThreads) engine_board_kernel(
         const uint16_t* __restrict__ boards, const int16_t* __restrict__ control, const int* __restrict__ move,
         const signed char* __restrict__ promo, const float* __restrict__ r, int n, uint16_t* boards_out,
         int16_t* control_out, unsigned char* __restrict__ irreversible, unsigned long long* mask,
-        unsigned char* __restrict__ in_check, int* __restrict__ move_out) {
+        unsigned char* __restrict__ in_check, int* __restrict__ move_out, unsigned long long* __restrict__ hash_out) {
     extern __shared__ unsigned long long tpb_smem[];
     unsigned long long* s_out = tpb_smem;                                        // [128][33]
     unsigned* s_in = reinterpret_cast<unsigned*>(tpb_smem + kTpbThreads * kTpbOutStride);   // [128][17]
@@ -636,6 +706,7 @@ __global__ void __launch_bounds__(kTpbThreads) engine_board_kernel(
             const bool chk = board_moves(my, ctl < 0, out);
             if (in_check != nullptr) in_check[first + tid] = chk ? 1 : 0;
         }
+        if (hash_out != nullptr) hash_out[first + tid] = board_hash(my, ctl < 0);
     }
     __syncthreads();
     if (kStep) {
@@ -651,16 +722,18 @@ __global__ void __launch_bounds__(kTpbThreads) engine_board_kernel(
             mask[first * 32 + j] = s_out[(j >> 5) * kTpbOutStride + (j & 31)];
 }
 
-// Why a game is over, one thread per board (brokefish/env/torch_impl.py:632-676 without the
-// repetition test, which needs the game's history): 1 checkmate, 2 stalemate (no legal move,
-// with or without check), else 3 when the control word's magnitude has reached 101 (fifty moves
-// without capture or pawn move), else 5 when neither side can mate -- no pawn, rook or queen and
+// Why a game is over, one thread per board (brokefish/env/torch_impl.py:632-676): 1 checkmate,
+// 2 stalemate (no legal move, with or without check), else 3 when the control word's magnitude
+// has reached 101 (fifty moves without capture or pawn move), else 4 when the position has
+// occurred three times (`rep_count`, from `repetition_kernel`; skipped when null), else 5 when
+// neither side can mate -- no pawn, rook or queen and
 // either no knight and every bishop on one colour of squares, or one knight and no bishop
 // (torch_impl.py:604-629) -- else 0.  `result` is -1 for checkmate (the side to move lost), else 0.
 __global__ void __launch_bounds__(128) terminal_kernel(const unsigned long long* __restrict__ mask,
                                                        const unsigned char* __restrict__ in_check,
                                                        const int16_t* __restrict__ control,
-                                                       const uint16_t* __restrict__ boards, int n,
+                                                       const uint16_t* __restrict__ boards,
+                                                       const int* __restrict__ rep_count, int n,
                                                        unsigned char* __restrict__ code, signed char* __restrict__ result) {
     const long board = static_cast<long>(blockIdx.x) * blockDim.x + threadIdx.x;
     if (board >= n) return;
@@ -692,9 +765,41 @@ __global__ void __launch_bounds__(128) terminal_kernel(const unsigned long long*
     int out = 0;
     if (any == 0ull) out = in_check[board] ? 1 : 2;
     else if ((c < 0 ? -c : c) >= 101) out = 3;
+    else if (rep_count != nullptr && rep_count[board] >= 3) out = 4;
     else if (heavy == 0 && ((knights == 0 && (dark == 0 || dark == bishops)) || (knights == 1 && bishops == 0))) out = 5;
     code[board] = static_cast<unsigned char>(out);
     if (result != nullptr) result[board] = out == 1 ? -1 : 0;
+}
+
+// The per-game repetition ring (brokefish/env/torch_impl.py:571-602): `ring` [n,100] position keys
+// since the last irreversible move, `length` [n].  Push: record the position being left (`hash`
+// is the key BEFORE the move, `irreversible` describes the move); an irreversible move empties
+// the ring, because nothing at or before it can recur.
+constexpr int kMaxHistory = 100;
+__global__ void __launch_bounds__(128) history_push_kernel(unsigned long long* __restrict__ ring,
+                                                           long long* __restrict__ length,
+                                                           const unsigned long long* __restrict__ hash,
+                                                           const unsigned char* __restrict__ irreversible, int n) {
+    const long g = static_cast<long>(blockIdx.x) * blockDim.x + threadIdx.x;
+    if (g >= n) return;
+    if (irreversible[g]) { length[g] = 0; return; }
+    const long long len = length[g];
+    ring[g * kMaxHistory + (len < kMaxHistory - 1 ? len : kMaxHistory - 1)] = hash[g];
+    length[g] = len + 1 < kMaxHistory ? len + 1 : kMaxHistory;
+}
+// How many times the position has occurred, counting the present one.
+__global__ void __launch_bounds__(128) repetition_kernel(const unsigned long long* __restrict__ hash,
+                                                         const unsigned long long* __restrict__ ring,
+                                                         const long long* __restrict__ length, int n,
+                                                         int* __restrict__ count) {
+    const long g = static_cast<long>(blockIdx.x) * blockDim.x + threadIdx.x;
+    if (g >= n) return;
+    const unsigned long long h = hash[g];
+    long long len = length[g];
+    len = len < kMaxHistory ? len : kMaxHistory;
+    int c = 1;
+    for (long long i = 0; i < len; ++i) c += ring[g * kMaxHistory + i] == h;
+    count[g] = c;
 }
 
 }  // namespace bfmg

@@ -65,11 +65,13 @@ def initial_boards(n: int = 1, device="cuda"):
     return start.unsqueeze(0).expand(n, -1).clone(), torch.ones(n, dtype=torch.int16, device=device)
 
 
-def step(boards, control, move, promo=None, with_moves: bool = False):
+def step(boards, control, move, promo=None, with_moves: bool = False, hash=None):
     """Apply ``move [n]`` (``slot * 64 + target``, -1 = no move) with ``promo [n]`` (0..3 =
-    N B R Q, default queen): ``(boards, control, None, irreversible)`` as the reference's
-    ``step`` returns them when no hash is tracked (brokefish/env/torch_impl.py:412-548).  With
-    ``with_moves`` the new positions' ``(mask, in_check)`` are generated in the same launch and
+    N B R Q, default queen): ``(boards, control, hash, irreversible)`` as the reference's
+    ``step`` returns them (brokefish/env/torch_impl.py:412-548); the third element is ``None``
+    unless ``hash`` (the key of the position before the move; any non-None value asks for it) is
+    given, in which case it is the new position's key, computed in the same launch.  With
+    ``with_moves`` the new positions' ``(mask, in_check)`` are generated in that launch too and
     appended.  Moves are not checked for legality."""
     n = _check_position(boards, control)
     dev = boards.device
@@ -84,12 +86,14 @@ def step(boards, control, move, promo=None, with_moves: bool = False):
     irr = torch.zeros(n, dtype=torch.uint8, device=dev)
     mask = torch.zeros(n, 32, dtype=torch.int64, device=dev) if with_moves else None
     chk = torch.zeros(n, dtype=torch.uint8, device=dev) if with_moves else None
+    new_hash = torch.zeros(n, dtype=torch.int64, device=dev) if hash is not None else None
     if n:
         b, c = boards.contiguous(), control.contiguous()
         stream = ctypes.c_void_p(torch.cuda.current_stream(dev).cuda_stream)
         _native.check(_native.lib().bf_step(dev.index or 0, _ptr(b), _ptr(c), _ptr(mv), _ptr(pr), n, _ptr(nb),
-                                            _ptr(nc), _ptr(irr), _ptr(mask), _ptr(chk), stream), "bf_step")
-    out = (nb, nc, None, irr.bool())
+                                            _ptr(nc), _ptr(irr), _ptr(mask), _ptr(chk), _ptr(new_hash), stream),
+                      "bf_step")
+    out = (nb, nc, new_hash, irr.bool())
     return out + (mask, chk.bool()) if with_moves else out
 
 
@@ -101,17 +105,73 @@ def play(boards, control, move, promo=None):
 
 
 NONE, CHECKMATE, STALEMATE, FIFTY_MOVE, REPETITION, INSUFFICIENT = range(6)
+MAX_HISTORY = 100
+
+
+def hash_position(boards, control):
+    """``[n] int64`` position keys (brokefish/env/torch_impl.py:374-401): pieces by (colour,
+    type, square), side to move, castling rights and the file of an en passant capture that is
+    really available.  The key values are this library's own; equal positions have equal keys,
+    which is all the repetition rules use."""
+    n = _check_position(boards, control)
+    h = torch.zeros(n, dtype=torch.int64, device=boards.device)
+    if n:
+        stream = ctypes.c_void_p(torch.cuda.current_stream(boards.device).cuda_stream)
+        _native.check(_native.lib().bf_hash(boards.device.index or 0, _ptr(boards.contiguous()),
+                                            _ptr(control.contiguous()), n, _ptr(h), stream), "bf_hash")
+    return h
+
+
+def empty_history(n: int, device="cuda"):
+    """A per-game repetition ring ``[n, 100] int64`` and its length ``[n] int64``
+    (brokefish/env/torch_impl.py:571-575)."""
+    return (torch.zeros(n, MAX_HISTORY, dtype=torch.int64, device=device),
+            torch.zeros(n, dtype=torch.int64, device=device))
+
+
+def push_history(ring, length, hash, irreversible):
+    """Record the position being left (``hash`` = its key, ``irreversible`` = what ``step`` said
+    about the move), as the reference's ``push_history`` (brokefish/env/torch_impl.py:578-593):
+    new ``(ring, length)``; an irreversible move empties the ring."""
+    n = ring.shape[0]
+    if tuple(ring.shape) != (n, MAX_HISTORY) or ring.dtype is not torch.int64 or not ring.is_cuda:
+        raise ValueError(f"ring must be a CUDA int64 tensor [n, {MAX_HISTORY}]")
+    if tuple(length.shape) != (n,) or length.dtype is not torch.int64 or tuple(hash.shape) != (n,) \
+            or hash.dtype is not torch.int64 or tuple(irreversible.shape) != (n,):
+        raise ValueError("length, hash [n] int64 and irreversible [n] are needed")
+    ring, length = ring.clone(), length.clone()
+    irr = irreversible.to(torch.uint8).contiguous()
+    if n:
+        stream = ctypes.c_void_p(torch.cuda.current_stream(ring.device).cuda_stream)
+        _native.check(_native.lib().bf_history_push(ring.device.index or 0, _ptr(ring), _ptr(length),
+                                                    _ptr(hash.contiguous()), _ptr(irr), n, stream), "bf_history_push")
+    return ring, length
+
+
+def repetition_count(hash, ring, length):
+    """``[n] int64``: how many times the position has occurred, the present one included
+    (brokefish/env/torch_impl.py:596-603); what the network's repetition input and the threefold
+    rule read."""
+    n = ring.shape[0]
+    count = torch.ones(n, dtype=torch.int32, device=ring.device)
+    if n:
+        stream = ctypes.c_void_p(torch.cuda.current_stream(ring.device).cuda_stream)
+        _native.check(_native.lib().bf_repetition_count(ring.device.index or 0, _ptr(hash.contiguous()),
+                                                        _ptr(ring.contiguous()), _ptr(length.contiguous()), n,
+                                                        _ptr(count), stream), "bf_repetition_count")
+    return count.long()
 
 
 def terminal(mask, in_check, control, boards, hash=None, ring=None, length=None):
     """``(code [n] uint8, result [n] int8)``: why each game is over (1 checkmate, 2 stalemate,
     3 fifty-move rule, 5 insufficient material, 0 not over; the first that applies) and its result
     for the side to move (-1 checkmate, else 0) -- the reference's ``terminal``
-    (brokefish/env/torch_impl.py:632-676) called without a history.  Threefold repetition (code
-    4) needs the game's hash ring, which is not kept here: passing one raises."""
-    if hash is not None or ring is not None or length is not None:
-        raise NotImplementedError("the repetition test needs the position hash and its ring, which are not built")
+    (brokefish/env/torch_impl.py:632-676).  Threefold repetition (code 4) is tested when the
+    position's key and the game's ring are given, and skipped otherwise, as in the reference."""
     n = _check_position(boards, control)
+    rep = None
+    if hash is not None and ring is not None and length is not None:
+        rep = repetition_count(hash, ring, length).to(torch.int32)
     dev = boards.device
     if tuple(mask.shape) != (n, 32) or mask.dtype is not torch.int64 or not mask.is_cuda:
         raise ValueError(f"mask must be a CUDA int64 tensor of shape [{n}, 32]")
@@ -123,8 +183,8 @@ def terminal(mask, in_check, control, boards, hash=None, ring=None, length=None)
     if n:
         stream = ctypes.c_void_p(torch.cuda.current_stream(dev).cuda_stream)
         _native.check(_native.lib().bf_terminal(dev.index or 0, _ptr(mask.contiguous()), _ptr(chk),
-                                                _ptr(control.contiguous()), _ptr(boards.contiguous()), n,
-                                                _ptr(code), _ptr(result), stream), "bf_terminal")
+                                                _ptr(control.contiguous()), _ptr(boards.contiguous()), _ptr(rep),
+                                                n, _ptr(code), _ptr(result), stream), "bf_terminal")
     return code, result
 
 

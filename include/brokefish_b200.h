@@ -132,17 +132,36 @@ int bf_movegen(int device, const uint16_t* boards, const int16_t* control, int n
  * checked for legality.  One thread per board; needs no handle. */
 int bf_step(int device, const uint16_t* boards, const int16_t* control, const int* move,
             const signed char* promo, int n, uint16_t* boards_out, int16_t* control_out,
-            unsigned char* irreversible, uint64_t* mask, unsigned char* in_check, void* stream);
+            unsigned char* irreversible, uint64_t* mask, unsigned char* in_check, uint64_t* hash, void* stream);
+
+/* Position keys for repetition detection: `hash` [n] of the given boards (bf_hash), or of the
+ * boards after the move (the `hash` output of bf_step, may be NULL).  A key combines piece
+ * (colour, type, square), side to move, castling rights and the file of an en passant capture
+ * that is really available (a capturer stands beside the pawn and the capture does not expose
+ * its king) -- the definition of the reference's `hash_position` (brokefish/env/torch_impl.py:
+ * 374-401, 321-371).  The key values are this library's own, not the reference's table: only
+ * their equality is meaningful, which is all repetition needs. */
+int bf_hash(int device, const uint16_t* boards, const int16_t* control, int n, uint64_t* hash, void* stream);
+
+/* The per-game repetition ring of the reference (brokefish/env/torch_impl.py:571-602): `ring`
+ * [n,100] keys since the last irreversible move and `length` [n] int64, both updated in place.
+ * bf_history_push records the position being LEFT (`hash` = its key, `irreversible` = what
+ * bf_step said about the move; an irreversible move empties the ring); bf_repetition_count
+ * gives how many times the position `hash` has occurred, counting the present one. */
+int bf_history_push(int device, uint64_t* ring, long long* length, const uint64_t* hash,
+                    const unsigned char* irreversible, int n, void* stream);
+int bf_repetition_count(int device, const uint64_t* hash, const uint64_t* ring, const long long* length, int n,
+                        int* count, void* stream);
 
 /* Why each of `n` games is over, from a position's legal words, check flag, control word and
  * board (device pointers): `code` [n] uint8 = 1 checkmate, 2 stalemate, 3 fifty-move rule
- * (control magnitude >= 101), 5 insufficient material, 0 not over -- the first that applies;
- * `result` [n] int8 (may be NULL) = -1 for checkmate, else 0, from the side to move's point of
- * view.  The reference's `terminal` called without a history
- * (brokefish/env/torch_impl.py:632-676, 604-629); its code 4, threefold repetition, needs the
- * game's hash ring, which this library does not keep. */
+ * (control magnitude >= 101), 4 threefold repetition (`rep_count` [n] from bf_repetition_count;
+ * NULL skips the test), 5 insufficient material, 0 not over -- the first that applies; `result`
+ * [n] int8 (may be NULL) = -1 for checkmate, else 0, from the side to move's point of view.  The
+ * reference's `terminal` (brokefish/env/torch_impl.py:632-676, 604-629). */
 int bf_terminal(int device, const uint64_t* mask, const unsigned char* in_check, const int16_t* control,
-                const uint16_t* boards, int n, unsigned char* code, signed char* result, void* stream);
+                const uint16_t* boards, const int* rep_count, int n, unsigned char* code, signed char* result,
+                void* stream);
 
 /* One ply of a uniform-random playout, in place (device pointers): from `mask` (the legal moves
  * of `boards`, bf_movegen's output) the floor(r[i] * count)-th legal move in (slot, square) order

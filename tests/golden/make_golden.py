@@ -201,6 +201,70 @@ def terminal_answers(env) -> None:
     np.savez_compressed(os.path.join(HERE, "ref_terminal.npz"), **out)
 
 
+def history_answers(env) -> None:
+    """Position keys, the repetition ring and the threefold rule along 192 random games of up to
+    100 plies -- half from the start position, half from positions with three or four pieces,
+    where random play repeats itself often -- as the reference engine counts them: per ply the
+    move played, the repetition count of the position reached and its terminal code with the
+    history given.  And pairs of positions with the reference's verdict on whether their keys
+    are equal (en passant flags that do and do not count, castling rights, side to move)."""
+    sparse = ["8/8/8/4k3/8/8/8/R3K3 w Q - 0 1", "8/8/8/4k3/8/8/8/4KQ2 w - - 0 1", "8/8/8/3nk3/8/8/8/4KN2 b - - 0 1",
+              "8/8/8/4k3/8/8/8/2B1KB2 w - - 0 1", "8/8/4k3/8/8/8/4P3/4K2R w K - 0 1", "6k1/8/8/8/8/8/8/R3K2R b KQ - 0 1"]
+    n, plies = 192, 100
+    bs, cs = [], []
+    for i in range(n):
+        b, c = env.initial_boards(1) if i < n // 2 else env.from_fen(sparse[i % len(sparse)])
+        bs.append(b); cs.append(c)
+    boards, control = torch.cat(bs), torch.cat(cs)
+    gen = torch.Generator(device="cpu").manual_seed(33)
+    mask, chk = env.movegen(boards, control)
+    h = env.hash_position(boards, control)
+    ring, length = env.empty_history(n)
+    active = torch.ones(n, dtype=torch.bool)
+    moves = np.full((plies, n), -1, dtype=np.int32)
+    promos = np.zeros((plies, n), dtype=np.int8)
+    counts = np.zeros((plies, n), dtype=np.uint8)
+    codes = np.zeros((plies, n), dtype=np.uint8)
+    for ply in range(plies):
+        legal = env.bitset_to_bool(mask).reshape(n, 32 * 64)
+        cnt = legal.sum(dim=1)
+        pick = torch.minimum((torch.rand(n, generator=gen) * cnt.clamp(min=1).float()).long(), (cnt - 1).clamp(min=0))
+        move = (legal.cumsum(dim=1) > pick[:, None]).float().argmax(dim=1)
+        move = torch.where(active & (cnt > 0), move, torch.full_like(move, -1))
+        promo = torch.randint(0, 4, (n,), generator=gen)
+        nb, nc, nh, irr = env.step(boards, control, move, promo=promo, hash=h)
+        played = move >= 0
+        r2, l2 = env.push_history(ring, length, h, irr)
+        ring = torch.where(played[:, None], r2, ring)
+        length = torch.where(played, l2, length)
+        boards, control, h = nb, nc, nh
+        mask, chk = env.movegen(boards, control)
+        code, _ = env.terminal(mask, chk, control, boards, h, ring, length)
+        moves[ply], promos[ply] = move.numpy(), promo.numpy()
+        counts[ply] = env.repetition_count(h, ring, length).clamp(max=255).numpy()
+        codes[ply] = code.numpy()
+        active &= code == 0
+    pairs = [("rnbqkbnr/ppp1p1pp/8/3pPp2/8/8/PPPP1PPP/RNBQKBNR w KQkq f6 0 3", "rnbqkbnr/ppp1p1pp/8/3pPp2/8/8/PPPP1PPP/RNBQKBNR w KQkq - 0 3"),
+             ("4k3/8/8/8/4Pp2/8/8/4K3 b - e3 0 1", "4k3/8/8/8/4Pp2/8/8/4K3 b - - 0 1"),
+             ("4k3/8/8/8/4P3/8/8/4K3 b - e3 0 1", "4k3/8/8/8/4P3/8/8/4K3 b - - 0 1"),
+             ("8/8/8/8/k2Pp2Q/8/8/4K3 b - d3 0 1", "8/8/8/8/k2Pp2Q/8/8/4K3 b - - 0 1"),
+             ("r3k2r/8/8/8/8/8/8/R3K2R w KQkq - 0 1", "r3k2r/8/8/8/8/8/8/R3K2R w KQ - 0 1"),
+             ("r3k2r/8/8/8/8/8/8/R3K2R w KQkq - 0 1", "r3k2r/8/8/8/8/8/8/R3K2R b KQkq - 0 1"),
+             ("r3k2r/8/8/8/8/8/8/R3K2R w KQkq - 0 1", "r3k2r/8/8/8/8/8/8/R3K2R w KQkq - 7 9")]
+    pa, pc, qa, qc = [], [], [], []
+    for a, b in pairs:
+        x, y = env.from_fen(a), env.from_fen(b)
+        pa.append(x[0]); pc.append(x[1]); qa.append(y[0]); qc.append(y[1])
+    pa, pc, qa, qc = torch.cat(pa), torch.cat(pc), torch.cat(qa), torch.cat(qc)
+    same = env.hash_position(pa, pc) == env.hash_position(qa, qc)
+    np.savez_compressed(os.path.join(HERE, "ref_history.npz"),
+                        boards=torch.cat(bs).numpy().astype(np.int16), control=torch.cat(cs).numpy().astype(np.int16),
+                        moves=moves, promos=promos, counts=counts, codes=codes,
+                        pair_a=pa.numpy().astype(np.int16), pair_a_control=pc.numpy().astype(np.int16),
+                        pair_b=qa.numpy().astype(np.int16), pair_b_control=qc.numpy().astype(np.int16),
+                        pair_same=same.numpy(), pairs=np.array([f"{a} | {b}" for a, b in pairs]))
+
+
 def main() -> int:
     ap = argparse.ArgumentParser()
     ap.add_argument("--reference", default="/root/reference")
@@ -208,6 +272,7 @@ def main() -> int:
     ap.add_argument("--only-step", action="store_true", help="write ref_step.npz and stop")
     ap.add_argument("--only-shuffled", action="store_true", help="write ref_shuffled.npz and stop")
     ap.add_argument("--only-terminal", action="store_true", help="write ref_terminal.npz and stop")
+    ap.add_argument("--only-history", action="store_true", help="write ref_history.npz and stop")
     args = ap.parse_args()
     sys.path.insert(0, args.reference)
     sys.dont_write_bytecode = True
@@ -222,6 +287,9 @@ def main() -> int:
         return 0
     if args.only_terminal:
         terminal_answers(env)
+        return 0
+    if args.only_history:
+        history_answers(env)
         return 0
     from brokefish.nn import quant as rq                             # reference
     from brokefish.nn.cuda_impl import _fold_norm                    # reference
@@ -381,6 +449,7 @@ def main() -> int:
     step_answers(env)
     shuffled_answers(env)
     terminal_answers(env)
+    history_answers(env)
 
     print("scheme known answers", flush=True)
     g = torch.Generator().manual_seed(1234)
