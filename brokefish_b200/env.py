@@ -3,10 +3,11 @@
 ``movegen(boards, control) -> (mask, in_check)`` with the reference's contract
 (brokefish/env/torch_impl.py:254-291): ``mask [n,32]`` int64, bit ``s`` of word ``p`` set when
 the piece in slot ``p`` may legally move to square ``s``; ``in_check [n]`` bool for the side
-to move.  ``step`` and ``play`` apply a move per board (torch_impl.py:412-548, 680-685; the
-position hash is not tracked), ``initial_boards`` is the start position (torch_impl.py:692-697)
+to move.  ``step`` and ``play`` apply a move per board (torch_impl.py:412-548, 680-685),
+``hash_position``, ``push_history``, ``repetition_count`` and ``terminal`` are the repetition and
+game-end rules (torch_impl.py:374-401, 571-676), ``initial_boards`` is the start position (torch_impl.py:692-697)
 and ``random_playouts`` plays uniform-random games to make evaluator inputs.  One thread per board
-in ``libbrokefish_b200`` (C ABI ``bf_movegen``, ``bf_step``, ``bf_random_ply``); CUDA tensors
+in ``libbrokefish_b200`` (C ABI ``bf_movegen``, ``bf_step``, ``bf_random_ply``, ``bf_hash`` ...); CUDA tensors
 in, CUDA tensors out, on the current stream.  There is no CPU path.
 """
 

@@ -126,7 +126,7 @@ int bf_movegen(int device, const uint16_t* boards, const int16_t* control, int n
  * queen.  Writes the new piece words (in place when boards_out == boards), the new control word
  * (side flipped; magnitude = the fifty-move counter, 1 after a capture or pawn move) and, when
  * non-NULL, `irreversible` [n] (capture, pawn move or a change of castling rights) -- the
- * reference's `step` without its position hash (brokefish/env/torch_impl.py:412-548;
+ * reference's `step` (brokefish/env/torch_impl.py:412-548; `hash` non-NULL: the new position's key too;
  * csrc/movegen.cuh).  When `mask` is non-NULL the legal moves of the NEW position follow in the
  * same launch (bf_movegen's outputs), which is one ply of a self-play loop.  Moves are not
  * checked for legality.  One thread per board; needs no handle. */
