@@ -237,6 +237,9 @@ def main() -> int:
                     help="add the in-kernel phase split (cycles per phase over 5 extra launches) to the line")
     ap.add_argument("--f16", action="store_true",
                     help="time the plain fp16 arithmetic (the reference's default) instead of int8")
+    ap.add_argument("--scheme", default="all", choices=["all", "ffn", "ffn+qkv"],
+                    help="which matmuls run in int8: all four (the shipped scheme, the metric's), the FFN only, "
+                         "or the FFN and QKV (the reference's partial schemes)")
     ap.add_argument("--fp8", action="store_true",
                     help="time the e4m3-FFN arithmetic instead of int8 (a separate line; not the headline)")
     args = ap.parse_args()
@@ -274,7 +277,7 @@ def main() -> int:
     if rank == 0 or world == 1:
         net = BrokefishNet().eval()
         net.load_state_dict(seeded_state(seed=0, std=0.02))
-    ev = ShardedEvaluator(net, rank, world, local, fp8=args.fp8, int8=not args.f16)   # one broadcast of the packed blob
+    ev = ShardedEvaluator(net, rank, world, local, fp8=args.fp8, int8=not args.f16, int8_scheme=args.scheme)   # one broadcast of the packed blob
     enc = ev.encoder
 
     if args.sweep:
@@ -388,7 +391,9 @@ def main() -> int:
         "metric": METRIC, "value": value, "unit": "positions/s", "n_gpus": world,
         "steps": args.steps, "warmup": warmup, "ms_per_step": dev_ms / args.steps,
         "higher_is_better": True, "scaling": scaling, "vs_baseline": None,
-        "dtype": "e4m3 (FFN) + f16" if args.fp8 else ("f16" if args.f16 else "s8"),
+        "dtype": "e4m3 (FFN) + f16" if args.fp8 else ("f16" if args.f16 else
+                                                      {"all": "s8", "ffn": "s8 (FFN) + f16",
+                                                       "ffn+qkv": "s8 (FFN, QKV) + f16"}[args.scheme]),
         "data": data,
         "config": {"workload": WORKLOAD, "positions_per_step": n_global, "parallelism": f"dp{world}",
                    "l2": "flushed between timed iterations (256 MiB fill)",
@@ -396,7 +401,8 @@ def main() -> int:
                    "wall_ms_incl_flush": t_wall * 1e3},
         "roofline": {"bound": "tensor", "achieved": achieved, "peak": peak, "unit": "TFLOP/s",
                      "frac": achieved / peak, "peak_source": peak_src + "; int8 dense nominal 4500",
-                     "traffic": NCU_DRAM_BYTES_PER_LAUNCH if (n_local == 4096 and not args.fp8 and not args.f16) else None,
+                     "traffic": NCU_DRAM_BYTES_PER_LAUNCH if (n_local == 4096 and not args.fp8 and not args.f16
+                                                               and args.scheme == "all") else None,
                      "traffic_source": "ncu dram__bytes_read.sum + dram__bytes_write.sum of one launch at "
                                        "batch 4096 (profiles/encoder_kernel_batch4096_ncu_full.md)",
                      "hbm_algorithmic_GBps": n_local * (BYTES_IN + BYTES_OUT) / (kern_avg_ms * 1e-3) / 1e9},
@@ -429,7 +435,7 @@ def main() -> int:
         # CUDA cores at the rate the row warps' own device functions reach in isolation
         # (per position and layer: 32 rows x the widths below; attention, heads and embedding
         # are not counted, so the floor is an underestimate)
-        if not args.f16 and not args.fp8:
+        if not args.f16 and not args.fp8 and args.scheme == "all":
             widths = {0: 1024, 1: 768 + 256, 2: 1024, 3: 2 * 256, 4: 2 * 256, 5: 256}
             rates, floor_s = {}, 0.0
             for block, width in widths.items():

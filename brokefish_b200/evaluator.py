@@ -63,20 +63,22 @@ class ShardedEvaluator:
     """
 
     def __init__(self, net, rank: int, world: int, device_index: int, fp8: bool = False,
-                 int8: bool = True):
+                 int8: bool = True, int8_scheme: str = "all"):
         import torch.distributed as dist
         from brokefish_b200.nn.cuda_impl import FusedEncoder
         from brokefish_b200.nn.pack import pack_blob
         self.rank, self.world = rank, world
         dev = torch.device("cuda", device_index)
         if world > 1:
-            fmt = "e4m3" if fp8 else ("int8" if int8 else "f16")
+            fmt = "e4m3" if fp8 else ({"all": "int8", "ffn": "int8_ffn", "ffn+qkv": "int8_ffn_qkv"}[int8_scheme]
+                                      if int8 else "f16")
             blob = pack_blob(net, fmt) if rank == 0 else None
             blob_dev = broadcast_blob(blob, dev, src=0)
             torch.cuda.synchronize(dev)
             self.encoder = FusedEncoder.from_blob(blob_dev, device=device_index)
         else:
-            self.encoder = FusedEncoder(net, device=device_index, fp8=fp8, int8=None if fp8 else int8)
+            self.encoder = FusedEncoder(net, device=device_index, fp8=fp8, int8=None if fp8 else int8,
+                                        int8_scheme=int8_scheme)
 
     def shard(self, n: int) -> Tuple[int, int]:
         return shard_bounds(n, self.world, self.rank)
