@@ -2319,14 +2319,31 @@ int bf_forward_host(bf_handle* h, const uint16_t* boards, const int16_t* control
     BF_CUDA(cudaMemcpyAsync(d_control, control, static_cast<size_t>(n) * 2, cudaMemcpyHostToDevice, s));
     BF_CUDA(cudaMemcpyAsync(d_rep, rep, static_cast<size_t>(n), cudaMemcpyHostToDevice, s));
     if (legal) BF_CUDA(cudaMemcpyAsync(d_legal, legal, static_cast<size_t>(n) * 256, cudaMemcpyHostToDevice, s));
-    // The batch goes out as launches of one full wave (one tile per SM) each, so that the
-    // copy-out of a finished wave overlaps the next wave's compute on a second stream.  (Letting
-    // the kernel store the 4.3 KB per position of logits straight into mapped host memory was
-    // measured 10 % slower: the stores back up behind the bus.)
+    // The batch goes out as a few launches of shrinking size, the last one a single wave (one
+    // tile per SM), so that the copy-out of a finished launch overlaps the next launch's compute
+    // on a second stream and only the last wave's copy is exposed.  Copying a position out takes
+    // about a sixth of the time of evaluating it, so each launch may be up to six times as large
+    // as the one after it and its copy still hides; large launches keep the kernel's tile-to-tile
+    // pipelining, which separate one-wave launches lose.  (Letting the kernel store the 4.3 KB
+    // per position of logits straight into mapped host memory was measured 10 % slower: the
+    // stores back up behind the bus.)
     const int wave = h->sm_count * 4;
+    int sizes[16];
+    int n_chunks = 0;
+    {
+        int rest = n, last = wave;
+        while (rest > 0 && n_chunks < 15) {
+            const int m = rest < last ? rest : last;
+            sizes[n_chunks++] = m;
+            rest -= m;
+            last = last <= (1 << 24) ? last * 6 : last;
+        }
+        if (rest > 0) sizes[n_chunks++] = rest;
+    }
     cudaStream_t c = h->copy_stream;
-    for (int lo = 0; lo < n; lo += wave) {
-        const int m = n - lo < wave ? n - lo : wave;
+    int lo = 0;
+    for (int k = n_chunks - 1; k >= 0; lo += sizes[k], --k) {          // largest first
+        const int m = sizes[k];
         const size_t o = static_cast<size_t>(lo);
         int rc = launch(h, reinterpret_cast<uint16_t*>(d_boards) + o * 32, reinterpret_cast<int16_t*>(d_control) + o,
                         d_rep + o, legal ? reinterpret_cast<uint64_t*>(d_legal) + o * 32 : nullptr, m,

@@ -211,8 +211,9 @@ int bf_forward_capture(bf_handle* h, const uint16_t* boards, const int16_t* cont
                        int32_t* acc, void* stream);
 
 /* End-to-end call with HOST buffers (pinned for best speed): copies the inputs to the
- * device, runs the evaluator as launches of one full wave of tiles each, copies each wave's
- * three outputs back on a second stream while the next wave computes, and synchronises.
+ * device, runs the evaluator as a few launches of shrinking size (the last one a single wave of
+ * tiles), copies each launch's three outputs back on a second stream while the next launch
+ * computes -- only the last wave's copy is exposed -- and synchronises.
  * Device staging buffers are owned by the handle and grow to the largest `n` seen. */
 int bf_forward_host(bf_handle* h, const uint16_t* boards, const int16_t* control,
                     const uint8_t* rep, const uint64_t* legal, int n, void* policy,
