@@ -628,12 +628,15 @@ __device__ __forceinline__ void attention_unit(const RowCtx& c, uint32_t alive) 
         mma_f16_f16(o[nt], pa[0], vb[0], vb[1]);      // keys 0-15, then 16-31
         mma_f16_f16(o[nt], pa[1], vb[2], vb[3]);
     }
-    __syncwarp();   // every lane's Q fragments are in registers before Q is overwritten
+    // the outputs go to the staging region's fourth block, which nothing else uses during the
+    // attention loop: the next head pair's Q, K and V can then be staged while a slower warp of
+    // the board is still reading these back
+    const uint32_t os = qs + 49152;
 #pragma unroll
     for (int nt = 0; nt < 4; ++nt) {
         const int row = rq + g;
-        sts32(qs + sw_off(row, 4 * hh + nt) + 4 * t, o[nt][0]);
-        sts32(qs + sw_off(row + 8, 4 * hh + nt) + 4 * t, o[nt][1]);
+        sts32(os + sw_off(row, 4 * hh + nt) + 4 * t, o[nt][0]);
+        sts32(os + sw_off(row + 8, 4 * hh + nt) + 4 * t, o[nt][1]);
     }
 }
 
@@ -689,13 +692,13 @@ __device__ __forceinline__ void attention_block(RowCtx& c, const Params& p, cons
         prof_mark<kDbg>(c, PH_PAIR_BAR);
         attention_unit(c, alive);
         prof_mark<kDbg>(c, PH_ATTENTION);
-        board_sync(c);                     // all four warps' outputs are in the Q block
+        board_sync(c);                     // all four warps' outputs are in the output block
         {
             // read back 16 of this row's 64 outputs of the head pair, park them in tensor memory
             uint32_t oh[8];
 #pragma unroll
             for (int k = 0; k < 2; ++k) {
-                const uint4 v = lds128(c.sm_r + sw_off(c.row, 2 * c.qt + k));
+                const uint4 v = lds128(c.sm_r + 49152 + sw_off(c.row, 2 * c.qt + k));
                 oh[4 * k] = v.x; oh[4 * k + 1] = v.y; oh[4 * k + 2] = v.z; oh[4 * k + 3] = v.w;
             }
             o_amax = fmaxf(o_amax, amax_h2<8>(oh, true));
@@ -703,7 +706,9 @@ __device__ __forceinline__ void attention_block(RowCtx& c, const Params& p, cons
             if (kDbg && dbgl && dbg == 4 && c.valid) store_words<8>(p.y + c.grow * kD + 64 * j + 16 * c.qt, oh);
         }
         prof_mark<kDbg>(c, PH_O_READBACK);
-        board_sync(c);                     // staging may be overwritten by the next chunk
+        // no barrier here: the next head pair's staging does not touch the output block, and its
+        // attention units (which do) start only after the barrier that follows that staging,
+        // which every warp reaches after this read-back
     }
     tmem_wait_st();
     prof_mark<kDbg>(c, PH_PAIR_BAR);
