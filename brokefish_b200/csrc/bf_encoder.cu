@@ -33,6 +33,7 @@
 #include <stdio.h>
 #include <string.h>
 
+#include <mutex>
 #include <new>
 #include <string>
 
@@ -1885,6 +1886,26 @@ int fail(int code, const std::string& msg) {
             return fail(BF_ECUDA, std::string(#call) + ": " + cudaGetErrorString(e_));    \
     } while (0)
 
+// Makes `device` current for the scope of an entry point and puts the caller's device back on
+// the way out, so that a call on cuda:1 does not leave a single-process multi-GPU program
+// allocating and launching on cuda:1 afterwards.
+struct DeviceScope {
+    int prev = -1;
+    cudaError_t err = cudaSuccess;
+    explicit DeviceScope(int device) {
+        err = cudaGetDevice(&prev);
+        if (err == cudaSuccess && prev != device) err = cudaSetDevice(device);
+        else if (err == cudaSuccess) prev = -1;          // already current: nothing to restore
+    }
+    ~DeviceScope() { if (prev >= 0) cudaSetDevice(prev); }
+    DeviceScope(const DeviceScope&) = delete;
+    DeviceScope& operator=(const DeviceScope&) = delete;
+};
+#define BF_ON_DEVICE(device)                                                                  \
+    DeviceScope device_scope_(device);                                                        \
+    if (device_scope_.err != cudaSuccess)                                                     \
+        return fail(BF_ECUDA, std::string("selecting the device: ") + cudaGetErrorString(device_scope_.err))
+
 struct BlobHeader {
     uint32_t magic, version, n_layers, n_value, vmode;
     float eps;
@@ -1959,7 +1980,7 @@ int launch(bf_handle* h, const uint16_t* boards, const int16_t* control, const u
     if (n == 0) return BF_OK;
     if (bb == nullptr && (boards == nullptr || control == nullptr || rep == nullptr))
         return fail(BF_EINVAL, "boards, control and rep must be non-null");
-    BF_CUDA(cudaSetDevice(h->device));
+    BF_ON_DEVICE(h->device);
     bf::Params p{};
     p.boards = boards; p.control = control; p.rep = rep; p.legal = legal;
     p.n = n; p.n_layers = static_cast<int>(h->hdr.n_layers);
@@ -2031,7 +2052,7 @@ int bf_create(const void* blob, size_t blob_bytes, int device, bf_handle** out) 
     if (out == nullptr) return fail(BF_EINVAL, "out is null");
     *out = nullptr;
     if (blob == nullptr || blob_bytes < 256) return fail(BF_EINVAL, "blob is null or too small");
-    BF_CUDA(cudaSetDevice(device));
+    BF_ON_DEVICE(device);
     BlobHeader hdr;
     BF_CUDA(cudaMemcpy(&hdr, blob, sizeof(hdr), cudaMemcpyDefault));
     if (hdr.magic != BF_BLOB_MAGIC) return fail(BF_EINVAL, "blob magic mismatch");
@@ -2101,7 +2122,7 @@ int bf_create(const void* blob, size_t blob_bytes, int device, bf_handle** out) 
 
 int bf_destroy(bf_handle* h) {
     if (h == nullptr) return BF_OK;
-    cudaSetDevice(h->device);
+    DeviceScope device_scope_(h->device);
     if (h->stream) { cudaStreamSynchronize(h->stream); cudaStreamDestroy(h->stream); }
     if (h->copy_stream) { cudaStreamSynchronize(h->copy_stream); cudaStreamDestroy(h->copy_stream); }
     if (h->chunk_done) cudaEventDestroy(h->chunk_done);
@@ -2161,7 +2182,7 @@ int bf_movegen(int device, const uint16_t* boards, const int16_t* control, int n
     if (n == 0) return BF_OK;
     if (boards == nullptr || control == nullptr || mask == nullptr)
         return fail(BF_EINVAL, "boards, control and mask must be non-null");
-    BF_CUDA(cudaSetDevice(device));
+    BF_ON_DEVICE(device);
     bfmg::engine_board_kernel<false, false><<<(n + bfmg::kTpbThreads - 1) / bfmg::kTpbThreads, bfmg::kTpbThreads,
                                                bfmg::kTpbSmem, static_cast<cudaStream_t>(stream)>>>(
         boards, control, nullptr, nullptr, nullptr, n, nullptr, nullptr, nullptr,
@@ -2175,7 +2196,7 @@ int bf_hash(int device, const uint16_t* boards, const int16_t* control, int n, u
     if (n == 0) return BF_OK;
     if (boards == nullptr || control == nullptr || hash == nullptr)
         return fail(BF_EINVAL, "boards, control and hash must be non-null");
-    BF_CUDA(cudaSetDevice(device));
+    BF_ON_DEVICE(device);
     bfmg::engine_board_kernel<false, false><<<(n + bfmg::kTpbThreads - 1) / bfmg::kTpbThreads, bfmg::kTpbThreads,
                                                bfmg::kTpbSmem, static_cast<cudaStream_t>(stream)>>>(
         boards, control, nullptr, nullptr, nullptr, n, nullptr, nullptr, nullptr, nullptr, nullptr, nullptr,
@@ -2190,7 +2211,7 @@ int bf_history_push(int device, uint64_t* ring, long long* length, const uint64_
     if (n == 0) return BF_OK;
     if (ring == nullptr || length == nullptr || hash == nullptr || irreversible == nullptr)
         return fail(BF_EINVAL, "ring, length, hash and irreversible must be non-null");
-    BF_CUDA(cudaSetDevice(device));
+    BF_ON_DEVICE(device);
     bfmg::history_push_kernel<<<(n + 127) / 128, 128, 0, static_cast<cudaStream_t>(stream)>>>(
         reinterpret_cast<unsigned long long*>(ring), length, reinterpret_cast<const unsigned long long*>(hash),
         irreversible, n);
@@ -2204,7 +2225,7 @@ int bf_repetition_count(int device, const uint64_t* hash, const uint64_t* ring, 
     if (n == 0) return BF_OK;
     if (ring == nullptr || length == nullptr || hash == nullptr || count == nullptr)
         return fail(BF_EINVAL, "hash, ring, length and count must be non-null");
-    BF_CUDA(cudaSetDevice(device));
+    BF_ON_DEVICE(device);
     bfmg::repetition_kernel<<<(n + 127) / 128, 128, 0, static_cast<cudaStream_t>(stream)>>>(
         reinterpret_cast<const unsigned long long*>(hash), reinterpret_cast<const unsigned long long*>(ring), length,
         n, count);
@@ -2219,7 +2240,7 @@ int bf_step(int device, const uint16_t* boards, const int16_t* control, const in
     if (n == 0) return BF_OK;
     if (boards == nullptr || control == nullptr || move == nullptr || boards_out == nullptr || control_out == nullptr)
         return fail(BF_EINVAL, "boards, control, move, boards_out and control_out must be non-null");
-    BF_CUDA(cudaSetDevice(device));
+    BF_ON_DEVICE(device);
     bfmg::engine_board_kernel<true, false><<<(n + bfmg::kTpbThreads - 1) / bfmg::kTpbThreads, bfmg::kTpbThreads,
                                               bfmg::kTpbSmem, static_cast<cudaStream_t>(stream)>>>(
         boards, control, move, promo, nullptr, n, boards_out, control_out, irreversible,
@@ -2235,7 +2256,7 @@ int bf_terminal(int device, const uint64_t* mask, const unsigned char* in_check,
     if (n == 0) return BF_OK;
     if (mask == nullptr || in_check == nullptr || control == nullptr || boards == nullptr || code == nullptr)
         return fail(BF_EINVAL, "mask, in_check, control, boards and code must be non-null");
-    BF_CUDA(cudaSetDevice(device));
+    BF_ON_DEVICE(device);
     bfmg::terminal_kernel<<<(n + 127) / 128, 128, 0, static_cast<cudaStream_t>(stream)>>>(
         reinterpret_cast<const unsigned long long*>(mask), in_check, control, boards, rep_count, n, code, result);
     BF_CUDA(cudaGetLastError());
@@ -2248,7 +2269,7 @@ int bf_random_ply(int device, uint16_t* boards, int16_t* control, uint64_t* mask
     if (n == 0) return BF_OK;
     if (boards == nullptr || control == nullptr || mask == nullptr || r == nullptr)
         return fail(BF_EINVAL, "boards, control, mask and r must be non-null");
-    BF_CUDA(cudaSetDevice(device));
+    BF_ON_DEVICE(device);
     bfmg::engine_board_kernel<true, true><<<(n + bfmg::kTpbThreads - 1) / bfmg::kTpbThreads, bfmg::kTpbThreads,
                                              bfmg::kTpbSmem, static_cast<cudaStream_t>(stream)>>>(
         boards, control, nullptr, promo, r, n, boards, control, nullptr,
@@ -2309,7 +2330,7 @@ int bf_forward_host(bf_handle* h, const uint16_t* boards, const int16_t* control
     if (n == 0) return BF_OK;
     if (boards == nullptr || control == nullptr || rep == nullptr)
         return fail(BF_EINVAL, "boards, control and rep must be non-null");
-    BF_CUDA(cudaSetDevice(h->device));
+    BF_ON_DEVICE(h->device);
     { const int rc = ensure_staging(h, n); if (rc != BF_OK) return rc; }
     const size_t N = static_cast<size_t>(h->cap_n);
     uint8_t* d_legal = h->d_in;                         // 8-byte aligned first
@@ -2377,7 +2398,7 @@ int bf_forward_priors_host(bf_handle* h, const uint16_t* boards, const int16_t* 
         return fail(BF_EINVAL, "boards, control, rep and legal must be non-null");
     if (prior == nullptr || move == nullptr || nedges == nullptr) return fail(BF_EINVAL, "prior, move and nedges must be non-null");
     if (e_cap < 1 || e_cap > 255) return fail(BF_EINVAL, "e_cap must be in 1..255");
-    BF_CUDA(cudaSetDevice(h->device));
+    BF_ON_DEVICE(h->device);
     { const int rc = ensure_staging(h, n); if (rc != BF_OK) return rc; }
     const size_t N = static_cast<size_t>(h->cap_n), E = static_cast<size_t>(e_cap);
     uint8_t* d_legal = h->d_in;
@@ -2441,7 +2462,7 @@ int bf_set_option(bf_handle* h, int option, int value) {
 
 int bf_status(bf_handle* h, int* status) {
     if (h == nullptr || status == nullptr) return fail(BF_EINVAL, "null argument");
-    BF_CUDA(cudaSetDevice(h->device));
+    BF_ON_DEVICE(h->device);
     BF_CUDA(cudaDeviceSynchronize());
     BF_CUDA(cudaMemcpy(status, h->status, sizeof(int), cudaMemcpyDeviceToHost));
     if (*status != 0) {
@@ -2455,7 +2476,7 @@ long long bf_launch_count(const bf_handle* h) { return h ? h->launches : 0; }
 
 int bf_profile(bf_handle* h, int enable) {
     if (h == nullptr) return fail(BF_EINVAL, "null handle");
-    BF_CUDA(cudaSetDevice(h->device));
+    BF_ON_DEVICE(h->device);
     if (enable && h->prof == nullptr) BF_CUDA(cudaMalloc(&h->prof, 16 * sizeof(unsigned long long)));
     if (h->prof != nullptr) BF_CUDA(cudaMemset(h->prof, 0, 16 * sizeof(unsigned long long)));
     h->prof_on = enable != 0;
@@ -2465,7 +2486,7 @@ int bf_profile(bf_handle* h, int enable) {
 int bf_profile_read(bf_handle* h, long long* cycles, int n) {
     if (h == nullptr || cycles == nullptr || n < 0) return fail(BF_EINVAL, "bad argument");
     if (h->prof == nullptr) return fail(BF_EINVAL, "profiling was never enabled on this handle");
-    BF_CUDA(cudaSetDevice(h->device));
+    BF_ON_DEVICE(h->device);
     BF_CUDA(cudaDeviceSynchronize());
     unsigned long long tmp[16];
     BF_CUDA(cudaMemcpy(tmp, h->prof, sizeof(tmp), cudaMemcpyDeviceToHost));
@@ -2482,7 +2503,7 @@ const char* bf_profile_phases(void) {
 
 int bf_measure_i8_peak(int device, int iters, double* tops, double* ms) {
     if (tops == nullptr || iters < 2 || iters > (1 << 22)) return fail(BF_EINVAL, "tops is null or iters out of range");
-    BF_CUDA(cudaSetDevice(device));
+    BF_ON_DEVICE(device);
     cudaDeviceProp prop;
     BF_CUDA(cudaGetDeviceProperties(&prop, device));
     if (prop.major != 10) return fail(BF_ENOTSUP, "this library needs a compute capability 10.x (sm_100a) device");
@@ -2520,7 +2541,7 @@ int bf_measure_i8_peak(int device, int iters, double* tops, double* ms) {
 int bf_measure_elementwise(int device, int block, int iters, double* elements_per_s, double* ms) {
     if (elements_per_s == nullptr || iters < 1 || iters > (1 << 22) || block < 0 || block > 7)
         return fail(BF_EINVAL, "elements_per_s is null, block not in 0..7 or iters out of range");
-    BF_CUDA(cudaSetDevice(device));
+    BF_ON_DEVICE(device);
     cudaDeviceProp prop;
     BF_CUDA(cudaGetDeviceProperties(&prop, device));
     if (prop.major != 10) return fail(BF_ENOTSUP, "this library needs a compute capability 10.x (sm_100a) device");
@@ -2563,7 +2584,7 @@ int bf_measure_elementwise(int device, int block, int iters, double* elements_pe
 
 int bf_selftest_timeout(int device, int code, int* status, long long* waited_cycles) {
     if (status == nullptr || code < 1 || code > 99) return fail(BF_EINVAL, "status is null or code not in 1..99");
-    BF_CUDA(cudaSetDevice(device));
+    BF_ON_DEVICE(device);
     int* d_status = nullptr;
     long long* d_waited = nullptr;
     BF_CUDA(cudaMalloc(&d_status, sizeof(int)));
@@ -2587,7 +2608,7 @@ int bf_selftest_timeout(int device, int code, int* status, long long* waited_cyc
 int bf_selftest_umma(int device, int mode, const void* a, const void* w_image, void* out) {
     if (mode < 0 || mode > 4 || a == nullptr || w_image == nullptr || out == nullptr)
         return fail(BF_EINVAL, "bad self-test argument");
-    BF_CUDA(cudaSetDevice(device));
+    BF_ON_DEVICE(device);
     int* status = nullptr;
     BF_CUDA(cudaMalloc(&status, sizeof(int)));
     BF_CUDA(cudaMemset(status, 0, sizeof(int)));
@@ -2637,14 +2658,17 @@ struct NoAllocDevice {
     BlobHeader hdr{};
 };
 NoAllocDevice g_noalloc[kNoAllocMaxDevices];
+// One lock for the per-device records: set-up, the header cache and its reads.  A call holds it
+// only while it looks the header up (and, for a blob it has not seen, reads it from the device),
+// never across the launch.
+std::mutex g_noalloc_mutex;
 
-// Once per device, with that device current: resolve the scratch array's device address (in
-// host code the array's name is only a handle, never an address a kernel may use), raise the
-// kernel's shared-memory limit, read the SM count, zero the scratch.
+// Once per device, with that device current and the lock held: resolve the scratch array's
+// device address (in host code the array's name is only a handle, never an address a kernel may
+// use), raise the kernel's shared-memory limit, read the SM count, zero the scratch.
 int noalloc_setup(int device, NoAllocDevice** out) {
     if (device < 0 || device >= kNoAllocMaxDevices) return fail(BF_EINVAL, "device index out of range");
     NoAllocDevice& d = g_noalloc[device];
-    BF_CUDA(cudaSetDevice(device));
     if (!d.ready) {
         cudaDeviceProp prop;
         BF_CUDA(cudaGetDeviceProperties(&prop, device));
@@ -2662,6 +2686,38 @@ int noalloc_setup(int device, NoAllocDevice** out) {
     *out = &d;
     return BF_OK;
 }
+
+// The header of `blob_dev`, from the device's cache or read and checked now.  Returns a COPY, so
+// that the launch below never reads a record another thread may be replacing.
+int noalloc_header(NoAllocDevice* d, const void* blob_dev, size_t blob_bytes, BlobHeader* out) {
+    if (d->blob != blob_dev || d->blob_bytes != blob_bytes) {
+        BlobHeader hdr;
+        BF_CUDA(cudaMemcpy(&hdr, blob_dev, sizeof(hdr), cudaMemcpyDeviceToHost));
+        if (hdr.magic != BF_BLOB_MAGIC || hdr.version != BF_BLOB_VERSION || hdr.total != blob_bytes)
+            return fail(BF_EINVAL, "blob header does not match (magic, version or size)");
+        if (hdr.quant != 3)
+            return fail(BF_ENOTSUP, "bf_forward_noalloc runs int8 \"all\" blobs (quant 3) only; this blob carries "
+                                    "arithmetic " + std::to_string(hdr.quant) + ": use a handle (bf_create)");
+        if (hdr.rj_mode != 0)
+            return fail(BF_ENOTSUP, "bf_forward_noalloc does not run re-injecting networks: use a handle (bf_create)");
+        if (hdr.n_layers < 1 || hdr.n_layers > 64 ||
+            hdr.bytes_w != static_cast<uint64_t>(hdr.n_layers) * bf::Cfg<bf::kArInt8>::kLayerStream +
+                               bf::kHeadStages * bf::kHeadStage ||
+            hdr.bytes_lp != static_cast<uint64_t>(hdr.n_layers) * bf::kLparamStride ||
+            hdr.bytes_emb != 184u * 256u * 2u || hdr.bytes_tail != bf::kTailBytes ||
+            ((hdr.off_w | hdr.off_lp | hdr.off_emb | hdr.off_tail) & 255u) ||
+            hdr.off_w + hdr.bytes_w > blob_bytes || hdr.off_lp + hdr.bytes_lp > blob_bytes ||
+            hdr.off_emb + hdr.bytes_emb > blob_bytes || hdr.off_tail + hdr.bytes_tail > blob_bytes)
+            return fail(BF_EINVAL, "blob sections do not match this build");
+        if ((hdr.n_value != 1 && hdr.n_value != 3) || hdr.vmode > 2)
+            return fail(BF_EINVAL, "n_value must be 1 or 3 and the value mode 0, 1 or 2");
+        if (reinterpret_cast<uintptr_t>(blob_dev) & 255u)
+            return fail(BF_EINVAL, "the device blob must be 256-byte aligned");
+        d->hdr = hdr; d->blob = blob_dev; d->blob_bytes = blob_bytes;
+    }
+    *out = d->hdr;
+    return BF_OK;
+}
 }  // namespace
 
 extern "C" {
@@ -2676,67 +2732,70 @@ int bf_forward_noalloc(int device, const void* blob_dev, size_t blob_bytes, cons
     if (blob_dev == nullptr || blob_bytes < 256) return fail(BF_EINVAL, "blob is null or too small");
     if (n > 0 && (boards == nullptr || control == nullptr || rep == nullptr))
         return fail(BF_EINVAL, "boards, control and rep must be non-null");
-    NoAllocDevice* d = nullptr;
-    int rc = noalloc_setup(device, &d);
-    if (rc != BF_OK) return rc;
-    if (d->blob != blob_dev || d->blob_bytes != blob_bytes) {
-        // a blob this device has not seen: read and check its header once
-        BlobHeader hdr;
-        BF_CUDA(cudaMemcpy(&hdr, blob_dev, sizeof(hdr), cudaMemcpyDeviceToHost));
-        if (hdr.magic != BF_BLOB_MAGIC || hdr.version != BF_BLOB_VERSION || hdr.total != blob_bytes)
-            return fail(BF_EINVAL, "blob header does not match (magic, version or size)");
-        if (hdr.n_layers < 1 || hdr.n_layers > 64 ||
-            hdr.quant != 3 ||
-            hdr.bytes_w != static_cast<uint64_t>(hdr.n_layers) * bf::Cfg<bf::kArInt8>::kLayerStream +
-                               bf::kHeadStages * bf::kHeadStage ||
-            hdr.bytes_lp != static_cast<uint64_t>(hdr.n_layers) * bf::kLparamStride ||
-            hdr.bytes_emb != 184u * 256u * 2u || hdr.bytes_tail != bf::kTailBytes || hdr.rj_mode != 0 ||
-            ((hdr.off_w | hdr.off_lp | hdr.off_emb | hdr.off_tail) & 255u) ||
-            hdr.off_w + hdr.bytes_w > blob_bytes || hdr.off_lp + hdr.bytes_lp > blob_bytes ||
-            hdr.off_emb + hdr.bytes_emb > blob_bytes || hdr.off_tail + hdr.bytes_tail > blob_bytes)
-            return fail(BF_EINVAL, "blob sections do not match this build");
-        if ((hdr.n_value != 1 && hdr.n_value != 3) || hdr.vmode > 1)
-            return fail(BF_ENOTSUP, "value head variant not built");
-        if (hdr.rj_mode != 0) return fail(BF_ENOTSUP, "re-injecting networks need a handle (bf_create)");
-        if (reinterpret_cast<uintptr_t>(blob_dev) & 255u)
-            return fail(BF_EINVAL, "the device blob must be 256-byte aligned");
-        d->hdr = hdr; d->blob = blob_dev; d->blob_bytes = blob_bytes;
+    if (device < 0 || device >= kNoAllocMaxDevices) return fail(BF_EINVAL, "device index out of range");
+    BF_ON_DEVICE(device);
+    BlobHeader hdr;
+    void* scratch = nullptr;
+    int sm_count = 0;
+    {
+        std::lock_guard<std::mutex> lock(g_noalloc_mutex);
+        NoAllocDevice* d = nullptr;
+        int rc = noalloc_setup(device, &d);
+        if (rc == BF_OK) rc = noalloc_header(d, blob_dev, blob_bytes, &hdr);
+        if (rc != BF_OK) return rc;
+        scratch = d->scratch;
+        sm_count = d->sm_count;
     }
     if (n == 0) return BF_OK;
     const uint8_t* base = static_cast<const uint8_t*>(blob_dev);
     bf::Params p{};
     p.boards = boards; p.control = control; p.rep = rep; p.legal = legal;
-    p.n = n; p.n_layers = static_cast<int>(d->hdr.n_layers);
-    p.n_value = static_cast<int>(d->hdr.n_value); p.vmode = static_cast<int>(d->hdr.vmode);
+    p.n = n; p.n_layers = static_cast<int>(hdr.n_layers);
+    p.n_value = static_cast<int>(hdr.n_value); p.vmode = static_cast<int>(hdr.vmode);
     p.quant = 3;
-    p.eps = d->hdr.eps;
+    p.eps = hdr.eps;
     p.one = 1.0f;
-    p.wstream = base + d->hdr.off_w;
-    p.lparams = base + d->hdr.off_lp;
-    p.emb = reinterpret_cast<const __half*>(base + d->hdr.off_emb);
-    p.tail = reinterpret_cast<const __half*>(base + d->hdr.off_tail);
+    p.wstream = base + hdr.off_w;
+    p.lparams = base + hdr.off_lp;
+    p.emb = reinterpret_cast<const __half*>(base + hdr.off_emb);
+    p.tail = reinterpret_cast<const __half*>(base + hdr.off_tail);
     p.rj = nullptr; p.rj_mode = 0;
     p.policy = static_cast<__half*>(policy); p.promo = static_cast<__half*>(promo); p.value = value;
     p.y = nullptr; p.debug_stage = 0; p.debug_layer = 0;
     p.cap_layer = -1; p.cap_op = -1; p.cap_a = nullptr; p.cap_acc = nullptr;
-    p.status = static_cast<int*>(d->scratch);      // the device address, not the symbol
+    p.status = static_cast<int*>(scratch);         // the device address, not the symbol
     p.prof = nullptr;
     const int n_tiles = (n + 3) / 4;
-    const int grid = n_tiles < d->sm_count ? n_tiles : d->sm_count;
+    const int grid = n_tiles < sm_count ? n_tiles : sm_count;
     bf::encoder_kernel<false, false, bf::kArInt8><<<grid, bf::kThreads, bf::kSmemRequest, static_cast<cudaStream_t>(stream)>>>(p);
     BF_CUDA(cudaGetLastError());
     return BF_OK;
 }
 
+int bf_noalloc_forget(int device) {
+    if (device < 0 || device >= kNoAllocMaxDevices) return fail(BF_EINVAL, "device index out of range");
+    std::lock_guard<std::mutex> lock(g_noalloc_mutex);
+    g_noalloc[device].blob = nullptr;
+    g_noalloc[device].blob_bytes = 0;
+    return BF_OK;
+}
+
 int bf_noalloc_status(int device, int* status) {
     if (status == nullptr) return fail(BF_EINVAL, "status is null");
-    NoAllocDevice* d = nullptr;
-    int rc = noalloc_setup(device, &d);
-    if (rc != BF_OK) return rc;
+    if (device < 0 || device >= kNoAllocMaxDevices) return fail(BF_EINVAL, "device index out of range");
+    BF_ON_DEVICE(device);
+    void* scratch = nullptr;
+    {
+        std::lock_guard<std::mutex> lock(g_noalloc_mutex);
+        NoAllocDevice* d = nullptr;
+        const int rc = noalloc_setup(device, &d);
+        if (rc != BF_OK) return rc;
+        scratch = d->scratch;
+    }
     BF_CUDA(cudaDeviceSynchronize());
-    BF_CUDA(cudaMemcpy(status, d->scratch, sizeof(int), cudaMemcpyDeviceToHost));
+    BF_CUDA(cudaMemcpy(status, scratch, sizeof(int), cudaMemcpyDeviceToHost));
     if (*status != 0) {
-        BF_CUDA(cudaMemset(d->scratch, 0, sizeof(int)));
+        BF_CUDA(cudaMemset(scratch, 0, sizeof(int)));
         return fail(BF_EDEVICE, "a device-side bounded wait ran out (code " + std::to_string(*status) + ")");
     }
     return BF_OK;

@@ -17,8 +17,9 @@ import torch
 def make_evaluator(net, impl: Optional[str] = None, **kw) -> Callable:
     """``(boards, control, rep) -> (policy_logits, promo, value)``.
 
-    ``impl=None`` is the plain PyTorch network (the fp32 oracle, CPU or GPU as the
-    module lives); ``"cuda"`` is the fused sm_100a evaluator.
+    ``impl=None`` calls ``net`` itself, which must then be a network with a forward path (the
+    reference's own module; this package's weight container has none); ``"cuda"`` is the fused
+    sm_100a evaluator.
     """
     if impl is None:
         return lambda b, c, r: net(b, c, r)
@@ -77,7 +78,7 @@ class ShardedEvaluator:
             torch.cuda.synchronize(dev)
             self.encoder = FusedEncoder.from_blob(blob_dev, device=device_index)
         else:
-            self.encoder = FusedEncoder(net, device=device_index, fp8=fp8, int8=None if fp8 else int8,
+            self.encoder = FusedEncoder(net, device=device_index, fp8=fp8, int8=bool(int8) and not fp8,
                                         int8_scheme=int8_scheme)
 
     def shard(self, n: int) -> Tuple[int, int]:

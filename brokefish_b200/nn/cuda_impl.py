@@ -6,12 +6,12 @@ Same constructor, attributes, methods and errors as the reference's CUDA impleme
 only.
 
 All five arithmetics of the reference are built: its ``int8=True`` path (scheme ``"all"``:
-QKV, out-projection and both FFN matmuls in int8, heads and attention in fp16), which is the
-default here and whose outputs equal the reference kernel's bit for bit; the partial schemes
+QKV, out-projection and both FFN matmuls in int8, heads and attention in fp16), whose
+outputs equal the reference kernel's bit for bit; the partial schemes
 ``int8_scheme="ffn"`` and ``"ffn+qkv"`` (the other GEMMs in fp16), bit for bit as well; its
 ``fp8=True`` path (the two FFN matmuls in e4m3 with ``amax/8`` scales, QKV and out-projection
-in fp16), a tolerance; and the plain fp16 arithmetic (``int8=False``: the reference's own
-default; every weight GEMM fp16 with fp16 accumulators on tcgen05, which carry the bits of
+in fp16), a tolerance; and the plain fp16 arithmetic (the default, as in the
+reference; every weight GEMM fp16 with fp16 accumulators on tcgen05, which carry the bits of
 the reference's fp16-accumulate ``mma.sync``), bit for bit.
 
 The weights are a *snapshot*: folded, quantised and uploaded once in the constructor.
@@ -38,6 +38,17 @@ OP_QKV, OP_OUT, OP_FF1, OP_FF2 = 0, 1, 2, 3
 _OP_WIDTH = {OP_QKV: 768, OP_OUT: 256, OP_FF1: 1024}
 
 
+#: What makes a module "the whole network" for the constructor: the parts the blob is packed from.
+_NETWORK_PARTS = ("encoder", "norm_f", "policy", "promo", "value", "emb_square", "emb_type_special",
+                  "emb_color_turn", "emb_clock", "emb_rep")
+
+
+def is_whole_network(source) -> bool:
+    """True for anything shaped like the reference's ``BrokefishNet`` (whichever class it is an
+    instance of), False for a bare encoder stack."""
+    return all(hasattr(source, part) for part in _NETWORK_PARTS)
+
+
 def _ptr(t: Optional[torch.Tensor]):
     return ctypes.c_void_p(t.data_ptr()) if t is not None and t.numel() else ctypes.c_void_p(0)
 
@@ -55,13 +66,16 @@ class FusedEncoder:
     vmode = 0
     rj_mode = 0
 
-    def __init__(self, source, acc_dtype: str = "fp16", fp8: bool = False,
-                 int8: Optional[bool] = None, two_boards: Optional[bool] = None,
-                 int8_scheme: str = SCHEME, device: Optional[int] = None):
-        net = source if isinstance(source, BrokefishNet) else None
-        encoder = net.encoder if net is not None else source
-        layers = encoder.layers
-        first = layers[0]
+    def __init__(self, source, acc_dtype: str = "fp16", fp8: bool = False, int8: bool = False,
+                 two_boards: Optional[bool] = None, int8_scheme: str = SCHEME,
+                 device: Optional[int] = None):
+        """``source``: a whole network -- any module with the reference network's parts
+        (``encoder.layers``, ``norm_f``, the ``policy`` / ``promo`` / ``value`` heads and the five
+        embedding tables; the reference's own ``BrokefishNet`` in fp32 or ``.half()``, or this
+        package's weight container) -- or a bare ``nn.TransformerEncoder`` for the backbone
+        entry alone.  Keywords and their defaults are the reference's
+        (brokefish/nn/cuda_impl.py:160-162): plain fp16 arithmetic unless ``int8`` or ``fp8``
+        is asked for."""
         if acc_dtype not in self.ACC_DTYPES:
             raise ValueError(f"acc_dtype must be one of {self.ACC_DTYPES}, got {acc_dtype!r}")
         if acc_dtype == "fp32":
@@ -69,25 +83,27 @@ class FusedEncoder:
                 "acc_dtype='fp32' is not built: the weight GEMMs accumulate exactly in s32, and "
                 "the attention and head products keep the fp16 accumulators of the reference's "
                 "shipped kernel so that outputs equal that kernel's bit for bit")
+        if fp8 and int8:
+            raise ValueError("fp8 and int8 quantise the same two matmuls; pick one")
+        if int8_scheme not in SCHEMES:
+            raise ValueError(f"int8_scheme must be one of {sorted(SCHEMES)}, got {int8_scheme!r}")
+        net = source if is_whole_network(source) else None
+        encoder = source.encoder if net is not None else source
+        if not hasattr(encoder, "layers") or len(encoder.layers) == 0:
+            raise ValueError("source must be a network with an `encoder`, or an nn.TransformerEncoder")
+        block = encoder.layers[0]
         self.acc_dtype = acc_dtype
-        self.n_layers = len(layers)
-        self.d_model = first.self_attn.embed_dim
-        self.n_heads = first.self_attn.num_heads
-        self.d_ff = first.linear1.out_features
+        self.n_layers = len(encoder.layers)
+        self.d_model = int(block.self_attn.embed_dim)
+        self.n_heads = int(block.self_attn.num_heads)
+        self.d_ff = int(block.linear1.out_features)
         self.d_head = self.d_model // self.n_heads
-        self.eps = first.norm1.eps
+        self.eps = float(block.norm1.eps)
         if (self.d_model, self.d_ff, self.n_heads) != (self.D, self.DFF, self.H):
             raise ValueError(
                 f"kernel is compiled for d_model={self.D}, d_ff={self.DFF}, heads={self.H}; "
                 f"got {self.d_model}, {self.d_ff}, {self.n_heads}")
-        self.fp8 = bool(fp8)
-        self.int8 = (not self.fp8) if int8 is None else bool(int8)
-        if self.fp8 and self.int8:
-            raise ValueError("fp8 and int8 quantise the same two matmuls; pick one")
-        if int8_scheme not in SCHEMES:
-            raise ValueError(f"int8_scheme must be one of {sorted(SCHEMES)}, got {int8_scheme!r}")
-        if self.fp8:
-            self.int8 = False
+        self.fp8, self.int8 = bool(fp8), bool(int8)
         self.int8_scheme = int8_scheme
         # the reference's kernel mode numbers: 3 = int8 on all four matmuls, 1 = e4m3 FFN,
         # 0 = the plain fp16 arithmetic (the reference's default; here `int8=False`)

@@ -1,10 +1,14 @@
-"""Host-side mirror of the Brokefish network definition (fp32 master weights).
+"""The network's weights on the host: a container with the reference's parameter tree.
 
-This is the object a caller hands to :class:`brokefish_b200.nn.cuda_impl.FusedEncoder`,
-with the same constructor arguments, attribute names and ``state_dict`` keys as the
-reference's ``BrokefishNet`` (brokefish/nn/model.py:268-361), so a checkpoint written by
-the reference loads here unchanged and a network built here loads there.  It is plain
-PyTorch and it is never on the evaluation hot path: the hot path is the sm_100a kernel.
+``BrokefishNet`` here holds the fp32 master weights under the constructor arguments,
+attribute names and ``state_dict`` keys of the reference's ``BrokefishNet``
+(brokefish/nn/model.py:268-361), so a checkpoint written by the reference loads here
+unchanged and one written here loads there.  It is what
+:class:`brokefish_b200.nn.cuda_impl.FusedEncoder` packs its blob from when no reference
+checkout is at hand (the reference's own module is accepted just the same).  It has no
+``forward``: evaluating positions is the sm_100a kernel's job, and the plain PyTorch
+evaluation of these weights, which only the tests and the CPU baseline need, lives with the
+test oracles.
 
 Architecture (brokefish/nn/model.py:38-47): 32 piece tokens, width 256, 8 pre-norm
 encoder layers with 8 heads of 32 and a 1024-wide ReLU FFN, a final LayerNorm, and
@@ -31,22 +35,6 @@ REINJECT_MODE_ID = {"ln1": 1, "both": 2}
 N_SOURCES = 5
 
 EMB_TABLES = ("emb_square", "emb_type_special", "emb_color_turn", "emb_clock", "emb_rep")
-
-
-def decode_boards(boards: torch.Tensor):
-    """Fields of the 12-bit piece word: (captured, color, special, type, square).
-
-    Bit 11 captured, bit 10 colour, bit 9 special, bits 6-8 type, bits 0-5 square
-    (brokefish/nn/model.py:251-265).  A captured slot is exactly ``1 << 11``.
-    """
-    w = boards.long()
-    return (w >> 11) & 1, (w >> 10) & 1, (w >> 9) & 1, (w >> 6) & 7, w & 63
-
-
-def wdl_to_scalar(logits: torch.Tensor) -> torch.Tensor:
-    """``[N, 3]`` (loss, draw, win) logits to ``p(win) - p(loss)``."""
-    p = torch.softmax(logits, dim=-1)
-    return p[..., 2] - p[..., 0]
 
 
 def n_value_of(state: dict) -> int:
@@ -84,7 +72,8 @@ def net_for_state(state: dict, **kw) -> "BrokefishNet":
 
 
 class BrokefishNet(nn.Module):
-    """Piece-token transformer; same parameters and key names as the reference."""
+    """Weight container of the piece-token transformer; same parameters and key names as the
+    reference's module, no forward path."""
 
     def __init__(self, d_model: int = D_MODEL, n_layers: int = N_LAYERS,
                  n_heads: int = N_HEADS, d_ff: int = D_FF, eps: float = 1e-5,
@@ -131,90 +120,10 @@ class BrokefishNet(nn.Module):
                     self.emb_clock, self.emb_rep, self.policy, self.promo, self.value):
             nn.init.normal_(mod.weight, mean=0.0, std=std)
 
-    # -- embedding ---------------------------------------------------------
-    def embed_indices(self, boards, control, rep):
-        captured, color, special, ptype, square = decode_boards(boards)
-        stm = (control < 0).long()
-        slot_color = (torch.arange(T, device=boards.device) >= T // 2).long()
-        idx = (square, ptype * 2 + special, color * 2 + stm[:, None],
-               (control.abs().long() - 1).clamp_(0, N_CLOCK - 1),
-               rep.long().clamp_(0, N_REP - 1),
-               slot_color[None, :] * 2 + stm[:, None])     # re-injection's colour row: by slot
-        return idx, captured == 0
-
-    def embed(self, boards, control, rep):
-        """Token embeddings with the normative grouping
-        ``((square + type_special) + color_turn) + (clock + rep)``
-        (brokefish/nn/model.py:383-397)."""
-        idx, alive = self.embed_indices(boards, control, rep)
-        per_board = self.emb_clock(idx[3]) + self.emb_rep(idx[4])
-        x = self.emb_square(idx[0])
-        x = x + self.emb_type_special(idx[1])
-        x = x + self.emb_color_turn(idx[2])
-        x = x + per_board[:, None, :]
-        return x, alive
-
-    def mix(self, idx, c: torch.Tensor) -> torch.Tensor:
-        """``sum_k c[k] * E_k`` for one re-injection site, ``[N, 32, d]``; the colour row is
-        chosen by the *slot* (0-15 white, 16-31 black), not by the decoded word
-        (brokefish/nn/model.py:481-509)."""
-        F = nn.functional
-        m = F.embedding(idx[0], c[0] * self.emb_square.weight)
-        m = m + F.embedding(idx[1], c[1] * self.emb_type_special.weight)
-        m = m + F.embedding(idx[5], c[2] * self.emb_color_turn.weight)
-        per_board = (F.embedding(idx[3], c[3] * self.emb_clock.weight)
-                     + F.embedding(idx[4], c[4] * self.emb_rep.weight))
-        return m + per_board[:, None, :]
-
-    def encode(self, x, alive, idx=None):
-        """The encoder stack; with re-injection every block's LayerNorm sees
-        ``h + mix`` while the residual stream itself is untouched
-        (brokefish/nn/model.py:511-538)."""
-        if self.reinject == "none":
-            return self.encoder(x, src_key_padding_mask=~alive)
-        if idx is None:
-            raise ValueError("reinject needs the embedding indices")
-        pad = ~alive
-        both = self.reinject == "both"
-        for i, lay in enumerate(self.encoder.layers):
-            site = i * 2 if both else i
-            x = x + lay._sa_block(lay.norm1(x + self.mix(idx, self.reinject_c[site])), None, pad,
-                                  is_causal=False)
-            n2 = lay.norm2(x + self.mix(idx, self.reinject_c[site + 1])) if both else lay.norm2(x)
-            x = x + lay._ff_block(n2)
-        return x
-
     @property
     def value_absolute(self) -> bool:
+        """Pooled and prenorm value heads score the position in White's frame."""
         return self.value_head in ("pooled", "prenorm")
-
-    def heads(self, h, control, alive: Optional[torch.Tensor] = None,
-              with_logits: bool = False, h_raw: Optional[torch.Tensor] = None):
-        """Normed tokens to ``(policy_logits, promo, value)``; logits are raw
-        (brokefish/nn/model.py:551-617)."""
-        if self.value_head == "prenorm":
-            m = alive.unsqueeze(-1).to(h_raw.dtype)
-            hv = self.norm_f((h_raw * m).sum(1) / m.sum(1).clamp(min=1))
-        elif self.value_head == "pooled":
-            m = alive.unsqueeze(-1).to(h.dtype)
-            hv = (h * m).sum(1) / m.sum(1).clamp(min=1)
-        else:
-            king = torch.where(control < 0, KING_SLOT_BLACK, KING_SLOT_WHITE).long()
-            hv = h[torch.arange(h.shape[0], device=h.device), king]
-        raw = self.value(hv).float()
-        value = torch.tanh(raw).squeeze(-1) if self.n_value == 1 else wdl_to_scalar(raw)
-        if self.value_absolute:
-            value = torch.where(control > 0, value, -value)
-        if with_logits:
-            return self.policy(h), self.promo(h), value, raw
-        return self.policy(h), self.promo(h), value
-
-    def forward(self, boards, control, rep, with_logits: bool = False, mask=None):
-        x, alive = self.embed(boards, control, rep)
-        idx, _ = self.embed_indices(boards, control, rep)
-        h = self.encode(x, alive, idx)
-        return self.heads(self.norm_f(h), control, alive=alive,
-                          with_logits=with_logits, h_raw=h)
 
 
 def seeded_state(seed: int = 0, std: Optional[float] = 0.02, perturb_norms: bool = False,

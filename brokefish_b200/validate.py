@@ -26,6 +26,8 @@ from __future__ import annotations
 
 import argparse
 import copy
+import os
+import sys
 from dataclasses import dataclass
 from typing import Callable, Dict, Optional, Sequence
 
@@ -246,9 +248,19 @@ def main(argv: Optional[Sequence[str]] = None) -> int:
     ap.add_argument("--limit", type=int, default=0)
     ap.add_argument("--e-cap", type=int, default=96)
     ap.add_argument("--std", type=float, default=0.02, help="N(0, std) seed-0 weights; 0 = default init scale")
+    ap.add_argument("--reference", default=os.environ.get("BROKEFISH_REFERENCE", ""),
+                    help="checkout of the reference: its BrokefishNet is the fp32 yardstick "
+                         "(default: $BROKEFISH_REFERENCE)")
     args = ap.parse_args(argv)
     from brokefish_b200.nn import encoder_impl
-    from brokefish_b200.nn.model import BrokefishNet, seeded_state
+    from brokefish_b200.nn.model import seeded_state
+    # the fp32 yardstick is the reference's own network, called as the reference's validator
+    # calls it; this package holds weights and the kernel, not a second torch forward path
+    if not args.reference or not os.path.isdir(os.path.join(args.reference, "brokefish")):
+        raise SystemExit("validate needs the reference's network as its yardstick: pass --reference "
+                         "<checkout> or set BROKEFISH_REFERENCE")
+    sys.path.insert(0, args.reference)
+    from brokefish.nn.model import BrokefishNet
     z = np.load(args.positions)
     n = args.limit or z["boards"].shape[0]
     dev = torch.device("cuda")
@@ -257,7 +269,7 @@ def main(argv: Optional[Sequence[str]] = None) -> int:
     net = BrokefishNet().eval()
     net.load_state_dict(seeded_state(seed=0, std=args.std or None, perturb_norms=not args.std))
     net = net.half().float()
-    forwards = {"b200-int8": encoder_impl("cuda")(net).forward_full,
+    forwards = {"b200-int8": encoder_impl("cuda")(net, int8=True).forward_full,
                 "b200-e4m3": encoder_impl("cuda")(net, fp8=True).forward_full}
     validate(net, boards, control, rep, legal, forwards, e_cap=args.e_cap)
     return 0

@@ -13,6 +13,9 @@
  *     not synchronise and allocate nothing.
  *   - `bf_forward_host` takes HOST pointers, copies in, runs, copies out and
  *     synchronises; it is the end-to-end call.
+ *   - Every entry point that names a device (through a handle or a `device` argument) makes
+ *     it current for the duration of the call and restores the caller's current device
+ *     before it returns.
  *   - Every device-side wait in the kernel is bounded.  If one runs out, the kernel
  *     finishes with garbage outputs and a non-zero status word that `bf_status()`
  *     reads back after the caller's stream synchronisation.
@@ -260,26 +263,42 @@ const char* bf_profile_phases(void);
  * host that forbids allocation after start-up -- and therefore cannot hold a `bf_handle`.
  *
  * The caller owns everything it passes: `blob_dev` is the packed weight blob already in
- * DEVICE memory (256-byte aligned, `blob_bytes` long), the rest is as for `bf_forward`.  The
- * kernel's only other memory, its status word, is a 256-byte `static __device__` array
+ * DEVICE memory (256-byte aligned, `blob_bytes` long), the other arguments are `bf_forward`'s.
+ * The kernel's only other memory, its status word, is a 256-byte `static __device__` array
  * inside the library: every GPU that loads the library holds those 256 bytes until the
  * process exits, and nothing is ever cudaMalloc'ed or freed here.
+ *
+ * What it runs: int8 "all" blobs (arithmetic 3) without re-injection, any of the three value
+ * heads.  A blob with another arithmetic or with re-injection is refused with BF_ENOTSUP and a
+ * text that says which; such networks need a handle.
  *
  * Limits and rules
  *   - `n` above BF_NOALLOC_MAX_POSITIONS is refused (BF_EINVAL, text says so): split it.
  *   - The first call on a device resolves the array's device address, sets the kernel's
- *     shared-memory attribute and zeroes the status word; a call with a blob pointer the
- *     device has not seen reads and checks its 256-byte header (a synchronous copy).  Make
- *     that first call before any stream capture.
+ *     shared-memory attribute and zeroes the status word; a call with a blob (pointer, size)
+ *     the device has not seen reads and checks its 256-byte header (a synchronous copy) and
+ *     remembers it.  Make such a call before any stream capture.
+ *   - The remembered header is keyed on the blob's ADDRESS and SIZE only.  After writing new
+ *     weights into the same device buffer (the rebuild-after-every-update pattern) call
+ *     `bf_noalloc_forget(device)` first: without it the next call runs the new weights with the
+ *     old header's value head, class count and epsilon.
  *   - All calls on a device share the one status word and it keeps what the last failing
  *     launch wrote until `bf_noalloc_status` reads it (which clears it).  Two launches that
  *     overlap on the GPU race on it: a time-out is still reported, but not whose it was.
- *   - Not thread-safe per device for the first call; afterwards concurrent callers only
- *     share the status word as described. */
+ *   - Host threads may call concurrently, with the same or different blobs: the per-device
+ *     record is read and replaced under a lock and each call launches from its own copy of the
+ *     header.  Threads that alternate between two blobs on one device re-read a header on
+ *     every switch.
+ *   - The caller's current device is restored before the call returns. */
 #define BF_NOALLOC_MAX_POSITIONS 1048576
 int bf_forward_noalloc(int device, const void* blob_dev, size_t blob_bytes, const uint16_t* boards,
                        const int16_t* control, const uint8_t* rep, const uint64_t* legal, int n,
                        void* policy, void* promo, float* value, void* stream);
+
+/* Drop what `bf_forward_noalloc` remembers about the blob last used on `device`, so that the
+ * next call reads the header again.  Mandatory after re-packing into the same device buffer.
+ * No counterpart in the reference. */
+int bf_noalloc_forget(int device);
 
 /* Synchronise `device` and read (and clear) the status word `bf_forward_noalloc` launches
  * share; 0 = clean.  No counterpart in the reference. */

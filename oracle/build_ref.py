@@ -135,7 +135,8 @@ def make_slabs(reference: str) -> None:
 
 def main() -> int:
     ap = argparse.ArgumentParser()
-    ap.add_argument("--reference", default="/root/reference")
+    ap.add_argument("--reference", default=os.environ.get("BROKEFISH_REFERENCE"), required="BROKEFISH_REFERENCE" not in os.environ,
+                    help="checkout of the reference (default: $BROKEFISH_REFERENCE)")
     ap.add_argument("--no-kernel", action="store_true")
     ap.add_argument("--no-slabs", action="store_true")
     args = ap.parse_args()

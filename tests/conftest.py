@@ -58,10 +58,12 @@ def oracle_weights(states):
 
 @pytest.fixture(scope="session")
 def nets(states):
-    from brokefish_b200.nn.model import BrokefishNet
+    """The two weight sets as callable torch networks (the product's weight container plus the
+    test oracle's forward path)."""
+    from oracle.torch_net import TorchNet
     out = {}
     for k, s in states.items():
-        net = BrokefishNet().eval()
+        net = TorchNet().eval()
         net.load_state_dict(s)
         out[k] = net
     return out

@@ -267,7 +267,8 @@ def history_answers(env) -> None:
 
 def main() -> int:
     ap = argparse.ArgumentParser()
-    ap.add_argument("--reference", default="/root/reference")
+    ap.add_argument("--reference", default=os.environ.get("BROKEFISH_REFERENCE"), required="BROKEFISH_REFERENCE" not in os.environ,
+                    help="checkout of the reference (default: $BROKEFISH_REFERENCE)")
     ap.add_argument("--skip-positions", action="store_true")
     ap.add_argument("--only-step", action="store_true", help="write ref_step.npz and stop")
     ap.add_argument("--only-shuffled", action="store_true", help="write ref_shuffled.npz and stop")

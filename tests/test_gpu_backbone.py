@@ -74,7 +74,7 @@ def test_other_sources_reach_the_same_bits(case):
     and for nothing else."""
     from brokefish_b200.nn import encoder_impl
     x, alive, want, net = case["x"], case["alive"], case["want"], case["net"]
-    e8 = encoder_impl("cuda")(net)
+    e8 = encoder_impl("cuda")(net, int8=True)
     assert e8.quant == 3 and same(e8(x, alive), want)
     pol = e8.forward_full(case["boards"], case["control"], case["rep"])[0]
     assert torch.isfinite(pol.float()).all()                 # its own arithmetic still runs
@@ -126,7 +126,7 @@ def test_refusals(case):
     import ctypes
     from brokefish_b200 import _native
     from brokefish_b200.nn import encoder_impl
-    e8 = encoder_impl("cuda")(case["net"])
+    e8 = encoder_impl("cuda")(case["net"], int8=True)
     rc = _native.lib().bf_forward_backbone(e8._handle, ctypes.c_void_p(x.data_ptr()), None, 4,
                                            ctypes.c_void_p(x.clone().data_ptr()), None)
     assert rc != 0 and b"fp16" in _native.lib().bf_last_error()

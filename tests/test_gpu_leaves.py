@@ -15,7 +15,7 @@ def enc():
     from brokefish_b200.nn.model import BrokefishNet, seeded_state
     net = BrokefishNet().eval()
     net.load_state_dict(seeded_state(seed=0, std=None, perturb_norms=True))
-    e = encoder_impl("cuda")(net)
+    e = encoder_impl("cuda")(net, int8=True)
     yield e
     e.check_status()
     e.close()

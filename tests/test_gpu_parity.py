@@ -50,7 +50,7 @@ def encoders(nets):
     reproduce; the default (the hardware approximation, as the reference kernel) is what
     `encoders_hw` and tests/test_gpu_reference_kernel.py run."""
     from brokefish_b200.nn import encoder_impl
-    out = {k: encoder_impl("cuda")(n) for k, n in nets.items()}
+    out = {k: encoder_impl("cuda")(n, int8=True) for k, n in nets.items()}
     for e in out.values():
         e.exact_rsqrt = True
     yield out
@@ -61,7 +61,7 @@ def encoders(nets):
 @pytest.fixture(scope="module")
 def encoders_hw(nets):
     from brokefish_b200.nn import encoder_impl
-    out = {k: encoder_impl("cuda")(n) for k, n in nets.items()}
+    out = {k: encoder_impl("cuda")(n, int8=True) for k, n in nets.items()}
     yield out
     for e in out.values():
         e.close()
@@ -391,7 +391,7 @@ def test_value_head_variants(pos256):
         st = seeded_state(seed=5, std=None, perturb_norms=True, n_value=nv, value_head=head)
         net = BrokefishNet(n_value=nv, value_head=head).eval()
         net.load_state_dict(st)
-        enc = encoder_impl("cuda")(net)
+        enc = encoder_impl("cuda")(net, int8=True)
         enc.exact_rsqrt = True
         w = O.prepare({k: v.numpy() for k, v in st.items()})
         sl = slice(0, 48)
@@ -441,7 +441,7 @@ def test_reinjection(mode, pos256):
     st = seeded_state(seed=7, std=None, perturb_norms=True, reinject=mode)
     net = net_for_state(st).eval()
     net.load_state_dict(st)
-    enc = encoder_impl("cuda")(net)
+    enc = encoder_impl("cuda")(net, int8=True)
     enc.exact_rsqrt = True
     assert enc.rj_mode == {"ln1": 1, "both": 2}[mode]
     w = aligned_oracle({"X": O.prepare({k: v.numpy() for k, v in st.items()})}, "X", enc)
@@ -463,7 +463,7 @@ def test_reinjection(mode, pos256):
     plain_state = {k: v for k, v in st0.items() if not k.startswith("reinject")}
     plain = net_for_state(plain_state).eval()
     plain.load_state_dict(plain_state)
-    e0, e1 = encoder_impl("cuda")(net0), encoder_impl("cuda")(plain)
+    e0, e1 = encoder_impl("cuda")(net0, int8=True), encoder_impl("cuda")(plain, int8=True)
     odd = slice(3, 3 + 131)
     a = [t.cpu().numpy().copy() for t in e0.forward_full(*inputs(pos256, odd))]
     b = [t.cpu().numpy().copy() for t in e1.forward_full(*inputs(pos256, odd))]

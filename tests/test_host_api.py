@@ -112,3 +112,69 @@ def test_shard_bounds():
             assert max(sizes) - min(sizes) <= 1
     with pytest.raises(ValueError):
         shard_bounds(4, 2, 2)
+
+
+class _Twin(torch.nn.Module):
+    """A module with the reference network's parts that is NOT this package's class: what
+    ``FusedEncoder`` sees when a trainer hands it the reference's own ``BrokefishNet``."""
+
+    def __init__(self, src):
+        super().__init__()
+        import copy
+        for part in ("encoder", "norm_f", "policy", "promo", "value", "emb_square", "emb_type_special",
+                     "emb_color_turn", "emb_clock", "emb_rep"):
+            setattr(self, part, copy.deepcopy(getattr(src, part)))
+        self.d_model, self.n_layers, self.n_value = src.d_model, src.n_layers, src.n_value
+        self.value_head, self.reinject = src.value_head, src.reinject
+
+
+def test_network_is_recognised_by_its_parts_not_its_class(nets):
+    """The constructor takes any module shaped like the reference's network (the class
+    `PackedWeights.pack` passes is the reference's own, brokefish/train/sync.py:60-86), packs
+    the same blob from it as from this package's container, from fp32 master weights and from
+    the `.half()` copy alike (tests/test_b2.py:61-67), and keeps the reference's defaults:
+    plain fp16 arithmetic unless `int8` or `fp8` is asked for."""
+    import inspect
+    from brokefish_b200.nn import pack
+    from brokefish_b200.nn.cuda_impl import is_whole_network
+    net = nets["B"]
+    twin = _Twin(net)
+    assert not isinstance(twin, BrokefishNet)
+    assert is_whole_network(twin) and is_whole_network(net) and not is_whole_network(net.encoder)
+    want = pack.pack_blob(net, "int8")
+    assert np.array_equal(pack.pack_blob(twin, "int8"), want)
+    half = _Twin(net).half()
+    net_h = __import__("copy").deepcopy(net).half()
+    assert np.array_equal(pack.pack_blob(half, "int8"), pack.pack_blob(net_h, "int8"))
+    sig = inspect.signature(FusedEncoder.__init__).parameters
+    assert sig["int8"].default is False and sig["fp8"].default is False and sig["acc_dtype"].default == "fp16"
+    assert list(sig)[1:7] == ["source", "acc_dtype", "fp8", "int8", "two_boards", "int8_scheme"]
+    if not torch.cuda.is_available():
+        # recognised as a whole network: the constructor gets as far as asking for the device
+        with pytest.raises(RuntimeError, match="CUDA device"):
+            FusedEncoder(twin, int8=True)
+
+
+def test_reference_network_packs_to_the_same_blob(states):
+    """Where a checkout of the reference is at hand (``BROKEFISH_REFERENCE``), its own
+    ``BrokefishNet`` -- fp32 and ``.half()`` -- gives the blob bytes this package's container
+    gives for the same state."""
+    import os
+    import sys
+    ref = os.environ.get("BROKEFISH_REFERENCE", "")
+    if not os.path.isdir(os.path.join(ref, "brokefish")):
+        pytest.skip("BROKEFISH_REFERENCE does not point at a checkout of the reference")
+    sys.path.insert(0, ref)
+    try:
+        from brokefish.nn.model import BrokefishNet as RefNet
+    finally:
+        sys.path.remove(ref)
+    from brokefish_b200.nn import pack
+    from brokefish_b200.nn.cuda_impl import is_whole_network
+    for name, fmt in (("A", "int8"), ("B", "int8"), ("B", "f16"), ("B", "e4m3")):
+        theirs, ours = RefNet().eval(), BrokefishNet().eval()
+        theirs.load_state_dict(states[name], strict=True)
+        ours.load_state_dict(states[name], strict=True)
+        assert is_whole_network(theirs)
+        assert np.array_equal(pack.pack_blob(theirs, fmt), pack.pack_blob(ours, fmt))
+        assert np.array_equal(pack.pack_blob(theirs.half(), fmt), pack.pack_blob(ours.half(), fmt))

@@ -79,7 +79,7 @@ def test_fused_expansion_generates_its_own_moves(pos4096):
     t = lambda a: torch.from_numpy(np.ascontiguousarray(a[:n])).cuda()
     boards, control, rep = t(pos4096["boards"]), t(pos4096["control"]), t(pos4096["rep"])
     legal = torch.from_numpy(pos4096["legal"][:n].view(np.int64).copy()).cuda()
-    enc = encoder_impl("cuda")(net)
+    enc = encoder_impl("cuda")(net, int8=True)
     for cap in (96, 12):
         want = [x.clone() for x in enc.forward_priors(boards, control, rep, legal, cap)]
         got = [x.clone() for x in enc.forward_priors(boards, control, rep, None, cap)]
@@ -180,7 +180,7 @@ def test_boards_that_do_not_keep_the_colours_apart_by_slot():
     from brokefish_b200.nn.model import BrokefishNet, seeded_state
     net = BrokefishNet().eval()
     net.load_state_dict(seeded_state(seed=0, std=0.02))
-    enc = encoder_impl("cuda")(net)
+    enc = encoder_impl("cuda")(net, int8=True)
     rep = torch.zeros(b.shape[0], dtype=torch.uint8, device="cuda")
     legal = torch.from_numpy(z["legal"].view(np.int64).copy()).cuda()
     want = [x.clone() for x in enc.forward_priors(b, c, rep, legal, 96)]

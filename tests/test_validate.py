@@ -76,8 +76,9 @@ def test_validate_on_cpu_scores_an_injected_error(pos256):
     """The suite bites: an evaluator whose policy logits are shifted on one slot moves the
     priors, an exact copy of the fp32 network does not (the method of the reference's
     tests/test_validate.py)."""
-    from brokefish_b200.nn.model import BrokefishNet, seeded_state
-    net = BrokefishNet().eval()
+    from brokefish_b200.nn.model import seeded_state
+    from oracle.torch_net import TorchNet
+    net = TorchNet().eval()
     net.load_state_dict(seeded_state(seed=0, std=None, perturb_norms=True))
     net = net.half().float()
     n = 48
@@ -113,8 +114,9 @@ def test_b200_evaluator_in_prior_space(pos4096):
     reference's).  These are properties of the int8 scheme, not of this kernel: its logits equal
     the reference kernel's bit for bit."""
     from brokefish_b200.nn import encoder_impl
-    from brokefish_b200.nn.model import BrokefishNet, seeded_state
-    net = BrokefishNet().eval()
+    from brokefish_b200.nn.model import seeded_state
+    from oracle.torch_net import TorchNet
+    net = TorchNet().eval()
     net.load_state_dict(seeded_state(seed=0, std=None, perturb_norms=True))
     net = net.half().float()
     dev = torch.device("cuda")
@@ -122,7 +124,7 @@ def test_b200_evaluator_in_prior_space(pos4096):
     t = lambda a: torch.from_numpy(np.ascontiguousarray(a[:n])).to(dev)
     boards, control, rep = t(pos4096["boards"]), t(pos4096["control"]), t(pos4096["rep"])
     legal = torch.from_numpy(pos4096["legal"][:n].view(np.int64).copy()).to(dev)
-    enc = encoder_impl("cuda")(net)
+    enc = encoder_impl("cuda")(net, int8=True)
     out = V.validate(net, boards, control, rep, legal, {"b200-int8": enc.forward_full}, verbose=True)
     d = out["b200-int8"]
     assert d.nonfinite == 0 and d.flushed == 0 and d.edge_set_differs == 0
@@ -140,15 +142,16 @@ def test_fused_expansion_equals_the_expansion_of_its_own_logits(cap, pos4096):
     labels equal, priors equal to one fp16 step (the kernel sums at most `cap` exponentials
     where torch sums 8192 masked ones), value identical; terminal positions give no edge."""
     from brokefish_b200.nn import encoder_impl
-    from brokefish_b200.nn.model import BrokefishNet, seeded_state
-    net = BrokefishNet().eval()
+    from brokefish_b200.nn.model import seeded_state
+    from oracle.torch_net import TorchNet
+    net = TorchNet().eval()
     net.load_state_dict(seeded_state(seed=0, std=None, perturb_norms=True))
     dev = torch.device("cuda")
     n = 1537                                                   # odd: the last tile is partial
     t = lambda a: torch.from_numpy(np.ascontiguousarray(a[:n])).to(dev)
     boards, control, rep = t(pos4096["boards"]), t(pos4096["control"]), t(pos4096["rep"])
     legal = torch.from_numpy(pos4096["legal"][:n].view(np.int64).copy()).to(dev)
-    enc = encoder_impl("cuda")(net)
+    enc = encoder_impl("cuda")(net, int8=True)
     pol, pro, val = (x.clone() for x in enc.forward_full(boards, control, rep))
     want_p, want_m, want_n = V.expand_priors(boards, control, legal, pol, pro, cap)
     got_p, got_m, got_n, got_v = (x.clone() for x in enc.forward_priors(boards, control, rep, legal, cap))
@@ -180,10 +183,11 @@ def test_fused_expansion_host_call_matches_the_device_call(pinned, pos256):
     """Pinned outputs are written by the kernel straight into host memory; pageable ones go
     through the staged path (wave-sized launches, copies on a second stream)."""
     from brokefish_b200.nn import encoder_impl
-    from brokefish_b200.nn.model import BrokefishNet, seeded_state
-    net = BrokefishNet().eval()
+    from brokefish_b200.nn.model import seeded_state
+    from oracle.torch_net import TorchNet
+    net = TorchNet().eval()
     net.load_state_dict(seeded_state(seed=0, std=0.02))
-    enc = encoder_impl("cuda")(net)
+    enc = encoder_impl("cuda")(net, int8=True)
     n, cap = 253, 96
     t = lambda a: torch.from_numpy(np.ascontiguousarray(a[:n]))
     boards, control, rep = t(pos256["boards"]), t(pos256["control"]), t(pos256["rep"])

@@ -32,7 +32,7 @@ def test_noalloc_entry_point_matches_the_handle_path_twice(nets, pos256):
     net = nets["B"]
     blob = torch.from_numpy(pack_blob(net)).to(dev)          # caller-owned device copy
     assert blob.data_ptr() % 256 == 0
-    enc = encoder_impl("cuda")(net, device=0)
+    enc = encoder_impl("cuda")(net, int8=True, device=0)
     stream = ctypes.c_void_p(torch.cuda.current_stream(0).cuda_stream)
 
     for lo, n in ((0, 101), (50, 206)):                      # two calls in a row, ragged tiles
@@ -68,3 +68,57 @@ def test_noalloc_rejects_what_it_cannot_serve(nets):
     rc = L.bf_forward_noalloc(0, _ptr(blob), blob.numel() - 256, _ptr(z), _ptr(z), _ptr(z), None, 1,
                               None, None, None, None)
     assert rc == -1 and b"header" in L.bf_last_error()
+    # a blob this entry point cannot run is refused with the reason, not as a malformed blob:
+    # another arithmetic (fp16, e4m3) or a re-injecting network needs a handle
+    from brokefish_b200.nn.model import BrokefishNet, seeded_state
+    for fmt, word in (("f16", b"arithmetic 0"), ("e4m3", b"arithmetic 1")):
+        other = torch.from_numpy(pack_blob(nets["A"], fmt)).to(dev)
+        rc = L.bf_forward_noalloc(0, _ptr(other), other.numel(), _ptr(z), _ptr(z), _ptr(z), None, 1,
+                                  None, None, None, None)
+        assert rc == -3 and word in L.bf_last_error(), L.bf_last_error()
+    rj = BrokefishNet(reinject="ln1")
+    rj.load_state_dict(seeded_state(seed=3, std=None, perturb_norms=True, reinject="ln1"))
+    other = torch.from_numpy(pack_blob(rj, "int8")).to(dev)
+    rc = L.bf_forward_noalloc(0, _ptr(other), other.numel(), _ptr(z), _ptr(z), _ptr(z), None, 1,
+                              None, None, None, None)
+    assert rc == -3 and b"re-injecting" in L.bf_last_error()
+
+
+def test_noalloc_repacked_buffer_needs_forget(pos256):
+    """The weight-refresh pattern of a caller with one fixed weight buffer: a second network of
+    the same blob size (another value head: king scalar, then pooled win/draw/loss) is copied
+    over the first at the same device address.  The entry point remembers a blob's header by
+    address and size, so the caller says `bf_noalloc_forget` after the copy; the values that
+    come back are then the new head's (equal to a handle built from the new network), and the
+    caller's current device is left as it was."""
+    from brokefish_b200 import _native
+    from brokefish_b200.nn import encoder_impl
+    from brokefish_b200.nn.model import BrokefishNet, seeded_state
+    from brokefish_b200.nn.pack import pack_blob
+    L = _native.lib()
+    dev = torch.device("cuda", 0)
+    n = 64
+    b, c, r = (torch.from_numpy(pos256[k][:n].copy()).to(dev) for k in ("boards", "control", "rep"))
+    stream = ctypes.c_void_p(torch.cuda.current_stream(0).cuda_stream)
+    nets_ = []
+    for kw in (dict(n_value=1, value_head="king"), dict(n_value=3, value_head="pooled")):
+        net = BrokefishNet(**kw).eval()
+        net.load_state_dict(seeded_state(seed=5, std=None, perturb_norms=True, **kw))
+        nets_.append(net)
+    blobs = [pack_blob(net, "int8") for net in nets_]
+    assert blobs[0].size == blobs[1].size                      # the tail section has a fixed size
+    buf = torch.empty(blobs[0].size, dtype=torch.uint8, device=dev)
+    val = torch.zeros(n, dtype=torch.float, device=dev)
+    for net, blob in zip(nets_, blobs):
+        buf.copy_(torch.from_numpy(blob))
+        torch.cuda.synchronize()
+        assert L.bf_noalloc_forget(0) == 0
+        rc = L.bf_forward_noalloc(0, _ptr(buf), buf.numel(), _ptr(b), _ptr(c), _ptr(r), None, n,
+                                  None, None, _ptr(val), stream)
+        assert rc == 0, L.bf_last_error()
+        enc = encoder_impl("cuda")(net, int8=True, device=0)
+        want = enc.forward_full(b, c, r)[2].clone()
+        enc.close()
+        torch.cuda.synchronize()
+        assert torch.equal(val, want)
+    assert torch.cuda.current_device() == 0
