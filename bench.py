@@ -13,8 +13,11 @@ evenly across the ranks.
 Rank 0 prints one JSON line.  ``value`` is device-timed with inputs resident in HBM;
 ``e2e`` is the same metric through the host-buffer C-ABI call with both copies inside
 the timed region; ``roofline`` is the int8 tensor throughput of the one kernel against
-twice the measured dense bf16 peak; ``cpu_baseline`` is the reference's fp32 PyTorch
-evaluator (restated in ``oracle/fp32_model.py``) on the host cores.
+the tensor pipe's int8 rate measured in the same run (rank 0's GPU, at every N);
+``cpu_baseline`` is the reference's fp32 PyTorch evaluator (restated in
+``oracle/fp32_model.py``) on the host cores.  Beside the headline, with timed loops of their
+own after it: ``reference_kernel`` (the reference's CUDA kernel compiled for sm_100a, timed
+interleaved with this one), ``batch_sweep``, ``fp8_batch16384`` and ``split_131072``.
 """
 
 from __future__ import annotations
@@ -36,12 +39,23 @@ import torch
 
 OPS_PER_POSITION = 402653184          # int8 ops of the 32 weight GEMMs of one position
 BYTES_IN, BYTES_OUT = 67, 4356        # boards+control+rep ; policy+promo+value
-#: DRAM bytes one launch of 4096 positions moved under ncu (read 6.92 MB: the weight blob once
-#: plus inputs; written 0.02 MB: the 17.8 MB of outputs were still in L2 when the launch ended)
-NCU_DRAM_BYTES_PER_LAUNCH = 6.94e6
+PROFILE_NCU = os.path.join(ROOT, "profiles", "encoder_kernel_batch4096_ncu_full.md")
 METRIC = "positions evaluated/sec at batch 4096 int8"
 WORKLOAD = ("8-layer d256 h8 ff1024 int8 evaluator, N(0,0.02) seed-0 weights, seeded "
             "random-playout positions, batch 4096 per GPU")
+WORKLOAD_CPU = ("8-layer d256 h8 ff1024 evaluator in fp32 on the host cores (the reference's CPU path), "
+                "N(0,0.02) seed-0 weights, seeded random-playout positions, batch 256 per step")
+
+
+def profiled_traffic():
+    """DRAM bytes per launch at batch 4096 from the committed ncu summary of this kernel
+    (its ``dram_bytes_per_launch = ...`` line), or ``None`` when the summary has none."""
+    import re
+    try:
+        m = re.search(r"dram_bytes_per_launch\s*=\s*([0-9.eE+]+)", open(PROFILE_NCU).read())
+        return float(m.group(1)) if m else None
+    except OSError:
+        return None
 
 
 def load_positions(n: int):
@@ -144,6 +158,151 @@ def engine(enc, dev, n=1 << 20, steps=10, warmup=3):
                       "ms_priors_moves_generated_in_kernel": t_own}))
 
 
+def timed_ms(fn, dev, launches: int, warmup: int = 2):
+    """Mean device time of ``fn`` over ``launches`` back-to-back calls (CUDA events)."""
+    for _ in range(warmup):
+        fn()
+    torch.cuda.synchronize(dev)
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(launches):
+        fn()
+    e1.record()
+    torch.cuda.synchronize(dev)
+    return e0.elapsed_time(e1) / launches
+
+
+def reference_kernel_leg(enc, args, dev, rounds: int = 8, launches: int = 5):
+    """The reference's own CUDA kernel (compiled for sm_100a under ``oracle/_ref``) against this
+    library on the same GPU and inputs, with the reference's protocol (bench/bench_model.py:
+    172-177): the two candidates interleaved in one process, order reversed on alternate rounds,
+    medians over the rounds.  ``None`` where the checker is not built."""
+    try:
+        from oracle import ref_kernel as R
+    except Exception:
+        return None
+    if not R.available("A_int8"):
+        return None
+    ref = R.RefKernel("A_int8", device=str(dev))
+    cand = {"ours": lambda: enc.forward_full(*args), "reference": lambda: ref.forward_full(*args)}
+    ms = {"ours": [], "reference": []}
+    for rnd in range(rounds):
+        order = ("ours", "reference") if rnd % 2 == 0 else ("reference", "ours")
+        for name in order:
+            ms[name].append(timed_ms(cand[name], dev, launches, warmup=1))
+    enc.check_status()
+    n = args[0].shape[0]
+    ours, theirs = float(np.median(ms["ours"])), float(np.median(ms["reference"]))
+    return {"ms": theirs, "positions_per_s": n / theirs * 1e3, "ours_ms": ours, "ratio": theirs / ours,
+            "rounds": rounds, "launches_per_round": launches,
+            "protocol": "interleaved in one process, order reversed on alternate rounds, median of rounds; "
+                        "the reference's csrc/encoder.cu compiled for sm_100a, int8 'all', same weights and positions",
+            "outputs": "bit-identical to ours (tests/test_gpu_reference_kernel.py)"}
+
+
+def other_configs(net, enc, dev, world, rank, barrier, all_max):
+    """The configurations beside the headline, each with a short timed loop of its own:
+    the batch sweep (piece counts uniform in 2..32, six sizes, median of 10 launches), the
+    e4m3-FFN arithmetic at batch 16384, and one 131072-position step split evenly across the
+    GPUs.  Rank 0 runs the first two; every rank takes part in the third."""
+    from brokefish_b200.evaluator import shard_bounds
+    from brokefish_b200.positions import varied
+    out = {}
+    flush = torch.empty(256 << 20, dtype=torch.uint8, device=dev)
+
+    def median_ms(fn, n=10):
+        for _ in range(3):
+            fn()
+        torch.cuda.synchronize(dev)
+        ms = []
+        for i in range(n):
+            flush.fill_(i & 0xFF)
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record()
+            fn()
+            e1.record()
+            torch.cuda.synchronize(dev)
+            ms.append(e0.elapsed_time(e1))
+        return float(np.median(ms))
+
+    if rank == 0:
+        rows = []
+        for n in (1, 64, 512, 4096, 16384, 65536):
+            b, c, r, _ = varied(n, seed=2)
+            d = [torch.from_numpy(a).to(dev) for a in (b, c, r)]
+            t = median_ms(lambda: enc.forward_full(*d))
+            rows.append({"batch": n, "ms": t, "positions_per_s": n / t * 1e3})
+        out["batch_sweep"] = {"rows": rows, "data": "synthetic: piece counts U{2..32}, side to move 50/50, seed 2",
+                              "timing": "median of 10 launches, L2 flushed between them"}
+        if net is not None:
+            from brokefish_b200.nn.cuda_impl import FusedEncoder
+            e8 = FusedEncoder(net, fp8=True, device=dev.index or 0)
+            b, c, r, _ = load_positions(16384)
+            d = [torch.from_numpy(a).to(dev) for a in (b, c, r)]
+            t = median_ms(lambda: e8.forward_full(*d))
+            e8.check_status()
+            e8.close()
+            out["fp8_batch16384"] = {"ms": t, "positions_per_s": 16384 / t * 1e3, "dtype": "e4m3 (FFN) + f16",
+                                     "int8_equivalent_TOPs": 16384 * OPS_PER_POSITION / t / 1e9}
+        enc.check_status()
+    total = 131072
+    lo, hi = shard_bounds(total, world, rank)
+    b, c, r, _ = (a[lo:hi] for a in load_positions(total))
+    d = [torch.from_numpy(np.ascontiguousarray(a)).to(dev) for a in (b, c, r)]
+    for _ in range(3):
+        enc.forward_full(*d)
+    barrier()
+    ms = []
+    for i in range(5):
+        flush.fill_(i & 0xFF)
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        enc.forward_full(*d)
+        e1.record()
+        torch.cuda.synchronize(dev)
+        ms.append(e0.elapsed_time(e1))
+    barrier()
+    enc.check_status()
+    t = all_max(float(np.mean(ms)))
+    out["split_131072"] = {"ms_per_step": t, "positions_per_s": total / t * 1e3, "positions_per_gpu": hi - lo,
+                           "timing": "mean of 5 launches per rank, max over ranks"}
+    return out
+
+
+def d2h_probe(dev, rank, world, barrier, nbytes=4096 * BYTES_OUT, reps=200):
+    """What the host side of the box takes: every rank copies `nbytes` (one step's logits) from
+    its GPU into pinned host memory `reps` times, all ranks at once, then rank 0 alone.  Prints
+    the per-rank and aggregate GB/s: the ceiling of the end-to-end logit stream at N GPUs."""
+    import torch.distributed as dist
+    src = torch.empty(nbytes, dtype=torch.uint8, device=dev)
+    dst = torch.empty(nbytes, dtype=torch.uint8).pin_memory()
+    out = {}
+    for label, active in (("all_ranks", True), ("rank0_alone", rank == 0)):
+        for _ in range(5):
+            dst.copy_(src, non_blocking=True)
+        barrier()
+        t0 = time.perf_counter()
+        if active:
+            for _ in range(reps):
+                dst.copy_(src, non_blocking=True)
+            torch.cuda.synchronize(dev)
+        dt = time.perf_counter() - t0
+        barrier()
+        gbs = torch.tensor([nbytes * reps / dt / 1e9 if active else 0.0], dtype=torch.float64, device=dev)
+        if world > 1:
+            rows = [torch.zeros_like(gbs) for _ in range(world)]
+            dist.all_gather(rows, gbs)
+            vals = [float(r[0]) for r in rows]
+        else:
+            vals = [float(gbs[0])]
+        out[label] = {"per_rank_GBps": vals, "aggregate_GBps": sum(vals)}
+    if rank == 0:
+        print(json.dumps({"d2h_probe": out, "bytes_per_copy": nbytes, "copies": reps, "n_gpus": world,
+                          "what": "device -> pinned host copies of one step's logits (4096 x 4356 B), "
+                                  "cudaMemcpyAsync back to back; the ceiling this box's host side puts on "
+                                  "the end-to-end logit stream is aggregate_GBps / 4356 positions/s"}))
+
+
 def peaks():
     path = os.path.join(ROOT, "MEASURED_PEAKS.json")
     if os.path.exists(path):
@@ -230,6 +389,10 @@ def main() -> int:
                     help="play this rank's positions on the device (random games from the start position, "
                          "seed 100 + rank) instead of tiling the committed 4096")
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--d2h-probe", action="store_true",
+                    help="measure the device-to-pinned-host copy bandwidth of all ranks at once and exit")
+    ap.add_argument("--no-extras", action="store_true",
+                    help="skip the other configurations and the reference-kernel comparison")
     ap.add_argument("--sweep", action="store_true", help="print one line per batch size 1..65536 and exit")
     ap.add_argument("--engine", action="store_true",
                     help="time the engine kernels (movegen, step) and the fused expansion; print their lines and exit")
@@ -256,7 +419,7 @@ def main() -> int:
         line = {"impl": "reference", "metric": METRIC, "value": value, "unit": "positions/s",
                 "n_gpus": args.gpus, "steps": steps, "warmup": min(warmup, 3), "ms_per_step": ms,
                 "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f32",
-                "data": "synthetic", "config": {"workload": WORKLOAD, "l2": "n/a (CPU)"},
+                "data": "synthetic", "config": {"workload": WORKLOAD_CPU, "positions_per_step": 256, "l2": "n/a (CPU)"},
                 "cpu_baseline": dict(info, value=value, unit="positions/s"),
                 "e2e": {"value": value, "unit": "positions/s", "h2d_bytes_per_step": 0,
                         "d2h_bytes_per_step": 0}, "gpu_launches": 0}
@@ -273,6 +436,15 @@ def main() -> int:
     dev = torch.device("cuda", local)
     if world > 1:
         dist.init_process_group("nccl", device_id=dev)
+    if args.d2h_probe:
+        def probe_barrier():
+            if world > 1:
+                dist.barrier()
+            torch.cuda.synchronize(dev)
+        d2h_probe(dev, rank, world, probe_barrier)
+        if world > 1:
+            dist.destroy_process_group()
+        return 0
     net = None
     if rank == 0 or world == 1:
         net = BrokefishNet().eval()
@@ -373,12 +545,29 @@ def main() -> int:
         phases = {k: v / 5 for k, v in enc.read_profile().items() if k}
         enc.set_profile(False)
 
+    def all_max(x: float) -> float:
+        t = torch.tensor([x], dtype=torch.float64, device=dev)
+        if world > 1:
+            dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        return float(t[0])
+
+    headline = not (args.fp8 or args.f16 or args.scheme != "all" or args.total or args.playouts
+                    or args.batch != 4096)
+    extras, ref_leg = {}, None
+    if headline and not args.no_extras:
+        # outside the timed regions: the other configurations, and the reference's own kernel
+        # timed against this one on the same GPU
+        extras = other_configs(net, enc, dev, world, rank, barrier, all_max)
+        if rank == 0:
+            ref_leg = reference_kernel_leg(enc, (d_b, d_c, d_r), dev)
+
     times = torch.tensor([dev_ms, e2e_ms, e2e_pri_ms], dtype=torch.float64, device=dev)
     if world > 1:
         dist.all_reduce(times, op=dist.ReduceOp.MAX)
     dev_ms, e2e_ms, e2e_pri_ms = float(times[0]), float(times[1]), float(times[2])
     if rank != 0:
         if world > 1:
+            dist.barrier()                          # rank 0's CPU baseline and probes end here
             dist.destroy_process_group()
         return 0
 
@@ -401,10 +590,10 @@ def main() -> int:
                    "wall_ms_incl_flush": t_wall * 1e3},
         "roofline": {"bound": "tensor", "achieved": achieved, "peak": peak, "unit": "TFLOP/s",
                      "frac": achieved / peak, "peak_source": peak_src + "; int8 dense nominal 4500",
-                     "traffic": NCU_DRAM_BYTES_PER_LAUNCH if (n_local == 4096 and not args.fp8 and not args.f16
-                                                               and args.scheme == "all") else None,
-                     "traffic_source": "ncu dram__bytes_read.sum + dram__bytes_write.sum of one launch at "
-                                       "batch 4096 (profiles/encoder_kernel_batch4096_ncu_full.md)",
+                     "traffic": profiled_traffic() if (n_local == 4096 and not args.fp8 and not args.f16
+                                                       and args.scheme == "all") else None,
+                     "traffic_source": "ncu dram__bytes_read.sum + dram__bytes_write.sum of one launch of this "
+                                       "kernel at batch 4096, read from profiles/encoder_kernel_batch4096_ncu_full.md",
                      "hbm_algorithmic_GBps": n_local * (BYTES_IN + BYTES_OUT) / (kern_avg_ms * 1e-3) / 1e9},
         "e2e": {"value": e2e, "unit": "positions/s", "h2d_bytes_per_step": n_local * BYTES_IN,
                 "d2h_bytes_per_step": n_local * BYTES_OUT},
@@ -417,8 +606,11 @@ def main() -> int:
     }
     if phases is not None:
         line["phases_cycles_per_launch"] = phases
-    if world == 1:
-        # the tensor pipe's own int8 rate on this GPU (a tcgen05 kind::i8 loop on resident
+    line.update(extras)
+    if ref_leg is not None:
+        line["reference_kernel"] = ref_leg
+    if True:
+        # the tensor pipe's own int8 rate on this GPU (rank 0's, at every N) (a tcgen05 kind::i8 loop on resident
         # operands) is the denominator when it can be measured; the fractions of 2 x the measured
         # bf16 rate and of the nominal int8 rate are kept beside it
         import ctypes
@@ -453,11 +645,12 @@ def main() -> int:
                     "what": "sum over the element-wise blocks of elements per launch / isolated rate "
                             "(bf_measure_elementwise: same device functions, operands in shared memory, "
                             "16 warps per SM, no tensor-memory loads, exchanges or barriers)"}
-    if world == 1 and not args.no_cpu_baseline:
+    if not args.no_cpu_baseline:
         cv, cms, info = cpu_reference(25, 3)
         line["cpu_baseline"] = dict(info, value=cv, unit="positions/s")
     print(json.dumps(line))
     if world > 1:
+        dist.barrier()
         dist.destroy_process_group()
     return 0
 

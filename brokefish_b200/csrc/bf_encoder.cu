@@ -15,7 +15,7 @@
 // Shape of the kernel
 //   * persistent grid, one CTA per SM, each CTA loops over tiles of 128 token rows
 //     (4 boards);
-//   * 18 warps: 16 "row" warps, one weight-stream producer, one MMA issuer;
+//   * 19 warps: 16 "row" warps, one weight-stream producer, two MMA issuers;
 //   * row warps: thread = (row, quarter).  Warp w works on TMEM lanes 32*(w%4)..+31, i.e.
 //     on board w%4 of the tile, and on quarter w/4 of each row's columns.  All LayerNorm /
 //     quantise / descale work is thread-local plus one exchange among the four quarters;
@@ -45,7 +45,7 @@ namespace bf {
 using namespace bfptx;
 
 constexpr int kD = 256, kDFF = 1024, kT = 32, kRows = 128;
-constexpr int kRowWarps = 16, kProducerWarp = 16, kMmaWarp = 17, kThreads = 576;
+constexpr int kRowWarps = 16, kProducerWarp = 16, kMmaWarp = 17, kMmaWarp2 = 18, kThreads = 608;
 constexpr int kLparamStride = 4736;
 constexpr int LP_SW_QKV = 0, LP_SW_O = 24, LP_SW_FF1 = 32, LP_SW_FF2 = 64;
 constexpr int LP_B_QKV = 128, LP_B_O = 1664, LP_B_FF1 = 2176, LP_B_FF2 = 4224;
@@ -586,16 +586,24 @@ __device__ __forceinline__ void attention_unit(const RowCtx& c, uint32_t alive) 
         mma_f16_f16(s[nt], qa[0], kb[0], kb[1]);      // dims 0-15, then 16-31
         mma_f16_f16(s[nt], qa[1], kb[2], kb[3]);
     }
+    // dead keys -> -inf: this lane's two keys of every n-tile are the same for both row halves,
+    // so the mask is one packed fp16 pair per n-tile (0 keeps a score bit for bit, -inf replaces
+    // it: a finite fp16 plus -inf is -inf) and applying it is one packed add per pair
+    uint32_t dead[4];
+#pragma unroll
+    for (int nt = 0; nt < 4; ++nt) {
+        const uint32_t two = (alive >> (8 * nt + 2 * t)) & 3u;
+        dead[nt] = ((two & 1u) ? 0u : 0xfc00u) | ((two & 2u) ? 0u : 0xfc000000u);
+    }
 #pragma unroll
     for (int hi = 0; hi < 2; ++hi) {
         float pv[4][2];
         float mx = -INFINITY;
 #pragma unroll
         for (int nt = 0; nt < 4; ++nt) {
-            const __half2 val = as_h2(s[nt][hi]);
-            const int col = 8 * nt + 2 * t;
-            pv[nt][0] = ((alive >> col) & 1u) ? __low2float(val) : -INFINITY;
-            pv[nt][1] = ((alive >> (col + 1)) & 1u) ? __high2float(val) : -INFINITY;
+            const __half2 val = __hadd2(as_h2(s[nt][hi]), as_h2(dead[nt]));
+            pv[nt][0] = __low2float(val);
+            pv[nt][1] = __high2float(val);
             mx = fmaxf(mx, fmaxf(pv[nt][0], pv[nt][1]));
         }
         mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 1));
@@ -1472,10 +1480,21 @@ __device__ __forceinline__ void mma_wait_operand(uint32_t smem, volatile int* ab
     tc_fence_after();
 }
 
+// Two threads (lane 0 of two warps) share the schedule: issuing one unit costs a thread well
+// over twice the unit's time on the tensor pipe (barrier waits, descriptors, a full MMA queue),
+// and the units of a step come in pairs -- the two 128-wide halves of an out-projection, of a
+// hidden chunk, of an ff2 chunk -- that are independent of one another.  Issuer `who` takes the
+// half-`who` unit of every pair (its accumulator slot is slot `who`) and steps over the other
+// half's weight stages; the QKV units, which follow one another on one accumulator, and the head
+// product are issuer 0's.  Both issuers wait for every phase of the operand barriers in order,
+// needed or not, because a parity wait must not fall a phase behind.  The fp16 arithmetic's FFN
+// (one running pair of ff2 accumulators) keeps a single issuer.
 template <int kAr>
 __device__ __forceinline__ void mma_loop(uint32_t smem, uint32_t tmem, volatile int* abort_flag,
-                                      const Params& p, int first_tile, int tile_step, int n_tiles) {
+                                      const Params& p, int first_tile, int tile_step, int n_tiles, int who) {
     using C = Cfg<kAr>;
+    constexpr bool kTwo = kAr != kArF16;
+    if (!kTwo && who != 0) return;
     MmaState st = {0, 0, {0, 0}, 0, {0, 0}};
     // int8: every weight GEMM is s8/u8 x s8.  e4m3: QKV and out-projection are fp16 x fp16 with
     // fp16 accumulators (the bits of the reference's mma.sync), the FFN is e4m3 x e4m3 with fp32
@@ -1493,14 +1512,18 @@ __device__ __forceinline__ void mma_loop(uint32_t smem, uint32_t tmem, volatile 
     constexpr int kFfnKind = kAr == kArE4M3 ? kKindF8 : (kAr == kArF16 ? kKindF16 : kKindI8);
     const uint32_t acc0 = tmem + TM_ACC, acc1 = tmem + TM_ACC + 128;
     const uint32_t sm_a = smem + C::SM_A, sm_r = smem + C::SM_R;
+    (void)kHalfA;
     for (int tile = first_tile; tile < n_tiles; tile += tile_step) {
         for (int layer = 0; layer < p.n_layers; ++layer) {
             mma_wait_operand(smem, abort_flag, B_A_READY, st.aready);          // LN1 output
-            for (int j = 0; j < 4; ++j)
-                mma_unit<kAr>(smem, abort_flag, st, acc0, 0, sm_a, true, C::kQkvSlabs, kI_QKV, kQkvKind);
+            if (who == 0)
+                for (int j = 0; j < 4; ++j)
+                    mma_unit<kAr>(smem, abort_flag, st, acc0, 0, sm_a, true, C::kQkvSlabs, kI_QKV, kQkvKind);
             mma_wait_operand(smem, abort_flag, B_A_READY, st.aready);          // attention output
-            mma_unit<kAr>(smem, abort_flag, st, acc0, 0, sm_a, false, C::kOutSlabs, kI_OUT, kOutKind);
-            mma_unit<kAr>(smem, abort_flag, st, acc1, 1, sm_a, false, C::kOutSlabs, kI_OUT, kOutKind);
+            if (!kTwo || who == 0) mma_unit<kAr>(smem, abort_flag, st, acc0, 0, sm_a, false, C::kOutSlabs, kI_OUT, kOutKind);
+            else                   st.rc += C::kOutSlabs;
+            if (!kTwo || who == 1) mma_unit<kAr>(smem, abort_flag, st, acc1, 1, sm_a, false, C::kOutSlabs, kI_OUT, kOutKind);
+            else                   st.rc += C::kOutSlabs;
             mma_wait_operand(smem, abort_flag, B_A_READY, st.aready);          // LN2 output
             if constexpr (kAr == kArF16) {
                 // fp16 FFN: ff1 units go into slot 0; once the rows have written a hidden chunk,
@@ -1548,10 +1571,11 @@ __device__ __forceinline__ void mma_loop(uint32_t smem, uint32_t tmem, volatile 
             for (int u = 0; u < 16; ++u) {
                 // kind/chunk of unit u: pairs (u>>1): F1 0, F1 1, F2 0, F1 2, F2 1, F1 3, F2 2, F2 3
                 const int pr = u >> 1, jh = u & 1;
+                if (jh != who) { st.rc += 2; continue; }                  // the other issuer's unit
                 const int kind2 = (0xD4 >> pr) & 1;                       // 0b11010100
                 const int ch = kind2 ? ((0x32010000u >> (4 * pr)) & 0xF) : ((0x00302010u >> (4 * pr)) & 0xF);
                 if (kind2) {
-                    if (jh == 0) mma_wait_operand(smem, abort_flag, B_A2_READY + (ch & 1), st.a2n[ch & 1]);
+                    mma_wait_operand(smem, abort_flag, B_A2_READY + (ch & 1), st.a2n[ch & 1]);
                     mma_unit<kAr>(smem, abort_flag, st, jh ? acc1 : acc0, jh, sm_r + (ch & 1) * 32768,
                                    false, 2, kI_FF2, kFfnKind);
                 } else {
@@ -1564,8 +1588,11 @@ __device__ __forceinline__ void mma_loop(uint32_t smem, uint32_t tmem, volatile 
         // sixteen in rising order -- the bits of the reference's fp16-accumulate mma.sync head
         // product (encoder.cu:309-352, 918-927); A is the final norm's output in the staging region
         mma_wait_operand(smem, abort_flag, B_A_READY, st.aready);
-        mma_unit<kAr>(smem, abort_flag, st, acc0, 0, sm_r, false, kHeadStages,
-                      umma_idesc(kAccF16, kFmtF16, kFmtF16, 128, 96), kKindF16);
+        if (who == 0)
+            mma_unit<kAr>(smem, abort_flag, st, acc0, 0, sm_r, false, kHeadStages,
+                          umma_idesc(kAccF16, kFmtF16, kFmtF16, 128, 96), kKindF16);
+        else
+            st.rc += kHeadStages;
     }
 }
 
@@ -1617,7 +1644,7 @@ __global__ void __launch_bounds__(kThreads, 1) encoder_kernel(const Params p) {
     } else if (warp == kProducerWarp) {
         if (lane == 0) producer_loop<kAr>(smem, abort_flag, p, blockIdx.x, gridDim.x, n_tiles);
     } else {
-        if (lane == 0) mma_loop<kAr>(smem, tmem, abort_flag, p, blockIdx.x, gridDim.x, n_tiles);
+        if (lane == 0) mma_loop<kAr>(smem, tmem, abort_flag, p, blockIdx.x, gridDim.x, n_tiles, warp - kMmaWarp);
     }
     __syncwarp();
     tc_fence_before();

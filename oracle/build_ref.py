@@ -45,6 +45,7 @@ SETS = {
     "A_int8": (dict(seed=0, std=0.02, perturb_norms=False), dict(int8=True)),
     "B_int8": (dict(seed=0, std=None, perturb_norms=True), dict(int8=True)),
     "A_e4m3": (dict(seed=0, std=0.02, perturb_norms=False), dict(fp8=True)),
+    "B_e4m3": (dict(seed=0, std=None, perturb_norms=True), dict(fp8=True)),
     "A_f16": (dict(seed=0, std=0.02, perturb_norms=False), dict()),
     "B_int8_ffn": (dict(seed=0, std=None, perturb_norms=True), dict(int8=True, int8_scheme="ffn")),
     "B_int8_ffn_qkv": (dict(seed=0, std=None, perturb_norms=True), dict(int8=True, int8_scheme="ffn+qkv")),

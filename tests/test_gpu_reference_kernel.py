@@ -218,16 +218,27 @@ def test_prenorm_wdl_value_against_reference_kernel(pos256):
     enc.close()
 
 
-def test_e4m3_path_against_reference_kernel(pos256):
+#: What the e4m3 arm is held to against the reference's e4m3 kernel, per weight set:
+#: max |dlogit| as a fraction of max |logit| -- the reference's own bar for a quantised path,
+#: 8 % (tests/test_quant.py:342-356) -- and the masked-argmax agreement at 16384 positions
+#: (measured value minus a small margin; set A's N(0, 0.02) weights give nearly flat logits, so
+#: its argmax is decided by differences far below the tolerance; set B has default-init scale).
+#: Measured on a B200: set A 6.2 % / 6.5 % of max|logit| (256 / 16384 positions), value 0.047,
+#: agreement 0.9496, worst regret 0.067; set B 4.7 %, value 0.102, agreement 0.9578, regret 0.083.
+E4M3_BARS = {"A": dict(rel=8e-2, value=8e-2, agree=0.94), "B": dict(rel=8e-2, value=1.2e-1, agree=0.95)}
+
+
+@pytest.mark.parametrize("name", ["A", "B"])
+def test_e4m3_arm_against_the_reference_e4m3_kernel(name, pos256):
     """The e4m3-FFN arithmetic.  Its fp16 GEMMs (QKV, out-projection) run on tcgen05 with fp16
     accumulators, which carry the bits of the reference's fp16-accumulate mma.sync, so layer 0 is
     bit-identical up to the FFN input: LN1, Q, K, V, attention output, residual, LN2.  The FFN
     itself accumulates e4m3 products in fp32 where the reference accumulates in fp16 (no tcgen05
-    form reproduces that instruction's roundings), so the outputs are a tolerance: 10 % of
-    max|logit| (measured about 6 %)."""
-    if not R.available("A_e4m3"):
-        pytest.skip("slabs missing")
-    enc, ref = product(SETS["A"], fp8=True), R.RefKernel("A_e4m3")
+    form reproduces that instruction's roundings), so the outputs are a tolerance, the reference's
+    own for a quantised path: 8 % of max|logit|."""
+    assert R.available(f"{name}_e4m3"), "slabs missing: rebuild oracle/_ref"
+    bars = E4M3_BARS[name]
+    enc, ref = product(SETS[name], fp8=True), R.RefKernel(f"{name}_e4m3")
     assert ref.quant == 1
     sl = slice(0, 128)
     for stage in (9, 1, 5, 6, 7, 4, 2, 3):
@@ -235,16 +246,15 @@ def test_e4m3_path_against_reference_kernel(pos256):
         want = ref.forward_stage(*inputs(pos256, sl), stage).cpu().numpy()
         assert same_bits(got, want), stage
     (pol, pro, val), (rpol, rpro, rval) = run_both(enc, ref, pos256, sl)
-    tol = rel_tol(rpol, 10e-2)
     d = np.abs(pol.astype(np.float32) - rpol.astype(np.float32)).max()
-    print(f"e4m3 arm vs reference e4m3 kernel: max|dlogit| {d:.4f} of max|logit| "
-          f"{np.abs(rpol.astype(np.float32)).max():.3f}, value {np.abs(val - rval).max():.4f}")
-    assert d <= tol
-    assert np.abs(val - rval).max() <= 8e-2
+    top = np.abs(rpol.astype(np.float32)).max()
+    print(f"e4m3 arm, set {name}, vs reference e4m3 kernel: max|dlogit| {d:.4f} = {d / top:.4f} of max|logit| "
+          f"{top:.3f}, value {np.abs(val - rval).max():.4f}")
+    assert d <= rel_tol(rpol, bars["rel"])
+    assert np.abs(val - rval).max() <= bars["value"]
     # the 16384-position configuration (piece counts 2..32, side to move flipped on half, seed 3):
     # same tolerance, everything finite, and the masked argmax of the two kernels agrees on
-    # most positions that have a legal move (measured 95 %: with N(0, 0.02) weights the logits
-    # are nearly flat, and the two FFN accumulator widths differ by up to 6 % of the largest)
+    # most positions that have a legal move
     from brokefish_b200.positions import varied
     b, c, r, lg = varied(16384, seed=3)
     args = [dev(a) for a in (b, c, r)]
@@ -253,14 +263,23 @@ def test_e4m3_path_against_reference_kernel(pos256):
     enc.check_status()
     assert np.isfinite(pol.astype(np.float32)).all() and np.isfinite(val).all()
     d = np.abs(pol.astype(np.float32) - rpol.astype(np.float32)).max()
-    assert d <= rel_tol(rpol, 10e-2) and np.abs(val - rval).max() <= 8e-2
+    top = np.abs(rpol.astype(np.float32)).max()
+    dv = float(np.abs(val - rval).max())
     alive = ((b.view(np.uint16) >> 11) & 1) == 0
     lg = np.where(alive, lg, 0)                       # captured pieces have no moves
     has_move = lg.any(axis=1) & (c > 0)               # words are the mover's only where nothing was flipped
     mine, theirs = O.masked_argmax(pol, lg), O.masked_argmax(rpol, lg)
     agree = (mine == theirs)[has_move].mean()
-    print(f"e4m3, 16384 positions: max|dlogit| {d:.4f}, masked-argmax agreement {agree:.4f} on {has_move.sum()}")
-    assert agree >= 0.93
+    # how much worse than the reference kernel's choice the product's choice is, by the
+    # reference kernel's own logits
+    flat = rpol.astype(np.float32).reshape(rpol.shape[0], -1)
+    rows = np.where(has_move & (mine != theirs))[0]
+    regret = float((flat[rows, theirs[rows]] - flat[rows, mine[rows]]).max()) if rows.size else 0.0
+    print(f"e4m3, set {name}, 16384 positions: max|dlogit| {d:.4f} = {d / top:.4f} of max|logit| {top:.3f}, "
+          f"value {dv:.4f}, masked-argmax agreement {agree:.4f} on {has_move.sum()}, worst regret {regret:.4f}")
+    assert d <= rel_tol(rpol, bars["rel"]) and dv <= bars["value"]
+    assert agree >= bars["agree"]
+    assert regret <= rel_tol(rpol, bars["rel"])
     enc.close()
 
 
