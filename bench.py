@@ -637,6 +637,18 @@ def main() -> int:
                     break
                 rates[block] = eps.value
                 floor_s += n_local * 8 * 32 * width / eps.value
+            # the same sum for the cheaper, no longer bit-exact forms of the blocks (one combined
+            # scale, requantisation in fp16 or fused into the normalise): what a tolerance arm
+            # could save at most on the CUDA cores
+            cheap_s, cheap = 0.0, {8: 1024, 10: 768 + 256, 11: 1024, 3: 2 * 256, 9: 2 * 256, 5: 256}
+            for block, width in cheap.items():
+                eps = ctypes.c_double(0)
+                if rates is None or _native.lib().bf_measure_elementwise(local, block, 4000, ctypes.byref(eps), None) != 0:
+                    cheap_s = None
+                    break
+                cheap_s += n_local * 8 * 32 * width / eps.value
+            if cheap_s:
+                rf["cuda_core_floor_cheaper_arithmetic_ms"] = cheap_s * 1e3
             if rates:
                 names = ["ff1_epilogue", "descale_bias", "ff2_step", "norm_statistics", "normalise_quantise", "quantise"]
                 rf["cuda_core_floor"] = {

@@ -301,19 +301,21 @@ __device__ __forceinline__ void descale(const uint32_t* acc, float sa, float sw,
             const int i = 4 * v + k;
             // exact s32 -> f32 on the conversion unit (otherwise idle here; the integer-add
             // form measured 6 % slower because it loads the FMA pipe, which is the busy one),
-            // then the two fp32 multiplies, both lanes at once
+            // then the two fp32 multiplies
             if (kAcc == kAccPlain) {
                 const uint32_t h = __byte_perm(acc[2 * i], acc[2 * i + 1], 0x5410);
                 out[i] = kRelu ? hfma2_relu(h, 0x3C003C00u, bw[k]) : as_u32(__hadd2(as_h2(h), as_h2(bw[k])));
                 continue;
             }
+            // the row-scale multiply as two scalar multiplies (they spread over both halves of
+            // the fp32 pipe; measured 0.5 % faster than the packed form), the weight-scale one packed
             uint64_t f;
             if (kAcc == kAccInt)
-                f = pk2(static_cast<float>(static_cast<int>(acc[2 * i])),
-                        static_cast<float>(static_cast<int>(acc[2 * i + 1])));
+                f = pk2(__fmul_rn(static_cast<float>(static_cast<int>(acc[2 * i])), sa),
+                        __fmul_rn(static_cast<float>(static_cast<int>(acc[2 * i + 1])), sa));
             else
-                f = pk2(__uint_as_float(acc[2 * i]), __uint_as_float(acc[2 * i + 1]));
-            f = mul2(mul2(f, sa2), sw2);
+                f = mul2(pk2(__uint_as_float(acc[2 * i]), __uint_as_float(acc[2 * i + 1])), sa2);
+            f = mul2(f, sw2);
             if (kRelu) {
                 // relu(x + b) in one instruction: x * 1 is exact, so the sum is rounded once
                 // exactly as the fp16 add is, and the clamp is part of the same operation
@@ -1664,7 +1666,10 @@ __global__ void __launch_bounds__(kThreads, 1) encoder_kernel(const Params p) {
 // evaluator calls.  Block 0: ff1 epilogue (s32 -> descale -> bias + ReLU -> row maximum -> u8);
 // 1: descale + bias -> fp16 (QKV and out-projection epilogues); 2: ff2 step (descale, fused add
 // to the fp16 running total); 3: norm statistics (sum, sum of squares, minimum, maximum); 4:
-// normalise -> fp16 -> s8; 5: fp16 -> int8 quantisation alone.  32 elements per thread and pass.
+// normalise -> fp16 -> s8; 5: fp16 -> int8 quantisation alone; 8-11: the cheaper forms of blocks 0,
+// 4, 1 and 2 that a not-bit-exact arithmetic could use (one combined scale, the requantisation in
+// fp16 or fused into the normalise), to measure what giving up the reference's bits would buy.
+// 32 elements per thread and pass.
 // The host entry also runs block 0 with eight and with thirty-two warps resident (its blocks 6
 // and 7), which shows how much a different number of row warps could change.
 // ------------------------------------------------------------------------------------------
@@ -1685,7 +1690,7 @@ __global__ void __launch_bounds__(kProbeThreads, 1) elementwise_probe_kernel(con
     for (int i = 0; i < 16; ++i) run[i] = 0;
     for (int it = 0; it < iters; ++it) {
         uint32_t acc[32], o[16];
-        if (kBlock <= 2) {
+        if (kBlock <= 2 || kBlock == 8 || kBlock >= 10) {
 #pragma unroll
             for (int k = 0; k < 32; ++k) acc[k] = probe_sm[k * kProbeThreads + tid] + it;
         } else {
@@ -1725,9 +1730,78 @@ __global__ void __launch_bounds__(kProbeThreads, 1) elementwise_probe_kernel(con
             for (int i = 0; i < 16; ++i) o[i] = f2_to_h2(mul2(add2(h2_to_f2(o[i]), sa2), sw2));
             const uint4 a = quant16(&o[0], sa, one2), b = quant16(&o[8], sa, one2);
             keep ^= a.x ^ a.y ^ a.z ^ a.w ^ b.x ^ b.y ^ b.z ^ b.w;
-        } else {
+        } else if (kBlock == 5) {
             const uint4 a = quant16(&o[0], sa, one2), b = quant16(&o[8], sa, one2);
             keep ^= a.x ^ a.y ^ a.z ^ a.w ^ b.x ^ b.y ^ b.z ^ b.w;
+        } else if (kBlock == 8) {
+            // ff1 epilogue, cheaper form: one combined scale, bias + ReLU as now, the u8
+            // requantisation in fp16 (the rounding add on 1024 leaves the integer in the low
+            // mantissa bits of each half: one packed fma and a quarter of a byte permute per
+            // element instead of two conversions, a multiply, an fma and three quarters)
+            const uint4* b4 = reinterpret_cast<const uint4*>(bias);
+            const float s = sa * sw;
+#pragma unroll
+            for (int v = 0; v < 4; ++v) {
+                const uint4 bv = __ldg(b4 + v);
+                const uint32_t bw[4] = {bv.x, bv.y, bv.z, bv.w};
+#pragma unroll
+                for (int k = 0; k < 4; ++k) {
+                    const int i = 4 * v + k;
+                    const uint64_t f = pk2(__fmul_rn(static_cast<float>(static_cast<int>(acc[2 * i])), s),
+                                           __fmul_rn(static_cast<float>(static_cast<int>(acc[2 * i + 1])), s));
+                    o[i] = hfma2_relu(f2_to_h2(f), 0x3C003C00u, bw[k]);
+                }
+            }
+            const float am = amax_h2<16>(o, false);
+            m = fmaxf(m, am);
+            const __half2 inv = __float2half2_rn(255.0f / fmaxf(am, 1e-3f)), magic = __float2half2_rn(1024.0f);
+#pragma unroll
+            for (int k = 0; k < 4; ++k) {
+                uint32_t q[4];
+#pragma unroll
+                for (int j = 0; j < 4; ++j) q[j] = as_u32(__hfma2(as_h2(o[4 * k + j]), inv, magic));
+                keep ^= __byte_perm(q[0], q[1], 0x6420) ^ __byte_perm(q[2], q[3], 0x6420);
+            }
+        } else if (kBlock == 9) {
+            // normalise + s8 quantise, cheaper form: (x - mean) * rstd * inv and the rounding add as
+            // one packed fma on the converted input
+            const uint64_t a2 = pk2(sw, sw), b2 = pk2(12582912.0f + sa, 12582912.0f + sa);
+#pragma unroll
+            for (int k = 0; k < 4; ++k) {
+                float a0, a1, b0, b1, c0, c1, d0, d1;
+                upk2(fma2(h2_to_f2(o[4 * k]), a2, b2), a0, a1);
+                upk2(fma2(h2_to_f2(o[4 * k + 1]), a2, b2), b0, b1);
+                upk2(fma2(h2_to_f2(o[4 * k + 2]), a2, b2), c0, c1);
+                upk2(fma2(h2_to_f2(o[4 * k + 3]), a2, b2), d0, d1);
+                keep ^= pack4(__float_as_uint(a0), __float_as_uint(a1), __float_as_uint(b0), __float_as_uint(b1)) ^
+                        pack4(__float_as_uint(c0), __float_as_uint(c1), __float_as_uint(d0), __float_as_uint(d1));
+            }
+        } else if (kBlock == 10) {
+            // descale + bias to fp16, cheaper form: one combined scale
+            const uint4* b4 = reinterpret_cast<const uint4*>(bias);
+            const float s = sa * sw;
+#pragma unroll
+            for (int v = 0; v < 4; ++v) {
+                const uint4 bv = __ldg(b4 + v);
+                const uint32_t bw[4] = {bv.x, bv.y, bv.z, bv.w};
+#pragma unroll
+                for (int k = 0; k < 4; ++k) {
+                    const int i = 4 * v + k;
+                    const uint64_t f = pk2(__fmul_rn(static_cast<float>(static_cast<int>(acc[2 * i])), s),
+                                           __fmul_rn(static_cast<float>(static_cast<int>(acc[2 * i + 1])), s));
+                    probe_sm[(16 + i) * kProbeThreads + tid] = as_u32(__hadd2(as_h2(f2_to_h2(f)), as_h2(bw[k])));
+                }
+            }
+        } else {
+            // ff2 step, cheaper form: one combined scale in the fused add to the running total
+            const float s = sa * sw;
+            const uint64_t s2 = pk2(s, s);
+#pragma unroll
+            for (int i = 0; i < 16; ++i) {
+                const uint64_t f = pk2(static_cast<float>(static_cast<int>(acc[2 * i])),
+                                       static_cast<float>(static_cast<int>(acc[2 * i + 1])));
+                run[i] = f2_to_h2(fma2(f, s2, h2_to_f2(run[i])));
+            }
         }
     }
     float a, b, c, d;
@@ -2566,17 +2640,19 @@ int bf_measure_i8_peak(int device, int iters, double* tops, double* ms) {
 }
 
 int bf_measure_elementwise(int device, int block, int iters, double* elements_per_s, double* ms) {
-    if (elements_per_s == nullptr || iters < 1 || iters > (1 << 22) || block < 0 || block > 7)
-        return fail(BF_EINVAL, "elements_per_s is null, block not in 0..7 or iters out of range");
+    if (elements_per_s == nullptr || iters < 1 || iters > (1 << 22) || block < 0 || block > 11)
+        return fail(BF_EINVAL, "elements_per_s is null, block not in 0..11 or iters out of range");
     BF_ON_DEVICE(device);
     cudaDeviceProp prop;
     BF_CUDA(cudaGetDeviceProperties(&prop, device));
     if (prop.major != 10) return fail(BF_ENOTSUP, "this library needs a compute capability 10.x (sm_100a) device");
     using Kernel = void (*)(const __half*, float, float, float, int, float*);
-    static const Kernel kernels[8] = {bf::elementwise_probe_kernel<0, 512>, bf::elementwise_probe_kernel<1, 512>,
-                                      bf::elementwise_probe_kernel<2, 512>, bf::elementwise_probe_kernel<3, 512>,
-                                      bf::elementwise_probe_kernel<4, 512>, bf::elementwise_probe_kernel<5, 512>,
-                                      bf::elementwise_probe_kernel<0, 256>, bf::elementwise_probe_kernel<0, 1024>};
+    static const Kernel kernels[12] = {bf::elementwise_probe_kernel<0, 512>, bf::elementwise_probe_kernel<1, 512>,
+                                       bf::elementwise_probe_kernel<2, 512>, bf::elementwise_probe_kernel<3, 512>,
+                                       bf::elementwise_probe_kernel<4, 512>, bf::elementwise_probe_kernel<5, 512>,
+                                       bf::elementwise_probe_kernel<0, 256>, bf::elementwise_probe_kernel<0, 1024>,
+                                       bf::elementwise_probe_kernel<8, 512>, bf::elementwise_probe_kernel<9, 512>,
+                                       bf::elementwise_probe_kernel<10, 512>, bf::elementwise_probe_kernel<11, 512>};
     const int threads = block == 6 ? 256 : (block == 7 ? 1024 : 512);
     const int kSmem = 32 * threads * 4;
     BF_CUDA(cudaFuncSetAttribute(kernels[block], cudaFuncAttributeMaxDynamicSharedMemorySize, kSmem));

@@ -317,7 +317,10 @@ int bf_measure_i8_peak(int device, int iters, double* tops, double* ms);
  * barriers).  `block`: 0 ff1 epilogue (descale, bias + ReLU, row maximum, u8 quantise), 1 descale
  * + bias to fp16 (QKV / out-projection epilogue), 2 ff2 step (descale + fused add to the fp16
  * running total), 3 norm statistics, 4 normalise + s8 quantise, 5 fp16 -> int8 quantise alone;
- * 6 and 7: block 0 again with eight and with thirty-two warps per SM.
+ * 6 and 7: block 0 again with eight and with thirty-two warps per SM; 8, 9, 10, 11: blocks 0, 4, 1
+ * and 2 in a cheaper arithmetic that no longer reproduces the reference's bits (one combined
+ * scale instead of two multiplies, the u8 requantisation done in fp16, the s8 quantisation fused
+ * into the normalise) -- what a tolerance arm could save, measured before building one.
  * With the element counts of one position these give the time the reference's element-wise
  * arithmetic needs on this GPU however it is scheduled -- the second roof of this kernel.  No
  * counterpart in the reference beyond its wish for a benchmark that reports achieved against
