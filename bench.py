@@ -567,7 +567,11 @@ def main() -> int:
     dev_ms, e2e_ms, e2e_pri_ms = float(times[0]), float(times[1]), float(times[2])
     if rank != 0:
         if world > 1:
-            dist.barrier()                          # rank 0's CPU baseline and probes end here
+            # rank 0 still has its probes and the CPU baseline to run: wait for it on the
+            # rendezvous store (a blocking socket read), not in a collective, whose waiters spin
+            # on host cores and would take them from the CPU baseline
+            from datetime import timedelta
+            dist.distributed_c10d._get_default_store().wait(["bench_rank0_done"], timedelta(minutes=20))
             dist.destroy_process_group()
         return 0
 
@@ -596,7 +600,11 @@ def main() -> int:
                                        "kernel at batch 4096, read from profiles/encoder_kernel_batch4096_ncu_full.md",
                      "hbm_algorithmic_GBps": n_local * (BYTES_IN + BYTES_OUT) / (kern_avg_ms * 1e-3) / 1e9},
         "e2e": {"value": e2e, "unit": "positions/s", "h2d_bytes_per_step": n_local * BYTES_IN,
-                "d2h_bytes_per_step": n_local * BYTES_OUT},
+                "d2h_bytes_per_step": n_local * BYTES_OUT,
+                "host_link_GBps_rank0": enc.host_link_gbps,
+                "plan": "the call splits the batch by the device-to-host rate it measured on its previous "
+                        "call: below 37 GB/s equal two-wave launches with the last wave written straight into "
+                        "the pinned buffers, else launches of shrinking size"},
         "e2e_fused_expansion": {"value": n_global * e2e_steps / (e2e_pri_ms * 1e-3), "unit": "positions/s",
                                 "what": "the same step through forward_priors_host: legality words in, "
                                         "edge lists (fp16 priors, move labels, counts) and values out",
@@ -662,7 +670,7 @@ def main() -> int:
         line["cpu_baseline"] = dict(info, value=cv, unit="positions/s")
     print(json.dumps(line))
     if world > 1:
-        dist.barrier()
+        dist.distributed_c10d._get_default_store().set("bench_rank0_done", "1")
         dist.destroy_process_group()
     return 0
 

@@ -2033,6 +2033,9 @@ struct bf_handle {
     cudaStream_t stream = nullptr;       // inputs and kernels of bf_forward_host
     cudaStream_t copy_stream = nullptr;  // its device-to-host copies
     cudaEvent_t chunk_done = nullptr;
+    cudaEvent_t copy_t0 = nullptr, copy_t1 = nullptr;   // around the first copy-out of bf_forward_host
+    double d2h_gbps = 0.0;        // what that copy last measured; 0 = not measured yet
+    int host_plan = 0;            // BF_OPT_HOST_PLAN: 0 by the measured link, 1 fast-link plan, 2 slow-link plan
 };
 
 namespace {
@@ -2056,6 +2059,11 @@ void* mapped_host(const void* p) {
     if (cudaPointerGetAttributes(&a, p) != cudaSuccess) { cudaGetLastError(); return nullptr; }
     return a.type == cudaMemoryTypeHost ? a.devicePointer : nullptr;
 }
+
+// Below this measured device-to-host rate bf_forward_host switches to its slow-link plan: the
+// point where the copy of a 3504-position launch stops hiding behind the last wave by more than
+// the slow-link plan's own cost.
+constexpr double kSlowLinkGBps = 37.0;
 
 struct PriorOut {
     void* prior;
@@ -2196,6 +2204,8 @@ int bf_create(const void* blob, size_t blob_bytes, int device, bf_handle** out) 
     if (e == cudaSuccess) e = cudaStreamCreateWithFlags(&h->stream, cudaStreamNonBlocking);
     if (e == cudaSuccess) e = cudaStreamCreateWithFlags(&h->copy_stream, cudaStreamNonBlocking);
     if (e == cudaSuccess) e = cudaEventCreateWithFlags(&h->chunk_done, cudaEventDisableTiming);
+    if (e == cudaSuccess) e = cudaEventCreate(&h->copy_t0);
+    if (e == cudaSuccess) e = cudaEventCreate(&h->copy_t1);
     const void* kernels[14] = {
         reinterpret_cast<const void*>(&bf::encoder_kernel<false, false, bf::kArI8Qkv>),
         reinterpret_cast<const void*>(&bf::encoder_kernel<true, false, bf::kArI8Qkv>),
@@ -2227,6 +2237,8 @@ int bf_destroy(bf_handle* h) {
     if (h->stream) { cudaStreamSynchronize(h->stream); cudaStreamDestroy(h->stream); }
     if (h->copy_stream) { cudaStreamSynchronize(h->copy_stream); cudaStreamDestroy(h->copy_stream); }
     if (h->chunk_done) cudaEventDestroy(h->chunk_done);
+    if (h->copy_t0) cudaEventDestroy(h->copy_t0);
+    if (h->copy_t1) cudaEventDestroy(h->copy_t1);
     cudaFree(h->blob); cudaFree(h->status); cudaFree(h->prof); cudaFree(h->d_in); cudaFree(h->d_out);
     delete h;
     return BF_OK;
@@ -2446,46 +2458,88 @@ int bf_forward_host(bf_handle* h, const uint16_t* boards, const int16_t* control
     BF_CUDA(cudaMemcpyAsync(d_control, control, static_cast<size_t>(n) * 2, cudaMemcpyHostToDevice, s));
     BF_CUDA(cudaMemcpyAsync(d_rep, rep, static_cast<size_t>(n), cudaMemcpyHostToDevice, s));
     if (legal) BF_CUDA(cudaMemcpyAsync(d_legal, legal, static_cast<size_t>(n) * 256, cudaMemcpyHostToDevice, s));
-    // The batch goes out as a few launches of shrinking size, the last one a single wave (one
-    // tile per SM), so that the copy-out of a finished launch overlaps the next launch's compute
-    // on a second stream and only the last wave's copy is exposed.  Copying a position out takes
-    // about a sixth of the time of evaluating it, so each launch may be up to six times as large
-    // as the one after it and its copy still hides; large launches keep the kernel's tile-to-tile
-    // pipelining, which separate one-wave launches lose.  (Letting the kernel store the 4.3 KB
-    // per position of logits straight into mapped host memory was measured 10 % slower: the
-    // stores back up behind the bus.)
+    // The batch goes out as a few launches so that the copy-out of a finished launch overlaps the
+    // next launch's compute on a second stream and only the last launch's copy is exposed.  Which
+    // plan is best depends on how fast this GPU reaches host memory right now, which the call
+    // measures on its own first copy and remembers for the next call (on this pool: 55 GB/s for
+    // one GPU alone, 12-19 GB/s each when eight GPUs copy at once; evaluating produces 8.8 GB/s):
+    //   fast link   a few launches of shrinking size, largest first, the last one a single wave
+    //               (one tile per SM).  Copying a position out takes about a sixth of the time of
+    //               evaluating it, so each launch may be six times the one after it and its copy
+    //               still hides; large launches keep the kernel's tile-to-tile pipelining.
+    //   slow link   equal launches of about two waves, so that every copy hides behind the next
+    //               launch as long as copying is not slower than evaluating, and the last wave
+    //               writes its logits straight into the caller's buffers when these are pinned
+    //               and device-mapped, so that nothing is left to copy at the end.  Costs about
+    //               5 % in launch granularity, which a slow link pays back several times.
+    // (Everything through mapped memory was measured 10 % slower: the stores back up behind the
+    // bus.)
     const int wave = h->sm_count * 4;
+    const bool slow_link = h->host_plan == 2 ||
+                           (h->host_plan == 0 && h->d2h_gbps > 0.0 && h->d2h_gbps < kSlowLinkGBps);
+    void* m_policy = mapped_host(policy);
+    void* m_promo = mapped_host(promo);
+    void* m_value = mapped_host(value);
+    const bool direct_last = slow_link && policy != nullptr && promo != nullptr && value != nullptr &&
+                             m_policy != nullptr && m_promo != nullptr && m_value != nullptr;
     int sizes[16];
     int n_chunks = 0;
-    {
-        int rest = n, last = wave;
-        while (rest > 0 && n_chunks < 15) {
+    if (slow_link) {
+        const int last = n < wave ? n : wave;
+        const int rest = n - last;
+        if (rest > 0) {
+            int m = (rest + 2 * wave - 1) / (2 * wave);
+            if (m > 14) m = 14;
+            const int piece = ((rest + m - 1) / m + 3) & ~3;
+            for (int left = rest; left > 0; left -= piece) sizes[n_chunks++] = left < piece ? left : piece;
+        }
+        sizes[n_chunks++] = last;
+    } else {
+        int rest = n, last = wave, tmp[16], k = 0;
+        while (rest > 0 && k < 15) {
             const int m = rest < last ? rest : last;
-            sizes[n_chunks++] = m;
+            tmp[k++] = m;
             rest -= m;
             last = last <= (1 << 24) ? last * 6 : last;
         }
-        if (rest > 0) sizes[n_chunks++] = rest;
+        if (rest > 0) tmp[k++] = rest;
+        for (int i = k - 1; i >= 0; --i) sizes[n_chunks++] = tmp[i];          // largest first
     }
     cudaStream_t c = h->copy_stream;
+    size_t timed_bytes = 0;
     int lo = 0;
-    for (int k = n_chunks - 1; k >= 0; lo += sizes[k], --k) {          // largest first
+    for (int k = 0; k < n_chunks; lo += sizes[k], ++k) {
         const int m = sizes[k];
         const size_t o = static_cast<size_t>(lo);
+        const bool direct = direct_last && k == n_chunks - 1;
         int rc = launch(h, reinterpret_cast<uint16_t*>(d_boards) + o * 32, reinterpret_cast<int16_t*>(d_control) + o,
                         d_rep + o, legal ? reinterpret_cast<uint64_t*>(d_legal) + o * 32 : nullptr, m,
-                        d_policy + o * 4096, d_promo + o * 256, reinterpret_cast<float*>(d_value) + o, nullptr,
+                        direct ? static_cast<uint8_t*>(m_policy) + o * 4096 : d_policy + o * 4096,
+                        direct ? static_cast<uint8_t*>(m_promo) + o * 256 : d_promo + o * 256,
+                        direct ? static_cast<float*>(m_value) + o : reinterpret_cast<float*>(d_value) + o, nullptr,
                         0, 0, -1, -1, nullptr, nullptr, s);
         if (rc != BF_OK) return rc;
+        if (direct) break;
         BF_CUDA(cudaEventRecord(h->chunk_done, s));
         BF_CUDA(cudaStreamWaitEvent(c, h->chunk_done, 0));
         const size_t M = static_cast<size_t>(m);
+        // the first launch's copy is the link measurement (large enough to mean something)
+        const bool timed = k == 0 && policy != nullptr && M * 4096 >= (1u << 20);
+        if (timed) BF_CUDA(cudaEventRecord(h->copy_t0, c));
         if (policy) BF_CUDA(cudaMemcpyAsync(static_cast<uint8_t*>(policy) + o * 4096, d_policy + o * 4096, M * 4096, cudaMemcpyDeviceToHost, c));
+        if (timed) { BF_CUDA(cudaEventRecord(h->copy_t1, c)); timed_bytes = M * 4096; }
         if (promo) BF_CUDA(cudaMemcpyAsync(static_cast<uint8_t*>(promo) + o * 256, d_promo + o * 256, M * 256, cudaMemcpyDeviceToHost, c));
         if (value) BF_CUDA(cudaMemcpyAsync(value + o, d_value + o * 4, M * 4, cudaMemcpyDeviceToHost, c));
     }
     BF_CUDA(cudaStreamSynchronize(s));
     BF_CUDA(cudaStreamSynchronize(c));
+    if (timed_bytes != 0) {
+        float ms = 0.f;
+        if (cudaEventElapsedTime(&ms, h->copy_t0, h->copy_t1) == cudaSuccess && ms > 0.f)
+            h->d2h_gbps = static_cast<double>(timed_bytes) / (ms * 1e-3) / 1e9;
+        else
+            cudaGetLastError();
+    }
     return BF_OK;
 }
 
@@ -2558,6 +2612,11 @@ int bf_forward_priors_host(bf_handle* h, const uint16_t* boards, const int16_t* 
 int bf_set_option(bf_handle* h, int option, int value) {
     if (h == nullptr) return fail(BF_EINVAL, "null handle");
     if (option == BF_OPT_RSQRT_RN) { h->rsqrt_rn = value != 0; return BF_OK; }
+    if (option == BF_OPT_HOST_PLAN) {
+        if (value < 0 || value > 2) return fail(BF_EINVAL, "BF_OPT_HOST_PLAN takes 0, 1 or 2");
+        h->host_plan = value;
+        return BF_OK;
+    }
     return fail(BF_EINVAL, "unknown option");
 }
 
@@ -2574,6 +2633,8 @@ int bf_status(bf_handle* h, int* status) {
 }
 
 long long bf_launch_count(const bf_handle* h) { return h ? h->launches : 0; }
+
+double bf_host_link_gbps(const bf_handle* h) { return h ? h->d2h_gbps : 0.0; }
 
 int bf_profile(bf_handle* h, int enable) {
     if (h == nullptr) return fail(BF_EINVAL, "null handle");

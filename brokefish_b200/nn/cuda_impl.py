@@ -502,6 +502,15 @@ class FusedEncoder:
         _native.check(_native.lib().bf_set_option(self._handle, 1, int(bool(on))), "bf_set_option")
         self._exact_rsqrt = bool(on)
 
+    # -- how forward_host splits a batch: by the measured host link (0), or forced (1 fast, 2 slow)
+    def set_host_plan(self, plan: int) -> None:
+        _native.check(_native.lib().bf_set_option(self._handle, 4, int(plan)), "bf_set_option")
+
+    @property
+    def host_link_gbps(self) -> float:
+        """GB/s the first device-to-host copy of the last ``forward_host`` call reached."""
+        return float(_native.lib().bf_host_link_gbps(self._handle))
+
     def check_status(self) -> None:
         """Synchronise and raise if any launch hit a device-side time-out."""
         st = ctypes.c_int(0)

@@ -238,7 +238,18 @@ int bf_forward_priors_host(bf_handle* h, const uint16_t* boards, const int16_t* 
  *                    1: correctly rounded 1/sqrt, the only form a CPU restatement can
  *                    reproduce bit for bit (the parity tests against the numpy oracle use it). */
 #define BF_OPT_RSQRT_RN 1
+/*   BF_OPT_HOST_PLAN 0 (default): `bf_forward_host` splits a batch into launches by the
+ *                    device-to-host rate its previous call measured; 1: always the fast-link
+ *                    plan (launches of shrinking size, largest first); 2: always the slow-link
+ *                    plan (equal launches of about two waves, the last wave written straight
+ *                    into the caller's buffers when they are pinned and device-mapped).  Same
+ *                    outputs either way. */
+#define BF_OPT_HOST_PLAN 4
 int bf_set_option(bf_handle* h, int option, int value);
+
+/* GB/s the first device-to-host copy of the last `bf_forward_host` call reached (0 before the
+ * first call): what the plan of the next call is chosen by.  No counterpart in the reference. */
+double bf_host_link_gbps(const bf_handle* h);
 
 /* Read (and clear) the device status word; 0 = every launch since the last call ran
  * clean.  Synchronises the device. */
