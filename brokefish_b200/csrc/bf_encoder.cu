@@ -1154,6 +1154,118 @@ __device__ __forceinline__ void prenorm_value(RowCtx& c, const Params& p, uint32
     for (int k = 0; k < 3; ++k) logit[k] = rstd * (t1[k] - mean * t2[k]) + t3[k];
 }
 
+// The head epilogue of one board: accumulators of the head product -> staged logits -> legality
+// mask, stores, fused expansion, value.
+template <bool kDbg>
+__device__ __forceinline__ void head_epilogue(RowCtx& c, const Params& p, int board, uint32_t word, int ctl,
+                                              uint32_t alive) {
+    // ---- heads: fp16 product [128 x 256] x [96 x 256]^T on the tensor pipe (tcgen05 kind::f16
+    //      with fp16 accumulators, k-steps in rising order: the bits of the reference's
+    //      fp16-accumulate mma.sync product, encoder.cu:309-352, 918-927).  Warp qt of a board
+    //      reads its rows' output columns 24 qt .. 24 qt + 23; they go through a staging tile in
+    //      the (idle) A-operand region so that each thread then finds its own row's 16 policy
+    //      columns and the expansion warp whole rows. ----
+    float pre[3] = {0.f, 0.f, 0.f};
+    if (p.vmode == 2) prenorm_value(c, p, c.valid ? alive : 0xffffffffu, pre);
+    prof_mark<kDbg>(c, PH_LN);
+    // Staging uses only this board's own rows of the A-operand slabs (another board may already
+    // be writing its rows for the next tile): policy columns 0-63 in K-slab 0 at the operand's
+    // swizzled row address, the 32 aux columns in K-slab 1.
+    const uint32_t stage_pol = c.sm_a, stage_aux = c.sm_a + 16384u;
+    // while the head product runs: the legality words, given or (for the expansion warp, lane =
+    // slot) generated here
+    unsigned long long lw = ~0ull, moves = 0ull;
+    if (p.legal != nullptr && c.valid) lw = p.legal[c.grow];
+    if (p.prior != nullptr && c.qt == 1 && c.valid) {
+        bool in_check;
+        moves = p.legal != nullptr ? lw : bfmg::legal_word(word, ctl, in_check);
+    }
+    row_wait_acc<kDbg>(c, 0, PH_LN);
+    {
+        // this thread's row, output columns 24 qt .. 24 qt + 23 (three groups of eight), one fp16
+        // in the low half of each accumulator word; packed and staged so that every thread then
+        // finds its own row's 16 policy columns and the expansion warp whole rows
+        uint32_t acc[24];
+#pragma unroll
+        for (int jj = 0; jj < 3; ++jj)
+            tmem_ld8(c.tm + TM_ACC + 24 * c.qt + 8 * jj, *reinterpret_cast<uint32_t(*)[8]>(&acc[8 * jj]));
+        row_release_acc(c, 0);                           // waits for the loads
+#pragma unroll
+        for (int jj = 0; jj < 3; ++jj) {
+            const int j = 3 * c.qt + jj;
+            const uint32_t base = j < 8 ? stage_pol : stage_aux;
+            sts128(base + sw_off(c.row, j & 7),
+                   make_uint4(__byte_perm(acc[8 * jj], acc[8 * jj + 1], 0x5410),
+                              __byte_perm(acc[8 * jj + 2], acc[8 * jj + 3], 0x5410),
+                              __byte_perm(acc[8 * jj + 4], acc[8 * jj + 5], 0x5410),
+                              __byte_perm(acc[8 * jj + 6], acc[8 * jj + 7], 0x5410)));
+        }
+    }
+    board_sync(c);                                       // the board's 32 x 96 logits are staged
+    {
+        uint32_t lgw[8], aux[4] = {0u, 0u, 0u, 0u};
+        {
+            const uint4 v0 = lds128(stage_pol + sw_off(c.row, 2 * c.qt));
+            const uint4 v1 = lds128(stage_pol + sw_off(c.row, 2 * c.qt + 1));
+            lgw[0] = v0.x; lgw[1] = v0.y; lgw[2] = v0.z; lgw[3] = v0.w;
+            lgw[4] = v1.x; lgw[5] = v1.y; lgw[6] = v1.z; lgw[7] = v1.w;
+            if (c.qt == 0) {
+                const uint4 va = lds128(stage_aux + sw_off(c.row, 0));        // columns 64..71
+                aux[0] = va.x; aux[1] = va.y; aux[2] = va.z; aux[3] = va.w;
+            }
+        }
+        uint32_t lg[8];
+        const uint32_t bits = static_cast<uint32_t>(lw >> (16 * c.qt)) & 0xffffu;
+#pragma unroll
+        for (int i = 0; i < 8; ++i) {
+            uint32_t v = lgw[i];
+            if (!((bits >> (2 * i)) & 1u)) v = (v & 0xffff0000u) | 0xfc00u;
+            if (!((bits >> (2 * i + 1)) & 1u)) v = (v & 0x0000ffffu) | 0xfc000000u;
+            lg[i] = v;
+        }
+        if (c.valid && p.policy != nullptr) store_words<8>(p.policy + c.grow * 64 + 16 * c.qt, lg);
+        if (p.prior != nullptr && c.qt == 1) {
+            expand_board(p, board, c.lane, c.valid, word, ctl, moves, stage_pol, stage_aux, c.row);
+        }
+        if (c.qt == 0) {
+            if (c.valid && p.promo != nullptr)
+                *reinterpret_cast<uint2*>(p.promo + c.grow * 4) = make_uint2(aux[0], aux[1]);
+            // value logits: the fp16 head outputs in columns 68, 69, 70
+            float a = __low2float(as_h2(aux[2])), b = __high2float(as_h2(aux[2]));
+            float d = __low2float(as_h2(aux[3]));
+            if (p.vmode == 1) {
+                // live tokens in slot order, one after the other (encoder.cu:1040-1057)
+                float ta = 0.f, tb = 0.f, td = 0.f;
+#pragma unroll 1
+                for (int tt = 0; tt < kT; ++tt) {
+                    const float at = __shfl_sync(0xffffffffu, a, tt), bt = __shfl_sync(0xffffffffu, b, tt);
+                    const float dt = __shfl_sync(0xffffffffu, d, tt);
+                    if ((alive >> tt) & 1u) { ta += at; tb += bt; td += dt; }
+                }
+                a = ta; b = tb; d = td;
+                const int nlive = __popc(alive);
+                const float inv = 1.0f / static_cast<float>(nlive > 0 ? nlive : 1);
+                a *= inv; b *= inv; d *= inv;
+            }
+            if (p.vmode == 2) { a = pre[0]; b = pre[1]; d = pre[2]; }
+            const bool writer = p.vmode != 0 ? c.lane == 0 : c.lane == (ctl < 0 ? 31 : 15);
+            if (writer && c.valid && p.value != nullptr) {
+                float v;
+                if (p.n_value == 1) {
+                    v = tanhf(a);
+                } else {
+                    const float m = fmaxf(a, fmaxf(b, d));
+                    const float ea = expf(a - m), eb = expf(b - m), ec = expf(d - m);
+                    v = (ec - ea) / (ea + eb + ec);
+                }
+                if (p.vmode != 0 && ctl < 0) v = -v;
+                p.value[board] = v;
+            }
+        }
+    }
+    prof_mark<kDbg>(c, PH_HEAD);
+}
+
 template <bool kDbg, bool kRJ, int kAr>
 __device__ __forceinline__ void row_warps_tile(RowCtx& c, const Params& p, int tile) {
     const int item = tile * 4 + c.q;
@@ -1263,112 +1375,12 @@ __device__ __forceinline__ void row_warps_tile(RowCtx& c, const Params& p, int t
         else      ffn_block<kDbg, kAr>(c, p, lp, sa, cap);
     }
 
-    // ---- heads: fp16 product [128 x 256] x [96 x 256]^T on the tensor pipe (tcgen05 kind::f16
-    //      with fp16 accumulators, k-steps in rising order: the bits of the reference's
-    //      fp16-accumulate mma.sync product, encoder.cu:309-352, 918-927).  Warp qt of a board
-    //      reads its rows' output columns 24 qt .. 24 qt + 23; they go through a staging tile in
-    //      the (idle) A-operand region so that each thread then finds its own row's 16 policy
-    //      columns and the expansion warp whole rows. ----
-    float pre[3] = {0.f, 0.f, 0.f};
-    if (p.vmode == 2) prenorm_value(c, p, c.valid ? alive : 0xffffffffu, pre);
-    prof_mark<kDbg>(c, PH_LN);
-    // Staging uses only this board's own rows of the A-operand slabs (another board may already
-    // be writing its rows for the next tile): policy columns 0-63 in K-slab 0 at the operand's
-    // swizzled row address, the 32 aux columns in K-slab 1.
-    const uint32_t stage_pol = c.sm_a, stage_aux = c.sm_a + 16384u;
-    // while the head product runs: the legality words, given or (for the expansion warp, lane =
-    // slot) generated here
-    unsigned long long lw = ~0ull, moves = 0ull;
-    if (p.legal != nullptr && c.valid) lw = p.legal[c.grow];
-    if (p.prior != nullptr && c.qt == 1 && c.valid) {
-        bool in_check;
-        moves = p.legal != nullptr ? lw : bfmg::legal_word(word, ctl, in_check);
-    }
-    row_wait_acc<kDbg>(c, 0, PH_LN);
-    {
-        // this thread's row, output columns 24 qt .. 24 qt + 23 (three groups of eight), one fp16
-        // in the low half of each accumulator word; packed and staged so that every thread then
-        // finds its own row's 16 policy columns and the expansion warp whole rows
-        uint32_t acc[24];
-#pragma unroll
-        for (int jj = 0; jj < 3; ++jj)
-            tmem_ld8(c.tm + TM_ACC + 24 * c.qt + 8 * jj, *reinterpret_cast<uint32_t(*)[8]>(&acc[8 * jj]));
-        row_release_acc(c, 0);                           // waits for the loads
-#pragma unroll
-        for (int jj = 0; jj < 3; ++jj) {
-            const int j = 3 * c.qt + jj;
-            const uint32_t base = j < 8 ? stage_pol : stage_aux;
-            sts128(base + sw_off(c.row, j & 7),
-                   make_uint4(__byte_perm(acc[8 * jj], acc[8 * jj + 1], 0x5410),
-                              __byte_perm(acc[8 * jj + 2], acc[8 * jj + 3], 0x5410),
-                              __byte_perm(acc[8 * jj + 4], acc[8 * jj + 5], 0x5410),
-                              __byte_perm(acc[8 * jj + 6], acc[8 * jj + 7], 0x5410)));
-        }
-    }
-    board_sync(c);                                       // the board's 32 x 96 logits are staged
-    {
-        uint32_t lgw[8], aux[4] = {0u, 0u, 0u, 0u};
-        {
-            const uint4 v0 = lds128(stage_pol + sw_off(c.row, 2 * c.qt));
-            const uint4 v1 = lds128(stage_pol + sw_off(c.row, 2 * c.qt + 1));
-            lgw[0] = v0.x; lgw[1] = v0.y; lgw[2] = v0.z; lgw[3] = v0.w;
-            lgw[4] = v1.x; lgw[5] = v1.y; lgw[6] = v1.z; lgw[7] = v1.w;
-            if (c.qt == 0) {
-                const uint4 va = lds128(stage_aux + sw_off(c.row, 0));        // columns 64..71
-                aux[0] = va.x; aux[1] = va.y; aux[2] = va.z; aux[3] = va.w;
-            }
-        }
-        uint32_t lg[8];
-        const uint32_t bits = static_cast<uint32_t>(lw >> (16 * c.qt)) & 0xffffu;
-#pragma unroll
-        for (int i = 0; i < 8; ++i) {
-            uint32_t v = lgw[i];
-            if (!((bits >> (2 * i)) & 1u)) v = (v & 0xffff0000u) | 0xfc00u;
-            if (!((bits >> (2 * i + 1)) & 1u)) v = (v & 0x0000ffffu) | 0xfc000000u;
-            lg[i] = v;
-        }
-        if (c.valid && p.policy != nullptr) store_words<8>(p.policy + c.grow * 64 + 16 * c.qt, lg);
-        if (p.prior != nullptr && c.qt == 1) {
-            expand_board(p, board, c.lane, c.valid, word, ctl, moves, stage_pol, stage_aux, c.row);
-        }
-        if (c.qt == 0) {
-            if (c.valid && p.promo != nullptr)
-                *reinterpret_cast<uint2*>(p.promo + c.grow * 4) = make_uint2(aux[0], aux[1]);
-            // value logits: the fp16 head outputs in columns 68, 69, 70
-            float a = __low2float(as_h2(aux[2])), b = __high2float(as_h2(aux[2]));
-            float d = __low2float(as_h2(aux[3]));
-            if (p.vmode == 1) {
-                // live tokens in slot order, one after the other (encoder.cu:1040-1057)
-                float ta = 0.f, tb = 0.f, td = 0.f;
-#pragma unroll 1
-                for (int tt = 0; tt < kT; ++tt) {
-                    const float at = __shfl_sync(0xffffffffu, a, tt), bt = __shfl_sync(0xffffffffu, b, tt);
-                    const float dt = __shfl_sync(0xffffffffu, d, tt);
-                    if ((alive >> tt) & 1u) { ta += at; tb += bt; td += dt; }
-                }
-                a = ta; b = tb; d = td;
-                const int nlive = __popc(alive);
-                const float inv = 1.0f / static_cast<float>(nlive > 0 ? nlive : 1);
-                a *= inv; b *= inv; d *= inv;
-            }
-            if (p.vmode == 2) { a = pre[0]; b = pre[1]; d = pre[2]; }
-            const bool writer = p.vmode != 0 ? c.lane == 0 : c.lane == (ctl < 0 ? 31 : 15);
-            if (writer && c.valid && p.value != nullptr) {
-                float v;
-                if (p.n_value == 1) {
-                    v = tanhf(a);
-                } else {
-                    const float m = fmaxf(a, fmaxf(b, d));
-                    const float ea = expf(a - m), eb = expf(b - m), ec = expf(d - m);
-                    v = (ec - ea) / (ea + eb + ec);
-                }
-                if (p.vmode != 0 && ctl < 0) v = -v;
-                p.value[board] = v;
-            }
-        }
-    }
-    prof_mark<kDbg>(c, PH_HEAD);
+    head_epilogue<kDbg>(c, p, board, word, ctl, alive);
 }
+
+}  // namespace bf
+#include "bf_encoder_one.cuh"
+namespace bf {
 
 // ------------------------------------------------------------------------------------------
 // Producer: streams the packed weight stage images through the ring.
@@ -1599,7 +1611,9 @@ __device__ __forceinline__ void mma_loop(uint32_t smem, uint32_t tmem, volatile 
 }
 
 // ------------------------------------------------------------------------------------------
-template <bool kDbg, bool kRJ, int kAr>
+// `kOne`: the small-batch form, one board per tile with its rows replicated in the four lane
+// quadrants (bf_encoder_one.cuh); plain int8 evaluation only.
+template <bool kDbg, bool kRJ, int kAr, bool kOne = false>
 __global__ void __launch_bounds__(kThreads, 1) encoder_kernel(const Params p) {
     extern __shared__ uint8_t smem_raw[];
     uint8_t* sm = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
@@ -1630,7 +1644,7 @@ __global__ void __launch_bounds__(kThreads, 1) encoder_kernel(const Params p) {
     // (clamped to the capacity the grid was sized for); every role reads the same word
     int n_eval = p.n;
     if (p.leaf_count != nullptr) n_eval = min(max(__ldg(p.leaf_count), 0), p.n);
-    const int n_tiles = (n_eval + 3) / 4;
+    const int n_tiles = kOne ? n_eval : (n_eval + 3) / 4;
     if (warp < kRowWarps) {
         RowCtx c;
         c.n = n_eval;
@@ -1642,7 +1656,14 @@ __global__ void __launch_bounds__(kThreads, 1) encoder_kernel(const Params p) {
         c.one2 = pk2(p.one, p.one);
         c.prof_on = kDbg && p.prof != nullptr && threadIdx.x == 0;
         c.t_last = c.prof_on ? clock64() : 0;
-        for (int tile = blockIdx.x; tile < n_tiles; tile += gridDim.x) row_warps_tile<kDbg, kRJ, kAr>(c, p, tile);
+        for (int tile = blockIdx.x; tile < n_tiles; tile += gridDim.x) {
+            if constexpr (kOne)
+                one::row_warps_tile(c, p, tile, [&](RowCtx& cc, int board, uint32_t word, int ctl, uint32_t alive) {
+                    head_epilogue<false>(cc, p, board, word, ctl, alive);
+                });
+            else
+                row_warps_tile<kDbg, kRJ, kAr>(c, p, tile);
+        }
     } else if (warp == kProducerWarp) {
         if (lane == 0) producer_loop<kAr>(smem, abort_flag, p, blockIdx.x, gridDim.x, n_tiles);
     } else {
@@ -2036,6 +2057,7 @@ struct bf_handle {
     cudaEvent_t copy_t0 = nullptr, copy_t1 = nullptr;   // around the first copy-out of bf_forward_host
     double d2h_gbps = 0.0;        // what that copy last measured; 0 = not measured yet
     int host_plan = 0;            // BF_OPT_HOST_PLAN: 0 by the measured link, 1 fast-link plan, 2 slow-link plan
+    int one_board_factor = 1;     // BF_OPT_ONE_BOARD: batches up to this many boards per SM use the one-board form
 };
 
 namespace {
@@ -2141,7 +2163,13 @@ int launch(bf_handle* h, const uint16_t* boards, const int16_t* control, const u
         if (dbg) bf::encoder_kernel<true, true, bf::kArInt8><<<grid, bf::kThreads, bf::kSmemRequest, stream>>>(p);
         else     bf::encoder_kernel<false, true, bf::kArInt8><<<grid, bf::kThreads, bf::kSmemRequest, stream>>>(p);
     } else {
+        // a batch that leaves SMs idle (at most one board per SM) runs in the one-board-per-tile
+        // form: sixteen row warps per board instead of four, about half the latency, same bits
+        const bool one = !dbg && bb == nullptr && p.vmode != 2 && n <= h->sm_count * h->one_board_factor;
         if (dbg) bf::encoder_kernel<true, false, bf::kArInt8><<<grid, bf::kThreads, bf::kSmemRequest, stream>>>(p);
+        else if (one)
+            bf::encoder_kernel<false, false, bf::kArInt8, true><<<n < h->sm_count ? n : h->sm_count, bf::kThreads,
+                                                                  bf::kSmemRequest, stream>>>(p);
         else     bf::encoder_kernel<false, false, bf::kArInt8><<<grid, bf::kThreads, bf::kSmemRequest, stream>>>(p);
     }
     BF_CUDA(cudaGetLastError());
@@ -2223,6 +2251,9 @@ int bf_create(const void* blob, size_t blob_bytes, int device, bf_handle** out) 
         reinterpret_cast<const void*>(&bf::encoder_kernel<true, false, bf::kArF16>)};
     for (int i = 0; i < 14 && e == cudaSuccess; ++i)
         e = cudaFuncSetAttribute(kernels[i], cudaFuncAttributeMaxDynamicSharedMemorySize, bf::kSmemRequest);
+    if (e == cudaSuccess)
+        e = cudaFuncSetAttribute(bf::encoder_kernel<false, false, bf::kArInt8, true>,
+                                 cudaFuncAttributeMaxDynamicSharedMemorySize, bf::kSmemRequest);
     if (e != cudaSuccess) {
         bf_destroy(h);
         return fail(BF_ECUDA, std::string("bf_create: ") + cudaGetErrorString(e));
@@ -2612,6 +2643,11 @@ int bf_forward_priors_host(bf_handle* h, const uint16_t* boards, const int16_t* 
 int bf_set_option(bf_handle* h, int option, int value) {
     if (h == nullptr) return fail(BF_EINVAL, "null handle");
     if (option == BF_OPT_RSQRT_RN) { h->rsqrt_rn = value != 0; return BF_OK; }
+    if (option == BF_OPT_ONE_BOARD) {
+        if (value < 0 || value > 8) return fail(BF_EINVAL, "BF_OPT_ONE_BOARD takes 0..8");
+        h->one_board_factor = value;
+        return BF_OK;
+    }
     if (option == BF_OPT_HOST_PLAN) {
         if (value < 0 || value > 2) return fail(BF_EINVAL, "BF_OPT_HOST_PLAN takes 0, 1 or 2");
         h->host_plan = value;

@@ -502,6 +502,11 @@ class FusedEncoder:
         _native.check(_native.lib().bf_set_option(self._handle, 1, int(bool(on))), "bf_set_option")
         self._exact_rsqrt = bool(on)
 
+    def set_one_board(self, boards_per_sm: int) -> None:
+        """Batches of at most this many boards per SM run in the small-batch form of the int8
+        kernel (one board per tile, sixteen row warps per board); 0 switches it off."""
+        _native.check(_native.lib().bf_set_option(self._handle, 5, int(boards_per_sm)), "bf_set_option")
+
     # -- how forward_host splits a batch: by the measured host link (0), or forced (1 fast, 2 slow)
     def set_host_plan(self, plan: int) -> None:
         _native.check(_native.lib().bf_set_option(self._handle, 4, int(plan)), "bf_set_option")

@@ -245,6 +245,11 @@ int bf_forward_priors_host(bf_handle* h, const uint16_t* boards, const int16_t* 
  *                    into the caller's buffers when they are pinned and device-mapped).  Same
  *                    outputs either way. */
 #define BF_OPT_HOST_PLAN 4
+/*   BF_OPT_ONE_BOARD k (default 1): an int8 evaluation of at most k boards per SM runs in the
+ *                    small-batch form of the kernel -- one board per tile, its rows replicated in
+ *                    the four lane quadrants, sixteen row warps per board instead of four, about
+ *                    half the latency of a tile; 0 switches the form off.  Same outputs. */
+#define BF_OPT_ONE_BOARD 5
 int bf_set_option(bf_handle* h, int option, int value);
 
 /* GB/s the first device-to-host copy of the last `bf_forward_host` call reached (0 before the

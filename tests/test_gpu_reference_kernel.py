@@ -283,6 +283,47 @@ def test_e4m3_arm_against_the_reference_e4m3_kernel(name, pos256):
     enc.close()
 
 
+@pytest.mark.parametrize("name", ["A", "V_int8_wdl"])
+def test_small_batches_in_the_one_board_form_keep_the_bits(name, pos256):
+    """A batch of at most one board per SM runs in the small-batch form of the kernel (one board
+    per tile, replicated in the four lane quadrants, sixteen row warps per board).  Its policy,
+    promotion logits and values equal the four-board form's and the reference kernel's bit for
+    bit, for the king-row scalar head and for the pooled win/draw/loss head, at one position, at
+    odd counts and at the largest count that still takes the form; the fused expansion and the
+    leaf list go through it too."""
+    kw = SETS["A"] if name == "A" else dict(seed=3, std=0.02, perturb_norms=True, n_value=3, value_head="pooled")
+    ref_name = "A_int8" if name == "A" else name
+    assert R.available(ref_name)
+    enc, ref = product(kw), R.RefKernel(ref_name)
+    sms = torch.cuda.get_device_properties(0).multi_processor_count
+    for n in (1, 3, 37, sms - 1, sms):
+        sl = slice(11, 11 + n)
+        enc.set_one_board(1)
+        mine = [t.clone() for t in enc.forward_full(*inputs(pos256, sl))]
+        enc.check_status()
+        enc.set_one_board(0)
+        four = [t.clone() for t in enc.forward_full(*inputs(pos256, sl))]
+        theirs = [t.clone() for t in ref.forward_full(*inputs(pos256, sl))]
+        torch.cuda.synchronize()
+        for a, b, c in zip(mine, four, theirs):
+            assert same_bits(a.cpu().numpy(), b.cpu().numpy()), n
+        assert same_bits(mine[0].cpu().numpy(), theirs[0].cpu().numpy()) and same_bits(mine[1].cpu().numpy(), theirs[1].cpu().numpy())
+        assert np.abs(mine[2].cpu().numpy() - theirs[2].cpu().numpy()).max() <= 1e-6
+    # fused expansion and masked policy through the small-batch form
+    n = 50
+    sl = slice(0, n)
+    legal = torch.from_numpy(pos256["legal"][sl].view(np.int64).copy()).cuda()
+    got = {}
+    for form in (1, 0):
+        enc.set_one_board(form)
+        pri, mov, ne, val = (t.clone() for t in enc.forward_priors(*inputs(pos256, sl), legal, 96, logits=True))
+        got[form] = (pri, mov, ne, val, enc.policy_out.clone())
+    for a, b in zip(got[1], got[0]):
+        assert torch.equal(a.view(torch.uint8) if a.dtype is torch.half else a, b.view(torch.uint8) if b.dtype is torch.half else b)
+    enc.set_one_board(1)
+    enc.close()
+
+
 def test_fp16_arithmetic_is_bit_identical_to_the_reference_kernel(pos256, pos4096):
     """`FusedEncoder(net, int8=False)`: the reference's default arithmetic, every weight GEMM fp16
     x fp16.  tcgen05 `kind::f16` with fp16 accumulators carries the bits of the reference's
