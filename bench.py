@@ -403,6 +403,8 @@ def main() -> int:
     ap.add_argument("--scheme", default="all", choices=["all", "ffn", "ffn+qkv"],
                     help="which matmuls run in int8: all four (the shipped scheme, the metric's), the FFN only, "
                          "or the FFN and QKV (the reference's partial schemes)")
+    ap.add_argument("--host-plan", type=int, default=0,
+                    help="how the end-to-end host call splits a batch (BF_OPT_HOST_PLAN; 0 = its own choice)")
     ap.add_argument("--fp8", action="store_true",
                     help="time the e4m3-FFN arithmetic instead of int8 (a separate line; not the headline)")
     args = ap.parse_args()
@@ -451,6 +453,8 @@ def main() -> int:
         net.load_state_dict(seeded_state(seed=0, std=0.02))
     ev = ShardedEvaluator(net, rank, world, local, fp8=args.fp8, int8=not args.f16, int8_scheme=args.scheme)   # one broadcast of the packed blob
     enc = ev.encoder
+    if args.host_plan:
+        enc.set_host_plan(args.host_plan)
 
     if args.sweep:
         if rank == 0:

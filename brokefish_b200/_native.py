@@ -18,8 +18,9 @@ ROOT = os.path.dirname(PKG_DIR)
 #: The in-tree library; ``BROKEFISH_B200_LIB`` points the loader at another build of it.
 LIB_PATH = os.environ.get("BROKEFISH_B200_LIB") or os.path.join(PKG_DIR, "libbrokefish_b200.so")
 SOURCES = [os.path.join(PKG_DIR, "csrc", "bf_encoder.cu")]
-DEPS = SOURCES + [os.path.join(PKG_DIR, "csrc", "bf_ptx.cuh"), os.path.join(PKG_DIR, "csrc", "bf_movegen.cuh"),
-                  os.path.join(ROOT, "include", "brokefish_b200.h")]
+DEPS = SOURCES + [os.path.join(PKG_DIR, "csrc", name) for name in
+                  ("bf_ptx.cuh", "bf_movegen.cuh", "bf_encoder_one.cuh")] + [
+                      os.path.join(ROOT, "include", "brokefish_b200.h")]
 NVCC_FLAGS = ["-gencode", "arch=compute_100a,code=sm_100a", "-O3", "-lineinfo", "-std=c++17",
               "-Xcompiler", "-fPIC", "-shared", "-diag-suppress", "177,550"]
 

@@ -1494,6 +1494,23 @@ __device__ __forceinline__ void mma_wait_operand(uint32_t smem, volatile int* ab
     tc_fence_after();
 }
 
+// Step over `n_stages` weight stages that the other issuer consumes: wait for each one's arrival
+// and release it as a consumer would.  A slot is refilled when both issuers have released it, so
+// both see every filling of every slot in order and neither can fall a phase behind on the ring's
+// barriers or run a phase ahead (a parity wait tells only the current phase from the one before,
+// and two bulk copies need not complete in the order they were issued).
+template <int kAr>
+__device__ __forceinline__ void mma_pass_over(uint32_t smem, volatile int* abort_flag, MmaState& st, int n_stages) {
+    using C = Cfg<kAr>;
+#pragma unroll 1
+    for (int i = 0; i < n_stages; ++i) {
+        const uint32_t k = st.rc % C::kRSlots;
+        mbar_wait(bar_addr(smem, B_WR_FULL + k), (st.rc / C::kRSlots) & 1u, abort_flag, kErrMmaWeights);
+        mbar_arrive(bar_addr(smem, B_WR_EMPTY + k));
+        st.rc++;
+    }
+}
+
 // Two threads (lane 0 of two warps) share the schedule: issuing one unit costs a thread well
 // over twice the unit's time on the tensor pipe (barrier waits, descriptors, a full MMA queue),
 // and the units of a step come in pairs -- the two 128-wide halves of an out-projection, of a
@@ -1501,14 +1518,14 @@ __device__ __forceinline__ void mma_wait_operand(uint32_t smem, volatile int* ab
 // half-`who` unit of every pair (its accumulator slot is slot `who`) and steps over the other
 // half's weight stages; the QKV units, which follow one another on one accumulator, and the head
 // product are issuer 0's.  Both issuers wait for every phase of the operand barriers in order,
-// needed or not, because a parity wait must not fall a phase behind.  The fp16 arithmetic's FFN
-// (one running pair of ff2 accumulators) keeps a single issuer.
+// needed or not, because a parity wait must not fall a phase behind; for the same reason the
+// other half's weight stages are passed over one by one (mma_pass_over).  In the fp16 arithmetic's
+// FFN (ff1 units on slot 0, one running pair of ff2 accumulators) issuer 0 takes the ff1 units
+// and issuer 1 the ff2 units; only issuer 1 waits on the hidden-chunk barrier there.
 template <int kAr>
 __device__ __forceinline__ void mma_loop(uint32_t smem, uint32_t tmem, volatile int* abort_flag,
                                       const Params& p, int first_tile, int tile_step, int n_tiles, int who) {
     using C = Cfg<kAr>;
-    constexpr bool kTwo = kAr != kArF16;
-    if (!kTwo && who != 0) return;
     MmaState st = {0, 0, {0, 0}, 0, {0, 0}};
     // int8: every weight GEMM is s8/u8 x s8.  e4m3: QKV and out-projection are fp16 x fp16 with
     // fp16 accumulators (the bits of the reference's mma.sync), the FFN is e4m3 x e4m3 with fp32
@@ -1534,10 +1551,10 @@ __device__ __forceinline__ void mma_loop(uint32_t smem, uint32_t tmem, volatile 
                 for (int j = 0; j < 4; ++j)
                     mma_unit<kAr>(smem, abort_flag, st, acc0, 0, sm_a, true, C::kQkvSlabs, kI_QKV, kQkvKind);
             mma_wait_operand(smem, abort_flag, B_A_READY, st.aready);          // attention output
-            if (!kTwo || who == 0) mma_unit<kAr>(smem, abort_flag, st, acc0, 0, sm_a, false, C::kOutSlabs, kI_OUT, kOutKind);
-            else                   st.rc += C::kOutSlabs;
-            if (!kTwo || who == 1) mma_unit<kAr>(smem, abort_flag, st, acc1, 1, sm_a, false, C::kOutSlabs, kI_OUT, kOutKind);
-            else                   st.rc += C::kOutSlabs;
+            if (who == 0) mma_unit<kAr>(smem, abort_flag, st, acc0, 0, sm_a, false, C::kOutSlabs, kI_OUT, kOutKind);
+            else                   mma_pass_over<kAr>(smem, abort_flag, st, C::kOutSlabs);
+            if (who == 1) mma_unit<kAr>(smem, abort_flag, st, acc1, 1, sm_a, false, C::kOutSlabs, kI_OUT, kOutKind);
+            else                   mma_pass_over<kAr>(smem, abort_flag, st, C::kOutSlabs);
             mma_wait_operand(smem, abort_flag, B_A_READY, st.aready);          // LN2 output
             if constexpr (kAr == kArF16) {
                 // fp16 FFN: ff1 units go into slot 0; once the rows have written a hidden chunk,
@@ -1548,11 +1565,23 @@ __device__ __forceinline__ void mma_loop(uint32_t smem, uint32_t tmem, volatile 
                 // issue order (= the packed weight order): F1 c0 j0, F1 c0 j1, then per chunk c:
                 // F1 c+1 j0 (so that it runs under the rows' epilogue of F1 c j1), F2 c j0, F2 c j1,
                 // F1 c+1 j1
-                mma_unit<kAr>(smem, abort_flag, st, acc0, 0, sm_a, false, 4, kI_FF1, kKindF16);
-                mma_unit<kAr>(smem, abort_flag, st, acc0, 0, sm_a, false, 4, kI_FF1, kKindF16);
+                // issuer 0 takes the ff1 units (slot 0), issuer 1 the ff2 units; each steps over
+                // the other's weight stages
+                auto pass_over = [&](int n_stages) { mma_pass_over<kAr>(smem, abort_flag, st, n_stages); };
+                if (who == 0) {
+                    mma_unit<kAr>(smem, abort_flag, st, acc0, 0, sm_a, false, 4, kI_FF1, kKindF16);
+                    mma_unit<kAr>(smem, abort_flag, st, acc0, 0, sm_a, false, 4, kI_FF1, kKindF16);
+#pragma unroll 1
+                    for (int ch = 0; ch < 4; ++ch) {
+                        if (ch < 3) mma_unit<kAr>(smem, abort_flag, st, acc0, 0, sm_a, false, 4, kI_FF1, kKindF16);
+                        pass_over(8);
+                        if (ch < 3) mma_unit<kAr>(smem, abort_flag, st, acc0, 0, sm_a, false, 4, kI_FF1, kKindF16);
+                    }
+                } else {
+                pass_over(8);
 #pragma unroll 1
                 for (int ch = 0; ch < 4; ++ch) {
-                    if (ch < 3) mma_unit<kAr>(smem, abort_flag, st, acc0, 0, sm_a, false, 4, kI_FF1, kKindF16);
+                    if (ch < 3) pass_over(4);
                     mma_wait_operand(smem, abort_flag, B_A2_READY, st.a2n[0]);
                     if (ch == 0) {
                         mbar_wait(bar_addr(smem, B_ACC_EMPTY + 1), (st.accn[1] - 1u) & 1u, abort_flag, kErrMmaAcc);
@@ -1576,16 +1605,17 @@ __device__ __forceinline__ void mma_loop(uint32_t smem, uint32_t tmem, volatile 
                         }
                     }
                     tc_commit(bar_addr(smem, B_ACC_FULL + 1));
-                    if (ch < 3) mma_unit<kAr>(smem, abort_flag, st, acc0, 0, sm_a, false, 4, kI_FF1, kKindF16);
+                    if (ch < 3) pass_over(4);
                 }
                 st.accn[1]++;
+                }
             } else {
             // FFN units in the order the weight stream was packed (pack.py: FFN_UNITS)
 #pragma unroll 1
             for (int u = 0; u < 16; ++u) {
                 // kind/chunk of unit u: pairs (u>>1): F1 0, F1 1, F2 0, F1 2, F2 1, F1 3, F2 2, F2 3
                 const int pr = u >> 1, jh = u & 1;
-                if (jh != who) { st.rc += 2; continue; }                  // the other issuer's unit
+                if (jh != who) { mma_pass_over<kAr>(smem, abort_flag, st, 2); continue; }   // the other issuer's unit
                 const int kind2 = (0xD4 >> pr) & 1;                       // 0b11010100
                 const int ch = kind2 ? ((0x32010000u >> (4 * pr)) & 0xF) : ((0x00302010u >> (4 * pr)) & 0xF);
                 if (kind2) {
@@ -1606,7 +1636,7 @@ __device__ __forceinline__ void mma_loop(uint32_t smem, uint32_t tmem, volatile 
             mma_unit<kAr>(smem, abort_flag, st, acc0, 0, sm_r, false, kHeadStages,
                           umma_idesc(kAccF16, kFmtF16, kFmtF16, 128, 96), kKindF16);
         else
-            st.rc += kHeadStages;
+            mma_pass_over<kAr>(smem, abort_flag, st, kHeadStages);
     }
 }
 
@@ -1625,7 +1655,9 @@ __global__ void __launch_bounds__(kThreads, 1) encoder_kernel(const Params p) {
     if (threadIdx.x == 0) {
         for (int i = 0; i < B_COUNT; ++i) {
             const bool many = (i >= B_ACC_EMPTY && i < B_ACC_EMPTY + 2) || i >= B_A_READY;
-            mbar_init(bar_addr(smem, i), many ? kRowWarps : 1);
+            // a slot of the 16 KB weight ring is released by both MMA issuers
+            const bool both = i >= B_WR_EMPTY && i < B_WR_EMPTY + 7;
+            mbar_init(bar_addr(smem, i), many ? kRowWarps : (both ? 2 : 1));
         }
         *abort_flag = 0;
         for (int i = 0; i < 16; ++i) reinterpret_cast<long long*>(sm + SM_PROF)[i] = 0;
@@ -2056,7 +2088,7 @@ struct bf_handle {
     cudaEvent_t chunk_done = nullptr;
     cudaEvent_t copy_t0 = nullptr, copy_t1 = nullptr;   // around the first copy-out of bf_forward_host
     double d2h_gbps = 0.0;        // what that copy last measured; 0 = not measured yet
-    int host_plan = 0;            // BF_OPT_HOST_PLAN: 0 by the measured link, 1 fast-link plan, 2 slow-link plan
+    int host_plan = 0;            // BF_OPT_HOST_PLAN: 0 by the measured link, 1 fast-link sizes, 2 equal launches
     int one_board_factor = 1;     // BF_OPT_ONE_BOARD: batches up to this many boards per SM use the one-board form
 };
 
@@ -2082,10 +2114,10 @@ void* mapped_host(const void* p) {
     return a.type == cudaMemoryTypeHost ? a.devicePointer : nullptr;
 }
 
-// Below this measured device-to-host rate bf_forward_host switches to its slow-link plan: the
-// point where the copy of a 3504-position launch stops hiding behind the last wave by more than
-// the slow-link plan's own cost.
-constexpr double kSlowLinkGBps = 37.0;
+// bf_forward_host sizes its launches by how many times faster this GPU copies a position's logits
+// to the host than it evaluates a position.
+constexpr double kEvalGBps = 8.8;        // logits a B200 produces per second at full rate (4356 B x 2.03 M)
+constexpr double kFastLinkRatio = 6.0;   // a GPU alone on its link: 55 GB/s against those 8.8
 
 struct PriorOut {
     void* prior;
@@ -2493,26 +2525,43 @@ int bf_forward_host(bf_handle* h, const uint16_t* boards, const int16_t* control
     // next launch's compute on a second stream and only the last launch's copy is exposed.  Which
     // plan is best depends on how fast this GPU reaches host memory right now, which the call
     // measures on its own first copy and remembers for the next call (on this pool: 55 GB/s for
-    // one GPU alone, 12-19 GB/s each when eight GPUs copy at once; evaluating produces 8.8 GB/s):
-    //   fast link   a few launches of shrinking size, largest first, the last one a single wave
-    //               (one tile per SM).  Copying a position out takes about a sixth of the time of
-    //               evaluating it, so each launch may be six times the one after it and its copy
-    //               still hides; large launches keep the kernel's tile-to-tile pipelining.
-    //   slow link   equal launches of about two waves, so that every copy hides behind the next
+    // one GPU alone, 12-19 GB/s each when eight GPUs copy at once; evaluating produces 8.8 GB/s).
+    // With r = copy rate / evaluation rate:
+    //   r >= 1.5    launches of shrinking size, largest first, the last one a single wave (one
+    //               tile per SM), each launch r times the one after it (in whole waves, rounded
+    //               down) so that its copy hides behind the next launch; r is capped at 6, a GPU
+    //               alone on its link: [3504, 592] positions for a batch of 4096.  Large launches
+    //               keep the kernel's tile-to-tile pipelining.
+    //   r < 1.5     equal launches of about two waves, so that every copy hides behind the next
     //               launch as long as copying is not slower than evaluating, and the last wave
     //               writes its logits straight into the caller's buffers when these are pinned
-    //               and device-mapped, so that nothing is left to copy at the end.  Costs about
-    //               5 % in launch granularity, which a slow link pays back several times.
-    // (Everything through mapped memory was measured 10 % slower: the stores back up behind the
-    // bus.)
+    //               and device-mapped: the link is the bottleneck then, and stores that cross it
+    //               while the wave computes beat a copy that starts when the wave has ended.
+    // (Everything through mapped memory was measured 10 % slower on a fast link -- the stores back
+    // up behind the bus -- and the last wave alone 4 % slower than copying it.)
     const int wave = h->sm_count * 4;
-    const bool slow_link = h->host_plan == 2 ||
-                           (h->host_plan == 0 && h->d2h_gbps > 0.0 && h->d2h_gbps < kSlowLinkGBps);
     void* m_policy = mapped_host(policy);
     void* m_promo = mapped_host(promo);
     void* m_value = mapped_host(value);
-    const bool direct_last = slow_link && policy != nullptr && promo != nullptr && value != nullptr &&
-                             m_policy != nullptr && m_promo != nullptr && m_value != nullptr;
+    const bool all_mapped = policy != nullptr && promo != nullptr && value != nullptr &&
+                            m_policy != nullptr && m_promo != nullptr && m_value != nullptr;
+    cudaStream_t c = h->copy_stream;
+    size_t timed_bytes = 0;
+    auto copy_out = [&](int lo, int m, bool timed) -> int {
+        const size_t o = static_cast<size_t>(lo), M = static_cast<size_t>(m);
+        if (timed) BF_CUDA(cudaEventRecord(h->copy_t0, c));
+        if (policy) BF_CUDA(cudaMemcpyAsync(static_cast<uint8_t*>(policy) + o * 4096, d_policy + o * 4096, M * 4096, cudaMemcpyDeviceToHost, c));
+        if (timed) { BF_CUDA(cudaEventRecord(h->copy_t1, c)); timed_bytes = M * 4096; }
+        if (promo) BF_CUDA(cudaMemcpyAsync(static_cast<uint8_t*>(promo) + o * 256, d_promo + o * 256, M * 256, cudaMemcpyDeviceToHost, c));
+        if (value) BF_CUDA(cudaMemcpyAsync(value + o, d_value + o * 4, M * 4, cudaMemcpyDeviceToHost, c));
+        return BF_OK;
+    };
+    // how many times faster this GPU copies a position out than it evaluates one
+    double ratio = kFastLinkRatio;
+    if (h->host_plan == 0 && h->d2h_gbps > 0.0) ratio = h->d2h_gbps / kEvalGBps;
+    if (ratio > kFastLinkRatio) ratio = kFastLinkRatio;
+    const bool slow_link = h->host_plan == 2 || ratio < 1.5;
+    const bool direct_last = slow_link && all_mapped;
     int sizes[16];
     int n_chunks = 0;
     if (slow_link) {
@@ -2526,18 +2575,18 @@ int bf_forward_host(bf_handle* h, const uint16_t* boards, const int16_t* control
         }
         sizes[n_chunks++] = last;
     } else {
-        int rest = n, last = wave, tmp[16], k = 0;
+        int rest = n, tmp[16], k = 0;
+        double want = wave;
         while (rest > 0 && k < 15) {
-            const int m = rest < last ? rest : last;
+            int m = static_cast<int>(want / wave) * wave;      // whole waves, rounded down: the margin
+            if (m > rest || want >= 1e9) m = rest;
             tmp[k++] = m;
             rest -= m;
-            last = last <= (1 << 24) ? last * 6 : last;
+            want *= ratio;
         }
         if (rest > 0) tmp[k++] = rest;
         for (int i = k - 1; i >= 0; --i) sizes[n_chunks++] = tmp[i];          // largest first
     }
-    cudaStream_t c = h->copy_stream;
-    size_t timed_bytes = 0;
     int lo = 0;
     for (int k = 0; k < n_chunks; lo += sizes[k], ++k) {
         const int m = sizes[k];
@@ -2553,14 +2602,9 @@ int bf_forward_host(bf_handle* h, const uint16_t* boards, const int16_t* control
         if (direct) break;
         BF_CUDA(cudaEventRecord(h->chunk_done, s));
         BF_CUDA(cudaStreamWaitEvent(c, h->chunk_done, 0));
-        const size_t M = static_cast<size_t>(m);
         // the first launch's copy is the link measurement (large enough to mean something)
-        const bool timed = k == 0 && policy != nullptr && M * 4096 >= (1u << 20);
-        if (timed) BF_CUDA(cudaEventRecord(h->copy_t0, c));
-        if (policy) BF_CUDA(cudaMemcpyAsync(static_cast<uint8_t*>(policy) + o * 4096, d_policy + o * 4096, M * 4096, cudaMemcpyDeviceToHost, c));
-        if (timed) { BF_CUDA(cudaEventRecord(h->copy_t1, c)); timed_bytes = M * 4096; }
-        if (promo) BF_CUDA(cudaMemcpyAsync(static_cast<uint8_t*>(promo) + o * 256, d_promo + o * 256, M * 256, cudaMemcpyDeviceToHost, c));
-        if (value) BF_CUDA(cudaMemcpyAsync(value + o, d_value + o * 4, M * 4, cudaMemcpyDeviceToHost, c));
+        rc = copy_out(lo, m, k == 0 && policy != nullptr && static_cast<size_t>(m) * 4096 >= (1u << 20));
+        if (rc != BF_OK) return rc;
     }
     BF_CUDA(cudaStreamSynchronize(s));
     BF_CUDA(cudaStreamSynchronize(c));

@@ -238,12 +238,13 @@ int bf_forward_priors_host(bf_handle* h, const uint16_t* boards, const int16_t* 
  *                    1: correctly rounded 1/sqrt, the only form a CPU restatement can
  *                    reproduce bit for bit (the parity tests against the numpy oracle use it). */
 #define BF_OPT_RSQRT_RN 1
-/*   BF_OPT_HOST_PLAN 0 (default): `bf_forward_host` splits a batch into launches by the
- *                    device-to-host rate its previous call measured; 1: always the fast-link
- *                    plan (launches of shrinking size, largest first); 2: always the slow-link
- *                    plan (equal launches of about two waves, the last wave written straight
- *                    into the caller's buffers when they are pinned and device-mapped).  Same
- *                    outputs either way. */
+/*   BF_OPT_HOST_PLAN 0 (default): `bf_forward_host` sizes its launches by the device-to-host
+ *                    rate its previous call measured: each launch as many times the next one as
+ *                    copying a position out is faster than evaluating it (at most six times, a
+ *                    GPU alone on its link), the last one a single wave; when copying is less than
+ *                    1.5 times faster, equal launches of about two waves with the last wave
+ *                    written straight into the caller's buffers (if pinned and device-mapped).
+ *                    1: always the fast-link sizes; 2: always the equal launches.  Same outputs. */
 #define BF_OPT_HOST_PLAN 4
 /*   BF_OPT_ONE_BOARD k (default 1): an int8 evaluation of at most k boards per SM runs in the
  *                    small-batch form of the kernel -- one board per tile, its rows replicated in

@@ -156,14 +156,15 @@ def test_network_is_recognised_by_its_parts_not_its_class(nets):
 
 
 def test_reference_network_packs_to_the_same_blob(states):
-    """Where a checkout of the reference is at hand (``BROKEFISH_REFERENCE``), its own
-    ``BrokefishNet`` -- fp32 and ``.half()`` -- gives the blob bytes this package's container
-    gives for the same state."""
+    """Where a checkout of the reference is at hand (``BROKEFISH_REFERENCE``, else a directory
+    ``reference`` beside this repository), its own ``BrokefishNet`` -- fp32 and ``.half()`` --
+    gives the blob bytes this package's container gives for the same state."""
     import os
     import sys
-    ref = os.environ.get("BROKEFISH_REFERENCE", "")
+    here = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    ref = os.environ.get("BROKEFISH_REFERENCE") or os.path.join(os.path.dirname(here), "reference")
     if not os.path.isdir(os.path.join(ref, "brokefish")):
-        pytest.skip("BROKEFISH_REFERENCE does not point at a checkout of the reference")
+        pytest.skip("no checkout of the reference here (BROKEFISH_REFERENCE)")
     sys.path.insert(0, ref)
     try:
         from brokefish.nn.model import BrokefishNet as RefNet
