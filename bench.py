@@ -606,9 +606,11 @@ def main() -> int:
         "e2e": {"value": e2e, "unit": "positions/s", "h2d_bytes_per_step": n_local * BYTES_IN,
                 "d2h_bytes_per_step": n_local * BYTES_OUT,
                 "host_link_GBps_rank0": enc.host_link_gbps,
-                "plan": "the call splits the batch by the device-to-host rate it measured on its previous "
-                        "call: below 37 GB/s equal two-wave launches with the last wave written straight into "
-                        "the pinned buffers, else launches of shrinking size"},
+                "launch_sizes_rank0": enc.host_plan(n_local),
+                "plan": "the call sizes its launches by the device-to-host rate it measured on its previous "
+                        "call: each launch as many times the next as copying a position is faster than "
+                        "evaluating it (at most 6), the last a single wave; under 1.5 times, equal two-wave "
+                        "launches with the last wave written straight into the pinned buffers"},
         "e2e_fused_expansion": {"value": n_global * e2e_steps / (e2e_pri_ms * 1e-3), "unit": "positions/s",
                                 "what": "the same step through forward_priors_host: legality words in, "
                                         "edge lists (fp16 priors, move labels, counts) and values out",

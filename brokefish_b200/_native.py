@@ -28,7 +28,7 @@ NVCC_FLAGS = ["-gencode", "arch=compute_100a,code=sm_100a", "-O3", "-lineinfo", 
 EXPORTS = ["bf_version", "bf_last_error", "bf_create", "bf_destroy", "bf_info", "bf_forward",
            "bf_forward_stage", "bf_forward_stage_at", "bf_forward_capture", "bf_forward_host", "bf_status",
            "bf_launch_count", "bf_profile", "bf_profile_read", "bf_profile_phases",
-           "bf_forward_noalloc", "bf_noalloc_status", "bf_noalloc_forget", "bf_host_link_gbps", "bf_selftest_umma", "bf_set_option", "bf_measure_i8_peak", "bf_forward_priors",
+           "bf_forward_noalloc", "bf_noalloc_status", "bf_noalloc_forget", "bf_host_link_gbps", "bf_host_plan", "bf_selftest_umma", "bf_set_option", "bf_measure_i8_peak", "bf_forward_priors",
            "bf_forward_priors_host", "bf_selftest_timeout", "bf_movegen", "bf_step", "bf_random_ply",
            "bf_forward_leaves", "bf_measure_elementwise", "bf_forward_backbone", "bf_int8_q_max",
            "bf_fp8_q_max", "bf_terminal", "bf_hash", "bf_history_push",
@@ -118,6 +118,7 @@ def lib() -> ctypes.CDLL:
     L.bf_noalloc_forget.argtypes = [i32]
     L.bf_host_link_gbps.argtypes = [vp]
     L.bf_host_link_gbps.restype = ctypes.c_double
+    L.bf_host_plan.argtypes = [i32, i32, i32, ctypes.c_double, ctypes.POINTER(i32)]
     L.bf_selftest_umma.argtypes = [i32, i32, vp, vp, vp]
     for name in EXPORTS:
         fn = getattr(L, name)

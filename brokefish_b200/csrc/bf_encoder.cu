@@ -2119,6 +2119,42 @@ void* mapped_host(const void* p) {
 constexpr double kEvalGBps = 8.8;        // logits a B200 produces per second at full rate (4356 B x 2.03 M)
 constexpr double kFastLinkRatio = 6.0;   // a GPU alone on its link: 55 GB/s against those 8.8
 
+// The launch sizes of bf_forward_host for `n` positions on a GPU whose wave is `wave` positions:
+// at most 16, in launch order, summing to n.  `gbps` is the measured copy rate (0: not known yet).
+int host_plan_sizes(int n, int wave, int plan, double gbps, int* sizes, bool* slow) {
+    // how many times faster this GPU copies a position out than it evaluates one
+    double ratio = kFastLinkRatio;
+    if (plan == 0 && gbps > 0.0) ratio = gbps / kEvalGBps;
+    if (ratio > kFastLinkRatio) ratio = kFastLinkRatio;
+    const bool slow_link = plan == 2 || ratio < 1.5;
+    int n_chunks = 0;
+    if (slow_link) {
+        const int last = n < wave ? n : wave;
+        const int rest = n - last;
+        if (rest > 0) {
+            int m = (rest + 2 * wave - 1) / (2 * wave);
+            if (m > 14) m = 14;
+            const int piece = ((rest + m - 1) / m + 3) & ~3;
+            for (int left = rest; left > 0; left -= piece) sizes[n_chunks++] = left < piece ? left : piece;
+        }
+        sizes[n_chunks++] = last;
+    } else {
+        int rest = n, tmp[16], k = 0;
+        double want = wave;
+        while (rest > 0 && k < 15) {
+            int m = static_cast<int>(want / wave) * wave;      // whole waves, rounded down: the margin
+            if (m > rest || want >= 1e9) m = rest;
+            tmp[k++] = m;
+            rest -= m;
+            want *= ratio;
+        }
+        if (rest > 0) tmp[k++] = rest;
+        for (int i = k - 1; i >= 0; --i) sizes[n_chunks++] = tmp[i];          // largest first
+    }
+    if (slow != nullptr) *slow = slow_link;
+    return n_chunks;
+}
+
 struct PriorOut {
     void* prior;
     int16_t* move;
@@ -2556,37 +2592,10 @@ int bf_forward_host(bf_handle* h, const uint16_t* boards, const int16_t* control
         if (value) BF_CUDA(cudaMemcpyAsync(value + o, d_value + o * 4, M * 4, cudaMemcpyDeviceToHost, c));
         return BF_OK;
     };
-    // how many times faster this GPU copies a position out than it evaluates one
-    double ratio = kFastLinkRatio;
-    if (h->host_plan == 0 && h->d2h_gbps > 0.0) ratio = h->d2h_gbps / kEvalGBps;
-    if (ratio > kFastLinkRatio) ratio = kFastLinkRatio;
-    const bool slow_link = h->host_plan == 2 || ratio < 1.5;
-    const bool direct_last = slow_link && all_mapped;
     int sizes[16];
-    int n_chunks = 0;
-    if (slow_link) {
-        const int last = n < wave ? n : wave;
-        const int rest = n - last;
-        if (rest > 0) {
-            int m = (rest + 2 * wave - 1) / (2 * wave);
-            if (m > 14) m = 14;
-            const int piece = ((rest + m - 1) / m + 3) & ~3;
-            for (int left = rest; left > 0; left -= piece) sizes[n_chunks++] = left < piece ? left : piece;
-        }
-        sizes[n_chunks++] = last;
-    } else {
-        int rest = n, tmp[16], k = 0;
-        double want = wave;
-        while (rest > 0 && k < 15) {
-            int m = static_cast<int>(want / wave) * wave;      // whole waves, rounded down: the margin
-            if (m > rest || want >= 1e9) m = rest;
-            tmp[k++] = m;
-            rest -= m;
-            want *= ratio;
-        }
-        if (rest > 0) tmp[k++] = rest;
-        for (int i = k - 1; i >= 0; --i) sizes[n_chunks++] = tmp[i];          // largest first
-    }
+    bool slow_link = false;
+    const int n_chunks = host_plan_sizes(n, wave, h->host_plan, h->d2h_gbps, sizes, &slow_link);
+    const bool direct_last = slow_link && all_mapped;
     int lo = 0;
     for (int k = 0; k < n_chunks; lo += sizes[k], ++k) {
         const int m = sizes[k];
@@ -2715,6 +2724,12 @@ int bf_status(bf_handle* h, int* status) {
 long long bf_launch_count(const bf_handle* h) { return h ? h->launches : 0; }
 
 double bf_host_link_gbps(const bf_handle* h) { return h ? h->d2h_gbps : 0.0; }
+
+int bf_host_plan(int n, int sm_count, int plan, double gbps, int* sizes) {
+    if (n < 1 || sm_count < 1 || plan < 0 || plan > 2 || sizes == nullptr)
+        return fail(BF_EINVAL, "bf_host_plan: n and sm_count must be positive, plan 0..2, sizes non-null");
+    return host_plan_sizes(n, sm_count * 4, plan, gbps, sizes, nullptr);
+}
 
 int bf_profile(bf_handle* h, int enable) {
     if (h == nullptr) return fail(BF_EINVAL, "null handle");

@@ -117,6 +117,7 @@ class FusedEncoder:
         self._bb_handle = None
         self._handle = ctypes.c_void_p(0)
         self._exact_rsqrt = False
+        self._host_plan = 0
         self._buffered = 0
         self._buffered_full = 0
         if net is not None:
@@ -152,6 +153,7 @@ class FusedEncoder:
         self.d_model, self.d_ff, self.n_heads, self.d_head = cls.D, cls.DFF, cls.H, 32
         self.net = None
         self._exact_rsqrt = False
+        self._host_plan = 0
         self._buffered = self._buffered_full = 0
         self.device = torch.cuda.current_device() if device is None else int(device)
         L = _native.lib()
@@ -510,11 +512,20 @@ class FusedEncoder:
     # -- how forward_host splits a batch: by the measured host link (0), or forced (1 fast, 2 slow)
     def set_host_plan(self, plan: int) -> None:
         _native.check(_native.lib().bf_set_option(self._handle, 4, int(plan)), "bf_set_option")
+        self._host_plan = int(plan)
 
     @property
     def host_link_gbps(self) -> float:
         """GB/s the first device-to-host copy of the last ``forward_host`` call reached."""
         return float(_native.lib().bf_host_link_gbps(self._handle))
+
+    def host_plan(self, n: int):
+        """The launch sizes ``forward_host`` would use for ``n`` positions now."""
+        sizes = (ctypes.c_int * 16)()
+        sms = torch.cuda.get_device_properties(self.device).multi_processor_count
+        k = _native.lib().bf_host_plan(int(n), sms, self._host_plan, self.host_link_gbps, sizes)
+        _native.check(min(k, 0), "bf_host_plan")
+        return list(sizes[:k])
 
     def check_status(self) -> None:
         """Synchronise and raise if any launch hit a device-side time-out."""

@@ -257,6 +257,12 @@ int bf_set_option(bf_handle* h, int option, int value);
  * first call): what the plan of the next call is chosen by.  No counterpart in the reference. */
 double bf_host_link_gbps(const bf_handle* h);
 
+/* The launch sizes `bf_forward_host` uses for `n` positions on a GPU with `sm_count` SMs under
+ * BF_OPT_HOST_PLAN `plan` when the measured copy rate is `gbps` (0: not measured yet): writes up
+ * to 16 sizes, in launch order, summing to n, and returns how many; no GPU is touched.  No
+ * counterpart in the reference. */
+int bf_host_plan(int n, int sm_count, int plan, double gbps, int* sizes);
+
 /* Read (and clear) the device status word; 0 = every launch since the last call ran
  * clean.  Synchronises the device. */
 int bf_status(bf_handle* h, int* status);

@@ -388,6 +388,7 @@ def test_end_to_end_host_call_matches_device_call(pinned, plan, encoders, pos409
     assert torch.equal(pro.view(torch.int16), dpro.view(torch.int16))
     assert torch.equal(val, dval)
     assert enc.host_link_gbps > 0.0
+    assert sum(enc.host_plan(n)) == n
 
 
 def test_value_head_variants(pos256):
