@@ -2596,7 +2596,9 @@ int bf_forward_host(bf_handle* h, const uint16_t* boards, const int16_t* control
     bool slow_link = false;
     const int n_chunks = host_plan_sizes(n, wave, h->host_plan, h->d2h_gbps, sizes, &slow_link);
     const bool direct_last = slow_link && all_mapped;
-    int lo = 0;
+    int lo = 0, k_timed = 0;
+    for (int k = 1; k < n_chunks; ++k)
+        if (sizes[k] > sizes[k_timed]) k_timed = k;
     for (int k = 0; k < n_chunks; lo += sizes[k], ++k) {
         const int m = sizes[k];
         const size_t o = static_cast<size_t>(lo);
@@ -2611,16 +2613,20 @@ int bf_forward_host(bf_handle* h, const uint16_t* boards, const int16_t* control
         if (direct) break;
         BF_CUDA(cudaEventRecord(h->chunk_done, s));
         BF_CUDA(cudaStreamWaitEvent(c, h->chunk_done, 0));
-        // the first launch's copy is the link measurement (large enough to mean something)
-        rc = copy_out(lo, m, k == 0 && policy != nullptr && static_cast<size_t>(m) * 4096 >= (1u << 20));
+        // the largest launch's copy is the link measurement (large enough to mean something)
+        rc = copy_out(lo, m, k == k_timed && policy != nullptr && static_cast<size_t>(m) * 4096 >= (1u << 20));
         if (rc != BF_OK) return rc;
     }
     BF_CUDA(cudaStreamSynchronize(s));
     BF_CUDA(cudaStreamSynchronize(c));
     if (timed_bytes != 0) {
         float ms = 0.f;
-        if (cudaEventElapsedTime(&ms, h->copy_t0, h->copy_t1) == cudaSuccess && ms > 0.f)
-            h->d2h_gbps = static_cast<double>(timed_bytes) / (ms * 1e-3) / 1e9;
+        if (cudaEventElapsedTime(&ms, h->copy_t0, h->copy_t1) == cudaSuccess && ms > 0.f) {
+            // averaged over the calls: with several GPUs on one link the rate a copy sees depends
+            // on the sizes the other GPUs chose, which depend on the rates they saw
+            const double now = static_cast<double>(timed_bytes) / (ms * 1e-3) / 1e9;
+            h->d2h_gbps = h->d2h_gbps > 0.0 ? 0.5 * (h->d2h_gbps + now) : now;
+        }
         else
             cudaGetLastError();
     }
