@@ -953,7 +953,7 @@ __device__ __forceinline__ float warp_sum_to_all(float v) {
 }
 __device__ __forceinline__ void expand_board(const Params& p, int board, int lane, bool valid, uint32_t word,
                                              int ctl, unsigned long long legal, uint32_t stage_pol,
-                                             uint32_t stage_aux, int row) {
+                                             uint32_t stage_aux, int row, uint8_t* list_buf) {
     // the staged row of this slot: 16-byte group g of the row lives at sw_off(row, g)
     const uint32_t row_smem = stage_pol + static_cast<uint32_t>(row) * 128u;
     const uint32_t row_xor = static_cast<uint32_t>(row & 7);
@@ -1023,17 +1023,33 @@ __device__ __forceinline__ void expand_board(const Params& p, int board, int lan
     const float z = warp_sum_to_all(part);
     const int kept = cut ? e_cap : total;
     if (valid) {
+        // The edge list is put together in shared memory (`list_buf`: 1 KB, priors in the first
+        // half, labels in the second) and leaves in 16-byte stores: the outputs may be pinned host
+        // memory, where every store is a transaction on the bus.
         __half* out_p = p.prior + static_cast<size_t>(board) * e_cap;
         int16_t* out_m = p.move + static_cast<size_t>(board) * e_cap;
+        __half* list_p = reinterpret_cast<__half*>(list_buf);
+        int16_t* list_m = reinterpret_cast<int16_t*>(list_buf + 512);
         tie_rank = tie_rank0;
         int at = first;
         each_candidate(legal, promos, row_smem, row_xor, type_lp, [&](int sq, int t, float lg) {
             if (!stays(lg)) return;
-            out_p[at] = __float2half_rn(__fdiv_rn(expf(__fsub_rn(lg, top)), z));
-            out_m[at] = static_cast<int16_t>((lane * 64 + sq) | (t << 11));
+            list_p[at] = __float2half_rn(__fdiv_rn(expf(__fsub_rn(lg, top)), z));
+            list_m[at] = static_cast<int16_t>((lane * 64 + sq) | (t << 11));
             ++at;
         });
-        for (int i = kept + lane; i < e_cap; i += 32) { out_p[i] = __float2half_rn(0.f); out_m[i] = 0; }
+        for (int i = kept + lane; i < e_cap; i += 32) { list_p[i] = __float2half_rn(0.f); list_m[i] = 0; }
+        __syncwarp();
+        const bool wide = (e_cap & 7) == 0 &&
+                          ((reinterpret_cast<uintptr_t>(out_p) | reinterpret_cast<uintptr_t>(out_m)) & 15u) == 0;
+        if (wide) {
+            for (int i = lane; i < e_cap / 8; i += 32) {
+                reinterpret_cast<uint4*>(out_p)[i] = reinterpret_cast<const uint4*>(list_p)[i];
+                reinterpret_cast<uint4*>(out_m)[i] = reinterpret_cast<const uint4*>(list_m)[i];
+            }
+        } else {
+            for (int i = lane; i < e_cap; i += 32) { out_p[i] = list_p[i]; out_m[i] = list_m[i]; }
+        }
         if (lane == 0) p.nedges[board] = kept;
     }
 }
@@ -1225,7 +1241,10 @@ __device__ __forceinline__ void head_epilogue(RowCtx& c, const Params& p, int bo
         }
         if (c.valid && p.policy != nullptr) store_words<8>(p.policy + c.grow * 64 + 16 * c.qt, lg);
         if (p.prior != nullptr && c.qt == 1) {
-            expand_board(p, board, c.lane, c.valid, word, ctl, moves, stage_pol, stage_aux, c.row);
+            // the list is put together in this board's rows of the staging region's third block,
+            // idle from the head product (which read it) to the next tile's first QKV staging
+            expand_board(p, board, c.lane, c.valid, word, ctl, moves, stage_pol, stage_aux, c.row,
+                         c.smem_gen + (c.sm_r - c.smem) + 32768u + 4096u * c.q);
         }
         if (c.qt == 0) {
             if (c.valid && p.promo != nullptr)
