@@ -2579,8 +2579,8 @@ int bf_forward_host(bf_handle* h, const uint16_t* boards, const int16_t* control
     // The batch goes out as a few launches so that the copy-out of a finished launch overlaps the
     // next launch's compute on a second stream and only the last launch's copy is exposed.  Which
     // plan is best depends on how fast this GPU reaches host memory right now, which the call
-    // measures on its own first copy and remembers for the next call (on this pool: 55 GB/s for
-    // one GPU alone, 12-19 GB/s each when eight GPUs copy at once; evaluating produces 8.8 GB/s).
+    // measures on its largest copy and averages over the calls (measured on 8-GPU B200 boxes: 55 GB/s
+    // for one GPU alone, 12-19 GB/s each when eight GPUs copy at once; evaluating produces 8.8 GB/s).
     // With r = copy rate / evaluation rate:
     //   r >= 1.5    launches of shrinking size, largest first, the last one a single wave (one
     //               tile per SM), each launch r times the one after it (in whole waves, rounded
