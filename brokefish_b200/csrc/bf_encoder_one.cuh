@@ -13,10 +13,10 @@
 // stream, MMA issue and tensor-memory map are those of the four-board kernel; the arithmetic is
 // the same, bit for bit.
 //
-// Exchanges are sixteen-way, across the CTA's row warps (named barrier 5, 512 threads).  The 12
-// pieces of a QKV unit's 192 outputs go to the first twelve threads of a row; the board's four
-// attention units per head pair, the read-back and quantisation of the attention output and the
-// head epilogue run on quadrant 0's four warps with the four-board kernel's own code.
+// Exchanges are sixteen-way, across the CTA's row warps (named barrier 5, 512 threads).  Attention
+// is split by head pair: quadrant j drains QKV unit j from its own copy of the accumulator and runs
+// pair j's four attention units on its own rows of the staging blocks with the four-board kernel's
+// own code, the four pairs side by side; the head epilogue runs on quadrant 0's four warps.
 #pragma once
 
 namespace bf {
@@ -166,54 +166,55 @@ __device__ __forceinline__ float ln_stage(RowCtx& c, const Params& p) {
 
 __device__ __forceinline__ void attention_block(RowCtx& c, const Params& p, const LayerParams& lp, float sa,
                                                 uint32_t alive) {
-    const int t16 = thread16(c);
-    float o_amax = 0.f;
+    // Head pair j is quadrant j's: its four warps drain QKV unit j from their own copy of the
+    // accumulator (48 of the 192 columns each, as a board's four warps do in the four-board
+    // kernel), stage Q, K and V in their own 32 rows of the staging blocks and run the pair's four
+    // attention units there, all four pairs side by side.  The other quadrants only account for a
+    // unit: they wait for it and hand the accumulator back (the barrier counts sixteen warps, and
+    // an arrival must fall into its own unit's phase).
+    const int j = c.q;
 #pragma unroll 1
-    for (int j = 0; j < 4; ++j) {
+    for (int u = 0; u < 4; ++u) {
         row_wait_acc<false>(c, 0, PH_LN);
-        if (t16 < 12) {
-            // piece t16 of the unit's twelve 16-column pieces
-            uint32_t acc[16], h[8];
-            const int c0 = 16 * t16, m = c0 >> 6, cm = c0 & 63;
-            tmem_ld16(c.tm + TM_ACC + c0, acc);
-            tmem_wait_ld();
-            descale<16, false, kAccInt>(acc, sa, __ldg(lp.sw_qkv + m * 2 + (j >> 1)), lp.b_qkv + j * 192 + c0, h);
+        if (u != j) {
+            row_release_acc(c, 0);
+            continue;
+        }
+        // all 48 columns are fetched at once and the accumulator goes back before they are worked
+        // on: the next unit's product runs under this one's descale
+        uint32_t acc[3][16];
+        tmem_ld16(c.tm + TM_ACC + 48 * c.qt, acc[0]);
+        tmem_ld16(c.tm + TM_ACC + 48 * c.qt + 16, acc[1]);
+        tmem_ld16(c.tm + TM_ACC + 48 * c.qt + 32, acc[2]);
+        row_release_acc(c, 0);             // waits for the loads
+#pragma unroll
+        for (int g = 0; g < 3; ++g) {
+            const int c0 = 48 * c.qt + 16 * g, m = c0 >> 6, cm = c0 & 63;
+            uint32_t h[8];
+            descale<16, false, kAccInt>(acc[g], sa, __ldg(lp.sw_qkv + m * 2 + (j >> 1)), lp.b_qkv + j * 192 + c0, h);
 #pragma unroll
             for (int k = 0; k < 2; ++k)
-                sts128(c.sm_r + m * 16384 + sw_off(c.lane, (cm >> 3) + k),
+                sts128(c.sm_r + m * 16384 + sw_off(c.row, (cm >> 3) + k),
                        make_uint4(h[4 * k], h[4 * k + 1], h[4 * k + 2], h[4 * k + 3]));
         }
-        row_release_acc(c, 0);
-        rows_sync();                       // the board's Q/K/V rows are staged
-        if (c.q == 0) attention_unit(c, alive);
-        rows_sync();                       // the outputs are in the output block
-        if (c.q == 0) {
-            uint32_t oh[8];
-#pragma unroll
-            for (int k = 0; k < 2; ++k) {
-                const uint4 v = lds128(c.sm_r + 49152 + sw_off(c.lane, 2 * c.qt + k));
-                oh[4 * k] = v.x; oh[4 * k + 1] = v.y; oh[4 * k + 2] = v.z; oh[4 * k + 3] = v.w;
-            }
-            o_amax = fmaxf(o_amax, amax_h2<8>(oh, true));
-            tmem_st8(c.tm + TM_OY + 32 * j + 8 * c.qt, oh);
-        }
     }
-    tmem_wait_st();
+    board_sync(c);                         // this pair's Q/K/V rows are staged
+    attention_unit(c, alive);
+    board_sync(c);                         // the pair's outputs are in the output block
     {
-        // the attention output becomes the s8 A operand of the out-projection (quadrant 0's
-        // threads hold it; the row maximum goes through the sixteen-way exchange)
-        const float amax = exchange_max16(c, o_amax);
-        sa = amax > 0.f ? __fdiv_rn(amax, kQMaxS8) : 1.0f;
-        if (c.q == 0) {
-            const float inv = __fdiv_rn(1.0f, sa);
-            uint32_t oh[4][8];
+        // this thread's 16 of the row's 256 attention outputs: columns 64 j + 16 qt .. +15.  The row
+        // maximum goes through the sixteen-way exchange, the quantised piece into all four row
+        // copies of the out-projection's A operand.
+        uint32_t oh[8];
 #pragma unroll
-            for (int j = 0; j < 4; ++j) tmem_ld8(c.tm + TM_OY + 32 * j + 8 * c.qt, oh[j]);
-            tmem_wait_ld();
-#pragma unroll
-            for (int j = 0; j < 4; ++j)
-                store_copies(c.sm_a + (j >> 1) * 16384, c.lane, 4 * (j & 1) + c.qt, quant16(oh[j], inv, c.one2));
+        for (int k = 0; k < 2; ++k) {
+            const uint4 v = lds128(c.sm_r + 49152 + sw_off(c.row, 2 * c.qt + k));
+            oh[4 * k] = v.x; oh[4 * k + 1] = v.y; oh[4 * k + 2] = v.z; oh[4 * k + 3] = v.w;
         }
+        const float amax = exchange_max16(c, amax_h2<8>(oh, true));
+        sa = amax > 0.f ? __fdiv_rn(amax, kQMaxS8) : 1.0f;
+        const float inv = __fdiv_rn(1.0f, sa);
+        store_copies(c.sm_a + (j >> 1) * 16384, c.lane, 4 * (j & 1) + c.qt, quant16(oh, inv, c.one2));
         row_publish(c, B_A_READY);
     }
     // out-projection: this thread's piece of slot q >> 1
