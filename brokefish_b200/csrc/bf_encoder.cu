@@ -1660,9 +1660,12 @@ __device__ __forceinline__ void mma_loop(uint32_t smem, uint32_t tmem, volatile 
 }
 
 // ------------------------------------------------------------------------------------------
-// `kOne`: the small-batch form, one board per tile with its rows replicated in the four lane
-// quadrants (bf_encoder_one.cuh); plain int8 evaluation only.
-template <bool kDbg, bool kRJ, int kAr, bool kOne = false>
+// `kForm`: 0 = four boards per tile; 1 = the small-batch form, one board per tile with its rows
+// replicated in the four lane quadrants (bf_encoder_one.cuh; plain int8 evaluation only); 2 = chosen
+// when the kernel starts, by the number of positions it finds (a leaf list's length is only known
+// on the device): one board per tile if every board gets a CTA of its own, else four.
+enum { kFormFour = 0, kFormOne = 1, kFormByCount = 2 };
+template <bool kDbg, bool kRJ, int kAr, int kForm = kFormFour>
 __global__ void __launch_bounds__(kThreads, 1) encoder_kernel(const Params p) {
     extern __shared__ uint8_t smem_raw[];
     uint8_t* sm = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
@@ -1695,7 +1698,8 @@ __global__ void __launch_bounds__(kThreads, 1) encoder_kernel(const Params p) {
     // (clamped to the capacity the grid was sized for); every role reads the same word
     int n_eval = p.n;
     if (p.leaf_count != nullptr) n_eval = min(max(__ldg(p.leaf_count), 0), p.n);
-    const int n_tiles = kOne ? n_eval : (n_eval + 3) / 4;
+    const bool one = kForm == kFormOne || (kForm == kFormByCount && n_eval <= static_cast<int>(gridDim.x));
+    const int n_tiles = one ? n_eval : (n_eval + 3) / 4;
     if (warp < kRowWarps) {
         RowCtx c;
         c.n = n_eval;
@@ -1708,12 +1712,16 @@ __global__ void __launch_bounds__(kThreads, 1) encoder_kernel(const Params p) {
         c.prof_on = kDbg && p.prof != nullptr && threadIdx.x == 0;
         c.t_last = c.prof_on ? clock64() : 0;
         for (int tile = blockIdx.x; tile < n_tiles; tile += gridDim.x) {
-            if constexpr (kOne)
-                one::row_warps_tile(c, p, tile, [&](RowCtx& cc, int board, uint32_t word, int ctl, uint32_t alive) {
-                    head_epilogue<false>(cc, p, board, word, ctl, alive);
-                });
-            else
+            if constexpr (kForm == kFormFour) {
                 row_warps_tile<kDbg, kRJ, kAr>(c, p, tile);
+            } else {
+                if (one)
+                    one::row_warps_tile(c, p, tile, [&](RowCtx& cc, int board, uint32_t word, int ctl, uint32_t alive) {
+                        head_epilogue<false>(cc, p, board, word, ctl, alive);
+                    });
+                else
+                    row_warps_tile<kDbg, kRJ, kAr>(c, p, tile);
+            }
         }
     } else if (warp == kProducerWarp) {
         if (lane == 0) producer_loop<kAr>(smem, abort_flag, p, blockIdx.x, gridDim.x, n_tiles);
@@ -2252,11 +2260,16 @@ int launch(bf_handle* h, const uint16_t* boards, const int16_t* control, const u
     } else {
         // a batch that leaves SMs idle (at most one board per SM) runs in the one-board-per-tile
         // form: sixteen row warps per board instead of four, about half the latency, same bits
-        const bool one = !dbg && bb == nullptr && p.vmode != 2 && n <= h->sm_count * h->one_board_factor;
+        const bool small_form = !dbg && bb == nullptr && p.vmode != 2 && h->one_board_factor > 0;
+        const bool one = small_form && n <= h->sm_count * h->one_board_factor;
+        const int grid_one = n < h->sm_count ? n : h->sm_count;
         if (dbg) bf::encoder_kernel<true, false, bf::kArInt8><<<grid, bf::kThreads, bf::kSmemRequest, stream>>>(p);
         else if (one)
-            bf::encoder_kernel<false, false, bf::kArInt8, true><<<n < h->sm_count ? n : h->sm_count, bf::kThreads,
-                                                                  bf::kSmemRequest, stream>>>(p);
+            bf::encoder_kernel<false, false, bf::kArInt8, bf::kFormOne><<<grid_one, bf::kThreads, bf::kSmemRequest, stream>>>(p);
+        else if (small_form && leaves != nullptr)
+            // a leaf list may turn out short: one CTA per SM, and the kernel picks the form by the
+            // count it reads
+            bf::encoder_kernel<false, false, bf::kArInt8, bf::kFormByCount><<<grid_one, bf::kThreads, bf::kSmemRequest, stream>>>(p);
         else     bf::encoder_kernel<false, false, bf::kArInt8><<<grid, bf::kThreads, bf::kSmemRequest, stream>>>(p);
     }
     BF_CUDA(cudaGetLastError());
@@ -2339,7 +2352,10 @@ int bf_create(const void* blob, size_t blob_bytes, int device, bf_handle** out) 
     for (int i = 0; i < 14 && e == cudaSuccess; ++i)
         e = cudaFuncSetAttribute(kernels[i], cudaFuncAttributeMaxDynamicSharedMemorySize, bf::kSmemRequest);
     if (e == cudaSuccess)
-        e = cudaFuncSetAttribute(bf::encoder_kernel<false, false, bf::kArInt8, true>,
+        e = cudaFuncSetAttribute(bf::encoder_kernel<false, false, bf::kArInt8, bf::kFormOne>,
+                                 cudaFuncAttributeMaxDynamicSharedMemorySize, bf::kSmemRequest);
+    if (e == cudaSuccess)
+        e = cudaFuncSetAttribute(bf::encoder_kernel<false, false, bf::kArInt8, bf::kFormByCount>,
                                  cudaFuncAttributeMaxDynamicSharedMemorySize, bf::kSmemRequest);
     if (e != cudaSuccess) {
         bf_destroy(h);

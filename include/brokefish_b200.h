@@ -101,7 +101,8 @@ int bf_forward_priors(bf_handle* h, const uint16_t* boards, const int16_t* contr
  * (`boards`, `control`, `rep`, `legal` indexed by place), the count read ON THE DEVICE when the
  * kernel starts, so the caller needs no host synchronisation to know it.  `capacity` is the most
  * the list can hold (the grid is sized for it; a larger count is clamped, a negative one is 0);
- * CTAs beyond the count's tiles leave at once, so a short list runs short.  Every output is
+ * CTAs beyond the count's tiles leave at once, so a short list runs short, and an int8 list of at
+ * most one position per SM runs in the small-batch form (BF_OPT_ONE_BOARD).  Every output is
  * written at the position's own place in the staged arrays (policy [place,32,64], value [place],
  * prior [place,e_cap] ...); places not in the list are not touched.  Any of policy / promo /
  * value may be NULL; pass prior, move and nedges (all three, else all NULL) for the fused
