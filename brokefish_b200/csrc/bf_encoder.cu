@@ -1474,24 +1474,30 @@ enum { kKindI8 = 0, kKindF16 = 1, kKindF8 = 2 };
 template <int kAr>
 __device__ __forceinline__ void mma_unit(uint32_t smem, volatile int* abort_flag, MmaState& st,
                                          uint32_t tmem_d, int slot, uint32_t a_base, bool qring,
-                                         int n_stages, uint32_t idesc, int kind) {
+                                         int n_stages, uint32_t idesc, int kind, bool pre = false) {
     using C = Cfg<kAr>;
-    mbar_wait(bar_addr(smem, B_ACC_EMPTY + slot), (st.accn[slot] - 1u) & 1u, abort_flag, kErrMmaAcc);
-    tc_fence_after();
+    // `pre`: mma_prewait has already seen the slot free and the first weight stage in place
+    // (the fences that order the MMAs after what those waits saw: after a pre-wait it is the
+    // operand wait's own fence, which comes later than both)
+    if (!pre) {
+        mbar_wait(bar_addr(smem, B_ACC_EMPTY + slot), (st.accn[slot] - 1u) & 1u, abort_flag, kErrMmaAcc);
+        tc_fence_after();
+    }
     for (int s = 0; s < n_stages; ++s) {
         uint32_t w_empty, w_addr;
+        const bool seen = pre && s == 0;
         if (qring) {
             const uint32_t k = st.qc % C::kQSlots;
-            mbar_wait(bar_addr(smem, B_WQ_FULL + k), (st.qc / C::kQSlots) & 1u, abort_flag, kErrMmaWeights);
+            if (!seen) mbar_wait(bar_addr(smem, B_WQ_FULL + k), (st.qc / C::kQSlots) & 1u, abort_flag, kErrMmaWeights);
             w_empty = bar_addr(smem, B_WQ_EMPTY + k); w_addr = smem + C::SM_RING + k * kQStage;
             st.qc++;
         } else {
             const uint32_t k = st.rc % C::kRSlots;
-            mbar_wait(bar_addr(smem, B_WR_FULL + k), (st.rc / C::kRSlots) & 1u, abort_flag, kErrMmaWeights);
+            if (!seen) mbar_wait(bar_addr(smem, B_WR_FULL + k), (st.rc / C::kRSlots) & 1u, abort_flag, kErrMmaWeights);
             w_empty = bar_addr(smem, B_WR_EMPTY + k); w_addr = smem + C::SM_RING + k * kRStage;
             st.rc++;
         }
-        tc_fence_after();
+        if (!seen) tc_fence_after();
         const uint64_t ad = umma_desc_k128(a_base + s * 16384), bd = umma_desc_k128(w_addr);
 #pragma unroll
         for (int k = 0; k < 4; ++k) {
@@ -1504,6 +1510,24 @@ __device__ __forceinline__ void mma_unit(uint32_t smem, volatile int* abort_flag
     }
     tc_commit(bar_addr(smem, B_ACC_FULL + slot));
     st.accn[slot]++;
+}
+
+// What a unit needs besides its A operand -- its accumulator slot handed back, its first weight
+// stage in place -- waited for BEFORE the issuer blocks on the operand barrier: both come from
+// work that is long done by then, and a wait costs a shared-memory round trip even when it
+// succeeds at once, which would otherwise sit between the operand's arrival and the first MMA.
+template <int kAr>
+__device__ __forceinline__ void mma_prewait(uint32_t smem, volatile int* abort_flag, const MmaState& st,
+                                            int slot, bool qring) {
+    using C = Cfg<kAr>;
+    mbar_wait(bar_addr(smem, B_ACC_EMPTY + slot), (st.accn[slot] - 1u) & 1u, abort_flag, kErrMmaAcc);
+    if (qring) {
+        const uint32_t k = st.qc % C::kQSlots;
+        mbar_wait(bar_addr(smem, B_WQ_FULL + k), (st.qc / C::kQSlots) & 1u, abort_flag, kErrMmaWeights);
+    } else {
+        const uint32_t k = st.rc % C::kRSlots;
+        mbar_wait(bar_addr(smem, B_WR_FULL + k), (st.rc / C::kRSlots) & 1u, abort_flag, kErrMmaWeights);
+    }
 }
 
 __device__ __forceinline__ void mma_wait_operand(uint32_t smem, volatile int* abort_flag, int bar_idx,
@@ -1565,15 +1589,27 @@ __device__ __forceinline__ void mma_loop(uint32_t smem, uint32_t tmem, volatile 
     (void)kHalfA;
     for (int tile = first_tile; tile < n_tiles; tile += tile_step) {
         for (int layer = 0; layer < p.n_layers; ++layer) {
+            if (who == 0) mma_prewait<kAr>(smem, abort_flag, st, 0, true);
             mma_wait_operand(smem, abort_flag, B_A_READY, st.aready);          // LN1 output
             if (who == 0)
                 for (int j = 0; j < 4; ++j)
-                    mma_unit<kAr>(smem, abort_flag, st, acc0, 0, sm_a, true, C::kQkvSlabs, kI_QKV, kQkvKind);
+                    mma_unit<kAr>(smem, abort_flag, st, acc0, 0, sm_a, true, C::kQkvSlabs, kI_QKV, kQkvKind, j == 0);
+            if (who == 1) mma_pass_over<kAr>(smem, abort_flag, st, C::kOutSlabs);
+            mma_prewait<kAr>(smem, abort_flag, st, who, false);
             mma_wait_operand(smem, abort_flag, B_A_READY, st.aready);          // attention output
-            if (who == 0) mma_unit<kAr>(smem, abort_flag, st, acc0, 0, sm_a, false, C::kOutSlabs, kI_OUT, kOutKind);
-            else                   mma_pass_over<kAr>(smem, abort_flag, st, C::kOutSlabs);
-            if (who == 1) mma_unit<kAr>(smem, abort_flag, st, acc1, 1, sm_a, false, C::kOutSlabs, kI_OUT, kOutKind);
-            else                   mma_pass_over<kAr>(smem, abort_flag, st, C::kOutSlabs);
+            if (who == 0) {
+                mma_unit<kAr>(smem, abort_flag, st, acc0, 0, sm_a, false, C::kOutSlabs, kI_OUT, kOutKind, true);
+                mma_pass_over<kAr>(smem, abort_flag, st, C::kOutSlabs);
+            } else {
+                mma_unit<kAr>(smem, abort_flag, st, acc1, 1, sm_a, false, C::kOutSlabs, kI_OUT, kOutKind, true);
+            }
+            // the FFN's first unit of this issuer (every arithmetic: ff1, chunk 0, half `who`)
+            bool ffn_pre = false;
+            if constexpr (kAr != kArF16) {
+                if (who == 1) mma_pass_over<kAr>(smem, abort_flag, st, 2);
+                mma_prewait<kAr>(smem, abort_flag, st, who, false);
+                ffn_pre = true;
+            }
             mma_wait_operand(smem, abort_flag, B_A_READY, st.aready);          // LN2 output
             if constexpr (kAr == kArF16) {
                 // fp16 FFN: ff1 units go into slot 0; once the rows have written a hidden chunk,
@@ -1634,15 +1670,20 @@ __device__ __forceinline__ void mma_loop(uint32_t smem, uint32_t tmem, volatile 
             for (int u = 0; u < 16; ++u) {
                 // kind/chunk of unit u: pairs (u>>1): F1 0, F1 1, F2 0, F1 2, F2 1, F1 3, F2 2, F2 3
                 const int pr = u >> 1, jh = u & 1;
-                if (jh != who) { mma_pass_over<kAr>(smem, abort_flag, st, 2); continue; }   // the other issuer's unit
+                if (jh != who) {                                          // the other issuer's unit
+                    if (!(u == 0 && ffn_pre)) mma_pass_over<kAr>(smem, abort_flag, st, 2);   // (unit 0: passed above)
+                    continue;
+                }
                 const int kind2 = (0xD4 >> pr) & 1;                       // 0b11010100
                 const int ch = kind2 ? ((0x32010000u >> (4 * pr)) & 0xF) : ((0x00302010u >> (4 * pr)) & 0xF);
                 if (kind2) {
+                    mma_prewait<kAr>(smem, abort_flag, st, jh, false);
                     mma_wait_operand(smem, abort_flag, B_A2_READY + (ch & 1), st.a2n[ch & 1]);
                     mma_unit<kAr>(smem, abort_flag, st, jh ? acc1 : acc0, jh, sm_r + (ch & 1) * 32768,
-                                   false, 2, kI_FF2, kFfnKind);
+                                   false, 2, kI_FF2, kFfnKind, true);
                 } else {
-                    mma_unit<kAr>(smem, abort_flag, st, jh ? acc1 : acc0, jh, sm_a, false, 2, kI_FF1, kFfnKind);
+                    mma_unit<kAr>(smem, abort_flag, st, jh ? acc1 : acc0, jh, sm_a, false, 2, kI_FF1, kFfnKind,
+                                   pr == 0 && ffn_pre);
                 }
             }
             }
@@ -1650,10 +1691,11 @@ __device__ __forceinline__ void mma_loop(uint32_t smem, uint32_t tmem, volatile 
         // heads: [128 x 256] x [96 x 256]^T in fp16 with fp16 accumulators, sixteen steps of
         // sixteen in rising order -- the bits of the reference's fp16-accumulate mma.sync head
         // product (encoder.cu:309-352, 918-927); A is the final norm's output in the staging region
+        if (who == 0) mma_prewait<kAr>(smem, abort_flag, st, 0, false);
         mma_wait_operand(smem, abort_flag, B_A_READY, st.aready);
         if (who == 0)
             mma_unit<kAr>(smem, abort_flag, st, acc0, 0, sm_r, false, kHeadStages,
-                          umma_idesc(kAccF16, kFmtF16, kFmtF16, 128, 96), kKindF16);
+                          umma_idesc(kAccF16, kFmtF16, kFmtF16, 128, 96), kKindF16, true);
         else
             mma_pass_over<kAr>(smem, abort_flag, st, kHeadStages);
     }
