@@ -1366,6 +1366,17 @@ __device__ __forceinline__ void row_warps_tile(RowCtx& c, const Params& p, int t
         const bool dbgl = layer == p.debug_layer;
         const bool dump_x = (dbg == 9 && ph == 0) || (dbg == 2 && odd && dbgl) ||
                             (dbg == 10 && !odd && ph > 0 && layer - 1 == p.debug_layer);
+        // This half-layer's scales and biases (the final norm's affine and value rows at the end)
+        // are asked into L1 now, a norm ahead of their first use: the eight layers' 37 KB do not
+        // stay there from one tile to the next beside 228 KB of shared memory.
+        {
+            const int t = 32 * (c.q + 4 * c.qt) + c.lane;
+            if (ph == n_ph) {
+                if (t < static_cast<int>(kTailBytes / 128)) prefetch_l1(reinterpret_cast<const uint8_t*>(p.tail) + 128 * t);
+            } else if (t < kLparamStride / 128) {
+                prefetch_l1(p.lparams + static_cast<size_t>(layer) * kLparamStride + 128 * t);
+            }
+        }
         if (ph == n_ph) {
             ln_stage<kDbg, kRJ, kAr>(c, p, true, dump_x, dbg == 8, false, -1);
             row_publish(c, B_A_READY);                   // the head product's A operand

@@ -62,6 +62,11 @@ __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity,
     return mbar_wait_slow(bar, parity, abort_flag, code);
 }
 
+// Ask a 128-byte line of global memory into L1 (no register, no wait).
+__device__ __forceinline__ void prefetch_l1(const void* p) {
+    asm volatile("prefetch.global.L1 [%0];" ::"l"(p));
+}
+
 // ---------------------------------------------------------------- shared-space loads / stores
 // Taking the 32-bit shared address keeps these in the shared window (no generic addressing).
 __device__ __forceinline__ void sts128(uint32_t addr, uint4 v) {
